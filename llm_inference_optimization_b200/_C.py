@@ -1,0 +1,74 @@
+"""Drop-in for the reference's ``sparse_kv._C`` extension module.
+
+Same function names, argument order, tensor layouts and error type
+(``RuntimeError``) as the pybind module defined in the reference's
+``csrc/pybind/bindings.cpp:19-31``; the work is done by the sm_100a kernels
+behind the C-ABI of ``include/skv_b200.h``.  Arguments the reference does not
+have are keyword-only, so every reference call site runs unchanged.
+"""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from . import _lib, _workspace
+
+
+def _dev_index(t: Tensor) -> int:
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _kv_strides(K: Tensor, V: Tensor, what: str) -> tuple[int, int, int]:
+    _require(K.stride(-1) == 1 and V.stride(-1) == 1, f"{what}: the channel dimension of K/V must be contiguous")
+    _require(K.stride() == V.stride(), f"{what}: K and V must share one memory layout")
+    return K.stride(0), K.stride(1), K.stride(2)
+
+
+def fused_gqa(Q: Tensor, K: Tensor, V: Tensor, scale: float, *, seq_lens: Tensor | None = None,
+              out: Tensor | None = None) -> Tensor:
+    """Dense GQA decode attention; reference: ``launch_fused_gqa`` (csrc/kernels/gqa_decode.cu:218-290).
+
+    Q ``[B, Hq, D]`` fp16, K/V ``[B, N, Hkv, D]`` fp16, returns ``[B, Hq, D]`` fp16 with
+    ``Out[b,h] = softmax(scale * Q[b,h] K[b,:,h // (Hq/Hkv)]^T) V[b,:,h // (Hq/Hkv)]``.
+    Unlike the reference, K/V may be any strided view with a contiguous channel
+    dimension (for example ``cache.permute(0, 2, 1, 3)`` of a ``[B, Hkv, N, D]``
+    cache), D may be 64 or 128, the launch goes to the current stream of Q's
+    device, and ``seq_lens`` (int32 ``[B]``) bounds the tokens read per sequence.
+    """
+    _require(Q.is_cuda and K.is_cuda and V.is_cuda, "Q/K/V must be CUDA tensors")
+    _require(Q.dtype == torch.float16 and K.dtype == torch.float16 and V.dtype == torch.float16,
+             "all inputs must be fp16")
+    _require(Q.dim() == 3 and K.dim() == 4 and V.dim() == 4, "expected Q [B,Hq,D] and K/V [B,N,Hkv,D]")
+    _require(Q.is_contiguous(), "Q must be contiguous")
+    B, Hq, D = Q.shape
+    N, Hkv = K.shape[1], K.shape[2]
+    _require(K.shape[0] == B and V.shape[0] == B, "batch size mismatch across Q/K/V")
+    _require(K.shape[3] == D and V.shape[3] == D, f"K/V head_dim must match Q head_dim={D}")
+    _require(V.shape[1] == N and V.shape[2] == Hkv, "V shape must be [B, N, Hkv, D] matching K")
+    _require(Hkv > 0 and Hq % Hkv == 0, f"Hq={Hq} must be divisible by Hkv={Hkv}")
+    _require(K.device == Q.device and V.device == Q.device, "Q/K/V must be on one device")
+    sb, sn, sh = _kv_strides(K, V, "fused_gqa")
+    dev = _dev_index(Q)
+    lib = _lib.load()
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=torch.float16, device=Q.device)
+    else:
+        _require(out.shape == (B, Hq, D) and out.dtype == torch.float16 and out.is_contiguous()
+                 and out.device == Q.device, "out must be a contiguous fp16 [B,Hq,D] tensor on Q's device")
+    lens_ptr = None
+    if seq_lens is not None:
+        _require(seq_lens.dtype == torch.int32 and seq_lens.shape == (B,) and seq_lens.device == Q.device
+                 and seq_lens.is_contiguous(), "seq_lens must be a contiguous int32 [B] tensor on Q's device")
+        lens_ptr = seq_lens.data_ptr()
+    nbytes = lib.skv_gqa_decode_workspace_bytes(B, N, Hq, Hkv, D, dev)
+    ws = _workspace.get("gqa", nbytes, Q.device)
+    stream = torch.cuda.current_stream(Q.device).cuda_stream
+    rc = lib.skv_gqa_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(),
+                            B, N, Hq, Hkv, D, _lib.KV_F16, None, None, sb, sn, sh, lens_ptr, float(scale), dev, stream)
+    _lib.check(rc, "fused_gqa")
+    return out

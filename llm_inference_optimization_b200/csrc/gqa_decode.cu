@@ -1,0 +1,525 @@
+// Dense grouped-query decode attention for one new token per sequence, split
+// over the KV length so that every SM streams a share of the cache, with the
+// log-sum-exp combine done by the last CTA to finish each (batch, kv-head).
+//
+// Replaces gqa_decode_kernel / launch_fused_gqa of the reference
+// (csrc/kernels/gqa_decode.cu:84-215, :218-290), which runs one CTA per query
+// head (re-reading the KV of a group once per query head) with no KV split.
+//
+//   Out[b, hq, :] = softmax(scale * Q[b, hq, :] . K[b, :, hq / G, :]^T) . V[b, :, hq / G, :]
+//
+// Mapping to the hardware:
+//   * grid (Hkv, splits, B): a CTA owns one kv-head of one sequence over a
+//     contiguous token range and serves all G = Hq / Hkv query heads of the
+//     group, so each K/V byte is read from HBM exactly once.
+//   * one producer warp issues TMA tile loads (cp.async.bulk.tensor, 128-byte
+//     swizzle, L2 evict-first) into a ring of shared-memory stages guarded by
+//     full/empty mbarriers; four consumer warps each take 16 tokens of every
+//     64-token stage.
+//   * the group x tile products run on the tensor cores as mma.sync m16n8k16
+//     with the query group on the M dimension (rows >= G are zero padding):
+//     S = Q K^T with K fragments read by ldmatrix, P V with V fragments read by
+//     ldmatrix.trans.  Softmax is online, fp32, in the exp2 domain.
+//   * every warp keeps its own (max, sum, O) state; warps are merged through
+//     shared memory, splits through an fp32 workspace and an atomic ticket.
+//   * every mbarrier wait is bounded; a wait that runs out sets a bit in the
+//     workspace status word instead of hanging.
+#include "skv_common.cuh"
+#include "skv_tmap.cuh"
+
+namespace skv {
+namespace gqa {
+
+constexpr int TILE = 64;            // tokens per pipeline stage
+constexpr int CONSUMER_WARPS = 4;   // each takes TILE / 4 = 16 tokens of a stage
+constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
+constexpr int THREADS = CONSUMER_THREADS + 32;
+constexpr int MAX_SPLITS = 512;
+constexpr int MAX_GROUP = 16;       // query heads per kv head (rows of one MMA tile)
+
+struct Params {
+    const __half* q;
+    __half* out;
+    float* partial_o;    // [B, Hkv, S, G, D]
+    float* partial_ml;   // [B, Hkv, S, G, 2]  (running max in the exp2 domain, running sum)
+    int* tickets;        // [B * Hkv], zero between launches
+    int* status;         // device status word
+    const int* seq_lens; // [B] or null
+    int N, Hq, Hkv, G;
+    int tiles_per_split, num_splits, stages;
+    long long q_stride_b, q_stride_h, o_stride_b, o_stride_h;
+    float scale_log2;    // softmax scale * log2(e)
+    KvMapPos pos;
+};
+
+template <int D>
+struct Smem {
+    static constexpr int NH = D / 64;                 // 128-byte halves per row
+    static constexpr int HALF_BYTES = TILE * 128;     // one [TILE][64] fp16 block
+    static constexpr int KV_BYTES = NH * HALF_BYTES;  // K (or V) part of a stage
+    static constexpr int STAGE_BYTES = 2 * KV_BYTES;
+    static size_t bytes(int stages) {
+        size_t ring = (size_t)stages * STAGE_BYTES;
+        size_t merge = (size_t)CONSUMER_WARPS * MAX_GROUP * D * 4 + CONSUMER_WARPS * MAX_GROUP * 8 +
+                       (size_t)CONSUMER_WARPS * MAX_SPLITS * 4;
+        size_t body = ring > merge ? ring : merge;
+        return 1024 /*alignment slack*/ + body + 2 * stages * 8 + 16;
+    }
+};
+
+__device__ __forceinline__ void kv_tile_load(uint32_t dst, const CUtensorMap* tm, uint32_t bar, const KvMapPos& pos,
+                                             int half, int tok, int head, int batch, uint64_t policy) {
+    int c[5] = {0, 0, 0, 0, 0};
+#pragma unroll
+    for (int i = 1; i < 5; ++i)
+        c[i] = (i == pos.half) ? half : (i == pos.tok) ? tok : (i == pos.head) ? head : batch;
+    tma_load_5d(dst, tm, bar, c[0], c[1], c[2], c[3], c[4], policy);
+}
+
+template <int D>
+__global__ void __launch_bounds__(THREADS, 1)
+gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                      const Params p) {
+    using S = Smem<D>;
+    constexpr int KSTEPS = D / 16;  // MMA k-steps across the head dimension
+    constexpr int NT_O = D / 8;     // 8-channel output tiles
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+
+    const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
+    const int tokens_per_split = p.tiles_per_split * TILE;
+    const int n_splits = len > 0 ? (len + tokens_per_split - 1) / tokens_per_split : 1;
+    if (split >= n_splits) return;
+    const int t_begin = split * tokens_per_split;
+    const int t_end = min(len, t_begin + tokens_per_split);
+    const int ntiles = (t_end - t_begin + TILE - 1) / TILE;  // 0 for an empty sequence
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t ring = smem_u32(smem);
+    size_t body = (size_t)p.stages * S::STAGE_BYTES;
+    {
+        size_t merge = (size_t)CONSUMER_WARPS * MAX_GROUP * D * 4 + CONSUMER_WARPS * MAX_GROUP * 8 +
+                       (size_t)CONSUMER_WARPS * MAX_SPLITS * 4;
+        if (merge > body) body = merge;
+    }
+    const uint32_t full_bar = ring + (uint32_t)body;
+    const uint32_t empty_bar = full_bar + p.stages * 8;
+    int* last_flag = reinterpret_cast<int*>(smem + body + 2 * p.stages * 8);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full_bar + s * 8, 1);
+            mbar_init(empty_bar + s * 8, CONSUMER_WARPS);
+        }
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    // ------------------------------------------------------------------ producer
+    if (warp == CONSUMER_WARPS) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tmK);
+            tma_prefetch_desc(&tmV);
+            const uint64_t policy = l2_policy_evict_first();
+            for (int it = 0; it < ntiles; ++it) {
+                const int s = it % p.stages;
+                const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+                if (it >= p.stages && !mbar_wait(empty_bar + s * 8, ph ^ 1u)) {
+                    atomicOr(p.status, SKV_DEV_TIMEOUT);
+                    break;
+                }
+                const uint32_t bar = full_bar + s * 8;
+                mbar_expect_tx(bar, S::STAGE_BYTES);
+                const int tok = t_begin + it * TILE;
+                const uint32_t kdst = ring + s * S::STAGE_BYTES;
+#pragma unroll
+                for (int hf = 0; hf < S::NH; ++hf) {
+                    kv_tile_load(kdst + hf * S::HALF_BYTES, &tmK, bar, p.pos, hf, tok, h, b, policy);
+                    kv_tile_load(kdst + S::KV_BYTES + hf * S::HALF_BYTES, &tmV, bar, p.pos, hf, tok, h, b, policy);
+                }
+            }
+        }
+        return;
+    }
+
+    // ----------------------------------------------------------------- consumers
+    const int g = lane >> 2;   // MMA row (query head within the group); rows g and g + 8
+    const int tq = lane & 3;   // column pair within an 8-wide tile
+    const int G = p.G;
+
+    // Query fragments for all k-steps, zero for padding rows.
+    uint32_t qa[KSTEPS][4];
+    {
+        const __half* q0 = p.q + (long long)b * p.q_stride_b + (long long)(h * G + g) * p.q_stride_h;
+        const __half* q1 = q0 + 8 * p.q_stride_h;
+        const bool v0 = g < G, v1 = g + 8 < G;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            const int col = kk * 16 + tq * 2;
+            qa[kk][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + col) : 0u;
+            qa[kk][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + col) : 0u;
+            qa[kk][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + col + 8) : 0u;
+            qa[kk][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
+        }
+    }
+
+    float o[NT_O][4];
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY;  // running max (exp2 domain), rows g / g + 8
+    float l0 = 0.f, l1 = 0.f;              // per-thread partial row sums
+
+    // ldmatrix lane roles: matrix j = lane / 8, row r8 = lane % 8.
+    const int lj = lane >> 3, r8 = lane & 7;
+    const int wtok = warp * 16;  // this warp's first token inside a stage
+
+    for (int it = 0; it < ntiles; ++it) {
+        const int s = it % p.stages;
+        const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+        if (!mbar_wait(full_bar + s * 8, ph)) {
+            if (lane == 0) atomicOr(p.status, SKV_DEV_TIMEOUT);
+            break;
+        }
+        const int tok0 = t_begin + it * TILE + wtok;  // global index of this warp's first token
+        if (tok0 < t_end) {
+            const uint32_t kbase = ring + s * S::STAGE_BYTES;
+            const uint32_t vbase = kbase + S::KV_BYTES;
+
+            // ---- S = Q K^T for 16 tokens: two 8-token tiles
+            float sc[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+            for (int kk2 = 0; kk2 < KSTEPS / 2; ++kk2) {
+                const int c = 4 * kk2 + lj;  // 16-byte chunk of the row
+                const uint32_t coff = (uint32_t)(c >> 3) * S::HALF_BYTES + (uint32_t)(((c & 7) ^ r8) << 4);
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const uint32_t row = (uint32_t)(wtok + nt * 8 + r8);
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(kbase + row * 128 + coff, b0, b1, b2, b3);
+                    mma_f16(sc[nt], qa[2 * kk2], b0, b1);
+                    mma_f16(sc[nt], qa[2 * kk2 + 1], b2, b3);
+                }
+            }
+
+            // ---- scale into the exp2 domain, mask the ragged end of the sequence
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sc[nt][j] *= p.scale_log2;
+            if (tok0 + 16 > t_end) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (tok0 + nt * 8 + tq * 2 + (j & 1) >= t_end) sc[nt][j] = -INFINITY;
+            }
+
+            // ---- online softmax
+            float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+            float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            if (__any_sync(0xffffffffu, (mn0 > m0) || (mn1 > m1))) {
+                const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
+                l0 *= c0;
+                l1 *= c1;
+#pragma unroll
+                for (int n = 0; n < NT_O; ++n) {
+                    o[n][0] *= c0; o[n][1] *= c0;
+                    o[n][2] *= c1; o[n][3] *= c1;
+                }
+                m0 = mn0;
+                m1 = mn1;
+            }
+            uint32_t pa[4];
+            {
+                const float p00 = fast_exp2(sc[0][0] - m0), p01 = fast_exp2(sc[0][1] - m0);
+                const float p02 = fast_exp2(sc[0][2] - m1), p03 = fast_exp2(sc[0][3] - m1);
+                const float p10 = fast_exp2(sc[1][0] - m0), p11 = fast_exp2(sc[1][1] - m0);
+                const float p12 = fast_exp2(sc[1][2] - m1), p13 = fast_exp2(sc[1][3] - m1);
+                l0 += (p00 + p01) + (p10 + p11);
+                l1 += (p02 + p03) + (p12 + p13);
+                pa[0] = pack_half2(p00, p01);
+                pa[1] = pack_half2(p02, p03);
+                pa[2] = pack_half2(p10, p11);
+                pa[3] = pack_half2(p12, p13);
+            }
+
+            // ---- rows past the end of the sequence may hold anything (even NaN): zero them in V
+            if (tok0 + 16 > t_end) {
+                for (int idx = lane; idx < 16 * (D / 8); idx += 32) {
+                    const int r = idx / (D / 8), c = idx - r * (D / 8);
+                    if (tok0 + r >= t_end)
+                        *reinterpret_cast<uint4*>(smem + (size_t)s * S::STAGE_BYTES + S::KV_BYTES +
+                                                  (size_t)(c >> 3) * S::HALF_BYTES + (size_t)(wtok + r) * 128 +
+                                                  (size_t)(c & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                __syncwarp();
+            }
+
+            // ---- O += P V over the 16 tokens
+#pragma unroll
+            for (int np = 0; np < NT_O / 2; ++np) {
+                const int c = 2 * np + (lj >> 1);
+                const uint32_t row = (uint32_t)(wtok + (lj & 1) * 8 + r8);
+                const uint32_t addr = vbase + (uint32_t)(c >> 3) * S::HALF_BYTES + row * 128 +
+                                      (uint32_t)(((c & 7) ^ r8) << 4);
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_t(addr, b0, b1, b2, b3);
+                mma_f16(o[2 * np], pa, b0, b1);
+                mma_f16(o[2 * np + 1], pa, b2, b3);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar + s * 8);
+    }
+
+    // ------------------------------------------------- merge the four warps
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    named_bar_sync(1, CONSUMER_THREADS);  // every stage is drained: the ring can be reused
+    float* mo = reinterpret_cast<float*>(smem);                          // [W][MAX_GROUP][D]
+    float* mm = mo + CONSUMER_WARPS * MAX_GROUP * D;                     // [W][MAX_GROUP]
+    float* ml = mm + CONSUMER_WARPS * MAX_GROUP;                         // [W][MAX_GROUP]
+    float* wts = ml + CONSUMER_WARPS * MAX_GROUP;                        // [W][MAX_SPLITS]
+    {
+        float* my = mo + (warp * MAX_GROUP) * D;
+        if (g < G) {
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n)
+                *reinterpret_cast<float2*>(my + g * D + n * 8 + tq * 2) = make_float2(o[n][0], o[n][1]);
+            if (tq == 0) { mm[warp * MAX_GROUP + g] = m0; ml[warp * MAX_GROUP + g] = l0; }
+        }
+        if (g + 8 < G) {
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n)
+                *reinterpret_cast<float2*>(my + (g + 8) * D + n * 8 + tq * 2) = make_float2(o[n][2], o[n][3]);
+            if (tq == 0) { mm[warp * MAX_GROUP + g + 8] = m1; ml[warp * MAX_GROUP + g + 8] = l1; }
+        }
+    }
+    named_bar_sync(1, CONSUMER_THREADS);
+
+    const long long bh = (long long)b * p.Hkv + h;
+    const long long pbase = (bh * p.num_splits + split) * G;  // row index into the partials
+    for (int idx = threadIdx.x; idx < G * D; idx += CONSUMER_THREADS) {
+        const int r = idx / D, d = idx - r * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < CONSUMER_WARPS; ++w) M = fmaxf(M, mm[w * MAX_GROUP + r]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < CONSUMER_WARPS; ++w) {
+            const float mw = mm[w * MAX_GROUP + r];
+            const float wgt = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+            L += ml[w * MAX_GROUP + r] * wgt;
+            O += mo[(w * MAX_GROUP + r) * D + d] * wgt;
+        }
+        if (n_splits == 1) {
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            p.out[(long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + d] = __float2half_rn(O * inv);
+        } else {
+            p.partial_o[(pbase + r) * D + d] = O;
+            if (d == 0) {
+                p.partial_ml[(pbase + r) * 2 + 0] = M;
+                p.partial_ml[(pbase + r) * 2 + 1] = L;
+            }
+        }
+    }
+    if (n_splits == 1) return;
+
+    // ------------------------------------------- last CTA of this (b, h) combines
+    __threadfence();
+    named_bar_sync(1, CONSUMER_THREADS);
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(&p.tickets[bh], 1);
+        const int last = (ticket == n_splits - 1);
+        if (last) p.tickets[bh] = 0;  // ready for the next launch on this workspace
+        *last_flag = last;
+    }
+    named_bar_sync(1, CONSUMER_THREADS);
+    if (!*last_flag) return;
+    __threadfence();
+
+    const long long rbase = bh * p.num_splits * G;
+    float* wrow = wts + warp * MAX_SPLITS;
+    for (int r = warp; r < G; r += CONSUMER_WARPS) {
+        float mx = -INFINITY;
+        for (int s = lane; s < n_splits; s += 32) mx = fmaxf(mx, __ldcg(&p.partial_ml[(rbase + (long long)s * G + r) * 2]));
+        mx = warp_max(mx);
+        float Ls = 0.f;
+        for (int s = lane; s < n_splits; s += 32) {
+            const float2 v = __ldcg(reinterpret_cast<const float2*>(&p.partial_ml[(rbase + (long long)s * G + r) * 2]));
+            const float w = (v.x == -INFINITY) ? 0.f : fast_exp2(v.x - mx);
+            Ls += v.y * w;
+            wrow[s] = w;
+        }
+        Ls = warp_sum(Ls);
+        __syncwarp();
+        if (lane < D / 4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float* src = p.partial_o + (rbase + r) * D + lane * 4;
+            const long long sstride = (long long)G * D;
+#pragma unroll 8
+            for (int s = 0; s < n_splits; ++s) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + s * sstride));
+                const float w = wrow[s];
+                acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+            }
+            const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+            __half2 lo = __floats2half2_rn(acc.x * inv, acc.y * inv);
+            __half2 hi = __floats2half2_rn(acc.z * inv, acc.w * inv);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(p.out + (long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + lane * 4) = pk;
+        }
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+struct Tuning {
+    int stages = 6;
+    int ctas_per_sm = 1;
+};
+static Tuning g_tuning;
+
+struct Plan {
+    int splits, tiles_per_split;
+    size_t off_status, off_tickets, off_ml, off_o, total;
+};
+
+static Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device) {
+    Plan pl;
+    const int G = Hq / Hkv;
+    const long long total_tiles = (N + TILE - 1) / TILE;
+    long long target = (long long)sm_count(device) * g_tuning.ctas_per_sm;
+    long long splits = target / ((long long)B * Hkv);
+    if (splits < 1) splits = 1;
+    if (splits > total_tiles) splits = total_tiles;
+    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
+    long long tps = (total_tiles + splits - 1) / splits;
+    splits = (total_tiles + tps - 1) / tps;
+    pl.splits = (int)splits;
+    pl.tiles_per_split = (int)tps;
+    auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+    size_t off = 256;  // the device status word sits at offset 0 of every workspace
+    pl.off_status = 0;
+    pl.off_tickets = off;
+    off += up((size_t)B * Hkv * sizeof(int));
+    pl.off_ml = off;
+    off += up((size_t)B * Hkv * splits * G * 2 * sizeof(float));
+    pl.off_o = off;
+    off += up((size_t)B * Hkv * splits * G * D * sizeof(float));
+    pl.total = off;
+    return pl;
+}
+
+template <int D>
+static int launch_f16(const CUtensorMap& tmK, const CUtensorMap& tmV, const Params& p, int B, cudaStream_t stream) {
+    static int configured_smem[64] = {0};
+    const size_t smem = Smem<D>::bytes(p.stages);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && configured_smem[dev] < (int)smem) {
+        SKV_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_f16_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured_smem[dev] = (int)smem;
+    }
+    dim3 grid(p.Hkv, p.num_splits, B);
+    gqa_decode_f16_kernel<D><<<grid, THREADS, smem, stream>>>(tmK, tmV, p);
+    SKV_CUDA_TRY(cudaGetLastError());
+    return SKV_OK;
+}
+
+}  // namespace gqa
+}  // namespace skv
+
+using namespace skv;
+
+extern "C" {
+
+// Tuning knobs for experiments: pipeline depth and CTAs resident per SM used
+// when the KV length is split.  Values outside the valid range are rejected.
+int skv_gqa_set_tuning(int stages, int ctas_per_sm) {
+    if (stages < 2 || stages > 6 || ctas_per_sm < 1 || ctas_per_sm > 4)
+        return fail(SKV_ERR_BAD_ARG, "tuning out of range: stages=%d ctas_per_sm=%d", stages, ctas_per_sm);
+    gqa::g_tuning.stages = stages;
+    gqa::g_tuning.ctas_per_sm = ctas_per_sm;
+    return SKV_OK;
+}
+
+size_t skv_gqa_decode_workspace_bytes(int B, int N, int Hq, int Hkv, int D, int device) {
+    if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || D <= 0) return 0;
+    return gqa::make_plan(B, N, Hq, Hkv, D, device).total;
+}
+
+int skv_gqa_decode_splits(int B, int N, int Hq, int Hkv, int D, int device) {
+    if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || D <= 0) return 0;
+    return gqa::make_plan(B, N, Hq, Hkv, D, device).splits;
+}
+
+int skv_gqa_decode(const void* q, const void* k, const void* v, void* out, void* workspace, size_t workspace_bytes,
+                   int B, int N, int Hq, int Hkv, int D, int kv_dtype, const float* k_scale, const float* v_scale,
+                   long long kv_stride_b, long long kv_stride_n, long long kv_stride_h, const int* seq_lens,
+                   float scale, int device, void* stream) {
+    if (!q || !k || !v || !out) return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode: null tensor pointer");
+    if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0) return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode: sizes must be positive");
+    if (Hq % Hkv != 0) return fail(SKV_ERR_BAD_ARG, "Hq=%d must be divisible by Hkv=%d", Hq, Hkv);
+    const int G = Hq / Hkv;
+    if (G > gqa::MAX_GROUP) return fail(SKV_ERR_UNSUPPORTED, "group size %d exceeds %d", G, gqa::MAX_GROUP);
+    if (D != 128 && D != 64) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (64 or 128)", D);
+    if (!(scale > 0.f)) return fail(SKV_ERR_BAD_ARG, "softmax scale must be positive");
+    if (kv_dtype != SKV_KV_F16) return fail(SKV_ERR_UNSUPPORTED, "kv_dtype %d not supported by this entry point", kv_dtype);
+    (void)k_scale; (void)v_scale;
+    if (Hkv > 65535 || B > 65535) return fail(SKV_ERR_UNSUPPORTED, "grid dimension too large");
+
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
+
+    gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device);
+    if (!workspace || workspace_bytes < pl.total)
+        return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, pl.total);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(SKV_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+
+    CUtensorMap tmK, tmV;
+    KvMapPos pos, pos2;
+    int rc = make_kv_tmap(&tmK, &pos, k, 2, 64, D / 64, B, N, Hkv, kv_stride_b, kv_stride_n, kv_stride_h, gqa::TILE);
+    if (rc) return rc;
+    rc = make_kv_tmap(&tmV, &pos2, v, 2, 64, D / 64, B, N, Hkv, kv_stride_b, kv_stride_n, kv_stride_h, gqa::TILE);
+    if (rc) return rc;
+
+    gqa::Params p;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    p.q = static_cast<const __half*>(q);
+    p.out = static_cast<__half*>(out);
+    p.tickets = reinterpret_cast<int*>(ws + pl.off_tickets);
+    p.status = reinterpret_cast<int*>(ws + pl.off_status);
+    p.partial_ml = reinterpret_cast<float*>(ws + pl.off_ml);
+    p.partial_o = reinterpret_cast<float*>(ws + pl.off_o);
+    p.seq_lens = seq_lens;
+    p.N = N; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
+    p.tiles_per_split = pl.tiles_per_split;
+    p.num_splits = pl.splits;
+    p.stages = gqa::g_tuning.stages;
+    p.q_stride_b = (long long)Hq * D; p.q_stride_h = D;
+    p.o_stride_b = (long long)Hq * D; p.o_stride_h = D;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.pos = pos;
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return D == 128 ? gqa::launch_f16<128>(tmK, tmV, p, B, st) : gqa::launch_f16<64>(tmK, tmV, p, B, st);
+}
+
+}  // extern "C"

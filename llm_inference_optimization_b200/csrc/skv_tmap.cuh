@@ -1,0 +1,99 @@
+// Host-side construction of TMA tensor maps over a KV cache.
+//
+// The caches this library reads are addressed as (batch, token, kv-head, channel)
+// with arbitrary element strides for batch / token / head (channel is contiguous),
+// which covers both layouts the reference uses: [B, N, Hkv, D] for the dense
+// decode entry point and [B, H, T, D] for the sparse entry points.
+//
+// A 16-bit cache row of D channels is exposed to TMA as D/64 "halves" of 64
+// channels (128 bytes) so that each half lands in shared memory as a
+// [tile_tokens][64] block with the 128-byte swizzle, which ldmatrix then reads
+// without bank conflicts.  Tensor dimensions above the innermost are sorted by
+// stride; the position each logical dimension ended up in is returned so the
+// kernel can place its coordinates.
+#pragma once
+
+#include <algorithm>
+
+#include "skv_common.cuh"
+
+namespace skv {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Where each logical coordinate sits among the tensor map's dimensions 1..4
+// (dimension 0 is always the contiguous channel run).
+struct KvMapPos {
+    int half, tok, head, batch;
+};
+
+// Build the map for a cache with `elem_bytes`-wide elements.
+//   inner_elems : channels per innermost run (64 for 16-bit, D for 8-bit)
+//   n_half      : D / inner_elems
+//   strides in ELEMENTS.
+inline int make_kv_tmap(CUtensorMap* out, KvMapPos* pos, const void* base, int elem_bytes, int inner_elems,
+                        int n_half, long long B, long long N, long long Hkv, long long stride_b, long long stride_n,
+                        long long stride_h, int tile_tokens) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(SKV_ERR_DRIVER, "cuTensorMapEncodeTiled entry point not available");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
+        return fail(SKV_ERR_BAD_ARG, "KV base pointer must be 16-byte aligned for TMA");
+
+    struct Dim {
+        int logical;  // 1 half, 2 token, 3 head, 4 batch
+        unsigned long long size, stride_bytes;
+        unsigned box;
+    } d[4] = {
+        {1, (unsigned long long)n_half, (unsigned long long)inner_elems * elem_bytes, 1u},
+        {2, (unsigned long long)N, (unsigned long long)stride_n * elem_bytes, (unsigned)tile_tokens},
+        {3, (unsigned long long)Hkv, (unsigned long long)stride_h * elem_bytes, 1u},
+        {4, (unsigned long long)B, (unsigned long long)stride_b * elem_bytes, 1u},
+    };
+    for (auto& x : d) {
+        if (x.size == 1 && (x.stride_bytes == 0 || (x.stride_bytes & 15))) x.stride_bytes = 16;  // unused stride
+        if (x.stride_bytes == 0 || (x.stride_bytes & 15))
+            return fail(SKV_ERR_BAD_ARG, "KV stride of %llu bytes is not a positive multiple of 16", x.stride_bytes);
+    }
+    std::stable_sort(d, d + 4, [](const Dim& a, const Dim& b) { return a.stride_bytes < b.stride_bytes; });
+
+    cuuint64_t gdim[5] = {(cuuint64_t)inner_elems, d[0].size, d[1].size, d[2].size, d[3].size};
+    cuuint64_t gstr[4] = {d[0].stride_bytes, d[1].stride_bytes, d[2].stride_bytes, d[3].stride_bytes};
+    cuuint32_t box[5] = {(cuuint32_t)inner_elems, d[0].box, d[1].box, d[2].box, d[3].box};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    for (int i = 0; i < 4; ++i) {
+        int p = i + 1;
+        switch (d[i].logical) {
+            case 1: pos->half = p; break;
+            case 2: pos->tok = p; break;
+            case 3: pos->head = p; break;
+            default: pos->batch = p; break;
+        }
+    }
+    CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    int inner_bytes = inner_elems * elem_bytes;
+    CUtensorMapSwizzle sw = inner_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : inner_bytes == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
+                                               : CU_TENSOR_MAP_SWIZZLE_NONE;
+    CUresult r = enc(out, dt, 5, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SKV_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return SKV_OK;
+}
+
+}  // namespace skv

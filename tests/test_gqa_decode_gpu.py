@@ -1,0 +1,107 @@
+"""Dense GQA decode through the C-ABI vs the CPU oracle (max-abs <= 2e-3, fp32 accumulation)."""
+import math
+
+import pytest
+import torch
+
+from llm_inference_optimization_b200 import _C, _workspace, workloads
+from oracle import skv_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3  # max-abs bound on attention outputs
+
+
+def run(Q, K, V, scale, dev, seq_lens=None):
+    lens = None if seq_lens is None else seq_lens.to(dev)
+    out = _C.fused_gqa(Q.to(dev), K.to(dev), V.to(dev), scale, seq_lens=lens)
+    torch.cuda.synchronize()
+    assert _workspace.status(_workspace.get("gqa", 0, dev)) == 0
+    return out.float().cpu()
+
+
+@pytest.mark.parametrize("N", [4096, 16384, 65536])
+def test_config2_llama_layer_shape(cuda_device, N):
+    Q, K, V, scale = workloads.dense_gqa(N)
+    got = run(Q, K, V, scale, cuda_device)
+    want = oracle.dense_gqa_decode(Q, K, V, scale)
+    assert (got - want).abs().max().item() <= TOL
+
+
+@pytest.mark.parametrize("N", [1, 7, 63, 64, 65, 127, 1000, 4097, 64000])
+def test_ragged_lengths(cuda_device, N):
+    Q, K, V, scale = workloads.dense_gqa(N, seed=100 + N % 97)
+    got = run(Q, K, V, scale, cuda_device)
+    want = oracle.dense_gqa_decode(Q, K, V, scale)
+    assert (got - want).abs().max().item() <= TOL
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,D", [(2, 8, 8, 128), (3, 16, 2, 128), (1, 8, 1, 64), (2, 32, 2, 64), (4, 12, 4, 128)])
+def test_group_sizes_and_head_dims(cuda_device, B, Hq, Hkv, D):
+    Q, K, V, scale = workloads.dense_gqa(777, B=B, Hq=Hq, Hkv=Hkv, D=D, seed=9)
+    got = run(Q, K, V, scale, cuda_device)
+    want = oracle.dense_gqa_decode(Q, K, V, scale)
+    assert (got - want).abs().max().item() <= TOL
+
+
+def test_unit_variance_inputs(cuda_device):
+    g = torch.Generator().manual_seed(3)
+    Q = torch.randn(1, 32, 128, generator=g).half()
+    K = torch.randn(1, 8192, 8, 128, generator=g).half()
+    V = torch.randn(1, 8192, 8, 128, generator=g).half()
+    got = run(Q, K, V, 1 / math.sqrt(128), cuda_device)
+    want = oracle.dense_gqa_decode(Q, K, V, 1 / math.sqrt(128))
+    assert (got - want).abs().max().item() <= TOL
+
+
+def test_seq_lens_and_strided_cache(cuda_device):
+    """Per-sequence lengths, and a [B,Hkv,N,D] cache passed as a permuted view (no copy)."""
+    B, N = 3, 3000
+    Q, K, V, scale = workloads.dense_gqa(N, B=B, seed=21)
+    lens = torch.tensor([3000, 1, 1537], dtype=torch.int32)
+    Kc = K.permute(0, 2, 1, 3).contiguous().to(cuda_device)  # [B,Hkv,N,D] as an HF cache stores it
+    Vc = V.permute(0, 2, 1, 3).contiguous().to(cuda_device)
+    out = _C.fused_gqa(Q.to(cuda_device), Kc.permute(0, 2, 1, 3), Vc.permute(0, 2, 1, 3), scale,
+                       seq_lens=lens.to(cuda_device))
+    want = oracle.dense_gqa_decode(Q, K, V, scale, lens)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+def test_repeated_calls_reuse_workspace(cuda_device):
+    Q, K, V, scale = workloads.dense_gqa(20000, seed=5)
+    want = oracle.dense_gqa_decode(Q, K, V, scale)
+    Qd, Kd, Vd = Q.to(cuda_device), K.to(cuda_device), V.to(cuda_device)
+    for _ in range(5):
+        got = _C.fused_gqa(Qd, Kd, Vd, scale).float().cpu()
+        assert (got - want).abs().max().item() <= TOL
+
+
+def test_split_invariance_full_size(cuda_device):
+    """At 128K the result must not depend on how the KV length is split (1 vs 2 CTAs per SM)."""
+    from llm_inference_optimization_b200 import _lib
+    Q, K, V, scale = workloads.dense_gqa(131072, seed=1)
+    Qd, Kd, Vd = Q.to(cuda_device), K.to(cuda_device), V.to(cuda_device)
+    lib = _lib.load()
+    outs = []
+    try:
+        for stages, per_sm in ((6, 1), (3, 2), (2, 2)):
+            _lib.check(lib.skv_gqa_set_tuning(stages, per_sm), "tuning")
+            outs.append(_C.fused_gqa(Qd, Kd, Vd, scale).float().cpu())
+    finally:
+        lib.skv_gqa_set_tuning(6, 1)
+    want = oracle.dense_gqa_decode(Q, K, V, scale)
+    for o in outs:
+        assert (o - want).abs().max().item() <= TOL
+    assert (outs[0] - outs[1]).abs().max().item() <= 1e-3
+
+
+def test_rejects_bad_arguments(cuda_device):
+    Q, K, V, scale = workloads.dense_gqa(128)
+    Qd, Kd, Vd = Q.to(cuda_device), K.to(cuda_device), V.to(cuda_device)
+    with pytest.raises(RuntimeError):
+        _C.fused_gqa(Qd.float(), Kd, Vd, scale)
+    with pytest.raises(RuntimeError):
+        _C.fused_gqa(Qd[:, :30].contiguous(), Kd, Vd, scale)  # 30 % 8 != 0
+    with pytest.raises(RuntimeError):
+        _C.fused_gqa(Qd, Kd, Vd[:, :64], scale)
+    with pytest.raises(RuntimeError):
+        _C.fused_gqa(Q, K, V, scale)  # CPU tensors

@@ -1,0 +1,140 @@
+"""Pins the CPU oracle against outputs of the reference's own Python functions (tests/golden/)."""
+import hashlib
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from llm_inference_optimization_b200 import workloads
+from oracle import skv_oracle as oracle
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def digest(*tensors) -> str:
+    h = hashlib.sha256()
+    for t in tensors:
+        h.update(t.contiguous().numpy().tobytes())
+    return h.hexdigest()
+
+
+def test_config1_token_sparse_matches_reference_outputs():
+    g = np.load(GOLDEN / "config1_token_sparse.npz")
+    Q, K, V = workloads.token_sparse_config1()
+    assert digest(Q, K, V) == str(g["inputs_sha256"]), "seeded inputs differ from the ones the fixture was made with"
+    for top_k, sink in ((256, 0), (256, 4), (32, 4)):
+        want = torch.from_numpy(g[f"out_k{top_k}_s{sink}"])
+        got = oracle.token_sparse_attention(Q, K, V, top_k, sink)
+        assert torch.allclose(got, want, atol=1e-6, rtol=1e-5)
+        Qh, Kh, Vh = (t.half().float() for t in (Q, K, V))
+        want_h = torch.from_numpy(g[f"out_h_k{top_k}_s{sink}"])
+        assert torch.allclose(oracle.token_sparse_attention(Qh, Kh, Vh, top_k, sink), want_h, atol=1e-6, rtol=1e-5)
+
+
+def test_multiquery_shape_family_of_reference_unit_tests():
+    g = np.load(GOLDEN / "token_sparse_multiquery.npz")
+    torch.manual_seed(11)
+    Q, K, V = torch.randn(1, 8, 16, 64), torch.randn(1, 8, 512, 64), torch.randn(1, 8, 512, 64)
+    assert digest(Q, K, V) == str(g["inputs_sha256"])
+    got = oracle.token_sparse_attention(Q, K, V, 64, 4)
+    assert got.shape == (1, 8, 16, 64) and not torch.isnan(got).any()
+    assert torch.allclose(got, torch.from_numpy(g["out_k64_s4"]), atol=1e-6, rtol=1e-5)
+
+
+def test_eviction_selection_and_gather_match_reference():
+    g = np.load(GOLDEN / "eviction_small.npz")
+    K, V, scores = (torch.from_numpy(g[k]) for k in ("K", "V", "scores"))
+    ref_idx = torch.from_numpy(g["topk_idx"])  # descending score, as the reference returns them
+    idx = oracle.eviction_keep_indices(scores, 24, recent=0)
+    assert torch.equal(idx, ref_idx.sort(-1).values)
+    Ko, Vo = oracle.evict_gather(K, V, ref_idx)
+    assert torch.equal(Ko, torch.from_numpy(g["K_out"])) and torch.equal(Vo, torch.from_numpy(g["V_out"]))
+
+
+def test_recent_window_is_kept_on_top_of_budget():
+    torch.manual_seed(1)
+    s = torch.rand(2, 3, 200)
+    idx = oracle.eviction_keep_indices(s, 16, recent=8)
+    assert idx.shape == (2, 3, 24)
+    assert torch.equal(idx[..., -8:], torch.arange(192, 200).expand(2, 3, 8))
+    best = s[..., :192].topk(16, -1).indices.sort(-1).values
+    assert torch.equal(idx[..., :16], best)
+
+
+def test_dense_oracle_equals_sdpa_with_repeated_kv():
+    Q, K, V, scale = workloads.dense_gqa(300, B=2, Hq=8, Hkv=2, D=64)
+    G = 4
+    kx = K.float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+    vx = V.float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+    want = torch.nn.functional.scaled_dot_product_attention(Q.float().unsqueeze(2), kx, vx, scale=scale).squeeze(2)
+    assert torch.allclose(oracle.dense_gqa_decode(Q, K, V, scale), want, atol=1e-6)
+
+
+def test_split_combine_equals_unsplit():
+    torch.manual_seed(2)
+    s = torch.randn(4, 1000) * 3
+    v = torch.randn(1000, 16)
+    want = torch.softmax(s, -1) @ v
+    ms, ls, os_ = [], [], []
+    for lo in range(0, 1000, 130):
+        c = s[:, lo:lo + 130]
+        m = c.max(-1).values
+        p = torch.exp(c - m[:, None])
+        ms.append(m); ls.append(p.sum(-1)); os_.append(p @ v[lo:lo + 130])
+    got = oracle.combine_split_partials(torch.stack(ms), torch.stack(ls), torch.stack(os_))
+    assert torch.allclose(got, want, atol=1e-5)
+
+
+def test_block_mean_rule_ragged_tail_and_topk_clip():
+    torch.manual_seed(3)
+    Q, K, V = torch.randn(1, 2, 1, 32), torch.randn(1, 2, 300, 32), torch.randn(1, 2, 300, 32)
+    out, blocks = oracle.block_sparse_mean_attention(Q, K, V, 64, 4)
+    assert out.shape == (1, 2, 1, 32) and blocks.shape == (1, 2, 4)
+    # by hand for head 0: block means, last block has 44 tokens
+    sc = [(K[0, 0, i * 64:(i + 1) * 64] @ Q[0, 0, 0]).mean() / 32 ** 0.5 for i in range(5)]
+    sc = torch.stack(sc)
+    top = sc.topk(4)
+    w = torch.softmax(top.values, 0)
+    want = sum(w[j] * V[0, 0, int(i) * 64:(int(i) + 1) * 64].mean(0) for j, i in enumerate(top.indices))
+    assert torch.allclose(out[0, 0, 0], want, atol=1e-5)
+    out2, blocks2 = oracle.block_sparse_mean_attention(Q, K, V, 64, 99)  # more blocks asked than exist
+    assert blocks2.shape[-1] == 5
+
+
+def test_int8_rule_and_fp8_rule():
+    torch.manual_seed(4)
+    x = torch.randn(5, 7, 128).half()
+    x[0, 0] = 0
+    q, s = oracle.quantize_int8(x)
+    assert q.dtype == torch.int8 and s[0, 0] == 1.0 and (q[0, 0] == 0).all()
+    assert q.abs().max() == 127
+    assert (oracle.dequantize(q, s) - x.float()).abs().max() <= s.max() * 0.5 + 1e-6
+    f, fs = oracle.quantize_e4m3(x)
+    assert f.dtype == torch.float8_e4m3fn and not torch.isnan(f.float()).any()
+    assert f.float().abs().max() == 448
+    assert oracle.e4m3_code_distance(f, f).max() == 0
+
+
+def test_minmax_meta_bounds_every_key_and_quest_score_is_upper_bound():
+    torch.manual_seed(6)
+    K = torch.randn(1, 2, 200, 16).half()
+    meta = oracle.block_minmax_meta(K, 64)
+    assert meta.shape == (1, 2, 4, 2, 16)
+    Q = torch.randn(1, 4, 16).half()
+    ub = oracle.quest_block_scores(Q, meta, 0.25)
+    for hq in range(4):
+        s = (K[0, hq // 2].float() @ Q[0, hq].float()) * 0.25
+        for j in range(4):
+            assert s[j * 64:(j + 1) * 64].max() <= ub[0, hq, j] + 1e-3
+
+
+def test_paged_pool_round_trip():
+    torch.manual_seed(7)
+    codes = torch.randint(-127, 127, (2, 3, 64, 8), dtype=torch.int8)
+    scales = torch.rand(2, 3, 64)
+    perm = torch.randperm(12)
+    pool, spool, table = oracle.build_paged_cache(codes, scales, 16, perm)
+    for b in range(2):
+        for i in range(4):
+            assert torch.equal(pool[table[b, i]], codes[b, :, i * 16:(i + 1) * 16])
+            assert torch.equal(spool[table[b, i]], scales[b, :, i * 16:(i + 1) * 16])
