@@ -35,7 +35,7 @@ HQ, HKV, D = 32, 8, 128
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch of the decode kernel at 64K measured with ncu (dram__bytes_read.sum +
 # dram__bytes_write.sum, see profiles/); None until a capture has been summarised there.
-NCU_TRAFFIC_BYTES_64K = None
+NCU_TRAFFIC_BYTES_64K = 272_600_000  # profiles/gqa_decode_f16_ctx65536.md
 
 
 def peaks():

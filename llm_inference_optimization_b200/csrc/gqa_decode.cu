@@ -391,7 +391,7 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
 // Host side
 // ---------------------------------------------------------------------------
 struct Tuning {
-    int stages = 6;
+    int stages = 4;
     int ctas_per_sm = 1;
 };
 static Tuning g_tuning;

@@ -1,0 +1,156 @@
+// Exact top-k selection by one CTA: radix select on order-preserving keys, then
+// an ordered compaction, so the chosen positions come out sorted ascending and
+// equal scores resolve to the lower position.
+//
+// The reference selects with a per-thread one-slot "heap" merged by a single
+// thread (csrc/kernels/kv_evict_quant.cu:181-239), which drops true top-k
+// members, and with a serial min-replace loop on thread 0
+// (csrc/kernels/sparse_attention.cu:88-117).  Both are replaced by this routine;
+// its result equals torch.topk(...).indices as a set.
+#pragma once
+
+#include "skv_common.cuh"
+
+namespace skv {
+
+// Larger float <=> larger key (total order; -0 < +0, NaNs at the ends).
+__device__ __forceinline__ uint32_t score_key(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// Shared-memory words block_topk_sorted needs for a CTA of NT threads.
+template <int NT>
+struct TopkSmem {
+    static constexpr int NW = NT / 32;
+    static constexpr int WORDS = NW * 256 + 4 * NW + 8;
+};
+
+// Writes the positions of the k largest of sc[0..T) to out[0..k), ascending.
+// All NT threads of the CTA must call it; `sm` is TopkSmem<NT>::WORDS words.
+// `sc` may live in global or shared memory and must not change during the call.
+template <int NT>
+__device__ void block_topk_sorted(const float* sc, int T, int k, int* out, uint32_t* sm) {
+    constexpr int NW = NT / 32;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (k <= 0) return;
+    if (k >= T) {
+        for (int i = tid; i < T; i += NT) out[i] = i;
+        return;
+    }
+    uint32_t* hist = sm;                  // [NW][256]
+    uint32_t* wcnt = sm + NW * 256;       // [4][NW]: gt, eq, sel-prefix, eq-prefix
+    uint32_t* bc = wcnt + 4 * NW;         // broadcast: digit, remaining
+
+    uint32_t prefix = 0, mask = 0;
+    int remaining = k;
+#pragma unroll 1
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        for (int i = tid; i < NW * 256; i += NT) hist[i] = 0;
+        __syncthreads();
+        uint32_t* myh = hist + warp * 256;
+        for (int i = tid; i < T; i += NT) {
+            const uint32_t key = score_key(sc[i]);
+            if ((key & mask) == prefix) atomicAdd(&myh[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        for (int b = tid; b < 256; b += NT) {  // fold the per-warp histograms into row 0
+            uint32_t s = 0;
+#pragma unroll 4
+            for (int w = 0; w < NW; ++w) s += hist[w * 256 + b];
+            hist[b] = s;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // lane l owns digits 255-8l .. 248-8l (descending); find where the running count reaches `remaining`
+            uint32_t mine = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mine += hist[255 - 8 * lane - j];
+            uint32_t incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const uint32_t hit = __ballot_sync(0xffffffffu, incl >= (uint32_t)remaining);
+            const int owner = __ffs(hit) - 1;  // always found: matching keys >= remaining
+            if (lane == owner) {
+                uint32_t above = incl - mine;  // keys with a larger digit
+                int d = 255 - 8 * lane;
+                for (int j = 0; j < 8; ++j, --d) {
+                    const uint32_t c = hist[d];
+                    if (above + c >= (uint32_t)remaining) break;
+                    above += c;
+                }
+                bc[0] = (uint32_t)d;
+                bc[1] = (uint32_t)remaining - above;
+            }
+        }
+        __syncthreads();
+        prefix |= bc[0] << shift;
+        mask |= 0xFFu << shift;
+        remaining = (int)bc[1];
+        __syncthreads();
+    }
+    const uint32_t thr = prefix;  // key of the k-th largest score
+    const int need = remaining;   // how many scores equal to it are taken (lowest positions first)
+
+    // contiguous, 32-aligned segment per warp
+    int seg = (T + NW - 1) / NW;
+    seg = (seg + 31) & ~31;
+    const int s0 = min(T, warp * seg), s1 = min(T, s0 + seg);
+    uint32_t gt = 0, eq = 0;
+    for (int i0 = s0; i0 < s1; i0 += 32) {
+        const int i = i0 + lane;
+        const bool in = i < s1;
+        const uint32_t key = in ? score_key(sc[i]) : 0u;
+        gt += __popc(__ballot_sync(0xffffffffu, in && key > thr));
+        eq += __popc(__ballot_sync(0xffffffffu, in && key == thr));
+    }
+    if (lane == 0) { wcnt[warp] = gt; wcnt[NW + warp] = eq; }
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t eqp = 0, selp = 0;
+        for (int base = 0; base < NW; base += 32) {
+            const int w = base + lane;
+            const uint32_t g = w < NW ? wcnt[w] : 0u, e = w < NW ? wcnt[NW + w] : 0u;
+            uint32_t ei = e;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xffffffffu, ei, o);
+                if (lane >= o) ei += v;
+            }
+            const uint32_t eex = eqp + ei - e;  // ties before this warp's segment
+            const uint32_t take = (uint32_t)max(0, min((int)e, need - (int)eex));
+            const uint32_t s = g + take;
+            uint32_t si = s;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xffffffffu, si, o);
+                if (lane >= o) si += v;
+            }
+            if (w < NW) { wcnt[2 * NW + w] = selp + si - s; wcnt[3 * NW + w] = eex; }
+            eqp += __shfl_sync(0xffffffffu, ei, 31);
+            selp += __shfl_sync(0xffffffffu, si, 31);
+        }
+    }
+    __syncthreads();
+    uint32_t pos = wcnt[2 * NW + warp], eqrun = wcnt[3 * NW + warp];
+    const uint32_t lt = (1u << lane) - 1u;
+    for (int i0 = s0; i0 < s1; i0 += 32) {
+        const int i = i0 + lane;
+        const bool in = i < s1;
+        const uint32_t key = in ? score_key(sc[i]) : 0u;
+        const bool isgt = in && key > thr, iseq = in && key == thr;
+        const uint32_t beq = __ballot_sync(0xffffffffu, iseq);
+        const bool sel = isgt || (iseq && (int)(eqrun + __popc(beq & lt)) < need);
+        const uint32_t bsel = __ballot_sync(0xffffffffu, sel);
+        if (sel) out[pos + __popc(bsel & lt)] = i;
+        pos += __popc(bsel);
+        eqrun += __popc(beq);
+    }
+    __syncthreads();
+}
+
+}  // namespace skv

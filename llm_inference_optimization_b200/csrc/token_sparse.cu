@@ -1,0 +1,305 @@
+// Token-sparse decode attention: score every cached key, keep the top_k best
+// (plus the first sink_tokens positions), softmax over the kept scores only and
+// sum the kept value rows.
+//
+// Replaces sparse_kv_attn_kernel / kv_evict_quant_forward of the reference
+// (csrc/kernels/kv_evict_quant.cu:107-269, :272-364) and follows the arithmetic of
+// its PyTorch path _reference_sparse_attention (sparse_kv/attention.py:25-38),
+// including the sink prefix, which the reference's CUDA path silently ignores, and
+// with an exact top-k instead of the reference kernel's lossy per-thread heaps.
+//
+// Two launches:
+//   1. token_scores_kernel   -- streams K once (HBM-bound), 16-byte loads, one
+//      row of D channels per D/8 lanes, scores to an fp32 scratch [rows, T];
+//   2. token_select_attend_kernel -- one 1024-thread CTA per (b, h, query):
+//      radix-select top-k over the scratch (L2 resident), softmax, gather of the
+//      kept V rows.
+#include "skv_common.cuh"
+#include "skv_select.cuh"
+
+namespace skv {
+namespace tsp {
+
+constexpr int SCORE_THREADS = 256;
+constexpr int ATT_THREADS = 1024;
+constexpr int MAX_KEEP = 4096;  // top_k + sink_tokens upper bound
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float dot8(const uint4& kv, const float (&q)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&kv);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        s = fmaf(f.x, q[2 * i], s);
+        s = fmaf(f.y, q[2 * i + 1], s);
+    }
+    return s;
+}
+
+struct ScoreParams {
+    const __half* q;   // element (b,h,s,d) at b*q_sb + h*q_sh + s*q_ss + d
+    const __half* k;   // element (b,h,t,d) at b*k_sb + h*k_sh + t*k_st + d
+    float* scores;     // [B, H, S, T]
+    int H, S, T;
+    long long q_sb, q_sh, q_ss, k_sb, k_sh, k_st;
+    float scale;
+};
+
+// grid (ceil(T / tokens_per_cta), H, B*S)
+template <int D>
+__global__ void __launch_bounds__(SCORE_THREADS)
+token_scores_kernel(const ScoreParams p, int tokens_per_cta) {
+    constexpr int LPR = D / 8;      // lanes per key row
+    constexpr int RPW = 32 / LPR;   // rows per warp-wide load
+    constexpr int SUB = 32 / RPW;   // loads per 32 tokens
+    __shared__ float stage[SCORE_THREADS / 32][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPR, rw = lane / LPR;
+    const int h = blockIdx.y, b = blockIdx.z / p.S, s = blockIdx.z % p.S;
+
+    float q[8];
+    {
+        const uint4 qv = *reinterpret_cast<const uint4*>(p.q + b * p.q_sb + h * p.q_sh + s * p.q_ss + sub * 8);
+        const __half2* hq = reinterpret_cast<const __half2*>(&qv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(hq[i]);
+            q[2 * i] = f.x;
+            q[2 * i + 1] = f.y;
+        }
+    }
+    const __half* kbase = p.k + b * p.k_sb + h * p.k_sh + sub * 8;
+    float* srow = p.scores + (((long long)b * p.H + h) * p.S + s) * p.T;
+    const int t0 = blockIdx.x * tokens_per_cta, t1 = min(p.T, t0 + tokens_per_cta);
+
+    for (int base = t0 + warp * 32; base < t1; base += (SCORE_THREADS / 32) * 32) {
+        uint4 kv[SUB];
+#pragma unroll
+        for (int j = 0; j < SUB; ++j) {
+            const int t = base + j * RPW + rw;
+            kv[j] = t < t1 ? ld_stream16(kbase + (long long)t * p.k_st) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < SUB; ++j) {
+            float d = dot8(kv[j], q);
+#pragma unroll
+            for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+            if (sub == 0) stage[warp][j * RPW + rw] = d * p.scale;
+        }
+        __syncwarp();
+        if (base + lane < t1) srow[base + lane] = stage[warp][lane];
+        __syncwarp();
+    }
+}
+
+struct AttendParams {
+    const float* scores;  // [rows, T]
+    const __half* v;      // element (b,h,t,d) at b*v_sb + h*v_sh + t*v_st + d
+    __half* out;          // [rows, D]
+    int* topk_idx;        // optional [rows, top_k], ascending, -1 padded
+    int H, S, T, top_k, sink;
+    long long v_sb, v_sh, v_st;
+};
+
+// grid (rows = B*H*S)
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS)
+token_select_attend_kernel(const AttendParams p) {
+    constexpr int LPR = D / 8;
+    constexpr int GROUPS = ATT_THREADS / LPR;  // value rows gathered in parallel
+    extern __shared__ uint32_t dsm[];
+    uint32_t* tk = dsm;                                             // TopkSmem words
+    int* sel = reinterpret_cast<int*>(tk + TopkSmem<ATT_THREADS>::WORDS);  // [MAX_KEEP]
+    float* w = reinterpret_cast<float*>(sel + MAX_KEEP);            // [MAX_KEEP]
+    float* red = w + MAX_KEEP;                                      // [GROUPS][D] (aliases nothing above)
+    __shared__ float bcast[2];
+
+    const int row = blockIdx.x;
+    const int s_ = row % p.S, h = (row / p.S) % p.H, b = row / (p.S * p.H);
+    (void)s_;
+    const float* sc = p.scores + (long long)row * p.T;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kk = min(p.top_k, p.T), sink = min(max(p.sink, 0), p.T);
+
+    // 1. exact top-k, ascending positions, into sel[sink ...)
+    int* top = sel + sink;
+    block_topk_sorted<ATT_THREADS>(sc, p.T, kk, top, tk);
+    if (p.topk_idx) {
+        for (int i = tid; i < p.top_k; i += ATT_THREADS) p.topk_idx[(long long)row * p.top_k + i] = i < kk ? top[i] : -1;
+    }
+    __syncthreads();
+    // 2. kept set = sink prefix U {top positions >= sink}: drop the leading top entries that fall inside the prefix
+    int c = 0;  // top is ascending, so entries < sink form a prefix of length c
+    {
+        int lo = 0, hi = kk;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (top[mid] < sink) lo = mid + 1; else hi = mid;
+        }
+        c = lo;
+    }
+    const int n = sink + kk - c;
+    __syncthreads();
+    // compact in place: positions [0, sink) then top[c ..)
+    for (int base = 0; base < kk - c; base += ATT_THREADS) {
+        const int i = base + tid;
+        const int v = i < kk - c ? top[c + i] : 0;
+        __syncthreads();
+        if (i < kk - c) sel[sink + i] = v;
+    }
+    for (int i = tid; i < sink; i += ATT_THREADS) sel[i] = i;
+    __syncthreads();
+
+    // 3. softmax over the kept scores
+    float mx = -INFINITY;
+    for (int i = tid; i < n; i += ATT_THREADS) {
+        const float x = sc[sel[i]];
+        w[i] = x;
+        mx = fmaxf(mx, x);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    if (warp == 0) {
+        float m2 = lane < ATT_THREADS / 32 ? red[lane] : -INFINITY;
+        m2 = warp_max(m2);
+        if (lane == 0) bcast[0] = m2;
+    }
+    __syncthreads();
+    mx = bcast[0];
+    float sum = 0.f;
+    for (int i = tid; i < n; i += ATT_THREADS) {
+        const float e = __expf(w[i] - mx);
+        w[i] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    __syncthreads();
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (warp == 0) {
+        float s2 = lane < ATT_THREADS / 32 ? red[lane] : 0.f;
+        s2 = warp_sum(s2);
+        if (lane == 0) bcast[1] = s2;
+    }
+    __syncthreads();
+    const float inv = 1.f / bcast[1];
+
+    // 4. out = sum_j w_j V[sel_j] / sum
+    const int grp = tid / LPR, sub = tid % LPR;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    const __half* vbase = p.v + b * p.v_sb + h * p.v_sh + sub * 8;
+    for (int j = grp; j < n; j += GROUPS) {
+        const uint4 vv = *reinterpret_cast<const uint4*>(vbase + (long long)sel[j] * p.v_st);
+        const float wj = w[j];
+        const __half2* hv = reinterpret_cast<const __half2*>(&vv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(hv[i]);
+            acc[2 * i] = fmaf(wj, f.x, acc[2 * i]);
+            acc[2 * i + 1] = fmaf(wj, f.y, acc[2 * i + 1]);
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[grp * D + sub * 8 + i] = acc[i];
+    __syncthreads();
+    for (int d = tid; d < D; d += ATT_THREADS) {
+        float o = 0.f;
+#pragma unroll 8
+        for (int g2 = 0; g2 < GROUPS; ++g2) o += red[g2 * D + d];
+        p.out[(long long)row * D + d] = __float2half_rn(o * inv);
+    }
+}
+
+template <int D>
+static size_t attend_smem() {
+    return (size_t)TopkSmem<ATT_THREADS>::WORDS * 4 + (size_t)MAX_KEEP * 8 + (size_t)(ATT_THREADS / (D / 8)) * D * 4;
+}
+
+template <int D>
+static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int device, cudaStream_t st) {
+    static bool configured[64] = {false};
+    const size_t smem = attend_smem<D>();
+    if (device < 64 && !configured[device]) {
+        SKV_CUDA_TRY(cudaFuncSetAttribute(token_select_attend_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[device] = true;
+    }
+    // enough CTAs to fill the machine a few times over, at least 512 tokens each
+    const long long rows = (long long)B * sp.H * sp.S;
+    long long want = ((long long)sm_count(device) * 8 + rows - 1) / rows;
+    int tokens_per_cta = (int)((sp.T + want - 1) / want);
+    tokens_per_cta = ((tokens_per_cta + 255) / 256) * 256;
+    if (tokens_per_cta < 512) tokens_per_cta = 512;
+    dim3 g1((sp.T + tokens_per_cta - 1) / tokens_per_cta, sp.H, B * sp.S);
+    token_scores_kernel<D><<<g1, SCORE_THREADS, 0, st>>>(sp, tokens_per_cta);
+    SKV_CUDA_TRY(cudaGetLastError());
+    token_select_attend_kernel<D><<<(unsigned)rows, ATT_THREADS, smem, st>>>(ap);
+    SKV_CUDA_TRY(cudaGetLastError());
+    return SKV_OK;
+}
+
+}  // namespace tsp
+}  // namespace skv
+
+using namespace skv;
+
+extern "C" {
+
+size_t skv_token_sparse_workspace_bytes(int B, int H, int S, int T) {
+    if (B <= 0 || H <= 0 || S <= 0 || T <= 0) return 0;
+    return 256 + (((size_t)B * H * S * T * sizeof(float)) + 255 & ~size_t(255));
+}
+
+int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* out, int* topk_idx_out,
+                            void* workspace, size_t workspace_bytes, int B, int H, int S, int T, int D,
+                            long long q_stride_b, long long q_stride_h, long long q_stride_s,
+                            long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
+                            int top_k, int sink_tokens, float scale, int device, void* stream) {
+    if (!q || !k || !v || !out) return fail(SKV_ERR_BAD_ARG, "skv_token_sparse_decode: null tensor pointer");
+    if (B <= 0 || H <= 0 || S <= 0 || T <= 0) return fail(SKV_ERR_BAD_ARG, "skv_token_sparse_decode: sizes must be positive");
+    if (top_k <= 0) return fail(SKV_ERR_BAD_ARG, "top_k must be positive");
+    if (sink_tokens < 0) return fail(SKV_ERR_BAD_ARG, "sink_tokens must not be negative");
+    if (D != 64 && D != 128) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (64 or 128)", D);
+    const int kk = top_k < T ? top_k : T, sk = sink_tokens < T ? sink_tokens : T;
+    if (kk + sk > tsp::MAX_KEEP)
+        return fail(SKV_ERR_UNSUPPORTED, "top_k + sink_tokens = %d exceeds %d", kk + sk, tsp::MAX_KEEP);
+    if (H > 65535 || (long long)B * S > 65535) return fail(SKV_ERR_UNSUPPORTED, "grid dimension too large");
+    if ((kv_stride_t % 8) || (kv_stride_h % 8) || (kv_stride_b % 8) || (q_stride_b % 8) || (q_stride_h % 8) || (q_stride_s % 8))
+        return fail(SKV_ERR_BAD_ARG, "strides must be multiples of 8 elements (16-byte rows)");
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15)
+        return fail(SKV_ERR_BAD_ARG, "q/k/v must be 16-byte aligned");
+    const size_t need = skv_token_sparse_workspace_bytes(B, H, S, T);
+    if (!workspace || workspace_bytes < need)
+        return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, need);
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
+
+    tsp::ScoreParams sp;
+    sp.q = static_cast<const __half*>(q);
+    sp.k = static_cast<const __half*>(k);
+    sp.scores = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
+    sp.H = H; sp.S = S; sp.T = T;
+    sp.q_sb = q_stride_b; sp.q_sh = q_stride_h; sp.q_ss = q_stride_s;
+    sp.k_sb = kv_stride_b; sp.k_sh = kv_stride_h; sp.k_st = kv_stride_t;
+    sp.scale = scale;
+    tsp::AttendParams ap;
+    ap.scores = sp.scores;
+    ap.v = static_cast<const __half*>(v);
+    ap.out = static_cast<__half*>(out);
+    ap.topk_idx = topk_idx_out;
+    ap.H = H; ap.S = S; ap.T = T; ap.top_k = top_k; ap.sink = sink_tokens;
+    ap.v_sb = kv_stride_b; ap.v_sh = kv_stride_h; ap.v_st = kv_stride_t;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return D == 128 ? tsp::launch<128>(sp, ap, B, device, st) : tsp::launch<64>(sp, ap, B, device, st);
+}
+
+}  // extern "C"
