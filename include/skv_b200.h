@@ -75,6 +75,22 @@ int skv_gqa_decode(const void* q, const void* k, const void* v, void* out,
  * at compile time, csrc/kernels/gqa_decode.cu:22-27). */
 int skv_gqa_set_tuning(int stages, int ctas_per_sm);
 
+/* Same computation as skv_gqa_decode (fp16 KV) for callers that cannot allocate device memory:
+ * a server that has already handed every free byte of HBM to its KV page pool, or a C / Go host
+ * with no torch allocator to borrow a workspace from.  NO COUNTERPART IN THE REFERENCE (its
+ * launchers allocate through torch on every call, csrc/kernels/gqa_decode.cu:253).
+ * The scratch is a fixed array inside the library: SKV_GQA_STATIC_SCRATCH_BYTES per GPU that loads
+ * the library, kept until exit.  Problems whose skv_gqa_decode_workspace_bytes() is larger are
+ * rejected with SKV_ERR_WORKSPACE.  The first call on a device looks the array's device address up
+ * (make that call before any stream capture).  All calls on a GPU share the array: what must be
+ * zero is cleared on `stream` before each launch, and calls that can overlap on one GPU race.
+ * Calls no cudaMalloc / cudaFree / allocating library routine. */
+#define SKV_GQA_STATIC_SCRATCH_BYTES (4u << 20)
+int skv_gqa_decode_noalloc(const void* q, const void* k, const void* v, void* out,
+                           int B, int N, int Hq, int Hkv, int D,
+                           long long kv_stride_b, long long kv_stride_n, long long kv_stride_h,
+                           const int* seq_lens, float scale, int device, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

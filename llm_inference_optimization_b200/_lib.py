@@ -26,6 +26,7 @@ SIGNATURES = {
     "skv_gqa_decode_splits": (_i, [_i, _i, _i, _i, _i, _i]),
     "skv_gqa_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _vp, _vp,
                             _ll, _ll, _ll, _vp, _f, _i, _vp]),
+    "skv_gqa_decode_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _ll, _vp, _f, _i, _vp]),
 }
 
 _lib = None

@@ -24,6 +24,8 @@
 //     shared memory, splits through an fp32 workspace and an atomic ticket.
 //   * every mbarrier wait is bounded; a wait that runs out sets a bit in the
 //     workspace status word instead of hanging.
+#include <mutex>
+
 #include "skv_common.cuh"
 #include "skv_tmap.cuh"
 
@@ -520,6 +522,70 @@ int skv_gqa_decode(const void* q, const void* k, const void* v, void* out, void*
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return D == 128 ? gqa::launch_f16<128>(tmK, tmV, p, B, st) : gqa::launch_f16<64>(tmK, tmV, p, B, st);
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of skv_gqa_decode.
+//
+// Some callers have no device allocator to take a workspace from: a serving
+// process that gave all remaining HBM to its KV page pool at start-up (a later
+// cudaMalloc fails, or stalls every stream while the driver looks for memory),
+// or a plain C / Go host that links this library without torch and its caching
+// allocator.  For them the split-KV scratch (status word, tickets, fp32
+// partials) lives in a fixed array inside the library image instead.
+//
+//   * The array is SKV_GQA_STATIC_SCRATCH_BYTES (4 MiB) per GPU that loads the
+//     library, held until the process exits.  A problem whose
+//     skv_gqa_decode_workspace_bytes() exceeds that is rejected with
+//     SKV_ERR_WORKSPACE; use skv_gqa_decode with a caller workspace then.
+//   * In host code the array's name is only a handle: its device address is
+//     looked up once per device with cudaGetSymbolAddress (device made current
+//     first) and that pointer is what the kernel receives.  The lookup happens
+//     in the FIRST call on each device, which therefore should be made before
+//     any stream capture begins on that device.
+//   * All calls on one GPU share the array and it keeps the previous call's
+//     contents: the part that must start at zero (status word and tickets) is
+//     cleared on `stream` before every launch.  Two calls that can overlap on
+//     the same GPU (different streams, no ordering) race on it -- serialise
+//     them, or use skv_gqa_decode with separate workspaces.
+//   * Nothing here calls cudaMalloc, cudaFree or any allocating library routine.
+// ---------------------------------------------------------------------------
+#define SKV_GQA_STATIC_SCRATCH_BYTES (4u << 20)
+
+static __device__ __align__(256) unsigned char skv_gqa_static_scratch[SKV_GQA_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_ptr[64] = {nullptr};  // device address of the array, per device ordinal
+static std::mutex g_static_scratch_mu;
+
+int skv_gqa_decode_noalloc(const void* q, const void* k, const void* v, void* out, int B, int N, int Hq, int Hkv,
+                           int D, long long kv_stride_b, long long kv_stride_n, long long kv_stride_h,
+                           const int* seq_lens, float scale, int device, void* stream) {
+    if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || Hq % Hkv != 0)
+        return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode_noalloc: sizes must be positive and Hq divisible by Hkv");
+    if (device < 0 || device >= 64) return fail(SKV_ERR_BAD_ARG, "device ordinal %d out of range", device);
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
+
+    const gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device);
+    if (pl.total > (size_t)SKV_GQA_STATIC_SCRATCH_BYTES)
+        return fail(SKV_ERR_WORKSPACE,
+                    "this problem needs %zu bytes of scratch but the built-in array holds %u: "
+                    "call skv_gqa_decode with a caller-provided workspace",
+                    pl.total, (unsigned)SKV_GQA_STATIC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+        scratch = g_static_scratch_ptr[device];
+        if (!scratch) {  // one-time set-up for this device (it is the current device here)
+            cudaError_t e = cudaGetSymbolAddress(&scratch, skv_gqa_static_scratch);
+            if (e != cudaSuccess || !scratch)
+                return fail(SKV_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+            g_static_scratch_ptr[device] = scratch;
+        }
+    }
+    // status word + tickets must be zero when the kernel starts; the partials need no clearing
+    SKV_CUDA_TRY(cudaMemsetAsync(scratch, 0, pl.off_ml, static_cast<cudaStream_t>(stream)));
+    return skv_gqa_decode(q, k, v, out, scratch, (size_t)SKV_GQA_STATIC_SCRATCH_BYTES, B, N, Hq, Hkv, D, SKV_KV_F16,
+                          nullptr, nullptr, kv_stride_b, kv_stride_n, kv_stride_h, seq_lens, scale, device, stream);
 }
 
 }  // extern "C"
