@@ -75,6 +75,40 @@ int skv_gqa_decode(const void* q, const void* k, const void* v, void* out,
  * at compile time, csrc/kernels/gqa_decode.cu:22-27). */
 int skv_gqa_set_tuning(int stages, int ctas_per_sm);
 
+/* ---- token-sparse decode ----------------------------------------------------------
+ * Replaces kv_evict_quant_forward(Q, K, V, top_k, use_int8=false)  (csrc/kernels/kv_evict_quant.cu:272-364,
+ * bound in csrc/pybind/bindings.cpp:28) with the arithmetic of _reference_sparse_attention
+ * (sparse_kv/attention.py:25-38): scores = scale * q.k over all T keys; only the top_k best keys and the
+ * first sink_tokens positions take part in the softmax; out = sum w v.  The top-k is exact.
+ * q [B,H,S,D], k/v [B,H,T,D] fp16 with element strides (channel contiguous, rows 16-byte aligned);
+ * out [B,H,S,D] fp16 contiguous; topk_idx_out optional int32 [B,H,S,top_k], ascending, -1 padded.
+ * D is 16, 32, 64, 128 or 256; min(top_k,T) + min(sink_tokens,T) <= 4096.  Workspace holds fp32 scores [B,H,S,T]. */
+size_t skv_token_sparse_workspace_bytes(int B, int H, int S, int T);
+int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* out, int* topk_idx_out,
+                            void* workspace, size_t workspace_bytes, int B, int H, int S, int T, int D,
+                            long long q_stride_b, long long q_stride_h, long long q_stride_s,
+                            long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
+                            int top_k, int sink_tokens, float scale, int device, void* stream);
+
+/* ---- fused KV eviction + quantisation ----------------------------------------------
+ * Replaces fused_kv_evict / _reference_eviction (sparse_kv/eviction.py:12-27, :30-44): per (b,h) keep the
+ * `budget` highest-scoring tokens (scores fp32 [B,H,T] contiguous) plus the last `recent` positions, gather
+ * their K and V rows and quantise them.  keep = skv_kv_evict_keep_count(T, budget, recent).
+ *   idx_out      int32 [B,H,keep]: kept positions, ascending (order 0) or by descending score (order 1,
+ *                the order torch.topk returns; equal scores: lower position first)
+ *   k_out/v_out  [B,H,keep,D]: fp16 rows (quant_mode 0), int8 codes (1), e4m3 codes (2), or the
+ *                reference's unscaled int8 cast (3; sparse_kv/eviction.py:41-43)
+ *   k/v_scale_out fp32 [B,H,keep], required for modes 1 and 2:
+ *                mode 1: scale = amax/127 (1.0 if the row is zero), code = clamp(rint(x/scale), -127, 127)
+ *                mode 2: scale = amax/448 (1.0 if zero),            code = e4m3_rne_satfinite(x/scale)
+ * k_cache/v_cache fp16 [B,H,T,D] with element strides.  D is 16, 32, 64, 128 or 256, keep <= 8192. */
+int skv_kv_evict_keep_count(int T, int budget, int recent);
+int skv_kv_evict_quant(const void* k_cache, const void* v_cache, const float* scores, int* idx_out,
+                       void* k_out, void* v_out, float* k_scale_out, float* v_scale_out,
+                       int B, int H, int T, int D,
+                       long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
+                       int budget, int recent, int quant_mode, int order, int device, void* stream);
+
 /* Same computation as skv_gqa_decode (fp16 KV) for callers that cannot allocate device memory:
  * a server that has already handed every free byte of HBM to its KV page pool, or a C / Go host
  * with no torch allocator to borrow a workspace from.  NO COUNTERPART IN THE REFERENCE (its

@@ -72,3 +72,49 @@ def fused_gqa(Q: Tensor, K: Tensor, V: Tensor, scale: float, *, seq_lens: Tensor
                             B, N, Hq, Hkv, D, _lib.KV_F16, None, None, sb, sn, sh, lens_ptr, float(scale), dev, stream)
     _lib.check(rc, "fused_gqa")
     return out
+
+
+def token_sparse_decode(Q: Tensor, K: Tensor, V: Tensor, top_k: int, sink_tokens: int = 0, *,
+                        return_indices: bool = False):
+    """Token-level top-k sparse attention on fp16 CUDA tensors.
+
+    Q ``[B,H,S,D]``, K/V ``[B,H,T,D]`` -> ``[B,H,S,D]`` fp16: softmax over the ``top_k`` best keys and the
+    first ``sink_tokens`` positions only (sparse_kv/attention.py:25-38).  With ``return_indices`` also
+    returns the selected key positions ``[B,H,S,top_k]`` int32, ascending, -1 padded.
+    """
+    _require(Q.is_cuda and K.is_cuda and V.is_cuda, "Q/K/V must be CUDA tensors")
+    _require(Q.dtype == torch.float16, "Q must be fp16")
+    _require(K.dtype == torch.float16, "K must be fp16")
+    _require(V.dtype == torch.float16, "V must be fp16")
+    _require(Q.dim() == 4 and K.dim() == 4 and V.dim() == 4, "expected Q [B,H,S,D] and K/V [B,H,T,D]")
+    B, H, S, D = Q.shape
+    T = K.shape[2]
+    _require(K.shape[0] == B and K.shape[1] == H, "K batch/head dims must match Q")
+    _require(K.shape[3] == D and V.shape == K.shape, "V shape must match K")
+    _require(top_k > 0, "top_k must be positive")
+    _require(K.device == Q.device and V.device == Q.device, "Q/K/V must be on one device")
+    if Q.stride(-1) != 1:
+        Q = Q.contiguous()
+    sb, sh, st = _kv_strides(K, V, "token_sparse_decode")
+    dev = _dev_index(Q)
+    lib = _lib.load()
+    out = torch.empty((B, H, S, D), dtype=torch.float16, device=Q.device)
+    idx = torch.empty((B, H, S, top_k), dtype=torch.int32, device=Q.device) if return_indices else None
+    ws = _workspace.get("token_sparse", lib.skv_token_sparse_workspace_bytes(B, H, S, T), Q.device)
+    stream = torch.cuda.current_stream(Q.device).cuda_stream
+    rc = lib.skv_token_sparse_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(),
+                                     None if idx is None else idx.data_ptr(), ws.data_ptr(), ws.numel(),
+                                     B, H, S, T, D, Q.stride(0), Q.stride(1), Q.stride(2), sb, sh, st,
+                                     int(top_k), int(sink_tokens), float(D) ** -0.5, dev, stream)
+    _lib.check(rc, "token_sparse_decode")
+    return (out, idx) if return_indices else out
+
+
+def kv_evict_quant_forward(Q: Tensor, K: Tensor, V: Tensor, top_k: int, use_int8: bool) -> Tensor:
+    """Reference binding ``kv_evict_quant_forward(Q, K, V, top_k, use_int8)`` (csrc/kernels/kv_evict_quant.cu:272-364).
+
+    Despite its name it is token-sparse attention: Q ``[B,H,1,D]``, K/V ``[B,H,T,D]`` fp16 -> ``[B,H,1,D]``.
+    As in the reference, ``use_int8=True`` is rejected (kv_evict_quant.cu:294).  The top-k here is exact.
+    """
+    _require(not use_int8, "INT8 path not enabled in this build")
+    return token_sparse_decode(Q, K, V, top_k, 0)

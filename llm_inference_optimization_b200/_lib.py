@@ -12,7 +12,8 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libskv_b200.so"
 
 KV_F16, KV_I8, KV_E4M3 = 0, 1, 2
-QUANT_INT8, QUANT_E4M3 = 1, 2
+QUANT_NONE, QUANT_INT8, QUANT_E4M3, QUANT_CAST = 0, 1, 2, 3
+ORDER_POSITION, ORDER_SCORE = 0, 1
 
 _vp, _i, _ll, _f, _sz = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_size_t
 
@@ -26,6 +27,12 @@ SIGNATURES = {
     "skv_gqa_decode_splits": (_i, [_i, _i, _i, _i, _i, _i]),
     "skv_gqa_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _vp, _vp,
                             _ll, _ll, _ll, _vp, _f, _i, _vp]),
+    "skv_token_sparse_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "skv_token_sparse_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i,
+                                     _ll, _ll, _ll, _ll, _ll, _ll, _i, _i, _f, _i, _vp]),
+    "skv_kv_evict_keep_count": (_i, [_i, _i, _i]),
+    "skv_kv_evict_quant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll,
+                                _i, _i, _i, _i, _i, _vp]),
     "skv_gqa_decode_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _ll, _vp, _f, _i, _vp]),
 }
 

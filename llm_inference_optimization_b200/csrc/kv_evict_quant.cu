@@ -226,7 +226,8 @@ int skv_kv_evict_quant(const void* k_cache, const void* v_cache, const float* sc
         return fail(SKV_ERR_BAD_ARG, "skv_kv_evict_quant: null tensor pointer");
     if (B <= 0 || H <= 0 || T <= 0) return fail(SKV_ERR_BAD_ARG, "skv_kv_evict_quant: sizes must be positive");
     if (budget < 0 || recent < 0) return fail(SKV_ERR_BAD_ARG, "budget and recent must not be negative");
-    if (D != 64 && D != 128) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (64 or 128)", D);
+    if (D != 16 && D != 32 && D != 64 && D != 128 && D != 256)
+        return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (16, 32, 64, 128 or 256)", D);
     if (quant_mode < SKV_QUANT_NONE || quant_mode > SKV_QUANT_CAST) return fail(SKV_ERR_BAD_ARG, "unknown quant_mode %d", quant_mode);
     if (order != SKV_ORDER_POSITION && order != SKV_ORDER_SCORE) return fail(SKV_ERR_BAD_ARG, "unknown order %d", order);
     if ((quant_mode == SKV_QUANT_INT8 || quant_mode == SKV_QUANT_E4M3) && (!k_scale_out || !v_scale_out))
@@ -261,7 +262,13 @@ int skv_kv_evict_quant(const void* k_cache, const void* v_cache, const float* sc
     gp.k_out = k_out; gp.v_out = v_out; gp.k_scale = k_scale_out; gp.v_scale = v_scale_out;
     gp.H = H; gp.keep = keep; gp.rows_total = (long long)B * H * keep;
     gp.sb = kv_stride_b; gp.sh = kv_stride_h; gp.st = kv_stride_t;
-    return D == 128 ? evq::launch_gather<128>(gp, quant_mode, device, st) : evq::launch_gather<64>(gp, quant_mode, device, st);
+    switch (D) {
+        case 16: return evq::launch_gather<16>(gp, quant_mode, device, st);
+        case 32: return evq::launch_gather<32>(gp, quant_mode, device, st);
+        case 64: return evq::launch_gather<64>(gp, quant_mode, device, st);
+        case 128: return evq::launch_gather<128>(gp, quant_mode, device, st);
+        default: return evq::launch_gather<256>(gp, quant_mode, device, st);
+    }
 }
 
 }  // extern "C"

@@ -256,7 +256,7 @@ extern "C" {
 
 size_t skv_token_sparse_workspace_bytes(int B, int H, int S, int T) {
     if (B <= 0 || H <= 0 || S <= 0 || T <= 0) return 0;
-    return 256 + (((size_t)B * H * S * T * sizeof(float)) + 255 & ~size_t(255));
+    return 256 + ((((size_t)B * H * S * T * sizeof(float)) + 255) & ~size_t(255));
 }
 
 int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* out, int* topk_idx_out,
@@ -268,7 +268,8 @@ int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* o
     if (B <= 0 || H <= 0 || S <= 0 || T <= 0) return fail(SKV_ERR_BAD_ARG, "skv_token_sparse_decode: sizes must be positive");
     if (top_k <= 0) return fail(SKV_ERR_BAD_ARG, "top_k must be positive");
     if (sink_tokens < 0) return fail(SKV_ERR_BAD_ARG, "sink_tokens must not be negative");
-    if (D != 64 && D != 128) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (64 or 128)", D);
+    if (D != 16 && D != 32 && D != 64 && D != 128 && D != 256)
+        return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (16, 32, 64, 128 or 256)", D);
     const int kk = top_k < T ? top_k : T, sk = sink_tokens < T ? sink_tokens : T;
     if (kk + sk > tsp::MAX_KEEP)
         return fail(SKV_ERR_UNSUPPORTED, "top_k + sink_tokens = %d exceeds %d", kk + sk, tsp::MAX_KEEP);
@@ -299,7 +300,13 @@ int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* o
     ap.H = H; ap.S = S; ap.T = T; ap.top_k = top_k; ap.sink = sink_tokens;
     ap.v_sb = kv_stride_b; ap.v_sh = kv_stride_h; ap.v_st = kv_stride_t;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return D == 128 ? tsp::launch<128>(sp, ap, B, device, st) : tsp::launch<64>(sp, ap, B, device, st);
+    switch (D) {
+        case 16: return tsp::launch<16>(sp, ap, B, device, st);
+        case 32: return tsp::launch<32>(sp, ap, B, device, st);
+        case 64: return tsp::launch<64>(sp, ap, B, device, st);
+        case 128: return tsp::launch<128>(sp, ap, B, device, st);
+        default: return tsp::launch<256>(sp, ap, B, device, st);
+    }
 }
 
 }  // extern "C"

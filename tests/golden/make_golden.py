@@ -64,6 +64,7 @@ def main(ref_root: str) -> None:
         HERE / "token_sparse_multiquery.npz",
         inputs_sha256=np.array(digest(Q2, K2, V2)),
         out_k64_s4=ref_attn(Q2, K2, V2, 64, 4).numpy(),
+        out_h_k64_s4=ref_attn(Q2.half().float(), K2.half().float(), V2.half().float(), 64, 4).numpy(),
     )
 
     # --- eviction on a small cache, inputs stored

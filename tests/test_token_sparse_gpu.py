@@ -1,0 +1,95 @@
+"""Token-sparse decode through the C-ABI vs the oracle and the reference-generated golden outputs."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import llm_inference_optimization_b200 as skv
+from llm_inference_optimization_b200 import _C, workloads
+from oracle import skv_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def boundary_gap(Q, K, top_k):
+    """Smallest gap between the k-th and (k+1)-th score over all heads (fp32, fp16-rounded inputs)."""
+    s = torch.matmul(Q.float(), K.float().transpose(-1, -2)) * Q.shape[-1] ** -0.5
+    v = s.topk(min(top_k + 1, s.shape[-1]), -1).values
+    return (v[..., top_k - 1] - v[..., top_k]).min().item() if top_k < s.shape[-1] else 1.0
+
+
+@pytest.mark.parametrize("top_k,sink", [(256, 0), (256, 4), (32, 4)])
+def test_config1_against_reference_golden(cuda_device, top_k, sink):
+    """Config 1 (B=1,H=8,D=64,T=1024, seed 0): public API vs outputs of the reference's own function."""
+    g = np.load(GOLDEN / "config1_token_sparse.npz")
+    Q, K, V = workloads.token_sparse_config1()
+    want = torch.from_numpy(g[f"out_h_k{top_k}_s{sink}"])  # reference evaluated on the fp16-rounded inputs
+    got = skv.sparse_attention(Q.to(cuda_device), K.to(cuda_device), V.to(cuda_device), top_k=top_k, sink_tokens=sink)
+    assert got.dtype == torch.float32 and got.shape == (1, 8, 1, 64)
+    assert (got.cpu() - want).abs().max().item() <= TOL
+
+
+def test_topk_sets_bit_exact_config1(cuda_device):
+    Q, K, V = workloads.token_sparse_config1()
+    Qh, Kh, Vh = Q.half(), K.half(), V.half()
+    assert boundary_gap(Qh, Kh, 256) > 1e-5
+    _, idx = _C.token_sparse_decode(Qh.to(cuda_device), Kh.to(cuda_device), Vh.to(cuda_device), 256, 0,
+                                    return_indices=True)
+    want = oracle.token_topk_sets(Qh, Kh, 256)
+    assert torch.equal(idx[:, :, 0].cpu().long(), want)
+
+
+@pytest.mark.parametrize("B,H,T,D,k,sink", [(1, 32, 4096, 128, 32, 0), (2, 4, 1000, 128, 64, 4), (1, 2, 70000, 128, 512, 4),
+                                            (1, 3, 50, 64, 64, 4), (2, 2, 333, 64, 1, 0), (1, 2, 5000, 128, 2048, 16)])
+def test_shapes_against_oracle(cuda_device, B, H, T, D, k, sink):
+    """Includes the reference's GPU test shape (1,32,4096,128,k=32), ragged T, top_k >= T and large k."""
+    g = torch.Generator().manual_seed(B * 1000 + T)
+    Q = torch.randn(B, H, 1, D, generator=g).half()
+    K = torch.randn(B, H, T, D, generator=g).half()
+    V = torch.randn(B, H, T, D, generator=g).half()
+    out, idx = _C.token_sparse_decode(Q.to(cuda_device), K.to(cuda_device), V.to(cuda_device), k, sink, return_indices=True)
+    want = oracle.token_sparse_attention(Q.float(), K.float(), V.float(), k, sink)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+    if boundary_gap(Q, K, k) > 1e-5:
+        kk = min(k, T)
+        assert torch.equal(idx[:, :, 0, :kk].cpu().long(), oracle.token_topk_sets(Q, K, k))
+        assert (idx[:, :, 0, kk:] == -1).all()
+
+
+def test_multi_query_rows(cuda_device):
+    g = np.load(GOLDEN / "token_sparse_multiquery.npz")
+    torch.manual_seed(11)
+    Q, K, V = torch.randn(1, 8, 16, 64), torch.randn(1, 8, 512, 64), torch.randn(1, 8, 512, 64)
+    got = skv.sparse_attention(Q.to(cuda_device), K.to(cuda_device), V.to(cuda_device), 64, 4).cpu()
+    want = oracle.token_sparse_attention(Q.half().float(), K.half().float(), V.half().float(), 64, 4)
+    assert (got - want).abs().max().item() <= TOL
+    assert (got - torch.from_numpy(g["out_h_k64_s4"])).abs().max().item() <= TOL  # reference on the fp16-rounded inputs
+
+
+def test_tied_scores_resolve_to_lower_position(cuda_device):
+    """Duplicate keys give exactly equal scores; the kept set must take the lower positions."""
+    g = torch.Generator().manual_seed(1)
+    Q = torch.randn(1, 1, 1, 64, generator=g).half()
+    base = torch.randn(1, 1, 8, 64, generator=g).half()
+    K = base.repeat(1, 1, 16, 1)  # 128 keys, every score value appears 16 times
+    V = torch.randn(1, 1, 128, 64, generator=g).half()
+    _, idx = _C.token_sparse_decode(Q.to(cuda_device), K.to(cuda_device), V.to(cuda_device), 20, 0, return_indices=True)
+    s = (K[0, 0].float() @ Q[0, 0, 0].float())
+    order = torch.argsort(s, descending=True, stable=True)[:20].sort().values
+    assert torch.equal(idx[0, 0, 0].cpu().long(), order)
+
+
+def test_reference_binding_semantics(cuda_device):
+    Q = torch.randn(1, 2, 1, 128).half().to(cuda_device)
+    K = torch.randn(1, 2, 256, 128).half().to(cuda_device)
+    out = skv.kv_evict_quant_forward(Q, K, K, 16, False)
+    assert out.shape == (1, 2, 1, 128) and out.dtype == torch.float16
+    with pytest.raises(RuntimeError, match="INT8"):
+        skv.kv_evict_quant_forward(Q, K, K, 16, True)
+    with pytest.raises(RuntimeError):
+        skv.kv_evict_quant_forward(Q.float(), K, K, 16, False)
+    with pytest.raises(RuntimeError):
+        skv.sparse_attention(Q.cpu(), K.cpu(), K.cpu())
