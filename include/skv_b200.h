@@ -90,6 +90,22 @@ int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* o
                             long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
                             int top_k, int sink_tokens, float scale, int device, void* stream);
 
+/* ---- block-sparse decode, block-mean rule -----------------------------------------
+ * Replaces sparse_attention_forward(Q, K, V, block_size, top_k_blocks)  (csrc/kernels/sparse_attention.cu:178-244,
+ * kernel :26-175; bound in csrc/pybind/bindings.cpp:27; same arithmetic as jax_ref/sparse_attention_pallas.py:52-136):
+ *   s_j = scale * mean_{t in block j} q.k_t;  top_k_blocks best blocks (ties: lower block);  w = softmax(s_top);
+ *   out = sum_j w_j * mean_{t in block j} v_t.   The ragged last block uses its own token count.
+ * q [B,H,D] (the reference's [B,H,1,D]), k/v [B,H,T,D] fp16 with element strides; out [B,H,D] fp16 contiguous;
+ * block_idx_out optional int32 [B,H,top_k_blocks], ascending, -1 padded (the reference computes and drops it,
+ * sparse_attention.cu:213-215,243).  D is 16, 32, 64, 128 or 256; min(top_k_blocks, nb) <= 4096.
+ * Workspace holds fp32 block scores [B,H,nb]. */
+size_t skv_block_sparse_workspace_bytes(int B, int H, int T, int block_size);
+int skv_block_sparse_decode(const void* q, const void* k, const void* v, void* out, int* block_idx_out,
+                            void* workspace, size_t workspace_bytes, int B, int H, int T, int D,
+                            long long q_stride_b, long long q_stride_h,
+                            long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
+                            int block_size, int top_k_blocks, float scale, int device, void* stream);
+
 /* ---- fused KV eviction + quantisation ----------------------------------------------
  * Replaces fused_kv_evict / _reference_eviction (sparse_kv/eviction.py:12-27, :30-44): per (b,h) keep the
  * `budget` highest-scoring tokens (scores fp32 [B,H,T] contiguous) plus the last `recent` positions, gather

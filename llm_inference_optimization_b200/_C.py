@@ -118,3 +118,41 @@ def kv_evict_quant_forward(Q: Tensor, K: Tensor, V: Tensor, top_k: int, use_int8
     """
     _require(not use_int8, "INT8 path not enabled in this build")
     return token_sparse_decode(Q, K, V, top_k, 0)
+
+
+def sparse_attention_forward(Q: Tensor, K: Tensor, V: Tensor, block_size: int, top_k_blocks: int, *,
+                             return_indices: bool = False):
+    """Reference binding ``sparse_attention_forward`` (csrc/kernels/sparse_attention.cu:178-244).
+
+    Q ``[B,H,1,D]``, K/V ``[B,H,T,D]`` fp16 -> ``[B,H,1,D]`` fp16: blocks of ``block_size`` tokens are scored by
+    the mean of ``q.k / sqrt(D)``, the ``top_k_blocks`` best are soft-maxed on those scores and the output is
+    the weighted sum of their mean value vectors.  ``return_indices`` also returns the chosen block ids
+    ``[B,H,top_k_blocks]`` int32 (ascending, -1 padded), which the reference computes but drops.
+    """
+    _require(Q.is_cuda and K.is_cuda and V.is_cuda, "Q/K/V must be CUDA")
+    _require(Q.dtype == torch.float16, "Q must be fp16")
+    _require(K.dtype == torch.float16, "K must be fp16")
+    _require(V.dtype == torch.float16, "V must be fp16")
+    _require(Q.dim() == 4 and K.dim() == 4 and V.dim() == 4, "expected Q [B,H,1,D] and K/V [B,H,T,D]")
+    _require(Q.shape[2] == 1, "sparse_attention_forward: Q must be decode-step shape [B,H,1,D]")
+    _require(K.shape[0] == Q.shape[0] and K.shape[1] == Q.shape[1], "K batch/head dims must match Q")
+    _require(V.shape[2] == K.shape[2] and V.shape[3] == K.shape[3] and K.shape[3] == Q.shape[3], "V shape must match K")
+    _require(top_k_blocks > 0, "top_k_blocks must be positive")
+    _require(block_size > 0, "block_size must be positive")
+    B, H, _, D = Q.shape
+    T = K.shape[2]
+    if Q.stride(-1) != 1:
+        Q = Q.contiguous()
+    sb, sh, st = _kv_strides(K, V, "sparse_attention_forward")
+    dev = _dev_index(Q)
+    lib = _lib.load()
+    out = torch.empty((B, H, 1, D), dtype=torch.float16, device=Q.device)
+    idx = torch.empty((B, H, top_k_blocks), dtype=torch.int32, device=Q.device) if return_indices else None
+    ws = _workspace.get("block_sparse", lib.skv_block_sparse_workspace_bytes(B, H, T, block_size), Q.device)
+    stream = torch.cuda.current_stream(Q.device).cuda_stream
+    rc = lib.skv_block_sparse_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(),
+                                     None if idx is None else idx.data_ptr(), ws.data_ptr(), ws.numel(),
+                                     B, H, T, D, Q.stride(0), Q.stride(1), sb, sh, st, int(block_size),
+                                     int(top_k_blocks), float(D) ** -0.5, dev, stream)
+    _lib.check(rc, "sparse_attention_forward")
+    return (out, idx) if return_indices else out

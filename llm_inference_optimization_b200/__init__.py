@@ -27,11 +27,11 @@ def _cuda_available() -> bool:
 CUDA_AVAILABLE = _cuda_available()
 
 from . import _C, attention, eviction  # noqa: E402
-from ._C import fused_gqa, kv_evict_quant_forward  # noqa: E402
+from ._C import fused_gqa, kv_evict_quant_forward, sparse_attention_forward  # noqa: E402
 from .attention import sparse_attention  # noqa: E402
 from .eviction import fused_kv_evict  # noqa: E402
 
-__all__ = ["sparse_attention", "fused_kv_evict", "kv_evict_quant_forward", "fused_gqa", "CUDA_AVAILABLE",
+__all__ = ["sparse_attention", "fused_kv_evict", "kv_evict_quant_forward", "sparse_attention_forward", "fused_gqa", "CUDA_AVAILABLE",
            "install_as_sparse_kv"]
 
 

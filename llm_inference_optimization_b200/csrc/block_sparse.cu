@@ -1,0 +1,254 @@
+// Block-sparse decode attention with the reference's block-mean rule.
+//
+// Replaces block_sparse_attn_kernel / sparse_attention_forward of the reference
+// (csrc/kernels/sparse_attention.cu:26-175, :178-244; same arithmetic as
+// jax_ref/sparse_attention_pallas.py:52-136):
+//   s_j   = scale * mean_{t in block j} q . k_t        (ragged last block: its own count)
+//   top-k blocks by s_j (equal scores: lower block first)
+//   w     = softmax(s_top)
+//   out   = sum_j w_j * mean_{t in block j} v_t
+// The reference runs ONE WARP per (b, h) with a lane per block; here
+//   1. block_mean_scores_kernel: a warp per block, D/8 lanes per key row, 16-byte
+//      streaming loads over all of K (HBM-bound), per-lane partial sums reduced
+//      once per block;
+//   2. block_select_attend_kernel: a 1024-thread CTA per (b, h): exact top-k over
+//      the block scores, softmax over k values, gather of k * block_size V rows.
+#include "skv_common.cuh"
+#include "skv_select.cuh"
+
+namespace skv {
+namespace bsp {
+
+constexpr int SCORE_THREADS = 256;
+constexpr int ATT_THREADS = 1024;
+constexpr int MAX_TOPK_BLOCKS = 4096;
+
+struct ScoreParams {
+    const __half* q;   // element (b,h,d) at b*q_sb + h*q_sh + d
+    const __half* k;   // element (b,h,t,d) at b*k_sb + h*k_sh + t*k_st + d
+    float* scores;     // [B, H, nb]
+    int H, T, block_size, nb;
+    long long q_sb, q_sh, k_sb, k_sh, k_st;
+    float scale;
+};
+
+// grid (ceil(nb / blocks_per_cta), H, B)
+template <int D>
+__global__ void __launch_bounds__(SCORE_THREADS)
+block_mean_scores_kernel(const ScoreParams p, int blocks_per_cta) {
+    constexpr int LPR = D / 8;
+    constexpr int RPW = 32 / LPR;
+    constexpr int U = 8;  // independent 16-byte loads in flight per lane
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPR, rw = lane / LPR;
+    const int h = blockIdx.y, b = blockIdx.z;
+    float q[8];
+    unpack8(*reinterpret_cast<const uint4*>(p.q + b * p.q_sb + h * p.q_sh + sub * 8), q);
+    const __half* kbase = p.k + b * p.k_sb + h * p.k_sh + sub * 8;
+    float* srow = p.scores + ((long long)b * p.H + h) * p.nb;
+    const int j0 = blockIdx.x * blocks_per_cta, j1 = min(p.nb, j0 + blocks_per_cta);
+    for (int j = j0 + warp; j < j1; j += SCORE_THREADS / 32) {
+        const int t0 = j * p.block_size, t1 = min(p.T, t0 + p.block_size);
+        float acc = 0.f;
+        for (int base = t0; base < t1; base += U * RPW) {
+            uint4 kv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int t = base + u * RPW + rw;
+                kv[u] = t < t1 ? ld_stream16(kbase + (long long)t * p.k_st) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) acc += dot8(kv[u], q);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) srow[j] = acc * p.scale / (float)(t1 - t0);
+    }
+}
+
+struct AttendParams {
+    const float* scores;  // [rows, nb]
+    const __half* v;
+    __half* out;          // [rows, D]
+    int* block_idx;       // optional [rows, top_k_blocks], ascending, -1 padded
+    int H, T, block_size, nb, top_k;
+    long long v_sb, v_sh, v_st;
+};
+
+// grid (B*H)
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS)
+block_select_attend_kernel(const AttendParams p) {
+    constexpr int LPR = D / 8;
+    constexpr int GROUPS = ATT_THREADS / LPR;
+    extern __shared__ uint32_t dsm[];
+    uint32_t* tk = dsm;
+    int* sel = reinterpret_cast<int*>(tk + TopkSmem<ATT_THREADS>::WORDS);  // [MAX_TOPK_BLOCKS]
+    float* w = reinterpret_cast<float*>(sel + MAX_TOPK_BLOCKS);            // [MAX_TOPK_BLOCKS]
+    float* red = w + MAX_TOPK_BLOCKS;                                      // [GROUPS][D]
+    __shared__ float bcast[2];
+
+    const int row = blockIdx.x, h = row % p.H, b = row / p.H;
+    const float* sc = p.scores + (long long)row * p.nb;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kk = min(p.top_k, p.nb);
+    block_topk_sorted<ATT_THREADS>(sc, p.nb, kk, sel, tk);
+    __syncthreads();
+    if (p.block_idx)
+        for (int i = tid; i < p.top_k; i += ATT_THREADS) p.block_idx[(long long)row * p.top_k + i] = i < kk ? sel[i] : -1;
+
+    // softmax over the kk selected block scores, folded with 1 / count of each block
+    float mx = -INFINITY;
+    for (int i = tid; i < kk; i += ATT_THREADS) {
+        const float x = sc[sel[i]];
+        w[i] = x;
+        mx = fmaxf(mx, x);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    if (warp == 0) {
+        float m2 = lane < ATT_THREADS / 32 ? red[lane] : -INFINITY;
+        m2 = warp_max(m2);
+        if (lane == 0) bcast[0] = m2;
+    }
+    __syncthreads();
+    mx = bcast[0];
+    float sum = 0.f;
+    for (int i = tid; i < kk; i += ATT_THREADS) {
+        const float e = __expf(w[i] - mx);
+        w[i] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    __syncthreads();
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (warp == 0) {
+        float s2 = lane < ATT_THREADS / 32 ? red[lane] : 0.f;
+        s2 = warp_sum(s2);
+        if (lane == 0) bcast[1] = s2;
+    }
+    __syncthreads();
+    const float inv = 1.f / fmaxf(bcast[1], 1e-9f);
+    for (int i = tid; i < kk; i += ATT_THREADS) {
+        const int t0 = sel[i] * p.block_size;
+        const int cnt = min(p.T, t0 + p.block_size) - t0;
+        w[i] = w[i] * inv / (float)cnt;  // per-token weight of block i
+    }
+    __syncthreads();
+
+    const int grp = tid / LPR, sub = tid % LPR;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    const __half* vbase = p.v + b * p.v_sb + h * p.v_sh + sub * 8;
+    const long long total = (long long)kk * p.block_size;
+    for (long long r = grp; r < total; r += GROUPS) {
+        const int i = (int)(r / p.block_size);
+        const int t = sel[i] * p.block_size + (int)(r - (long long)i * p.block_size);
+        if (t < p.T) {
+            float x[8];
+            unpack8(*reinterpret_cast<const uint4*>(vbase + (long long)t * p.v_st), x);
+            const float wi = w[i];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[c] = fmaf(wi, x[c], acc[c]);
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[grp * D + sub * 8 + i] = acc[i];
+    __syncthreads();
+    for (int d = tid; d < D; d += ATT_THREADS) {
+        float o = 0.f;
+#pragma unroll 8
+        for (int g2 = 0; g2 < GROUPS; ++g2) o += red[g2 * D + d];
+        p.out[(long long)row * D + d] = __float2half_rn(o);
+    }
+}
+
+template <int D>
+static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int device, cudaStream_t st) {
+    static bool configured[64] = {false};
+    const size_t smem = (size_t)TopkSmem<ATT_THREADS>::WORDS * 4 + (size_t)MAX_TOPK_BLOCKS * 8 +
+                        (size_t)(ATT_THREADS / (D / 8)) * D * 4;
+    if (device < 64 && !configured[device]) {
+        SKV_CUDA_TRY(cudaFuncSetAttribute(block_select_attend_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[device] = true;
+    }
+    const long long rows = (long long)B * sp.H;
+    long long want = ((long long)sm_count(device) * 8 + rows - 1) / rows;  // CTAs per (b, h)
+    int blocks_per_cta = (int)((sp.nb + want - 1) / want);
+    const int warps = SCORE_THREADS / 32;
+    blocks_per_cta = ((blocks_per_cta + warps - 1) / warps) * warps;
+    dim3 g1((sp.nb + blocks_per_cta - 1) / blocks_per_cta, sp.H, B);
+    block_mean_scores_kernel<D><<<g1, SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);
+    SKV_CUDA_TRY(cudaGetLastError());
+    block_select_attend_kernel<D><<<(unsigned)rows, ATT_THREADS, smem, st>>>(ap);
+    SKV_CUDA_TRY(cudaGetLastError());
+    return SKV_OK;
+}
+
+}  // namespace bsp
+}  // namespace skv
+
+using namespace skv;
+
+extern "C" {
+
+size_t skv_block_sparse_workspace_bytes(int B, int H, int T, int block_size) {
+    if (B <= 0 || H <= 0 || T <= 0 || block_size <= 0) return 0;
+    const size_t nb = ((size_t)T + block_size - 1) / block_size;
+    return 256 + (((size_t)B * H * nb * sizeof(float) + 255) & ~size_t(255));
+}
+
+int skv_block_sparse_decode(const void* q, const void* k, const void* v, void* out, int* block_idx_out,
+                            void* workspace, size_t workspace_bytes, int B, int H, int T, int D,
+                            long long q_stride_b, long long q_stride_h,
+                            long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
+                            int block_size, int top_k_blocks, float scale, int device, void* stream) {
+    if (!q || !k || !v || !out) return fail(SKV_ERR_BAD_ARG, "skv_block_sparse_decode: null tensor pointer");
+    if (B <= 0 || H <= 0 || T <= 0) return fail(SKV_ERR_BAD_ARG, "skv_block_sparse_decode: sizes must be positive");
+    if (top_k_blocks <= 0) return fail(SKV_ERR_BAD_ARG, "top_k_blocks must be positive");
+    if (block_size <= 0) return fail(SKV_ERR_BAD_ARG, "block_size must be positive");
+    if (D != 16 && D != 32 && D != 64 && D != 128 && D != 256)
+        return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (16, 32, 64, 128 or 256)", D);
+    const int nb = (T + block_size - 1) / block_size;
+    if ((top_k_blocks < nb ? top_k_blocks : nb) > bsp::MAX_TOPK_BLOCKS)
+        return fail(SKV_ERR_UNSUPPORTED, "top_k_blocks=%d exceeds %d", top_k_blocks, bsp::MAX_TOPK_BLOCKS);
+    if (H > 65535 || B > 65535) return fail(SKV_ERR_UNSUPPORTED, "grid dimension too large");
+    if ((kv_stride_t % 8) || (kv_stride_h % 8) || (kv_stride_b % 8) || (q_stride_b % 8) || (q_stride_h % 8))
+        return fail(SKV_ERR_BAD_ARG, "strides must be multiples of 8 elements (16-byte rows)");
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15)
+        return fail(SKV_ERR_BAD_ARG, "q/k/v must be 16-byte aligned");
+    const size_t need = skv_block_sparse_workspace_bytes(B, H, T, block_size);
+    if (!workspace || workspace_bytes < need)
+        return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, need);
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
+
+    bsp::ScoreParams sp;
+    sp.q = static_cast<const __half*>(q);
+    sp.k = static_cast<const __half*>(k);
+    sp.scores = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
+    sp.H = H; sp.T = T; sp.block_size = block_size; sp.nb = nb;
+    sp.q_sb = q_stride_b; sp.q_sh = q_stride_h;
+    sp.k_sb = kv_stride_b; sp.k_sh = kv_stride_h; sp.k_st = kv_stride_t;
+    sp.scale = scale;
+    bsp::AttendParams ap;
+    ap.scores = sp.scores;
+    ap.v = static_cast<const __half*>(v);
+    ap.out = static_cast<__half*>(out);
+    ap.block_idx = block_idx_out;
+    ap.H = H; ap.T = T; ap.block_size = block_size; ap.nb = nb; ap.top_k = top_k_blocks;
+    ap.v_sb = kv_stride_b; ap.v_sh = kv_stride_h; ap.v_st = kv_stride_t;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (D) {
+        case 16: return bsp::launch<16>(sp, ap, B, device, st);
+        case 32: return bsp::launch<32>(sp, ap, B, device, st);
+        case 64: return bsp::launch<64>(sp, ap, B, device, st);
+        case 128: return bsp::launch<128>(sp, ap, B, device, st);
+        default: return bsp::launch<256>(sp, ap, B, device, st);
+    }
+}
+
+}  // extern "C"

@@ -196,6 +196,37 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// 16-byte streaming (evict-first) global load: data that is read exactly once.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// fp32 dot product of 8 fp16 values (one 16-byte load) with 8 floats.
+__device__ __forceinline__ float dot8(const uint4& kv, const float (&q)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&kv);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        s = fmaf(f.x, q[2 * i], s);
+        s = fmaf(f.y, q[2 * i + 1], s);
+    }
+    return s;
+}
+
+// 8 fp16 values of a 16-byte word as floats.
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&x)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+    }
+}
+
 #endif  // __CUDACC__
 
 }  // namespace skv

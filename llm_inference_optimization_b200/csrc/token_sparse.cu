@@ -24,24 +24,6 @@ constexpr int SCORE_THREADS = 256;
 constexpr int ATT_THREADS = 1024;
 constexpr int MAX_KEEP = 4096;  // top_k + sink_tokens upper bound
 
-__device__ __forceinline__ uint4 ld_stream16(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
-__device__ __forceinline__ float dot8(const uint4& kv, const float (&q)[8]) {
-    const __half2* h = reinterpret_cast<const __half2*>(&kv);
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(h[i]);
-        s = fmaf(f.x, q[2 * i], s);
-        s = fmaf(f.y, q[2 * i + 1], s);
-    }
-    return s;
-}
-
 struct ScoreParams {
     const __half* q;   // element (b,h,s,d) at b*q_sb + h*q_sh + s*q_ss + d
     const __half* k;   // element (b,h,t,d) at b*k_sb + h*k_sh + t*k_st + d
