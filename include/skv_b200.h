@@ -75,6 +75,29 @@ int skv_gqa_decode(const void* q, const void* k, const void* v, void* out,
  * at compile time, csrc/kernels/gqa_decode.cu:22-27). */
 int skv_gqa_set_tuning(int stages, int ctas_per_sm);
 
+/* ---- dense GQA decode over a paged 8-bit cache -----------------------------------
+ * No reference counterpart (the reference reads an unpaged fp16 cache only, csrc/kernels/gqa_decode.cu:84-90, and
+ * disables its INT8 path, csrc/kernels/kv_evict_quant.cu:294).
+ *   out[b,hq,:] = softmax_t(scale * ks[t] * q[b,hq,:].kc[t,:]) . (vs[t] * vc[t,:])     kv-head = hq/(Hq/Hkv)
+ * k_pool/v_pool : 1-byte codes (SKV_KV_I8 or SKV_KV_E4M3), element (page,h,slot,d) at
+ *                 page*pool_stride_page + h*pool_stride_head + slot*pool_stride_slot + d, D = 128
+ * k/v_scale_pool: fp32, element (page,h,slot) at page*scale_stride_page + h*scale_stride_head + slot
+ * page_table    : int32 [B, max_pages] (physical page of tokens [i*page_size, (i+1)*page_size) of sequence b),
+ *                 or NULL for page = b*max_pages + i (an unpaged [B,H,T,D] cache is page_size = T, max_pages = 1)
+ * seq_lens      : int32 [B] or NULL (then every sequence holds N tokens).  N = longest length the launch must cover.
+ * page_size is a multiple of 16.  Workspace: skv_gqa_decode_workspace_bytes(B, N, Hq, Hkv, D, device). */
+int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool,
+                         const float* k_scale_pool, const float* v_scale_pool,
+                         const int* page_table, const int* seq_lens, void* out,
+                         void* workspace, size_t workspace_bytes,
+                         int B, int N, int Hq, int Hkv, int D, int kv_dtype,
+                         int page_size, int max_pages, int num_pages,
+                         long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
+                         long long scale_stride_page, long long scale_stride_head,
+                         float scale, int device, void* stream);
+/* Ring depth of the 8-bit kernel (3..12 stages of 17 KB); process-wide.  No reference counterpart. */
+int skv_gqa_set_q8_stages(int stages);
+
 /* ---- token-sparse decode ----------------------------------------------------------
  * Replaces kv_evict_quant_forward(Q, K, V, top_k, use_int8=false)  (csrc/kernels/kv_evict_quant.cu:272-364,
  * bound in csrc/pybind/bindings.cpp:28) with the arithmetic of _reference_sparse_attention

@@ -156,3 +156,61 @@ def sparse_attention_forward(Q: Tensor, K: Tensor, V: Tensor, block_size: int, t
                                      int(top_k_blocks), float(D) ** -0.5, dev, stream)
     _lib.check(rc, "sparse_attention_forward")
     return (out, idx) if return_indices else out
+
+
+def _code_dtype(t: Tensor) -> int:
+    if t.dtype == torch.int8:
+        return _lib.KV_I8
+    if t.dtype == torch.float8_e4m3fn:
+        return _lib.KV_E4M3
+    raise RuntimeError("8-bit KV pools must be int8 or float8_e4m3fn")
+
+
+def fused_gqa_paged(Q: Tensor, k_pool: Tensor, v_pool: Tensor, k_scale: Tensor, v_scale: Tensor,
+                    page_table: Tensor | None, seq_lens: Tensor | None, scale: float, *,
+                    max_seq_len: int | None = None, out: Tensor | None = None) -> Tensor:
+    """Dense GQA decode over a paged INT8 / FP8-E4M3 cache with per-token-per-head fp32 scales.
+
+    Q ``[B,Hq,128]`` fp16; pools ``[num_pages, Hkv, page_size, 128]`` int8 or float8_e4m3fn; scale pools
+    ``[num_pages, Hkv, page_size]`` fp32; ``page_table`` int32 ``[B, max_pages]`` (``None``: sequence b owns
+    pages ``b*max_pages ...``, so a ``[B,Hkv,T,128]`` compacted cache is passed with ``page_size = T``);
+    ``seq_lens`` int32 ``[B]``.  Returns ``[B,Hq,128]`` fp16.  No reference counterpart.
+    """
+    _require(Q.is_cuda and Q.dtype == torch.float16 and Q.dim() == 3 and Q.is_contiguous(),
+             "Q must be a contiguous fp16 CUDA tensor [B,Hq,D]")
+    _require(k_pool.dim() == 4 and v_pool.shape == k_pool.shape and k_pool.dtype == v_pool.dtype,
+             "k_pool and v_pool must both be [num_pages,Hkv,page_size,D] of one 8-bit dtype")
+    kvt = _code_dtype(k_pool)
+    B, Hq, D = Q.shape
+    num_pages, Hkv, P, Dk = k_pool.shape
+    _require(Dk == D, "pool head_dim must match Q")
+    _require(k_pool.stride(-1) == 1 and k_pool.stride() == v_pool.stride(), "pools must share a channel-contiguous layout")
+    _require(k_scale.shape == (num_pages, Hkv, P) and v_scale.shape == k_scale.shape and k_scale.dtype == torch.float32
+             and v_scale.dtype == torch.float32 and k_scale.stride() == v_scale.stride() and k_scale.stride(-1) == 1,
+             "scale pools must be fp32 [num_pages,Hkv,page_size] with one layout")
+    if page_table is not None:
+        _require(page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.shape[0] == B
+                 and page_table.is_contiguous() and page_table.device == Q.device, "page_table must be int32 [B,max_pages]")
+        max_pages = page_table.shape[1]
+    else:
+        _require(num_pages % B == 0, "without a page table num_pages must be B * max_pages")
+        max_pages = num_pages // B
+    if seq_lens is not None:
+        _require(seq_lens.dtype == torch.int32 and seq_lens.shape == (B,) and seq_lens.is_contiguous()
+                 and seq_lens.device == Q.device, "seq_lens must be a contiguous int32 [B] tensor on Q's device")
+    N = int(max_seq_len) if max_seq_len is not None else max_pages * P
+    _require(0 < N <= max_pages * P, "max_seq_len must be in (0, max_pages * page_size]")
+    dev = _dev_index(Q)
+    lib = _lib.load()
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=torch.float16, device=Q.device)
+    ws = _workspace.get("gqa", lib.skv_gqa_decode_workspace_bytes(B, N, Hq, Hkv, D, dev), Q.device)
+    stream = torch.cuda.current_stream(Q.device).cuda_stream
+    rc = lib.skv_gqa_decode_paged(
+        Q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_scale.data_ptr(), v_scale.data_ptr(),
+        None if page_table is None else page_table.data_ptr(), None if seq_lens is None else seq_lens.data_ptr(),
+        out.data_ptr(), ws.data_ptr(), ws.numel(), B, N, Hq, Hkv, D, kvt, P, max_pages, num_pages,
+        k_pool.stride(0), k_pool.stride(1), k_pool.stride(2), k_scale.stride(0), k_scale.stride(1),
+        float(scale), dev, stream)
+    _lib.check(rc, "fused_gqa_paged")
+    return out

@@ -26,18 +26,12 @@
 //     workspace status word instead of hanging.
 #include <mutex>
 
+#include "gqa_epilogue.cuh"
 #include "skv_common.cuh"
 #include "skv_tmap.cuh"
 
 namespace skv {
 namespace gqa {
-
-constexpr int TILE = 64;            // tokens per pipeline stage
-constexpr int CONSUMER_WARPS = 4;   // each takes TILE / 4 = 16 tokens of a stage
-constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
-constexpr int THREADS = CONSUMER_THREADS + 32;
-constexpr int MAX_SPLITS = 512;
-constexpr int MAX_GROUP = 16;       // query heads per kv head (rows of one MMA tile)
 
 struct Params {
     const __half* q;
@@ -293,7 +287,6 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     float* mo = reinterpret_cast<float*>(smem);                          // [W][MAX_GROUP][D]
     float* mm = mo + CONSUMER_WARPS * MAX_GROUP * D;                     // [W][MAX_GROUP]
     float* ml = mm + CONSUMER_WARPS * MAX_GROUP;                         // [W][MAX_GROUP]
-    float* wts = ml + CONSUMER_WARPS * MAX_GROUP;                        // [W][MAX_SPLITS]
     {
         float* my = mo + (warp * MAX_GROUP) * D;
         if (g < G) {
@@ -310,125 +303,15 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         }
     }
     named_bar_sync(1, CONSUMER_THREADS);
-
-    const long long bh = (long long)b * p.Hkv + h;
-    const long long pbase = (bh * p.num_splits + split) * G;  // row index into the partials
-    for (int idx = threadIdx.x; idx < G * D; idx += CONSUMER_THREADS) {
-        const int r = idx / D, d = idx - r * D;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < CONSUMER_WARPS; ++w) M = fmaxf(M, mm[w * MAX_GROUP + r]);
-        float L = 0.f, O = 0.f;
-#pragma unroll
-        for (int w = 0; w < CONSUMER_WARPS; ++w) {
-            const float mw = mm[w * MAX_GROUP + r];
-            const float wgt = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-            L += ml[w * MAX_GROUP + r] * wgt;
-            O += mo[(w * MAX_GROUP + r) * D + d] * wgt;
-        }
-        if (n_splits == 1) {
-            const float inv = L > 0.f ? 1.f / L : 0.f;
-            p.out[(long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + d] = __float2half_rn(O * inv);
-        } else {
-            p.partial_o[(pbase + r) * D + d] = O;
-            if (d == 0) {
-                p.partial_ml[(pbase + r) * 2 + 0] = M;
-                p.partial_ml[(pbase + r) * 2 + 1] = L;
-            }
-        }
-    }
-    if (n_splits == 1) return;
-
-    // ------------------------------------------- last CTA of this (b, h) combines
-    __threadfence();
-    named_bar_sync(1, CONSUMER_THREADS);
-    if (threadIdx.x == 0) {
-        const int ticket = atomicAdd(&p.tickets[bh], 1);
-        const int last = (ticket == n_splits - 1);
-        if (last) p.tickets[bh] = 0;  // ready for the next launch on this workspace
-        *last_flag = last;
-    }
-    named_bar_sync(1, CONSUMER_THREADS);
-    if (!*last_flag) return;
-    __threadfence();
-
-    const long long rbase = bh * p.num_splits * G;
-    float* wrow = wts + warp * MAX_SPLITS;
-    for (int r = warp; r < G; r += CONSUMER_WARPS) {
-        float mx = -INFINITY;
-        for (int s = lane; s < n_splits; s += 32) mx = fmaxf(mx, __ldcg(&p.partial_ml[(rbase + (long long)s * G + r) * 2]));
-        mx = warp_max(mx);
-        float Ls = 0.f;
-        for (int s = lane; s < n_splits; s += 32) {
-            const float2 v = __ldcg(reinterpret_cast<const float2*>(&p.partial_ml[(rbase + (long long)s * G + r) * 2]));
-            const float w = (v.x == -INFINITY) ? 0.f : fast_exp2(v.x - mx);
-            Ls += v.y * w;
-            wrow[s] = w;
-        }
-        Ls = warp_sum(Ls);
-        __syncwarp();
-        if (lane < D / 4) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            const float* src = p.partial_o + (rbase + r) * D + lane * 4;
-            const long long sstride = (long long)G * D;
-#pragma unroll 8
-            for (int s = 0; s < n_splits; ++s) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + s * sstride));
-                const float w = wrow[s];
-                acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
-            }
-            const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
-            __half2 lo = __floats2half2_rn(acc.x * inv, acc.y * inv);
-            __half2 hi = __floats2half2_rn(acc.z * inv, acc.w * inv);
-            uint2 pk;
-            pk.x = *reinterpret_cast<uint32_t*>(&lo);
-            pk.y = *reinterpret_cast<uint32_t*>(&hi);
-            *reinterpret_cast<uint2*>(p.out + (long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + lane * 4) = pk;
-        }
-        __syncwarp();
-    }
+    EpilogueArgs ea;
+    ea.partial_o = p.partial_o; ea.partial_ml = p.partial_ml; ea.tickets = p.tickets; ea.out = p.out;
+    ea.Hkv = p.Hkv; ea.G = G; ea.num_splits = p.num_splits; ea.o_stride_b = p.o_stride_b; ea.o_stride_h = p.o_stride_h;
+    merge_and_combine<D>(ea, smem, last_flag, b, h, split, n_splits, 1.f);
 }
 
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-struct Tuning {
-    int stages = 4;
-    int ctas_per_sm = 1;
-};
-static Tuning g_tuning;
-
-struct Plan {
-    int splits, tiles_per_split;
-    size_t off_status, off_tickets, off_ml, off_o, total;
-};
-
-static Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device) {
-    Plan pl;
-    const int G = Hq / Hkv;
-    const long long total_tiles = (N + TILE - 1) / TILE;
-    long long target = (long long)sm_count(device) * g_tuning.ctas_per_sm;
-    long long splits = target / ((long long)B * Hkv);
-    if (splits < 1) splits = 1;
-    if (splits > total_tiles) splits = total_tiles;
-    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
-    long long tps = (total_tiles + splits - 1) / splits;
-    splits = (total_tiles + tps - 1) / tps;
-    pl.splits = (int)splits;
-    pl.tiles_per_split = (int)tps;
-    auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
-    size_t off = 256;  // the device status word sits at offset 0 of every workspace
-    pl.off_status = 0;
-    pl.off_tickets = off;
-    off += up((size_t)B * Hkv * sizeof(int));
-    pl.off_ml = off;
-    off += up((size_t)B * Hkv * splits * G * 2 * sizeof(float));
-    pl.off_o = off;
-    off += up((size_t)B * Hkv * splits * G * D * sizeof(float));
-    pl.total = off;
-    return pl;
-}
-
 template <int D>
 static int launch_f16(const CUtensorMap& tmK, const CUtensorMap& tmV, const Params& p, int B, cudaStream_t stream) {
     static int configured_smem[64] = {0};
@@ -457,8 +340,8 @@ extern "C" {
 int skv_gqa_set_tuning(int stages, int ctas_per_sm) {
     if (stages < 2 || stages > 6 || ctas_per_sm < 1 || ctas_per_sm > 4)
         return fail(SKV_ERR_BAD_ARG, "tuning out of range: stages=%d ctas_per_sm=%d", stages, ctas_per_sm);
-    gqa::g_tuning.stages = stages;
-    gqa::g_tuning.ctas_per_sm = ctas_per_sm;
+    gqa::tuning().stages = stages;
+    gqa::tuning().ctas_per_sm = ctas_per_sm;
     return SKV_OK;
 }
 
@@ -514,7 +397,7 @@ int skv_gqa_decode(const void* q, const void* k, const void* v, void* out, void*
     p.N = N; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
     p.tiles_per_split = pl.tiles_per_split;
     p.num_splits = pl.splits;
-    p.stages = gqa::g_tuning.stages;
+    p.stages = gqa::tuning().stages;
     p.q_stride_b = (long long)Hq * D; p.q_stride_h = D;
     p.o_stride_b = (long long)Hq * D; p.o_stride_h = D;
     p.scale_log2 = scale * 1.4426950408889634f;

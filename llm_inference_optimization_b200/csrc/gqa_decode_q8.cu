@@ -1,0 +1,451 @@
+// Dense GQA decode attention over a PAGED 8-bit KV cache (INT8 or FP8-E4M3 codes
+// with one fp32 scale per token and kv-head), dequantisation fused into the kernel.
+//
+// No reference counterpart: the reference kernel reads an unpaged fp16 cache only
+// (csrc/kernels/gqa_decode.cu:84-90) and its INT8 path is disabled
+// (csrc/kernels/kv_evict_quant.cu:294).  The arithmetic is
+//   Out[b,hq] = softmax_t(scale * ks[t] * q . kc[t]) . (vs[t] * vc[t])
+// with kc/vc the stored codes and ks/vs their scales.
+//
+// Cache layout: code pools addressed (page, kv-head, slot, channel) with D = 128
+// one-byte channels per row; scale pools (page, kv-head, slot) fp32;
+// page_table[b, i] gives the physical page of tokens [i*P, (i+1)*P) of sequence b.
+// P (tokens per page) is a multiple of 16; an unpaged [B, H, T, D] cache is the
+// special case P = T with a null page table.
+//
+// Same structure as the fp16 kernel: grid (Hkv, splits, B), a producer warp
+// feeding a ring of 64-token stages, four consumer warps with mma.sync, online
+// softmax, in-CTA merge, ticketed split combine.  Differences:
+//   * a stage is filled by up to four 16-token TMA boxes per pool (one per page
+//     chunk) plus four 64-byte bulk copies per scale pool; the producer warp
+//     prefetches page ids for eight tiles at a time;
+//   * codes are converted to fp16 in registers right after ldmatrix (e4m3x2 ->
+//     f16x2 by cvt, int8 by a byte-permute + subtract); because four bytes arrive
+//     per lane where an fp16 fragment has two halves, the contraction index of
+//     S = Q K^T and the output channels of P V are permuted consistently;
+//   * ks[t] multiplies the fp32 score; vs[t] (times 2^6, undone at the end, to stay
+//     clear of fp16 subnormals) is folded into P before it is rounded to fp16.
+#include <cuda_fp8.h>
+
+#include "gqa_epilogue.cuh"
+#include "skv_common.cuh"
+#include "skv_tmap.cuh"
+
+namespace skv {
+namespace gqa {
+
+constexpr int Q8_D = 128;
+constexpr int CHUNK = 16;                                  // tokens per TMA box / scale copy
+constexpr int Q8_CODE_BYTES = TILE * Q8_D;                 // 8 KB of K (or V) codes per stage
+constexpr int Q8_STAGE_BYTES = 2 * Q8_CODE_BYTES + 1024;   // + K scales [64] + V scales [64] (512 B, padded)
+constexpr float P_BOOST = 64.f;
+
+struct Q8Params {
+    const __half* q;
+    __half* out;
+    float* partial_o;
+    float* partial_ml;
+    int* tickets;
+    int* status;
+    const int* seq_lens;     // [B] or null
+    const int* page_table;   // [B, max_pages] or null (then page = b * max_pages + i)
+    const float* k_scale;    // element (page, h, slot) at page*sc_sp + h*sc_sh + slot
+    const float* v_scale;
+    int N, Hq, Hkv, G;
+    int tiles_per_split, num_splits, stages;
+    int page_size, max_pages;
+    long long sc_sp, sc_sh;
+    long long q_stride_b, q_stride_h, o_stride_b, o_stride_h;
+    float scale_log2;
+    PoolMapPos pos;
+};
+
+static size_t q8_smem_bytes(int stages) {
+    size_t ring = (size_t)stages * Q8_STAGE_BYTES;
+    size_t merge = merge_smem_bytes<Q8_D>();
+    return 1024 + (ring > merge ? ring : merge) + 2 * stages * 8 + 16;
+}
+
+// Two 8-bit codes in the low 16 bits -> two fp16 values (as a packed register).
+template <int KVT>
+__device__ __forceinline__ uint32_t cvt_pair(uint32_t v16) {
+    if (KVT == SKV_KV_E4M3) {
+        const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v16 & 0xFFFFu), __NV_E4M3);
+        return (uint32_t)h.x | ((uint32_t)h.y << 16);
+    } else {
+        // int8 b -> fp16: 0x6400 | (b ^ 0x80) is exactly 1024 + (b + 128); subtract 1152
+        const uint32_t x = v16 ^ 0x8080u;
+        uint32_t h = __byte_perm(x, 0x64646464u, 0x4140);
+        const __half2 r = __hsub2(*reinterpret_cast<__half2*>(&h), __float2half2_rn(1152.f));
+        return *reinterpret_cast<const uint32_t*>(&r);
+    }
+}
+
+__device__ __forceinline__ void pool_tile_load(uint32_t dst, const CUtensorMap* tm, uint32_t bar, const PoolMapPos& pos,
+                                               int slot, int head, int page, uint64_t policy) {
+    int c[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 1; i < 4; ++i) c[i] = (i == pos.slot) ? slot : (i == pos.head) ? head : page;
+    tma_load_4d(dst, tm, bar, c[0], c[1], c[2], c[3], policy);
+}
+
+template <int KVT>
+__global__ void __launch_bounds__(THREADS, 1)
+gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                     const Q8Params p) {
+    constexpr int D = Q8_D;
+    constexpr int NCH = D / 16;  // 16-byte chunks per row = MMA k-steps of S = Q K^T
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+
+    const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
+    const int tokens_per_split = p.tiles_per_split * TILE;
+    const int n_splits = len > 0 ? (len + tokens_per_split - 1) / tokens_per_split : 1;
+    if (split >= n_splits) return;
+    const int t_begin = split * tokens_per_split;
+    const int t_end = min(len, t_begin + tokens_per_split);
+    const int ntiles = (t_end - t_begin + TILE - 1) / TILE;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t ring = smem_u32(smem);
+    size_t body = (size_t)p.stages * Q8_STAGE_BYTES;
+    if (merge_smem_bytes<D>() > body) body = merge_smem_bytes<D>();
+    const uint32_t full_bar = ring + (uint32_t)body;
+    const uint32_t empty_bar = full_bar + p.stages * 8;
+    int* last_flag = reinterpret_cast<int*>(smem + body + 2 * p.stages * 8);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full_bar + s * 8, 1);
+            mbar_init(empty_bar + s * 8, CONSUMER_WARPS);
+        }
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    // ------------------------------------------------------------------ producer (whole warp)
+    if (warp == CONSUMER_WARPS) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tmK);
+            tma_prefetch_desc(&tmV);
+        }
+        const uint64_t policy = l2_policy_evict_first();
+        const int P = p.page_size;
+        auto page_of = [&](int group_first_tile) -> int {  // lane l: tile group_first_tile + l/4, chunk l%4
+            const int t = t_begin + (group_first_tile + (lane >> 2)) * TILE + (lane & 3) * CHUNK;
+            if (t >= t_end) return 0;
+            const int lp = t / P;
+            return p.page_table ? __ldg(p.page_table + (long long)b * p.max_pages + lp) : b * p.max_pages + lp;
+        };
+        int pid_next = page_of(0);
+        bool ok = true;
+        for (int it0 = 0; it0 < ntiles && ok; it0 += 8) {
+            const int pid = pid_next;
+            pid_next = page_of(it0 + 8);
+            for (int j = 0; j < 8 && it0 + j < ntiles; ++j) {
+                const int it = it0 + j;
+                int pg[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) pg[c] = __shfl_sync(0xffffffffu, pid, j * 4 + c);
+                if (lane == 0) {
+                    const int s = it % p.stages;
+                    const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+                    if (it >= p.stages && !mbar_wait(empty_bar + s * 8, ph ^ 1u)) {
+                        atomicOr(p.status, SKV_DEV_TIMEOUT);
+                        ok = false;
+                    } else {
+                        const int tok = t_begin + it * TILE;
+                        const int nch = min(4, (t_end - tok + CHUNK - 1) / CHUNK);
+                        const uint32_t bar = full_bar + s * 8;
+                        mbar_expect_tx(bar, (uint32_t)nch * (2 * CHUNK * D + 2 * CHUNK * 4));
+                        const uint32_t kdst = ring + s * Q8_STAGE_BYTES;
+                        for (int c = 0; c < nch; ++c) {
+                            const int slot = (tok + c * CHUNK) % P;
+                            pool_tile_load(kdst + c * CHUNK * D, &tmK, bar, p.pos, slot, h, pg[c], policy);
+                            pool_tile_load(kdst + Q8_CODE_BYTES + c * CHUNK * D, &tmV, bar, p.pos, slot, h, pg[c], policy);
+                            const long long so = (long long)pg[c] * p.sc_sp + (long long)h * p.sc_sh + slot;
+                            bulk_load(kdst + 2 * Q8_CODE_BYTES + c * CHUNK * 4, p.k_scale + so, CHUNK * 4, bar);
+                            bulk_load(kdst + 2 * Q8_CODE_BYTES + 256 + c * CHUNK * 4, p.v_scale + so, CHUNK * 4, bar);
+                        }
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+            }
+        }
+        return;
+    }
+
+    // ----------------------------------------------------------------- consumers
+    const int g = lane >> 2, tq = lane & 3;
+    const int G = p.G;
+
+    // Query fragments.  Lane (g, tq) receives bytes 4tq..4tq+3 of every 16-byte chunk c of a key row, so
+    // MMA k-index 2tq+{0,1} of k-step c stands for channel 16c+4tq+{0,1} and k-index 2tq+8+{0,1} for 16c+4tq+{2,3}.
+    uint32_t qa[NCH][4];
+    {
+        const __half* q0 = p.q + (long long)b * p.q_stride_b + (long long)(h * G + g) * p.q_stride_h;
+        const __half* q1 = q0 + 8 * p.q_stride_h;
+        const bool v0 = g < G, v1 = g + 8 < G;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+            const int col = c * 16 + tq * 4;
+            const uint2 a = v0 ? *reinterpret_cast<const uint2*>(q0 + col) : make_uint2(0u, 0u);
+            const uint2 bq = v1 ? *reinterpret_cast<const uint2*>(q1 + col) : make_uint2(0u, 0u);
+            qa[c][0] = a.x; qa[c][2] = a.y;
+            qa[c][1] = bq.x; qa[c][3] = bq.y;
+        }
+    }
+
+    // o[2c+e] is the 8-column tile whose column n stands for channel 16c + 2n + e
+    float o[2 * NCH][4];
+#pragma unroll
+    for (int n = 0; n < 2 * NCH; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int lj = lane >> 3, r8 = lane & 7;
+    const int wtok = warp * 16;
+
+    for (int it = 0; it < ntiles; ++it) {
+        const int s = it % p.stages;
+        const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+        if (!mbar_wait(full_bar + s * 8, ph)) {
+            if (lane == 0) atomicOr(p.status, SKV_DEV_TIMEOUT);
+            break;
+        }
+        const int tok0 = t_begin + it * TILE + wtok;
+        if (tok0 < t_end) {
+            const uint32_t kbase = ring + s * Q8_STAGE_BYTES;
+            const uint32_t vbase = kbase + Q8_CODE_BYTES;
+            const float* ks = reinterpret_cast<const float*>(smem + (size_t)s * Q8_STAGE_BYTES + 2 * Q8_CODE_BYTES);
+            const float* vs = ks + 64;
+            const bool ragged = tok0 + 16 > t_end;
+
+            float sc[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const uint32_t row = (uint32_t)(wtok + nt * 8 + r8);
+#pragma unroll
+                for (int m = 0; m < NCH / 4; ++m) {
+                    uint32_t br[4];
+                    ldsm_x4(kbase + row * 128 + (uint32_t)(((4 * m + lj) ^ r8) << 4), br[0], br[1], br[2], br[3]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        mma_f16(sc[nt], qa[4 * m + j], cvt_pair<KVT>(br[j] & 0xFFFFu), cvt_pair<KVT>(br[j] >> 16));
+                }
+            }
+
+            // per-token scales of this lane's two columns in each 8-token tile
+            float2 ksc[2], vsc[2];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                ksc[nt] = *reinterpret_cast<const float2*>(ks + wtok + nt * 8 + tq * 2);
+                vsc[nt] = *reinterpret_cast<const float2*>(vs + wtok + nt * 8 + tq * 2);
+            }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                sc[nt][0] *= ksc[nt].x * p.scale_log2; sc[nt][1] *= ksc[nt].y * p.scale_log2;
+                sc[nt][2] *= ksc[nt].x * p.scale_log2; sc[nt][3] *= ksc[nt].y * p.scale_log2;
+            }
+            if (ragged) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int t = tok0 + nt * 8 + tq * 2;
+                    if (t >= t_end) { sc[nt][0] = sc[nt][2] = -INFINITY; vsc[nt].x = 0.f; }
+                    if (t + 1 >= t_end) { sc[nt][1] = sc[nt][3] = -INFINITY; vsc[nt].y = 0.f; }
+                }
+                // rows past the end hold stale bytes (possibly NaN codes): zero them in V
+                for (int idx = lane; idx < 16 * 8; idx += 32) {
+                    const int r = idx >> 3, c = idx & 7;
+                    if (tok0 + r >= t_end)
+                        *reinterpret_cast<uint4*>(smem + (size_t)s * Q8_STAGE_BYTES + Q8_CODE_BYTES +
+                                                  (size_t)(wtok + r) * 128 + (size_t)c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                __syncwarp();
+            }
+
+            float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+            float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            if (__any_sync(0xffffffffu, (mn0 > m0) || (mn1 > m1))) {
+                const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
+                l0 *= c0;
+                l1 *= c1;
+#pragma unroll
+                for (int n = 0; n < 2 * NCH; ++n) {
+                    o[n][0] *= c0; o[n][1] *= c0;
+                    o[n][2] *= c1; o[n][3] *= c1;
+                }
+                m0 = mn0;
+                m1 = mn1;
+            }
+            uint32_t pa[4];
+            {
+                const float p00 = fast_exp2(sc[0][0] - m0), p01 = fast_exp2(sc[0][1] - m0);
+                const float p02 = fast_exp2(sc[0][2] - m1), p03 = fast_exp2(sc[0][3] - m1);
+                const float p10 = fast_exp2(sc[1][0] - m0), p11 = fast_exp2(sc[1][1] - m0);
+                const float p12 = fast_exp2(sc[1][2] - m1), p13 = fast_exp2(sc[1][3] - m1);
+                l0 += (p00 + p01) + (p10 + p11);
+                l1 += (p02 + p03) + (p12 + p13);
+                const float a0 = vsc[0].x * P_BOOST, a1 = vsc[0].y * P_BOOST;
+                const float b0 = vsc[1].x * P_BOOST, b1 = vsc[1].y * P_BOOST;
+                pa[0] = pack_half2(p00 * a0, p01 * a1);
+                pa[1] = pack_half2(p02 * a0, p03 * a1);
+                pa[2] = pack_half2(p10 * b0, p11 * b1);
+                pa[3] = pack_half2(p12 * b0, p13 * b1);
+            }
+
+            // O += P V.  A transposed 8x8 b16 matrix hands lane (g, tq) the bytes
+            // [v(t0,2g), v(t0,2g+1), v(t0+1,2g), v(t0+1,2g+1)], t0 = 2tq: even and odd channels split into two tiles.
+#pragma unroll
+            for (int m = 0; m < NCH / 2; ++m) {
+                const int c = 2 * m + (lj >> 1);
+                const uint32_t row = (uint32_t)(wtok + (lj & 1) * 8 + r8);
+                uint32_t r0, r1, r2, r3;
+                ldsm_x4_t(vbase + row * 128 + (uint32_t)((c ^ r8) << 4), r0, r1, r2, r3);
+                mma_f16(o[4 * m + 0], pa, cvt_pair<KVT>(__byte_perm(r0, 0u, 0x4420)), cvt_pair<KVT>(__byte_perm(r1, 0u, 0x4420)));
+                mma_f16(o[4 * m + 1], pa, cvt_pair<KVT>(__byte_perm(r0, 0u, 0x4431)), cvt_pair<KVT>(__byte_perm(r1, 0u, 0x4431)));
+                mma_f16(o[4 * m + 2], pa, cvt_pair<KVT>(__byte_perm(r2, 0u, 0x4420)), cvt_pair<KVT>(__byte_perm(r3, 0u, 0x4420)));
+                mma_f16(o[4 * m + 3], pa, cvt_pair<KVT>(__byte_perm(r2, 0u, 0x4431)), cvt_pair<KVT>(__byte_perm(r3, 0u, 0x4431)));
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar + s * 8);
+    }
+
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    named_bar_sync(1, CONSUMER_THREADS);
+    float* mo = reinterpret_cast<float*>(smem);
+    float* mm = mo + CONSUMER_WARPS * MAX_GROUP * D;
+    float* ml = mm + CONSUMER_WARPS * MAX_GROUP;
+    {
+        float* my = mo + (warp * MAX_GROUP) * D;
+        if (g < G) {
+#pragma unroll
+            for (int c = 0; c < NCH; ++c)
+                *reinterpret_cast<float4*>(my + g * D + c * 16 + tq * 4) =
+                    make_float4(o[2 * c][0], o[2 * c + 1][0], o[2 * c][1], o[2 * c + 1][1]);
+            if (tq == 0) { mm[warp * MAX_GROUP + g] = m0; ml[warp * MAX_GROUP + g] = l0; }
+        }
+        if (g + 8 < G) {
+#pragma unroll
+            for (int c = 0; c < NCH; ++c)
+                *reinterpret_cast<float4*>(my + (g + 8) * D + c * 16 + tq * 4) =
+                    make_float4(o[2 * c][2], o[2 * c + 1][2], o[2 * c][3], o[2 * c + 1][3]);
+            if (tq == 0) { mm[warp * MAX_GROUP + g + 8] = m1; ml[warp * MAX_GROUP + g + 8] = l1; }
+        }
+    }
+    named_bar_sync(1, CONSUMER_THREADS);
+    EpilogueArgs ea;
+    ea.partial_o = p.partial_o; ea.partial_ml = p.partial_ml; ea.tickets = p.tickets; ea.out = p.out;
+    ea.Hkv = p.Hkv; ea.G = G; ea.num_splits = p.num_splits; ea.o_stride_b = p.o_stride_b; ea.o_stride_h = p.o_stride_h;
+    merge_and_combine<D>(ea, smem, last_flag, b, h, split, n_splits, 1.f / P_BOOST);
+}
+
+template <int KVT>
+static int launch_q8(const CUtensorMap& tmK, const CUtensorMap& tmV, const Q8Params& p, int B, cudaStream_t stream) {
+    static int configured_smem[64] = {0};
+    const size_t smem = q8_smem_bytes(p.stages);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && configured_smem[dev] < (int)smem) {
+        SKV_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_q8_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured_smem[dev] = (int)smem;
+    }
+    dim3 grid(p.Hkv, p.num_splits, B);
+    gqa_decode_q8_kernel<KVT><<<grid, THREADS, smem, stream>>>(tmK, tmV, p);
+    SKV_CUDA_TRY(cudaGetLastError());
+    return SKV_OK;
+}
+
+}  // namespace gqa
+}  // namespace skv
+
+using namespace skv;
+
+extern "C" {
+
+int skv_gqa_set_q8_stages(int stages) {
+    if (stages < 3 || stages > 12) return fail(SKV_ERR_BAD_ARG, "q8 stages out of range: %d", stages);
+    gqa::tuning().q8_stages = stages;
+    return SKV_OK;
+}
+
+int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, const float* k_scale_pool,
+                         const float* v_scale_pool, const int* page_table, const int* seq_lens, void* out,
+                         void* workspace, size_t workspace_bytes, int B, int N, int Hq, int Hkv, int D, int kv_dtype,
+                         int page_size, int max_pages, int num_pages, long long pool_stride_page,
+                         long long pool_stride_head, long long pool_stride_slot, long long scale_stride_page,
+                         long long scale_stride_head, float scale, int device, void* stream) {
+    if (!q || !k_pool || !v_pool || !k_scale_pool || !v_scale_pool || !out)
+        return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode_paged: null tensor pointer");
+    if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || num_pages <= 0 || max_pages <= 0)
+        return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode_paged: sizes must be positive");
+    if (Hq % Hkv != 0) return fail(SKV_ERR_BAD_ARG, "Hq=%d must be divisible by Hkv=%d", Hq, Hkv);
+    const int G = Hq / Hkv;
+    if (G > gqa::MAX_GROUP) return fail(SKV_ERR_UNSUPPORTED, "group size %d exceeds %d", G, gqa::MAX_GROUP);
+    if (D != gqa::Q8_D) return fail(SKV_ERR_UNSUPPORTED, "8-bit KV decode supports head dim 128 only (got %d)", D);
+    if (kv_dtype != SKV_KV_I8 && kv_dtype != SKV_KV_E4M3) return fail(SKV_ERR_UNSUPPORTED, "kv_dtype %d is not an 8-bit type", kv_dtype);
+    if (page_size < gqa::CHUNK || page_size % gqa::CHUNK) return fail(SKV_ERR_UNSUPPORTED, "page_size %d must be a multiple of 16", page_size);
+    if ((long long)max_pages * page_size < N) return fail(SKV_ERR_BAD_ARG, "max_pages * page_size < N");
+    if (!(scale > 0.f)) return fail(SKV_ERR_BAD_ARG, "softmax scale must be positive");
+    if ((scale_stride_page % 4) || (scale_stride_head % 4) || (reinterpret_cast<uintptr_t>(k_scale_pool) & 15) ||
+        (reinterpret_cast<uintptr_t>(v_scale_pool) & 15))
+        return fail(SKV_ERR_BAD_ARG, "scale pools must be 16-byte aligned with strides that are multiples of 4 floats");
+    if (Hkv > 65535 || B > 65535) return fail(SKV_ERR_UNSUPPORTED, "grid dimension too large");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
+
+    gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device);
+    if (!workspace || workspace_bytes < pl.total)
+        return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, pl.total);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(SKV_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+
+    CUtensorMap tmK, tmV;
+    PoolMapPos pos, pos2;
+    int rc = make_pool_tmap(&tmK, &pos, k_pool, D, num_pages, Hkv, page_size, pool_stride_page, pool_stride_head,
+                            pool_stride_slot, gqa::CHUNK);
+    if (rc) return rc;
+    rc = make_pool_tmap(&tmV, &pos2, v_pool, D, num_pages, Hkv, page_size, pool_stride_page, pool_stride_head,
+                        pool_stride_slot, gqa::CHUNK);
+    if (rc) return rc;
+
+    gqa::Q8Params p;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    p.q = static_cast<const __half*>(q);
+    p.out = static_cast<__half*>(out);
+    p.tickets = reinterpret_cast<int*>(ws + pl.off_tickets);
+    p.status = reinterpret_cast<int*>(ws + pl.off_status);
+    p.partial_ml = reinterpret_cast<float*>(ws + pl.off_ml);
+    p.partial_o = reinterpret_cast<float*>(ws + pl.off_o);
+    p.seq_lens = seq_lens;
+    p.page_table = page_table;
+    p.k_scale = k_scale_pool;
+    p.v_scale = v_scale_pool;
+    p.N = N; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
+    p.tiles_per_split = pl.tiles_per_split;
+    p.num_splits = pl.splits;
+    p.stages = gqa::tuning().q8_stages;
+    p.page_size = page_size;
+    p.max_pages = max_pages;
+    p.sc_sp = scale_stride_page; p.sc_sh = scale_stride_head;
+    p.q_stride_b = (long long)Hq * D; p.q_stride_h = D;
+    p.o_stride_b = (long long)Hq * D; p.o_stride_h = D;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.pos = pos;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3>(tmK, tmV, p, B, st)
+                                   : gqa::launch_q8<SKV_KV_I8>(tmK, tmV, p, B, st);
+}
+
+}  // extern "C"

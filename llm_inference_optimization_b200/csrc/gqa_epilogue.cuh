@@ -1,0 +1,179 @@
+// Shared by the dense decode kernels (fp16 and 8-bit KV): tile geometry, the
+// split plan and workspace layout, and the epilogue that merges the consumer
+// warps of a CTA, publishes the split partial and lets the last CTA of each
+// (batch, kv-head) do the log-sum-exp combine.
+//
+// No reference counterpart: the reference kernel never splits the KV length
+// (csrc/kernels/gqa_decode.cu:255 launches one CTA per query head).
+#pragma once
+
+#include "skv_common.cuh"
+
+namespace skv {
+namespace gqa {
+
+constexpr int TILE = 64;            // tokens per pipeline stage
+constexpr int CONSUMER_WARPS = 4;   // each takes TILE / 4 = 16 tokens of a stage
+constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
+constexpr int THREADS = CONSUMER_THREADS + 32;
+constexpr int MAX_SPLITS = 512;
+constexpr int MAX_GROUP = 16;       // query heads per kv head (rows of one MMA tile)
+
+// Shared-memory words the epilogue needs at the start of the (drained) stage ring.
+template <int D>
+__host__ __device__ constexpr size_t merge_smem_bytes() {
+    return (size_t)CONSUMER_WARPS * MAX_GROUP * D * 4 + (size_t)CONSUMER_WARPS * MAX_GROUP * 8 +
+           (size_t)CONSUMER_WARPS * MAX_SPLITS * 4;
+}
+
+struct Tuning {
+    int stages = 4;        // fp16 ring depth (64-token stages of 32 KB at D = 128)
+    int ctas_per_sm = 1;
+    int q8_stages = 8;     // 8-bit ring depth (stages of 17 KB)
+};
+inline Tuning& tuning() {
+    static Tuning t;
+    return t;
+}
+
+struct Plan {
+    int splits, tiles_per_split;
+    size_t off_status, off_tickets, off_ml, off_o, total;
+};
+
+// How the KV length is cut: about one CTA per SM (times ctas_per_sm) over all
+// (batch, kv-head) pairs, whole 64-token tiles per split.
+inline Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device) {
+    Plan pl;
+    const int G = Hq / Hkv;
+    const long long total_tiles = (N + TILE - 1) / TILE;
+    long long target = (long long)sm_count(device) * tuning().ctas_per_sm;
+    long long splits = target / ((long long)B * Hkv);
+    if (splits < 1) splits = 1;
+    if (splits > total_tiles) splits = total_tiles;
+    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
+    long long tps = (total_tiles + splits - 1) / splits;
+    splits = (total_tiles + tps - 1) / tps;
+    pl.splits = (int)splits;
+    pl.tiles_per_split = (int)tps;
+    auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+    size_t off = 256;  // the device status word sits at offset 0 of every workspace
+    pl.off_status = 0;
+    pl.off_tickets = off;
+    off += up((size_t)B * Hkv * sizeof(int));
+    pl.off_ml = off;
+    off += up((size_t)B * Hkv * splits * G * 2 * sizeof(float));
+    pl.off_o = off;
+    off += up((size_t)B * Hkv * splits * G * D * sizeof(float));
+    pl.total = off;
+    return pl;
+}
+
+#if defined(__CUDACC__)
+
+struct EpilogueArgs {
+    float* partial_o;    // [B, Hkv, S, G, D]
+    float* partial_ml;   // [B, Hkv, S, G, 2]
+    int* tickets;        // [B * Hkv]
+    __half* out;         // element (b, hq, d) at b*o_stride_b + hq*o_stride_h + d
+    int Hkv, G, num_splits;
+    long long o_stride_b, o_stride_h;
+};
+
+// Called by all CONSUMER_THREADS threads (threadIdx.x < CONSUMER_THREADS) after
+// every warp has stored its state at `smem`: O [W][MAX_GROUP][D], running max
+// [W][MAX_GROUP] (exp2 domain), running sum [W][MAX_GROUP], and after a named
+// barrier.  `out_scale` multiplies the un-normalised output (1 for fp16 KV).
+template <int D>
+__device__ __forceinline__ void merge_and_combine(const EpilogueArgs& p, uint8_t* smem, int* last_flag, int b, int h,
+                                                  int split, int n_splits, float out_scale) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.G;
+    float* mo = reinterpret_cast<float*>(smem);
+    float* mm = mo + CONSUMER_WARPS * MAX_GROUP * D;
+    float* ml = mm + CONSUMER_WARPS * MAX_GROUP;
+    float* wts = ml + CONSUMER_WARPS * MAX_GROUP;  // [W][MAX_SPLITS]
+
+    const long long bh = (long long)b * p.Hkv + h;
+    const long long pbase = (bh * p.num_splits + split) * G;  // row index into the partials
+    for (int idx = threadIdx.x; idx < G * D; idx += CONSUMER_THREADS) {
+        const int r = idx / D, d = idx - r * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < CONSUMER_WARPS; ++w) M = fmaxf(M, mm[w * MAX_GROUP + r]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < CONSUMER_WARPS; ++w) {
+            const float mw = mm[w * MAX_GROUP + r];
+            const float wgt = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+            L += ml[w * MAX_GROUP + r] * wgt;
+            O += mo[(w * MAX_GROUP + r) * D + d] * wgt;
+        }
+        O *= out_scale;
+        if (n_splits == 1) {
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            p.out[(long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + d] = __float2half_rn(O * inv);
+        } else {
+            p.partial_o[(pbase + r) * D + d] = O;
+            if (d == 0) {
+                p.partial_ml[(pbase + r) * 2 + 0] = M;
+                p.partial_ml[(pbase + r) * 2 + 1] = L;
+            }
+        }
+    }
+    if (n_splits == 1) return;
+
+    // ------------------------------------------- last CTA of this (b, h) combines
+    __threadfence();
+    named_bar_sync(1, CONSUMER_THREADS);
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(&p.tickets[bh], 1);
+        const int last = (ticket == n_splits - 1);
+        if (last) p.tickets[bh] = 0;  // ready for the next launch on this workspace
+        *last_flag = last;
+    }
+    named_bar_sync(1, CONSUMER_THREADS);
+    if (!*last_flag) return;
+    __threadfence();
+
+    const long long rbase = bh * p.num_splits * G;
+    float* wrow = wts + warp * MAX_SPLITS;
+    for (int r = warp; r < G; r += CONSUMER_WARPS) {
+        float mx = -INFINITY;
+        for (int s = lane; s < n_splits; s += 32) mx = fmaxf(mx, __ldcg(&p.partial_ml[(rbase + (long long)s * G + r) * 2]));
+        mx = warp_max(mx);
+        float Ls = 0.f;
+        for (int s = lane; s < n_splits; s += 32) {
+            const float2 v = __ldcg(reinterpret_cast<const float2*>(&p.partial_ml[(rbase + (long long)s * G + r) * 2]));
+            const float w = (v.x == -INFINITY) ? 0.f : fast_exp2(v.x - mx);
+            Ls += v.y * w;
+            wrow[s] = w;
+        }
+        Ls = warp_sum(Ls);
+        __syncwarp();
+        if (lane < D / 4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float* src = p.partial_o + (rbase + r) * D + lane * 4;
+            const long long sstride = (long long)G * D;
+#pragma unroll 8
+            for (int s = 0; s < n_splits; ++s) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + s * sstride));
+                const float w = wrow[s];
+                acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+            }
+            const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+            __half2 lo = __floats2half2_rn(acc.x * inv, acc.y * inv);
+            __half2 hi = __floats2half2_rn(acc.z * inv, acc.w * inv);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(p.out + (long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + lane * 4) = pk;
+        }
+        __syncwarp();
+    }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace gqa
+}  // namespace skv

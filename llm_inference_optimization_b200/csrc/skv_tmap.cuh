@@ -96,4 +96,48 @@ inline int make_kv_tmap(CUtensorMap* out, KvMapPos* pos, const void* base, int e
     return SKV_OK;
 }
 
+// Where each logical coordinate of a paged 8-bit pool sits among tensor-map dimensions 1..3.
+struct PoolMapPos {
+    int slot, head, page;
+};
+
+// Map over a pool of 1-byte codes addressed as (page, head, slot, channel): rows of D bytes,
+// box = `box_slots` consecutive slots of one (page, head), 128-byte swizzle (D must be 128).
+inline int make_pool_tmap(CUtensorMap* out, PoolMapPos* pos, const void* base, int D, long long num_pages,
+                          long long Hkv, long long page_size, long long stride_page, long long stride_head,
+                          long long stride_slot, int box_slots) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(SKV_ERR_DRIVER, "cuTensorMapEncodeTiled entry point not available");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
+        return fail(SKV_ERR_BAD_ARG, "pool base pointer must be 16-byte aligned for TMA");
+    struct Dim {
+        int logical;  // 1 slot, 2 head, 3 page
+        unsigned long long size, stride_bytes;
+        unsigned box;
+    } d[3] = {
+        {1, (unsigned long long)page_size, (unsigned long long)stride_slot, (unsigned)box_slots},
+        {2, (unsigned long long)Hkv, (unsigned long long)stride_head, 1u},
+        {3, (unsigned long long)num_pages, (unsigned long long)stride_page, 1u},
+    };
+    for (auto& x : d) {
+        if (x.size == 1 && (x.stride_bytes == 0 || (x.stride_bytes & 15))) x.stride_bytes = 16;
+        if (x.stride_bytes == 0 || (x.stride_bytes & 15))
+            return fail(SKV_ERR_BAD_ARG, "pool stride of %llu bytes is not a positive multiple of 16", x.stride_bytes);
+    }
+    std::stable_sort(d, d + 3, [](const Dim& a, const Dim& b) { return a.stride_bytes < b.stride_bytes; });
+    cuuint64_t gdim[4] = {(cuuint64_t)D, d[0].size, d[1].size, d[2].size};
+    cuuint64_t gstr[3] = {d[0].stride_bytes, d[1].stride_bytes, d[2].stride_bytes};
+    cuuint32_t box[4] = {(cuuint32_t)D, d[0].box, d[1].box, d[2].box};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    for (int i = 0; i < 3; ++i) {
+        const int p = i + 1;
+        if (d[i].logical == 1) pos->slot = p; else if (d[i].logical == 2) pos->head = p; else pos->page = p;
+    }
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), gdim, gstr, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SKV_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return SKV_OK;
+}
+
 }  // namespace skv

@@ -1,0 +1,69 @@
+"""Dense decode over a paged INT8 / FP8 cache vs the oracle on the dequantised cache (max-abs <= 2e-3)."""
+import pytest
+import torch
+
+from llm_inference_optimization_b200 import _C, _workspace
+from oracle import skv_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def make_case(B, Hq, Hkv, T, fmt, seed, page_size=16, unit=False):
+    g = torch.Generator().manual_seed(seed)
+    D = 128
+    s = 1.0 if unit else D ** -0.5
+    Q = (torch.randn(B, Hq, D, generator=g) * s).half()
+    K = (torch.randn(B, Hkv, T, D, generator=g) * s).half()
+    V = (torch.randn(B, Hkv, T, D, generator=g) * s).half()
+    quant = oracle.quantize_e4m3 if fmt == "fp8" else oracle.quantize_int8
+    kc, ks = quant(K)
+    vc, vs = quant(V)
+    pps = T // page_size
+    perm = torch.randperm(B * pps + 5, generator=g)  # a few unused pages in the pool
+    kp, ksp, table = oracle.build_paged_cache(kc, ks, page_size, perm)
+    vp, vsp, _ = oracle.build_paged_cache(vc, vs, page_size, perm)
+    Kd, Vd = oracle.dequantize(kc, ks), oracle.dequantize(vc, vs)  # [B,Hkv,T,D] fp32
+    return Q, (kp, vp, ksp, vsp, table), (Kd.permute(0, 2, 1, 3), Vd.permute(0, 2, 1, 3))
+
+
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+@pytest.mark.parametrize("B,Hq,Hkv,T,lens", [(1, 32, 8, 4096, None), (3, 32, 8, 2048, [2048, 1, 1037]),
+                                             (2, 8, 2, 8192, [8192, 5000]), (1, 16, 1, 64, [17])])
+def test_paged_decode(cuda_device, fmt, B, Hq, Hkv, T, lens):
+    Q, pools, (Kd, Vd) = make_case(B, Hq, Hkv, T, fmt, seed=T + B)
+    kp, vp, ksp, vsp, table = (t.to(cuda_device) for t in pools)
+    sl = None if lens is None else torch.tensor(lens, dtype=torch.int32)
+    scale = 128 ** -0.5
+    out = _C.fused_gqa_paged(Q.to(cuda_device), kp, vp, ksp, vsp, table, None if sl is None else sl.to(cuda_device), scale)
+    torch.cuda.synchronize()
+    assert _workspace.status(_workspace.get("gqa", 0, cuda_device)) == 0
+    want = oracle.dense_gqa_decode(Q, Kd, Vd, scale, sl)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+def test_unit_variance_long_context(cuda_device, fmt):
+    """N(0,1) values at 64K tokens: exercises scale folding and the running-max rescale."""
+    Q, pools, (Kd, Vd) = make_case(1, 32, 8, 65536, fmt, seed=3, unit=True)
+    kp, vp, ksp, vsp, table = (t.to(cuda_device) for t in pools)
+    scale = 128 ** -0.5
+    out = _C.fused_gqa_paged(Q.to(cuda_device), kp, vp, ksp, vsp, table, None, scale)
+    want = oracle.dense_gqa_decode(Q, Kd, Vd, scale)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+def test_compacted_cache_without_page_table(cuda_device):
+    """The [B,H,keep,D] codes + [B,H,keep] scales an eviction produces are read as one page per sequence."""
+    g = torch.Generator().manual_seed(9)
+    B, Hq, Hkv, T = 2, 8, 2, 4160
+    Q = torch.randn(B, Hq, 128, generator=g).half()
+    K = torch.randn(B, Hkv, T, 128, generator=g).half()
+    V = torch.randn(B, Hkv, T, 128, generator=g).half()
+    kc, ks = oracle.quantize_int8(K)
+    vc, vs = oracle.quantize_int8(V)
+    out = _C.fused_gqa_paged(Q.to(cuda_device), kc.view(B, Hkv, T, 128).to(cuda_device), vc.to(cuda_device),
+                             ks.to(cuda_device), vs.to(cuda_device), None, None, 128 ** -0.5)
+    want = oracle.dense_gqa_decode(Q, oracle.dequantize(kc, ks).permute(0, 2, 1, 3),
+                                   oracle.dequantize(vc, vs).permute(0, 2, 1, 3), 128 ** -0.5)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
