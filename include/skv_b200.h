@@ -98,6 +98,34 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool,
 /* Ring depth of the 8-bit kernel (3..12 stages of 17 KB); process-wide.  No reference counterpart. */
 int skv_gqa_set_q8_stages(int stages);
 
+/* ---- Quest-style block-sparse decode over a paged 8-bit cache ----------------------
+ * No reference counterpart (the reference scores blocks by the mean of q.k over an unpaged fp16 cache,
+ * csrc/kernels/sparse_attention.cu:51-78).  Pools, scales, page_table, seq_lens as for skv_gqa_decode_paged.
+ * skv_quest_build_meta: meta_out fp16 [B, Hkv, nb, 2, D], nb = skv_quest_num_blocks(N, block_size): channel-wise
+ *   min ([..,0,:]) and max ([..,1,:]) of the dequantised keys (code * scale, fp32, rounded to fp16) of each block;
+ *   a ragged last block covers its valid tokens only.
+ * skv_quest_decode: block score for query head hq = scale * sum_d max(q_d*min_d, q_d*max_d) (fp32); the top_k_blocks
+ *   best blocks per query head (ties: lower block id) among the blocks the sequence has; out[b,hq,:] = exact softmax
+ *   attention over the tokens of those blocks (dequantised, fp32).  block_idx_out optional int32 [B,Hq,top_k_blocks],
+ *   ascending, -1 padded.  D = 128, Hq/Hkv <= 8, top_k_blocks <= 256, top_k_blocks*block_size <= 4096.
+ *   Workspace holds fp32 block scores [B,Hq,nb]. */
+int skv_quest_num_blocks(int N, int block_size);
+size_t skv_quest_workspace_bytes(int B, int Hq, int N, int block_size);
+int skv_quest_build_meta(const void* k_pool, const float* k_scale_pool, const int* page_table, const int* seq_lens,
+                         void* meta_out, int B, int N, int Hkv, int D, int kv_dtype, int block_size,
+                         int page_size, int max_pages,
+                         long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
+                         long long scale_stride_page, long long scale_stride_head, int device, void* stream);
+int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool,
+                     const float* k_scale_pool, const float* v_scale_pool,
+                     const int* page_table, const int* seq_lens, const void* meta,
+                     void* out, int* block_idx_out, void* workspace, size_t workspace_bytes,
+                     int B, int N, int Hq, int Hkv, int D, int kv_dtype,
+                     int block_size, int top_k_blocks, int page_size, int max_pages,
+                     long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
+                     long long scale_stride_page, long long scale_stride_head,
+                     float scale, int device, void* stream);
+
 /* ---- token-sparse decode ----------------------------------------------------------
  * Replaces kv_evict_quant_forward(Q, K, V, top_k, use_int8=false)  (csrc/kernels/kv_evict_quant.cu:272-364,
  * bound in csrc/pybind/bindings.cpp:28) with the arithmetic of _reference_sparse_attention

@@ -1,0 +1,420 @@
+// Quest-style block-sparse decode over a paged 8-bit KV cache.
+//
+// No reference counterpart: the reference's block-sparse kernel scores blocks by
+// the mean of q.k over all keys of an unpaged fp16 cache
+// (csrc/kernels/sparse_attention.cu:51-78).  Here, per block of `block_size`
+// tokens and kv-head, the channel-wise min and max of the dequantised keys are
+// kept as metadata; a block's score for a query head is the upper bound
+//     scale * sum_d max(q_d * min_d, q_d * max_d)
+// of scale * q.k over the block; the top_k_blocks best blocks are chosen per
+// QUERY head (ties: lower block) and exact softmax attention runs over the tokens
+// of the chosen blocks only, gathered page by page.
+//
+// Kernels:
+//   block_meta_build_kernel  -- cache maintenance: one warp per (b, kv-head,
+//       block) reads the block's codes and scales once and writes min|max fp16.
+//   quest_scores_kernel      -- streams the metadata (HBM-bound), D/8 lanes per
+//       block, all G query heads of the group scored from one read.
+//   quest_select_attend_kernel -- one CTA per (b, query head): exact top-k over
+//       the block scores, then scores / softmax / weighted value sum over the
+//       <= k * block_size gathered tokens, all fp32.
+#include <cuda_fp8.h>
+
+#include "skv_common.cuh"
+#include "skv_select.cuh"
+
+namespace skv {
+namespace quest {
+
+constexpr int D = 128;
+constexpr int CH = 16;            // tokens per page chunk handled at a time
+constexpr int META_THREADS = 256;
+constexpr int SCORE_THREADS = 256;
+constexpr int ATT_THREADS = 256;
+constexpr int MAX_SEL_TOKENS = 4096;  // top_k_blocks * block_size upper bound
+constexpr int MAX_TOPK = 256;
+
+template <int KVT>
+__device__ __forceinline__ float code_to_float(uint32_t byte) {
+    if (KVT == SKV_KV_E4M3) {
+        const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)byte, __NV_E4M3);
+        return __half2float(*reinterpret_cast<const __half*>(&h));
+    }
+    return (float)(int)(int8_t)byte;
+}
+
+template <int KVT>
+__device__ __forceinline__ void unpack16(const uint4& raw, float (&x)[16]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) x[i] = code_to_float<KVT>((w[i >> 2] >> (8 * (i & 3))) & 0xFFu);
+}
+
+struct Pool {
+    const uint8_t* codes;   // element (page,h,slot,d) at page*sp + h*sh + slot*ss + d
+    const float* scales;    // element (page,h,slot) at page*csp + h*csh + slot
+    long long sp, sh, ss, csp, csh;
+};
+
+struct MetaParams {
+    Pool k;
+    const int* page_table;  // [B, max_pages] or null
+    const int* seq_lens;    // [B] or null
+    __half* meta;           // [B, Hkv, nb, 2, D]
+    int B, Hkv, N, nb, block_size, page_size, max_pages;
+};
+
+__device__ __forceinline__ int phys_page(const int* page_table, int b, int max_pages, int lp) {
+    return page_table ? __ldg(page_table + (long long)b * max_pages + lp) : b * max_pages + lp;
+}
+
+// one warp per (b, h, block); lanes: 8 per token row (16 codes each), 4 rows per step
+template <int KVT>
+__global__ void __launch_bounds__(META_THREADS)
+block_meta_build_kernel(const MetaParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane & 7, rw = lane >> 3;
+    const long long total = (long long)p.B * p.Hkv * p.nb;
+    for (long long item = (long long)blockIdx.x * (META_THREADS / 32) + warp; item < total;
+         item += (long long)gridDim.x * (META_THREADS / 32)) {
+        const int blk = (int)(item % p.nb);
+        const int h = (int)((item / p.nb) % p.Hkv);
+        const int b = (int)(item / ((long long)p.nb * p.Hkv));
+        const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
+        const int t0 = blk * p.block_size, t1 = min(len, t0 + p.block_size);
+        float lo[16], hi[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { lo[i] = INFINITY; hi[i] = -INFINITY; }
+        for (int t = t0 + rw; t < t1; t += 4) {
+            const int page = phys_page(p.page_table, b, p.max_pages, t / p.page_size), slot = t % p.page_size;
+            const uint4 raw = *reinterpret_cast<const uint4*>(p.k.codes + page * p.k.sp + h * p.k.sh + slot * p.k.ss + sub * 16);
+            const float s = p.k.scales[page * p.k.csp + h * p.k.csh + slot];
+            float x[16];
+            unpack16<KVT>(raw, x);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float v = x[i] * s;
+                lo[i] = fminf(lo[i], v);
+                hi[i] = fmaxf(hi[i], v);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            lo[i] = fminf(lo[i], __shfl_xor_sync(0xffffffffu, lo[i], 8));
+            hi[i] = fmaxf(hi[i], __shfl_xor_sync(0xffffffffu, hi[i], 8));
+            lo[i] = fminf(lo[i], __shfl_xor_sync(0xffffffffu, lo[i], 16));
+            hi[i] = fmaxf(hi[i], __shfl_xor_sync(0xffffffffu, hi[i], 16));
+        }
+        if (rw < 2) {  // row-group 0 writes the mins, row-group 1 the maxes
+            __half* dst = p.meta + (item * 2 + rw) * D + sub * 16;
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = rw == 0 ? pack_half2(lo[2 * i], lo[2 * i + 1]) : pack_half2(hi[2 * i], hi[2 * i + 1]);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+    }
+}
+
+struct ScoreParams {
+    const __half* q;      // [B, Hq, D]
+    const __half* meta;   // [B, Hkv, nb, 2, D]
+    float* scores;        // [B, Hq, nb]
+    int Hq, Hkv, G, nb;
+    float scale;
+};
+
+// grid (ceil(nb / blocks_per_cta), Hkv, B); 16 lanes per block (8 channels each), 2 blocks per warp step
+template <int MAXG>
+__global__ void __launch_bounds__(SCORE_THREADS)
+quest_scores_kernel(const ScoreParams p, int blocks_per_cta) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane & 15, rw = lane >> 4;
+    const int h = blockIdx.y, b = blockIdx.z;
+    float q[MAXG][8];
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) {
+        if (g < p.G) unpack8(*reinterpret_cast<const uint4*>(p.q + ((long long)b * p.Hq + h * p.G + g) * D + sub * 8), q[g]);
+        else
+#pragma unroll
+            for (int i = 0; i < 8; ++i) q[g][i] = 0.f;
+    }
+    const __half* mbase = p.meta + ((long long)b * p.Hkv + h) * p.nb * 2 * D + sub * 8;
+    const int j0 = blockIdx.x * blocks_per_cta, j1 = min(p.nb, j0 + blocks_per_cta);
+    for (int base = j0 + warp * 2; base < j1; base += (SCORE_THREADS / 32) * 2) {
+        const int j = base + rw;
+        float acc[MAXG];
+#pragma unroll
+        for (int g = 0; g < MAXG; ++g) acc[g] = 0.f;
+        if (j < j1) {
+            float lo[8], hi[8];
+            unpack8(*reinterpret_cast<const uint4*>(mbase + (long long)j * 2 * D), lo);
+            unpack8(*reinterpret_cast<const uint4*>(mbase + (long long)j * 2 * D + D), hi);
+#pragma unroll
+            for (int g = 0; g < MAXG; ++g)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[g] += fmaxf(q[g][i] * lo[i], q[g][i] * hi[i]);
+        }
+#pragma unroll
+        for (int g = 0; g < MAXG; ++g) {
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], o);
+        }
+        if (j < j1 && sub == 0) {
+#pragma unroll
+            for (int g = 0; g < MAXG; ++g)
+                if (g < p.G) p.scores[((long long)b * p.Hq + h * p.G + g) * p.nb + j] = acc[g] * p.scale;
+        }
+    }
+}
+
+struct AttendParams {
+    const __half* q;       // [B, Hq, D]
+    const float* scores;   // [B, Hq, nb]
+    Pool k, v;
+    const int* page_table;
+    const int* seq_lens;
+    __half* out;           // [B, Hq, D]
+    int* block_idx;        // optional [B, Hq, top_k]
+    int Hq, G, N, nb, block_size, page_size, max_pages, top_k;
+    float scale;
+};
+
+// grid (B * Hq)
+template <int KVT>
+__global__ void __launch_bounds__(ATT_THREADS)
+quest_select_attend_kernel(const AttendParams p) {
+    __shared__ uint32_t tk[TopkSmem<ATT_THREADS>::WORDS];
+    __shared__ int sel[MAX_TOPK];
+    __shared__ float w[MAX_SEL_TOKENS];
+    __shared__ float qs[D];
+    __shared__ float red[ATT_THREADS / 8 * 16 + 32];  // per row-group partial outputs are reduced through here
+    __shared__ float bcast[2];
+
+    const int row = blockIdx.x, hq = row % p.Hq, b = row / p.Hq, h = hq / p.G;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
+    const int nb = (len + p.block_size - 1) / p.block_size;  // blocks this sequence really has
+    const float* sc = p.scores + (long long)row * p.nb;
+    const int kk = min(p.top_k, nb);
+    block_topk_sorted<ATT_THREADS>(sc, nb, kk, sel, tk);
+    for (int i = tid; i < D; i += ATT_THREADS) qs[i] = __half2float(p.q[(long long)row * D + i]);
+    __syncthreads();
+    if (p.block_idx)
+        for (int i = tid; i < p.top_k; i += ATT_THREADS) p.block_idx[(long long)row * p.top_k + i] = i < kk ? sel[i] : -1;
+
+    // ---- scores of the gathered tokens: 8 lanes per token row, 32 rows per pass
+    const int sub = tid & 7, grp = tid >> 3;  // grp in [0, 32)
+    const int ntok = kk * p.block_size;
+    float qv[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) qv[i] = qs[sub * 16 + i];
+    float mx = -INFINITY;
+    for (int r0 = 0; r0 < ntok; r0 += ATT_THREADS / 8) {  // uniform trip count: the shuffles below need whole warps
+        const int r = r0 + grp;
+        int t = -1;
+        if (r < ntok) t = sel[r / p.block_size] * p.block_size + r % p.block_size;
+        const bool valid = t >= 0 && t < len;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        float ksc = 0.f;
+        if (valid) {
+            const int page = phys_page(p.page_table, b, p.max_pages, t / p.page_size), slot = t % p.page_size;
+            raw = *reinterpret_cast<const uint4*>(p.k.codes + page * p.k.sp + h * p.k.sh + slot * p.k.ss + sub * 16);
+            ksc = p.k.scales[page * p.k.csp + h * p.k.csh + slot];
+        }
+        float x[16];
+        unpack16<KVT>(raw, x);
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) d = fmaf(x[i], qv[i], d);
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        d += __shfl_xor_sync(0xffffffffu, d, 4);
+        const float s = valid ? d * ksc * p.scale : -INFINITY;
+        if (sub == 0 && r < ntok) w[r] = s;
+        mx = fmaxf(mx, s);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    if (warp == 0) {
+        float m2 = lane < ATT_THREADS / 32 ? red[lane] : -INFINITY;
+        m2 = warp_max(m2);
+        if (lane == 0) bcast[0] = m2;
+    }
+    __syncthreads();
+    mx = bcast[0];
+    float sum = 0.f;
+    for (int r = tid; r < ntok; r += ATT_THREADS) {
+        const float e = w[r] == -INFINITY ? 0.f : __expf(w[r] - mx);
+        w[r] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    __syncthreads();
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (warp == 0) {
+        float s2 = lane < ATT_THREADS / 32 ? red[lane] : 0.f;
+        s2 = warp_sum(s2);
+        if (lane == 0) bcast[1] = s2;
+    }
+    __syncthreads();
+    const float inv = bcast[1] > 0.f ? 1.f / bcast[1] : 0.f;
+
+    // ---- out = sum_t p_t * vs_t * vc_t
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+    for (int r = grp; r < ntok; r += ATT_THREADS / 8) {
+        const int t = sel[r / p.block_size] * p.block_size + r % p.block_size;
+        if (t < len) {
+            const int page = phys_page(p.page_table, b, p.max_pages, t / p.page_size), slot = t % p.page_size;
+            const uint4 raw = *reinterpret_cast<const uint4*>(p.v.codes + page * p.v.sp + h * p.v.sh + slot * p.v.ss + sub * 16);
+            const float wt = w[r] * p.v.scales[page * p.v.csp + h * p.v.csh + slot];
+            float x[16];
+            unpack16<KVT>(raw, x);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = fmaf(wt, x[i], acc[i]);
+        }
+    }
+    // reduce the 32 row-groups: first inside each warp (4 groups), then across the 8 warps through shared memory
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 8);
+        acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 16);
+    }
+    __syncthreads();
+    float* part = w;  // the token weights are no longer needed: reuse as [8 warps][D]
+    if (lane < 8) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) part[warp * D + sub * 16 + i] = acc[i];
+    }
+    __syncthreads();
+    for (int d = tid; d < D; d += ATT_THREADS) {
+        float o = 0.f;
+#pragma unroll
+        for (int w2 = 0; w2 < ATT_THREADS / 32; ++w2) o += part[w2 * D + d];
+        p.out[(long long)row * D + d] = __float2half_rn(o * inv);
+    }
+}
+
+}  // namespace quest
+}  // namespace skv
+
+using namespace skv;
+
+static int check_pool_args(const void* codes, const float* scales, int page_size, long long ss, const char* what) {
+    if (!codes || !scales) return fail(SKV_ERR_BAD_ARG, "%s: null pool pointer", what);
+    if (page_size <= 0) return fail(SKV_ERR_BAD_ARG, "%s: page_size must be positive", what);
+    if (reinterpret_cast<uintptr_t>(codes) & 15) return fail(SKV_ERR_BAD_ARG, "%s: code pool must be 16-byte aligned", what);
+    if (ss % 16) return fail(SKV_ERR_BAD_ARG, "%s: slot stride must be a multiple of 16 bytes", what);
+    return SKV_OK;
+}
+
+extern "C" {
+
+// Number of metadata blocks for a cache of N tokens.
+int skv_quest_num_blocks(int N, int block_size) { return (N <= 0 || block_size <= 0) ? 0 : (N + block_size - 1) / block_size; }
+
+size_t skv_quest_workspace_bytes(int B, int Hq, int N, int block_size) {
+    const int nb = skv_quest_num_blocks(N, block_size);
+    if (B <= 0 || Hq <= 0 || nb <= 0) return 0;
+    return 256 + (((size_t)B * Hq * nb * sizeof(float) + 255) & ~size_t(255));
+}
+
+int skv_quest_build_meta(const void* k_pool, const float* k_scale_pool, const int* page_table, const int* seq_lens,
+                         void* meta_out, int B, int N, int Hkv, int D, int kv_dtype, int block_size, int page_size,
+                         int max_pages, long long pool_stride_page, long long pool_stride_head,
+                         long long pool_stride_slot, long long scale_stride_page, long long scale_stride_head,
+                         int device, void* stream) {
+    if (!meta_out) return fail(SKV_ERR_BAD_ARG, "skv_quest_build_meta: null output");
+    int rc = check_pool_args(k_pool, k_scale_pool, page_size, pool_stride_slot, "skv_quest_build_meta");
+    if (rc) return rc;
+    if (B <= 0 || N <= 0 || Hkv <= 0 || block_size <= 0 || max_pages <= 0)
+        return fail(SKV_ERR_BAD_ARG, "skv_quest_build_meta: sizes must be positive");
+    if (D != quest::D) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (128)", D);
+    if (kv_dtype != SKV_KV_I8 && kv_dtype != SKV_KV_E4M3) return fail(SKV_ERR_UNSUPPORTED, "kv_dtype %d is not an 8-bit type", kv_dtype);
+    if ((long long)max_pages * page_size < N) return fail(SKV_ERR_BAD_ARG, "max_pages * page_size < N");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
+    quest::MetaParams p;
+    p.k.codes = static_cast<const uint8_t*>(k_pool); p.k.scales = k_scale_pool;
+    p.k.sp = pool_stride_page; p.k.sh = pool_stride_head; p.k.ss = pool_stride_slot;
+    p.k.csp = scale_stride_page; p.k.csh = scale_stride_head;
+    p.page_table = page_table; p.seq_lens = seq_lens; p.meta = static_cast<__half*>(meta_out);
+    p.B = B; p.Hkv = Hkv; p.N = N; p.nb = skv_quest_num_blocks(N, block_size);
+    p.block_size = block_size; p.page_size = page_size; p.max_pages = max_pages;
+    const long long items = (long long)B * Hkv * p.nb;
+    long long blocks = (items + quest::META_THREADS / 32 - 1) / (quest::META_THREADS / 32);
+    const long long cap = (long long)sm_count(device) * 16;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (kv_dtype == SKV_KV_E4M3) quest::block_meta_build_kernel<SKV_KV_E4M3><<<(unsigned)blocks, quest::META_THREADS, 0, st>>>(p);
+    else quest::block_meta_build_kernel<SKV_KV_I8><<<(unsigned)blocks, quest::META_THREADS, 0, st>>>(p);
+    SKV_CUDA_TRY(cudaGetLastError());
+    return SKV_OK;
+}
+
+int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, const float* k_scale_pool,
+                     const float* v_scale_pool, const int* page_table, const int* seq_lens, const void* meta,
+                     void* out, int* block_idx_out, void* workspace, size_t workspace_bytes, int B, int N, int Hq,
+                     int Hkv, int D, int kv_dtype, int block_size, int top_k_blocks, int page_size, int max_pages,
+                     long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
+                     long long scale_stride_page, long long scale_stride_head, float scale, int device, void* stream) {
+    if (!q || !meta || !out) return fail(SKV_ERR_BAD_ARG, "skv_quest_decode: null tensor pointer");
+    int rc = check_pool_args(k_pool, k_scale_pool, page_size, pool_stride_slot, "skv_quest_decode");
+    if (rc) return rc;
+    rc = check_pool_args(v_pool, v_scale_pool, page_size, pool_stride_slot, "skv_quest_decode");
+    if (rc) return rc;
+    if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || max_pages <= 0) return fail(SKV_ERR_BAD_ARG, "skv_quest_decode: sizes must be positive");
+    if (Hq % Hkv != 0) return fail(SKV_ERR_BAD_ARG, "Hq=%d must be divisible by Hkv=%d", Hq, Hkv);
+    const int G = Hq / Hkv;
+    if (G > 8) return fail(SKV_ERR_UNSUPPORTED, "group size %d exceeds 8", G);
+    if (D != quest::D) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (128)", D);
+    if (kv_dtype != SKV_KV_I8 && kv_dtype != SKV_KV_E4M3) return fail(SKV_ERR_UNSUPPORTED, "kv_dtype %d is not an 8-bit type", kv_dtype);
+    if (block_size <= 0 || top_k_blocks <= 0) return fail(SKV_ERR_BAD_ARG, "block_size and top_k_blocks must be positive");
+    if (top_k_blocks > quest::MAX_TOPK || (long long)top_k_blocks * block_size > quest::MAX_SEL_TOKENS)
+        return fail(SKV_ERR_UNSUPPORTED, "top_k_blocks * block_size = %lld exceeds %d tokens (or %d blocks)",
+                    (long long)top_k_blocks * block_size, quest::MAX_SEL_TOKENS, quest::MAX_TOPK);
+    if ((long long)max_pages * page_size < N) return fail(SKV_ERR_BAD_ARG, "max_pages * page_size < N");
+    if (Hkv > 65535 || B > 65535) return fail(SKV_ERR_UNSUPPORTED, "grid dimension too large");
+    const size_t need = skv_quest_workspace_bytes(B, Hq, N, block_size);
+    if (!workspace || workspace_bytes < need)
+        return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, need);
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int nb = skv_quest_num_blocks(N, block_size);
+
+    quest::ScoreParams sp;
+    sp.q = static_cast<const __half*>(q);
+    sp.meta = static_cast<const __half*>(meta);
+    sp.scores = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
+    sp.Hq = Hq; sp.Hkv = Hkv; sp.G = G; sp.nb = nb; sp.scale = scale;
+    const long long rows = (long long)B * Hkv;
+    long long want = ((long long)sm_count(device) * 8 + rows - 1) / rows;
+    int blocks_per_cta = (int)((nb + want - 1) / want);
+    blocks_per_cta = ((blocks_per_cta + 15) / 16) * 16;
+    dim3 g1((nb + blocks_per_cta - 1) / blocks_per_cta, Hkv, B);
+    if (G <= 4) quest::quest_scores_kernel<4><<<g1, quest::SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);
+    else quest::quest_scores_kernel<8><<<g1, quest::SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);
+    SKV_CUDA_TRY(cudaGetLastError());
+
+    quest::AttendParams ap;
+    ap.q = sp.q; ap.scores = sp.scores;
+    ap.k.codes = static_cast<const uint8_t*>(k_pool); ap.k.scales = k_scale_pool;
+    ap.v.codes = static_cast<const uint8_t*>(v_pool); ap.v.scales = v_scale_pool;
+    ap.k.sp = ap.v.sp = pool_stride_page; ap.k.sh = ap.v.sh = pool_stride_head; ap.k.ss = ap.v.ss = pool_stride_slot;
+    ap.k.csp = ap.v.csp = scale_stride_page; ap.k.csh = ap.v.csh = scale_stride_head;
+    ap.page_table = page_table; ap.seq_lens = seq_lens;
+    ap.out = static_cast<__half*>(out); ap.block_idx = block_idx_out;
+    ap.Hq = Hq; ap.G = G; ap.N = N; ap.nb = nb; ap.block_size = block_size; ap.page_size = page_size;
+    ap.max_pages = max_pages; ap.top_k = top_k_blocks; ap.scale = scale;
+    if (kv_dtype == SKV_KV_E4M3) quest::quest_select_attend_kernel<SKV_KV_E4M3><<<(unsigned)(B * Hq), quest::ATT_THREADS, 0, st>>>(ap);
+    else quest::quest_select_attend_kernel<SKV_KV_I8><<<(unsigned)(B * Hq), quest::ATT_THREADS, 0, st>>>(ap);
+    SKV_CUDA_TRY(cudaGetLastError());
+    return SKV_OK;
+}
+
+}  // extern "C"

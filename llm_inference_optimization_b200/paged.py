@@ -1,0 +1,101 @@
+"""Paged 8-bit KV cache: container, block metadata and Quest-style sparse decode.
+
+No counterpart in the reference, whose caches are unpaged fp16 tensors; the layout is
+code pools ``[num_pages, Hkv, page_size, D]`` (int8 or float8_e4m3fn), fp32 scale pools
+``[num_pages, Hkv, page_size]`` and an int32 ``page_table [B, max_pages]``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+from torch import Tensor
+
+from . import _C, _lib, _workspace
+
+
+@dataclass
+class PagedKV:
+    k_pool: Tensor
+    v_pool: Tensor
+    k_scale: Tensor
+    v_scale: Tensor
+    page_table: Tensor | None   # int32 [B, max_pages]; None: sequence b owns pages b*max_pages ...
+    seq_lens: Tensor | None     # int32 [B]
+    batch: int
+
+    @property
+    def page_size(self) -> int:
+        return self.k_pool.shape[2]
+
+    @property
+    def max_pages(self) -> int:
+        return self.page_table.shape[1] if self.page_table is not None else self.k_pool.shape[0] // self.batch
+
+    @property
+    def capacity(self) -> int:
+        return self.max_pages * self.page_size
+
+    def decode(self, Q: Tensor, scale: float, max_seq_len: int | None = None) -> Tensor:
+        """Dense GQA decode over the whole cache (``_C.fused_gqa_paged``)."""
+        return _C.fused_gqa_paged(Q, self.k_pool, self.v_pool, self.k_scale, self.v_scale, self.page_table,
+                                  self.seq_lens, scale, max_seq_len=max_seq_len)
+
+
+def _pool_args(kv: PagedKV):
+    kp, ks = kv.k_pool, kv.k_scale
+    _C._require(kp.is_cuda and kp.dim() == 4 and kp.stride(-1) == 1 and kv.v_pool.shape == kp.shape
+                and kv.v_pool.stride() == kp.stride(), "pools must be CUDA [num_pages,Hkv,page_size,D] with one layout")
+    _C._require(ks.dtype == torch.float32 and ks.shape == kp.shape[:3] and ks.stride(-1) == 1
+                and kv.v_scale.stride() == ks.stride(), "scale pools must be fp32 [num_pages,Hkv,page_size]")
+    return (kp.stride(0), kp.stride(1), kp.stride(2), ks.stride(0), ks.stride(1))
+
+
+def build_block_meta(kv: PagedKV, block_size: int = 64, max_seq_len: int | None = None) -> Tensor:
+    """Channel-wise min/max of the dequantised keys per block: fp16 ``[B, Hkv, nb, 2, D]``."""
+    strides = _pool_args(kv)
+    lib = _lib.load()
+    _, Hkv, P, D = kv.k_pool.shape
+    N = int(max_seq_len) if max_seq_len is not None else kv.capacity
+    nb = lib.skv_quest_num_blocks(N, block_size)
+    meta = torch.empty((kv.batch, Hkv, nb, 2, D), dtype=torch.float16, device=kv.k_pool.device)
+    dev = _C._dev_index(kv.k_pool)
+    rc = lib.skv_quest_build_meta(
+        kv.k_pool.data_ptr(), kv.k_scale.data_ptr(), None if kv.page_table is None else kv.page_table.data_ptr(),
+        None if kv.seq_lens is None else kv.seq_lens.data_ptr(), meta.data_ptr(), kv.batch, N, Hkv, D,
+        _C._code_dtype(kv.k_pool), int(block_size), P, kv.max_pages, *strides, dev,
+        torch.cuda.current_stream(kv.k_pool.device).cuda_stream)
+    _lib.check(rc, "build_block_meta")
+    return meta
+
+
+def quest_sparse_decode(Q: Tensor, kv: PagedKV, meta: Tensor, scale: float, block_size: int = 64,
+                        top_k_blocks: int = 8, max_seq_len: int | None = None, return_indices: bool = False):
+    """Top-k block-sparse decode with the min/max upper-bound score, exact attention inside the chosen blocks.
+
+    Q ``[B,Hq,D]`` fp16 -> ``[B,Hq,D]`` fp16 (and the chosen block ids ``[B,Hq,top_k_blocks]`` int32).
+    """
+    strides = _pool_args(kv)
+    _C._require(Q.is_cuda and Q.dtype == torch.float16 and Q.dim() == 3 and Q.is_contiguous(),
+                "Q must be a contiguous fp16 CUDA tensor [B,Hq,D]")
+    B, Hq, D = Q.shape
+    _, Hkv, P, _ = kv.k_pool.shape
+    _C._require(B == kv.batch, "batch mismatch between Q and the cache")
+    lib = _lib.load()
+    N = int(max_seq_len) if max_seq_len is not None else kv.capacity
+    nb = lib.skv_quest_num_blocks(N, block_size)
+    _C._require(meta.dtype == torch.float16 and meta.shape == (B, Hkv, nb, 2, D) and meta.is_contiguous(),
+                "meta must be fp16 [B,Hkv,nb,2,D] built with the same block_size and max_seq_len")
+    out = torch.empty((B, Hq, D), dtype=torch.float16, device=Q.device)
+    idx = torch.empty((B, Hq, top_k_blocks), dtype=torch.int32, device=Q.device) if return_indices else None
+    ws = _workspace.get("quest", lib.skv_quest_workspace_bytes(B, Hq, N, block_size), Q.device)
+    dev = _C._dev_index(Q)
+    rc = lib.skv_quest_decode(
+        Q.data_ptr(), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.k_scale.data_ptr(), kv.v_scale.data_ptr(),
+        None if kv.page_table is None else kv.page_table.data_ptr(),
+        None if kv.seq_lens is None else kv.seq_lens.data_ptr(), meta.data_ptr(), out.data_ptr(),
+        None if idx is None else idx.data_ptr(), ws.data_ptr(), ws.numel(), B, N, Hq, Hkv, D,
+        _C._code_dtype(kv.k_pool), int(block_size), int(top_k_blocks), P, kv.max_pages, *strides, float(scale), dev,
+        torch.cuda.current_stream(Q.device).cuda_stream)
+    _lib.check(rc, "quest_sparse_decode")
+    return (out, idx) if return_indices else out

@@ -54,3 +54,33 @@ def eviction(B: int = 4, H: int = 8, T: int = 32768, D: int = 128, rounds: int =
     for _ in range(rounds):
         scores += torch.softmax(2.0 * torch.randn(B, H, T, generator=g), dim=-1)
     return K.half(), V.half(), scores
+
+
+def planted_block_cache(B: int, Hq: int, Hkv: int, T: int, D: int = 128, block_size: int = 64, planted: int = 8,
+                        cosine: float = 0.9, seed: int = 3):
+    """Q [B,Hq,D], K/V [B,Hkv,T,D] ~ N(0,1) (fp16) with `planted` high-affinity blocks per (b, kv-head).
+
+    Every key of a planted block is re-aimed at the normalised sum of the group's queries with the given
+    cosine, keeping its norm.  Returns (Q, K, V, planted_block_ids [B,Hkv,planted]).
+    """
+    g = _gen(seed)
+    G = Hq // Hkv
+    nb = T // block_size
+    Q = torch.randn(B, Hq, D, generator=g)
+    K = torch.randn(B, Hkv, T, D, generator=g)
+    V = torch.randn(B, Hkv, T, D, generator=g)
+    ids = torch.empty(B, Hkv, planted, dtype=torch.long)
+    sin = math.sqrt(1.0 - cosine * cosine)
+    for b in range(B):
+        for h in range(Hkv):
+            u = Q[b, h * G:(h + 1) * G].sum(0)
+            u = u / u.norm()
+            blocks = torch.randperm(nb, generator=g)[:planted]
+            ids[b, h] = blocks.sort().values
+            for j in blocks.tolist():
+                k = K[b, h, j * block_size:(j + 1) * block_size]
+                norm = k.norm(dim=-1, keepdim=True)
+                orth = k - (k @ u)[:, None] * u
+                orth = orth / orth.norm(dim=-1, keepdim=True)
+                K[b, h, j * block_size:(j + 1) * block_size] = norm * (cosine * u + sin * orth)
+    return Q.half(), K.half(), V.half(), ids

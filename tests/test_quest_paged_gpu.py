@@ -1,0 +1,83 @@
+"""Quest-style block-sparse decode over a paged FP8 / INT8 cache: metadata, block sets and outputs vs the oracle."""
+import pytest
+import torch
+
+from llm_inference_optimization_b200 import paged, workloads
+from oracle import skv_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def paged_case(Q, K, V, fmt, dev, seed, page_size=16, seq_lens=None):
+    quant = oracle.quantize_e4m3 if fmt == "fp8" else oracle.quantize_int8
+    kc, ks = quant(K)
+    vc, vs = quant(V)
+    B, Hkv, T, D = K.shape
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(B * (T // page_size) + 3, generator=g)
+    kp, ksp, table = oracle.build_paged_cache(kc, ks, page_size, perm)
+    vp, vsp, _ = oracle.build_paged_cache(vc, vs, page_size, perm)
+    kv = paged.PagedKV(kp.to(dev), vp.to(dev), ksp.to(dev), vsp.to(dev), table.to(dev),
+                       None if seq_lens is None else seq_lens.to(dev), B)
+    return kv, oracle.dequantize(kc, ks), oracle.dequantize(vc, vs)
+
+
+def score_gap(scores, k):
+    if k >= scores.shape[-1]:
+        return 1.0
+    v = scores.topk(k + 1, -1).values
+    return (v[..., k - 1] - v[..., k]).min().item()
+
+
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+@pytest.mark.parametrize("B,Hq,Hkv,T,bs,k", [(2, 32, 8, 8192, 64, 8), (1, 8, 2, 1024, 64, 4), (1, 4, 4, 512, 32, 16)])
+def test_meta_blocks_and_outputs(cuda_device, fmt, B, Hq, Hkv, T, bs, k):
+    Q, K, V, _ = workloads.planted_block_cache(B, Hq, Hkv, T, block_size=bs, planted=min(8, T // bs))
+    kv, Kd, Vd = paged_case(Q, K, V, fmt, cuda_device, seed=T)
+    meta = paged.build_block_meta(kv, bs)
+    want_meta = oracle.block_minmax_meta(Kd, bs)
+    assert torch.equal(meta.cpu(), want_meta)                     # metadata bit-exact
+    scale = 128 ** -0.5
+    out, idx = paged.quest_sparse_decode(Q.to(cuda_device), kv, meta, scale, bs, k, return_indices=True)
+    sc = oracle.quest_block_scores(Q, want_meta, scale)
+    blocks = oracle.topk_blocks(sc, k)
+    if score_gap(sc, k) > 1e-5:
+        assert torch.equal(idx.cpu().long(), blocks)              # block sets bit-exact
+    want = oracle.attend_selected_blocks(Q, Kd, Vd, idx.cpu().long(), bs, scale)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+def test_ragged_sequences(cuda_device):
+    B, Hq, Hkv, T, bs, k = 3, 8, 2, 2048, 64, 8
+    Q, K, V, _ = workloads.planted_block_cache(B, Hq, Hkv, T, seed=17)
+    lens = torch.tensor([2048, 100, 1000], dtype=torch.int32)   # 100 < one k*bs window; 1000 ends mid-block
+    kv, Kd, Vd = paged_case(Q, K, V, "fp8", cuda_device, seed=5, seq_lens=lens)
+    meta = paged.build_block_meta(kv, bs)
+    scale = 128 ** -0.5
+    out, idx = paged.quest_sparse_decode(Q.to(cuda_device), kv, meta, scale, bs, k, return_indices=True)
+    idx = idx.cpu().long()
+    for b in range(B):
+        n = int(lens[b])
+        nb = (n + bs - 1) // bs
+        m = oracle.block_minmax_meta(Kd[b:b + 1, :, :n], bs)
+        assert torch.equal(meta[b:b + 1, :, :nb].cpu(), m)
+        sc = oracle.quest_block_scores(Q[b:b + 1], m, scale)
+        kk = min(k, nb)
+        if score_gap(sc, kk) > 1e-5:
+            assert torch.equal(idx[b:b + 1, :, :kk], oracle.topk_blocks(sc, kk))
+        assert (idx[b, :, kk:] == -1).all()
+    want = oracle.attend_selected_blocks(Q, Kd, Vd, idx, bs, scale, lens)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+def test_exact_when_every_block_is_selected(cuda_device):
+    """With top_k_blocks >= number of blocks the sparse path must equal dense attention."""
+    Q, K, V, _ = workloads.planted_block_cache(1, 8, 2, 1024, seed=23)
+    kv, Kd, Vd = paged_case(Q, K, V, "int8", cuda_device, seed=1)
+    meta = paged.build_block_meta(kv, 64)
+    out = paged.quest_sparse_decode(Q.to(cuda_device), kv, meta, 128 ** -0.5, 64, 16)
+    want = oracle.dense_gqa_decode(Q, Kd.permute(0, 2, 1, 3), Vd.permute(0, 2, 1, 3), 128 ** -0.5)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+    dense = kv.decode(Q.to(cuda_device), 128 ** -0.5)
+    assert (out.float() - dense.float()).abs().max().item() <= TOL
