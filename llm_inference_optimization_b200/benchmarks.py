@@ -1,0 +1,180 @@
+"""Kernel-level sweep of the decode path on one B200: the counterpart of the reference's
+``benchmarks/run_benchmarks.py`` (its 4K-128K sweep at B=1, H=32, D=128, :22-80) for the kernels here.
+
+    python -m llm_inference_optimization_b200.benchmarks [--only dense,paged,token,block,evict,quest] [--iters 20]
+
+Prints one JSON line per (workload, size): median CUDA-event time of the whole operator (all of its
+launches), the algorithmic bytes, GB/s and the fraction of the measured HBM copy bandwidth.  Inputs are
+generated on the device (seeded); before every timed call a 512 MB buffer is READ, which replaces the L2
+contents with clean lines (a written buffer would leave dirty lines whose write-back competes with the call).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import statistics
+import sys
+from pathlib import Path
+
+import torch
+
+from . import _C, eviction, paged
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def hbm_peak() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class Timer:
+    def __init__(self, dev, iters):
+        self.dev, self.iters = dev, iters
+        self.flush_buf = torch.zeros(128 << 20, dtype=torch.int32, device=dev)
+
+    def __call__(self, fn, warmup=3):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize(self.dev)
+        times = []
+        for _ in range(self.iters):
+            self.flush_buf.max()  # a read-only pass over 512 MB: evicts the previous call's data, leaves L2 clean
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize(self.dev)
+            times.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(times), min(times)
+
+
+def emit(name, cfg, us, us_min, nbytes, peak, peak_kind, **extra):
+    gbs = nbytes / us / 1e3
+    line = {"workload": name, **cfg, "us": round(us, 2), "us_min": round(us_min, 2), "algorithmic_MB": round(nbytes / 1e6, 2),
+            "GBps": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3), "peak_GBps": peak, "peak_source": peak_kind, **extra}
+    print(json.dumps(line), flush=True)
+
+
+def randn16(shape, dev, g, scale=1.0):
+    return (torch.randn(shape, device=dev, generator=g, dtype=torch.float32) * scale).half()
+
+
+def random_pools(num_pages, Hkv, P, D, dev, g, fp8=True):
+    codes = torch.randint(0, 256, (num_pages, Hkv, P, D), device=dev, generator=g, dtype=torch.uint8)
+    if fp8:
+        codes = torch.where((codes & 0x7F) == 0x7F, codes & 0xFE, codes)  # no NaN patterns
+        codes = codes.view(torch.float8_e4m3fn)
+    else:
+        codes = codes.view(torch.int8)
+    scales = torch.rand((num_pages, Hkv, P), device=dev, generator=g, dtype=torch.float32) * 0.01 + 0.005
+    return codes, scales
+
+
+def bench_dense(t, dev, g, peak, pk):
+    D, Hq, Hkv = 128, 32, 8
+    for N in (4096, 16384, 65536, 131072):
+        Q = randn16((1, Hq, D), dev, g, D ** -0.5)
+        K = randn16((1, N, Hkv, D), dev, g, D ** -0.5)
+        V = randn16((1, N, Hkv, D), dev, g, D ** -0.5)
+        out = torch.empty_like(Q)
+        us, mn = t(lambda: _C.fused_gqa(Q, K, V, D ** -0.5, out=out))
+        emit("dense_gqa_f16", {"B": 1, "Hq": Hq, "Hkv": Hkv, "D": D, "ctx": N}, us, mn, 2 * N * Hkv * D * 2, peak, pk)
+        del K, V
+
+
+def bench_paged(t, dev, g, peak, pk):
+    D, Hq, Hkv, P = 128, 32, 8, 16
+    for fp8 in (True, False):
+        for B, N in ((1, 65536), (1, 131072), (16, 65536)):
+            pages = B * N // P
+            kp, ks = random_pools(pages, Hkv, P, D, dev, g, fp8)
+            vp, vs = random_pools(pages, Hkv, P, D, dev, g, fp8)
+            table = torch.randperm(pages, device=dev, generator=g).to(torch.int32).view(B, N // P)
+            Q = randn16((B, Hq, D), dev, g)
+            out = torch.empty_like(Q)
+            us, mn = t(lambda: _C.fused_gqa_paged(Q, kp, vp, ks, vs, table, None, D ** -0.5, out=out))
+            nbytes = 2 * B * N * Hkv * (D + 4)
+            emit("dense_gqa_paged_" + ("fp8" if fp8 else "int8"), {"B": B, "Hq": Hq, "Hkv": Hkv, "D": D, "ctx": N, "page": P},
+                 us, mn, nbytes, peak, pk)
+            del kp, vp, ks, vs
+
+
+def bench_token(t, dev, g, peak, pk):
+    D, H = 128, 32
+    for T in (4096, 16384, 65536, 131072):
+        Q, K, V = randn16((1, H, 1, D), dev, g), randn16((1, H, T, D), dev, g), randn16((1, H, T, D), dev, g)
+        us, mn = t(lambda: _C.token_sparse_decode(Q, K, V, 32, 4))
+        emit("token_sparse_top32", {"B": 1, "H": H, "D": D, "ctx": T, "top_k": 32, "sink": 4}, us, mn,
+             H * T * D * 2 + H * T * 4 + 36 * H * D * 2, peak, pk)
+        del K, V
+
+
+def bench_block(t, dev, g, peak, pk):
+    D, H = 128, 32
+    for T in (4096, 16384, 65536, 131072):
+        Q, K, V = randn16((1, H, 1, D), dev, g), randn16((1, H, T, D), dev, g), randn16((1, H, T, D), dev, g)
+        us, mn = t(lambda: _C.sparse_attention_forward(Q, K, V, 64, 8))
+        emit("block_sparse_mean_64x8", {"B": 1, "H": H, "D": D, "ctx": T, "block": 64, "top_k_blocks": 8}, us, mn,
+             H * T * D * 2 + H * 512 * D * 2, peak, pk)
+        del K, V
+
+
+def bench_evict(t, dev, g, peak, pk):
+    B, H, T, D, budget, recent = 4, 8, 32768, 128, 4096, 64
+    K, V = randn16((B, H, T, D), dev, g), randn16((B, H, T, D), dev, g)
+    scores = torch.rand((B, H, T), device=dev, generator=g, dtype=torch.float32)
+    keep = budget + recent
+    for quant in ("int8", "fp8"):
+        us, mn = t(lambda: eviction.fused_kv_evict(K, V, scores, budget, recent_tokens=recent, quant=quant, return_aux=True))
+        nbytes = B * H * T * 4 + 2 * B * H * keep * D * 2 + 2 * B * H * keep * D + 2 * B * H * keep * 4 + B * H * keep * 4
+        emit("kv_evict_quant_" + quant, {"B": B, "H": H, "T": T, "D": D, "budget": budget, "recent": recent}, us, mn, nbytes, peak, pk)
+
+
+def bench_quest(t, dev, g, peak, pk):
+    B, Hq, Hkv, D, T, P, bs, k = 8, 32, 8, 128, 131072, 16, 64, 8
+    pages = B * T // P
+    kp, ks = random_pools(pages, Hkv, P, D, dev, g, True)
+    vp, vs = random_pools(pages, Hkv, P, D, dev, g, True)
+    table = torch.randperm(pages, device=dev, generator=g).to(torch.int32).view(B, T // P)
+    kv = paged.PagedKV(kp, vp, ks, vs, table, None, B)
+    Q = randn16((B, Hq, D), dev, g)
+    us, mn = t(lambda: paged.build_block_meta(kv, bs))
+    emit("quest_build_meta_fp8", {"B": B, "Hkv": Hkv, "D": D, "ctx": T, "block": bs}, us, mn,
+         B * Hkv * T * (D + 4) + B * Hkv * (T // bs) * 2 * D * 2, peak, pk)
+    meta = paged.build_block_meta(kv, bs)
+    us, mn = t(lambda: paged.quest_sparse_decode(Q, kv, meta, D ** -0.5, bs, k))
+    nbytes = B * Hkv * (T // bs) * 2 * D * 2 + B * Hq * k * bs * 2 * (D + 4) + B * Hq * k * (bs // P) * 4
+    emit("quest_sparse_decode_fp8", {"B": B, "Hq": Hq, "Hkv": Hkv, "D": D, "ctx": T, "page": P, "block": bs, "top_k_blocks": k},
+         us, mn, nbytes, peak, pk)
+
+
+ALL = {"dense": bench_dense, "paged": bench_paged, "token": bench_token, "block": bench_block, "evict": bench_evict,
+       "quest": bench_quest}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=",".join(ALL))
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device: there is no CPU fallback")
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234)
+    peak, pk = hbm_peak()
+    t = Timer(dev, args.iters)
+    for name in args.only.split(","):
+        ALL[name.strip()](t, dev, g, peak, pk)
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

@@ -39,6 +39,9 @@ constexpr int CHUNK = 16;                                  // tokens per TMA box
 constexpr int Q8_CODE_BYTES = TILE * Q8_D;                 // 8 KB of K (or V) codes per stage
 constexpr int Q8_STAGE_BYTES = 2 * Q8_CODE_BYTES + 1024;   // + K scales [64] + V scales [64] (512 B, padded)
 constexpr float P_BOOST = 64.f;
+constexpr int Q8_WARPS = MAX_CONSUMER_WARPS;               // two groups of four: group g takes stages with it % 2 == g
+constexpr int Q8_CONSUMER_THREADS = Q8_WARPS * 32;
+constexpr int Q8_THREADS = Q8_CONSUMER_THREADS + 32;
 
 struct Q8Params {
     const __half* q;
@@ -62,22 +65,27 @@ struct Q8Params {
 
 static size_t q8_smem_bytes(int stages) {
     size_t ring = (size_t)stages * Q8_STAGE_BYTES;
-    size_t merge = merge_smem_bytes<Q8_D>();
+    size_t merge = merge_smem_bytes<Q8_D, Q8_WARPS>();
     return 1024 + (ring > merge ? ring : merge) + 2 * stages * 8 + 16;
 }
 
-// Two 8-bit codes in the low 16 bits -> two fp16 values (as a packed register).
+// Four 8-bit codes [c0,c1,c2,c3] in one register -> half2(c0,c1) and half2(c2,c3).
 template <int KVT>
-__device__ __forceinline__ uint32_t cvt_pair(uint32_t v16) {
+__device__ __forceinline__ void cvt_quad(uint32_t v, uint32_t& lo, uint32_t& hi) {
     if (KVT == SKV_KV_E4M3) {
-        const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v16 & 0xFFFFu), __NV_E4M3);
-        return (uint32_t)h.x | ((uint32_t)h.y << 16);
+        asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\t"
+            "cvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+            : "=r"(lo), "=r"(hi)
+            : "r"(v));
     } else {
         // int8 b -> fp16: 0x6400 | (b ^ 0x80) is exactly 1024 + (b + 128); subtract 1152
-        const uint32_t x = v16 ^ 0x8080u;
-        uint32_t h = __byte_perm(x, 0x64646464u, 0x4140);
-        const __half2 r = __hsub2(*reinterpret_cast<__half2*>(&h), __float2half2_rn(1152.f));
-        return *reinterpret_cast<const uint32_t*>(&r);
+        const uint32_t x = v ^ 0x80808080u;
+        uint32_t a = __byte_perm(x, 0x64646464u, 0x4140), b = __byte_perm(x, 0x64646464u, 0x4342);
+        const __half2 bias = __float2half2_rn(1152.f);
+        const __half2 ra = __hsub2(*reinterpret_cast<__half2*>(&a), bias);
+        const __half2 rb = __hsub2(*reinterpret_cast<__half2*>(&b), bias);
+        lo = *reinterpret_cast<const uint32_t*>(&ra);
+        hi = *reinterpret_cast<const uint32_t*>(&rb);
     }
 }
 
@@ -90,7 +98,7 @@ __device__ __forceinline__ void pool_tile_load(uint32_t dst, const CUtensorMap* 
 }
 
 template <int KVT>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(Q8_THREADS, 1)
 gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const Q8Params p) {
     constexpr int D = Q8_D;
@@ -110,7 +118,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t ring = smem_u32(smem);
     size_t body = (size_t)p.stages * Q8_STAGE_BYTES;
-    if (merge_smem_bytes<D>() > body) body = merge_smem_bytes<D>();
+    if (merge_smem_bytes<D, Q8_WARPS>() > body) body = merge_smem_bytes<D, Q8_WARPS>();
     const uint32_t full_bar = ring + (uint32_t)body;
     const uint32_t empty_bar = full_bar + p.stages * 8;
     int* last_flag = reinterpret_cast<int*>(smem + body + 2 * p.stages * 8);
@@ -125,53 +133,60 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     __syncthreads();
 
     // ------------------------------------------------------------------ producer (whole warp)
-    if (warp == CONSUMER_WARPS) {
+    // Lane l looks after chunk l % 4 of tile (group * 8 + l / 4): it resolves that chunk's page once per
+    // group of eight tiles and later issues the chunk's four copies itself, so the per-tile issue work
+    // (two TMA boxes and two scale copies per 16-token chunk) is spread over four lanes.
+    if (warp == Q8_WARPS) {
         if (lane == 0) {
             tma_prefetch_desc(&tmK);
             tma_prefetch_desc(&tmV);
         }
         const uint64_t policy = l2_policy_evict_first();
         const int P = p.page_size;
-        auto page_of = [&](int group_first_tile) -> int {  // lane l: tile group_first_tile + l/4, chunk l%4
+        struct ChunkRef { int page, slot; };
+        auto chunk_of = [&](int group_first_tile) -> ChunkRef {
             const int t = t_begin + (group_first_tile + (lane >> 2)) * TILE + (lane & 3) * CHUNK;
-            if (t >= t_end) return 0;
-            const int lp = t / P;
-            return p.page_table ? __ldg(p.page_table + (long long)b * p.max_pages + lp) : b * p.max_pages + lp;
+            ChunkRef r{-1, 0};
+            if (t < t_end) {
+                const int lp = t / P;
+                r.slot = t - lp * P;
+                r.page = p.page_table ? __ldg(p.page_table + (long long)b * p.max_pages + lp) : b * p.max_pages + lp;
+            }
+            return r;
         };
-        int pid_next = page_of(0);
-        bool ok = true;
+        ChunkRef next = chunk_of(0);
+        int ok = 1;
         for (int it0 = 0; it0 < ntiles && ok; it0 += 8) {
-            const int pid = pid_next;
-            pid_next = page_of(it0 + 8);
-            for (int j = 0; j < 8 && it0 + j < ntiles; ++j) {
+            const ChunkRef cur = next;
+            next = chunk_of(it0 + 8);
+            const int jn = min(8, ntiles - it0);
+            for (int j = 0; j < jn; ++j) {
                 const int it = it0 + j;
-                int pg[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) pg[c] = __shfl_sync(0xffffffffu, pid, j * 4 + c);
+                const int s = it % p.stages;
+                const uint32_t bar = full_bar + s * 8;
                 if (lane == 0) {
-                    const int s = it % p.stages;
                     const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
                     if (it >= p.stages && !mbar_wait(empty_bar + s * 8, ph ^ 1u)) {
                         atomicOr(p.status, SKV_DEV_TIMEOUT);
-                        ok = false;
+                        ok = 0;
                     } else {
                         const int tok = t_begin + it * TILE;
                         const int nch = min(4, (t_end - tok + CHUNK - 1) / CHUNK);
-                        const uint32_t bar = full_bar + s * 8;
                         mbar_expect_tx(bar, (uint32_t)nch * (2 * CHUNK * D + 2 * CHUNK * 4));
-                        const uint32_t kdst = ring + s * Q8_STAGE_BYTES;
-                        for (int c = 0; c < nch; ++c) {
-                            const int slot = (tok + c * CHUNK) % P;
-                            pool_tile_load(kdst + c * CHUNK * D, &tmK, bar, p.pos, slot, h, pg[c], policy);
-                            pool_tile_load(kdst + Q8_CODE_BYTES + c * CHUNK * D, &tmV, bar, p.pos, slot, h, pg[c], policy);
-                            const long long so = (long long)pg[c] * p.sc_sp + (long long)h * p.sc_sh + slot;
-                            bulk_load(kdst + 2 * Q8_CODE_BYTES + c * CHUNK * 4, p.k_scale + so, CHUNK * 4, bar);
-                            bulk_load(kdst + 2 * Q8_CODE_BYTES + 256 + c * CHUNK * 4, p.v_scale + so, CHUNK * 4, bar);
-                        }
                     }
                 }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
+                if ((lane >> 2) == j && cur.page >= 0) {
+                    const int c = lane & 3;
+                    const uint32_t kdst = ring + s * Q8_STAGE_BYTES;
+                    pool_tile_load(kdst + c * CHUNK * D, &tmK, bar, p.pos, cur.slot, h, cur.page, policy);
+                    pool_tile_load(kdst + Q8_CODE_BYTES + c * CHUNK * D, &tmV, bar, p.pos, cur.slot, h, cur.page, policy);
+                    const long long so = (long long)cur.page * p.sc_sp + (long long)h * p.sc_sh + cur.slot;
+                    bulk_load(kdst + 2 * Q8_CODE_BYTES + c * CHUNK * 4, p.k_scale + so, CHUNK * 4, bar);
+                    bulk_load(kdst + 2 * Q8_CODE_BYTES + 256 + c * CHUNK * 4, p.v_scale + so, CHUNK * 4, bar);
+                }
+                __syncwarp();
             }
         }
         return;
@@ -204,9 +219,10 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     for (int n = 0; n < 2 * NCH; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     const int lj = lane >> 3, r8 = lane & 7;
-    const int wtok = warp * 16;
+    const int group = warp >> 2;          // which of the two consumer groups
+    const int wtok = (warp & 3) * 16;     // this warp's first token inside a stage
 
-    for (int it = 0; it < ntiles; ++it) {
+    for (int it = group; it < ntiles; it += 2) {
         const int s = it % p.stages;
         const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
         if (!mbar_wait(full_bar + s * 8, ph)) {
@@ -232,8 +248,11 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                     uint32_t br[4];
                     ldsm_x4(kbase + row * 128 + (uint32_t)(((4 * m + lj) ^ r8) << 4), br[0], br[1], br[2], br[3]);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        mma_f16(sc[nt], qa[4 * m + j], cvt_pair<KVT>(br[j] & 0xFFFFu), cvt_pair<KVT>(br[j] >> 16));
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t b0, b1;
+                        cvt_quad<KVT>(br[j], b0, b1);
+                        mma_f16(sc[nt], qa[4 * m + j], b0, b1);
+                    }
                 }
             }
 
@@ -309,10 +328,16 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 const uint32_t row = (uint32_t)(wtok + (lj & 1) * 8 + r8);
                 uint32_t r0, r1, r2, r3;
                 ldsm_x4_t(vbase + row * 128 + (uint32_t)((c ^ r8) << 4), r0, r1, r2, r3);
-                mma_f16(o[4 * m + 0], pa, cvt_pair<KVT>(__byte_perm(r0, 0u, 0x4420)), cvt_pair<KVT>(__byte_perm(r1, 0u, 0x4420)));
-                mma_f16(o[4 * m + 1], pa, cvt_pair<KVT>(__byte_perm(r0, 0u, 0x4431)), cvt_pair<KVT>(__byte_perm(r1, 0u, 0x4431)));
-                mma_f16(o[4 * m + 2], pa, cvt_pair<KVT>(__byte_perm(r2, 0u, 0x4420)), cvt_pair<KVT>(__byte_perm(r3, 0u, 0x4420)));
-                mma_f16(o[4 * m + 3], pa, cvt_pair<KVT>(__byte_perm(r2, 0u, 0x4431)), cvt_pair<KVT>(__byte_perm(r3, 0u, 0x4431)));
+                // bytes [a0,a1,b0,b1] -> [a0,b0,a1,b1]: low half = even channel of both tokens, high half = odd channel
+                uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
+                cvt_quad<KVT>(__byte_perm(r0, 0u, 0x3120), e0, o0);
+                cvt_quad<KVT>(__byte_perm(r1, 0u, 0x3120), e1, o1);
+                cvt_quad<KVT>(__byte_perm(r2, 0u, 0x3120), e2, o2);
+                cvt_quad<KVT>(__byte_perm(r3, 0u, 0x3120), e3, o3);
+                mma_f16(o[4 * m + 0], pa, e0, e1);
+                mma_f16(o[4 * m + 1], pa, o0, o1);
+                mma_f16(o[4 * m + 2], pa, e2, e3);
+                mma_f16(o[4 * m + 3], pa, o2, o3);
             }
         }
         __syncwarp();
@@ -324,10 +349,10 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 
-    named_bar_sync(1, CONSUMER_THREADS);
+    named_bar_sync(1, Q8_CONSUMER_THREADS);
     float* mo = reinterpret_cast<float*>(smem);
-    float* mm = mo + CONSUMER_WARPS * MAX_GROUP * D;
-    float* ml = mm + CONSUMER_WARPS * MAX_GROUP;
+    float* mm = mo + Q8_WARPS * MAX_GROUP * D;
+    float* ml = mm + Q8_WARPS * MAX_GROUP;
     {
         float* my = mo + (warp * MAX_GROUP) * D;
         if (g < G) {
@@ -345,11 +370,11 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             if (tq == 0) { mm[warp * MAX_GROUP + g + 8] = m1; ml[warp * MAX_GROUP + g + 8] = l1; }
         }
     }
-    named_bar_sync(1, CONSUMER_THREADS);
+    named_bar_sync(1, Q8_CONSUMER_THREADS);
     EpilogueArgs ea;
     ea.partial_o = p.partial_o; ea.partial_ml = p.partial_ml; ea.tickets = p.tickets; ea.out = p.out;
     ea.Hkv = p.Hkv; ea.G = G; ea.num_splits = p.num_splits; ea.o_stride_b = p.o_stride_b; ea.o_stride_h = p.o_stride_h;
-    merge_and_combine<D>(ea, smem, last_flag, b, h, split, n_splits, 1.f / P_BOOST);
+    merge_and_combine<D, Q8_WARPS>(ea, smem, last_flag, b, h, split, n_splits, 1.f / P_BOOST);
 }
 
 template <int KVT>
@@ -363,7 +388,7 @@ static int launch_q8(const CUtensorMap& tmK, const CUtensorMap& tmV, const Q8Par
         configured_smem[dev] = (int)smem;
     }
     dim3 grid(p.Hkv, p.num_splits, B);
-    gqa_decode_q8_kernel<KVT><<<grid, THREADS, smem, stream>>>(tmK, tmV, p);
+    gqa_decode_q8_kernel<KVT><<<grid, Q8_THREADS, smem, stream>>>(tmK, tmV, p);
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }

@@ -13,17 +13,17 @@ namespace skv {
 namespace gqa {
 
 constexpr int TILE = 64;            // tokens per pipeline stage
-constexpr int CONSUMER_WARPS = 4;   // each takes TILE / 4 = 16 tokens of a stage
+constexpr int CONSUMER_WARPS = 4;   // fp16 kernel: each warp takes TILE / 4 = 16 tokens of a stage
 constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMER_THREADS + 32;
+constexpr int MAX_CONSUMER_WARPS = 8;  // the 8-bit kernel runs two groups of four warps on alternate stages
 constexpr int MAX_SPLITS = 512;
 constexpr int MAX_GROUP = 16;       // query heads per kv head (rows of one MMA tile)
 
 // Shared-memory words the epilogue needs at the start of the (drained) stage ring.
-template <int D>
+template <int D, int NW = CONSUMER_WARPS>
 __host__ __device__ constexpr size_t merge_smem_bytes() {
-    return (size_t)CONSUMER_WARPS * MAX_GROUP * D * 4 + (size_t)CONSUMER_WARPS * MAX_GROUP * 8 +
-           (size_t)CONSUMER_WARPS * MAX_SPLITS * 4;
+    return (size_t)NW * MAX_GROUP * D * 4 + (size_t)NW * MAX_GROUP * 8 + (size_t)NW * MAX_SPLITS * 4;
 }
 
 struct Tuning {
@@ -80,30 +80,30 @@ struct EpilogueArgs {
     long long o_stride_b, o_stride_h;
 };
 
-// Called by all CONSUMER_THREADS threads (threadIdx.x < CONSUMER_THREADS) after
-// every warp has stored its state at `smem`: O [W][MAX_GROUP][D], running max
-// [W][MAX_GROUP] (exp2 domain), running sum [W][MAX_GROUP], and after a named
+// Called by all NW * 32 consumer threads (threadIdx.x < NW * 32) after every
+// warp has stored its state at `smem`: O [NW][MAX_GROUP][D], running max
+// [NW][MAX_GROUP] (exp2 domain), running sum [NW][MAX_GROUP], and after a named
 // barrier.  `out_scale` multiplies the un-normalised output (1 for fp16 KV).
-template <int D>
+template <int D, int NW = CONSUMER_WARPS>
 __device__ __forceinline__ void merge_and_combine(const EpilogueArgs& p, uint8_t* smem, int* last_flag, int b, int h,
                                                   int split, int n_splits, float out_scale) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.G;
     float* mo = reinterpret_cast<float*>(smem);
-    float* mm = mo + CONSUMER_WARPS * MAX_GROUP * D;
-    float* ml = mm + CONSUMER_WARPS * MAX_GROUP;
-    float* wts = ml + CONSUMER_WARPS * MAX_GROUP;  // [W][MAX_SPLITS]
+    float* mm = mo + NW * MAX_GROUP * D;
+    float* ml = mm + NW * MAX_GROUP;
+    float* wts = ml + NW * MAX_GROUP;  // [W][MAX_SPLITS]
 
     const long long bh = (long long)b * p.Hkv + h;
     const long long pbase = (bh * p.num_splits + split) * G;  // row index into the partials
-    for (int idx = threadIdx.x; idx < G * D; idx += CONSUMER_THREADS) {
+    for (int idx = threadIdx.x; idx < G * D; idx += (NW * 32)) {
         const int r = idx / D, d = idx - r * D;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < CONSUMER_WARPS; ++w) M = fmaxf(M, mm[w * MAX_GROUP + r]);
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, mm[w * MAX_GROUP + r]);
         float L = 0.f, O = 0.f;
 #pragma unroll
-        for (int w = 0; w < CONSUMER_WARPS; ++w) {
+        for (int w = 0; w < NW; ++w) {
             const float mw = mm[w * MAX_GROUP + r];
             const float wgt = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
             L += ml[w * MAX_GROUP + r] * wgt;
@@ -125,20 +125,20 @@ __device__ __forceinline__ void merge_and_combine(const EpilogueArgs& p, uint8_t
 
     // ------------------------------------------- last CTA of this (b, h) combines
     __threadfence();
-    named_bar_sync(1, CONSUMER_THREADS);
+    named_bar_sync(1, (NW * 32));
     if (threadIdx.x == 0) {
         const int ticket = atomicAdd(&p.tickets[bh], 1);
         const int last = (ticket == n_splits - 1);
         if (last) p.tickets[bh] = 0;  // ready for the next launch on this workspace
         *last_flag = last;
     }
-    named_bar_sync(1, CONSUMER_THREADS);
+    named_bar_sync(1, (NW * 32));
     if (!*last_flag) return;
     __threadfence();
 
     const long long rbase = bh * p.num_splits * G;
     float* wrow = wts + warp * MAX_SPLITS;
-    for (int r = warp; r < G; r += CONSUMER_WARPS) {
+    for (int r = warp; r < G; r += NW) {
         float mx = -INFINITY;
         for (int s = lane; s < n_splits; s += 32) mx = fmaxf(mx, __ldcg(&p.partial_ml[(rbase + (long long)s * G + r) * 2]));
         mx = warp_max(mx);
