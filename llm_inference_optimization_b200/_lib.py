@@ -9,7 +9,10 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libskv_b200.so"
+import os
+
+# SKV_B200_LIB points the loader at another build of the same library (for example an instrumented one).
+LIB_PATH = Path(os.environ.get("SKV_B200_LIB") or Path(__file__).resolve().parent / "csrc" / "libskv_b200.so")
 
 KV_F16, KV_I8, KV_E4M3 = 0, 1, 2
 QUANT_NONE, QUANT_INT8, QUANT_E4M3, QUANT_CAST = 0, 1, 2, 3

@@ -101,9 +101,15 @@ def bench_paged(t, dev, g, peak, pk):
             out = torch.empty_like(Q)
             us, mn = t(lambda: _C.fused_gqa_paged(Q, kp, vp, ks, vs, table, None, D ** -0.5, out=out))
             nbytes = 2 * B * N * Hkv * (D + 4)
-            emit("dense_gqa_paged_" + ("fp8" if fp8 else "int8"), {"B": B, "Hq": Hq, "Hkv": Hkv, "D": D, "ctx": N, "page": P},
-                 us, mn, nbytes, peak, pk)
+            emit("dense_gqa_paged_" + ("fp8" if fp8 else "int8"), {"B": B, "Hq": Hq, "Hkv": Hkv, "D": D, "ctx": N, "page": P,
+                                                                    "layout": "separate pools"}, us, mn, nbytes, peak, pk)
+            buf = paged.pack_fused(kp, vp, ks, vs)
             del kp, vp, ks, vs
+            kv = paged.PagedKV.from_fused(buf, torch.float8_e4m3fn if fp8 else torch.int8, table, None, B)
+            us, mn = t(lambda: _C.fused_gqa_paged(Q, kv.k_pool, kv.v_pool, kv.k_scale, kv.v_scale, table, None, D ** -0.5, out=out))
+            emit("dense_gqa_paged_" + ("fp8" if fp8 else "int8"), {"B": B, "Hq": Hq, "Hkv": Hkv, "D": D, "ctx": N, "page": P,
+                                                                    "layout": "fused page records"}, us, mn, nbytes, peak, pk)
+            del buf, kv
 
 
 def bench_token(t, dev, g, peak, pk):

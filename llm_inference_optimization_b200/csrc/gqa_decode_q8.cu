@@ -39,6 +39,15 @@ constexpr int CHUNK = 16;                                  // tokens per TMA box
 constexpr int Q8_CODE_BYTES = TILE * Q8_D;                 // 8 KB of K (or V) codes per stage
 constexpr int Q8_STAGE_BYTES = 2 * Q8_CODE_BYTES + 1024;   // + K scales [64] + V scales [64] (512 B, padded)
 constexpr float P_BOOST = 64.f;
+// How a 64-token stage is fetched.  Every async copy costs its issuing lane about 100 cycles, so a stage
+// should be made of few requests:
+//   Q8_SEPARATE16: four 16-token chunks, each a K box, a V box and two 64-byte scale copies (16 requests);
+//   Q8_SEPARATE64: pages of a multiple of 64 tokens: one K box, one V box, two 256-byte scale copies;
+//   Q8_FUSED     : "page records" -- K codes, V codes and both scale vectors of a (page, head) stored as
+//                  33 consecutive 128-byte rows, fetched by ONE box per 16-token chunk (4 requests).
+constexpr int Q8_SEPARATE16 = 0, Q8_SEPARATE64 = 1, Q8_FUSED = 2;
+constexpr int RECORD_ROWS = 33;                            // 16 K rows, 16 V rows, 1 row of 16 + 16 fp32 scales
+constexpr int RECORD_BYTES = RECORD_ROWS * Q8_D;           // 4224
 constexpr int Q8_WARPS = MAX_CONSUMER_WARPS;               // two groups of four: group g takes stages with it % 2 == g
 constexpr int Q8_CONSUMER_THREADS = Q8_WARPS * 32;
 constexpr int Q8_THREADS = Q8_CONSUMER_THREADS + 32;
@@ -57,6 +66,7 @@ struct Q8Params {
     int N, Hq, Hkv, G;
     int tiles_per_split, num_splits, stages;
     int page_size, max_pages;
+    int mode;                // Q8_SEPARATE16, Q8_SEPARATE64 or Q8_FUSED
     long long sc_sp, sc_sh;
     long long q_stride_b, q_stride_h, o_stride_b, o_stride_h;
     float scale_log2;
@@ -133,9 +143,8 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     __syncthreads();
 
     // ------------------------------------------------------------------ producer (whole warp)
-    // Lane l looks after chunk l % 4 of tile (group * 8 + l / 4): it resolves that chunk's page once per
-    // group of eight tiles and later issues the chunk's four copies itself, so the per-tile issue work
-    // (two TMA boxes and two scale copies per 16-token chunk) is spread over four lanes.
+    // Every lane resolves the page of one request group ahead of time (one page-table read per lane per
+    // group of tiles) and later issues one of that group's copies itself.
     if (warp == Q8_WARPS) {
         if (lane == 0) {
             tma_prefetch_desc(&tmK);
@@ -143,9 +152,19 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         }
         const uint64_t policy = l2_policy_evict_first();
         const int P = p.page_size;
+        const int ck_shift = p.mode == Q8_SEPARATE64 ? 6 : 4;     // log2(tokens per request group)
+        const int ck = 1 << ck_shift;
+        const int nck = TILE >> ck_shift;                         // request groups per stage (4 or 1)
+        // The loop below runs once per 64-token stage and must stay well under the ~700 cycles a stage
+        // lasts at full HBM rate: no integer divisions, and the (about 100-cycle) issue of each async copy
+        // is spread over lanes -- lane l serves request group (l / 4) % nck of tile l / (4 * nck) with
+        // role l % 4 (K box, V box, K scales, V scales; role 0 alone in the fused layout).
+        const int role = lane & 3;
+        const int my_tile = (lane >> 2) / nck, my_c = (lane >> 2) - my_tile * nck;  // my_tile in [0, 8 / nck)
+        const int tiles_per_group = 8 / nck;                      // 2 (16-token groups) or 8 (64-token groups)
         struct ChunkRef { int page, slot; };
         auto chunk_of = [&](int group_first_tile) -> ChunkRef {
-            const int t = t_begin + (group_first_tile + (lane >> 2)) * TILE + (lane & 3) * CHUNK;
+            const int t = t_begin + (group_first_tile + my_tile) * TILE + (my_c << ck_shift);
             ChunkRef r{-1, 0};
             if (t < t_end) {
                 const int lp = t / P;
@@ -154,39 +173,45 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             }
             return r;
         };
+        const uint32_t chunk_tx = p.mode == Q8_FUSED ? (uint32_t)RECORD_BYTES : (uint32_t)(2 * ck * D + 2 * ck * 4);
         ChunkRef next = chunk_of(0);
-        int ok = 1;
-        for (int it0 = 0; it0 < ntiles && ok; it0 += 8) {
+        int ok = 1, s = 0;
+        uint32_t ph = 0;                                          // phase of the ring pass the producer is filling
+        int remaining = t_end - t_begin;                          // tokens not yet requested
+        for (int it0 = 0; it0 < ntiles && ok; it0 += tiles_per_group) {
             const ChunkRef cur = next;
-            next = chunk_of(it0 + 8);
-            const int jn = min(8, ntiles - it0);
+            next = chunk_of(it0 + tiles_per_group);
+            const int jn = min(tiles_per_group, ntiles - it0);
             for (int j = 0; j < jn; ++j) {
-                const int it = it0 + j;
-                const int s = it % p.stages;
                 const uint32_t bar = full_bar + s * 8;
                 if (lane == 0) {
-                    const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
-                    if (it >= p.stages && !mbar_wait(empty_bar + s * 8, ph ^ 1u)) {
+                    if (it0 + j >= p.stages && !mbar_wait(empty_bar + s * 8, ph ^ 1u)) {
                         atomicOr(p.status, SKV_DEV_TIMEOUT);
                         ok = 0;
                     } else {
-                        const int tok = t_begin + it * TILE;
-                        const int nch = min(4, (t_end - tok + CHUNK - 1) / CHUNK);
-                        mbar_expect_tx(bar, (uint32_t)nch * (2 * CHUNK * D + 2 * CHUNK * 4));
+                        const int nch = min(nck, (remaining + ck - 1) >> ck_shift);
+                        mbar_expect_tx(bar, (uint32_t)nch * chunk_tx);
                     }
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
-                if ((lane >> 2) == j && cur.page >= 0) {
-                    const int c = lane & 3;
+                if (my_tile == j && cur.page >= 0) {
                     const uint32_t kdst = ring + s * Q8_STAGE_BYTES;
-                    pool_tile_load(kdst + c * CHUNK * D, &tmK, bar, p.pos, cur.slot, h, cur.page, policy);
-                    pool_tile_load(kdst + Q8_CODE_BYTES + c * CHUNK * D, &tmV, bar, p.pos, cur.slot, h, cur.page, policy);
-                    const long long so = (long long)cur.page * p.sc_sp + (long long)h * p.sc_sh + cur.slot;
-                    bulk_load(kdst + 2 * Q8_CODE_BYTES + c * CHUNK * 4, p.k_scale + so, CHUNK * 4, bar);
-                    bulk_load(kdst + 2 * Q8_CODE_BYTES + 256 + c * CHUNK * 4, p.v_scale + so, CHUNK * 4, bar);
+                    if (p.mode == Q8_FUSED) {
+                        if (role == 0) pool_tile_load(kdst + my_c * RECORD_BYTES, &tmK, bar, p.pos, 0, h, cur.page, policy);
+                    } else if (role == 0) {
+                        pool_tile_load(kdst + (my_c << ck_shift) * D, &tmK, bar, p.pos, cur.slot, h, cur.page, policy);
+                    } else if (role == 1) {
+                        pool_tile_load(kdst + Q8_CODE_BYTES + (my_c << ck_shift) * D, &tmV, bar, p.pos, cur.slot, h, cur.page, policy);
+                    } else {
+                        const long long so = (long long)cur.page * p.sc_sp + (long long)h * p.sc_sh + cur.slot;
+                        const float* src = (role == 2 ? p.k_scale : p.v_scale) + so;
+                        bulk_load(kdst + 2 * Q8_CODE_BYTES + (role == 3 ? 256 : 0) + (my_c << ck_shift) * 4, src, ck * 4, bar);
+                    }
                 }
                 __syncwarp();
+                remaining -= TILE;
+                if (++s == p.stages) { s = 0; ph ^= 1u; }
             }
         }
         return;
@@ -220,21 +245,31 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     const int lj = lane >> 3, r8 = lane & 7;
     const int group = warp >> 2;          // which of the two consumer groups
-    const int wtok = (warp & 3) * 16;     // this warp's first token inside a stage
+    const int wc = warp & 3;              // this warp's 16-token chunk of a stage
+    const int wtok = wc * 16;
+    // Byte offsets inside a stage of this warp's 16 K rows, 16 V rows and 16 + 16 scales, and the swizzle
+    // phase of its first row (rows are 128 bytes; TMA XORs the 16-byte chunk index with the row index mod 8).
+    const bool fused = p.mode == Q8_FUSED;
+    const uint32_t k_off = fused ? wc * RECORD_BYTES : wtok * D;
+    const uint32_t v_off = fused ? wc * RECORD_BYTES + 16 * D : Q8_CODE_BYTES + wtok * D;
+    const uint32_t ks_off = fused ? wc * RECORD_BYTES + 32 * D : 2 * Q8_CODE_BYTES + wtok * 4;
+    const uint32_t vs_off = fused ? ks_off + 64 : ks_off + 256;
+    const int sc_phase = fused ? wc : 0;                  // the scale row of a record is swizzled too
+    const uint32_t sw = (uint32_t)((r8 + (fused ? wc : 0)) & 7);
 
-    for (int it = group; it < ntiles; it += 2) {
-        const int s = it % p.stages;
-        const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+    int s = group;          // stage of tile `it`; p.stages >= 3, so one wrap per step at most
+    uint32_t ph = 0;
+    for (int it = group; it < ntiles; it += 2, s += 2) {
+        if (s >= p.stages) { s -= p.stages; ph ^= 1u; }
         if (!mbar_wait(full_bar + s * 8, ph)) {
             if (lane == 0) atomicOr(p.status, SKV_DEV_TIMEOUT);
             break;
         }
         const int tok0 = t_begin + it * TILE + wtok;
         if (tok0 < t_end) {
-            const uint32_t kbase = ring + s * Q8_STAGE_BYTES;
-            const uint32_t vbase = kbase + Q8_CODE_BYTES;
-            const float* ks = reinterpret_cast<const float*>(smem + (size_t)s * Q8_STAGE_BYTES + 2 * Q8_CODE_BYTES);
-            const float* vs = ks + 64;
+            const uint32_t kbase = ring + s * Q8_STAGE_BYTES + k_off;   // this warp's K rows
+            const uint32_t vbase = ring + s * Q8_STAGE_BYTES + v_off;   // this warp's V rows
+            const uint8_t* stage = smem + (size_t)s * Q8_STAGE_BYTES;
             const bool ragged = tok0 + 16 > t_end;
 
             float sc[2][4];
@@ -242,11 +277,11 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                const uint32_t row = (uint32_t)(wtok + nt * 8 + r8);
+                const uint32_t row = (uint32_t)(nt * 8 + r8);
 #pragma unroll
                 for (int m = 0; m < NCH / 4; ++m) {
                     uint32_t br[4];
-                    ldsm_x4(kbase + row * 128 + (uint32_t)(((4 * m + lj) ^ r8) << 4), br[0], br[1], br[2], br[3]);
+                    ldsm_x4(kbase + row * 128 + (((uint32_t)(4 * m + lj) ^ sw) << 4), br[0], br[1], br[2], br[3]);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         uint32_t b0, b1;
@@ -260,8 +295,10 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             float2 ksc[2], vsc[2];
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                ksc[nt] = *reinterpret_cast<const float2*>(ks + wtok + nt * 8 + tq * 2);
-                vsc[nt] = *reinterpret_cast<const float2*>(vs + wtok + nt * 8 + tq * 2);
+                const int i = nt * 8 + tq * 2;  // token within the warp's 16; its 16-byte chunk is i / 4
+                const uint32_t off = (uint32_t)((((i >> 2) ^ sc_phase) << 4) + (i & 3) * 4);
+                ksc[nt] = *reinterpret_cast<const float2*>(stage + ks_off + off);
+                vsc[nt] = *reinterpret_cast<const float2*>(stage + vs_off + off);
             }
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
@@ -279,8 +316,8 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 for (int idx = lane; idx < 16 * 8; idx += 32) {
                     const int r = idx >> 3, c = idx & 7;
                     if (tok0 + r >= t_end)
-                        *reinterpret_cast<uint4*>(smem + (size_t)s * Q8_STAGE_BYTES + Q8_CODE_BYTES +
-                                                  (size_t)(wtok + r) * 128 + (size_t)c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                        *reinterpret_cast<uint4*>(smem + (size_t)s * Q8_STAGE_BYTES + v_off + (size_t)r * 128 +
+                                                  (size_t)c * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 __syncwarp();
             }
@@ -325,9 +362,9 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 #pragma unroll
             for (int m = 0; m < NCH / 2; ++m) {
                 const int c = 2 * m + (lj >> 1);
-                const uint32_t row = (uint32_t)(wtok + (lj & 1) * 8 + r8);
+                const uint32_t row = (uint32_t)((lj & 1) * 8 + r8);
                 uint32_t r0, r1, r2, r3;
-                ldsm_x4_t(vbase + row * 128 + (uint32_t)((c ^ r8) << 4), r0, r1, r2, r3);
+                ldsm_x4_t(vbase + row * 128 + (((uint32_t)c ^ sw) << 4), r0, r1, r2, r3);
                 // bytes [a0,a1,b0,b1] -> [a0,b0,a1,b1]: low half = even channel of both tokens, high half = odd channel
                 uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
                 cvt_quad<KVT>(__byte_perm(r0, 0u, 0x3120), e0, o0);
@@ -436,14 +473,36 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
         return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, pl.total);
     if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(SKV_ERR_WORKSPACE, "workspace must be 256-byte aligned");
 
+    // Pick how stages are fetched (see the Q8_* modes): fused page records when the four pools are views of one
+    // [num_pages, Hkv, 33, 128]-byte buffer, 64-token boxes when pages allow it, 16-token chunks otherwise.
+    const uint8_t* kb = static_cast<const uint8_t*>(k_pool);
+    int mode = gqa::Q8_SEPARATE16;
+    if (page_size == gqa::CHUNK && static_cast<const uint8_t*>(v_pool) == kb + 16 * D &&
+        reinterpret_cast<const uint8_t*>(k_scale_pool) == kb + 32 * D &&
+        reinterpret_cast<const uint8_t*>(v_scale_pool) == kb + 32 * D + 64 && pool_stride_slot == D &&
+        pool_stride_head == gqa::RECORD_BYTES && pool_stride_page == (long long)Hkv * gqa::RECORD_BYTES &&
+        scale_stride_head * 4 == pool_stride_head && scale_stride_page * 4 == pool_stride_page)
+        mode = gqa::Q8_FUSED;
+    else if (page_size % gqa::TILE == 0)
+        mode = gqa::Q8_SEPARATE64;
+
     CUtensorMap tmK, tmV;
     PoolMapPos pos, pos2;
-    int rc = make_pool_tmap(&tmK, &pos, k_pool, D, num_pages, Hkv, page_size, pool_stride_page, pool_stride_head,
-                            pool_stride_slot, gqa::CHUNK);
-    if (rc) return rc;
-    rc = make_pool_tmap(&tmV, &pos2, v_pool, D, num_pages, Hkv, page_size, pool_stride_page, pool_stride_head,
-                        pool_stride_slot, gqa::CHUNK);
-    if (rc) return rc;
+    int rc;
+    if (mode == gqa::Q8_FUSED) {
+        rc = make_pool_tmap(&tmK, &pos, k_pool, D, num_pages, Hkv, gqa::RECORD_ROWS, pool_stride_page, pool_stride_head,
+                            pool_stride_slot, gqa::RECORD_ROWS);
+        if (rc) return rc;
+        tmV = tmK;
+    } else {
+        const int box = mode == gqa::Q8_SEPARATE64 ? gqa::TILE : gqa::CHUNK;
+        rc = make_pool_tmap(&tmK, &pos, k_pool, D, num_pages, Hkv, page_size, pool_stride_page, pool_stride_head,
+                            pool_stride_slot, box);
+        if (rc) return rc;
+        rc = make_pool_tmap(&tmV, &pos2, v_pool, D, num_pages, Hkv, page_size, pool_stride_page, pool_stride_head,
+                            pool_stride_slot, box);
+        if (rc) return rc;
+    }
 
     gqa::Q8Params p;
     uint8_t* ws = static_cast<uint8_t*>(workspace);
@@ -463,6 +522,7 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.stages = gqa::tuning().q8_stages;
     p.page_size = page_size;
     p.max_pages = max_pages;
+    p.mode = mode;
     p.sc_sp = scale_stride_page; p.sc_sh = scale_stride_head;
     p.q_stride_b = (long long)Hq * D; p.q_stride_h = D;
     p.o_stride_b = (long long)Hq * D; p.o_stride_h = D;

@@ -125,15 +125,17 @@ inline int make_pool_tmap(CUtensorMap* out, PoolMapPos* pos, const void* base, i
             return fail(SKV_ERR_BAD_ARG, "pool stride of %llu bytes is not a positive multiple of 16", x.stride_bytes);
     }
     std::stable_sort(d, d + 3, [](const Dim& a, const Dim& b) { return a.stride_bytes < b.stride_bytes; });
-    cuuint64_t gdim[4] = {(cuuint64_t)D, d[0].size, d[1].size, d[2].size};
+    // Rows are declared as D/4 32-bit words rather than D bytes: the copy is byte-identical (the 128-byte
+    // swizzle works on addresses), and wider elements keep the TMA unit's per-element work low.
+    cuuint64_t gdim[4] = {(cuuint64_t)D / 4, d[0].size, d[1].size, d[2].size};
     cuuint64_t gstr[3] = {d[0].stride_bytes, d[1].stride_bytes, d[2].stride_bytes};
-    cuuint32_t box[4] = {(cuuint32_t)D, d[0].box, d[1].box, d[2].box};
+    cuuint32_t box[4] = {(cuuint32_t)D / 4, d[0].box, d[1].box, d[2].box};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     for (int i = 0; i < 3; ++i) {
         const int p = i + 1;
         if (d[i].logical == 1) pos->slot = p; else if (d[i].logical == 2) pos->head = p; else pos->page = p;
     }
-    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), gdim, gstr, box, estr,
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, const_cast<void*>(base), gdim, gstr, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SKV_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);

@@ -1,0 +1,221 @@
+"""One decode step of a Llama-architecture model over a paged FP8 KV cache, tensor-parallel by KV head.
+
+The reference measures this step by calling a Hugging Face model whose attention forward is
+monkey-patched (benchmarks/llama_integration_benchmark.py:114-230, timed at :252-279); it is single-GPU
+and needs the gated Llama-3.1-8B weights.  Here the step is written out directly so that it runs with
+random weights of the same architecture on 1, 2, 4 or 8 GPUs:
+
+    x -> [RMSNorm -> qkv GEMM -> RoPE -> quantise + append k,v to the paged cache -> paged decode
+          attention (sm_100a kernel) -> o_proj GEMM -> all-reduce -> RMSNorm -> SwiGLU MLP -> all-reduce] x L
+      -> RMSNorm -> lm_head
+
+Rank r owns kv heads ``shard.kv_heads`` with their query heads (column-parallel q/k/v, gate, up;
+row-parallel o_proj and down_proj), so the attention kernel reads only local pages and the only
+collective is the sum all-reduce of the ``[batch, hidden]`` activations after o_proj and after down_proj
+(NCCL over NVLink).  GEMMs are plain library GEMMs (cuBLAS through torch); the attention is this
+package's kernel.  Weights are drawn per matrix from a generator seeded by (seed, layer, matrix) and
+then sliced, so every tensor-parallel degree computes with the same full-model weights.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from . import paged
+from .sharding import HeadShard, shard_columns
+
+
+@dataclass(frozen=True)
+class ModelConfig:
+    layers: int = 32
+    hidden: int = 4096
+    Hq: int = 32
+    Hkv: int = 8
+    D: int = 128
+    mlp: int = 14336
+    vocab: int = 128256
+    rope_theta: float = 500000.0
+    rms_eps: float = 1e-5
+    init_std: float = 0.02
+
+
+def _matrix(seed: int, layer: int, name: str, shape, device, dtype, std) -> Tensor:
+    """Full (unsharded) weight matrix from a generator keyed by (seed, layer, name)."""
+    g = torch.Generator(device=device)
+    g.manual_seed((seed * 1000003 + layer * 101 + sum(map(ord, name))) & 0x7FFFFFFF)
+    return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std).to(dtype)
+
+
+def rms_norm(x: Tensor, w: Tensor, eps: float) -> Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+def rope(x: Tensor, pos: Tensor, theta: float) -> Tensor:
+    """Plain rotary embedding (rotate-half form) of ``x [B, H, D]`` at integer positions ``pos [B]``."""
+    D = x.shape[-1]
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, device=x.device, dtype=torch.float32) / D))
+    ang = pos.float()[:, None] * inv[None, :]
+    cos = torch.cat([ang.cos(), ang.cos()], -1)[:, None, :]
+    sin = torch.cat([ang.sin(), ang.sin()], -1)[:, None, :]
+    xf = x.float()
+    rot = torch.cat([-xf[..., D // 2:], xf[..., :D // 2]], -1)
+    return (xf * cos + rot * sin).to(x.dtype)
+
+
+def quantize_rows_e4m3(x: Tensor):
+    """Per-row FP8-E4M3 codes and fp32 scales (scale = amax / 448, 1 for a zero row) of ``x [..., D]``."""
+    xf = x.float()
+    amax = xf.abs().amax(-1)
+    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    return (xf / scale[..., None]).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn), scale
+
+
+class LayerCache:
+    """Paged FP8 cache of one layer on one rank (fused page records, page size 16)."""
+
+    def __init__(self, num_pages: int, n_kv: int, device):
+        self.buf = torch.zeros((num_pages, n_kv, paged.RECORD_ROWS, 128), dtype=torch.uint8, device=device)
+        self.k, self.v, self.ks, self.vs = paged.fused_views(self.buf, torch.float8_e4m3fn)
+
+    def append(self, k: Tensor, v: Tensor, page_table: Tensor, seq_lens: Tensor) -> None:
+        """Quantise the new token's ``k, v [B, n_kv, D]`` and store them at position ``seq_lens[b]``."""
+        B = k.shape[0]
+        lens = seq_lens.long()
+        page = page_table[torch.arange(B, device=k.device), lens // 16].long()
+        slot = lens % 16
+        kc, ksc = quantize_rows_e4m3(k)
+        vc, vsc = quantize_rows_e4m3(v)
+        self.k.view(torch.uint8)[page, :, slot] = kc.view(torch.uint8)
+        self.v.view(torch.uint8)[page, :, slot] = vc.view(torch.uint8)
+        self.ks[page, :, slot] = ksc
+        self.vs[page, :, slot] = vsc
+
+
+AttentionFn = Callable[[Tensor, LayerCache, Tensor, Tensor, float, int], Tensor]
+
+
+def kernel_attention(q: Tensor, cache: LayerCache, page_table: Tensor, seq_lens: Tensor, scale: float,
+                     max_seq_len: int) -> Tensor:
+    """The product path: paged FP8 decode attention on the sm_100a kernel (fp16 query in, fp16 out)."""
+    from . import _C
+    return _C.fused_gqa_paged(q.to(torch.float16).contiguous(), cache.k, cache.v, cache.ks, cache.vs, page_table,
+                              seq_lens, scale, max_seq_len=max_seq_len)
+
+
+class DecodeModel:
+    """The rank-local slice of the model and of every layer's cache."""
+
+    def __init__(self, cfg: ModelConfig, shard: HeadShard, device, *, seed: int = 4, dtype=torch.bfloat16,
+                 attention: AttentionFn = kernel_attention, group=None):
+        self.cfg, self.shard, self.device, self.dtype = cfg, shard, torch.device(device), dtype
+        self.attention, self.group = attention, group
+        D, hid = cfg.D, cfg.hidden
+        qs = slice(shard.q_heads.start * D, shard.q_heads.stop * D)
+        ks = slice(shard.kv_heads.start * D, shard.kv_heads.stop * D)
+        ms = shard_columns(cfg.mlp, shard.world, shard.rank)
+        ms = slice(ms.start, ms.stop)
+        mk = lambda l, n, shp: _matrix(seed, l, n, shp, self.device, dtype, cfg.init_std)  # noqa: E731
+        self.embed = mk(-1, "embed", (cfg.vocab, hid))
+        self.lm_head = mk(-2, "lm_head", (hid, cfg.vocab))
+        self.final_norm = torch.ones(hid, device=self.device, dtype=dtype)
+        self.layers = []
+        for l in range(cfg.layers):
+            wq, wk, wv = mk(l, "wq", (hid, cfg.Hq * D)), mk(l, "wk", (hid, cfg.Hkv * D)), mk(l, "wv", (hid, cfg.Hkv * D))
+            wqkv = torch.cat([wq[:, qs], wk[:, ks], wv[:, ks]], 1).contiguous()
+            del wq, wk, wv
+            wo = mk(l, "wo", (cfg.Hq * D, hid))[qs].contiguous()
+            wgu = torch.cat([mk(l, "wg", (hid, cfg.mlp))[:, ms], mk(l, "wu", (hid, cfg.mlp))[:, ms]], 1).contiguous()
+            wd = mk(l, "wd", (cfg.mlp, hid))[ms].contiguous()
+            self.layers.append(dict(wqkv=wqkv, wo=wo, wgu=wgu, wd=wd,
+                                    n1=torch.ones(hid, device=self.device, dtype=dtype),
+                                    n2=torch.ones(hid, device=self.device, dtype=dtype)))
+        self.caches: list[LayerCache] = []
+        self.page_table: Tensor | None = None
+        self.seq_lens: Tensor | None = None
+        self.max_seq_len = 0
+
+    # ------------------------------------------------------------------ cache set-up
+    def init_cache(self, seq_lens: Tensor, *, fill: str = "normal", seed: int = 4, extra_tokens: int = 64) -> None:
+        """Allocate every layer's pages for sequences of the given lengths and pre-fill them.
+
+        No prefill pass is run (only the decode step is the workload): ``fill="normal"`` writes N(0,1)
+        keys/values quantised row by row to FP8; ``fill="random_codes"`` writes uniformly random FP8 codes with
+        scales near 0.008 (values within about +-4), which is much faster to generate for a 70 GB cache and
+        costs the kernels the same time.  Pages are assigned to (sequence, logical page) by a seeded permutation.
+        """
+        cfg, dev = self.cfg, self.device
+        B = seq_lens.numel()
+        cap = (seq_lens.max().item() + extra_tokens + 15) // 16
+        pages_per_seq = [(int(n) + extra_tokens + 15) // 16 for n in seq_lens.tolist()]
+        total = sum(pages_per_seq)
+        g = torch.Generator().manual_seed(seed)
+        perm = torch.randperm(total, generator=g)
+        table = torch.zeros((B, cap), dtype=torch.int32)
+        o = 0
+        for b, n in enumerate(pages_per_seq):
+            table[b, :n] = perm[o:o + n].to(torch.int32)
+            o += n
+        self.page_table = table.to(dev)
+        self.seq_lens = seq_lens.to(device=dev, dtype=torch.int32).clone()
+        self.max_seq_len = cap * 16
+        self.caches = []
+        gd = torch.Generator(device=dev)
+        for l in range(cfg.layers):
+            c = LayerCache(total, self.shard.n_kv, dev)
+            for i, head in enumerate(self.shard.kv_heads):  # keyed by the GLOBAL head: same bytes at every TP degree
+                gd.manual_seed((seed * 7919 + l * 131 + head) & 0x7FFFFFFF)
+                if fill == "normal":
+                    for dst, dsc in ((c.k, c.ks), (c.v, c.vs)):
+                        codes, sc = quantize_rows_e4m3(torch.randn((total, 16, 128), generator=gd, device=dev))
+                        dst.view(torch.uint8)[:, i].copy_(codes.view(torch.uint8))
+                        dsc[:, i].copy_(sc)
+                elif fill == "random_codes":
+                    codes = torch.randint(0, 256, (total, paged.RECORD_ROWS, 128), generator=gd, device=dev, dtype=torch.uint8)
+                    codes = torch.where((codes & 0x7F) == 0x7F, codes & 0xFE, codes)  # keep clear of the NaN patterns
+                    c.buf[:, i].copy_(codes)
+                    del codes
+                    c.ks[:, i].copy_(torch.rand((total, 16), generator=gd, device=dev) * 0.004 + 0.006)
+                    c.vs[:, i].copy_(torch.rand((total, 16), generator=gd, device=dev) * 0.004 + 0.006)
+                elif fill != "zeros":
+                    raise ValueError(f"unknown fill {fill!r}")
+            self.caches.append(c)
+
+    # ------------------------------------------------------------------ the step
+    def _all_reduce(self, x: Tensor) -> Tensor:
+        if self.shard.world > 1:
+            dist.all_reduce(x, op=dist.ReduceOp.SUM, group=self.group)
+        return x
+
+    def step(self, tokens: Tensor) -> Tensor:
+        """Decode one token per sequence: ``tokens [B]`` int64 -> logits ``[B, vocab]``; advances ``seq_lens``."""
+        cfg, sh = self.cfg, self.shard
+        D = cfg.D
+        B = tokens.shape[0]
+        scale = 1.0 / math.sqrt(D)
+        x = self.embed[tokens]
+        pos = self.seq_lens
+        new_lens = self.seq_lens + 1
+        for w, cache in zip(self.layers, self.caches):
+            h = rms_norm(x, w["n1"], cfg.rms_eps)
+            qkv = h @ w["wqkv"]
+            q = qkv[:, :sh.n_q * D].view(B, sh.n_q, D)
+            k = qkv[:, sh.n_q * D:(sh.n_q + sh.n_kv) * D].view(B, sh.n_kv, D)
+            v = qkv[:, (sh.n_q + sh.n_kv) * D:].view(B, sh.n_kv, D)
+            q, k = rope(q, pos, cfg.rope_theta), rope(k, pos, cfg.rope_theta)
+            cache.append(k, v, self.page_table, pos)
+            a = self.attention(q, cache, self.page_table, new_lens, scale, self.max_seq_len)
+            o = a.to(x.dtype).reshape(B, sh.n_q * D) @ w["wo"]
+            x = x + self._all_reduce(o)
+            h = rms_norm(x, w["n2"], cfg.rms_eps)
+            gu = h @ w["wgu"]
+            half = gu.shape[1] // 2
+            act = torch.nn.functional.silu(gu[:, :half]) * gu[:, half:]
+            x = x + self._all_reduce(act @ w["wd"])
+        self.seq_lens.add_(1)
+        return rms_norm(x, self.final_norm, cfg.rms_eps) @ self.lm_head

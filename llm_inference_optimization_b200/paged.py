@@ -36,10 +36,46 @@ class PagedKV:
     def capacity(self) -> int:
         return self.max_pages * self.page_size
 
+    @classmethod
+    def from_fused(cls, buf: Tensor, code_dtype: torch.dtype, page_table: Tensor | None, seq_lens: Tensor | None,
+                   batch: int) -> "PagedKV":
+        """Cache whose pools are views of one fused page-record buffer (see ``fused_views``)."""
+        k, v, ks, vs = fused_views(buf, code_dtype)
+        return cls(k, v, ks, vs, page_table, seq_lens, batch)
+
     def decode(self, Q: Tensor, scale: float, max_seq_len: int | None = None) -> Tensor:
         """Dense GQA decode over the whole cache (``_C.fused_gqa_paged``)."""
         return _C.fused_gqa_paged(Q, self.k_pool, self.v_pool, self.k_scale, self.v_scale, self.page_table,
                                   self.seq_lens, scale, max_seq_len=max_seq_len)
+
+
+RECORD_ROWS = 33  # rows of 128 bytes per (page, head): 16 of K codes, 16 of V codes, 1 of 16 + 16 fp32 scales
+
+
+def fused_views(buf: Tensor, code_dtype: torch.dtype):
+    """Views ``(k_pool, v_pool, k_scale, v_scale)`` over a fused page-record buffer.
+
+    ``buf`` is uint8 ``[num_pages, Hkv, 33, 128]``: for every (page, head) the 16 K rows, the 16 V rows
+    and one row holding the 16 K scales then the 16 V scales (fp32) are contiguous, so the decode kernel
+    fetches a 16-token chunk with a single TMA request instead of four.  The views have the shapes every
+    entry point expects (``[num_pages,Hkv,16,128]`` codes, ``[num_pages,Hkv,16]`` scales).
+    """
+    _C._require(buf.dtype == torch.uint8 and buf.dim() == 4 and buf.shape[2:] == (RECORD_ROWS, 128) and buf.is_contiguous(),
+                "fused buffer must be contiguous uint8 [num_pages, Hkv, 33, 128]")
+    k = buf[:, :, 0:16, :].view(code_dtype)
+    v = buf[:, :, 16:32, :].view(code_dtype)
+    sc = buf[:, :, 32, :].view(torch.float32)  # [num_pages, Hkv, 32]
+    return k, v, sc[:, :, 0:16], sc[:, :, 16:32]
+
+
+def pack_fused(k_pool: Tensor, v_pool: Tensor, k_scale: Tensor, v_scale: Tensor) -> Tensor:
+    """Copy separate pools (page size 16, D = 128) into one fused page-record buffer."""
+    num_pages, Hkv, P, D = k_pool.shape
+    _C._require(P == 16 and D == 128, "fused page records need page_size 16 and head_dim 128")
+    buf = torch.zeros((num_pages, Hkv, RECORD_ROWS, 128), dtype=torch.uint8, device=k_pool.device)
+    k, v, ks, vs = fused_views(buf, k_pool.dtype)
+    k.copy_(k_pool); v.copy_(v_pool); ks.copy_(k_scale); vs.copy_(v_scale)
+    return buf
 
 
 def _pool_args(kv: PagedKV):

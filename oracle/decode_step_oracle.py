@@ -1,0 +1,56 @@
+"""fp32 CPU restatement of one Llama-architecture decode step.  TEST INFRASTRUCTURE ONLY.
+
+Follows the step the reference times on its Hugging Face model (benchmarks/llama_integration_benchmark.py:266-279
+with the attention of :152-213): RMSNorm, q/k/v projections, rotate-half RoPE, attention of the new token over the
+cached keys/values plus itself, o_proj, SwiGLU MLP, final norm and lm_head.  The KV history is passed dequantised
+and unpaged; the new token's k/v go through the same FP8-E4M3 row quantisation the cache applies (no reference
+counterpart for that part), so that the only differences from the product path are GEMM precision and paging.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import skv_oracle
+
+
+def _rms(x, w, eps):
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
+
+
+def _rope(x, pos, theta):
+    D = x.shape[-1]
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = pos.float()[:, None] * inv[None, :]
+    cos = torch.cat([ang.cos(), ang.cos()], -1)[:, None, :]
+    sin = torch.cat([ang.sin(), ang.sin()], -1)[:, None, :]
+    rot = torch.cat([-x[..., D // 2:], x[..., :D // 2]], -1)
+    return x * cos + rot * sin
+
+
+def decode_step(weights: dict, cfg, tokens, k_hist, v_hist, seq_lens):
+    """``weights``: fp32 full matrices (embed, lm_head, final_norm, layers[l][wq|wk|wv|wo|wg|wu|wd|n1|n2]);
+    ``k_hist[l]``/``v_hist[l]``: ``[B, Hkv, Tmax, D]`` fp32 dequantised history; returns logits ``[B, vocab]``."""
+    B = tokens.shape[0]
+    D, Hq, Hkv = cfg.D, cfg.Hq, cfg.Hkv
+    x = weights["embed"][tokens]
+    pos = seq_lens.long()
+    for l, w in enumerate(weights["layers"]):
+        h = _rms(x, w["n1"], cfg.rms_eps)
+        q = _rope((h @ w["wq"]).view(B, Hq, D), pos, cfg.rope_theta)
+        k = _rope((h @ w["wk"]).view(B, Hkv, D), pos, cfg.rope_theta)
+        v = (h @ w["wv"]).view(B, Hkv, D)
+        kc, ks = skv_oracle.quantize_e4m3(k)
+        vc, vs = skv_oracle.quantize_e4m3(v)
+        kq, vq = skv_oracle.dequantize(kc, ks), skv_oracle.dequantize(vc, vs)
+        K, V = k_hist[l].clone(), v_hist[l].clone()
+        for b in range(B):
+            K[b, :, pos[b]] = kq[b]
+            V[b, :, pos[b]] = vq[b]
+        a = skv_oracle.dense_gqa_decode(q.half().float(), K.permute(0, 2, 1, 3), V.permute(0, 2, 1, 3), 1.0 / math.sqrt(D),
+                                        (seq_lens + 1).to(torch.int32))
+        x = x + a.reshape(B, Hq * D) @ w["wo"]
+        h = _rms(x, w["n2"], cfg.rms_eps)
+        x = x + (torch.nn.functional.silu(h @ w["wg"]) * (h @ w["wu"])) @ w["wd"]
+    return _rms(x, weights["final_norm"], cfg.rms_eps) @ weights["lm_head"]

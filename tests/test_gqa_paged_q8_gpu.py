@@ -53,6 +53,27 @@ def test_unit_variance_long_context(cuda_device, fmt):
     assert (out.float().cpu() - want).abs().max().item() <= TOL
 
 
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+def test_fused_page_records(cuda_device, fmt):
+    """K codes, V codes and scales of a page in one 33-row record: same result, one TMA request per chunk."""
+    from llm_inference_optimization_b200 import paged
+    B, Hq, Hkv, T = 2, 32, 8, 8192
+    Q, pools, (Kd, Vd) = make_case(B, Hq, Hkv, T, fmt, seed=77)
+    kp, vp, ksp, vsp, table = (t.to(cuda_device) for t in pools)
+    lens = torch.tensor([8192, 4999], dtype=torch.int32)
+    buf = paged.pack_fused(kp, vp, ksp, vsp)
+    kv = paged.PagedKV.from_fused(buf, kp.dtype, table, lens.to(cuda_device), B)
+    assert kv.v_pool.data_ptr() == kv.k_pool.data_ptr() + 2048
+    scale = 128 ** -0.5
+    out = kv.decode(Q.to(cuda_device), scale)
+    torch.cuda.synchronize()
+    assert _workspace.status(_workspace.get("gqa", 0, cuda_device)) == 0
+    want = oracle.dense_gqa_decode(Q, Kd, Vd, scale, lens)
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+    sep = _C.fused_gqa_paged(Q.to(cuda_device), kp, vp, ksp, vsp, table, lens.to(cuda_device), scale)
+    assert (out.float() - sep.float()).abs().max().item() <= 1e-3
+
+
 def test_compacted_cache_without_page_table(cuda_device):
     """The [B,H,keep,D] codes + [B,H,keep] scales an eviction produces are read as one page per sequence."""
     g = torch.Generator().manual_seed(9)
