@@ -119,9 +119,10 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
             tma_prefetch_desc(&tmK);
             tma_prefetch_desc(&tmV);
             const uint64_t policy = l2_policy_evict_first();
-            for (int it = 0; it < ntiles; ++it) {
-                const int s = it % p.stages;
-                const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+            int s = 0;        // stage and ring-pass phase advance incrementally: no divisions in this loop
+            uint32_t ph = 0;
+            for (int it = 0; it < ntiles; ++it, ++s) {
+                if (s == p.stages) { s = 0; ph ^= 1u; }
                 if (it >= p.stages && !mbar_wait(empty_bar + s * 8, ph ^ 1u)) {
                     atomicOr(p.status, SKV_DEV_TIMEOUT);
                     break;
@@ -171,9 +172,10 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const int lj = lane >> 3, r8 = lane & 7;
     const int wtok = warp * 16;  // this warp's first token inside a stage
 
-    for (int it = 0; it < ntiles; ++it) {
-        const int s = it % p.stages;
-        const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+    int s = 0;
+    uint32_t ph = 0;
+    for (int it = 0; it < ntiles; ++it, ++s) {
+        if (s == p.stages) { s = 0; ph ^= 1u; }
         if (!mbar_wait(full_bar + s * 8, ph)) {
             if (lane == 0) atomicOr(p.status, SKV_DEV_TIMEOUT);
             break;

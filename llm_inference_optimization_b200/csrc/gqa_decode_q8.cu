@@ -50,7 +50,8 @@ constexpr int RECORD_ROWS = 33;                            // 16 K rows, 16 V ro
 constexpr int RECORD_BYTES = RECORD_ROWS * Q8_D;           // 4224
 constexpr int Q8_WARPS = MAX_CONSUMER_WARPS;               // two groups of four: group g takes stages with it % 2 == g
 constexpr int Q8_CONSUMER_THREADS = Q8_WARPS * 32;
-constexpr int Q8_THREADS = Q8_CONSUMER_THREADS + 32;
+constexpr int Q8_PRODUCERS = 4;                            // producer warps: each issues one share of every stage
+constexpr int Q8_THREADS = Q8_CONSUMER_THREADS + Q8_PRODUCERS * 32;
 
 struct Q8Params {
     const __half* q;
@@ -135,82 +136,78 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
-            mbar_init(full_bar + s * 8, 1);
+            mbar_init(full_bar + s * 8, Q8_PRODUCERS);
             mbar_init(empty_bar + s * 8, CONSUMER_WARPS);
         }
         fence_barrier_init();
     }
     __syncthreads();
 
-    // ------------------------------------------------------------------ producer (whole warp)
-    // Every lane resolves the page of one request group ahead of time (one page-table read per lane per
-    // group of tiles) and later issues one of that group's copies itself.
-    if (warp == Q8_WARPS) {
-        if (lane == 0) {
+    // ------------------------------------------------------------------ producers
+    // Issuing one async copy costs its warp 100-200 cycles, and the copies of one warp are issued one after
+    // another, so a single producer warp cannot keep up with the ~700 cycles a 64-token stage lasts at full
+    // HBM rate.  Four producer warps therefore share every stage; each waits for the stage to be free, adds
+    // its own byte count to the stage's full-barrier (arrival count Q8_PRODUCERS) and issues its copies:
+    //   16-token request groups (fused records / separate pools): warp w fetches chunk w of the stage;
+    //   64-token boxes: warp 0 the K box, 1 the V box, 2 the K scales, 3 the V scales.
+    // Lane l of a producer warp resolves the page of tile (batch * 32 + l) ahead of time, one page-table
+    // read per lane per 32 tiles; lane 0 does the waiting and issuing.
+    if (warp >= Q8_WARPS) {
+        const int pw = warp - Q8_WARPS;
+        if (lane == 0 && pw == 0) {
             tma_prefetch_desc(&tmK);
             tma_prefetch_desc(&tmV);
         }
         const uint64_t policy = l2_policy_evict_first();
         const int P = p.page_size;
-        const int ck_shift = p.mode == Q8_SEPARATE64 ? 6 : 4;     // log2(tokens per request group)
-        const int ck = 1 << ck_shift;
-        const int nck = TILE >> ck_shift;                         // request groups per stage (4 or 1)
-        // The loop below runs once per 64-token stage and must stay well under the ~700 cycles a stage
-        // lasts at full HBM rate: no integer divisions, and the (about 100-cycle) issue of each async copy
-        // is spread over lanes -- lane l serves request group (l / 4) % nck of tile l / (4 * nck) with
-        // role l % 4 (K box, V box, K scales, V scales; role 0 alone in the fused layout).
-        const int role = lane & 3;
-        const int my_tile = (lane >> 2) / nck, my_c = (lane >> 2) - my_tile * nck;  // my_tile in [0, 8 / nck)
-        const int tiles_per_group = 8 / nck;                      // 2 (16-token groups) or 8 (64-token groups)
-        struct ChunkRef { int page, slot; };
-        auto chunk_of = [&](int group_first_tile) -> ChunkRef {
-            const int t = t_begin + (group_first_tile + my_tile) * TILE + (my_c << ck_shift);
-            ChunkRef r{-1, 0};
-            if (t < t_end) {
-                const int lp = t / P;
-                r.slot = t - lp * P;
-                r.page = p.page_table ? __ldg(p.page_table + (long long)b * p.max_pages + lp) : b * p.max_pages + lp;
+        const bool big = p.mode == Q8_SEPARATE64;
+        const int tok_off = big ? 0 : pw * CHUNK;                 // first token of this warp's share inside a stage
+        const uint32_t my_tx = p.mode == Q8_FUSED ? (uint32_t)RECORD_BYTES
+                             : big ? (pw < 2 ? (uint32_t)(TILE * D) : (uint32_t)(TILE * 4))
+                                   : (uint32_t)(2 * CHUNK * D + 2 * CHUNK * 4);
+        int s = 0;
+        uint32_t ph = 0;
+        int ok = 1;
+        for (int it0 = 0; it0 < ntiles && ok; it0 += 32) {
+            int page = -1, slot = 0;
+            {
+                const int t = t_begin + (it0 + lane) * TILE + tok_off;
+                if (t < t_end) {
+                    const int lp = t / P;
+                    slot = t - lp * P;
+                    page = p.page_table ? __ldg(p.page_table + (long long)b * p.max_pages + lp) : b * p.max_pages + lp;
+                }
             }
-            return r;
-        };
-        const uint32_t chunk_tx = p.mode == Q8_FUSED ? (uint32_t)RECORD_BYTES : (uint32_t)(2 * ck * D + 2 * ck * 4);
-        ChunkRef next = chunk_of(0);
-        int ok = 1, s = 0;
-        uint32_t ph = 0;                                          // phase of the ring pass the producer is filling
-        int remaining = t_end - t_begin;                          // tokens not yet requested
-        for (int it0 = 0; it0 < ntiles && ok; it0 += tiles_per_group) {
-            const ChunkRef cur = next;
-            next = chunk_of(it0 + tiles_per_group);
-            const int jn = min(tiles_per_group, ntiles - it0);
+            const int jn = min(32, ntiles - it0);
             for (int j = 0; j < jn; ++j) {
-                const uint32_t bar = full_bar + s * 8;
+                const int pg = __shfl_sync(0xffffffffu, page, j), sl = __shfl_sync(0xffffffffu, slot, j);
                 if (lane == 0) {
+                    const uint32_t bar = full_bar + s * 8;
                     if (it0 + j >= p.stages && !mbar_wait(empty_bar + s * 8, ph ^ 1u)) {
                         atomicOr(p.status, SKV_DEV_TIMEOUT);
                         ok = 0;
+                    } else if (pg < 0) {
+                        mbar_arrive(bar);                         // nothing of this warp's share lies inside the sequence
                     } else {
-                        const int nch = min(nck, (remaining + ck - 1) >> ck_shift);
-                        mbar_expect_tx(bar, (uint32_t)nch * chunk_tx);
+                        mbar_expect_tx(bar, my_tx);
+                        const uint32_t kdst = ring + s * Q8_STAGE_BYTES;
+                        const long long so = (long long)pg * p.sc_sp + (long long)h * p.sc_sh + sl;
+                        if (p.mode == Q8_FUSED) {
+                            pool_tile_load(kdst + pw * RECORD_BYTES, &tmK, bar, p.pos, 0, h, pg, policy);
+                        } else if (big) {
+                            if (pw == 0) pool_tile_load(kdst, &tmK, bar, p.pos, sl, h, pg, policy);
+                            else if (pw == 1) pool_tile_load(kdst + Q8_CODE_BYTES, &tmV, bar, p.pos, sl, h, pg, policy);
+                            else bulk_load(kdst + 2 * Q8_CODE_BYTES + (pw == 3 ? 256 : 0), (pw == 2 ? p.k_scale : p.v_scale) + so, TILE * 4, bar);
+                        } else {
+                            pool_tile_load(kdst + tok_off * D, &tmK, bar, p.pos, sl, h, pg, policy);
+                            pool_tile_load(kdst + Q8_CODE_BYTES + tok_off * D, &tmV, bar, p.pos, sl, h, pg, policy);
+                            bulk_load(kdst + 2 * Q8_CODE_BYTES + tok_off * 4, p.k_scale + so, CHUNK * 4, bar);
+                            bulk_load(kdst + 2 * Q8_CODE_BYTES + 256 + tok_off * 4, p.v_scale + so, CHUNK * 4, bar);
+                        }
                     }
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
-                if (my_tile == j && cur.page >= 0) {
-                    const uint32_t kdst = ring + s * Q8_STAGE_BYTES;
-                    if (p.mode == Q8_FUSED) {
-                        if (role == 0) pool_tile_load(kdst + my_c * RECORD_BYTES, &tmK, bar, p.pos, 0, h, cur.page, policy);
-                    } else if (role == 0) {
-                        pool_tile_load(kdst + (my_c << ck_shift) * D, &tmK, bar, p.pos, cur.slot, h, cur.page, policy);
-                    } else if (role == 1) {
-                        pool_tile_load(kdst + Q8_CODE_BYTES + (my_c << ck_shift) * D, &tmV, bar, p.pos, cur.slot, h, cur.page, policy);
-                    } else {
-                        const long long so = (long long)cur.page * p.sc_sp + (long long)h * p.sc_sh + cur.slot;
-                        const float* src = (role == 2 ? p.k_scale : p.v_scale) + so;
-                        bulk_load(kdst + 2 * Q8_CODE_BYTES + (role == 3 ? 256 : 0) + (my_c << ck_shift) * 4, src, ck * 4, bar);
-                    }
-                }
-                __syncwarp();
-                remaining -= TILE;
                 if (++s == p.stages) { s = 0; ph ^= 1u; }
             }
         }
