@@ -183,6 +183,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=65536)
     ap.add_argument("--no-extras", action="store_true", help="skip the 128K / e2e / CPU legs (profiling runs)")
     ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--no-decode-step", action="store_true", help="skip the full decode-step tokens/s leg")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -367,6 +368,17 @@ def main():
         if world == 1 and rank == 0:
             base, _, _ = cpu_reference_run(args.ctx, 1000, 2, budget_s=15.0)
             line["cpu_baseline"] = base
+
+    if not args.no_extras and not args.no_decode_step:
+        # ---- the other half of the metric: tokens/s of the full tensor-parallel decode step (all ranks take part)
+        from llm_inference_optimization_b200 import bench_decode
+        torch.cuda.empty_cache()
+        try:
+            res = bench_decode.run(steps=10, warmup=3)
+        except Exception as e:  # reported, never fatal for the headline line
+            res = {"error": f"{type(e).__name__}: {e}"}
+        if rank == 0:
+            line["decode_step"] = res
 
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -107,7 +107,7 @@ int skv_gqa_set_q8_stages(int stages);
  * skv_quest_decode: block score for query head hq = scale * sum_d max(q_d*min_d, q_d*max_d) (fp32); the top_k_blocks
  *   best blocks per query head (ties: lower block id) among the blocks the sequence has; out[b,hq,:] = exact softmax
  *   attention over the tokens of those blocks (dequantised, fp32).  block_idx_out optional int32 [B,Hq,top_k_blocks],
- *   ascending, -1 padded.  D = 128, Hq/Hkv <= 8, top_k_blocks <= 256, top_k_blocks*block_size <= 4096.
+ *   ascending, -1 padded.  D = 128, Hq/Hkv <= 8, top_k_blocks <= 256, top_k_blocks*block_size <= 2048.
  *   Workspace holds fp32 block scores [B,Hq,nb]. */
 int skv_quest_num_blocks(int N, int block_size);
 size_t skv_quest_workspace_bytes(int B, int Hq, int N, int block_size);

@@ -1,0 +1,117 @@
+"""Throughput of the full tensor-parallel decode step (random-init Llama-3.1-8B architecture, FP8 paged KV).
+
+    python -m llm_inference_optimization_b200.bench_decode [--steps 20] [--warmup 3] [--layers 32]
+    python -m torch.distributed.run --nproc-per-node N -m llm_inference_optimization_b200.bench_decode ...
+
+Batch 16, context lengths uniform in [8K, 128K] (seed 4), one decode step captured in a CUDA graph and
+replayed; tokens/s = batch / step time (max over ranks).  The reference times the same step on its patched
+Hugging Face model with ``time.perf_counter`` (benchmarks/llama_integration_benchmark.py:266-279).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import decode_step as ds
+from .sharding import shard_heads
+
+
+def ideal_bytes(cfg: ds.ModelConfig, lens: torch.Tensor, world: int) -> dict:
+    per_layer_w = cfg.hidden * (cfg.Hq + 2 * cfg.Hkv) * cfg.D + cfg.Hq * cfg.D * cfg.hidden + 3 * cfg.hidden * cfg.mlp
+    weights = 2 * (cfg.layers * per_layer_w / world + cfg.hidden * cfg.vocab)       # bf16; lm_head replicated
+    kv = int(lens.sum()) * cfg.layers * 2 * (cfg.Hkv // world) * (cfg.D + 4)        # fp8 codes + fp32 scales
+    return {"weight_bytes_per_gpu": int(weights), "kv_bytes_per_gpu": int(kv)}
+
+
+def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, seed: int = 4, use_graph: bool = True,
+        fill: str = "random_codes") -> dict | None:
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    own_group = False
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+        own_group = True
+    cfg = ds.ModelConfig(layers=layers)
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(8192, 131073, (batch,), generator=g, dtype=torch.int32)
+    model = ds.DecodeModel(cfg, shard_heads(cfg.Hq, cfg.Hkv, world, rank), dev, seed=seed)
+    model.init_cache(lens, fill=fill, seed=seed, extra_tokens=steps + warmup + 16)
+    tok = torch.randint(0, cfg.vocab, (batch,), generator=g).to(dev)
+
+    for _ in range(warmup):
+        logits = model.step(tok)
+    torch.cuda.synchronize()
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            model.step(tok)  # once on the capture stream so that its workspaces exist
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(graph):
+            logits = model.step(tok)
+        step = graph.replay
+    else:
+        def step():
+            nonlocal logits
+            logits = model.step(tok)
+    step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    finite = bool(torch.isfinite(logits.float()).all().item())
+    ib = ideal_bytes(cfg, lens, world)
+    out = {
+        "metric": "decode_step_tokens_per_s", "value": batch / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms,
+        "n_gpus": world, "steps": steps, "warmup": warmup, "cuda_graph": use_graph, "logits_finite": finite,
+        "config": {"model": "Llama-3.1-8B architecture, random init N(0,0.02), bf16 weights", "layers": layers,
+                   "batch": batch, "context_lengths": "uniform 8192..131072, seed 4", "total_context_tokens": int(lens.sum()),
+                   "kv": "FP8-E4M3 paged (page 16, fused page records), per-token-per-head fp32 scales, " + fill,
+                   "parallelism": f"tp{world} by KV head, NCCL all-reduce after o_proj and down_proj"},
+        **ib,
+        "hbm_bytes_per_step_per_gpu": ib["weight_bytes_per_gpu"] + ib["kv_bytes_per_gpu"],
+        "achieved_GBps_per_gpu": (ib["weight_bytes_per_gpu"] + ib["kv_bytes_per_gpu"]) / (ms * 1e-3) / 1e9,
+    }
+    del model
+    torch.cuda.empty_cache()
+    if own_group:
+        dist.destroy_process_group()
+    return out if rank == 0 else None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    res = run(args.steps, args.warmup, args.layers, args.batch, use_graph=not args.no_graph)
+    if res is not None:
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

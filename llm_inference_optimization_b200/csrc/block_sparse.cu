@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(SCORE_THREADS)
 block_mean_scores_kernel(const ScoreParams p, int blocks_per_cta) {
     constexpr int LPR = D / 8;
     constexpr int RPW = 32 / LPR;
-    constexpr int U = 8;  // independent 16-byte loads in flight per lane
+    constexpr int U = 16;  // independent 16-byte loads in flight per lane
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPR, rw = lane / LPR;
     const int h = blockIdx.y, b = blockIdx.z;

@@ -41,14 +41,24 @@ struct Plan {
     size_t off_status, off_tickets, off_ml, off_o, total;
 };
 
-// How the KV length is cut: about one CTA per SM (times ctas_per_sm) over all
-// (batch, kv-head) pairs, whole 64-token tiles per split.
+// How the KV length is cut into whole 64-token tiles per split: one CTA per SM (times ctas_per_sm) when
+// there are few (batch, kv-head) pairs, about four waves of CTAs when there are many.
 inline Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device) {
     Plan pl;
     const int G = Hq / Hkv;
     const long long total_tiles = (N + TILE - 1) / TILE;
-    long long target = (long long)sm_count(device) * tuning().ctas_per_sm;
-    long long splits = target / ((long long)B * Hkv);
+    const long long pairs = (long long)B * Hkv;
+    const long long target = (long long)sm_count(device) * tuning().ctas_per_sm;
+    long long splits;
+    if (pairs * 2 <= target) {
+        splits = target / pairs;              // few (batch, head) pairs: one wave, every SM gets one CTA
+    } else {
+        // many pairs, usually with ragged sequence lengths the host does not know: cut into about four
+        // waves of CTAs so that long sequences spread over several SMs (CTAs past a sequence's end exit at once)
+        splits = (4 * target + pairs - 1) / pairs;
+        const long long max_by_size = total_tiles / 16 > 0 ? total_tiles / 16 : 1;   // at least 16 tiles per split
+        if (splits > max_by_size) splits = max_by_size;
+    }
     if (splits < 1) splits = 1;
     if (splits > total_tiles) splits = total_tiles;
     if (splits > MAX_SPLITS) splits = MAX_SPLITS;

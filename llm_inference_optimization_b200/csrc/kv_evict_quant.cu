@@ -109,9 +109,10 @@ struct GatherParams {
     long long sb, sh, st;
 };
 
+// `valid` only guards the stores: every lane of the warp runs the shuffles.
 template <int MODE>
 __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, uint8_t* out_row, float* scale_out,
-                                          __half* out_row_f16) {
+                                          __half* out_row_f16, bool valid) {
     const __half2* hx = reinterpret_cast<const __half2*>(&raw);
     float x[8];
 #pragma unroll
@@ -121,7 +122,7 @@ __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, ui
         x[2 * i + 1] = f.y;
     }
     if (MODE == SKV_QUANT_NONE) {
-        *reinterpret_cast<uint4*>(out_row_f16 + sub * 8) = raw;
+        if (valid) *reinterpret_cast<uint4*>(out_row_f16 + sub * 8) = raw;
         return;
     }
     if (MODE == SKV_QUANT_CAST) {
@@ -131,7 +132,7 @@ __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, ui
             lo |= (uint32_t)((int)x[i] & 0xFF) << (8 * i);      // cvt.rzi then wrap to 8 bits, as the host cast does
             hi |= (uint32_t)((int)x[4 + i] & 0xFF) << (8 * i);
         }
-        *reinterpret_cast<uint2*>(out_row + sub * 8) = make_uint2(lo, hi);
+        if (valid) *reinterpret_cast<uint2*>(out_row + sub * 8) = make_uint2(lo, hi);
         return;
     }
     float amax = 0.f;
@@ -142,10 +143,16 @@ __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, ui
     const float scale = amax > 0.f ? __fdiv_rn(amax, qmax) : 1.f;
     uint32_t lo = 0, hi = 0;
 #pragma unroll
+    // x / scale by an IEEE divide costs ~10 instructions per element and made this kernel issue-bound.
+    // x * (1 / scale) is within 2 ulp of the correctly rounded quotient, so for INT8 (codes must be bit-exact)
+    // the divide is only redone when the product lies within 1e-4 of a rounding boundary (|q| <= 127, ulp <= 8e-6);
+    // FP8 codes are allowed one code step and take the product as is.
+    const float inv = __frcp_rn(scale);
     for (int i = 0; i < 8; ++i) {
-        const float y = __fdiv_rn(x[i], scale);
+        float y = x[i] * inv;
         uint32_t code;
         if (MODE == SKV_QUANT_INT8) {
+            if (fabsf(y - floorf(y) - 0.5f) < 1e-4f) y = __fdiv_rn(x[i], scale);
             int c = __float2int_rn(y);  // round half to even
             c = max(-127, min(127, c));
             code = (uint32_t)c & 0xFFu;
@@ -155,31 +162,53 @@ __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, ui
         }
         if (i < 4) lo |= code << (8 * i); else hi |= code << (8 * (i - 4));
     }
-    *reinterpret_cast<uint2*>(out_row + sub * 8) = make_uint2(lo, hi);
-    if (sub == 0) *scale_out = scale;
+    if (valid) *reinterpret_cast<uint2*>(out_row + sub * 8) = make_uint2(lo, hi);
+    if (valid && sub == 0) *scale_out = scale;
 }
 
-// one group of D/8 lanes per kept (row, j); grid-stride over all kept rows
+// one group of D/8 lanes per kept (row, j); grid-stride over all kept rows, four rows per group and step
+// so that four index loads and then eight 16-byte row loads are in flight per lane
 template <int D, int MODE>
 __global__ void __launch_bounds__(GQ_THREADS)
 evict_gather_quant_kernel(const GatherParams p) {
     constexpr int LPR = D / 8;
     constexpr int GPB = GQ_THREADS / LPR;
+    constexpr int U = 4;
     const int sub = threadIdx.x % LPR, grp = threadIdx.x / LPR;
-    for (long long r = (long long)blockIdx.x * GPB + grp; r < p.rows_total; r += (long long)gridDim.x * GPB) {
-        const long long row = r / p.keep;  // (b, h)
-        const int h = (int)(row % p.H);
-        const long long b = row / p.H;
-        const int t = p.idx[r];
-        const long long src = b * p.sb + h * p.sh + (long long)t * p.st + sub * 8;
-        const uint4 kr = *reinterpret_cast<const uint4*>(p.k + src);
-        const uint4 vr = *reinterpret_cast<const uint4*>(p.v + src);
-        if (MODE == SKV_QUANT_NONE) {
-            quant_row<MODE>(kr, sub, LPR, nullptr, nullptr, static_cast<__half*>(p.k_out) + r * D);
-            quant_row<MODE>(vr, sub, LPR, nullptr, nullptr, static_cast<__half*>(p.v_out) + r * D);
-        } else {
-            quant_row<MODE>(kr, sub, LPR, static_cast<uint8_t*>(p.k_out) + r * D, p.k_scale ? p.k_scale + r : nullptr, nullptr);
-            quant_row<MODE>(vr, sub, LPR, static_cast<uint8_t*>(p.v_out) + r * D, p.v_scale ? p.v_scale + r : nullptr, nullptr);
+    const long long stride = (long long)gridDim.x * GPB;
+    // the trip count is taken from group 0 of the block so that it is the same for every lane of a warp
+    for (long long rb = (long long)blockIdx.x * GPB; rb < p.rows_total; rb += stride * U) {
+        const long long r0 = rb + grp;
+        int t[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long r = r0 + u * stride;
+            t[u] = r < p.rows_total ? __ldg(p.idx + r) : -1;
+        }
+        uint4 kr[U], vr[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long r = r0 + u * stride;
+            if (t[u] >= 0) {
+                const long long row = r / p.keep;  // (b, h)
+                const long long src = (row / p.H) * p.sb + (row % p.H) * p.sh + (long long)t[u] * p.st + sub * 8;
+                kr[u] = ld_stream16(p.k + src);
+                vr[u] = ld_stream16(p.v + src);
+            } else {
+                kr[u] = vr[u] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long r = r0 + u * stride;
+            const bool valid = r < p.rows_total;
+            if (MODE == SKV_QUANT_NONE) {
+                quant_row<MODE>(kr[u], sub, LPR, nullptr, nullptr, static_cast<__half*>(p.k_out) + r * D, valid);
+                quant_row<MODE>(vr[u], sub, LPR, nullptr, nullptr, static_cast<__half*>(p.v_out) + r * D, valid);
+            } else {
+                quant_row<MODE>(kr[u], sub, LPR, static_cast<uint8_t*>(p.k_out) + r * D, p.k_scale + r, nullptr, valid);
+                quant_row<MODE>(vr[u], sub, LPR, static_cast<uint8_t*>(p.v_out) + r * D, p.v_scale + r, nullptr, valid);
+            }
         }
     }
 }

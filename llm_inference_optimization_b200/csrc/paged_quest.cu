@@ -31,7 +31,7 @@ constexpr int CH = 16;            // tokens per page chunk handled at a time
 constexpr int META_THREADS = 256;
 constexpr int SCORE_THREADS = 256;
 constexpr int ATT_THREADS = 256;
-constexpr int MAX_SEL_TOKENS = 4096;  // top_k_blocks * block_size upper bound
+constexpr int MAX_SEL_TOKENS = 2048;  // top_k_blocks * block_size upper bound
 constexpr int MAX_TOPK = 256;
 
 template <int KVT>
@@ -141,29 +141,38 @@ quest_scores_kernel(const ScoreParams p, int blocks_per_cta) {
     }
     const __half* mbase = p.meta + ((long long)b * p.Hkv + h) * p.nb * 2 * D + sub * 8;
     const int j0 = blockIdx.x * blocks_per_cta, j1 = min(p.nb, j0 + blocks_per_cta);
-    for (int base = j0 + warp * 2; base < j1; base += (SCORE_THREADS / 32) * 2) {
-        const int j = base + rw;
-        float acc[MAXG];
+    constexpr int U = 4;  // blocks per half-warp and step: eight 16-byte loads in flight per lane
+    for (int base = j0 + warp * 2 * U; base < j1; base += (SCORE_THREADS / 32) * 2 * U) {
+        uint4 lo4[U], hi4[U];
 #pragma unroll
-        for (int g = 0; g < MAXG; ++g) acc[g] = 0.f;
-        if (j < j1) {
-            float lo[8], hi[8];
-            unpack8(*reinterpret_cast<const uint4*>(mbase + (long long)j * 2 * D), lo);
-            unpack8(*reinterpret_cast<const uint4*>(mbase + (long long)j * 2 * D + D), hi);
+        for (int u = 0; u < U; ++u) {
+            const int j = base + u * 2 + rw;
+            if (j < j1) {
+                lo4[u] = *reinterpret_cast<const uint4*>(mbase + (long long)j * 2 * D);
+                hi4[u] = *reinterpret_cast<const uint4*>(mbase + (long long)j * 2 * D + D);
+            } else {
+                lo4[u] = hi4[u] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
 #pragma unroll
-            for (int g = 0; g < MAXG; ++g)
+        for (int u = 0; u < U; ++u) {
+            const int j = base + u * 2 + rw;
+            float lo[8], hi[8], acc[MAXG];
+            unpack8(lo4[u], lo);
+            unpack8(hi4[u], hi);
+#pragma unroll
+            for (int g = 0; g < MAXG; ++g) {
+                acc[g] = 0.f;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[g] += fmaxf(q[g][i] * lo[i], q[g][i] * hi[i]);
-        }
 #pragma unroll
-        for (int g = 0; g < MAXG; ++g) {
+                for (int o = 8; o > 0; o >>= 1) acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], o);
+            }
+            if (j < j1 && sub == 0) {
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], o);
-        }
-        if (j < j1 && sub == 0) {
-#pragma unroll
-            for (int g = 0; g < MAXG; ++g)
-                if (g < p.G) p.scores[((long long)b * p.Hq + h * p.G + g) * p.nb + j] = acc[g] * p.scale;
+                for (int g = 0; g < MAXG; ++g)
+                    if (g < p.G) p.scores[((long long)b * p.Hq + h * p.G + g) * p.nb + j] = acc[g] * p.scale;
+            }
         }
     }
 }
@@ -187,6 +196,7 @@ quest_select_attend_kernel(const AttendParams p) {
     __shared__ uint32_t tk[TopkSmem<ATT_THREADS>::WORDS];
     __shared__ int sel[MAX_TOPK];
     __shared__ float w[MAX_SEL_TOKENS];
+    __shared__ int2 where[MAX_SEL_TOKENS];  // (page, slot) of every gathered token, page < 0 past the sequence end
     __shared__ float qs[D];
     __shared__ float red[ATT_THREADS / 8 * 16 + 32];  // per row-group partial outputs are reduced through here
     __shared__ float bcast[2];
@@ -209,30 +219,46 @@ quest_select_attend_kernel(const AttendParams p) {
     float qv[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) qv[i] = qs[sub * 16 + i];
+    // resolve every gathered token's page once (one page-table read per token, all in flight together)
+    for (int r = tid; r < ntok; r += ATT_THREADS) {
+        const int t = sel[r / p.block_size] * p.block_size + r % p.block_size;
+        int2 pw = make_int2(-1, 0);
+        if (t < len) pw = make_int2(phys_page(p.page_table, b, p.max_pages, t / p.page_size), t % p.page_size);
+        where[r] = pw;
+    }
+    __syncthreads();
+    constexpr int RU = 4;  // token rows per group and step: their code and scale loads are issued back to back
     float mx = -INFINITY;
-    for (int r0 = 0; r0 < ntok; r0 += ATT_THREADS / 8) {  // uniform trip count: the shuffles below need whole warps
-        const int r = r0 + grp;
-        int t = -1;
-        if (r < ntok) t = sel[r / p.block_size] * p.block_size + r % p.block_size;
-        const bool valid = t >= 0 && t < len;
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        float ksc = 0.f;
-        if (valid) {
-            const int page = phys_page(p.page_table, b, p.max_pages, t / p.page_size), slot = t % p.page_size;
-            raw = *reinterpret_cast<const uint4*>(p.k.codes + page * p.k.sp + h * p.k.sh + slot * p.k.ss + sub * 16);
-            ksc = p.k.scales[page * p.k.csp + h * p.k.csh + slot];
-        }
-        float x[16];
-        unpack16<KVT>(raw, x);
-        float d = 0.f;
+    for (int r0 = 0; r0 < ntok; r0 += RU * (ATT_THREADS / 8)) {  // uniform trip count: the shuffles need whole warps
+        uint4 raw[RU];
+        float ksc[RU];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) d = fmaf(x[i], qv[i], d);
-        d += __shfl_xor_sync(0xffffffffu, d, 1);
-        d += __shfl_xor_sync(0xffffffffu, d, 2);
-        d += __shfl_xor_sync(0xffffffffu, d, 4);
-        const float s = valid ? d * ksc * p.scale : -INFINITY;
-        if (sub == 0 && r < ntok) w[r] = s;
-        mx = fmaxf(mx, s);
+        for (int u = 0; u < RU; ++u) {
+            const int r = r0 + u * (ATT_THREADS / 8) + grp;
+            const int2 pw = r < ntok ? where[r] : make_int2(-1, 0);
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            ksc[u] = 0.f;
+            if (pw.x >= 0) {
+                raw[u] = *reinterpret_cast<const uint4*>(p.k.codes + pw.x * p.k.sp + h * p.k.sh + pw.y * p.k.ss + sub * 16);
+                ksc[u] = p.k.scales[pw.x * p.k.csp + h * p.k.csh + pw.y];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < RU; ++u) {
+            const int r = r0 + u * (ATT_THREADS / 8) + grp;
+            const bool valid = r < ntok && where[r].x >= 0;
+            float x[16];
+            unpack16<KVT>(raw[u], x);
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) d = fmaf(x[i], qv[i], d);
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            const float sv = valid ? d * ksc[u] * p.scale : -INFINITY;
+            if (sub == 0 && r < ntok) w[r] = sv;
+            mx = fmaxf(mx, sv);
+        }
     }
     mx = warp_max(mx);
     if (lane == 0) red[warp] = mx;
@@ -266,16 +292,26 @@ quest_select_attend_kernel(const AttendParams p) {
     float acc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-    for (int r = grp; r < ntok; r += ATT_THREADS / 8) {
-        const int t = sel[r / p.block_size] * p.block_size + r % p.block_size;
-        if (t < len) {
-            const int page = phys_page(p.page_table, b, p.max_pages, t / p.page_size), slot = t % p.page_size;
-            const uint4 raw = *reinterpret_cast<const uint4*>(p.v.codes + page * p.v.sp + h * p.v.sh + slot * p.v.ss + sub * 16);
-            const float wt = w[r] * p.v.scales[page * p.v.csp + h * p.v.csh + slot];
-            float x[16];
-            unpack16<KVT>(raw, x);
+    for (int r0 = grp; r0 < ntok; r0 += RU * (ATT_THREADS / 8)) {
+        uint4 raw[RU];
+        float wt[RU];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] = fmaf(wt, x[i], acc[i]);
+        for (int u = 0; u < RU; ++u) {
+            const int r = r0 + u * (ATT_THREADS / 8);
+            const int2 pw = r < ntok ? where[r] : make_int2(-1, 0);
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            wt[u] = 0.f;
+            if (pw.x >= 0) {
+                raw[u] = *reinterpret_cast<const uint4*>(p.v.codes + pw.x * p.v.sp + h * p.v.sh + pw.y * p.v.ss + sub * 16);
+                wt[u] = w[r] * p.v.scales[pw.x * p.v.csp + h * p.v.csh + pw.y];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < RU; ++u) {
+            float x[16];
+            unpack16<KVT>(raw[u], x);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = fmaf(wt[u], x[i], acc[i]);
         }
     }
     // reduce the 32 row-groups: first inside each warp (4 groups), then across the 8 warps through shared memory
@@ -395,7 +431,7 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
     const long long rows = (long long)B * Hkv;
     long long want = ((long long)sm_count(device) * 8 + rows - 1) / rows;
     int blocks_per_cta = (int)((nb + want - 1) / want);
-    blocks_per_cta = ((blocks_per_cta + 15) / 16) * 16;
+    blocks_per_cta = ((blocks_per_cta + 63) / 64) * 64;  // one CTA step covers 8 warps x 2 half-warps x 4 blocks
     dim3 g1((nb + blocks_per_cta - 1) / blocks_per_cta, Hkv, B);
     if (G <= 4) quest::quest_scores_kernel<4><<<g1, quest::SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);
     else quest::quest_scores_kernel<8><<<g1, quest::SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);

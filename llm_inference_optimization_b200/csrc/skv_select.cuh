@@ -32,6 +32,7 @@ struct TopkSmem {
 template <int NT>
 __device__ void block_topk_sorted(const float* sc, int T, int k, int* out, uint32_t* sm) {
     constexpr int NW = NT / 32;
+    constexpr int LOADS = 8;  // scores fetched per thread before any is processed
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (k <= 0) return;
     if (k >= T) {
@@ -50,9 +51,33 @@ __device__ void block_topk_sorted(const float* sc, int T, int k, int* out, uint3
         for (int i = tid; i < NW * 256; i += NT) hist[i] = 0;
         __syncthreads();
         uint32_t* myh = hist + warp * 256;
-        for (int i = tid; i < T; i += NT) {
-            const uint32_t key = score_key(sc[i]);
-            if ((key & mask) == prefix) atomicAdd(&myh[(key >> shift) & 255u], 1u);
+        for (int base = 0; base < T; base += NT * LOADS) {  // uniform trip count: the warp votes need every lane
+            float v[LOADS];
+#pragma unroll
+            for (int u = 0; u < LOADS; ++u) {  // independent loads first: their latencies overlap
+                const int i = base + u * NT + tid;
+                v[u] = i < T ? sc[i] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < LOADS; ++u) {
+                const int i = base + u * NT + tid;
+                const uint32_t key = score_key(v[u]);
+                const bool act = i < T && (key & mask) == prefix;
+                const uint32_t digit = (key >> shift) & 255u;
+                // Scores cluster in a few exponent values, so the leading digits of a warp's 32 keys are often
+                // all equal: then one lane adds the whole count instead of 32 conflicting atomics on one address.
+                const uint32_t voters = __ballot_sync(0xffffffffu, act);
+                if (voters) {
+                    const int leader = __ffs(voters) - 1;
+                    const uint32_t d0 = __shfl_sync(0xffffffffu, digit, leader);
+                    const uint32_t same = __ballot_sync(0xffffffffu, act && digit == d0);
+                    if (same == voters) {
+                        if (lane == leader) atomicAdd(&myh[d0], (uint32_t)__popc(voters));
+                    } else if (act) {
+                        atomicAdd(&myh[digit], 1u);
+                    }
+                }
+            }
         }
         __syncthreads();
         for (int b = tid; b < 256; b += NT) {  // fold the per-warp histograms into row 0
@@ -101,12 +126,20 @@ __device__ void block_topk_sorted(const float* sc, int T, int k, int* out, uint3
     seg = (seg + 31) & ~31;
     const int s0 = min(T, warp * seg), s1 = min(T, s0 + seg);
     uint32_t gt = 0, eq = 0;
-    for (int i0 = s0; i0 < s1; i0 += 32) {
-        const int i = i0 + lane;
-        const bool in = i < s1;
-        const uint32_t key = in ? score_key(sc[i]) : 0u;
-        gt += __popc(__ballot_sync(0xffffffffu, in && key > thr));
-        eq += __popc(__ballot_sync(0xffffffffu, in && key == thr));
+    for (int i0 = s0; i0 < s1; i0 += 32 * LOADS) {
+        float v[LOADS];
+#pragma unroll
+        for (int u = 0; u < LOADS; ++u) {
+            const int i = i0 + u * 32 + lane;
+            v[u] = i < s1 ? sc[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < LOADS; ++u) {
+            const bool in = i0 + u * 32 + lane < s1;
+            const uint32_t key = score_key(v[u]);
+            gt += __popc(__ballot_sync(0xffffffffu, in && key > thr));
+            eq += __popc(__ballot_sync(0xffffffffu, in && key == thr));
+        }
     }
     if (lane == 0) { wcnt[warp] = gt; wcnt[NW + warp] = eq; }
     __syncthreads();
@@ -138,17 +171,26 @@ __device__ void block_topk_sorted(const float* sc, int T, int k, int* out, uint3
     __syncthreads();
     uint32_t pos = wcnt[2 * NW + warp], eqrun = wcnt[3 * NW + warp];
     const uint32_t lt = (1u << lane) - 1u;
-    for (int i0 = s0; i0 < s1; i0 += 32) {
-        const int i = i0 + lane;
-        const bool in = i < s1;
-        const uint32_t key = in ? score_key(sc[i]) : 0u;
-        const bool isgt = in && key > thr, iseq = in && key == thr;
-        const uint32_t beq = __ballot_sync(0xffffffffu, iseq);
-        const bool sel = isgt || (iseq && (int)(eqrun + __popc(beq & lt)) < need);
-        const uint32_t bsel = __ballot_sync(0xffffffffu, sel);
-        if (sel) out[pos + __popc(bsel & lt)] = i;
-        pos += __popc(bsel);
-        eqrun += __popc(beq);
+    for (int i0 = s0; i0 < s1; i0 += 32 * LOADS) {
+        float v[LOADS];
+#pragma unroll
+        for (int u = 0; u < LOADS; ++u) {
+            const int i = i0 + u * 32 + lane;
+            v[u] = i < s1 ? sc[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < LOADS; ++u) {
+            const int i = i0 + u * 32 + lane;
+            const bool in = i < s1;
+            const uint32_t key = score_key(v[u]);
+            const bool isgt = in && key > thr, iseq = in && key == thr;
+            const uint32_t beq = __ballot_sync(0xffffffffu, iseq);
+            const bool sel = isgt || (iseq && (int)(eqrun + __popc(beq & lt)) < need);
+            const uint32_t bsel = __ballot_sync(0xffffffffu, sel);
+            if (sel) out[pos + __popc(bsel & lt)] = i;
+            pos += __popc(bsel);
+            eqrun += __popc(beq);
+        }
     }
     __syncthreads();
 }

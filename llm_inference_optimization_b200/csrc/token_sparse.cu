@@ -23,6 +23,10 @@ namespace tsp {
 constexpr int SCORE_THREADS = 256;
 constexpr int ATT_THREADS = 1024;
 constexpr int MAX_KEEP = 4096;  // top_k + sink_tokens upper bound
+constexpr int MAX_CAND_K = 256;  // largest top_k served by the per-chunk candidate path
+
+// Chunk slots reserved in the workspace for candidates (scores CTAs: about 8 per SM plus one per row).
+inline long long cand_capacity_chunks(long long rows) { return 2048 + 2 * rows; }
 
 struct ScoreParams {
     const __half* q;   // element (b,h,s,d) at b*q_sb + h*q_sh + s*q_ss + d
@@ -31,6 +35,10 @@ struct ScoreParams {
     int H, S, T;
     long long q_sb, q_sh, q_ss, k_sb, k_sh, k_st;
     float scale;
+    // candidate mode (cand_k > 0): every CTA also leaves the cand_k best tokens of its chunk
+    float* cand_score;   // [rows, nchunks, cand_k], -inf padded
+    int* cand_pos;       // [rows, nchunks, cand_k], -1 padded
+    int cand_k;
 };
 
 // grid (ceil(T / tokens_per_cta), H, B*S)
@@ -41,6 +49,8 @@ token_scores_kernel(const ScoreParams p, int tokens_per_cta) {
     constexpr int RPW = 32 / LPR;   // rows per warp-wide load
     constexpr int SUB = 32 / RPW;   // loads per 32 tokens
     __shared__ float stage[SCORE_THREADS / 32][32];
+    extern __shared__ uint32_t cand_sm[];  // candidate mode: chunk scores [tokens_per_cta], select scratch, positions
+    float* chunk_sc = reinterpret_cast<float*>(cand_sm);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPR, rw = lane / LPR;
     const int h = blockIdx.y, b = blockIdx.z / p.S, s = blockIdx.z % p.S;
@@ -75,8 +85,27 @@ token_scores_kernel(const ScoreParams p, int tokens_per_cta) {
             if (sub == 0) stage[warp][j * RPW + rw] = d * p.scale;
         }
         __syncwarp();
-        if (base + lane < t1) srow[base + lane] = stage[warp][lane];
+        if (base + lane < t1) {
+            srow[base + lane] = stage[warp][lane];
+            if (p.cand_k > 0) chunk_sc[base + lane - t0] = stage[warp][lane];
+        }
         __syncwarp();
+    }
+    if (p.cand_k > 0) {
+        // The global top-k is a subset of the union of every chunk's top-k, so the row-wide selection later
+        // only has to look at nchunks * cand_k candidates instead of all T scores.
+        uint32_t* tk = cand_sm + tokens_per_cta;
+        int* csel = reinterpret_cast<int*>(tk + TopkSmem<SCORE_THREADS>::WORDS);
+        const int n = t1 - t0, kc = min(p.cand_k, n);
+        __syncthreads();
+        block_topk_sorted<SCORE_THREADS>(chunk_sc, n, kc, csel, tk);
+        __syncthreads();
+        const long long row = ((long long)b * p.H + h) * p.S + s;
+        const long long o = (row * gridDim.x + blockIdx.x) * p.cand_k;
+        for (int i = threadIdx.x; i < p.cand_k; i += SCORE_THREADS) {
+            p.cand_pos[o + i] = i < kc ? t0 + csel[i] : -1;
+            p.cand_score[o + i] = i < kc ? chunk_sc[csel[i]] : -INFINITY;
+        }
     }
 }
 
@@ -87,6 +116,9 @@ struct AttendParams {
     int* topk_idx;        // optional [rows, top_k], ascending, -1 padded
     int H, S, T, top_k, sink;
     long long v_sb, v_sh, v_st;
+    const float* cand_score;  // candidate mode: [rows, nc]; null otherwise
+    const int* cand_pos;
+    int nc;
 };
 
 // grid (rows = B*H*S)
@@ -111,7 +143,16 @@ token_select_attend_kernel(const AttendParams p) {
 
     // 1. exact top-k, ascending positions, into sel[sink ...)
     int* top = sel + sink;
-    block_topk_sorted<ATT_THREADS>(sc, p.T, kk, top, tk);
+    if (p.cand_score) {
+        // candidates are ordered by token position (chunk by chunk, ascending inside a chunk), so "equal scores:
+        // lower candidate index first" is the same rule as "lower token position first"
+        block_topk_sorted<ATT_THREADS>(p.cand_score + (long long)row * p.nc, p.nc, kk, top, tk);
+        __syncthreads();
+        for (int i = tid; i < kk; i += ATT_THREADS) top[i] = p.cand_pos[(long long)row * p.nc + top[i]];
+        __syncthreads();
+    } else {
+        block_topk_sorted<ATT_THREADS>(sc, p.T, kk, top, tk);
+    }
     if (p.topk_idx) {
         for (int i = tid; i < p.top_k; i += ATT_THREADS) p.topk_idx[(long long)row * p.top_k + i] = i < kk ? top[i] : -1;
     }
@@ -208,7 +249,7 @@ static size_t attend_smem() {
 }
 
 template <int D>
-static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int device, cudaStream_t st) {
+static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int device, cudaStream_t st, float* cand_base) {
     static bool configured[64] = {false};
     const size_t smem = attend_smem<D>();
     if (device < 64 && !configured[device]) {
@@ -222,9 +263,30 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     tokens_per_cta = ((tokens_per_cta + 255) / 256) * 256;
     if (tokens_per_cta < 512) tokens_per_cta = 512;
     dim3 g1((sp.T + tokens_per_cta - 1) / tokens_per_cta, sp.H, B * sp.S);
-    token_scores_kernel<D><<<g1, SCORE_THREADS, 0, st>>>(sp, tokens_per_cta);
+    ScoreParams sp2 = sp;
+    AttendParams ap2 = ap;
+    const int nchunks = (int)g1.x;
+    const int kk = ap.top_k < sp.T ? ap.top_k : sp.T;
+    size_t smem1 = 0;
+    if (kk <= MAX_CAND_K && nchunks >= 2 && tokens_per_cta <= 8192 && (long long)nchunks * kk * 4 <= sp.T &&
+        (long long)rows * nchunks <= cand_capacity_chunks(rows)) {
+        sp2.cand_k = kk;
+        sp2.cand_score = cand_base;
+        sp2.cand_pos = reinterpret_cast<int*>(cand_base + cand_capacity_chunks(rows) * MAX_CAND_K);
+        ap2.cand_score = sp2.cand_score;
+        ap2.cand_pos = sp2.cand_pos;
+        ap2.nc = nchunks * kk;
+        smem1 = (size_t)tokens_per_cta * 4 + (size_t)TopkSmem<SCORE_THREADS>::WORDS * 4 + (size_t)MAX_CAND_K * 4;
+        static bool configured1[64] = {false};
+        if (device < 64 && !configured1[device]) {
+            SKV_CUDA_TRY(cudaFuncSetAttribute(token_scores_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              8192 * 4 + (int)TopkSmem<SCORE_THREADS>::WORDS * 4 + MAX_CAND_K * 4));
+            configured1[device] = true;
+        }
+    }
+    token_scores_kernel<D><<<g1, SCORE_THREADS, smem1, st>>>(sp2, tokens_per_cta);
     SKV_CUDA_TRY(cudaGetLastError());
-    token_select_attend_kernel<D><<<(unsigned)rows, ATT_THREADS, smem, st>>>(ap);
+    token_select_attend_kernel<D><<<(unsigned)rows, ATT_THREADS, smem, st>>>(ap2);
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }
@@ -238,7 +300,8 @@ extern "C" {
 
 size_t skv_token_sparse_workspace_bytes(int B, int H, int S, int T) {
     if (B <= 0 || H <= 0 || S <= 0 || T <= 0) return 0;
-    return 256 + ((((size_t)B * H * S * T * sizeof(float)) + 255) & ~size_t(255));
+    const size_t scores = (((size_t)B * H * S * T * sizeof(float)) + 255) & ~size_t(255);
+    return 256 + scores + (size_t)tsp::cand_capacity_chunks((long long)B * H * S) * tsp::MAX_CAND_K * 8;
 }
 
 int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* out, int* topk_idx_out,
@@ -274,6 +337,7 @@ int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* o
     sp.q_sb = q_stride_b; sp.q_sh = q_stride_h; sp.q_ss = q_stride_s;
     sp.k_sb = kv_stride_b; sp.k_sh = kv_stride_h; sp.k_st = kv_stride_t;
     sp.scale = scale;
+    sp.cand_score = nullptr; sp.cand_pos = nullptr; sp.cand_k = 0;
     tsp::AttendParams ap;
     ap.scores = sp.scores;
     ap.v = static_cast<const __half*>(v);
@@ -281,13 +345,16 @@ int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* o
     ap.topk_idx = topk_idx_out;
     ap.H = H; ap.S = S; ap.T = T; ap.top_k = top_k; ap.sink = sink_tokens;
     ap.v_sb = kv_stride_b; ap.v_sh = kv_stride_h; ap.v_st = kv_stride_t;
+    ap.cand_score = nullptr; ap.cand_pos = nullptr; ap.nc = 0;
+    const size_t scores_bytes = (((size_t)B * H * S * T * sizeof(float)) + 255) & ~size_t(255);
+    float* cand_base = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256 + scores_bytes);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (D) {
-        case 16: return tsp::launch<16>(sp, ap, B, device, st);
-        case 32: return tsp::launch<32>(sp, ap, B, device, st);
-        case 64: return tsp::launch<64>(sp, ap, B, device, st);
-        case 128: return tsp::launch<128>(sp, ap, B, device, st);
-        default: return tsp::launch<256>(sp, ap, B, device, st);
+        case 16: return tsp::launch<16>(sp, ap, B, device, st, cand_base);
+        case 32: return tsp::launch<32>(sp, ap, B, device, st, cand_base);
+        case 64: return tsp::launch<64>(sp, ap, B, device, st, cand_base);
+        case 128: return tsp::launch<128>(sp, ap, B, device, st, cand_base);
+        default: return tsp::launch<256>(sp, ap, B, device, st, cand_base);
     }
 }
 
