@@ -112,6 +112,7 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         fence_barrier_init();
     }
     __syncthreads();
+    pdl_launch_dependents();  // the next launch may start its own prologue and K/V streaming as SMs free up
 
     // ------------------------------------------------------------------ producer
     if (warp == CONSUMER_WARPS) {
@@ -145,6 +146,10 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const int g = lane >> 2;   // MMA row (query head within the group); rows g and g + 8
     const int tq = lane & 3;   // column pair within an 8-wide tile
     const int G = p.G;
+
+    // The K/V stream of the producer warp does not depend on the previous kernel, the query might (it can be
+    // that kernel's output) and the workspace / output written below certainly do: wait for it here.
+    pdl_wait_prior_grids();
 
     // Query fragments for all k-steps, zero for padding rows.
     uint32_t qa[KSTEPS][4];
@@ -325,7 +330,7 @@ static int launch_f16(const CUtensorMap& tmK, const CUtensorMap& tmV, const Para
         configured_smem[dev] = (int)smem;
     }
     dim3 grid(p.Hkv, p.num_splits, B);
-    gqa_decode_f16_kernel<D><<<grid, THREADS, smem, stream>>>(tmK, tmV, p);
+    SKV_CUDA_TRY(launch_pdl(gqa_decode_f16_kernel<D>, grid, dim3(THREADS), smem, stream, tmK, tmV, p));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }
@@ -349,7 +354,9 @@ int skv_gqa_set_tuning(int stages, int ctas_per_sm) {
 
 size_t skv_gqa_decode_workspace_bytes(int B, int N, int Hq, int Hkv, int D, int device) {
     if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || D <= 0) return 0;
-    return gqa::make_plan(B, N, Hq, Hkv, D, device).total;
+    // large enough for either split policy (with or without per-sequence lengths)
+    const size_t a = gqa::make_plan(B, N, Hq, Hkv, D, device, false).total, b = gqa::make_plan(B, N, Hq, Hkv, D, device, true).total;
+    return a > b ? a : b;
 }
 
 int skv_gqa_decode_splits(int B, int N, int Hq, int Hkv, int D, int device) {
@@ -375,7 +382,7 @@ int skv_gqa_decode(const void* q, const void* k, const void* v, void* out, void*
     DeviceGuard guard(device);
     if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
 
-    gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device);
+    gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device, seq_lens != nullptr);
     if (!workspace || workspace_bytes < pl.total)
         return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, pl.total);
     if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(SKV_ERR_WORKSPACE, "workspace must be 256-byte aligned");
@@ -450,7 +457,7 @@ int skv_gqa_decode_noalloc(const void* q, const void* k, const void* v, void* ou
     DeviceGuard guard(device);
     if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
 
-    const gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device);
+    const gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device, seq_lens != nullptr);
     if (pl.total > (size_t)SKV_GQA_STATIC_SCRATCH_BYTES)
         return fail(SKV_ERR_WORKSPACE,
                     "this problem needs %zu bytes of scratch but the built-in array holds %u: "

@@ -142,6 +142,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         fence_barrier_init();
     }
     __syncthreads();
+    pdl_launch_dependents();
 
     // ------------------------------------------------------------------ producers
     // Issuing one async copy costs its warp 100-200 cycles, and the copies of one warp are issued one after
@@ -215,6 +216,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     }
 
     // ----------------------------------------------------------------- consumers
+    pdl_wait_prior_grids();  // the query, the workspace and the output may belong to the previous kernel until now
     const int g = lane >> 2, tq = lane & 3;
     const int G = p.G;
 
@@ -422,7 +424,7 @@ static int launch_q8(const CUtensorMap& tmK, const CUtensorMap& tmV, const Q8Par
         configured_smem[dev] = (int)smem;
     }
     dim3 grid(p.Hkv, p.num_splits, B);
-    gqa_decode_q8_kernel<KVT><<<grid, Q8_THREADS, smem, stream>>>(tmK, tmV, p);
+    SKV_CUDA_TRY(launch_pdl(gqa_decode_q8_kernel<KVT>, grid, dim3(Q8_THREADS), smem, stream, tmK, tmV, p));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }
@@ -465,7 +467,7 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     DeviceGuard guard(device);
     if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
 
-    gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device);
+    gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device, seq_lens != nullptr);
     if (!workspace || workspace_bytes < pl.total)
         return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, pl.total);
     if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(SKV_ERR_WORKSPACE, "workspace must be 256-byte aligned");

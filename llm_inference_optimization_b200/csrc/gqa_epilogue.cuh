@@ -43,19 +43,21 @@ struct Plan {
 
 // How the KV length is cut into whole 64-token tiles per split: one CTA per SM (times ctas_per_sm) when
 // there are few (batch, kv-head) pairs, about four waves of CTAs when there are many.
-inline Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device) {
+inline Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device, bool ragged = false) {
     Plan pl;
     const int G = Hq / Hkv;
     const long long total_tiles = (N + TILE - 1) / TILE;
     const long long pairs = (long long)B * Hkv;
     const long long target = (long long)sm_count(device) * tuning().ctas_per_sm;
     long long splits;
-    if (pairs * 2 <= target) {
-        splits = target / pairs;              // few (batch, head) pairs: one wave, every SM gets one CTA
+    if (!ragged && pairs * 2 <= target) {
+        splits = target / pairs;              // few equally long (batch, head) pairs: one wave, one CTA per SM
     } else {
-        // many pairs, usually with ragged sequence lengths the host does not know: cut into about four
-        // waves of CTAs so that long sequences spread over several SMs (CTAs past a sequence's end exit at once)
-        splits = (4 * target + pairs - 1) / pairs;
+        // Many pairs, or per-sequence lengths the host does not know: a CTA streams at about 1/SMs of the HBM
+        // rate, so work is cut into about eight waves of CTAs to let long sequences spread over many SMs
+        // (CTAs past a sequence's end exit at once).
+        const long long waves = ragged ? 8 : 4;
+        splits = (waves * target + pairs - 1) / pairs;
         const long long max_by_size = total_tiles / 16 > 0 ? total_tiles / 16 : 1;   // at least 16 tiles per split
         if (splits > max_by_size) splits = max_by_size;
     }

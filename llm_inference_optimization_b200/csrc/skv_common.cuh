@@ -78,6 +78,26 @@ inline int sm_count(int device) {
     return n;
 }
 
+#if defined(__CUDACC__)
+// Launch with the programmatic-stream-serialization attribute: if the previous kernel in the stream calls
+// griddepcontrol.launch_dependents, this one may begin (its prologue and independent loads) before that
+// kernel has drained; it must execute griddepcontrol.wait before touching anything that kernel writes.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
 // ---------------------------------------------------------------------------
 // Device helpers
 // ---------------------------------------------------------------------------
@@ -197,6 +217,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// Programmatic dependent launch: let the next kernel in the stream start while this one is still running ...
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ... and, in that next kernel, wait until every earlier kernel has finished and its writes are visible.
+__device__ __forceinline__ void pdl_wait_prior_grids() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
