@@ -271,24 +271,32 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             const uint8_t* stage = smem + (size_t)s * Q8_STAGE_BYTES;
             const bool ragged = tok0 + 16 > t_end;
 
-            float sc[2][4];
+            // Two accumulators per 8-token tile (even / odd ldmatrix groups) halve the dependent MMA chain.
+            float sc[2][4], sd[2][4];
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+            for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                const uint32_t row = (uint32_t)(nt * 8 + r8);
+                for (int j = 0; j < 4; ++j) sc[nt][j] = sd[nt][j] = 0.f;
 #pragma unroll
-                for (int m = 0; m < NCH / 4; ++m) {
+            for (int m = 0; m < NCH / 4; ++m) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const uint32_t row = (uint32_t)(nt * 8 + r8);
                     uint32_t br[4];
                     ldsm_x4(kbase + row * 128 + (((uint32_t)(4 * m + lj) ^ sw) << 4), br[0], br[1], br[2], br[3]);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         uint32_t b0, b1;
                         cvt_quad<KVT>(br[j], b0, b1);
-                        mma_f16(sc[nt], qa[4 * m + j], b0, b1);
+                        if (j & 1) mma_f16(sd[nt], qa[4 * m + j], b0, b1);
+                        else mma_f16(sc[nt], qa[4 * m + j], b0, b1);
                     }
                 }
             }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sc[nt][j] += sd[nt][j];
 
             // per-token scales of this lane's two columns in each 8-token tile
             float2 ksc[2], vsc[2];

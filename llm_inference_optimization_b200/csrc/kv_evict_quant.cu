@@ -18,6 +18,7 @@
 //      the K and V rows, row amax by shuffles, IEEE divide + round-half-even, one
 //      8-byte store of codes per lane.  HBM-bound: 2 x 256 B read and 2 x 128 B
 //      written per kept token at D = 128.
+#include <cooperative_groups.h>
 #include <cuda_fp8.h>
 
 #include "skv_common.cuh"
@@ -96,6 +97,197 @@ evict_select_kernel(const SelectParams p) {
     for (int i = tid; i < keep; i += SEL_THREADS) out[i] = sel[i];
 }
 
+// ---------------------------------------------------------------------------
+// Cluster variant of the selection (position order only).  One CTA is issue-bound at about 6 us per radix
+// pass over 32 K scores, so a thread-block cluster of CL CTAs shares each (b, h) row: every CTA keeps its
+// slice of the keys in registers (loaded once), the per-pass digit histograms are summed across the cluster
+// through distributed shared memory, and each CTA writes its part of the ascending position list.
+// Serves rows of up to CL * 1024 * KR competing scores; longer rows take the single-CTA kernel.
+// ---------------------------------------------------------------------------
+constexpr int CL = 4;   // CTAs per cluster
+constexpr int KR = 8;   // keys per thread
+
+__global__ void __cluster_dims__(CL, 1, 1) __launch_bounds__(SEL_THREADS)
+evict_select_cluster_kernel(const SelectParams p) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    constexpr int NW = SEL_THREADS / 32;
+    __shared__ uint32_t hist[NW * 256];   // per-warp private digit counts
+    __shared__ uint32_t chist[2][256];    // this CTA's folded counts, double-buffered across passes
+    __shared__ uint32_t thist[256];       // cluster-wide counts
+    __shared__ uint32_t wcnt[4 * NW];
+    __shared__ uint32_t ctot[2];          // this CTA's (greater, equal) totals
+    __shared__ uint32_t bc[4];
+
+    const int crank = (int)cluster.block_rank();
+    const int row = blockIdx.x / CL;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float* sc = p.scores + (long long)row * p.T;
+    const int recent = min(p.recent, p.T);
+    const int head = p.T - recent;        // positions competing on score
+    const int kb = min(p.budget, head);   // how many of them survive
+    int* out = p.idx + (long long)row * p.keep;
+
+    // slice of this CTA, then a contiguous 32-aligned segment per warp; lane l holds elements s0 + 32 j + l
+    int span = (head + CL - 1) / CL;
+    span = (span + 31) & ~31;
+    const int e0 = min(head, crank * span), e1 = min(head, e0 + span);
+    int seg = (span + NW - 1) / NW;
+    seg = (seg + 31) & ~31;               // <= 32 * KR by the host-side size check
+    const int s0 = min(e1, e0 + warp * seg), s1 = min(e1, s0 + seg);
+    uint32_t key[KR];
+    uint32_t have = 0;                    // bit j: element j exists
+#pragma unroll
+    for (int j = 0; j < KR; ++j) {
+        const int i = s0 + j * 32 + lane;
+        key[j] = 0u;
+        if (i < s1) { key[j] = score_key(sc[i]); have |= 1u << j; }
+    }
+
+    uint32_t thr = 0;
+    int need = 0;
+    if (kb < head && kb > 0) {
+        uint32_t prefix = 0, mask = 0;
+        int remaining = kb;
+#pragma unroll 1
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            for (int i = tid; i < NW * 256; i += SEL_THREADS) hist[i] = 0;
+            __syncthreads();
+            uint32_t* myh = hist + warp * 256;
+#pragma unroll
+            for (int j = 0; j < KR; ++j) {
+                const bool act = ((have >> j) & 1u) && (key[j] & mask) == prefix;
+                const uint32_t digit = (key[j] >> shift) & 255u;
+                const uint32_t voters = __ballot_sync(0xffffffffu, act);
+                if (voters) {
+                    const int leader = __ffs(voters) - 1;
+                    const uint32_t d0 = __shfl_sync(0xffffffffu, digit, leader);
+                    const uint32_t same = __ballot_sync(0xffffffffu, act && digit == d0);
+                    if (same == voters) {
+                        if (lane == leader) atomicAdd(&myh[d0], (uint32_t)__popc(voters));
+                    } else if (act) {
+                        atomicAdd(&myh[digit], 1u);
+                    }
+                }
+            }
+            __syncthreads();
+            if (tid < 256) {
+                uint32_t t = 0;
+#pragma unroll 8
+                for (int w = 0; w < NW; ++w) t += hist[w * 256 + tid];
+                chist[pass & 1][tid] = t;
+            }
+            cluster.sync();   // every CTA's folded counts of this pass are in place
+            if (tid < 256) {
+                uint32_t t = 0;
+#pragma unroll
+                for (int c = 0; c < CL; ++c) t += cluster.map_shared_rank(&chist[pass & 1][0], c)[tid];
+                thist[tid] = t;
+            }
+            __syncthreads();
+            if (warp == 0) {  // same digit search as the single-CTA routine, on the cluster-wide counts
+                uint32_t mine = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mine += thist[255 - 8 * lane - j];
+                uint32_t incl = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                const uint32_t hit = __ballot_sync(0xffffffffu, incl >= (uint32_t)remaining);
+                const int owner = __ffs(hit) - 1;
+                if (lane == owner) {
+                    uint32_t above = incl - mine;
+                    int d = 255 - 8 * lane;
+                    for (int j = 0; j < 8; ++j, --d) {
+                        const uint32_t c = thist[d];
+                        if (above + c >= (uint32_t)remaining) break;
+                        above += c;
+                    }
+                    bc[0] = (uint32_t)d;
+                    bc[1] = (uint32_t)remaining - above;
+                }
+            }
+            __syncthreads();
+            prefix |= bc[0] << shift;
+            mask |= 0xFFu << shift;
+            remaining = (int)bc[1];
+            __syncthreads();
+        }
+        thr = prefix;
+        need = remaining;
+    } else {
+        need = head;  // kb >= head: every competing score survives (thr = 0 makes every key "greater or equal")
+    }
+
+    // per-warp counts of keys above / equal to the threshold
+    uint32_t gt = 0, eq = 0;
+#pragma unroll
+    for (int j = 0; j < KR; ++j) {
+        const bool in = (have >> j) & 1u;
+        gt += __popc(__ballot_sync(0xffffffffu, in && (kb >= head || key[j] > thr)));
+        eq += __popc(__ballot_sync(0xffffffffu, in && kb < head && key[j] == thr));
+    }
+    if (lane == 0) { wcnt[warp] = gt; wcnt[NW + warp] = eq; }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t g = 0, e = 0;
+        for (int w = 0; w < NW; ++w) { g += wcnt[w]; e += wcnt[NW + w]; }
+        ctot[0] = g;
+        ctot[1] = e;
+    }
+    cluster.sync();
+    // ties and selected positions in the CTAs before this one
+    uint32_t eq_before = 0, sel_before = 0;
+    for (int c = 0; c < crank; ++c) {
+        const uint32_t* o = cluster.map_shared_rank(&ctot[0], c);
+        const uint32_t g = o[0], e = o[1];
+        sel_before += g + (uint32_t)max(0, min((int)e, need - (int)eq_before));
+        eq_before += e;
+    }
+    if (warp == 0) {
+        const uint32_t g = wcnt[lane], e = wcnt[NW + lane];   // NW == 32
+        uint32_t ei = e;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, ei, o);
+            if (lane >= o) ei += v;
+        }
+        const uint32_t eex = eq_before + ei - e;
+        const uint32_t take = (uint32_t)max(0, min((int)e, need - (int)eex));
+        const uint32_t sl = g + take;
+        uint32_t si = sl;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, si, o);
+            if (lane >= o) si += v;
+        }
+        wcnt[2 * NW + lane] = sel_before + si - sl;
+        wcnt[3 * NW + lane] = eex;
+    }
+    __syncthreads();
+    uint32_t pos = wcnt[2 * NW + warp], eqrun = wcnt[3 * NW + warp];
+    const uint32_t lt = (1u << lane) - 1u;
+    if (kb > 0) {
+#pragma unroll
+        for (int j = 0; j < KR; ++j) {
+            const bool in = (have >> j) & 1u;
+            const bool isgt = in && (kb >= head || key[j] > thr), iseq = in && kb < head && key[j] == thr;
+            const uint32_t beq = __ballot_sync(0xffffffffu, iseq);
+            const bool sel = isgt || (iseq && (int)(eqrun + __popc(beq & lt)) < need);
+            const uint32_t bsel = __ballot_sync(0xffffffffu, sel);
+            if (sel) out[pos + __popc(bsel & lt)] = s0 + j * 32 + lane;
+            pos += __popc(bsel);
+            eqrun += __popc(beq);
+        }
+    }
+    if (crank == 0)
+        for (int i = tid; i < recent; i += SEL_THREADS) out[kb + i] = head + i;
+    cluster.sync();   // nobody leaves while a neighbour may still read its shared memory
+}
+
 struct GatherParams {
     const __half* k;   // element (b,h,t,d) at b*sb + h*sh + t*st + d
     const __half* v;
@@ -142,26 +334,26 @@ __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, ui
     const float qmax = MODE == SKV_QUANT_INT8 ? 127.f : 448.f;
     const float scale = amax > 0.f ? __fdiv_rn(amax, qmax) : 1.f;
     uint32_t lo = 0, hi = 0;
-#pragma unroll
     // x / scale by an IEEE divide costs ~10 instructions per element and made this kernel issue-bound.
     // x * (1 / scale) is within 2 ulp of the correctly rounded quotient, so for INT8 (codes must be bit-exact)
     // the divide is only redone when the product lies within 1e-4 of a rounding boundary (|q| <= 127, ulp <= 8e-6);
     // FP8 codes are allowed one code step and take the product as is.
     const float inv = __frcp_rn(scale);
+    int c[8];
+#pragma unroll
     for (int i = 0; i < 8; ++i) {
         float y = x[i] * inv;
-        uint32_t code;
         if (MODE == SKV_QUANT_INT8) {
+            // |y| <= 127 (1 + 2^-22) because |x| <= amax = 127 * scale, so rounding already lands in [-127, 127]
             if (fabsf(y - floorf(y) - 0.5f) < 1e-4f) y = __fdiv_rn(x[i], scale);
-            int c = __float2int_rn(y);  // round half to even
-            c = max(-127, min(127, c));
-            code = (uint32_t)c & 0xFFu;
+            c[i] = __float2int_rn(y);  // round half to even
         } else {
-            const float yc = fminf(fmaxf(y, -448.f), 448.f);
-            code = (uint32_t)__nv_cvt_float_to_fp8(yc, __NV_SATFINITE, __NV_E4M3);
+            c[i] = (int)__nv_cvt_float_to_fp8(fminf(fmaxf(y, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
         }
-        if (i < 4) lo |= code << (8 * i); else hi |= code << (8 * (i - 4));
     }
+    // low bytes of eight ints -> two words
+    lo = __byte_perm(__byte_perm(c[0], c[1], 0x0040), __byte_perm(c[2], c[3], 0x0040), 0x5410);
+    hi = __byte_perm(__byte_perm(c[4], c[5], 0x0040), __byte_perm(c[6], c[7], 0x0040), 0x5410);
     if (valid) *reinterpret_cast<uint2*>(out_row + sub * 8) = make_uint2(lo, hi);
     if (valid && sub == 0) *scale_out = scale;
 }
@@ -281,7 +473,12 @@ int skv_kv_evict_quant(const void* k_cache, const void* v_cache, const float* sc
     }
     evq::SelectParams sp;
     sp.scores = scores; sp.idx = idx_out; sp.T = T; sp.budget = budget; sp.recent = recent; sp.keep = keep; sp.order = order;
-    evq::evict_select_kernel<<<(unsigned)((long long)B * H), evq::SEL_THREADS, smem, st>>>(sp);
+    const int competing = T - (recent < T ? recent : T);
+    if (order == SKV_ORDER_POSITION && competing <= evq::CL * evq::SEL_THREADS * evq::KR && (long long)B * H * evq::CL <= 65535LL * 32) {
+        evq::evict_select_cluster_kernel<<<(unsigned)((long long)B * H * evq::CL), evq::SEL_THREADS, 0, st>>>(sp);
+    } else {
+        evq::evict_select_kernel<<<(unsigned)((long long)B * H), evq::SEL_THREADS, smem, st>>>(sp);
+    }
     SKV_CUDA_TRY(cudaGetLastError());
 
     evq::GatherParams gp;
