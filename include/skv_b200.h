@@ -126,6 +126,21 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool,
                      long long scale_stride_page, long long scale_stride_head,
                      float scale, int device, void* stream);
 
+/* ---- decode-step glue: RoPE + quantise + append -------------------------------------
+ * Replaces the cache update the reference leaves to Hugging Face (DynamicCache.update concatenation and a
+ * permute().contiguous() copy of the whole cache per layer and token, benchmarks/llama_integration_benchmark.py:173,
+ * :302-303) and its RoPE call (:152-160).  qkv: [B, (Hq + 2 Hkv) * D] fp16 or bf16 (q heads, k heads, v heads);
+ * q_out: [B, Hq, D] fp16 = rotate-half RoPE(q) at position seq_lens[b]; RoPE(k) and v are quantised per row
+ * (scale = amax/448 for SKV_KV_E4M3, amax/127 for SKV_KV_I8; 1.0 for a zero row) and stored at token position
+ * seq_lens[b] of sequence b in the paged pools (layout as for skv_gqa_decode_paged).  seq_lens is not modified.
+ * D = 128. */
+int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k_pool, void* v_pool,
+                          float* k_scale_pool, float* v_scale_pool, const int* page_table, const int* seq_lens,
+                          int B, int Hq, int Hkv, int D, int kv_dtype, int page_size, int max_pages,
+                          long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
+                          long long scale_stride_page, long long scale_stride_head,
+                          float rope_theta, int device, void* stream);
+
 /* ---- token-sparse decode ----------------------------------------------------------
  * Replaces kv_evict_quant_forward(Q, K, V, top_k, use_int8=false)  (csrc/kernels/kv_evict_quant.cu:272-364,
  * bound in csrc/pybind/bindings.cpp:28) with the arithmetic of _reference_sparse_attention

@@ -1,0 +1,143 @@
+// Decode-step glue in front of the attention kernel: rotary embedding of the new token's query and key,
+// quantisation of its key and value rows (FP8-E4M3 or INT8, one fp32 scale per row) and their store into the
+// paged cache at position seq_lens[b] -- one launch instead of the concatenate-and-copy the reference does
+// (DynamicCache.update plus permute().contiguous() of the whole cache per layer and token,
+// benchmarks/llama_integration_benchmark.py:173,302-303; benchmarks/profile_fused_gqa.py:143-144).
+//
+// qkv : [B, (Hq + 2 Hkv) * D] bf16 or fp16, the output of the fused q/k/v projection (q heads, then k, then v)
+// q_out : [B, Hq, D] fp16, rotated query for the decode kernel
+// pools : as for skv_gqa_decode_paged (separate or fused page records; addressed through strides)
+// One warp per (b, head): D = 128 -> 4 channels per lane; rotate-half pairs channel d with d + D/2.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "skv_common.cuh"
+
+namespace skv {
+namespace app {
+
+constexpr int D = 128;
+constexpr int THREADS = 128;
+
+struct Params {
+    const void* qkv;
+    __half* q_out;
+    uint8_t* k_codes; uint8_t* v_codes;   // element (page,h,slot,d) at page*sp + h*sh + slot*ss + d
+    float* k_scale; float* v_scale;       // element (page,h,slot) at page*csp + h*csh + slot
+    const int* page_table;                // [B, max_pages] or null
+    const int* seq_lens;                  // [B]: position the new token takes
+    long long sp, sh, ss, csp, csh;
+    int B, Hq, Hkv, page_size, max_pages, kv_dtype;
+    float log2_theta;
+};
+
+template <typename T>
+__device__ __forceinline__ float load_elem(const void* p, long long i);
+template <>
+__device__ __forceinline__ float load_elem<__half>(const void* p, long long i) {
+    return __half2float(static_cast<const __half*>(p)[i]);
+}
+template <>
+__device__ __forceinline__ float load_elem<__nv_bfloat16>(const void* p, long long i) {
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+// grid: ceil(B * (Hq + 2 Hkv) / 4) CTAs of 4 warps
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+rope_quant_append_kernel(const Params p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = p.Hq + 2 * p.Hkv;
+    const long long item = (long long)blockIdx.x * (THREADS / 32) + warp;
+    if (item >= (long long)p.B * heads) return;
+    const int b = (int)(item / heads), hh = (int)(item % heads);
+    const int pos = p.seq_lens[b];
+    const long long src = ((long long)b * heads + hh) * D;
+    // lane holds channels lane*2, lane*2+1 of the first half and the same of the second half
+    float lo0 = load_elem<T>(p.qkv, src + lane * 2), lo1 = load_elem<T>(p.qkv, src + lane * 2 + 1);
+    float hi0 = load_elem<T>(p.qkv, src + D / 2 + lane * 2), hi1 = load_elem<T>(p.qkv, src + D / 2 + lane * 2 + 1);
+    const bool is_v = hh >= p.Hq + p.Hkv;
+    if (!is_v) {  // rotate-half RoPE: (x_d, x_{d+D/2}) -> (x_d cos - x_{d+D/2} sin, x_{d+D/2} cos + x_d sin)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int d = lane * 2 + j;
+            const float inv_freq = exp2f(-p.log2_theta * (float)(2 * d) / (float)D);
+            float sn, cs;
+            sincosf((float)pos * inv_freq, &sn, &cs);
+            float& a = j ? lo1 : lo0;
+            float& c = j ? hi1 : hi0;
+            const float ra = a * cs - c * sn, rc = c * cs + a * sn;
+            a = ra;
+            c = rc;
+        }
+    }
+    if (hh < p.Hq) {
+        __half* dst = p.q_out + ((long long)b * p.Hq + hh) * D;
+        *reinterpret_cast<__half2*>(dst + lane * 2) = __floats2half2_rn(lo0, lo1);
+        *reinterpret_cast<__half2*>(dst + D / 2 + lane * 2) = __floats2half2_rn(hi0, hi1);
+        return;
+    }
+    // key or value row: per-row scale = amax / qmax, round-to-nearest-even codes
+    const int h = is_v ? hh - p.Hq - p.Hkv : hh - p.Hq;
+    float amax = fmaxf(fmaxf(fabsf(lo0), fabsf(lo1)), fmaxf(fabsf(hi0), fabsf(hi1)));
+    amax = warp_max(amax);
+    const float qmax = p.kv_dtype == SKV_KV_E4M3 ? 448.f : 127.f;
+    const float scale = amax > 0.f ? __fdiv_rn(amax, qmax) : 1.f;
+    const float x[4] = {lo0, lo1, hi0, hi1};
+    uint32_t code[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float y = __fdiv_rn(x[i], scale);
+        if (p.kv_dtype == SKV_KV_E4M3)
+            code[i] = (uint32_t)__nv_cvt_float_to_fp8(fminf(fmaxf(y, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
+        else
+            code[i] = (uint32_t)max(-127, min(127, __float2int_rn(y))) & 0xFFu;
+    }
+    const int lp = pos / p.page_size, slot = pos - lp * p.page_size;
+    const int page = p.page_table ? p.page_table[(long long)b * p.max_pages + lp] : b * p.max_pages + lp;
+    uint8_t* row = (is_v ? p.v_codes : p.k_codes) + page * p.sp + h * p.sh + slot * p.ss;
+    *reinterpret_cast<uint16_t*>(row + lane * 2) = (uint16_t)(code[0] | (code[1] << 8));
+    *reinterpret_cast<uint16_t*>(row + D / 2 + lane * 2) = (uint16_t)(code[2] | (code[3] << 8));
+    if (lane == 0) (is_v ? p.v_scale : p.k_scale)[page * p.csp + h * p.csh + slot] = scale;
+}
+
+}  // namespace app
+}  // namespace skv
+
+using namespace skv;
+
+extern "C" {
+
+int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k_pool, void* v_pool, float* k_scale_pool,
+                          float* v_scale_pool, const int* page_table, const int* seq_lens, int B, int Hq, int Hkv,
+                          int D, int kv_dtype, int page_size, int max_pages, long long pool_stride_page,
+                          long long pool_stride_head, long long pool_stride_slot, long long scale_stride_page,
+                          long long scale_stride_head, float rope_theta, int device, void* stream) {
+    if (!qkv || !q_out || !k_pool || !v_pool || !k_scale_pool || !v_scale_pool || !seq_lens)
+        return fail(SKV_ERR_BAD_ARG, "skv_rope_quant_append: null pointer");
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || page_size <= 0 || max_pages <= 0)
+        return fail(SKV_ERR_BAD_ARG, "skv_rope_quant_append: sizes must be positive");
+    if (D != app::D) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (128)", D);
+    if (kv_dtype != SKV_KV_I8 && kv_dtype != SKV_KV_E4M3) return fail(SKV_ERR_UNSUPPORTED, "kv_dtype %d is not an 8-bit type", kv_dtype);
+    if (!(rope_theta > 1.f)) return fail(SKV_ERR_BAD_ARG, "rope_theta must exceed 1");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
+    app::Params p;
+    p.qkv = qkv; p.q_out = static_cast<__half*>(q_out);
+    p.k_codes = static_cast<uint8_t*>(k_pool); p.v_codes = static_cast<uint8_t*>(v_pool);
+    p.k_scale = k_scale_pool; p.v_scale = v_scale_pool;
+    p.page_table = page_table; p.seq_lens = seq_lens;
+    p.sp = pool_stride_page; p.sh = pool_stride_head; p.ss = pool_stride_slot;
+    p.csp = scale_stride_page; p.csh = scale_stride_head;
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.max_pages = max_pages; p.kv_dtype = kv_dtype;
+    p.log2_theta = log2f(rope_theta);
+    const long long items = (long long)B * (Hq + 2 * Hkv);
+    const unsigned blocks = (unsigned)((items + 3) / 4);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (qkv_is_bf16) app::rope_quant_append_kernel<__nv_bfloat16><<<blocks, app::THREADS, 0, st>>>(p);
+    else app::rope_quant_append_kernel<__half><<<blocks, app::THREADS, 0, st>>>(p);
+    SKV_CUDA_TRY(cudaGetLastError());
+    return SKV_OK;
+}
+
+}  // extern "C"

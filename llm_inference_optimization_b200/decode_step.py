@@ -52,8 +52,7 @@ def _matrix(seed: int, layer: int, name: str, shape, device, dtype, std) -> Tens
 
 
 def rms_norm(x: Tensor, w: Tensor, eps: float) -> Tensor:
-    xf = x.float()
-    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+    return torch.nn.functional.rms_norm(x, (x.shape[-1],), w, eps)
 
 
 def rope(x: Tensor, pos: Tensor, theta: float) -> Tensor:
@@ -115,6 +114,9 @@ class DecodeModel:
                  attention: AttentionFn = kernel_attention, group=None):
         self.cfg, self.shard, self.device, self.dtype = cfg, shard, torch.device(device), dtype
         self.attention, self.group = attention, group
+        # the fused RoPE + quantise + append kernel needs fp16/bf16 activations on a CUDA device
+        self.fused_glue = (self.device.type == "cuda" and dtype in (torch.float16, torch.bfloat16)
+                           and attention is kernel_attention)
         D, hid = cfg.D, cfg.hidden
         qs = slice(shard.q_heads.start * D, shard.q_heads.stop * D)
         ks = slice(shard.kv_heads.start * D, shard.kv_heads.stop * D)
@@ -204,6 +206,18 @@ class DecodeModel:
         for w, cache in zip(self.layers, self.caches):
             h = rms_norm(x, w["n1"], cfg.rms_eps)
             qkv = h @ w["wqkv"]
+            if self.fused_glue:
+                # one launch: RoPE(q, k), quantise k and v, store them at position seq_lens[b] of the paged cache
+                kvv = paged.PagedKV(cache.k, cache.v, cache.ks, cache.vs, self.page_table, pos, B)
+                q = paged.rope_quant_append(qkv, kvv, sh.n_q, cfg.rope_theta)
+                a = self.attention(q, cache, self.page_table, new_lens, scale, self.max_seq_len)
+                o = a.to(x.dtype).reshape(B, sh.n_q * D) @ w["wo"]
+                x = x + self._all_reduce(o)
+                h = rms_norm(x, w["n2"], cfg.rms_eps)
+                gu = h @ w["wgu"]
+                half = gu.shape[1] // 2
+                x = x + self._all_reduce((torch.nn.functional.silu(gu[:, :half]) * gu[:, half:]) @ w["wd"])
+                continue
             q = qkv[:, :sh.n_q * D].view(B, sh.n_q, D)
             k = qkv[:, sh.n_q * D:(sh.n_q + sh.n_kv) * D].view(B, sh.n_kv, D)
             v = qkv[:, (sh.n_q + sh.n_kv) * D:].view(B, sh.n_kv, D)

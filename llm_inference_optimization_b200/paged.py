@@ -135,3 +135,25 @@ def quest_sparse_decode(Q: Tensor, kv: PagedKV, meta: Tensor, scale: float, bloc
         torch.cuda.current_stream(Q.device).cuda_stream)
     _lib.check(rc, "quest_sparse_decode")
     return (out, idx) if return_indices else out
+
+
+def rope_quant_append(qkv: Tensor, kv: PagedKV, Hq: int, rope_theta: float) -> Tensor:
+    """RoPE the new token's q and k, quantise k and v and store them at position ``seq_lens[b]`` of the cache.
+
+    ``qkv`` ``[B, (Hq + 2*Hkv) * 128]`` fp16 or bf16 (fused projection output); returns the rotated query
+    ``[B, Hq, 128]`` fp16.  ``kv.seq_lens`` is read, not advanced.  One launch (``skv_rope_quant_append``).
+    """
+    strides = _pool_args(kv)
+    _, Hkv, P, D = kv.k_pool.shape
+    B = qkv.shape[0]
+    _C._require(qkv.is_cuda and qkv.dim() == 2 and qkv.is_contiguous() and qkv.shape[1] == (Hq + 2 * Hkv) * D
+                and qkv.dtype in (torch.float16, torch.bfloat16), "qkv must be contiguous fp16/bf16 [B,(Hq+2Hkv)*D]")
+    _C._require(kv.seq_lens is not None and B == kv.batch, "the cache needs seq_lens and a matching batch")
+    q = torch.empty((B, Hq, D), dtype=torch.float16, device=qkv.device)
+    rc = _lib.load().skv_rope_quant_append(
+        qkv.data_ptr(), int(qkv.dtype == torch.bfloat16), q.data_ptr(), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(),
+        kv.k_scale.data_ptr(), kv.v_scale.data_ptr(), None if kv.page_table is None else kv.page_table.data_ptr(),
+        kv.seq_lens.data_ptr(), B, Hq, Hkv, D, _C._code_dtype(kv.k_pool), P, kv.max_pages, *strides, float(rope_theta),
+        _C._dev_index(qkv), torch.cuda.current_stream(qkv.device).cuda_stream)
+    _lib.check(rc, "rope_quant_append")
+    return q

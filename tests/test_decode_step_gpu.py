@@ -122,3 +122,39 @@ def test_two_gpu_tensor_parallel_matches_single(cuda_device):
         p.join(120)
         assert p.exitcode == 0
     assert torch.allclose(got, want, atol=2e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("code_dtype", [torch.int8, torch.float8_e4m3fn])
+def test_rope_quant_append_kernel(cuda_device, dtype, code_dtype):
+    """The one-launch RoPE + quantise + append against an fp32 restatement of the same three steps."""
+    from llm_inference_optimization_b200 import paged
+    B, Hq, Hkv, D, pages = 3, 8, 2, 128, 64
+    g = torch.Generator().manual_seed(12)
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).to(dtype)
+    lens = torch.tensor([0, 17, 255], dtype=torch.int32)
+    table = torch.randperm(pages, generator=g)[:B * 16].view(B, 16).to(torch.int32)
+    buf = torch.zeros(pages, Hkv, paged.RECORD_ROWS, 128, dtype=torch.uint8, device=cuda_device)
+    kv = paged.PagedKV.from_fused(buf, code_dtype, table.to(cuda_device), lens.to(cuda_device), B)
+    q = paged.rope_quant_append(qkv.to(cuda_device), kv, Hq, 500000.0).float().cpu()
+    x = qkv.float().view(B, Hq + 2 * Hkv, D)
+    want_q = ds.rope(x[:, :Hq], lens, 500000.0)
+    want_k = ds.rope(x[:, Hq:Hq + Hkv], lens, 500000.0)
+    want_v = x[:, Hq + Hkv:]
+    assert (q - want_q).abs().max().item() <= 4e-3
+    quant = oracle.quantize_int8 if code_dtype == torch.int8 else oracle.quantize_e4m3
+    for pool, spool, want in ((kv.k_pool, kv.k_scale, want_k), (kv.v_pool, kv.v_scale, want_v)):
+        for b in range(B):
+            page, slot = int(table[b, int(lens[b]) // 16]), int(lens[b]) % 16
+            codes, scale = pool[page, :, slot].cpu(), spool[page, :, slot].cpu()
+            wc, ws = quant(want[b])
+            assert torch.allclose(scale, ws, rtol=1e-5)
+            if code_dtype == torch.int8:
+                assert (codes.int() - wc.int()).abs().max().item() <= 1   # sin/cos differ in the last ulp
+            else:
+                assert oracle.e4m3_code_distance(codes, wc).max().item() <= 1
+    # nothing else in the pool was touched
+    touched = torch.zeros(pages, dtype=torch.bool)
+    for b in range(B):
+        touched[int(table[b, int(lens[b]) // 16])] = True
+    assert (buf.cpu()[~touched] == 0).all()
