@@ -124,20 +124,26 @@ struct ScoreParams {
     float scale;
 };
 
-// grid (ceil(nb / blocks_per_cta), Hkv, B); 16 lanes per block (8 channels each), 2 blocks per warp step
+// grid (ceil(nb / blocks_per_cta), Hkv, B); 16 lanes per block (8 channels each), 2 blocks per warp step.
+// max(q*lo, q*hi) is q*hi for q > 0 and q*lo for q < 0 (lo <= hi), so with q split into its positive and negative
+// parts the bound is two FMAs per channel and head, one of which adds an exact zero.
 template <int MAXG>
 __global__ void __launch_bounds__(SCORE_THREADS)
 quest_scores_kernel(const ScoreParams p, int blocks_per_cta) {
+    static_assert(MAXG == 4 || MAXG == 8, "the packed reduction below is written for 4 or 8 heads");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane & 15, rw = lane >> 4;
     const int h = blockIdx.y, b = blockIdx.z;
-    float q[MAXG][8];
+    float qp[MAXG][8], qn[MAXG][8];
 #pragma unroll
     for (int g = 0; g < MAXG; ++g) {
-        if (g < p.G) unpack8(*reinterpret_cast<const uint4*>(p.q + ((long long)b * p.Hq + h * p.G + g) * D + sub * 8), q[g]);
+        float q[8];
+        if (g < p.G) unpack8(*reinterpret_cast<const uint4*>(p.q + ((long long)b * p.Hq + h * p.G + g) * D + sub * 8), q);
         else
 #pragma unroll
-            for (int i = 0; i < 8; ++i) q[g][i] = 0.f;
+            for (int i = 0; i < 8; ++i) q[i] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { qp[g][i] = fmaxf(q[i], 0.f); qn[g][i] = fminf(q[i], 0.f); }
     }
     const __half* mbase = p.meta + ((long long)b * p.Hkv + h) * p.nb * 2 * D + sub * 8;
     const int j0 = blockIdx.x * blocks_per_cta, j1 = min(p.nb, j0 + blocks_per_cta);
@@ -164,15 +170,46 @@ quest_scores_kernel(const ScoreParams p, int blocks_per_cta) {
             for (int g = 0; g < MAXG; ++g) {
                 acc[g] = 0.f;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[g] += fmaxf(q[g][i] * lo[i], q[g][i] * hi[i]);
-#pragma unroll
-                for (int o = 8; o > 0; o >>= 1) acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], o);
+                for (int i = 0; i < 8; ++i) acc[g] = fmaf(qn[g][i], lo[i], fmaf(qp[g][i], hi[i], acc[g]));
             }
-            if (j < j1 && sub == 0) {
+            // Sum over the 16 lanes of the half-warp, several heads at once: at each of the first steps a lane
+            // keeps half of its values and hands the other half to its partner, so MAXG values cost
+            // MAXG/2 + MAXG/4 + ... + 1 shuffles plus the remaining plain steps instead of 4 * MAXG.
+            int head = 0;  // which head this lane ends up holding
+            float v4[4];
+            if (MAXG == 8) {
+                const bool up = sub & 8;
 #pragma unroll
-                for (int g = 0; g < MAXG; ++g)
-                    if (g < p.G) p.scores[((long long)b * p.Hq + h * p.G + g) * p.nb + j] = acc[g] * p.scale;
+                for (int g = 0; g < 4; ++g) {
+                    const float keep = up ? acc[g + 4] : acc[g], send = up ? acc[g] : acc[g + 4];
+                    v4[g] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                }
+                head = up ? 4 : 0;
+            } else {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) v4[g] = acc[g] + __shfl_xor_sync(0xffffffffu, acc[g], 8);
             }
+            float v2[2];
+            {
+                const bool up = sub & 4;
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    const float keep = up ? v4[g + 2] : v4[g], send = up ? v4[g] : v4[g + 2];
+                    v2[g] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+                }
+                head += up ? 2 : 0;
+            }
+            float v1;
+            {
+                const bool up = sub & 2;
+                const float keep = up ? v2[1] : v2[0], send = up ? v2[0] : v2[1];
+                v1 = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+                head += up ? 1 : 0;
+            }
+            v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+            if (MAXG == 4) v1 += 0.f;  // (for 4 heads the xor-8 step above was a plain sum, so all 16 lanes are covered)
+            if (j < j1 && (sub & 1) == 0 && head < p.G)
+                p.scores[((long long)b * p.Hq + h * p.G + head) * p.nb + j] = v1 * p.scale;
         }
     }
 }
