@@ -55,7 +55,7 @@ evict_select_kernel(const SelectParams p) {
     const int recent = min(p.recent, p.T);
     const int head = p.T - recent;              // positions competing on score
     const int kb = min(p.budget, head);         // how many of them survive
-    block_topk_sorted<SEL_THREADS>(sc, head, kb, sel, tk);
+    block_topk_sorted_auto<SEL_THREADS, 16>(sc, head, kb, sel, tk);
     for (int i = tid; i < recent; i += SEL_THREADS) sel[kb + i] = head + i;
     __syncthreads();
     const int keep = kb + recent;  // equals p.keep by construction on the host

@@ -85,17 +85,42 @@ block_meta_build_kernel(const MetaParams p) {
         float lo[16], hi[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) { lo[i] = INFINITY; hi[i] = -INFINITY; }
-        for (int t = t0 + rw; t < t1; t += 4) {
-            const int page = phys_page(p.page_table, b, p.max_pages, t / p.page_size), slot = t % p.page_size;
-            const uint4 raw = *reinterpret_cast<const uint4*>(p.k.codes + page * p.k.sp + h * p.k.sh + slot * p.k.ss + sub * 16);
-            const float s = p.k.scales[page * p.k.csp + h * p.k.csh + slot];
-            float x[16];
-            unpack16<KVT>(raw, x);
+        constexpr int RU = 4;  // rows per lane group and step: page ids, then codes and scales, all issued together
+        for (int tb = t0 + rw; tb < t1; tb += 4 * RU) {
+            int page[RU], slot[RU];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float v = x[i] * s;
-                lo[i] = fminf(lo[i], v);
-                hi[i] = fmaxf(hi[i], v);
+            for (int u = 0; u < RU; ++u) {
+                const int t = tb + 4 * u;
+                page[u] = -1;
+                slot[u] = 0;
+                if (t < t1) {
+                    const int lp = t / p.page_size;
+                    slot[u] = t - lp * p.page_size;
+                    page[u] = phys_page(p.page_table, b, p.max_pages, lp);
+                }
+            }
+            uint4 raw[RU];
+            float sc[RU];
+#pragma unroll
+            for (int u = 0; u < RU; ++u) {
+                raw[u] = make_uint4(0u, 0u, 0u, 0u);
+                sc[u] = 0.f;
+                if (page[u] >= 0) {
+                    raw[u] = ld_stream16(p.k.codes + page[u] * p.k.sp + h * p.k.sh + slot[u] * p.k.ss + sub * 16);
+                    sc[u] = p.k.scales[page[u] * p.k.csp + h * p.k.csh + slot[u]];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < RU; ++u) {
+                if (page[u] < 0) continue;
+                float x[16];
+                unpack16<KVT>(raw[u], x);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float v = x[i] * sc[u];
+                    lo[i] = fminf(lo[i], v);
+                    hi[i] = fmaxf(hi[i], v);
+                }
             }
         }
 #pragma unroll
@@ -244,7 +269,7 @@ quest_select_attend_kernel(const AttendParams p) {
     const int nb = (len + p.block_size - 1) / p.block_size;  // blocks this sequence really has
     const float* sc = p.scores + (long long)row * p.nb;
     const int kk = min(p.top_k, nb);
-    block_topk_sorted<ATT_THREADS>(sc, nb, kk, sel, tk);
+    block_topk_sorted_auto<ATT_THREADS, 16>(sc, nb, kk, sel, tk);
     for (int i = tid; i < D; i += ATT_THREADS) qs[i] = __half2float(p.q[(long long)row * D + i]);
     __syncthreads();
     if (p.block_idx)

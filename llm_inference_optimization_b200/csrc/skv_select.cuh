@@ -195,4 +195,155 @@ __device__ void block_topk_sorted(const float* sc, int T, int k, int* out, uint3
     __syncthreads();
 }
 
+// Same result as block_topk_sorted for T <= NT * R, with every score loaded ONCE: lane l of a warp keeps the keys of
+// elements s0 + 32 j + l (j < R) of the warp's contiguous segment in registers, so the four histogram passes, the
+// count and the ordered write-out run on registers only.
+template <int NT, int R>
+__device__ void block_topk_sorted_cached(const float* sc, int T, int k, int* out, uint32_t* sm) {
+    constexpr int NW = NT / 32;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (k <= 0) return;
+    if (k >= T) {
+        for (int i = tid; i < T; i += NT) out[i] = i;
+        return;
+    }
+    uint32_t* hist = sm;
+    uint32_t* wcnt = sm + NW * 256;
+    uint32_t* bc = wcnt + 4 * NW;
+
+    int seg = (T + NW - 1) / NW;
+    seg = (seg + 31) & ~31;  // <= 32 * R because T <= NT * R
+    const int s0 = min(T, warp * seg), s1 = min(T, s0 + seg);
+    uint32_t key[R];
+    uint32_t have = 0;
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+        const int i = s0 + j * 32 + lane;
+        key[j] = 0u;
+        if (i < s1) { key[j] = score_key(sc[i]); have |= 1u << j; }
+    }
+
+    uint32_t prefix = 0, mask = 0;
+    int remaining = k;
+#pragma unroll 1
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        for (int i = tid; i < NW * 256; i += NT) hist[i] = 0;
+        __syncthreads();
+        uint32_t* myh = hist + warp * 256;
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            const bool act = ((have >> j) & 1u) && (key[j] & mask) == prefix;
+            const uint32_t digit = (key[j] >> shift) & 255u;
+            const uint32_t voters = __ballot_sync(0xffffffffu, act);
+            if (voters) {
+                const int leader = __ffs(voters) - 1;
+                const uint32_t d0 = __shfl_sync(0xffffffffu, digit, leader);
+                const uint32_t same = __ballot_sync(0xffffffffu, act && digit == d0);
+                if (same == voters) {
+                    if (lane == leader) atomicAdd(&myh[d0], (uint32_t)__popc(voters));
+                } else if (act) {
+                    atomicAdd(&myh[digit], 1u);
+                }
+            }
+        }
+        __syncthreads();
+        for (int b = tid; b < 256; b += NT) {
+            uint32_t t = 0;
+#pragma unroll 4
+            for (int w = 0; w < NW; ++w) t += hist[w * 256 + b];
+            hist[b] = t;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            uint32_t mine = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mine += hist[255 - 8 * lane - j];
+            uint32_t incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const uint32_t hit = __ballot_sync(0xffffffffu, incl >= (uint32_t)remaining);
+            const int owner = __ffs(hit) - 1;
+            if (lane == owner) {
+                uint32_t above = incl - mine;
+                int d = 255 - 8 * lane;
+                for (int j = 0; j < 8; ++j, --d) {
+                    const uint32_t c = hist[d];
+                    if (above + c >= (uint32_t)remaining) break;
+                    above += c;
+                }
+                bc[0] = (uint32_t)d;
+                bc[1] = (uint32_t)remaining - above;
+            }
+        }
+        __syncthreads();
+        prefix |= bc[0] << shift;
+        mask |= 0xFFu << shift;
+        remaining = (int)bc[1];
+        __syncthreads();
+    }
+    const uint32_t thr = prefix;
+    const int need = remaining;
+
+    uint32_t gt = 0, eq = 0;
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+        const bool in = (have >> j) & 1u;
+        gt += __popc(__ballot_sync(0xffffffffu, in && key[j] > thr));
+        eq += __popc(__ballot_sync(0xffffffffu, in && key[j] == thr));
+    }
+    if (lane == 0) { wcnt[warp] = gt; wcnt[NW + warp] = eq; }
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t eqp = 0, selp = 0;
+        for (int base = 0; base < NW; base += 32) {
+            const int w = base + lane;
+            const uint32_t g = w < NW ? wcnt[w] : 0u, e = w < NW ? wcnt[NW + w] : 0u;
+            uint32_t ei = e;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xffffffffu, ei, o);
+                if (lane >= o) ei += v;
+            }
+            const uint32_t eex = eqp + ei - e;
+            const uint32_t take = (uint32_t)max(0, min((int)e, need - (int)eex));
+            const uint32_t sl = g + take;
+            uint32_t si = sl;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xffffffffu, si, o);
+                if (lane >= o) si += v;
+            }
+            if (w < NW) { wcnt[2 * NW + w] = selp + si - sl; wcnt[3 * NW + w] = eex; }
+            eqp += __shfl_sync(0xffffffffu, ei, 31);
+            selp += __shfl_sync(0xffffffffu, si, 31);
+        }
+    }
+    __syncthreads();
+    uint32_t pos = wcnt[2 * NW + warp], eqrun = wcnt[3 * NW + warp];
+    const uint32_t lt = (1u << lane) - 1u;
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+        const bool in = (have >> j) & 1u;
+        const bool isgt = in && key[j] > thr, iseq = in && key[j] == thr;
+        const uint32_t beq = __ballot_sync(0xffffffffu, iseq);
+        const bool sel = isgt || (iseq && (int)(eqrun + __popc(beq & lt)) < need);
+        const uint32_t bsel = __ballot_sync(0xffffffffu, sel);
+        if (sel) out[pos + __popc(bsel & lt)] = s0 + j * 32 + lane;
+        pos += __popc(bsel);
+        eqrun += __popc(beq);
+    }
+    __syncthreads();
+}
+
+// Picks the register-cached routine when the row is short enough for R keys per thread.
+template <int NT, int R>
+__device__ __forceinline__ void block_topk_sorted_auto(const float* sc, int T, int k, int* out, uint32_t* sm) {
+    if (T <= NT * R) block_topk_sorted_cached<NT, R>(sc, T, k, out, sm);
+    else block_topk_sorted<NT>(sc, T, k, out, sm);
+}
+
 }  // namespace skv
