@@ -56,9 +56,21 @@ inline Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device, bool rag
         // Many pairs, or per-sequence lengths the host does not know: a CTA streams at about 1/SMs of the HBM
         // rate, so work is cut into about eight waves of CTAs to let long sequences spread over many SMs
         // (CTAs past a sequence's end exit at once).
-        const long long waves = ragged ? 8 : 4;
-        splits = (waves * target + pairs - 1) / pairs;
         const long long max_by_size = total_tiles / 16 > 0 ? total_tiles / 16 : 1;   // at least 16 tiles per split
+        if (ragged) {
+            splits = (8 * target + pairs - 1) / pairs;
+        } else {
+            // equal lengths: every CTA lasts the same, so pick the split count between about 2 and 8 waves whose
+            // last wave is fullest (pairs * splits CTAs over `target` slots), the smallest such count on ties
+            splits = 1;
+            double best = 0.0;
+            const long long lo = (2 * target + pairs - 1) / pairs, hi = (8 * target + pairs - 1) / pairs;
+            for (long long c = lo < 1 ? 1 : lo; c <= hi && c <= max_by_size; ++c) {
+                const double w = (double)(pairs * c) / (double)target;
+                const double eff = w / (double)(long long)(w + 0.999999);
+                if (eff > best + 0.02) { best = eff; splits = c; }
+            }
+        }
         if (splits > max_by_size) splits = max_by_size;
     }
     if (splits < 1) splits = 1;
