@@ -133,13 +133,16 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool,
  * q_out: [B, Hq, D] fp16 = rotate-half RoPE(q) at position seq_lens[b]; RoPE(k) and v are quantised per row
  * (scale = amax/448 for SKV_KV_E4M3, amax/127 for SKV_KV_I8; 1.0 for a zero row) and stored at token position
  * seq_lens[b] of sequence b in the paged pools (layout as for skv_gqa_decode_paged).  seq_lens is not modified.
+ * meta (optional, else NULL): the fp16 [B,Hkv,meta_num_blocks,2,D] metadata of skv_quest_build_meta, whose block
+ * containing the new token is updated with the dequantised new key (re-initialised when the token opens a block).
  * D = 128. */
 int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k_pool, void* v_pool,
                           float* k_scale_pool, float* v_scale_pool, const int* page_table, const int* seq_lens,
                           int B, int Hq, int Hkv, int D, int kv_dtype, int page_size, int max_pages,
                           long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
                           long long scale_stride_page, long long scale_stride_head,
-                          float rope_theta, int device, void* stream);
+                          float rope_theta, void* meta, int meta_block_size, int meta_num_blocks,
+                          int device, void* stream);
 
 /* ---- token-sparse decode ----------------------------------------------------------
  * Replaces kv_evict_quant_forward(Q, K, V, top_k, use_int8=false)  (csrc/kernels/kv_evict_quant.cu:272-364,

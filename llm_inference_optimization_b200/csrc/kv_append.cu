@@ -29,6 +29,8 @@ struct Params {
     long long sp, sh, ss, csp, csh;
     int B, Hq, Hkv, page_size, max_pages, kv_dtype;
     float log2_theta;
+    __half* meta;                         // optional [B, Hkv, nb, 2, D] min/max block metadata to keep current
+    int meta_block, meta_nb;
 };
 
 template <typename T>
@@ -99,6 +101,32 @@ rope_quant_append_kernel(const Params p) {
     *reinterpret_cast<uint16_t*>(row + lane * 2) = (uint16_t)(code[0] | (code[1] << 8));
     *reinterpret_cast<uint16_t*>(row + D / 2 + lane * 2) = (uint16_t)(code[2] | (code[3] << 8));
     if (lane == 0) (is_v ? p.v_scale : p.k_scale)[page * p.csp + h * p.csh + slot] = scale;
+
+    // Keep the Quest metadata of the key's block current: min/max with the DEQUANTISED new key (code * scale),
+    // starting afresh when the token opens a new block.  One warp owns a (b, head) row, so no other writer exists.
+    if (!is_v && p.meta) {
+        const int blk = pos / p.meta_block;
+        if (blk < p.meta_nb) {
+            const bool fresh = pos - blk * p.meta_block == 0;
+            __half* mn = p.meta + ((((long long)b * p.Hkv + h) * p.meta_nb + blk) * 2) * D;
+            __half* mx = mn + D;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int d = (i < 2 ? 0 : D / 2) + lane * 2 + (i & 1);
+                float v;
+                if (p.kv_dtype == SKV_KV_E4M3) {
+                    const __half_raw hr = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)code[i], __NV_E4M3);
+                    v = __half2float(*reinterpret_cast<const __half*>(&hr)) * scale;
+                } else {
+                    v = (float)(int)(int8_t)code[i] * scale;
+                }
+                const float lo = fresh ? v : fminf(__half2float(mn[d]), v);
+                const float hi = fresh ? v : fmaxf(__half2float(mx[d]), v);
+                mn[d] = __float2half_rn(lo);
+                mx[d] = __float2half_rn(hi);
+            }
+        }
+    }
 }
 
 }  // namespace app
@@ -112,7 +140,8 @@ int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k
                           float* v_scale_pool, const int* page_table, const int* seq_lens, int B, int Hq, int Hkv,
                           int D, int kv_dtype, int page_size, int max_pages, long long pool_stride_page,
                           long long pool_stride_head, long long pool_stride_slot, long long scale_stride_page,
-                          long long scale_stride_head, float rope_theta, int device, void* stream) {
+                          long long scale_stride_head, float rope_theta, void* meta, int meta_block_size,
+                          int meta_num_blocks, int device, void* stream) {
     if (!qkv || !q_out || !k_pool || !v_pool || !k_scale_pool || !v_scale_pool || !seq_lens)
         return fail(SKV_ERR_BAD_ARG, "skv_rope_quant_append: null pointer");
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || page_size <= 0 || max_pages <= 0)
@@ -131,6 +160,9 @@ int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k
     p.csp = scale_stride_page; p.csh = scale_stride_head;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.max_pages = max_pages; p.kv_dtype = kv_dtype;
     p.log2_theta = log2f(rope_theta);
+    p.meta = static_cast<__half*>(meta);
+    p.meta_block = meta_block_size > 0 ? meta_block_size : 1;
+    p.meta_nb = meta ? meta_num_blocks : 0;
     const long long items = (long long)B * (Hq + 2 * Hkv);
     const unsigned blocks = (unsigned)((items + 3) / 4);
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -137,11 +137,14 @@ def quest_sparse_decode(Q: Tensor, kv: PagedKV, meta: Tensor, scale: float, bloc
     return (out, idx) if return_indices else out
 
 
-def rope_quant_append(qkv: Tensor, kv: PagedKV, Hq: int, rope_theta: float) -> Tensor:
+def rope_quant_append(qkv: Tensor, kv: PagedKV, Hq: int, rope_theta: float, *, meta: Tensor | None = None,
+                      block_size: int = 64) -> Tensor:
     """RoPE the new token's q and k, quantise k and v and store them at position ``seq_lens[b]`` of the cache.
 
     ``qkv`` ``[B, (Hq + 2*Hkv) * 128]`` fp16 or bf16 (fused projection output); returns the rotated query
-    ``[B, Hq, 128]`` fp16.  ``kv.seq_lens`` is read, not advanced.  One launch (``skv_rope_quant_append``).
+    ``[B, Hq, 128]`` fp16.  ``kv.seq_lens`` is read, not advanced.  With ``meta`` (the tensor
+    ``build_block_meta`` returns) the min/max metadata of the block that receives the token is updated in the
+    same launch (``skv_rope_quant_append``).
     """
     strides = _pool_args(kv)
     _, Hkv, P, D = kv.k_pool.shape
@@ -149,11 +152,15 @@ def rope_quant_append(qkv: Tensor, kv: PagedKV, Hq: int, rope_theta: float) -> T
     _C._require(qkv.is_cuda and qkv.dim() == 2 and qkv.is_contiguous() and qkv.shape[1] == (Hq + 2 * Hkv) * D
                 and qkv.dtype in (torch.float16, torch.bfloat16), "qkv must be contiguous fp16/bf16 [B,(Hq+2Hkv)*D]")
     _C._require(kv.seq_lens is not None and B == kv.batch, "the cache needs seq_lens and a matching batch")
+    if meta is not None:
+        _C._require(meta.dtype == torch.float16 and meta.dim() == 5 and meta.shape[:2] == (B, Hkv) and meta.shape[3:] == (2, D)
+                    and meta.is_contiguous() and meta.device == qkv.device, "meta must be fp16 [B,Hkv,nb,2,D] on qkv's device")
     q = torch.empty((B, Hq, D), dtype=torch.float16, device=qkv.device)
     rc = _lib.load().skv_rope_quant_append(
         qkv.data_ptr(), int(qkv.dtype == torch.bfloat16), q.data_ptr(), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(),
         kv.k_scale.data_ptr(), kv.v_scale.data_ptr(), None if kv.page_table is None else kv.page_table.data_ptr(),
         kv.seq_lens.data_ptr(), B, Hq, Hkv, D, _C._code_dtype(kv.k_pool), P, kv.max_pages, *strides, float(rope_theta),
+        None if meta is None else meta.data_ptr(), int(block_size), 0 if meta is None else meta.shape[2],
         _C._dev_index(qkv), torch.cuda.current_stream(qkv.device).cuda_stream)
     _lib.check(rc, "rope_quant_append")
     return q

@@ -81,3 +81,21 @@ def test_exact_when_every_block_is_selected(cuda_device):
     assert (out.float().cpu() - want).abs().max().item() <= TOL
     dense = kv.decode(Q.to(cuda_device), 128 ** -0.5)
     assert (out.float() - dense.float()).abs().max().item() <= TOL
+
+
+def test_append_keeps_block_metadata_current(cuda_device):
+    """Appending tokens one by one with metadata update equals rebuilding the metadata from the final cache."""
+    B, Hq, Hkv, D, pages = 2, 8, 2, 128, 40
+    g = torch.Generator().manual_seed(31)
+    table = torch.randperm(pages, generator=g)[:B * 16].view(B, 16).to(torch.int32).to(cuda_device)
+    buf = torch.zeros(pages, Hkv, paged.RECORD_ROWS, 128, dtype=torch.uint8, device=cuda_device)
+    lens = torch.zeros(B, dtype=torch.int32, device=cuda_device)
+    kv = paged.PagedKV.from_fused(buf, torch.float8_e4m3fn, table, lens, B)
+    meta = torch.zeros(B, Hkv, 4, 2, D, dtype=torch.float16, device=cuda_device)
+    for step in range(70):   # crosses the block edge at token 64
+        qkv = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).half().to(cuda_device)
+        paged.rope_quant_append(qkv, kv, Hq, 500000.0, meta=meta, block_size=64)
+        lens += 1
+    torch.cuda.synchronize()
+    rebuilt = paged.build_block_meta(kv, 64, max_seq_len=256)
+    assert torch.equal(meta[:, :, :2], rebuilt[:, :, :2])   # 70 tokens: block 0 full, block 1 holds 6 tokens
