@@ -49,18 +49,28 @@ block_mean_scores_kernel(const ScoreParams p, int blocks_per_cta) {
     const int j0 = blockIdx.x * blocks_per_cta, j1 = min(p.nb, j0 + blocks_per_cta);
     for (int j = j0 + warp; j < j1; j += SCORE_THREADS / 32) {
         const int t0 = j * p.block_size, t1 = min(p.T, t0 + p.block_size);
-        float acc = 0.f;
+        float acc = 0.f, acc1 = 0.f;
         for (int base = t0; base < t1; base += U * RPW) {
             uint4 kv[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int t = base + u * RPW + rw;
-                kv[u] = t < t1 ? ld_stream16(kbase + (long long)t * p.k_st) : make_uint4(0u, 0u, 0u, 0u);
+                // rows past the block's end are clamped to its last row and discarded below: unconditional loads
+                // can all be issued before the first use
+                const int t = min(base + u * RPW + rw, t1 - 1);
+                kv[u] = ld_stream16(kbase + (long long)t * p.k_st);
             }
 #pragma unroll
-            for (int u = 0; u < U; ++u) acc += dot8(kv[u], q);
+            for (int u = 0; u < U; ++u) pin_loaded(kv[u]);
+            float d[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) d[u] = base + u * RPW + rw < t1 ? dot8(kv[u], q) : 0.f;
+#pragma unroll
+            for (int w = U / 2; w > 0; w >>= 1)
+#pragma unroll
+                for (int u = 0; u < w; ++u) d[u] += d[u + w];
+            acc += d[0];
         }
-        acc = warp_sum(acc);
+        acc = warp_sum(acc + acc1);
         if (lane == 0) srow[j] = acc * p.scale / (float)(t1 - t0);
     }
 }

@@ -252,6 +252,13 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     return v;
 }
 
+// Compiler fence on a loaded value: volatile asm statements keep their order, so everything that uses `v` after
+// this call is scheduled after every load issued before it -- a batch of loads stays in flight together instead
+// of being interleaved with (and serialised behind) the arithmetic on the first ones.
+__device__ __forceinline__ void pin_loaded(uint4& v) {
+    asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w));
+}
+
 // fp32 dot product of 8 fp16 values (one 16-byte load) with 8 floats.
 __device__ __forceinline__ float dot8(const uint4& kv, const float (&q)[8]) {
     const __half2* h = reinterpret_cast<const __half2*>(&kv);
