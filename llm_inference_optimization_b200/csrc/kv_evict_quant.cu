@@ -371,24 +371,18 @@ evict_gather_quant_kernel(const GatherParams p) {
     // the trip count is taken from group 0 of the block so that it is the same for every lane of a warp
     for (long long rb = (long long)blockIdx.x * GPB; rb < p.rows_total; rb += stride * U) {
         const long long r0 = rb + grp;
+        // Rows past the end are clamped to the last row and only their stores are suppressed: loads under a
+        // condition would be issued one by one, each behind the use of the one before.
         int t[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const long long r = r0 + u * stride;
-            t[u] = r < p.rows_total ? __ldg(p.idx + r) : -1;
-        }
+        for (int u = 0; u < U; ++u) t[u] = __ldg(p.idx + min(r0 + u * stride, p.rows_total - 1));
         uint4 kr[U], vr[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const long long r = r0 + u * stride;
-            if (t[u] >= 0) {
-                const long long row = r / p.keep;  // (b, h)
-                const long long src = (row / p.H) * p.sb + (row % p.H) * p.sh + (long long)t[u] * p.st + sub * 8;
-                kr[u] = ld_stream16(p.k + src);
-                vr[u] = ld_stream16(p.v + src);
-            } else {
-                kr[u] = vr[u] = make_uint4(0u, 0u, 0u, 0u);
-            }
+            const long long row = min(r0 + u * stride, p.rows_total - 1) / p.keep;  // (b, h)
+            const long long src = (row / p.H) * p.sb + (row % p.H) * p.sh + (long long)max(t[u], 0) * p.st + sub * 8;
+            kr[u] = ld_stream16(p.k + src);
+            vr[u] = ld_stream16(p.v + src);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {

@@ -33,6 +33,7 @@ constexpr int SCORE_THREADS = 256;
 constexpr int ATT_THREADS = 256;
 constexpr int MAX_SEL_TOKENS = 2048;  // top_k_blocks * block_size upper bound
 constexpr int MAX_TOPK = 256;
+constexpr int PAST_END = 1 << 30;  // flag in the slot word of a gathered token that lies past the sequence end
 
 template <int KVT>
 __device__ __forceinline__ float code_to_float(uint32_t byte) {
@@ -87,32 +88,25 @@ block_meta_build_kernel(const MetaParams p) {
         for (int i = 0; i < 16; ++i) { lo[i] = INFINITY; hi[i] = -INFINITY; }
         constexpr int RU = 4;  // rows per lane group and step: page ids, then codes and scales, all issued together
         for (int tb = t0 + rw; tb < t1; tb += 4 * RU) {
+            // Rows past the block's end are clamped to its last row: a repeated row changes no minimum or maximum,
+            // and loads without a condition are all issued before the first use.
             int page[RU], slot[RU];
 #pragma unroll
             for (int u = 0; u < RU; ++u) {
-                const int t = tb + 4 * u;
-                page[u] = -1;
-                slot[u] = 0;
-                if (t < t1) {
-                    const int lp = t / p.page_size;
-                    slot[u] = t - lp * p.page_size;
-                    page[u] = phys_page(p.page_table, b, p.max_pages, lp);
-                }
+                const int t = min(tb + 4 * u, t1 - 1);
+                const int lp = t / p.page_size;
+                slot[u] = t - lp * p.page_size;
+                page[u] = phys_page(p.page_table, b, p.max_pages, lp);
             }
             uint4 raw[RU];
             float sc[RU];
 #pragma unroll
             for (int u = 0; u < RU; ++u) {
-                raw[u] = make_uint4(0u, 0u, 0u, 0u);
-                sc[u] = 0.f;
-                if (page[u] >= 0) {
-                    raw[u] = ld_stream16(p.k.codes + page[u] * p.k.sp + h * p.k.sh + slot[u] * p.k.ss + sub * 16);
-                    sc[u] = p.k.scales[page[u] * p.k.csp + h * p.k.csh + slot[u]];
-                }
+                raw[u] = ld_stream16(p.k.codes + page[u] * p.k.sp + h * p.k.sh + slot[u] * p.k.ss + sub * 16);
+                sc[u] = __ldg(p.k.scales + page[u] * p.k.csp + h * p.k.csh + slot[u]);
             }
 #pragma unroll
             for (int u = 0; u < RU; ++u) {
-                if (page[u] < 0) continue;
                 float x[16];
                 unpack16<KVT>(raw[u], x);
 #pragma unroll
@@ -177,13 +171,9 @@ quest_scores_kernel(const ScoreParams p, int blocks_per_cta) {
         uint4 lo4[U], hi4[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int j = base + u * 2 + rw;
-            if (j < j1) {
-                lo4[u] = *reinterpret_cast<const uint4*>(mbase + (long long)j * 2 * D);
-                hi4[u] = *reinterpret_cast<const uint4*>(mbase + (long long)j * 2 * D + D);
-            } else {
-                lo4[u] = hi4[u] = make_uint4(0u, 0u, 0u, 0u);
-            }
+            const int j = min(base + u * 2 + rw, j1 - 1);  // clamped; the store below is guarded
+            lo4[u] = ld_stream16(mbase + (long long)j * 2 * D);
+            hi4[u] = ld_stream16(mbase + (long long)j * 2 * D + D);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -258,7 +248,7 @@ quest_select_attend_kernel(const AttendParams p) {
     __shared__ uint32_t tk[TopkSmem<ATT_THREADS>::WORDS];
     __shared__ int sel[MAX_TOPK];
     __shared__ float w[MAX_SEL_TOKENS];
-    __shared__ int2 where[MAX_SEL_TOKENS];  // (page, slot) of every gathered token, page < 0 past the sequence end
+    __shared__ int2 where[MAX_SEL_TOKENS];  // (page, slot) of every gathered token; PAST_END set in slot past the sequence end
     __shared__ float qs[D];
     __shared__ float red[ATT_THREADS / 8 * 16 + 32];  // per row-group partial outputs are reduced through here
     __shared__ float bcast[2];
@@ -284,9 +274,11 @@ quest_select_attend_kernel(const AttendParams p) {
     // resolve every gathered token's page once (one page-table read per token, all in flight together)
     for (int r = tid; r < ntok; r += ATT_THREADS) {
         const int t = sel[r / p.block_size] * p.block_size + r % p.block_size;
-        int2 pw = make_int2(-1, 0);
-        if (t < len) pw = make_int2(phys_page(p.page_table, b, p.max_pages, t / p.page_size), t % p.page_size);
-        where[r] = pw;
+        // a token past the end points at the last real token and carries a flag, so that every later load has a
+        // valid address and needs no condition (conditional loads are issued one behind the other)
+        const int tc = min(t, len - 1);
+        where[r] = make_int2(phys_page(p.page_table, b, p.max_pages, tc / p.page_size),
+                             (tc % p.page_size) | (t < len ? 0 : PAST_END));
     }
     __syncthreads();
     constexpr int RU = 4;  // token rows per group and step: their code and scale loads are issued back to back
@@ -296,19 +288,15 @@ quest_select_attend_kernel(const AttendParams p) {
         float ksc[RU];
 #pragma unroll
         for (int u = 0; u < RU; ++u) {
-            const int r = r0 + u * (ATT_THREADS / 8) + grp;
-            const int2 pw = r < ntok ? where[r] : make_int2(-1, 0);
-            raw[u] = make_uint4(0u, 0u, 0u, 0u);
-            ksc[u] = 0.f;
-            if (pw.x >= 0) {
-                raw[u] = *reinterpret_cast<const uint4*>(p.k.codes + pw.x * p.k.sp + h * p.k.sh + pw.y * p.k.ss + sub * 16);
-                ksc[u] = p.k.scales[pw.x * p.k.csp + h * p.k.csh + pw.y];
-            }
+            const int2 pw = where[min(r0 + u * (ATT_THREADS / 8) + grp, ntok - 1)];
+            const int slot = pw.y & ~PAST_END;
+            raw[u] = ld_stream16(p.k.codes + pw.x * p.k.sp + h * p.k.sh + slot * p.k.ss + sub * 16);
+            ksc[u] = __ldg(p.k.scales + pw.x * p.k.csp + h * p.k.csh + slot);
         }
 #pragma unroll
         for (int u = 0; u < RU; ++u) {
             const int r = r0 + u * (ATT_THREADS / 8) + grp;
-            const bool valid = r < ntok && where[r].x >= 0;
+            const bool valid = r < ntok && !(where[min(r, ntok - 1)].y & PAST_END);
             float x[16];
             unpack16<KVT>(raw[u], x);
             float d = 0.f;
@@ -360,13 +348,12 @@ quest_select_attend_kernel(const AttendParams p) {
 #pragma unroll
         for (int u = 0; u < RU; ++u) {
             const int r = r0 + u * (ATT_THREADS / 8);
-            const int2 pw = r < ntok ? where[r] : make_int2(-1, 0);
-            raw[u] = make_uint4(0u, 0u, 0u, 0u);
-            wt[u] = 0.f;
-            if (pw.x >= 0) {
-                raw[u] = *reinterpret_cast<const uint4*>(p.v.codes + pw.x * p.v.sp + h * p.v.sh + pw.y * p.v.ss + sub * 16);
-                wt[u] = w[r] * p.v.scales[pw.x * p.v.csp + h * p.v.csh + pw.y];
-            }
+            const int2 pw = where[min(r, ntok - 1)];
+            const int slot = pw.y & ~PAST_END;
+            raw[u] = ld_stream16(p.v.codes + pw.x * p.v.sp + h * p.v.sh + slot * p.v.ss + sub * 16);
+            // the weight of a token past the end is already an exact zero; rows past ntok get zero here
+            const float vs = __ldg(p.v.scales + pw.x * p.v.csp + h * p.v.csh + slot);
+            wt[u] = r < ntok ? w[min(r, ntok - 1)] * vs : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < RU; ++u) {

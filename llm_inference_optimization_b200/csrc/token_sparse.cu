@@ -74,8 +74,10 @@ token_scores_kernel(const ScoreParams p, int tokens_per_cta) {
         uint4 kv[SUB];
 #pragma unroll
         for (int j = 0; j < SUB; ++j) {
-            const int t = base + j * RPW + rw;
-            kv[j] = t < t1 ? ld_stream16(kbase + (long long)t * p.k_st) : make_uint4(0u, 0u, 0u, 0u);
+            // rows past the end are clamped to the last row (their scores are never stored): loads without a
+            // condition are all issued before the first use
+            const int t = min(base + j * RPW + rw, t1 - 1);
+            kv[j] = ld_stream16(kbase + (long long)t * p.k_st);
         }
 #pragma unroll
         for (int j = 0; j < SUB; ++j) {
