@@ -48,7 +48,8 @@ constexpr float P_BOOST = 64.f;
 constexpr int Q8_SEPARATE16 = 0, Q8_SEPARATE64 = 1, Q8_FUSED = 2;
 constexpr int RECORD_ROWS = 33;                            // 16 K rows, 16 V rows, 1 row of 16 + 16 fp32 scales
 constexpr int RECORD_BYTES = RECORD_ROWS * Q8_D;           // 4224
-constexpr int Q8_WARPS = MAX_CONSUMER_WARPS;               // two groups of four: group g takes stages with it % 2 == g
+constexpr int Q8_GROUPS = 2;                               // consumer groups of four warps; group g takes the stages with it % Q8_GROUPS == g
+constexpr int Q8_WARPS = Q8_GROUPS * CONSUMER_WARPS;
 constexpr int Q8_CONSUMER_THREADS = Q8_WARPS * 32;
 constexpr int Q8_PRODUCERS = 4;                            // producer warps: each issues one share of every stage
 constexpr int Q8_THREADS = Q8_CONSUMER_THREADS + Q8_PRODUCERS * 32;
@@ -108,7 +109,7 @@ __device__ __forceinline__ void pool_tile_load(uint32_t dst, const CUtensorMap* 
     tma_load_4d(dst, tm, bar, c[0], c[1], c[2], c[3], policy);
 }
 
-template <int KVT>
+template <int KVT, int NT>
 __global__ void __launch_bounds__(Q8_THREADS, 1)
 gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const Q8Params p) {
@@ -217,33 +218,39 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 
     // ----------------------------------------------------------------- consumers
     pdl_wait_prior_grids();  // the query, the workspace and the output may belong to the previous kernel until now
+    // Tokens sit on the M side of both products (S^T = K Q^T, O^T = V^T P^T) and the query heads on the 8-wide N
+    // side, so a group of up to 8 heads costs one n-tile (NT = 1) instead of a mostly empty 16-row M tile.
     const int g = lane >> 2, tq = lane & 3;
     const int G = p.G;
 
-    // Query fragments.  Lane (g, tq) receives bytes 4tq..4tq+3 of every 16-byte chunk c of a key row, so
-    // MMA k-index 2tq+{0,1} of k-step c stands for channel 16c+4tq+{0,1} and k-index 2tq+8+{0,1} for 16c+4tq+{2,3}.
-    uint32_t qa[NCH][4];
-    {
-        const __half* q0 = p.q + (long long)b * p.q_stride_b + (long long)(h * G + g) * p.q_stride_h;
-        const __half* q1 = q0 + 8 * p.q_stride_h;
-        const bool v0 = g < G, v1 = g + 8 < G;
+    // Query as the B operand.  Lane (g, tq) receives bytes 4tq..4tq+3 of every 16-byte chunk c of a key row, so
+    // MMA k-index 2tq+{0,1} of k-step c stands for channel 16c+4tq+{0,1} and k-index 2tq+8+{0,1} for 16c+4tq+{2,3};
+    // column n of n-tile nt is head 8nt + n.
+    uint32_t qb[NT][NCH][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int head = nt * 8 + g;
+        const __half* qrow = p.q + (long long)b * p.q_stride_b + (long long)(h * G + head) * p.q_stride_h + tq * 4;
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
-            const int col = c * 16 + tq * 4;
-            const uint2 a = v0 ? *reinterpret_cast<const uint2*>(q0 + col) : make_uint2(0u, 0u);
-            const uint2 bq = v1 ? *reinterpret_cast<const uint2*>(q1 + col) : make_uint2(0u, 0u);
-            qa[c][0] = a.x; qa[c][2] = a.y;
-            qa[c][1] = bq.x; qa[c][3] = bq.y;
+            const uint2 v = head < G ? *reinterpret_cast<const uint2*>(qrow + c * 16) : make_uint2(0u, 0u);
+            qb[nt][c][0] = v.x;
+            qb[nt][c][1] = v.y;
         }
     }
 
-    // o[2c+e] is the 8-column tile whose column n stands for channel 16c + 2n + e
-    float o[2 * NCH][4];
+    // o[nt][c][j], o[nt][c][j+2]: channels 16c+2g and 16c+2g+1 of head 8nt+2tq+j
+    float o[NT][NCH][4];
+    float mrun[NT][2], lrun[NT][2];
 #pragma unroll
-    for (int n = 0; n < 2 * NCH; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) o[nt][c][0] = o[nt][c][1] = o[nt][c][2] = o[nt][c][3] = 0.f;
+        mrun[nt][0] = mrun[nt][1] = -INFINITY;
+        lrun[nt][0] = lrun[nt][1] = 0.f;
+    }
     const int lj = lane >> 3, r8 = lane & 7;
-    const int group = warp >> 2;          // which of the two consumer groups
+    const int group = warp >> 2;          // consumer group: takes the stages with it % Q8_GROUPS == group
     const int wc = warp & 3;              // this warp's 16-token chunk of a stage
     const int wtok = wc * 16;
     // Byte offsets inside a stage of this warp's 16 K rows, 16 V rows and 16 + 16 scales, and the swizzle
@@ -255,10 +262,17 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const uint32_t vs_off = fused ? ks_off + 64 : ks_off + 256;
     const int sc_phase = fused ? wc : 0;                  // the scale row of a record is swizzled too
     const uint32_t sw = (uint32_t)((r8 + (fused ? wc : 0)) & 7);
+    // ldmatrix x4 addressing, the same for K and V: matrices (tokens 0-7, chunk c), (tokens 8-15, chunk c),
+    // (tokens 0-7, chunk c+1), (tokens 8-15, chunk c+1)
+    const uint32_t ld_row_off = (uint32_t)(((lj & 1) * 8 + r8) * 128);
+    const uint32_t ld_ch = (uint32_t)(lj >> 1);
+    // scales of this lane's two tokens (rows g and g+8 of the warp's 16)
+    const uint32_t sc_off0 = (uint32_t)(((((g) >> 2) ^ sc_phase) << 4) + (g & 3) * 4);
+    const uint32_t sc_off1 = (uint32_t)(((((g + 8) >> 2) ^ sc_phase) << 4) + (g & 3) * 4);
 
-    int s = group;          // stage of tile `it`; p.stages >= 3, so one wrap per step at most
+    int s = group;          // stage of tile `it`; p.stages >= Q8_GROUPS, so one wrap per step at most
     uint32_t ph = 0;
-    for (int it = group; it < ntiles; it += 2, s += 2) {
+    for (int it = group; it < ntiles; it += Q8_GROUPS, s += Q8_GROUPS) {
         if (s >= p.stages) { s -= p.stages; ph ^= 1u; }
         if (!mbar_wait(full_bar + s * 8, ph)) {
             if (lane == 0) atomicOr(p.status, SKV_DEV_TIMEOUT);
@@ -266,59 +280,11 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         }
         const int tok0 = t_begin + it * TILE + wtok;
         if (tok0 < t_end) {
-            const uint32_t kbase = ring + s * Q8_STAGE_BYTES + k_off;   // this warp's K rows
-            const uint32_t vbase = ring + s * Q8_STAGE_BYTES + v_off;   // this warp's V rows
+            const uint32_t kbase = ring + s * Q8_STAGE_BYTES + k_off + ld_row_off;   // this lane's K row
+            const uint32_t vbase = ring + s * Q8_STAGE_BYTES + v_off + ld_row_off;   // this lane's V row
             const uint8_t* stage = smem + (size_t)s * Q8_STAGE_BYTES;
             const bool ragged = tok0 + 16 > t_end;
-
-            // Two accumulators per 8-token tile (even / odd ldmatrix groups) halve the dependent MMA chain.
-            float sc[2][4], sd[2][4];
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) sc[nt][j] = sd[nt][j] = 0.f;
-#pragma unroll
-            for (int m = 0; m < NCH / 4; ++m) {
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-                    const uint32_t row = (uint32_t)(nt * 8 + r8);
-                    uint32_t br[4];
-                    ldsm_x4(kbase + row * 128 + (((uint32_t)(4 * m + lj) ^ sw) << 4), br[0], br[1], br[2], br[3]);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t b0, b1;
-                        cvt_quad<KVT>(br[j], b0, b1);
-                        if (j & 1) mma_f16(sd[nt], qa[4 * m + j], b0, b1);
-                        else mma_f16(sc[nt], qa[4 * m + j], b0, b1);
-                    }
-                }
-            }
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) sc[nt][j] += sd[nt][j];
-
-            // per-token scales of this lane's two columns in each 8-token tile
-            float2 ksc[2], vsc[2];
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                const int i = nt * 8 + tq * 2;  // token within the warp's 16; its 16-byte chunk is i / 4
-                const uint32_t off = (uint32_t)((((i >> 2) ^ sc_phase) << 4) + (i & 3) * 4);
-                ksc[nt] = *reinterpret_cast<const float2*>(stage + ks_off + off);
-                vsc[nt] = *reinterpret_cast<const float2*>(stage + vs_off + off);
-            }
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                sc[nt][0] *= ksc[nt].x * p.scale_log2; sc[nt][1] *= ksc[nt].y * p.scale_log2;
-                sc[nt][2] *= ksc[nt].x * p.scale_log2; sc[nt][3] *= ksc[nt].y * p.scale_log2;
-            }
             if (ragged) {
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-                    const int t = tok0 + nt * 8 + tq * 2;
-                    if (t >= t_end) { sc[nt][0] = sc[nt][2] = -INFINITY; vsc[nt].x = 0.f; }
-                    if (t + 1 >= t_end) { sc[nt][1] = sc[nt][3] = -INFINITY; vsc[nt].y = 0.f; }
-                }
                 // rows past the end hold stale bytes (possibly NaN codes): zero them in V
                 for (int idx = lane; idx < 16 * 8; idx += 32) {
                     const int r = idx >> 3, c = idx & 7;
@@ -329,69 +295,112 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 __syncwarp();
             }
 
-            float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
-            float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-            if (__any_sync(0xffffffffu, (mn0 > m0) || (mn1 > m1))) {
-                const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
-                l0 *= c0;
-                l1 *= c1;
+            // S^T = K Q^T: two accumulators per n-tile (even / odd k-steps) halve the dependent MMA chain
+            float sc[NT][4], sd[NT][4];
 #pragma unroll
-                for (int n = 0; n < 2 * NCH; ++n) {
-                    o[n][0] *= c0; o[n][1] *= c0;
-                    o[n][2] *= c1; o[n][3] *= c1;
-                }
-                m0 = mn0;
-                m1 = mn1;
-            }
-            uint32_t pa[4];
-            {
-                const float p00 = fast_exp2(sc[0][0] - m0), p01 = fast_exp2(sc[0][1] - m0);
-                const float p02 = fast_exp2(sc[0][2] - m1), p03 = fast_exp2(sc[0][3] - m1);
-                const float p10 = fast_exp2(sc[1][0] - m0), p11 = fast_exp2(sc[1][1] - m0);
-                const float p12 = fast_exp2(sc[1][2] - m1), p13 = fast_exp2(sc[1][3] - m1);
-                l0 += (p00 + p01) + (p10 + p11);
-                l1 += (p02 + p03) + (p12 + p13);
-                const float a0 = vsc[0].x * P_BOOST, a1 = vsc[0].y * P_BOOST;
-                const float b0 = vsc[1].x * P_BOOST, b1 = vsc[1].y * P_BOOST;
-                pa[0] = pack_half2(p00 * a0, p01 * a1);
-                pa[1] = pack_half2(p02 * a0, p03 * a1);
-                pa[2] = pack_half2(p10 * b0, p11 * b1);
-                pa[3] = pack_half2(p12 * b0, p13 * b1);
-            }
-
-            // O += P V.  A transposed 8x8 b16 matrix hands lane (g, tq) the bytes
-            // [v(t0,2g), v(t0,2g+1), v(t0+1,2g), v(t0+1,2g+1)], t0 = 2tq: even and odd channels split into two tiles.
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sc[nt][j] = sd[nt][j] = 0.f;
 #pragma unroll
             for (int m = 0; m < NCH / 2; ++m) {
-                const int c = 2 * m + (lj >> 1);
-                const uint32_t row = (uint32_t)((lj & 1) * 8 + r8);
                 uint32_t r0, r1, r2, r3;
-                ldsm_x4_t(vbase + row * 128 + (((uint32_t)c ^ sw) << 4), r0, r1, r2, r3);
-                // bytes [a0,a1,b0,b1] -> [a0,b0,a1,b1]: low half = even channel of both tokens, high half = odd channel
-                uint32_t e0, o0, e1, o1, e2, o2, e3, o3;
-                cvt_quad<KVT>(__byte_perm(r0, 0u, 0x3120), e0, o0);
-                cvt_quad<KVT>(__byte_perm(r1, 0u, 0x3120), e1, o1);
-                cvt_quad<KVT>(__byte_perm(r2, 0u, 0x3120), e2, o2);
-                cvt_quad<KVT>(__byte_perm(r3, 0u, 0x3120), e3, o3);
-                mma_f16(o[4 * m + 0], pa, e0, e1);
-                mma_f16(o[4 * m + 1], pa, o0, o1);
-                mma_f16(o[4 * m + 2], pa, e2, e3);
-                mma_f16(o[4 * m + 3], pa, o2, o3);
+                ldsm_x4(kbase + (((uint32_t)(2 * m) + ld_ch) ^ sw) * 16, r0, r1, r2, r3);
+                uint32_t a0[4], a1[4];
+                cvt_quad<KVT>(r0, a0[0], a0[2]);   // token g:   k-indices 2tq.. and 2tq+8..
+                cvt_quad<KVT>(r1, a0[1], a0[3]);   // token g+8
+                cvt_quad<KVT>(r2, a1[0], a1[2]);
+                cvt_quad<KVT>(r3, a1[1], a1[3]);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mma_f16(sc[nt], a0, qb[nt][2 * m][0], qb[nt][2 * m][1]);
+                    mma_f16(sd[nt], a1, qb[nt][2 * m + 1][0], qb[nt][2 * m + 1][1]);
+                }
+            }
+            float ks0 = *reinterpret_cast<const float*>(stage + ks_off + sc_off0) * p.scale_log2;
+            float ks1 = *reinterpret_cast<const float*>(stage + ks_off + sc_off1) * p.scale_log2;
+            float vs0 = *reinterpret_cast<const float*>(stage + vs_off + sc_off0) * P_BOOST;
+            float vs1 = *reinterpret_cast<const float*>(stage + vs_off + sc_off1) * P_BOOST;
+            const bool dead0 = ragged && tok0 + g >= t_end, dead1 = ragged && tok0 + g + 8 >= t_end;
+            if (dead0) vs0 = 0.f;
+            if (dead1) vs1 = 0.f;
+            float mnew[NT][2];
+            bool grow = false;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                sc[nt][0] = dead0 ? -INFINITY : (sc[nt][0] + sd[nt][0]) * ks0;
+                sc[nt][1] = dead0 ? -INFINITY : (sc[nt][1] + sd[nt][1]) * ks0;
+                sc[nt][2] = dead1 ? -INFINITY : (sc[nt][2] + sd[nt][2]) * ks1;
+                sc[nt][3] = dead1 ? -INFINITY : (sc[nt][3] + sd[nt][3]) * ks1;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {   // maximum over the 16 tokens: this lane's two rows, then the 8 lanes g
+                    float mx = fmaxf(sc[nt][j], sc[nt][j + 2]);
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                    mnew[nt][j] = fmaxf(mrun[nt][j], mx);
+                    grow |= mnew[nt][j] > mrun[nt][j];
+                }
+            }
+            if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const float c0 = fast_exp2(mrun[nt][0] - mnew[nt][0]), c1 = fast_exp2(mrun[nt][1] - mnew[nt][1]);
+                    lrun[nt][0] *= c0;
+                    lrun[nt][1] *= c1;
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c) {
+                        o[nt][c][0] *= c0; o[nt][c][1] *= c1;
+                        o[nt][c][2] *= c0; o[nt][c][3] *= c1;
+                    }
+                    mrun[nt][0] = mnew[nt][0];
+                    mrun[nt][1] = mnew[nt][1];
+                }
+            }
+            // P^T as the B operand of O^T = V^T P^T: the accumulator layout holds (token g | g+8, heads 2tq, 2tq+1);
+            // a transposing 8x8 move turns it into (tokens 2tq, 2tq+1 | +8, head g)
+            uint32_t pb[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float p0 = fast_exp2(sc[nt][0] - mrun[nt][0]), p1 = fast_exp2(sc[nt][1] - mrun[nt][1]);
+                const float p2 = fast_exp2(sc[nt][2] - mrun[nt][0]), p3 = fast_exp2(sc[nt][3] - mrun[nt][1]);
+                lrun[nt][0] += p0 + p2;
+                lrun[nt][1] += p1 + p3;
+                pb[nt][0] = movmatrix_trans(pack_half2(p0 * vs0, p1 * vs0));
+                pb[nt][1] = movmatrix_trans(pack_half2(p2 * vs1, p3 * vs1));
+            }
+
+            // O^T += V^T P^T.  A transposed 8x8 b16 matrix hands lane (g, tq) the bytes
+            // [v(t0,2g), v(t0,2g+1), v(t0+1,2g), v(t0+1,2g+1)], t0 = 2tq, of a 16-byte chunk: after the byte
+            // shuffle the even channel 2g of both tokens is row g and the odd channel 2g+1 row g+8 of the M tile.
+#pragma unroll
+            for (int m = 0; m < NCH / 2; ++m) {
+                uint32_t r0, r1, r2, r3;
+                ldsm_x4_t(vbase + (((uint32_t)(2 * m) + ld_ch) ^ sw) * 16, r0, r1, r2, r3);
+                uint32_t a0[4], a1[4];
+                cvt_quad<KVT>(__byte_perm(r0, 0u, 0x3120), a0[0], a0[1]);   // tokens 0-7:  even | odd channel
+                cvt_quad<KVT>(__byte_perm(r1, 0u, 0x3120), a0[2], a0[3]);   // tokens 8-15
+                cvt_quad<KVT>(__byte_perm(r2, 0u, 0x3120), a1[0], a1[1]);
+                cvt_quad<KVT>(__byte_perm(r3, 0u, 0x3120), a1[2], a1[3]);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mma_f16(o[nt][2 * m], a0, pb[nt][0], pb[nt][1]);
+                    mma_f16(o[nt][2 * m + 1], a1, pb[nt][0], pb[nt][1]);
+                }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar + s * 8);
     }
 
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    // the running sums are per lane (its two token rows): total over the 8 lanes g
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            lrun[nt][j] += __shfl_xor_sync(0xffffffffu, lrun[nt][j], 4);
+            lrun[nt][j] += __shfl_xor_sync(0xffffffffu, lrun[nt][j], 8);
+            lrun[nt][j] += __shfl_xor_sync(0xffffffffu, lrun[nt][j], 16);
+        }
 
     named_bar_sync(1, Q8_CONSUMER_THREADS);
     float* mo = reinterpret_cast<float*>(smem);
@@ -399,20 +408,18 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     float* ml = mm + Q8_WARPS * MAX_GROUP;
     {
         float* my = mo + (warp * MAX_GROUP) * D;
-        if (g < G) {
 #pragma unroll
-            for (int c = 0; c < NCH; ++c)
-                *reinterpret_cast<float4*>(my + g * D + c * 16 + tq * 4) =
-                    make_float4(o[2 * c][0], o[2 * c + 1][0], o[2 * c][1], o[2 * c + 1][1]);
-            if (tq == 0) { mm[warp * MAX_GROUP + g] = m0; ml[warp * MAX_GROUP + g] = l0; }
-        }
-        if (g + 8 < G) {
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int c = 0; c < NCH; ++c)
-                *reinterpret_cast<float4*>(my + (g + 8) * D + c * 16 + tq * 4) =
-                    make_float4(o[2 * c][2], o[2 * c + 1][2], o[2 * c][3], o[2 * c + 1][3]);
-            if (tq == 0) { mm[warp * MAX_GROUP + g + 8] = m1; ml[warp * MAX_GROUP + g + 8] = l1; }
-        }
+            for (int j = 0; j < 2; ++j) {
+                const int head = nt * 8 + tq * 2 + j;
+                if (head < G) {
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c)
+                        *reinterpret_cast<float2*>(my + head * D + c * 16 + g * 2) = make_float2(o[nt][c][j], o[nt][c][j + 2]);
+                    if (g == 0) { mm[warp * MAX_GROUP + head] = mrun[nt][j]; ml[warp * MAX_GROUP + head] = lrun[nt][j]; }
+                }
+            }
     }
     named_bar_sync(1, Q8_CONSUMER_THREADS);
     EpilogueArgs ea;
@@ -421,18 +428,18 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     merge_and_combine<D, Q8_WARPS>(ea, smem, last_flag, b, h, split, n_splits, 1.f / P_BOOST);
 }
 
-template <int KVT>
+template <int KVT, int NT>
 static int launch_q8(const CUtensorMap& tmK, const CUtensorMap& tmV, const Q8Params& p, int B, cudaStream_t stream) {
     static int configured_smem[64] = {0};
     const size_t smem = q8_smem_bytes(p.stages);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && configured_smem[dev] < (int)smem) {
-        SKV_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_q8_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        SKV_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_q8_kernel<KVT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured_smem[dev] = (int)smem;
     }
     dim3 grid(p.Hkv, p.num_splits, B);
-    SKV_CUDA_TRY(launch_pdl(gqa_decode_q8_kernel<KVT>, grid, dim3(Q8_THREADS), smem, stream, tmK, tmV, p));
+    SKV_CUDA_TRY(launch_pdl(gqa_decode_q8_kernel<KVT, NT>, grid, dim3(Q8_THREADS), smem, stream, tmK, tmV, p));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }
@@ -536,8 +543,11 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.scale_log2 = scale * 1.4426950408889634f;
     p.pos = pos;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3>(tmK, tmV, p, B, st)
-                                   : gqa::launch_q8<SKV_KV_I8>(tmK, tmV, p, B, st);
+    if (G <= 8)
+        return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3, 1>(tmK, tmV, p, B, st)
+                                       : gqa::launch_q8<SKV_KV_I8, 1>(tmK, tmV, p, B, st);
+    return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3, 2>(tmK, tmV, p, B, st)
+                                   : gqa::launch_q8<SKV_KV_I8, 2>(tmK, tmV, p, B, st);
 }
 
 }  // extern "C"
