@@ -95,7 +95,7 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool,
                          long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
                          long long scale_stride_page, long long scale_stride_head,
                          float scale, int device, void* stream);
-/* Ring depth of the 8-bit kernel (3..12 stages of 17 KB); process-wide.  No reference counterpart. */
+/* Ring depth of the 8-bit kernel (an even number of 17 KB stages in 4..12); process-wide.  No reference counterpart. */
 int skv_gqa_set_q8_stages(int stages);
 
 /* ---- Quest-style block-sparse decode over a paged 8-bit cache ----------------------

@@ -48,11 +48,13 @@ constexpr float P_BOOST = 64.f;
 constexpr int Q8_SEPARATE16 = 0, Q8_SEPARATE64 = 1, Q8_FUSED = 2;
 constexpr int RECORD_ROWS = 33;                            // 16 K rows, 16 V rows, 1 row of 16 + 16 fp32 scales
 constexpr int RECORD_BYTES = RECORD_ROWS * Q8_D;           // 4224
-constexpr int Q8_GROUPS = 2;                               // consumer groups of four warps; group g takes the stages with it % Q8_GROUPS == g
-constexpr int Q8_WARPS = Q8_GROUPS * CONSUMER_WARPS;
-constexpr int Q8_CONSUMER_THREADS = Q8_WARPS * 32;
+// Consumer groups of four warps; group g takes the stages with it % groups == g.  The ring depth must be a
+// multiple of the group count so that a stage always belongs to the same group: a group that could reach a
+// stage two uses ahead of another group's wait would pass a parity wait meant for the use before.  Two groups
+// are enough (a third, tried with 123 registers per thread, brought no gain at 16 x 64K).
+__host__ __device__ constexpr int q8_groups(int /*nt*/) { return 2; }
 constexpr int Q8_PRODUCERS = 4;                            // producer warps: each issues one share of every stage
-constexpr int Q8_THREADS = Q8_CONSUMER_THREADS + Q8_PRODUCERS * 32;
+__host__ __device__ constexpr int q8_threads(int nt) { return (q8_groups(nt) * CONSUMER_WARPS + Q8_PRODUCERS) * 32; }
 
 struct Q8Params {
     const __half* q;
@@ -75,9 +77,10 @@ struct Q8Params {
     PoolMapPos pos;
 };
 
+template <int NT>
 static size_t q8_smem_bytes(int stages) {
     size_t ring = (size_t)stages * Q8_STAGE_BYTES;
-    size_t merge = merge_smem_bytes<Q8_D, Q8_WARPS>();
+    size_t merge = merge_smem_bytes<Q8_D, q8_groups(NT) * CONSUMER_WARPS>();
     return 1024 + (ring > merge ? ring : merge) + 2 * stages * 8 + 16;
 }
 
@@ -110,10 +113,13 @@ __device__ __forceinline__ void pool_tile_load(uint32_t dst, const CUtensorMap* 
 }
 
 template <int KVT, int NT>
-__global__ void __launch_bounds__(Q8_THREADS, 1)
+__global__ void __launch_bounds__(q8_threads(NT), 1)
 gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const Q8Params p) {
     constexpr int D = Q8_D;
+    constexpr int Q8_GROUPS = q8_groups(NT);
+    constexpr int Q8_WARPS = Q8_GROUPS * CONSUMER_WARPS;
+    constexpr int Q8_CONSUMER_THREADS = Q8_WARPS * 32;
     constexpr int NCH = D / 16;  // 16-byte chunks per row = MMA k-steps of S = Q K^T
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
@@ -431,7 +437,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 template <int KVT, int NT>
 static int launch_q8(const CUtensorMap& tmK, const CUtensorMap& tmV, const Q8Params& p, int B, cudaStream_t stream) {
     static int configured_smem[64] = {0};
-    const size_t smem = q8_smem_bytes(p.stages);
+    const size_t smem = q8_smem_bytes<NT>(p.stages);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && configured_smem[dev] < (int)smem) {
@@ -439,7 +445,7 @@ static int launch_q8(const CUtensorMap& tmK, const CUtensorMap& tmV, const Q8Par
         configured_smem[dev] = (int)smem;
     }
     dim3 grid(p.Hkv, p.num_splits, B);
-    SKV_CUDA_TRY(launch_pdl(gqa_decode_q8_kernel<KVT, NT>, grid, dim3(Q8_THREADS), smem, stream, tmK, tmV, p));
+    SKV_CUDA_TRY(launch_pdl(gqa_decode_q8_kernel<KVT, NT>, grid, dim3(q8_threads(NT)), smem, stream, tmK, tmV, p));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }
@@ -452,7 +458,8 @@ using namespace skv;
 extern "C" {
 
 int skv_gqa_set_q8_stages(int stages) {
-    if (stages < 3 || stages > 12) return fail(SKV_ERR_BAD_ARG, "q8 stages out of range: %d", stages);
+    // even, so that a stage is always drained by the same consumer group
+    if (stages < 4 || stages > 12 || stages % 2) return fail(SKV_ERR_BAD_ARG, "q8 stages must be even and in 4..12: %d", stages);
     gqa::tuning().q8_stages = stages;
     return SKV_OK;
 }

@@ -16,7 +16,7 @@ constexpr int TILE = 64;            // tokens per pipeline stage
 constexpr int CONSUMER_WARPS = 4;   // fp16 kernel: each warp takes TILE / 4 = 16 tokens of a stage
 constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMER_THREADS + 32;
-constexpr int MAX_CONSUMER_WARPS = 8;  // the 8-bit kernel runs two groups of four warps on alternate stages
+constexpr int MAX_CONSUMER_WARPS = 12;  // the 8-bit kernel runs up to three groups of four warps on rotating stages
 constexpr int MAX_SPLITS = 512;
 constexpr int MAX_GROUP = 16;       // query heads per kv head (rows of one MMA tile)
 
