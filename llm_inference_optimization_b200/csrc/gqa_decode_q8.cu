@@ -13,16 +13,21 @@
 // P (tokens per page) is a multiple of 16; an unpaged [B, H, T, D] cache is the
 // special case P = T with a null page table.
 //
-// Same structure as the fp16 kernel: grid (Hkv, splits, B), a producer warp
-// feeding a ring of 64-token stages, four consumer warps with mma.sync, online
-// softmax, in-CTA merge, ticketed split combine.  Differences:
-//   * a stage is filled by up to four 16-token TMA boxes per pool (one per page
-//     chunk) plus four 64-byte bulk copies per scale pool; the producer warp
-//     prefetches page ids for eight tiles at a time;
+// Same skeleton as the fp16 kernel: grid (Hkv, splits, B), producers feeding a ring
+// of 64-token stages through mbarriers, consumers with mma.sync, online softmax,
+// in-CTA merge, ticketed split combine.  Differences:
+//   * four producer warps share every stage (an async copy costs its issuing warp
+//     100-200 cycles); a stage is four fused page records (one TMA box each), or K/V
+//     boxes plus bulk copies of the scales for separate pools; page ids are
+//     prefetched 32 tiles ahead, one per lane;
+//   * two groups of four consumer warps work on alternate stages;
+//   * tokens are on the M side of both products (S^T = K Q^T, O^T = V^T P^T) and the
+//     query heads on the 8-wide N side: a group of <= 8 heads needs one n-tile;
+//     P is moved to the B-operand layout with movmatrix;
 //   * codes are converted to fp16 in registers right after ldmatrix (e4m3x2 ->
 //     f16x2 by cvt, int8 by a byte-permute + subtract); because four bytes arrive
 //     per lane where an fp16 fragment has two halves, the contraction index of
-//     S = Q K^T and the output channels of P V are permuted consistently;
+//     S^T and the output channels of O^T are permuted consistently;
 //   * ks[t] multiplies the fp32 score; vs[t] (times 2^6, undone at the end, to stay
 //     clear of fp16 subnormals) is folded into P before it is rounded to fp16.
 #include <cuda_fp8.h>
