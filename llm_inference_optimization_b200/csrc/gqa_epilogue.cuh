@@ -36,6 +36,11 @@ inline Tuning& tuning() {
     return t;
 }
 
+// Waves of CTAs the KV length is cut into when the per-sequence lengths are not known to the host.
+#ifndef SKV_RAGGED_WAVES
+#define SKV_RAGGED_WAVES 8
+#endif
+
 struct Plan {
     int splits, tiles_per_split;
     size_t off_status, off_tickets, off_ml, off_o, total;
@@ -58,7 +63,7 @@ inline Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device, bool rag
         // (CTAs past a sequence's end exit at once).
         const long long max_by_size = total_tiles / 16 > 0 ? total_tiles / 16 : 1;   // at least 16 tiles per split
         if (ragged) {
-            splits = (8 * target + pairs - 1) / pairs;
+            splits = (SKV_RAGGED_WAVES * target + pairs - 1) / pairs;
         } else {
             // equal lengths: every CTA lasts the same, so pick the split count between about 2 and 8 waves whose
             // last wave is fullest (pairs * splits CTAs over `target` slots), the smallest such count on ties

@@ -29,7 +29,10 @@ def make_case(B, Hq, Hkv, T, fmt, seed, page_size=16, unit=False):
 
 @pytest.mark.parametrize("fmt", ["fp8", "int8"])
 @pytest.mark.parametrize("B,Hq,Hkv,T,lens", [(1, 32, 8, 4096, None), (3, 32, 8, 2048, [2048, 1, 1037]),
-                                             (2, 8, 2, 8192, [8192, 5000]), (1, 16, 1, 64, [17])])
+                                             (2, 8, 2, 8192, [8192, 5000]), (1, 16, 1, 64, [17]),
+                                             # group sizes 16 (two head tiles), 8, 1 (no grouping) and 6 (not a power of two)
+                                             (2, 32, 2, 4096, [4096, 777]), (1, 16, 2, 2048, None),
+                                             (1, 4, 4, 1024, [1000]), (1, 12, 2, 1024, None)])
 def test_paged_decode(cuda_device, fmt, B, Hq, Hkv, T, lens):
     Q, pools, (Kd, Vd) = make_case(B, Hq, Hkv, T, fmt, seed=T + B)
     kp, vp, ksp, vsp, table = (t.to(cuda_device) for t in pools)
