@@ -39,6 +39,8 @@ extern "C" {
 #define SKV_KV_F16 0
 #define SKV_KV_I8 1
 #define SKV_KV_E4M3 2
+/* OR-ed into kv_dtype of skv_gqa_decode_paged: the output tensor holds bf16 instead of fp16 elements. */
+#define SKV_OUT_BF16 0x100
 
 /* bit in the workspace status word: a bounded wait inside a kernel ran out */
 #define SKV_DEV_TIMEOUT 1
@@ -209,6 +211,17 @@ int skv_gqa_decode_noalloc(const void* q, const void* k, const void* v, void* ou
                            int B, int N, int Hq, int Hkv, int D,
                            long long kv_stride_b, long long kv_stride_n, long long kv_stride_h,
                            const int* seq_lens, float scale, int device, void* stream);
+
+/* ---- decode-step glue around the attention call -------------------------------------
+ * The reference runs Hugging Face's LlamaRMSNorm / LlamaMLP modules here (the model it patches,
+ * benchmarks/llama_integration_benchmark.py:266-279); with 16 rows per step those are launch-bound.
+ * skv_residual_rmsnorm: resid[r,:] <- round(resid + delta) when delta is non-null (in place), then
+ *   out[r,:] = round(resid * rsqrt(mean(resid^2) + eps) * weight); [rows, hidden] row-major, hidden % 8 == 0,
+ *   hidden <= 8192, fp16 (is_bf16 = 0) or bf16 elements, 16-byte aligned.
+ * skv_silu_mul: out[r,c] = round(round(silu(gate_up[r,c])) * gate_up[r,inter+c]); gate_up [rows, 2*inter], out [rows, inter]. */
+int skv_residual_rmsnorm(const void* delta, void* resid, const void* weight, void* out, int rows, int hidden, float eps,
+                         int is_bf16, int device, void* stream);
+int skv_silu_mul(const void* gate_up, void* out, int rows, int inter, int is_bf16, int device, void* stream);
 
 #ifdef __cplusplus
 }

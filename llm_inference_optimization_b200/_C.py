@@ -158,6 +158,9 @@ def sparse_attention_forward(Q: Tensor, K: Tensor, V: Tensor, block_size: int, t
     return (out, idx) if return_indices else out
 
 
+SKV_OUT_BF16 = 0x100  # OR-ed into the kv_dtype argument of skv_gqa_decode_paged: bf16 output elements
+
+
 def _code_dtype(t: Tensor) -> int:
     if t.dtype == torch.int8:
         return _lib.KV_I8
@@ -174,7 +177,8 @@ def fused_gqa_paged(Q: Tensor, k_pool: Tensor, v_pool: Tensor, k_scale: Tensor, 
     Q ``[B,Hq,128]`` fp16; pools ``[num_pages, Hkv, page_size, 128]`` int8 or float8_e4m3fn; scale pools
     ``[num_pages, Hkv, page_size]`` fp32; ``page_table`` int32 ``[B, max_pages]`` (``None``: sequence b owns
     pages ``b*max_pages ...``, so a ``[B,Hkv,T,128]`` compacted cache is passed with ``page_size = T``);
-    ``seq_lens`` int32 ``[B]``.  Returns ``[B,Hq,128]`` fp16.  No reference counterpart.
+    ``seq_lens`` int32 ``[B]``.  Returns ``[B,Hq,128]`` fp16, or bf16 when ``out`` is a bf16 tensor.  No
+    reference counterpart.
     """
     _require(Q.is_cuda and Q.dtype == torch.float16 and Q.dim() == 3 and Q.is_contiguous(),
              "Q must be a contiguous fp16 CUDA tensor [B,Hq,D]")
@@ -204,6 +208,10 @@ def fused_gqa_paged(Q: Tensor, k_pool: Tensor, v_pool: Tensor, k_scale: Tensor, 
     lib = _lib.load()
     if out is None:
         out = torch.empty((B, Hq, D), dtype=torch.float16, device=Q.device)
+    _require(out.dtype in (torch.float16, torch.bfloat16) and out.shape == (B, Hq, D) and out.is_contiguous()
+             and out.device == Q.device, "out must be a contiguous fp16 or bf16 [B,Hq,D] tensor on Q's device")
+    if out.dtype == torch.bfloat16:
+        kvt |= SKV_OUT_BF16
     ws = _workspace.get("gqa", lib.skv_gqa_decode_workspace_bytes(B, N, Hq, Hkv, D, dev), Q.device)
     stream = torch.cuda.current_stream(Q.device).cuda_stream
     rc = lib.skv_gqa_decode_paged(

@@ -76,6 +76,7 @@ struct Q8Params {
     int tiles_per_split, num_splits, stages;
     int page_size, max_pages;
     int mode;                // Q8_SEPARATE16, Q8_SEPARATE64 or Q8_FUSED
+    int out_bf16;            // output elements are bf16 instead of fp16
     long long sc_sp, sc_sh;
     long long q_stride_b, q_stride_h, o_stride_b, o_stride_h;
     float scale_log2;
@@ -435,6 +436,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     named_bar_sync(1, Q8_CONSUMER_THREADS);
     EpilogueArgs ea;
     ea.partial_o = p.partial_o; ea.partial_ml = p.partial_ml; ea.tickets = p.tickets; ea.out = p.out;
+    ea.out_bf16 = p.out_bf16 != 0;
     ea.Hkv = p.Hkv; ea.G = G; ea.num_splits = p.num_splits; ea.o_stride_b = p.o_stride_b; ea.o_stride_h = p.o_stride_h;
     merge_and_combine<D, Q8_WARPS>(ea, smem, last_flag, b, h, split, n_splits, 1.f / P_BOOST);
 }
@@ -475,6 +477,8 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
                          int page_size, int max_pages, int num_pages, long long pool_stride_page,
                          long long pool_stride_head, long long pool_stride_slot, long long scale_stride_page,
                          long long scale_stride_head, float scale, int device, void* stream) {
+    const int out_bf16 = (kv_dtype & SKV_OUT_BF16) ? 1 : 0;
+    kv_dtype &= ~SKV_OUT_BF16;
     if (!q || !k_pool || !v_pool || !k_scale_pool || !v_scale_pool || !out)
         return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode_paged: null tensor pointer");
     if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || num_pages <= 0 || max_pages <= 0)
@@ -546,6 +550,7 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.tiles_per_split = pl.tiles_per_split;
     p.num_splits = pl.splits;
     p.stages = gqa::tuning().q8_stages;
+    p.out_bf16 = out_bf16;
     p.page_size = page_size;
     p.max_pages = max_pages;
     p.mode = mode;

@@ -7,6 +7,8 @@
 // (csrc/kernels/gqa_decode.cu:255 launches one CTA per query head).
 #pragma once
 
+#include <cuda_bf16.h>
+
 #include "skv_common.cuh"
 
 namespace skv {
@@ -107,7 +109,12 @@ struct EpilogueArgs {
     __half* out;         // element (b, hq, d) at b*o_stride_b + hq*o_stride_h + d
     int Hkv, G, num_splits;
     long long o_stride_b, o_stride_h;
+    bool out_bf16 = false;   // store bf16 instead of fp16 (same element size and strides)
 };
+
+__device__ __forceinline__ uint16_t out_bits(float x, bool bf16) {
+    return bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(x)) : __half_as_ushort(__float2half_rn(x));
+}
 
 // Called by all NW * 32 consumer threads (threadIdx.x < NW * 32) after every
 // warp has stored its state at `smem`: O [NW][MAX_GROUP][D], running max
@@ -141,7 +148,8 @@ __device__ __forceinline__ void merge_and_combine(const EpilogueArgs& p, uint8_t
         O *= out_scale;
         if (n_splits == 1) {
             const float inv = L > 0.f ? 1.f / L : 0.f;
-            p.out[(long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + d] = __float2half_rn(O * inv);
+            reinterpret_cast<uint16_t*>(p.out)[(long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + d] =
+                out_bits(O * inv, p.out_bf16);
         } else {
             p.partial_o[(pbase + r) * D + d] = O;
             if (d == 0) {
@@ -191,11 +199,9 @@ __device__ __forceinline__ void merge_and_combine(const EpilogueArgs& p, uint8_t
                 acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
             }
             const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
-            __half2 lo = __floats2half2_rn(acc.x * inv, acc.y * inv);
-            __half2 hi = __floats2half2_rn(acc.z * inv, acc.w * inv);
             uint2 pk;
-            pk.x = *reinterpret_cast<uint32_t*>(&lo);
-            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            pk.x = (uint32_t)out_bits(acc.x * inv, p.out_bf16) | ((uint32_t)out_bits(acc.y * inv, p.out_bf16) << 16);
+            pk.y = (uint32_t)out_bits(acc.z * inv, p.out_bf16) | ((uint32_t)out_bits(acc.w * inv, p.out_bf16) << 16);
             *reinterpret_cast<uint2*>(p.out + (long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + lane * 4) = pk;
         }
         __syncwarp();

@@ -26,6 +26,7 @@
 #define SKV_KV_F16 0
 #define SKV_KV_I8 1
 #define SKV_KV_E4M3 2
+#define SKV_OUT_BF16 0x100
 
 // Bit set in the per-workspace device status word when a bounded wait gave up.
 #define SKV_DEV_TIMEOUT 1

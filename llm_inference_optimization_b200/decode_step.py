@@ -203,21 +203,28 @@ class DecodeModel:
         x = self.embed[tokens]
         pos = self.seq_lens
         new_lens = self.seq_lens + 1
+        if self.fused_glue:
+            # Per layer: residual+RMSNorm, qkv GEMM, RoPE+quantise+append, attention (writing the model dtype),
+            # o_proj GEMM, residual+RMSNorm, gate/up GEMM, SiLU*up, down GEMM -- four of our launches and four GEMMs.
+            # The residual stream x is updated in place; `delta` is the MLP output still to be added to it.
+            from . import _C, glue
+            delta = None
+            for w, cache in zip(self.layers, self.caches):
+                h = glue.residual_rmsnorm(x, delta, w["n1"], cfg.rms_eps)
+                qkv = h @ w["wqkv"]
+                kvv = paged.PagedKV(cache.k, cache.v, cache.ks, cache.vs, self.page_table, pos, B)
+                q = paged.rope_quant_append(qkv, kvv, sh.n_q, cfg.rope_theta)
+                a = torch.empty((B, sh.n_q, D), dtype=x.dtype, device=x.device)
+                _C.fused_gqa_paged(q, cache.k, cache.v, cache.ks, cache.vs, self.page_table, new_lens, scale,
+                                   max_seq_len=self.max_seq_len, out=a)
+                o = self._all_reduce(a.view(B, sh.n_q * D) @ w["wo"])
+                h = glue.residual_rmsnorm(x, o, w["n2"], cfg.rms_eps)
+                delta = self._all_reduce(glue.silu_mul(h @ w["wgu"]) @ w["wd"])
+            self.seq_lens.add_(1)
+            return glue.residual_rmsnorm(x, delta, self.final_norm, cfg.rms_eps) @ self.lm_head
         for w, cache in zip(self.layers, self.caches):
             h = rms_norm(x, w["n1"], cfg.rms_eps)
             qkv = h @ w["wqkv"]
-            if self.fused_glue:
-                # one launch: RoPE(q, k), quantise k and v, store them at position seq_lens[b] of the paged cache
-                kvv = paged.PagedKV(cache.k, cache.v, cache.ks, cache.vs, self.page_table, pos, B)
-                q = paged.rope_quant_append(qkv, kvv, sh.n_q, cfg.rope_theta)
-                a = self.attention(q, cache, self.page_table, new_lens, scale, self.max_seq_len)
-                o = a.to(x.dtype).reshape(B, sh.n_q * D) @ w["wo"]
-                x = x + self._all_reduce(o)
-                h = rms_norm(x, w["n2"], cfg.rms_eps)
-                gu = h @ w["wgu"]
-                half = gu.shape[1] // 2
-                x = x + self._all_reduce((torch.nn.functional.silu(gu[:, :half]) * gu[:, half:]) @ w["wd"])
-                continue
             q = qkv[:, :sh.n_q * D].view(B, sh.n_q, D)
             k = qkv[:, sh.n_q * D:(sh.n_q + sh.n_kv) * D].view(B, sh.n_kv, D)
             v = qkv[:, (sh.n_q + sh.n_kv) * D:].view(B, sh.n_kv, D)
