@@ -99,6 +99,11 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool,
                          float scale, int device, void* stream);
 /* Ring depth of the 8-bit kernel (an even number of 17 KB stages in 4..12); process-wide.  No reference counterpart. */
 int skv_gqa_set_q8_stages(int stages);
+/* The decode kernels are launched with programmatic stream serialisation.  on = 0 (default): they wait for the
+ * previous kernel of the stream before reading anything.  on = 1: K, V, the page table and seq_lens may be read
+ * before that kernel has completed -- valid when it produces none of them (consecutive layers' decode calls over
+ * caches written earlier); q, out and the workspace are always ordered.  Process-wide.  No reference counterpart. */
+int skv_gqa_set_early_kv(int on);
 
 /* ---- Quest-style block-sparse decode over a paged 8-bit cache ----------------------
  * No reference counterpart (the reference scores blocks by the mean of q.k over an unpaged fp16 cache,

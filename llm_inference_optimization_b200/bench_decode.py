@@ -34,10 +34,8 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    own_group = False
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
-        own_group = True
     cfg = ds.ModelConfig(layers=layers)
     g = torch.Generator().manual_seed(seed)
     lens = torch.randint(8192, 131073, (batch,), generator=g, dtype=torch.int32)
@@ -93,10 +91,13 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
         "hbm_bytes_per_step_per_gpu": ib["weight_bytes_per_gpu"] + ib["kv_bytes_per_gpu"],
         "achieved_GBps_per_gpu": (ib["weight_bytes_per_gpu"] + ib["kv_bytes_per_gpu"]) / (ms * 1e-3) / 1e9,
     }
+    # the captured graph holds NCCL kernels: release it (and the model) before anybody tears the communicator down
+    step = None
+    if use_graph:
+        del graph
     del model
+    torch.cuda.synchronize()
     torch.cuda.empty_cache()
-    if own_group:
-        dist.destroy_process_group()
     return out if rank == 0 else None
 
 
@@ -111,6 +112,9 @@ def main():
     res = run(args.steps, args.warmup, args.layers, args.batch, use_graph=not args.no_graph)
     if res is not None:
         print(json.dumps(res), flush=True)
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -45,6 +45,7 @@ struct Params {
     int tiles_per_split, num_splits, stages;
     long long q_stride_b, q_stride_h, o_stride_b, o_stride_h;
     float scale_log2;    // softmax scale * log2(e)
+    int early_kv;        // K/V and seq_lens are not produced by the previous kernel: stream them before it completes
     KvMapPos pos;
 };
 
@@ -83,6 +84,11 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
 
+    // Launched with programmatic stream serialisation, this kernel may start before the previous one in the stream
+    // has completed.  By default every thread waits for it here, so the kernel is ordered like any other; only when
+    // the caller has declared that K, V and seq_lens are not produced by the previous kernel (early_kv) does the
+    // wait move down to the consumers, and the producer streams K/V meanwhile.
+    if (!p.early_kv) pdl_wait_prior_grids();
     const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
     const int tokens_per_split = p.tiles_per_split * TILE;
     const int n_splits = len > 0 ? (len + tokens_per_split - 1) / tokens_per_split : 1;
@@ -112,8 +118,6 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         fence_barrier_init();
     }
     __syncthreads();
-    pdl_launch_dependents();  // the next launch may start its own prologue and K/V streaming as SMs free up
-
     // ------------------------------------------------------------------ producer
     if (warp == CONSUMER_WARPS) {
         if (lane == 0) {
@@ -147,9 +151,12 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const int tq = lane & 3;   // column pair within an 8-wide tile
     const int G = p.G;
 
-    // The K/V stream of the producer warp does not depend on the previous kernel, the query might (it can be
-    // that kernel's output) and the workspace / output written below certainly do: wait for it here.
-    pdl_wait_prior_grids();
+    // The query may be the previous kernel's output and the workspace / output written below certainly depend on
+    // it: in early_kv mode the wait is here.  Only after it is the NEXT launch released (it may start its prologue,
+    // and in early_kv mode its K/V stream, as SMs free up): a kernel released at this point starts after
+    // everything older than this kernel has completed, and this kernel itself never writes K or V.
+    if (p.early_kv) pdl_wait_prior_grids();
+    pdl_launch_dependents();
 
     // Query fragments for all k-steps, zero for padding rows.
     uint32_t qa[KSTEPS][4];
@@ -352,6 +359,14 @@ int skv_gqa_set_tuning(int stages, int ctas_per_sm) {
     return SKV_OK;
 }
 
+// 1: the decode kernels may read K, V, the page table and seq_lens before the previous kernel in the stream has
+// completed (valid when that kernel produces none of them, e.g. consecutive layers' decode calls over caches
+// written earlier); 0 (default): they wait for it first.  Process-wide.
+int skv_gqa_set_early_kv(int on) {
+    gqa::tuning().early_kv = on ? 1 : 0;
+    return SKV_OK;
+}
+
 size_t skv_gqa_decode_workspace_bytes(int B, int N, int Hq, int Hkv, int D, int device) {
     if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || D <= 0) return 0;
     // large enough for either split policy (with or without per-sequence lengths)
@@ -407,6 +422,7 @@ int skv_gqa_decode(const void* q, const void* k, const void* v, void* out, void*
     p.tiles_per_split = pl.tiles_per_split;
     p.num_splits = pl.splits;
     p.stages = gqa::tuning().stages;
+    p.early_kv = gqa::tuning().early_kv;
     p.q_stride_b = (long long)Hq * D; p.q_stride_h = D;
     p.o_stride_b = (long long)Hq * D; p.o_stride_h = D;
     p.scale_log2 = scale * 1.4426950408889634f;

@@ -77,6 +77,7 @@ struct Q8Params {
     int page_size, max_pages;
     int mode;                // Q8_SEPARATE16, Q8_SEPARATE64 or Q8_FUSED
     int out_bf16;            // output elements are bf16 instead of fp16
+    int early_kv;            // pages, page table and seq_lens are not produced by the previous kernel
     long long sc_sp, sc_sh;
     long long q_stride_b, q_stride_h, o_stride_b, o_stride_h;
     float scale_log2;
@@ -130,6 +131,8 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
 
+    // Ordered like any other kernel unless the caller declared the cache static (see the fp16 kernel).
+    if (!p.early_kv) pdl_wait_prior_grids();
     const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
     const int tokens_per_split = p.tiles_per_split * TILE;
     const int n_splits = len > 0 ? (len + tokens_per_split - 1) / tokens_per_split : 1;
@@ -155,7 +158,6 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         fence_barrier_init();
     }
     __syncthreads();
-    pdl_launch_dependents();
 
     // ------------------------------------------------------------------ producers
     // Issuing one async copy costs its warp 100-200 cycles, and the copies of one warp are issued one after
@@ -229,7 +231,11 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     }
 
     // ----------------------------------------------------------------- consumers
-    pdl_wait_prior_grids();  // the query, the workspace and the output may belong to the previous kernel until now
+    // The query, the workspace and the output may belong to the previous kernel until now (early_kv mode; otherwise
+    // the whole CTA has already waited).  The next launch is released only after this wait: it then starts after
+    // everything older than this kernel has completed, and this kernel writes no K/V.
+    if (p.early_kv) pdl_wait_prior_grids();
+    pdl_launch_dependents();
     // Tokens sit on the M side of both products (S^T = K Q^T, O^T = V^T P^T) and the query heads on the 8-wide N
     // side, so a group of up to 8 heads costs one n-tile (NT = 1) instead of a mostly empty 16-row M tile.
     const int g = lane >> 2, tq = lane & 3;
@@ -551,6 +557,7 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.num_splits = pl.splits;
     p.stages = gqa::tuning().q8_stages;
     p.out_bf16 = out_bf16;
+    p.early_kv = gqa::tuning().early_kv;
     p.page_size = page_size;
     p.max_pages = max_pages;
     p.mode = mode;

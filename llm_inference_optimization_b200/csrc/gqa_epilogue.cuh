@@ -32,6 +32,7 @@ struct Tuning {
     int stages = 4;        // fp16 ring depth (64-token stages of 32 KB at D = 128)
     int ctas_per_sm = 1;
     int q8_stages = 8;     // 8-bit ring depth (stages of 17 KB)
+    int early_kv = 0;      // 1: K/V, page table and lengths may be read before the previous kernel has completed
 };
 inline Tuning& tuning() {
     static Tuning t;
