@@ -338,15 +338,19 @@ __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, ui
     // x * (1 / scale) is within 2 ulp of the correctly rounded quotient, so for INT8 (codes must be bit-exact)
     // the divide is only redone when the product lies within 1e-4 of a rounding boundary (|q| <= 127, ulp <= 8e-6);
     // FP8 codes are allowed one code step and take the product as is.
+    // INT8 rounding: y + 1.5 * 2^23 is rounded to the integer grid (half to even) by the add itself and leaves
+    // the integer, in two's complement, in the low mantissa bits -- its low byte is the code.
     const float inv = __frcp_rn(scale);
+    constexpr float MAGIC = 12582912.f;
     int c[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         float y = x[i] * inv;
         if (MODE == SKV_QUANT_INT8) {
             // |y| <= 127 (1 + 2^-22) because |x| <= amax = 127 * scale, so rounding already lands in [-127, 127]
-            if (fabsf(y - floorf(y) - 0.5f) < 1e-4f) y = __fdiv_rn(x[i], scale);
-            c[i] = __float2int_rn(y);  // round half to even
+            float r = y + MAGIC;
+            if (fabsf(y - (r - MAGIC)) > 0.5f - 1e-4f) r = __fdiv_rn(x[i], scale) + MAGIC;
+            c[i] = __float_as_int(r);
         } else {
             c[i] = (int)__nv_cvt_float_to_fp8(fminf(fmaxf(y, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
         }
@@ -367,26 +371,48 @@ evict_gather_quant_kernel(const GatherParams p) {
     constexpr int GPB = GQ_THREADS / LPR;
     constexpr int U = 4;
     const int sub = threadIdx.x % LPR, grp = threadIdx.x / LPR;
-    const long long stride = (long long)gridDim.x * GPB;
-    // the trip count is taken from group 0 of the block so that it is the same for every lane of a warp
-    for (long long rb = (long long)blockIdx.x * GPB; rb < p.rows_total; rb += stride * U) {
+    // A CTA takes GPB * U consecutive kept rows per step (row of (u, group) = base + u * GPB + group) and strides
+    // over the whole list.  Rows past the end fall back to the group's first row of the step -- a real row that
+    // is in flight anyway -- and only their stores are suppressed: loads under a condition would be issued one by
+    // one, each behind the use of the one before, and one shared fallback row would be a hot spot.
+    constexpr long long CHUNK = (long long)GPB * U;
+    const long long step = (long long)gridDim.x * CHUNK;
+    const long long last = p.rows_total - 1;
+    // The positions of the NEXT step are fetched while this step's rows are in flight, so a step costs one memory
+    // round trip instead of two dependent ones.  The trip count is the same for every lane of a CTA.
+    int tn[U];
+    {
+        const long long r0 = (long long)blockIdx.x * CHUNK + grp;
+#pragma unroll
+        for (int u = 0; u < U; ++u) tn[u] = __ldg(p.idx + min(r0 + u * GPB, last));
+    }
+    for (long long rb = (long long)blockIdx.x * CHUNK; rb < p.rows_total; rb += step) {
         const long long r0 = rb + grp;
-        // Rows past the end are clamped to the last row and only their stores are suppressed: loads under a
-        // condition would be issued one by one, each behind the use of the one before.
+        const long long safe = min(r0, last);
         int t[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) t[u] = __ldg(p.idx + min(r0 + u * stride, p.rows_total - 1));
+        for (int u = 0; u < U; ++u) t[u] = tn[u];
+        if (rb + step < p.rows_total) {   // block-uniform
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const long long rn = r0 + step + u * GPB;
+                tn[u] = __ldg(p.idx + (rn <= last ? rn : safe));
+            }
+        }
         uint4 kr[U], vr[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const long long row = min(r0 + u * stride, p.rows_total - 1) / p.keep;  // (b, h)
-            const long long src = (row / p.H) * p.sb + (row % p.H) * p.sh + (long long)max(t[u], 0) * p.st + sub * 8;
+            const long long r = r0 + u * GPB;
+            const long long rr = r <= last ? r : safe;
+            const long long row = rr / p.keep;  // (b, h)
+            const int tt = r <= last ? t[u] : t[0];
+            const long long src = (row / p.H) * p.sb + (row % p.H) * p.sh + (long long)max(tt, 0) * p.st + sub * 8;
             kr[u] = ld_stream16(p.k + src);
             vr[u] = ld_stream16(p.v + src);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const long long r = r0 + u * stride;
+            const long long r = r0 + u * GPB;
             const bool valid = r < p.rows_total;
             if (MODE == SKV_QUANT_NONE) {
                 quant_row<MODE>(kr[u], sub, LPR, nullptr, nullptr, static_cast<__half*>(p.k_out) + r * D, valid);
@@ -404,8 +430,11 @@ static size_t select_smem() { return (size_t)TopkSmem<SEL_THREADS>::WORDS * 4 + 
 template <int D>
 static int launch_gather(const GatherParams& gp, int mode, int device, cudaStream_t st) {
     constexpr int GPB = GQ_THREADS / (D / 8);
-    long long blocks = (gp.rows_total + GPB - 1) / GPB;
-    const long long cap = (long long)sm_count(device) * 16;
+    long long blocks = (gp.rows_total + GPB * 4 - 1) / (GPB * 4);   // U = 4 rows per group and step
+#ifndef SKV_GATHER_CAP
+#define SKV_GATHER_CAP 16
+#endif
+    const long long cap = (long long)sm_count(device) * SKV_GATHER_CAP;
     if (blocks > cap) blocks = cap;
     switch (mode) {
         case SKV_QUANT_NONE: evict_gather_quant_kernel<D, SKV_QUANT_NONE><<<(unsigned)blocks, GQ_THREADS, 0, st>>>(gp); break;
