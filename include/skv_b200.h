@@ -201,6 +201,19 @@ int skv_kv_evict_quant(const void* k_cache, const void* v_cache, const float* sc
                        long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
                        int budget, int recent, int quant_mode, int order, int device, void* stream);
 
+/* skv_gqa_decode (fp16 KV) that also ACCUMULATES the attention mass of every cached token:
+ *   mass[b, hkv, t] += sum over the query heads hq of kv-head hkv of softmax_t(scale * q[b,hq] . k[b,t,hkv])
+ * mass: fp32 [B, Hkv, N], read-modify-write for t < seq_lens[b] (N without seq_lens).  This is the per-token
+ * importance score that the reference's fused_kv_evict takes as `scores` (sparse_kv/eviction.py:12-22) and leaves
+ * to its caller to produce; summed over decode steps it drives skv_kv_evict_quant.  The decode kernel stores its
+ * scaled scores (fp32 [B,Hq,N]) and each head's final softmax maximum and denominator in the workspace, and a
+ * second small kernel turns them into probabilities.  Workspace: skv_gqa_decode_mass_workspace_bytes(). */
+size_t skv_gqa_decode_mass_workspace_bytes(int B, int N, int Hq, int Hkv, int D, int device);
+int skv_gqa_decode_mass(const void* q, const void* k, const void* v, void* out, float* mass,
+                        void* workspace, size_t workspace_bytes, int B, int N, int Hq, int Hkv, int D,
+                        long long kv_stride_b, long long kv_stride_n, long long kv_stride_h,
+                        const int* seq_lens, float scale, int device, void* stream);
+
 /* Same computation as skv_gqa_decode (fp16 KV) for callers that cannot allocate device memory:
  * a server that has already handed every free byte of HBM to its KV page pool, or a C / Go host
  * with no torch allocator to borrow a workspace from.  NO COUNTERPART IN THE REFERENCE (its

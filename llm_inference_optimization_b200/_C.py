@@ -30,7 +30,7 @@ def _kv_strides(K: Tensor, V: Tensor, what: str) -> tuple[int, int, int]:
 
 
 def fused_gqa(Q: Tensor, K: Tensor, V: Tensor, scale: float, *, seq_lens: Tensor | None = None,
-              out: Tensor | None = None) -> Tensor:
+              out: Tensor | None = None, mass: Tensor | None = None) -> Tensor:
     """Dense GQA decode attention; reference: ``launch_fused_gqa`` (csrc/kernels/gqa_decode.cu:218-290).
 
     Q ``[B, Hq, D]`` fp16, K/V ``[B, N, Hkv, D]`` fp16, returns ``[B, Hq, D]`` fp16 with
@@ -39,6 +39,8 @@ def fused_gqa(Q: Tensor, K: Tensor, V: Tensor, scale: float, *, seq_lens: Tensor
     dimension (for example ``cache.permute(0, 2, 1, 3)`` of a ``[B, Hkv, N, D]``
     cache), D may be 64 or 128, the launch goes to the current stream of Q's
     device, and ``seq_lens`` (int32 ``[B]``) bounds the tokens read per sequence.
+    ``mass`` (fp32 ``[B, Hkv, N]``, optional) receives, added in place, every token's attention probability
+    summed over the query heads of its kv-head: the running ``scores`` of ``fused_kv_evict``.
     """
     _require(Q.is_cuda and K.is_cuda and V.is_cuda, "Q/K/V must be CUDA tensors")
     _require(Q.dtype == torch.float16 and K.dtype == torch.float16 and V.dtype == torch.float16,
@@ -65,9 +67,18 @@ def fused_gqa(Q: Tensor, K: Tensor, V: Tensor, scale: float, *, seq_lens: Tensor
         _require(seq_lens.dtype == torch.int32 and seq_lens.shape == (B,) and seq_lens.device == Q.device
                  and seq_lens.is_contiguous(), "seq_lens must be a contiguous int32 [B] tensor on Q's device")
         lens_ptr = seq_lens.data_ptr()
+    stream = torch.cuda.current_stream(Q.device).cuda_stream
+    if mass is not None:
+        _require(mass.dtype == torch.float32 and mass.shape == (B, Hkv, N) and mass.is_contiguous()
+                 and mass.device == Q.device, "mass must be a contiguous fp32 [B,Hkv,N] tensor on Q's device")
+        ws = _workspace.get("gqa_mass", lib.skv_gqa_decode_mass_workspace_bytes(B, N, Hq, Hkv, D, dev), Q.device)
+        rc = lib.skv_gqa_decode_mass(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), mass.data_ptr(),
+                                     ws.data_ptr(), ws.numel(), B, N, Hq, Hkv, D, sb, sn, sh, lens_ptr, float(scale),
+                                     dev, stream)
+        _lib.check(rc, "fused_gqa")
+        return out
     nbytes = lib.skv_gqa_decode_workspace_bytes(B, N, Hq, Hkv, D, dev)
     ws = _workspace.get("gqa", nbytes, Q.device)
-    stream = torch.cuda.current_stream(Q.device).cuda_stream
     rc = lib.skv_gqa_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(),
                             B, N, Hq, Hkv, D, _lib.KV_F16, None, None, sb, sn, sh, lens_ptr, float(scale), dev, stream)
     _lib.check(rc, "fused_gqa")

@@ -46,6 +46,8 @@ struct Params {
     long long q_stride_b, q_stride_h, o_stride_b, o_stride_h;
     float scale_log2;    // softmax scale * log2(e)
     int early_kv;        // K/V and seq_lens are not produced by the previous kernel: stream them before it completes
+    float* score_out;    // optional [B, Hq, N] fp32: scaled scores in the exp2 domain, for the attention-mass pass
+    float* ml_final;     // optional [B, Hq, 2]: final softmax maximum and denominator per head
     KvMapPos pos;
 };
 
@@ -228,6 +230,25 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
                         if (tok0 + nt * 8 + tq * 2 + (j & 1) >= t_end) sc[nt][j] = -INFINITY;
             }
 
+            // ---- optional: keep the scores, so that a second pass can turn them into attention probabilities once
+            //      the softmax maximum and denominator of the whole sequence are known
+            if (p.score_out) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int t = tok0 + nt * 8 + tq * 2;
+                    if (g < G) {
+                        float* d0 = p.score_out + ((long long)b * p.Hq + h * G + g) * p.N + t;
+                        if (t < t_end) d0[0] = sc[nt][0];
+                        if (t + 1 < t_end) d0[1] = sc[nt][1];
+                    }
+                    if (g + 8 < G) {
+                        float* d1 = p.score_out + ((long long)b * p.Hq + h * G + g + 8) * p.N + t;
+                        if (t < t_end) d1[0] = sc[nt][2];
+                        if (t + 1 < t_end) d1[1] = sc[nt][3];
+                    }
+                }
+            }
+
             // ---- online softmax
             float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
             float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
@@ -320,7 +341,29 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     EpilogueArgs ea;
     ea.partial_o = p.partial_o; ea.partial_ml = p.partial_ml; ea.tickets = p.tickets; ea.out = p.out;
     ea.Hkv = p.Hkv; ea.G = G; ea.num_splits = p.num_splits; ea.o_stride_b = p.o_stride_b; ea.o_stride_h = p.o_stride_h;
+    ea.ml_final = p.ml_final;
     merge_and_combine<D>(ea, smem, last_flag, b, h, split, n_splits, 1.f);
+}
+
+// Attention mass of every cached token, summed over the query heads of its group and ADDED to `mass`:
+//   mass[b, hkv, t] += sum_g exp2(score[b, hkv*G+g, t] - M[b, hkv*G+g]) / L[b, hkv*G+g]
+// -- the running importance score an eviction policy keeps per token (the `scores` argument of the reference's
+// fused_kv_evict, sparse_kv/eviction.py:12-22, which the reference leaves to the caller to produce).
+// grid (ceil(N / 256), Hkv, B)
+__global__ void __launch_bounds__(256)
+attention_mass_kernel(const float* __restrict__ score, const float* __restrict__ ml, float* __restrict__ mass,
+                      const int* __restrict__ seq_lens, int N, int Hq, int Hkv, int G) {
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int t = blockIdx.x * 256 + threadIdx.x;
+    const int len = seq_lens ? min(max(seq_lens[b], 0), N) : N;
+    if (t >= len) return;
+    float acc = 0.f;
+    for (int g = 0; g < G; ++g) {
+        const long long hq = (long long)b * Hq + h * G + g;
+        const float M = ml[hq * 2], L = ml[hq * 2 + 1];
+        if (L > 0.f) acc += fast_exp2(score[hq * N + t] - M) / L;
+    }
+    mass[((long long)b * Hkv + h) * N + t] += acc;
 }
 
 // ---------------------------------------------------------------------------
@@ -379,10 +422,16 @@ int skv_gqa_decode_splits(int B, int N, int Hq, int Hkv, int D, int device) {
     return gqa::make_plan(B, N, Hq, Hkv, D, device).splits;
 }
 
-int skv_gqa_decode(const void* q, const void* k, const void* v, void* out, void* workspace, size_t workspace_bytes,
-                   int B, int N, int Hq, int Hkv, int D, int kv_dtype, const float* k_scale, const float* v_scale,
-                   long long kv_stride_b, long long kv_stride_n, long long kv_stride_h, const int* seq_lens,
-                   float scale, int device, void* stream) {
+// Shared by skv_gqa_decode and skv_gqa_decode_mass; `mass` (optional) adds the attention-mass pass, whose scratch
+// (scores [B,Hq,N] and final max/denominator [B,Hq,2], fp32) follows the decode plan in the workspace.
+static size_t mass_scratch_bytes(int B, int N, int Hq) {
+    return (((size_t)B * Hq * 2 * sizeof(float) + 255) & ~size_t(255)) + (size_t)B * Hq * N * sizeof(float);
+}
+
+static int decode_f16_impl(const void* q, const void* k, const void* v, void* out, float* mass, void* workspace,
+                           size_t workspace_bytes, int B, int N, int Hq, int Hkv, int D, int kv_dtype,
+                           long long kv_stride_b, long long kv_stride_n, long long kv_stride_h, const int* seq_lens,
+                           float scale, int device, void* stream) {
     if (!q || !k || !v || !out) return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode: null tensor pointer");
     if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0) return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode: sizes must be positive");
     if (Hq % Hkv != 0) return fail(SKV_ERR_BAD_ARG, "Hq=%d must be divisible by Hkv=%d", Hq, Hkv);
@@ -391,15 +440,17 @@ int skv_gqa_decode(const void* q, const void* k, const void* v, void* out, void*
     if (D != 128 && D != 64) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (64 or 128)", D);
     if (!(scale > 0.f)) return fail(SKV_ERR_BAD_ARG, "softmax scale must be positive");
     if (kv_dtype != SKV_KV_F16) return fail(SKV_ERR_UNSUPPORTED, "kv_dtype %d not supported by this entry point", kv_dtype);
-    (void)k_scale; (void)v_scale;
     if (Hkv > 65535 || B > 65535) return fail(SKV_ERR_UNSUPPORTED, "grid dimension too large");
 
     DeviceGuard guard(device);
     if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
 
     gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device, seq_lens != nullptr);
-    if (!workspace || workspace_bytes < pl.total)
-        return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, pl.total);
+    // the mass scratch sits behind the LARGER of the two split plans, so that its place does not depend on seq_lens
+    const size_t plan_max = skv_gqa_decode_workspace_bytes(B, N, Hq, Hkv, D, device);
+    const size_t need = mass ? plan_max + mass_scratch_bytes(B, N, Hq) : pl.total;
+    if (!workspace || workspace_bytes < need)
+        return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, need);
     if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(SKV_ERR_WORKSPACE, "workspace must be 256-byte aligned");
 
     CUtensorMap tmK, tmV;
@@ -427,9 +478,41 @@ int skv_gqa_decode(const void* q, const void* k, const void* v, void* out, void*
     p.o_stride_b = (long long)Hq * D; p.o_stride_h = D;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.pos = pos;
+    p.ml_final = mass ? reinterpret_cast<float*>(ws + plan_max) : nullptr;
+    p.score_out = mass ? reinterpret_cast<float*>(ws + plan_max + (((size_t)B * Hq * 2 * sizeof(float) + 255) & ~size_t(255))) : nullptr;
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return D == 128 ? gqa::launch_f16<128>(tmK, tmV, p, B, st) : gqa::launch_f16<64>(tmK, tmV, p, B, st);
+    rc = D == 128 ? gqa::launch_f16<128>(tmK, tmV, p, B, st) : gqa::launch_f16<64>(tmK, tmV, p, B, st);
+    if (rc || !mass) return rc;
+    dim3 grid((N + 255) / 256, Hkv, B);
+    gqa::attention_mass_kernel<<<grid, 256, 0, st>>>(p.score_out, p.ml_final, mass, seq_lens, N, Hq, Hkv, G);
+    SKV_CUDA_TRY(cudaGetLastError());
+    return SKV_OK;
+}
+
+int skv_gqa_decode(const void* q, const void* k, const void* v, void* out, void* workspace, size_t workspace_bytes,
+                   int B, int N, int Hq, int Hkv, int D, int kv_dtype, const float* k_scale, const float* v_scale,
+                   long long kv_stride_b, long long kv_stride_n, long long kv_stride_h, const int* seq_lens,
+                   float scale, int device, void* stream) {
+    (void)k_scale; (void)v_scale;
+    return decode_f16_impl(q, k, v, out, nullptr, workspace, workspace_bytes, B, N, Hq, Hkv, D, kv_dtype, kv_stride_b,
+                           kv_stride_n, kv_stride_h, seq_lens, scale, device, stream);
+}
+
+// Dense decode that also accumulates every cached token's attention mass (summed over the query heads of its
+// kv-head) into `mass` fp32 [B, Hkv, N]: the importance scores an eviction policy feeds to skv_kv_evict_quant.
+size_t skv_gqa_decode_mass_workspace_bytes(int B, int N, int Hq, int Hkv, int D, int device) {
+    const size_t base = skv_gqa_decode_workspace_bytes(B, N, Hq, Hkv, D, device);
+    return base ? base + mass_scratch_bytes(B, N, Hq) : 0;
+}
+
+int skv_gqa_decode_mass(const void* q, const void* k, const void* v, void* out, float* mass, void* workspace,
+                        size_t workspace_bytes, int B, int N, int Hq, int Hkv, int D, long long kv_stride_b,
+                        long long kv_stride_n, long long kv_stride_h, const int* seq_lens, float scale, int device,
+                        void* stream) {
+    if (!mass) return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode_mass: null mass pointer");
+    return decode_f16_impl(q, k, v, out, mass, workspace, workspace_bytes, B, N, Hq, Hkv, D, SKV_KV_F16, kv_stride_b,
+                           kv_stride_n, kv_stride_h, seq_lens, scale, device, stream);
 }
 
 // ---------------------------------------------------------------------------

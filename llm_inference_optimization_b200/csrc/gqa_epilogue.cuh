@@ -111,6 +111,7 @@ struct EpilogueArgs {
     int Hkv, G, num_splits;
     long long o_stride_b, o_stride_h;
     bool out_bf16 = false;   // store bf16 instead of fp16 (same element size and strides)
+    float* ml_final = nullptr;  // optional [B, Hkv * G, 2]: softmax maximum (exp2 domain) and denominator of every head
 };
 
 __device__ __forceinline__ uint16_t out_bits(float x, bool bf16) {
@@ -148,6 +149,10 @@ __device__ __forceinline__ void merge_and_combine(const EpilogueArgs& p, uint8_t
         }
         O *= out_scale;
         if (n_splits == 1) {
+            if (p.ml_final && d == 0) {
+                p.ml_final[(bh * G + r) * 2] = M;
+                p.ml_final[(bh * G + r) * 2 + 1] = L;
+            }
             const float inv = L > 0.f ? 1.f / L : 0.f;
             reinterpret_cast<uint16_t*>(p.out)[(long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + d] =
                 out_bits(O * inv, p.out_bf16);
@@ -188,6 +193,10 @@ __device__ __forceinline__ void merge_and_combine(const EpilogueArgs& p, uint8_t
             wrow[s] = w;
         }
         Ls = warp_sum(Ls);
+        if (p.ml_final && lane == 0) {
+            p.ml_final[(bh * G + r) * 2] = mx;
+            p.ml_final[(bh * G + r) * 2 + 1] = Ls;
+        }
         __syncwarp();
         if (lane < D / 4) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);

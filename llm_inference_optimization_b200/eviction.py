@@ -81,3 +81,32 @@ def fused_kv_evict(K_cache: Tensor, V_cache: Tensor, attn_scores: Tensor, top_k:
     if return_aux:
         return EvictionResult(Ko, Vo, ks, vs, idx)
     return Ko, Vo
+
+
+class AttentionMassPolicy:
+    """Eviction policy loop: accumulate every token's attention mass while decoding, evict on demand.
+
+    ``decode(Q, K, V, scale)`` is ``fused_gqa`` with the mass output switched on: each call adds, per cached
+    token, the attention probability summed over the query heads of its kv-head into ``self.mass``
+    (``[B, Hkv, N]`` fp32).  ``evict(K, V, budget, ...)`` hands that running score to ``fused_kv_evict`` -- the
+    argument the reference leaves to its caller to produce (sparse_kv/eviction.py:12-22) -- and clears it.
+    K and V use the decode layout ``[B, N, Hkv, D]``; the eviction call sees them as ``[B, Hkv, N, D]`` views.
+    """
+
+    def __init__(self, batch: int, kv_heads: int, max_tokens: int, device):
+        self.mass = torch.zeros((batch, kv_heads, max_tokens), dtype=torch.float32, device=device)
+        self.steps = 0
+
+    def decode(self, Q: Tensor, K: Tensor, V: Tensor, scale: float, *, seq_lens: Tensor | None = None) -> Tensor:
+        _C._require(K.shape[1] == self.mass.shape[2], "the cache length must equal the accumulator's max_tokens")
+        out = _C.fused_gqa(Q, K, V, scale, seq_lens=seq_lens, mass=self.mass)
+        self.steps += 1
+        return out
+
+    def evict(self, K: Tensor, V: Tensor, budget: int, *, recent_tokens: int = 0, quant: str = "int8", **kw):
+        """``fused_kv_evict`` on the accumulated mass; returns its result and resets the accumulator."""
+        res = fused_kv_evict(K.permute(0, 2, 1, 3), V.permute(0, 2, 1, 3), self.mass, budget,
+                             recent_tokens=recent_tokens, quant=quant, **kw)
+        self.mass.zero_()
+        self.steps = 0
+        return res

@@ -50,6 +50,26 @@ def dense_gqa_decode(Q: Tensor, K: Tensor, V: Tensor, scale: float, seq_lens: Te
     return torch.matmul(p, v).reshape(B, Hq, D)
 
 
+def attention_mass(Q: Tensor, K: Tensor, scale: float, seq_lens: Tensor | None = None) -> Tensor:
+    """Attention probability of every cached token, summed over the query heads of its kv-head: ``[B,Hkv,N]`` fp32.
+
+    The per-token importance an eviction policy accumulates over decode steps; it is what the reference's
+    ``fused_kv_evict`` expects as ``scores`` (sparse_kv/eviction.py:12-22; the reference has no code that
+    produces it).  Tokens past ``seq_lens`` get zero.
+    """
+    B, Hq, D = Q.shape
+    N, Hkv = K.shape[1], K.shape[2]
+    G = Hq // Hkv
+    q = Q.float().reshape(B, Hkv, G, D)
+    k = K.float().permute(0, 2, 1, 3)
+    s = torch.matmul(q, k.transpose(-1, -2)) * float(scale)
+    if seq_lens is not None:
+        pos = torch.arange(N).view(1, 1, 1, N)
+        s = s.masked_fill(pos >= seq_lens.view(B, 1, 1, 1).long(), float("-inf"))
+    p = torch.nan_to_num(torch.softmax(s, dim=-1), nan=0.0)
+    return p.sum(dim=2)
+
+
 def combine_split_partials(m: Tensor, l: Tensor, o: Tensor) -> Tensor:
     """Log-sum-exp merge of per-split partial results (no reference counterpart).
 
