@@ -139,7 +139,8 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool,
  * :302-303) and its RoPE call (:152-160).  qkv: [B, (Hq + 2 Hkv) * D] fp16 or bf16 (q heads, k heads, v heads);
  * q_out: [B, Hq, D] fp16 = rotate-half RoPE(q) at position seq_lens[b]; RoPE(k) and v are quantised per row
  * (scale = amax/448 for SKV_KV_E4M3, amax/127 for SKV_KV_I8; 1.0 for a zero row) and stored at token position
- * seq_lens[b] of sequence b in the paged pools (layout as for skv_gqa_decode_paged).  seq_lens is not modified.
+ * seq_lens[b] of sequence b in the paged pools (layout as for skv_gqa_decode_paged).  seq_lens is not modified; a
+ * sequence whose position lies past its max_pages * page_size slots stores nothing.
  * meta (optional, else NULL): the fp16 [B,Hkv,meta_num_blocks,2,D] metadata of skv_quest_build_meta, whose block
  * containing the new token is updated with the dequantised new key (re-initialised when the token opens a block).
  * D = 128. */

@@ -96,6 +96,7 @@ rope_quant_append_kernel(const Params p) {
             code[i] = (uint32_t)max(-127, min(127, __float2int_rn(y))) & 0xFFu;
     }
     const int lp = pos / p.page_size, slot = pos - lp * p.page_size;
+    if (pos < 0 || lp >= p.max_pages) return;   // no room left in this sequence's page list: nothing is stored
     const int page = p.page_table ? p.page_table[(long long)b * p.max_pages + lp] : b * p.max_pages + lp;
     uint8_t* row = (is_v ? p.v_codes : p.k_codes) + page * p.sp + h * p.sh + slot * p.ss;
     *reinterpret_cast<uint16_t*>(row + lane * 2) = (uint16_t)(code[0] | (code[1] << 8));
