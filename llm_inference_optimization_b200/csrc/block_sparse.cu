@@ -36,6 +36,7 @@ struct ScoreParams {
 template <int D>
 __global__ void __launch_bounds__(SCORE_THREADS)
 block_mean_scores_kernel(const ScoreParams p, int blocks_per_cta) {
+    pdl_launch_dependents();  // the kernel that consumes these results may be scheduled now; it waits for this grid to finish
     constexpr int LPR = D / 8;
     constexpr int RPW = 32 / LPR;
     constexpr int U = 16;  // independent 16-byte loads in flight per lane
@@ -88,6 +89,7 @@ struct AttendParams {
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS)
 block_select_attend_kernel(const AttendParams p) {
+    pdl_wait_prior_grids();   // launched as a programmatic dependent of the scoring kernel: its results are complete from here on
     constexpr int LPR = D / 8;
     constexpr int GROUPS = ATT_THREADS / LPR;
     extern __shared__ uint32_t dsm[];
@@ -193,7 +195,7 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     dim3 g1((sp.nb + blocks_per_cta - 1) / blocks_per_cta, sp.H, B);
     block_mean_scores_kernel<D><<<g1, SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);
     SKV_CUDA_TRY(cudaGetLastError());
-    block_select_attend_kernel<D><<<(unsigned)rows, ATT_THREADS, smem, st>>>(ap);
+    SKV_CUDA_TRY(launch_pdl(block_select_attend_kernel<D>, dim3((unsigned)rows), dim3(ATT_THREADS), smem, st, ap));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }

@@ -47,6 +47,7 @@ struct SelectParams {
 
 __global__ void __launch_bounds__(SEL_THREADS)
 evict_select_kernel(const SelectParams p) {
+    pdl_launch_dependents();  // the kernel that consumes the kept positions may be scheduled now; it waits for this grid to finish
     extern __shared__ uint32_t dsm[];
     uint32_t* tk = dsm;
     int* sel = reinterpret_cast<int*>(tk + TopkSmem<SEL_THREADS>::WORDS);  // [pow2 >= keep]
@@ -109,6 +110,7 @@ constexpr int KR = 8;   // keys per thread
 
 __global__ void __cluster_dims__(CL, 1, 1) __launch_bounds__(SEL_THREADS)
 evict_select_cluster_kernel(const SelectParams p) {
+    pdl_launch_dependents();  // the kernel that consumes the kept positions may be scheduled now; it waits for this grid to finish
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     constexpr int NW = SEL_THREADS / 32;
@@ -367,6 +369,7 @@ __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, ui
 template <int D, int MODE>
 __global__ void __launch_bounds__(GQ_THREADS)
 evict_gather_quant_kernel(const GatherParams p) {
+    pdl_wait_prior_grids();   // launched as a programmatic dependent of the selection kernel: its results are complete from here on
     constexpr int LPR = D / 8;
     constexpr int GPB = GQ_THREADS / LPR;
     constexpr int U = 4;
@@ -437,10 +440,10 @@ static int launch_gather(const GatherParams& gp, int mode, int device, cudaStrea
     const long long cap = (long long)sm_count(device) * SKV_GATHER_CAP;
     if (blocks > cap) blocks = cap;
     switch (mode) {
-        case SKV_QUANT_NONE: evict_gather_quant_kernel<D, SKV_QUANT_NONE><<<(unsigned)blocks, GQ_THREADS, 0, st>>>(gp); break;
-        case SKV_QUANT_INT8: evict_gather_quant_kernel<D, SKV_QUANT_INT8><<<(unsigned)blocks, GQ_THREADS, 0, st>>>(gp); break;
-        case SKV_QUANT_E4M3: evict_gather_quant_kernel<D, SKV_QUANT_E4M3><<<(unsigned)blocks, GQ_THREADS, 0, st>>>(gp); break;
-        default: evict_gather_quant_kernel<D, SKV_QUANT_CAST><<<(unsigned)blocks, GQ_THREADS, 0, st>>>(gp); break;
+        case SKV_QUANT_NONE: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_NONE>, dim3((unsigned)blocks), dim3(GQ_THREADS), 0, st, gp)); break;
+        case SKV_QUANT_INT8: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_INT8>, dim3((unsigned)blocks), dim3(GQ_THREADS), 0, st, gp)); break;
+        case SKV_QUANT_E4M3: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_E4M3>, dim3((unsigned)blocks), dim3(GQ_THREADS), 0, st, gp)); break;
+        default: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_CAST>, dim3((unsigned)blocks), dim3(GQ_THREADS), 0, st, gp)); break;
     }
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;

@@ -27,7 +27,6 @@ namespace skv {
 namespace quest {
 
 constexpr int D = 128;
-constexpr int CH = 16;            // tokens per page chunk handled at a time
 constexpr int META_THREADS = 256;
 constexpr int SCORE_THREADS = 256;
 constexpr int ATT_THREADS = 256;
@@ -69,7 +68,29 @@ __device__ __forceinline__ int phys_page(const int* page_table, int b, int max_p
     return page_table ? __ldg(page_table + (long long)b * max_pages + lp) : b * max_pages + lp;
 }
 
-// one warp per (b, h, block); lanes: 8 per token row (16 codes each), 4 rows per step
+// Four codes of one 32-bit word as floats.
+template <int KVT>
+__device__ __forceinline__ void word_to_floats(uint32_t w, float (&f)[4]) {
+    if (KVT == SKV_KV_E4M3) {
+        uint32_t h0, h1;
+        asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\t"
+            "cvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+            : "=r"(h0), "=r"(h1)
+            : "r"(w));
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h0));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h1));
+        f[0] = f0.x; f[1] = f0.y; f[2] = f1.x; f[3] = f1.y;
+    } else {
+        // int8 b -> float: the bits 0x4B000000 | (b ^ 0x80) are 2^23 + b + 128 exactly
+        const uint32_t x = w ^ 0x80808080u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540u + i)) - 8388736.f;
+    }
+}
+
+// one warp per (b, h, block); lanes: 8 per token row (16 codes each), 4 rows per step.  The dequantised value
+// code * scale is formed in fp32 and rounded to fp16 BEFORE the comparisons (rounding is monotone, so the minimum
+// of the rounded values is the rounded minimum): minima and maxima then run two channels per instruction.
 template <int KVT>
 __global__ void __launch_bounds__(META_THREADS)
 block_meta_build_kernel(const MetaParams p) {
@@ -83,9 +104,12 @@ block_meta_build_kernel(const MetaParams p) {
         const int b = (int)(item / ((long long)p.nb * p.Hkv));
         const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
         const int t0 = blk * p.block_size, t1 = min(len, t0 + p.block_size);
-        float lo[16], hi[16];
+        __half2 lo[8], hi[8];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) { lo[i] = INFINITY; hi[i] = -INFINITY; }
+        for (int i = 0; i < 8; ++i) {
+            lo[i] = __float2half2_rn(INFINITY);
+            hi[i] = __float2half2_rn(-INFINITY);
+        }
         constexpr int RU = 4;  // rows per lane group and step: page ids, then codes and scales, all issued together
         for (int tb = t0 + rw; tb < t1; tb += 4 * RU) {
             // Rows past the block's end are clamped to its last row: a repeated row changes no minimum or maximum,
@@ -107,28 +131,36 @@ block_meta_build_kernel(const MetaParams p) {
             }
 #pragma unroll
             for (int u = 0; u < RU; ++u) {
-                float x[16];
-                unpack16<KVT>(raw[u], x);
+                const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float v = x[i] * sc[u];
-                    lo[i] = fminf(lo[i], v);
-                    hi[i] = fmaxf(hi[i], v);
+                for (int j = 0; j < 4; ++j) {
+                    float f[4];
+                    word_to_floats<KVT>(w[j], f);
+                    const __half2 v0 = __floats2half2_rn(f[0] * sc[u], f[1] * sc[u]);
+                    const __half2 v1 = __floats2half2_rn(f[2] * sc[u], f[3] * sc[u]);
+                    lo[2 * j] = __hmin2(lo[2 * j], v0);
+                    hi[2 * j] = __hmax2(hi[2 * j], v0);
+                    lo[2 * j + 1] = __hmin2(lo[2 * j + 1], v1);
+                    hi[2 * j + 1] = __hmax2(hi[2 * j + 1], v1);
                 }
             }
         }
+        uint32_t wlo[8], whi[8];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            lo[i] = fminf(lo[i], __shfl_xor_sync(0xffffffffu, lo[i], 8));
-            hi[i] = fmaxf(hi[i], __shfl_xor_sync(0xffffffffu, hi[i], 8));
-            lo[i] = fminf(lo[i], __shfl_xor_sync(0xffffffffu, lo[i], 16));
-            hi[i] = fmaxf(hi[i], __shfl_xor_sync(0xffffffffu, hi[i], 16));
+        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+            for (int o = 8; o <= 16; o <<= 1) {
+                const uint32_t a = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<uint32_t*>(&lo[i]), o);
+                const uint32_t c = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<uint32_t*>(&hi[i]), o);
+                lo[i] = __hmin2(lo[i], *reinterpret_cast<const __half2*>(&a));
+                hi[i] = __hmax2(hi[i], *reinterpret_cast<const __half2*>(&c));
+            }
+            wlo[i] = *reinterpret_cast<uint32_t*>(&lo[i]);
+            whi[i] = *reinterpret_cast<uint32_t*>(&hi[i]);
         }
         if (rw < 2) {  // row-group 0 writes the mins, row-group 1 the maxes
             __half* dst = p.meta + (item * 2 + rw) * D + sub * 16;
-            uint32_t w[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) w[i] = rw == 0 ? pack_half2(lo[2 * i], lo[2 * i + 1]) : pack_half2(hi[2 * i], hi[2 * i + 1]);
+            const uint32_t* w = rw == 0 ? wlo : whi;
             *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
             *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
         }
@@ -149,6 +181,7 @@ struct ScoreParams {
 template <int MAXG>
 __global__ void __launch_bounds__(SCORE_THREADS)
 quest_scores_kernel(const ScoreParams p, int blocks_per_cta) {
+    pdl_launch_dependents();  // the kernel that consumes these results may be scheduled now; it waits for this grid to finish
     static_assert(MAXG == 4 || MAXG == 8, "the packed reduction below is written for 4 or 8 heads");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane & 15, rw = lane >> 4;
@@ -245,6 +278,7 @@ struct AttendParams {
 template <int KVT>
 __global__ void __launch_bounds__(ATT_THREADS)
 quest_select_attend_kernel(const AttendParams p) {
+    pdl_wait_prior_grids();   // launched as a programmatic dependent of the scoring kernel: its results are complete from here on
     __shared__ uint32_t tk[TopkSmem<ATT_THREADS>::WORDS];
     __shared__ int sel[MAX_TOPK];
     __shared__ float w[MAX_SEL_TOKENS];
@@ -478,7 +512,10 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
     sp.scores = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
     sp.Hq = Hq; sp.Hkv = Hkv; sp.G = G; sp.nb = nb; sp.scale = scale;
     const long long rows = (long long)B * Hkv;
-    long long want = ((long long)sm_count(device) * 8 + rows - 1) / rows;
+#ifndef SKV_QUEST_SCORE_CTAS_PER_SM
+#define SKV_QUEST_SCORE_CTAS_PER_SM 4
+#endif
+    long long want = ((long long)sm_count(device) * SKV_QUEST_SCORE_CTAS_PER_SM + rows - 1) / rows;
     int blocks_per_cta = (int)((nb + want - 1) / want);
     blocks_per_cta = ((blocks_per_cta + 63) / 64) * 64;  // one CTA step covers 8 warps x 2 half-warps x 4 blocks
     dim3 g1((nb + blocks_per_cta - 1) / blocks_per_cta, Hkv, B);
@@ -496,8 +533,8 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
     ap.out = static_cast<__half*>(out); ap.block_idx = block_idx_out;
     ap.Hq = Hq; ap.G = G; ap.N = N; ap.nb = nb; ap.block_size = block_size; ap.page_size = page_size;
     ap.max_pages = max_pages; ap.top_k = top_k_blocks; ap.scale = scale;
-    if (kv_dtype == SKV_KV_E4M3) quest::quest_select_attend_kernel<SKV_KV_E4M3><<<(unsigned)(B * Hq), quest::ATT_THREADS, 0, st>>>(ap);
-    else quest::quest_select_attend_kernel<SKV_KV_I8><<<(unsigned)(B * Hq), quest::ATT_THREADS, 0, st>>>(ap);
+    if (kv_dtype == SKV_KV_E4M3) SKV_CUDA_TRY(launch_pdl(quest::quest_select_attend_kernel<SKV_KV_E4M3>, dim3((unsigned)(B * Hq)), dim3(quest::ATT_THREADS), 0, st, ap));
+    else SKV_CUDA_TRY(launch_pdl(quest::quest_select_attend_kernel<SKV_KV_I8>, dim3((unsigned)(B * Hq)), dim3(quest::ATT_THREADS), 0, st, ap));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }

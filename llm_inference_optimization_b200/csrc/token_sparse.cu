@@ -45,6 +45,7 @@ struct ScoreParams {
 template <int D>
 __global__ void __launch_bounds__(SCORE_THREADS)
 token_scores_kernel(const ScoreParams p, int tokens_per_cta) {
+    pdl_launch_dependents();  // the kernel that consumes these results may be scheduled now; it waits for this grid to finish
     constexpr int LPR = D / 8;      // lanes per key row
     constexpr int RPW = 32 / LPR;   // rows per warp-wide load
     constexpr int SUB = 32 / RPW;   // loads per 32 tokens
@@ -127,6 +128,7 @@ struct AttendParams {
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS)
 token_select_attend_kernel(const AttendParams p) {
+    pdl_wait_prior_grids();   // launched as a programmatic dependent of the scoring kernel: its results are complete from here on
     constexpr int LPR = D / 8;
     constexpr int GROUPS = ATT_THREADS / LPR;  // value rows gathered in parallel
     extern __shared__ uint32_t dsm[];
@@ -288,7 +290,7 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     }
     token_scores_kernel<D><<<g1, SCORE_THREADS, smem1, st>>>(sp2, tokens_per_cta);
     SKV_CUDA_TRY(cudaGetLastError());
-    token_select_attend_kernel<D><<<(unsigned)rows, ATT_THREADS, smem, st>>>(ap2);
+    SKV_CUDA_TRY(launch_pdl(token_select_attend_kernel<D>, dim3((unsigned)rows), dim3(ATT_THREADS), smem, st, ap2));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }
