@@ -242,6 +242,19 @@ int skv_residual_rmsnorm(const void* delta, void* resid, const void* weight, voi
                          int is_bf16, int device, void* stream);
 int skv_silu_mul(const void* gate_up, void* out, int rows, int inter, int is_bf16, int device, void* stream);
 
+/* ---- tensor-parallel decode step: all-reduce + residual add + RMSNorm in one kernel over peer memory ----
+ * No reference counterpart (the reference is single-GPU).  Every rank passes the same arrays, indexed by rank:
+ * peer_partials[r] = device address, valid on THIS GPU, of rank r's [rows, hidden] partial sum (peer-mapped /
+ * symmetric memory); peer_flags[r] = rank r's flag array of 8 uint32 (zero before the first call, written by
+ * peers).  sync_words: 4 zero-initialised uint32 in this rank's own memory ([0] epoch, [1] ticket, [2] status).
+ * The kernel tells the peers that this rank's partial is complete, waits (at most max_spins polls per peer, then
+ * status |= 1 (SKV_DEV_TIMEOUT) and nothing is stored) until every peer has said the same, and computes
+ *   resid <- round(resid + round(sum_r partial_r)),  out <- round(resid * rsqrt(mean(resid^2) + eps) * weight).
+ * Consecutive calls must alternate between two partial buffers.  world in {1,2,4,8}; fp16 or bf16. */
+int skv_allreduce_residual_rmsnorm(const void* const* peer_partials, void* const* peer_flags, void* sync_words,
+                                   void* resid, const void* weight, void* out, int rows, int hidden, float eps,
+                                   int is_bf16, int rank, int world, unsigned max_spins, int device, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

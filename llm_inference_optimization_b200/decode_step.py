@@ -117,6 +117,7 @@ class DecodeModel:
         # the fused RoPE + quantise + append kernel needs fp16/bf16 activations on a CUDA device
         self.fused_glue = (self.device.type == "cuda" and dtype in (torch.float16, torch.bfloat16)
                            and attention is kernel_attention)
+        self.fused_allreduce = False   # see enable_fused_allreduce
         D, hid = cfg.D, cfg.hidden
         qs = slice(shard.q_heads.start * D, shard.q_heads.stop * D)
         ks = slice(shard.kv_heads.start * D, shard.kv_heads.stop * D)
@@ -194,6 +195,39 @@ class DecodeModel:
             dist.all_reduce(x, op=dist.ReduceOp.SUM, group=self.group)
         return x
 
+    def _step_fused_allreduce(self, x: Tensor, pos: Tensor, new_lens: Tensor, scale: float) -> Tensor:
+        """The layer loop with both all-reduces fused into the RMSNorm kernels that follow them (no NCCL call).
+
+        o_proj writes its partial into buffer 0 and down_proj into buffer 1 of ``self.arn``; the kernel that
+        normalises for the next GEMM sums the peers' partials over NVLink first.
+        """
+        from . import _C, glue
+        cfg, sh, arn = self.cfg, self.shard, self.arn
+        D, B = cfg.D, x.shape[0]
+        h = glue.residual_rmsnorm(x, None, self.layers[0]["n1"], cfg.rms_eps)
+        for li, (w, cache) in enumerate(zip(self.layers, self.caches)):
+            qkv = h @ w["wqkv"]
+            kvv = paged.PagedKV(cache.k, cache.v, cache.ks, cache.vs, self.page_table, pos, B)
+            q = paged.rope_quant_append(qkv, kvv, sh.n_q, cfg.rope_theta)
+            a = torch.empty((B, sh.n_q, D), dtype=x.dtype, device=x.device)
+            _C.fused_gqa_paged(q, cache.k, cache.v, cache.ks, cache.vs, self.page_table, new_lens, scale,
+                               max_seq_len=self.max_seq_len, out=a)
+            torch.matmul(a.view(B, sh.n_q * D), w["wo"], out=arn.partial(0))
+            h = arn.reduce_norm(0, x, w["n2"], cfg.rms_eps)
+            torch.matmul(glue.silu_mul(h @ w["wgu"]), w["wd"], out=arn.partial(1))
+            nxt = self.layers[li + 1]["n1"] if li + 1 < len(self.layers) else self.final_norm
+            h = arn.reduce_norm(1, x, nxt, cfg.rms_eps)
+        self.seq_lens.add_(1)
+        return h @ self.lm_head
+
+    def enable_fused_allreduce(self, batch: int) -> None:
+        """Replace the two NCCL all-reduces per layer by the fused peer-memory kernel (CUDA, world > 1, fixed batch)."""
+        from . import glue
+        if not self.fused_glue or self.shard.world == 1:
+            raise RuntimeError("the fused all-reduce needs the CUDA glue path and more than one rank")
+        self.arn = glue.AllReduceNorm(batch, self.cfg.hidden, self.dtype, self.device, self.group)
+        self.fused_allreduce = True
+
     def step(self, tokens: Tensor) -> Tensor:
         """Decode one token per sequence: ``tokens [B]`` int64 -> logits ``[B, vocab]``; advances ``seq_lens``."""
         cfg, sh = self.cfg, self.shard
@@ -208,6 +242,8 @@ class DecodeModel:
             # o_proj GEMM, residual+RMSNorm, gate/up GEMM, SiLU*up, down GEMM -- four of our launches and four GEMMs.
             # The residual stream x is updated in place; `delta` is the MLP output still to be added to it.
             from . import _C, glue
+            if self.fused_allreduce:
+                return self._step_fused_allreduce(x, pos, new_lens, scale)
             delta = None
             for w, cache in zip(self.layers, self.caches):
                 h = glue.residual_rmsnorm(x, delta, w["n1"], cfg.rms_eps)

@@ -52,3 +52,74 @@ def silu_mul(gate_up: Tensor, out: Tensor | None = None) -> Tensor:
                                   _C._dev_index(gate_up), torch.cuda.current_stream(gate_up.device).cuda_stream)
     _lib.check(rc, "silu_mul")
     return out
+
+
+class AllReduceNorm:
+    """Sum all-reduce over the GPUs of one node fused with the residual add and RMSNorm that consume it.
+
+    Each rank's GEMM writes its partial ``[rows, hidden]`` result into ``partial(i)`` (``i`` alternates 0, 1
+    between consecutive calls), a buffer in symmetric memory that every peer can read; ``reduce_norm(i, ...)``
+    is then ONE kernel (``skv_allreduce_residual_rmsnorm``) that signals the peers, waits for them with a bounded
+    spin, sums the partials over NVLink in rank order, adds the residual stream in place and returns the
+    normalised rows.  No library collective runs; a wait that runs out is reported by :meth:`status`.
+    ``peers`` (tests only) replaces the symmetric-memory rendezvous by explicit ``(partial, flags)`` tensors.
+    """
+
+    FLAG_WORDS = 8
+
+    def __init__(self, rows: int, hidden: int, dtype: torch.dtype, device, group=None, *, max_spins: int = 1 << 24,
+                 peers=None, rank: int | None = None):
+        import ctypes
+
+        _C._require(dtype in (torch.float16, torch.bfloat16), "dtype must be fp16 or bf16")
+        self.rows, self.hidden, self.dtype, self.device = rows, hidden, dtype, torch.device(device)
+        self.max_spins = int(max_spins)
+        part_bytes = (rows * hidden * 2 + 255) // 256 * 256
+        self.sync = torch.zeros(4, dtype=torch.int32, device=self.device)
+        if peers is None:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm
+
+            group = group if group is not None else dist.group.WORLD
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+            self._buf = symm.empty(2 * part_bytes + 256, dtype=torch.uint8, device=self.device)
+            self._buf.zero_()
+            torch.cuda.synchronize(self.device)
+            handle = symm.rendezvous(self._buf, group)
+            dist.barrier(group)                      # every rank's flags are zero before anybody signals
+            bases = [int(p) for p in handle.buffer_ptrs]
+            self._partials = [self._buf[i * part_bytes:i * part_bytes + rows * hidden * 2].view(dtype).view(rows, hidden)
+                              for i in range(2)]
+            part_ptrs = [[b + i * part_bytes for b in bases] for i in range(2)]
+            flag_ptrs = [b + 2 * part_bytes for b in bases]
+        else:
+            self.world, self.rank = len(peers[0]), int(rank or 0)
+            self._keep = peers
+            self._partials = [peers[i][self.rank][0] for i in range(2)]
+            part_ptrs = [[p[0].data_ptr() for p in peers[i]] for i in range(2)]
+            flag_ptrs = [p[1].data_ptr() for p in peers[0]]
+        arr = ctypes.c_void_p * self.world
+        self._part_arr = [arr(*ptrs) for ptrs in part_ptrs]
+        self._flag_arr = arr(*flag_ptrs)
+
+    def partial(self, i: int) -> Tensor:
+        """This rank's partial-sum buffer ``i`` (0 or 1): pass it as ``out=`` of the GEMM that produces the partial."""
+        return self._partials[i]
+
+    def reduce_norm(self, i: int, resid: Tensor, weight: Tensor, eps: float, out: Tensor | None = None) -> Tensor:
+        _check_2d(resid, "resid")
+        _C._require(resid.shape == (self.rows, self.hidden) and resid.dtype == self.dtype, "resid must match the buffers")
+        _C._require(weight.shape == (self.hidden,) and weight.dtype == self.dtype and weight.is_contiguous(),
+                    "weight must be a contiguous [hidden] vector of the buffers' dtype")
+        if out is None:
+            out = torch.empty_like(resid)
+        rc = _lib.load().skv_allreduce_residual_rmsnorm(
+            self._part_arr[i], self._flag_arr, self.sync.data_ptr(), resid.data_ptr(), weight.data_ptr(), out.data_ptr(),
+            self.rows, self.hidden, float(eps), int(self.dtype == torch.bfloat16), self.rank, self.world, self.max_spins,
+            _C._dev_index(resid), torch.cuda.current_stream(resid.device).cuda_stream)
+        _lib.check(rc, "allreduce_residual_rmsnorm")
+        return out
+
+    def status(self) -> int:
+        """Device status word (synchronises): 0, or 1 when a peer did not arrive within ``max_spins`` polls."""
+        return int(self.sync[2].item())
