@@ -248,7 +248,8 @@ int skv_silu_mul(const void* gate_up, void* out, int rows, int inter, int is_bf1
  * symmetric memory); peer_flags[r] = rank r's flag array of 8 uint32 (zero before the first call, written by
  * peers).  sync_words: 4 zero-initialised uint32 in this rank's own memory ([0] epoch, [1] ticket, [2] status).
  * The kernel tells the peers that this rank's partial is complete, waits (at most max_spins polls per peer, then
- * status |= 1 (SKV_DEV_TIMEOUT) and nothing is stored) until every peer has said the same, and computes
+ * status |= 1 (SKV_DEV_TIMEOUT) and nothing is stored; while the status word is non-zero later calls
+ * fail at once instead of waiting) until every peer has said the same, and computes
  *   resid <- round(resid + round(sum_r partial_r)),  out <- round(resid * rsqrt(mean(resid^2) + eps) * weight).
  * Consecutive calls must alternate between two partial buffers.  world in {1,2,4,8}; fp16 or bf16. */
 int skv_allreduce_residual_rmsnorm(const void* const* peer_partials, void* const* peer_flags, void* sync_words,

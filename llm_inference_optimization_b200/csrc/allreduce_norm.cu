@@ -10,7 +10,8 @@
 //   * the kernel's first CTA tells every peer "my partial of epoch e is complete" by storing e into slot [rank] of
 //     the peer's flag array (release, system scope) -- at kernel start the GEMM before it in the stream is done;
 //   * every CTA waits until all slots of its OWN flag array have reached e (acquire, system scope; BOUNDED: after
-//     max_spins polls the kernel records SKV_DEV_TIMEOUT in its status word and stores nothing);
+//     max_spins polls the kernel records SKV_DEV_TIMEOUT in its status word and stores nothing, and while the
+//     status word is set later calls fail at once instead of waiting again);
 //   * it then reads its row from all peers' partials, sums them in rank order in fp32 (so every rank gets the same
 //     bits), rounds to the storage type, adds the residual stream in place and writes the normalised row;
 //   * the epoch lives in device memory and is advanced by the last CTA, so a captured graph replays correctly.
@@ -91,11 +92,14 @@ allreduce_residual_rmsnorm_kernel(const Peers pp, uint32_t* sync, uint16_t* __re
         __threadfence_system();
         st_release_sys(pp.flags[tid] + rank, epoch);
     }
+    // Once a wait has run out the status word stays set and later calls do not wait again: a dead peer costs one
+    // bounded wait, not one per call.
+    const bool failed_before = *reinterpret_cast<volatile uint32_t*>(sync + 2) != 0u;
     bool arrived = true;
     if (tid < WORLD) {
         arrived = false;
         const uint32_t* slot = pp.flags[rank] + tid;
-        for (uint32_t i = 0; i < max_spins; ++i) {
+        for (uint32_t i = 0; i < (failed_before ? 0u : max_spins); ++i) {
             if ((int32_t)(ld_acquire_sys(slot) - epoch) >= 0) { arrived = true; break; }
             __nanosleep(64);
         }

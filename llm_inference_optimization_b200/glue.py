@@ -67,7 +67,7 @@ class AllReduceNorm:
 
     FLAG_WORDS = 8
 
-    def __init__(self, rows: int, hidden: int, dtype: torch.dtype, device, group=None, *, max_spins: int = 1 << 24,
+    def __init__(self, rows: int, hidden: int, dtype: torch.dtype, device, group=None, *, max_spins: int = 1 << 21,
                  peers=None, rank: int | None = None):
         import ctypes
 
