@@ -105,3 +105,25 @@ def test_rejects_bad_arguments(cuda_device):
         _C.fused_gqa(Qd, Kd, Vd[:, :64], scale)
     with pytest.raises(RuntimeError):
         _C.fused_gqa(Q, K, V, scale)  # CPU tensors
+
+
+@pytest.mark.parametrize("early", [0, 1])
+def test_back_to_back_launches_both_launch_orders(cuda_device, early):
+    """Eight launches over different static caches without a sync in between, in the default (fully ordered) mode
+    and with early K/V streaming switched on: every launch still returns its own cache's attention."""
+    from llm_inference_optimization_b200 import _lib
+    cases = [workloads.dense_gqa(6000 + 500 * i, seed=40 + i) for i in range(8)]
+    dev = [(Q.to(cuda_device), K.to(cuda_device), V.to(cuda_device), s) for Q, K, V, s in cases]
+    outs = [torch.empty_like(d[0]) for d in dev]
+    lib = _lib.load()
+    assert lib.skv_gqa_set_early_kv(early) == 0
+    try:
+        for _ in range(3):
+            for (Q, K, V, s), o in zip(dev, outs):
+                _C.fused_gqa(Q, K, V, s, out=o)
+        torch.cuda.synchronize()
+    finally:
+        lib.skv_gqa_set_early_kv(0)
+    assert _workspace.status(_workspace.get("gqa", 0, cuda_device)) == 0
+    for (Q, K, V, s), o in zip(cases, outs):
+        assert (o.float().cpu() - oracle.dense_gqa_decode(Q, K, V, s)).abs().max().item() <= 2e-3
