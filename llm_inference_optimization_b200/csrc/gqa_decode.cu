@@ -413,8 +413,13 @@ int skv_gqa_set_early_kv(int on) {
 size_t skv_gqa_decode_workspace_bytes(int B, int N, int Hq, int Hkv, int D, int device) {
     if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || D <= 0) return 0;
     // large enough for either split policy (with or without per-sequence lengths)
-    const size_t a = gqa::make_plan(B, N, Hq, Hkv, D, device, false).total, b = gqa::make_plan(B, N, Hq, Hkv, D, device, true).total;
-    return a > b ? a : b;
+    size_t best = 0;
+    for (int slots = 1; slots <= 2; ++slots)
+        for (int ragged = 0; ragged <= 1; ++ragged) {
+            const size_t t = gqa::make_plan(B, N, Hq, Hkv, D, device, ragged != 0, slots).total;
+            if (t > best) best = t;
+        }
+    return best;
 }
 
 int skv_gqa_decode_splits(int B, int N, int Hq, int Hkv, int D, int device) {

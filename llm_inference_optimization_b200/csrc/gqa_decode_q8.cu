@@ -57,9 +57,11 @@ constexpr int RECORD_BYTES = RECORD_ROWS * Q8_D;           // 4224
 // multiple of the group count so that a stage always belongs to the same group: a group that could reach a
 // stage two uses ahead of another group's wait would pass a parity wait meant for the use before.  Two groups
 // are enough (a third, tried with 123 registers per thread, brought no gain at 16 x 64K).
-__host__ __device__ constexpr int q8_groups(int /*nt*/) { return 2; }
+// A one-group variant (256 threads, <= 128 registers, 6 stages) fits two CTAs on an SM, so that one streams while
+// the other is in its prologue or epilogue.  It is used for FP8 caches when a launch has many CTAs per SM
+// (16 x 64K: 379 -> 350 us); the INT8 conversion costs the consumers more and keeps two groups per CTA.
 constexpr int Q8_PRODUCERS = 4;                            // producer warps: each issues one share of every stage
-__host__ __device__ constexpr int q8_threads(int nt) { return (q8_groups(nt) * CONSUMER_WARPS + Q8_PRODUCERS) * 32; }
+__host__ __device__ constexpr int q8_threads(int ng) { return (ng * CONSUMER_WARPS + Q8_PRODUCERS) * 32; }
 
 struct Q8Params {
     const __half* q;
@@ -84,10 +86,10 @@ struct Q8Params {
     PoolMapPos pos;
 };
 
-template <int NT>
+template <int NG>
 static size_t q8_smem_bytes(int stages) {
     size_t ring = (size_t)stages * Q8_STAGE_BYTES;
-    size_t merge = merge_smem_bytes<Q8_D, q8_groups(NT) * CONSUMER_WARPS>();
+    size_t merge = merge_smem_bytes<Q8_D, NG * CONSUMER_WARPS>();
     return 1024 + (ring > merge ? ring : merge) + 2 * stages * 8 + 16;
 }
 
@@ -119,12 +121,12 @@ __device__ __forceinline__ void pool_tile_load(uint32_t dst, const CUtensorMap* 
     tma_load_4d(dst, tm, bar, c[0], c[1], c[2], c[3], policy);
 }
 
-template <int KVT, int NT>
-__global__ void __launch_bounds__(q8_threads(NT), 1)
+template <int KVT, int NT, int NG>
+__global__ void __launch_bounds__(q8_threads(NG), NG == 1 ? 2 : 1)
 gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const Q8Params p) {
     constexpr int D = Q8_D;
-    constexpr int Q8_GROUPS = q8_groups(NT);
+    constexpr int Q8_GROUPS = NG;
     constexpr int Q8_WARPS = Q8_GROUPS * CONSUMER_WARPS;
     constexpr int Q8_CONSUMER_THREADS = Q8_WARPS * 32;
     constexpr int NCH = D / 16;  // 16-byte chunks per row = MMA k-steps of S = Q K^T
@@ -447,18 +449,18 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     merge_and_combine<D, Q8_WARPS>(ea, smem, last_flag, b, h, split, n_splits, 1.f / P_BOOST);
 }
 
-template <int KVT, int NT>
+template <int KVT, int NT, int NG>
 static int launch_q8(const CUtensorMap& tmK, const CUtensorMap& tmV, const Q8Params& p, int B, cudaStream_t stream) {
     static int configured_smem[64] = {0};
-    const size_t smem = q8_smem_bytes<NT>(p.stages);
+    const size_t smem = q8_smem_bytes<NG>(p.stages);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && configured_smem[dev] < (int)smem) {
-        SKV_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_q8_kernel<KVT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        SKV_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_q8_kernel<KVT, NT, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured_smem[dev] = (int)smem;
     }
     dim3 grid(p.Hkv, p.num_splits, B);
-    SKV_CUDA_TRY(launch_pdl(gqa_decode_q8_kernel<KVT, NT>, grid, dim3(q8_threads(NT)), smem, stream, tmK, tmV, p));
+    SKV_CUDA_TRY(launch_pdl(gqa_decode_q8_kernel<KVT, NT, NG>, grid, dim3(q8_threads(NG)), smem, stream, tmK, tmV, p));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }
@@ -504,7 +506,9 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     DeviceGuard guard(device);
     if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
 
-    gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device, seq_lens != nullptr);
+    const bool many = seq_lens != nullptr || (long long)B * Hkv * 2 > sm_count(device);
+    const int slots = (kv_dtype == SKV_KV_E4M3 && G <= 8 && many) ? 2 : 1;   // CTAs resident per SM
+    gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device, seq_lens != nullptr, slots);
     if (!workspace || workspace_bytes < pl.total)
         return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, pl.total);
     if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(SKV_ERR_WORKSPACE, "workspace must be 256-byte aligned");
@@ -555,7 +559,7 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.N = N; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
     p.tiles_per_split = pl.tiles_per_split;
     p.num_splits = pl.splits;
-    p.stages = gqa::tuning().q8_stages;
+    p.stages = slots == 2 ? (gqa::tuning().q8_stages < 6 ? gqa::tuning().q8_stages : 6) : gqa::tuning().q8_stages;
     p.out_bf16 = out_bf16;
     p.early_kv = gqa::tuning().early_kv;
     p.page_size = page_size;
@@ -567,11 +571,12 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.scale_log2 = scale * 1.4426950408889634f;
     p.pos = pos;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (slots == 2) return gqa::launch_q8<SKV_KV_E4M3, 1, 1>(tmK, tmV, p, B, st);
     if (G <= 8)
-        return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3, 1>(tmK, tmV, p, B, st)
-                                       : gqa::launch_q8<SKV_KV_I8, 1>(tmK, tmV, p, B, st);
-    return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3, 2>(tmK, tmV, p, B, st)
-                                   : gqa::launch_q8<SKV_KV_I8, 2>(tmK, tmV, p, B, st);
+        return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3, 1, 2>(tmK, tmV, p, B, st)
+                                       : gqa::launch_q8<SKV_KV_I8, 1, 2>(tmK, tmV, p, B, st);
+    return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3, 2, 2>(tmK, tmV, p, B, st)
+                                   : gqa::launch_q8<SKV_KV_I8, 2, 2>(tmK, tmV, p, B, st);
 }
 
 }  // extern "C"

@@ -51,12 +51,12 @@ struct Plan {
 
 // How the KV length is cut into whole 64-token tiles per split: one CTA per SM (times ctas_per_sm) when
 // there are few (batch, kv-head) pairs, about four waves of CTAs when there are many.
-inline Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device, bool ragged = false) {
+inline Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device, bool ragged = false, int slots_per_sm = 0) {
     Plan pl;
     const int G = Hq / Hkv;
     const long long total_tiles = (N + TILE - 1) / TILE;
     const long long pairs = (long long)B * Hkv;
-    const long long target = (long long)sm_count(device) * tuning().ctas_per_sm;
+    const long long target = (long long)sm_count(device) * (slots_per_sm > 0 ? slots_per_sm : tuning().ctas_per_sm);
     long long splits;
     if (!ragged && pairs * 2 <= target) {
         splits = target / pairs;              // few equally long (batch, head) pairs: one wave, one CTA per SM
