@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is mounted:
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /root/reference
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py <path to the reference checkout>
 
 It imports ``sparse_kv.attention._reference_sparse_attention`` and
 ``sparse_kv.eviction._reference_eviction`` unmodified, evaluates them on seeded
@@ -83,4 +83,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path to the reference checkout>")
+    main(sys.argv[1])
