@@ -315,7 +315,7 @@ quest_select_attend_kernel(const AttendParams p) {
                              (tc % p.page_size) | (t < len ? 0 : PAST_END));
     }
     __syncthreads();
-    constexpr int RU = 4;  // token rows per group and step: their code and scale loads are issued back to back
+    constexpr int RU = 8;  // token rows per group and step: their code and scale loads are issued back to back
     float mx = -INFINITY;
     for (int r0 = 0; r0 < ntok; r0 += RU * (ATT_THREADS / 8)) {  // uniform trip count: the shuffles need whole warps
         uint4 raw[RU];
