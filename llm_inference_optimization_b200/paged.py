@@ -164,3 +164,45 @@ def rope_quant_append(qkv: Tensor, kv: PagedKV, Hq: int, rope_theta: float, *, m
         _C._dev_index(qkv), torch.cuda.current_stream(qkv.device).cuda_stream)
     _lib.check(rc, "rope_quant_append")
     return q
+
+
+def repage_evicted(res, *, pool: Tensor | None = None, page_ids: Tensor | None = None) -> PagedKV:
+    """Put the compacted, quantised output of ``fused_kv_evict`` back into paged form (page reclamation).
+
+    ``res`` is the ``EvictionResult`` of a scaled-quantisation eviction in position order: codes
+    ``[B, H, keep, 128]`` (int8 or e4m3) and fp32 scales ``[B, H, keep]``.  Slot ``j`` of every head's new
+    sequence is that head's ``j``-th kept token (heads keep different positions; the keys already carry their
+    rotary phase, so attention does not need the original positions).  The rows are written as fused page
+    records of 16 tokens, either into fresh storage or -- with ``pool`` (a fused page-record buffer) and
+    ``page_ids`` (int ``[B, ceil(keep/16)]``, the pages handed out by the caller's allocator) -- into an
+    existing pool; the pages the sequences occupied before are then free for reuse.  Returns the ``PagedKV``
+    with ``seq_lens = keep``.
+    """
+    K, V, ks, vs = res.K, res.V, res.k_scale, res.v_scale
+    _C._require(ks is not None and vs is not None, "repage_evicted needs a scaled (int8 or fp8) eviction result")
+    B, H, keep, D = K.shape
+    _C._require(D == 128, "page records hold 128-channel rows")
+    n = (keep + 15) // 16
+    pad = n * 16 - keep
+
+    def rows(t):      # [B,H,keep,...] -> [B*n, H, 16, ...]
+        if pad:
+            t = torch.cat([t, t.new_zeros((B, H, pad) + tuple(t.shape[3:]))], dim=2)
+        t = t.reshape((B, H, n, 16) + tuple(t.shape[3:]))
+        return t.permute(0, 2, 1, 3, *range(4, t.dim())).reshape((B * n, H, 16) + tuple(t.shape[4:]))
+
+    code_dtype = K.dtype
+    records = pack_fused(rows(K.view(torch.uint8)).view(code_dtype), rows(V.view(torch.uint8)).view(code_dtype),
+                         rows(ks), rows(vs))
+    if pool is None:
+        table = torch.arange(B * n, dtype=torch.int32, device=K.device).view(B, n)
+        buf = records
+    else:
+        _C._require(page_ids is not None and tuple(page_ids.shape) == (B, n), "page_ids must be [B, ceil(keep/16)]")
+        _C._require(pool.dtype == torch.uint8 and pool.dim() == 4 and tuple(pool.shape[1:]) == (H, RECORD_ROWS, 128),
+                    "pool must be a fused page-record buffer [num_pages, H, 33, 128]")
+        pool[page_ids.reshape(-1).long()] = records
+        table = page_ids.to(torch.int32).contiguous()
+        buf = pool
+    lens = torch.full((B,), keep, dtype=torch.int32, device=K.device)
+    return PagedKV.from_fused(buf, code_dtype, table, lens, B)
