@@ -61,6 +61,10 @@ def emit(name, cfg, us, us_min, nbytes, peak, peak_kind, **extra):
     line = {"workload": name, **cfg, "us": round(us, 2), "us_min": round(us_min, 2), "algorithmic_MB": round(nbytes / 1e6, 2),
             "GBps": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3), "peak_GBps": peak, "peak_source": peak_kind, **extra}
     print(json.dumps(line), flush=True)
+    RESULTS.append(line)
+
+
+RESULTS: list = []   # every line printed in this process, for the --csv / --json files
 
 
 def randn16(shape, dev, g, scale=1.0):
@@ -170,6 +174,9 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=",".join(ALL))
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--csv", help="also write the results as a CSV table (the reference's sweep writes CSV and JSON, "
+                                  "benchmarks/run_benchmarks.py:64-80)")
+    ap.add_argument("--json", help="also write the results as one JSON array")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device: there is no CPU fallback")
@@ -181,6 +188,18 @@ def main(argv=None):
     for name in args.only.split(","):
         ALL[name.strip()](t, dev, g, peak, pk)
         torch.cuda.empty_cache()
+    if args.json:
+        with open(args.json, "w") as f:
+            json.dump(RESULTS, f, indent=1)
+    if args.csv:
+        import csv
+        cols = []
+        for r in RESULTS:
+            cols += [k for k in r if k not in cols]
+        with open(args.csv, "w", newline="") as f:
+            w = csv.DictWriter(f, fieldnames=cols)
+            w.writeheader()
+            w.writerows(RESULTS)
 
 
 if __name__ == "__main__":
