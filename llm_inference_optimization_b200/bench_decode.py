@@ -43,7 +43,19 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
     model.init_cache(lens, fill=fill, seed=seed, extra_tokens=steps + warmup + 16)
     fused_allreduce = fused_allreduce and world > 1
     if fused_allreduce:
-        model.enable_fused_allreduce(batch)   # all-reduce + residual + RMSNorm in one peer-memory kernel, no NCCL call
+        # all-reduce + residual + RMSNorm in one peer-memory kernel, no NCCL call; if the symmetric-memory
+        # rendezvous is not available on this machine every rank falls back to NCCL all-reduces together
+        try:
+            model.enable_fused_allreduce(batch)
+            ok = 1
+        except Exception as e:  # noqa: BLE001 -- reported below, the NCCL path still measures the step
+            print(f"[bench_decode] rank {rank}: fused all-reduce unavailable ({type(e).__name__}: {e})", flush=True)
+            ok = 0
+        agree = torch.tensor([ok], device=dev, dtype=torch.int32)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if int(agree.item()) == 0:
+            model.fused_allreduce = False
+            fused_allreduce = False
     tok = torch.randint(0, cfg.vocab, (batch,), generator=g).to(dev)
 
     for _ in range(warmup):
