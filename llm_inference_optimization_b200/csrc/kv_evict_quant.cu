@@ -366,8 +366,11 @@ __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, ui
 
 // one group of D/8 lanes per kept (row, j); grid-stride over all kept rows, four rows per group and step
 // so that four index loads and then eight 16-byte row loads are in flight per lane
+#ifndef SKV_GATHER_MIN_CTAS
+#define SKV_GATHER_MIN_CTAS 4
+#endif
 template <int D, int MODE>
-__global__ void __launch_bounds__(GQ_THREADS)
+__global__ void __launch_bounds__(GQ_THREADS, SKV_GATHER_MIN_CTAS)
 evict_gather_quant_kernel(const GatherParams p) {
     pdl_wait_prior_grids();   // launched as a programmatic dependent of the selection kernel: its results are complete from here on
     constexpr int LPR = D / 8;
