@@ -39,6 +39,11 @@ inline Tuning& tuning() {
     return t;
 }
 
+// Fewest 64-token tiles a split may hold: shorter CTAs are dominated by their start and end.
+#ifndef SKV_MIN_TILES_PER_SPLIT
+#define SKV_MIN_TILES_PER_SPLIT 16
+#endif
+
 // Waves of CTAs the KV length is cut into when the per-sequence lengths are not known to the host.
 #ifndef SKV_RAGGED_WAVES
 #define SKV_RAGGED_WAVES 8
@@ -64,7 +69,7 @@ inline Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device, bool rag
         // Many pairs, or per-sequence lengths the host does not know: a CTA streams at about 1/SMs of the HBM
         // rate, so work is cut into about eight waves of CTAs to let long sequences spread over many SMs
         // (CTAs past a sequence's end exit at once).
-        const long long max_by_size = total_tiles / 16 > 0 ? total_tiles / 16 : 1;   // at least 16 tiles per split
+        const long long max_by_size = total_tiles / SKV_MIN_TILES_PER_SPLIT > 0 ? total_tiles / SKV_MIN_TILES_PER_SPLIT : 1;
         if (ragged) {
             splits = (SKV_RAGGED_WAVES * target + pairs - 1) / pairs;
         } else {
