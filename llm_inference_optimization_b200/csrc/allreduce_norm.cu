@@ -17,7 +17,7 @@
 //   * the epoch lives in device memory and is advanced by the last CTA, so a captured graph replays correctly.
 // Two partial buffers alternate between consecutive calls: a rank overwrites a buffer only after it has passed the
 // barrier of the call in between, which every peer reaches after it has finished reading that buffer.
-// Only plain peer loads and stores are used (no multicast objects).
+// Only plain peer loads and stores are used.
 #include <cuda_bf16.h>
 
 #include "skv_common.cuh"

@@ -158,7 +158,7 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
 }
 
-// 5-D tiled TMA load global -> shared, completion signalled on an mbarrier.
+// Every CTA fetches its own tile (no sharing of a load between the CTAs of a cluster).
 // No cluster multicast: every CTA fetches its own tile.
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
                                             int c0, int c1, int c2, int c3, int c4, uint64_t policy) {
