@@ -20,7 +20,8 @@
 //     100-200 cycles); a stage is four fused page records (one TMA box each), or K/V
 //     boxes plus bulk copies of the scales for separate pools; page ids are
 //     prefetched 32 tiles ahead, one per lane;
-//   * two groups of four consumer warps work on alternate stages;
+//   * NG groups of four consumer warps work on the stages in turn: two groups in one 384-thread CTA per SM, or
+//     one group in 256-thread CTAs of which two share an SM (so that one streams while the other starts or ends);
 //   * tokens are on the M side of both products (S^T = K Q^T, O^T = V^T P^T) and the
 //     query heads on the 8-wide N side: a group of <= 8 heads needs one n-tile;
 //     P is moved to the B-operand layout with movmatrix;
