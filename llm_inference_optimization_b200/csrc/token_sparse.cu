@@ -41,6 +41,11 @@ struct ScoreParams {
     int cand_k;
 };
 
+// Rows shorter than this skip the per-chunk candidates: the row-wide select over all scores is cheaper there.
+#ifndef SKV_CAND_MIN_T
+#define SKV_CAND_MIN_T 32768
+#endif
+
 // grid (ceil(T / tokens_per_cta), H, B*S)
 template <int D>
 __global__ void __launch_bounds__(SCORE_THREADS)
@@ -272,7 +277,7 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     const int nchunks = (int)g1.x;
     const int kk = ap.top_k < sp.T ? ap.top_k : sp.T;
     size_t smem1 = 0;
-    if (kk <= MAX_CAND_K && nchunks >= 2 && tokens_per_cta <= 8192 && (long long)nchunks * kk * 4 <= sp.T &&
+    if (sp.T >= SKV_CAND_MIN_T && kk <= MAX_CAND_K && nchunks >= 2 && tokens_per_cta <= 8192 && (long long)nchunks * kk * 4 <= sp.T &&
         (long long)rows * nchunks <= cand_capacity_chunks(rows)) {
         sp2.cand_k = kk;
         sp2.cand_score = cand_base;
