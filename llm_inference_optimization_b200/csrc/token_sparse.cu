@@ -267,7 +267,10 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     }
     // enough CTAs to fill the machine a few times over, at least 512 tokens each
     const long long rows = (long long)B * sp.H * sp.S;
-    long long want = ((long long)sm_count(device) * 8 + rows - 1) / rows;
+#ifndef SKV_TOKEN_CTAS_PER_SM
+#define SKV_TOKEN_CTAS_PER_SM 8
+#endif
+    long long want = ((long long)sm_count(device) * SKV_TOKEN_CTAS_PER_SM + rows - 1) / rows;
     int tokens_per_cta = (int)((sp.T + want - 1) / want);
     tokens_per_cta = ((tokens_per_cta + 255) / 256) * 256;
     if (tokens_per_cta < 512) tokens_per_cta = 512;
