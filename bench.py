@@ -7,21 +7,24 @@ Workload ("config 2", Llama-3.1-8B layer shape): B=1 per GPU-share, Hq=32, Hkv=8
 cache of `ctx` tokens in the reference's [B, N, Hkv, D] layout, one query token.  One STEP is one
 decode pass over the attention of a 32-layer model: 32 launches of the decode kernel, each over
 its own layer's KV cache (32 x 268 MB at 64K, so consecutive launches never find their input in
-the 126 MB L2).  `value` is KV bytes streamed per second (GB/s) with the caches resident in HBM;
-`us_per_layer` is the same time divided by 32.
+the 126 MB L2).  `value` is KV bytes streamed per second (GB/s) with the caches resident in HBM and
+launches in the library's default order (each launch waits for the one before, as it must inside a
+real decode step); `us_per_layer` is the same time divided by 32.
 
 With N > 1 GPUs the path is partitioned by KV head and needs no collective: rank r owns
 Hkv / N kv-heads (and their 4 query heads each) of N sequences, so the work per GPU stays that
 of one sequence ("weak" scaling) while the global batch grows with N.
 
-`--impl reference` times the CPU restatement of the reference's own check of this path
-(fp32 softmax(QK^T)V over repeat_kv-expanded heads) on the host cores, on a bounded sample.
+`--impl reference` times the reference's CPU check of this path (fp32 softmax(QK^T)V over
+repeat_kv-expanded heads, restated in oracle/) on all host cores: same workload description, the
+same number of warm-up and timed steps, every step really run.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import statistics
 import sys
 import threading
 import time
@@ -33,9 +36,11 @@ sys.path.insert(0, str(ROOT))
 LAYERS = 32
 HQ, HKV, D = 32, 8, 128
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes per launch of the decode kernel at 64K measured with ncu (dram__bytes_read.sum +
-# dram__bytes_write.sum, see profiles/); None until a capture has been summarised there.
-NCU_TRAFFIC_BYTES_64K = 272_600_000  # profiles/gqa_decode_f16_ctx65536.md
+METRIC = "decode_attn_kv_stream_bandwidth"
+DTYPE = "f16 storage, f32 accumulate"
+# DRAM bytes one launch of the decode kernel moves at context 65536 (dram__bytes_read.sum + dram__bytes_write.sum of one
+# ncu capture of gqa_decode_f16_kernel<128>); other contexts report null.
+NCU_TRAFFIC_BYTES_64K = 272_600_000
 
 
 def peaks():
@@ -46,6 +51,17 @@ def peaks():
         except Exception:
             pass
     return FALLBACK_HBM_GBS, "fallback"
+
+
+def workload_config(ctx: int, layers: int, world: int) -> dict:
+    """The workload both arms run; identical dictionaries so the two JSON lines can be compared key by key."""
+    per_layer = kv_bytes(ctx, HKV // world, world)
+    return {
+        "workload": f"config2 dense GQA decode, Llama-3.1-8B layer shape, context {ctx}, {layers} layers per step",
+        "global_batch": world, "Hq": HQ, "Hkv": HKV, "D": D, "ctx": ctx, "layers_per_step": layers,
+        "partition": f"kv-head: {HKV // world} kv-heads x {world} sequences per GPU, no collective",
+        "l2": f"inputs larger than L2: each layer pass reads its own {per_layer / 1e6:.0f} MB cache per GPU",
+    }
 
 
 class ClockSampler:
@@ -124,53 +140,124 @@ def kv_bytes(ctx: int, heads: int, batch: int) -> int:
 
 
 # ------------------------------------------------------------------------------------ CPU arm
-def cpu_reference_run(ctx: int, steps: int, warmup: int, budget_s: float = 20.0):
-    """Times the oracle port of the reference's CPU check of dense GQA decode on one layer."""
+def use_all_host_cores() -> int:
+    """Thread count for the CPU legs.  Must run before torch is imported: a multi-process launcher exports
+    OMP_NUM_THREADS=1 to its ranks, which would time the host path on one core."""
+    n = os.cpu_count() or 1
+    if "torch" not in sys.modules:
+        os.environ["OMP_NUM_THREADS"] = str(n)
+        os.environ["MKL_NUM_THREADS"] = str(n)
+    import torch
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
+def cpu_dense_sample(ctx: int, layers: int, steps: int, warmup: int, budget_s: float):
+    """Times the oracle port of the reference's CPU check of dense GQA decode (kind "port": the reference has no
+    CPU function of its own for this op; benchmarks/llama_integration_benchmark.py:464-471 is the formula).
+
+    A step is `layers_run` layer passes of ONE sequence, cycling over 4 distinct layer caches (1 GB at 64K: no pass
+    finds its input in the host's last-level cache).  `layers_run` is `layers` unless the whole run would exceed
+    `budget_s`, in which case every step is a smaller, stated sample.  Returns (dict, layers_run, seconds per step)."""
+    cores = use_all_host_cores()
     import torch
     from llm_inference_optimization_b200 import workloads
     from oracle import skv_oracle as oracle
 
-    Q, K, V, scale = workloads.dense_gqa(ctx)
-    for _ in range(max(1, min(warmup, 3))):
-        oracle.dense_gqa_decode(Q, K, V, scale)
+    caches = []
+    for i in range(4):
+        Q, K, V, scale = workloads.dense_gqa(ctx, seed=1 + i)
+        caches.append((Q, K, V))
+    oracle.dense_gqa_decode(*caches[0], scale)
     t0 = time.perf_counter()
-    oracle.dense_gqa_decode(Q, K, V, scale)
+    oracle.dense_gqa_decode(*caches[1], scale)
     one = time.perf_counter() - t0
-    reps = max(1, min(steps, int(budget_s / max(one, 1e-6))))
-    times = []
-    for _ in range(reps):
-        t0 = time.perf_counter()
-        oracle.dense_gqa_decode(Q, K, V, scale)
-        times.append(time.perf_counter() - t0)
-    times.sort()
-    med = times[len(times) // 2]
-    gbs = kv_bytes(ctx, HKV, 1) / med / 1e9
-    return {
-        "value": gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-        "sample": f"{reps} passes over ONE layer's fp16 KV ({ctx} tokens, 8 kv-heads, D=128) with the fp32 torch "
-                  f"restatement of the reference's SDPA+repeat_kv check; median {med * 1e3:.1f} ms/layer",
-        "ms_per_layer": med * 1e3, "host_cpus": os.cpu_count(),
-    }, reps, med
+    layers_run = layers
+    if one * layers * (steps + warmup) > budget_s:
+        layers_run = max(1, int(budget_s / ((steps + warmup) * one)))
+
+    def step():
+        for l in range(layers_run):
+            oracle.dense_gqa_decode(*caches[l % 4], scale)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    per_step = (time.perf_counter() - t0) / steps
+    gbs = layers_run * kv_bytes(ctx, HKV, 1) / per_step / 1e9
+    sample = (f"{steps} timed steps (after {warmup} warm-up) of {layers_run} layer passes over ONE sequence's fp16 KV "
+              f"({ctx} tokens, 8 kv-heads, D=128), fp32 torch restatement of the reference's SDPA+repeat_kv check, "
+              f"{cores} threads; {per_step / layers_run * 1e3:.1f} ms per layer pass")
+    if layers_run != layers:
+        sample += f"; bounded sample: {layers_run} of {layers} layers per step to stay inside {budget_s:.0f} s"
+    return {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample,
+            "ms_per_layer": per_step / layers_run * 1e3, "host_cpus": os.cpu_count()}, layers_run, per_step
 
 
 def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    base, reps, med = cpu_reference_run(args.ctx, max(args.steps, 1), args.warmup)
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    steps, warmup = max(args.steps, 1), max(args.warmup, 0)
+    base, layers_run, per_step = cpu_dense_sample(args.ctx, args.layers, steps, warmup, budget_s=150.0)
     line = {
-        "impl": "reference", "metric": "decode_attn_kv_stream_bandwidth", "value": base["value"], "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": reps, "warmup": min(args.warmup, 3), "ms_per_step": med * 1e3 * LAYERS,
-        "us_per_layer": med * 1e6, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16 storage, f32 accumulate", "data": "synthetic (seeded N(0,1)/sqrt(D))",
-        "config": {"workload": f"config2 dense GQA decode, Llama-3.1-8B layer shape, context {args.ctx}",
-                   "B": 1, "Hq": HQ, "Hkv": HKV, "D": D, "ctx": args.ctx,
-                   "note": "a step of this arm is ONE layer (bounded sample); ms_per_step is scaled to 32 layers"},
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "GB/s",
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": per_step * 1e3,
+        "us_per_layer": per_step / layers_run * 1e6, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": DTYPE, "data": "synthetic (seeded N(0,1)/sqrt(D))",
+        "config": workload_config(args.ctx, args.layers, world),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "note": "host path: the rate does not depend on N, so at N > 1 rank 0 times one sequence's share of the job",
     }
     print(json.dumps(line), flush=True)
+
+
+def cpu_other_ops(budget_s: float = 8.0) -> dict:
+    """CPU baselines of the other two ops of the path, oracle ports pinned to the reference's own Python functions:
+    config 1 (sparse_kv/attention.py:25-38) and config 3 (sparse_kv/eviction.py:30-44)."""
+    cores = use_all_host_cores()
+    import torch
+    from llm_inference_optimization_b200 import workloads
+    from oracle import skv_oracle as oracle
+
+    def timed(fn):
+        fn()
+        t0 = time.perf_counter()
+        fn()
+        one = time.perf_counter() - t0
+        n = max(1, min(50, int(budget_s / max(one, 1e-6))))
+        ts = []
+        for _ in range(n):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return statistics.median(ts), n
+
+    out = {}
+    Q, K, V = workloads.token_sparse_config1()
+    sec, n = timed(lambda: oracle.token_sparse_attention(Q, K, V, 256, 4))
+    out["config1_token_sparse"] = {"ms": sec * 1e3, "cores": cores, "kind": "port",
+                                   "sample": f"median of {n} calls, B=1 H=8 T=1024 D=64 top_k=256 sinks=4, fp32"}
+    Ke, Ve, sc = workloads.eviction()
+    def ev():
+        idx = oracle.eviction_keep_indices(sc, 4096, 64)
+        Kw, Vw = oracle.evict_gather(Ke, Ve, idx)
+        oracle.quantize_int8(Kw)
+        oracle.quantize_int8(Vw)
+    sec, n = timed(ev)
+    nbytes = eviction_bytes(4, 8, 32768, 128, 4160)
+    out["config3_evict_int8"] = {"ms": sec * 1e3, "GBps": nbytes / sec / 1e9, "cores": cores, "kind": "port",
+                                 "sample": f"median of {n} calls, B=4 H=8 T=32768 D=128 keep 4096+64, topk+gather+INT8"}
+    return out
+
+
+def eviction_bytes(B, H, T, Dh, keep):
+    return B * H * T * 4 + 2 * B * H * keep * Dh * 2 + 2 * B * H * keep * Dh + 2 * B * H * keep * 4 + B * H * keep * 4
 
 
 # ------------------------------------------------------------------------------------ GPU arm
@@ -181,7 +268,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=65536)
-    ap.add_argument("--no-extras", action="store_true", help="skip the 128K / e2e / CPU legs (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true", help="skip every leg but the headline loop (profiling runs)")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-decode-step", action="store_true", help="skip the full decode-step tokens/s leg")
     args = ap.parse_args()
@@ -190,6 +277,8 @@ def main():
         reference_arm(args)
         return
 
+    if not args.no_extras and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        use_all_host_cores()   # the CPU baseline legs of this run; before torch is imported
     import torch
     import torch.distributed as dist
     from llm_inference_optimization_b200 import _C, _lib, _workspace
@@ -207,6 +296,7 @@ def main():
         raise SystemExit(f"cannot partition {HKV} kv-heads over {world} GPUs")
     warmup = max(args.warmup, 3)
     layers = args.layers
+    lib = _lib.load()
 
     # rank-local share of the head-partitioned problem: `world` sequences x (Hkv / world) kv-heads
     hkv_l, hq_l, batch = HKV // world, HQ // world, world
@@ -222,48 +312,57 @@ def main():
         Q = torch.randn(batch, hq_l, D, generator=g, device=dev, dtype=torch.float16) * scale
         return Q, Ks, Vs
 
-    def time_steps(ctx, n_layers, steps, warm, early_kv=True):
+    def gather_ranks(x: float) -> list:
+        if world == 1:
+            return [x]
+        t = torch.zeros(world, device=dev, dtype=torch.float64)
+        t[rank] = x
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return [float(v) for v in t.tolist()]
+
+    def time_steps(ctx, n_layers, steps, warm, early_kv=False):
+        """ms per step (max over ranks), every rank's ms, and the host's enqueue time per call in us."""
         Q, Ks, Vs = make_layers(ctx, n_layers, seed=1)
         out = torch.empty(batch, hq_l, D, device=dev, dtype=torch.float16)
-        # The layers' caches are static during the timed region, so a launch may stream K/V while the previous
-        # launch's combine tail drains; with early_kv off every launch first waits for the one before.
-        _lib.load().skv_gqa_set_early_kv(1 if early_kv else 0)
 
         def step():
             for l in range(n_layers):
                 _C.fused_gqa(Q, Ks[l], Vs[l], scale, out=out)
 
-        for _ in range(warm):
-            step()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            step()
-        e1.record()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        _lib.load().skv_gqa_set_early_kv(0)
+        # early_kv: the caller's statement that no launch writes the K/V a later launch reads (true here: the
+        # caches are static), which lets a launch stream K/V while the previous launch's combine tail drains.
+        lib.skv_gqa_set_early_kv(1 if early_kv else 0)
+        try:
+            for _ in range(warm):
+                step()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            h0 = time.perf_counter()
+            e0.record()
+            for _ in range(steps):
+                step()
+            e1.record()
+            host_us = (time.perf_counter() - h0) * 1e6 / (steps * n_layers)   # un-synchronised: the enqueue cost
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            lib.skv_gqa_set_early_kv(0)
+        ms_all = gather_ranks(e0.elapsed_time(e1) / steps)
         st = _workspace.status(_workspace.get("gqa", 0, dev))
         if st != 0:
             raise SystemExit(f"device status word {st}: a bounded wait inside the decode kernel ran out")
         del Ks, Vs
         torch.cuda.empty_cache()
-        return ms / steps
+        return max(ms_all), ms_all, max(gather_ranks(host_us))
 
     sampler = ClockSampler(local)
     with sampler:
-        ms_step = time_steps(args.ctx, layers, args.steps, warmup)
+        ms_step, ms_ranks, host_us = time_steps(args.ctx, layers, args.steps, warmup)
     clocks = sampler.summary()
 
     bytes_layer_rank = kv_bytes(args.ctx, hkv_l, batch)
@@ -271,28 +370,26 @@ def main():
     per_gpu_gbs = bytes_layer_rank / (us_layer * 1e-6) / 1e9
     value = per_gpu_gbs * world
     peak, peak_kind = peaks()
+    us_ranks = sorted(m * 1e3 / layers for m in ms_ranks)
 
     line = {
-        "metric": "decode_attn_kv_stream_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world,
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "us_per_layer": us_layer,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16 storage, f32 accumulate", "data": "synthetic (seeded N(0,1)/sqrt(D), generated on device)",
-        "config": {
-            "workload": f"config2 dense GQA decode, Llama-3.1-8B layer shape, context {args.ctx}, "
-                        f"{layers} layers per step",
-            "global_batch": batch, "Hq": HQ, "Hkv": HKV, "D": D, "ctx": args.ctx, "layers_per_step": layers,
-            "partition": f"kv-head: {hkv_l} kv-heads x {batch} sequences per GPU, no collective",
-            "l2": f"each launch reads its own layer's {bytes_layer_rank / 1e6:.0f} MB cache; "
-                  f"{layers * bytes_layer_rank / 1e9:.1f} GB cycle >> 126 MB L2",
-            "kv_splits": _lib.load().skv_gqa_decode_splits(batch, args.ctx, hq_l, hkv_l, D, local),
-            "launch_order": "skv_gqa_set_early_kv(1): the caches are static while timed, so a launch streams K/V "
-                            "before the previous launch has completed (q, out, workspace stay ordered); the "
-                            "default fully ordered launches are timed in 'ordered_launches'",
+        "dtype": DTYPE, "data": "synthetic (seeded N(0,1)/sqrt(D), generated on device)",
+        "config": workload_config(args.ctx, layers, world),
+        "launch": {
+            "kv_splits": lib.skv_gqa_decode_splits(batch, args.ctx, hq_l, hkv_l, D, local),
+            "order": "default: every launch waits for the one before it (what a real decode step needs, since the "
+                     "layer's K/V page is written just before its attention launch); 'early_kv_launches' times the "
+                     "opt-in mode for static caches",
         },
+        "per_rank_us": {"min": us_ranks[0], "median": us_ranks[len(us_ranks) // 2], "max": us_ranks[-1]},
+        "host_us_per_call": host_us,
         "roofline": {
             "bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
             "peak_source": f"{peak_kind} copy bandwidth", "frac_of_nominal_8000": per_gpu_gbs / 8000.0,
-            "traffic": NCU_TRAFFIC_BYTES_64K if args.ctx == 65536 else None,
+            "traffic": NCU_TRAFFIC_BYTES_64K if (args.ctx == 65536 and world == 1) else None,
             "algorithmic_bytes_per_launch": bytes_layer_rank, "avg_launch_us": us_layer,
         },
         "clocks": clocks,
@@ -300,21 +397,21 @@ def main():
     }
 
     if not args.no_extras:
-        # ---- 128K point of the metric (fewer layers: same bytes per step)
+        half = max(3, args.steps // 2)
+        # ---- the opt-in launch mode for static caches, and the 128K point of the metric (fewer layers: same bytes)
+        ms_e, _, _ = time_steps(args.ctx, layers, half, 3, early_kv=True)
+        g_e = bytes_layer_rank / (ms_e * 1e-3 / layers) / 1e9
+        line["early_kv_launches"] = {"us_per_layer": ms_e * 1e3 / layers, "gbs_per_gpu": g_e, "frac_of_peak": g_e / peak,
+                                     "note": "skv_gqa_set_early_kv(1): a launch streams K/V before the previous launch "
+                                             "has completed; valid only while no launch writes K/V (not inside a decode step)"}
+        by_ctx = {str(args.ctx): {"us_per_layer": us_layer, "gbs_per_gpu": per_gpu_gbs, "frac_of_peak": per_gpu_gbs / peak}}
         if args.ctx != 131072:
             l128 = max(2, layers // 2)
-            ms128 = time_steps(131072, l128, max(3, args.steps // 2), 3)
+            ms128, _, _ = time_steps(131072, l128, half, 3)
             us128 = ms128 * 1e3 / l128
             g128 = kv_bytes(131072, hkv_l, batch) / (us128 * 1e-6) / 1e9
-            ms_ord = time_steps(args.ctx, layers, max(3, args.steps // 2), 3, early_kv=False)
-            g_ord = kv_bytes(args.ctx, hkv_l, batch) / (ms_ord * 1e-3 / layers) / 1e9
-            line["ordered_launches"] = {"us_per_layer": ms_ord * 1e3 / layers, "gbs_per_gpu": g_ord,
-                                        "frac_of_peak": g_ord / peak,
-                                        "note": "default launch order: every launch waits for the one before"}
-            line["by_context"] = {
-                str(args.ctx): {"us_per_layer": us_layer, "gbs_per_gpu": per_gpu_gbs, "frac_of_peak": per_gpu_gbs / peak},
-                "131072": {"us_per_layer": us128, "gbs_per_gpu": g128, "frac_of_peak": g128 / peak},
-            }
+            by_ctx["131072"] = {"us_per_layer": us128, "gbs_per_gpu": g128, "frac_of_peak": g128 / peak}
+        line["by_context"] = by_ctx
 
         # ---- end to end through the public API with HOST buffers
         e2e_steps = max(3, min(args.steps, 10))
@@ -351,12 +448,7 @@ def main():
                 fn()
             e1.record()
             torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / n
-            if world > 1:
-                t = torch.tensor([ms], device=dev, dtype=torch.float64)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                ms = float(t.item())
-            return ms
+            return max(gather_ranks(e0.elapsed_time(e1) / n))
 
         ms_e2e = timed(e2e_host_kv, e2e_steps)
         ms_res = timed(e2e_resident, e2e_steps * 20)
@@ -365,8 +457,9 @@ def main():
             "value": world * bytes_layer_rank / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
             "h2d_bytes_per_step": qo + bytes_layer_rank, "d2h_bytes_per_step": qo,
             "ms_per_layer": ms_e2e, "steps": e2e_steps,
-            "note": "one layer per step: pinned host Q, K, V -> device, fused_gqa(), output -> pinned host; "
-                    "PCIe-bound because the whole KV cache crosses the bus every step",
+            "note": "one layer per step: pinned host Q, K, V -> device, fused_gqa(), output -> pinned host; PCIe-bound by "
+                    "construction (the whole KV cache crosses the bus every step), and at N > 1 every rank pushes its "
+                    "cache through the host's PCIe complex at once, so the per-GPU figure falls with N",
         }
         line["e2e_resident_kv"] = {
             "value": world * bytes_layer_rank / (ms_res * 1e-3) / 1e9, "unit": "GB/s",
@@ -376,10 +469,15 @@ def main():
         }
         del dK, dV, hK, hV
 
-        # ---- CPU baseline next to it (rank 0, single-GPU run only)
+        # ---- the other two ops of the path at their configs, head-partitioned like the headline (weak scaling)
+        line["other_configs"] = other_configs(dev, world, rank, peak, gather_ranks)
+
+        # ---- CPU baselines next to it (rank 0, single-GPU run only)
         if world == 1 and rank == 0:
-            base, _, _ = cpu_reference_run(args.ctx, 1000, 2, budget_s=15.0)
+            base, _, _ = cpu_dense_sample(args.ctx, layers, 3, 1, budget_s=15.0)
             line["cpu_baseline"] = base
+            line["cpu_baseline_other_ops"] = cpu_other_ops()
+            line["reference_cuda"] = reference_cuda_leg(dev)
 
     if not args.no_extras and not args.no_decode_step:
         # ---- the other half of the metric: tokens/s of the full tensor-parallel decode step (all ranks take part)
@@ -396,6 +494,109 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def other_configs(dev, world, rank, peak, gather_ranks) -> dict:
+    """Fused eviction + INT8 (config 3) and Quest block-sparse decode over paged FP8 (config 4) on every rank's share:
+    rank r owns H / world heads of world x the batch, so the work per GPU is the configuration's own."""
+    import torch
+    from llm_inference_optimization_b200 import eviction, paged
+
+    flush = torch.zeros(64 << 20, dtype=torch.int32, device=dev)   # 256 MB read between calls: larger than L2
+
+    def timed(fn, iters=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            flush.max()
+            flush.max()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return max(gather_ranks(statistics.median(ts)))
+
+    out = {}
+    g = torch.Generator(device=dev)
+    g.manual_seed(77 + rank)
+    # config 3
+    B, H, T, Dh, budget, recent = 4 * world, 8 // world, 32768, 128, 4096, 64
+    K = torch.randn((B, H, T, Dh), device=dev, generator=g, dtype=torch.float32).half()
+    V = torch.randn((B, H, T, Dh), device=dev, generator=g, dtype=torch.float32).half()
+    sc = torch.rand((B, H, T), device=dev, generator=g, dtype=torch.float32)
+    us = timed(lambda: eviction.fused_kv_evict(K, V, sc, budget, recent_tokens=recent, quant="int8", return_aux=True))
+    nbytes = eviction_bytes(B, H, T, Dh, budget + recent)
+    out["config3_evict_int8"] = {"us": us, "GBps_total": world * nbytes / us / 1e3, "frac_of_peak_per_gpu": nbytes / us / 1e3 / peak,
+                                 "algorithmic_MB_per_gpu": nbytes / 1e6, "per_gpu_shape": [B, H, T, Dh]}
+    del K, V, sc
+    # config 4
+    B, Hq, Hkv, T, P, bs, k = 8 * world, 32 // world, 8 // world, 131072, 16, 64, 8
+    pages = B * T // P
+    buf = torch.randint(0, 256, (pages, Hkv, paged.RECORD_ROWS, 128), device=dev, generator=g, dtype=torch.uint8)
+    buf[:, :, :32] = torch.where((buf[:, :, :32] & 0x7F) == 0x7F, buf[:, :, :32] & 0xFE, buf[:, :, :32])  # no NaN codes
+    table = torch.randperm(pages, device=dev, generator=g).to(torch.int32).view(B, T // P)
+    kv = paged.PagedKV.from_fused(buf, torch.float8_e4m3fn, table, None, B)
+    kv.k_scale.copy_(torch.rand(kv.k_scale.shape, device=dev, generator=g) * 0.01 + 0.005)
+    kv.v_scale.copy_(torch.rand(kv.v_scale.shape, device=dev, generator=g) * 0.01 + 0.005)
+    Q = torch.randn((B, Hq, Dh), device=dev, generator=g, dtype=torch.float32).half()
+    meta = paged.build_block_meta(kv, bs)
+    us = timed(lambda: paged.quest_sparse_decode(Q, kv, meta, Dh ** -0.5, bs, k))
+    nbytes = B * Hkv * (T // bs) * 2 * Dh * 2 + B * Hq * k * bs * 2 * (Dh + 4) + B * Hq * k * (bs // P) * 4
+    out["config4_quest_fp8"] = {"us": us, "GBps_total": world * nbytes / us / 1e3, "frac_of_peak_per_gpu": nbytes / us / 1e3 / peak,
+                                "algorithmic_MB_per_gpu": nbytes / 1e6, "per_gpu_shape": {"B": B, "Hq": Hq, "Hkv": Hkv, "ctx": T}}
+    del buf, kv, meta, flush
+    torch.cuda.empty_cache()
+    return out
+
+
+def reference_cuda_leg(dev) -> dict:
+    """The reference's OWN CUDA kernels (its three .cu files compiled unchanged for sm_100a, oracle/build_ref.py) timed
+    on this GPU beside this library's kernels, at the shapes of the reference's sweep (benchmarks/run_benchmarks.py:22-80:
+    B=1, H=32, D=128; the dense kernel with 8 kv-heads).  Checker-side code: nothing in the product path loads it."""
+    import torch
+    from llm_inference_optimization_b200 import _C
+    from oracle import build_ref
+    if not build_ref.available():
+        return {"unavailable": "oracle/_ref holds no built module (run `python oracle/build_ref.py` where the reference checkout is)"}
+    ref = build_ref.load()
+
+    def t(fn, it):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(it):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / it * 1e3
+
+    res = {}
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    for N in (4096, 16384, 65536):
+        Q = (torch.randn(1, 32, 128, device=dev, generator=g) * 128 ** -0.5).half()
+        K = (torch.randn(1, N, 8, 128, device=dev, generator=g) * 128 ** -0.5).half()
+        V = (torch.randn(1, N, 8, 128, device=dev, generator=g) * 128 ** -0.5).half()
+        Q4 = torch.randn(1, 32, 1, 128, device=dev, generator=g).half()
+        K4 = torch.randn(1, 32, N, 128, device=dev, generator=g).half()
+        V4 = torch.randn(1, 32, N, 128, device=dev, generator=g).half()
+        res[str(N)] = {
+            "fused_gqa_us": {"reference": t(lambda: ref.fused_gqa(Q, K, V, 128 ** -0.5), 3),
+                             "ours": t(lambda: _C.fused_gqa(Q, K, V, 128 ** -0.5), 20)},
+            "kv_evict_quant_forward_top32_us": {"reference": t(lambda: ref.kv_evict_quant_forward(Q4, K4, V4, 32, False), 3),
+                                                "ours": t(lambda: _C.kv_evict_quant_forward(Q4, K4, V4, 32, False), 20)},
+            "sparse_attention_forward_64x8_us": {"reference": t(lambda: ref.sparse_attention_forward(Q4, K4, V4, 64, 8), 3),
+                                                 "ours": t(lambda: _C.sparse_attention_forward(Q4, K4, V4, 64, 8), 20)},
+        }
+        del K, V, K4, V4
+    res["note"] = ("back-to-back calls on one input (L2-warm at 4K and 16K for both sides); the reference's token kernel "
+                   "keeps an approximate top-k, ours is exact")
+    return res
 
 
 if __name__ == "__main__":

@@ -44,6 +44,9 @@ extern "C" {
 
 /* bit in the workspace status word: a bounded wait inside a kernel ran out */
 #define SKV_DEV_TIMEOUT 1
+/* bit in a status word: a page id read from the caller's page table lay outside [0, num_pages); the kernel read
+ * page 0 in its place (decode) or stored nothing (append) instead of forming an address from it */
+#define SKV_DEV_BAD_PAGE 2
 
 /* Replaces the c10::Error message carried by TORCH_CHECK in the reference launchers
  * (csrc/kernels/gqa_decode.cu:225-251). */
@@ -115,20 +118,23 @@ int skv_gqa_set_early_kv(int on);
  *   best blocks per query head (ties: lower block id) among the blocks the sequence has; out[b,hq,:] = exact softmax
  *   attention over the tokens of those blocks (dequantised, fp32).  block_idx_out optional int32 [B,Hq,top_k_blocks],
  *   ascending, -1 padded.  D = 128, Hq/Hkv <= 8, top_k_blocks <= 256, top_k_blocks*block_size <= 2048.
- *   Workspace holds fp32 block scores [B,Hq,nb]. */
+ *   Workspace holds a status word (offset 0) and fp32 block scores [B,Hq,nb].
+ * num_pages: pages in the pools.  A page-table entry outside [0, num_pages) is never turned into an address: page 0 is
+ *   read in its place and SKV_DEV_BAD_PAGE is set in the status word (skv_quest_build_meta: in *status, an optional
+ *   int32 device word; skv_quest_decode: at offset 0 of the workspace, read with skv_workspace_status). */
 int skv_quest_num_blocks(int N, int block_size);
 size_t skv_quest_workspace_bytes(int B, int Hq, int N, int block_size);
 int skv_quest_build_meta(const void* k_pool, const float* k_scale_pool, const int* page_table, const int* seq_lens,
                          void* meta_out, int B, int N, int Hkv, int D, int kv_dtype, int block_size,
-                         int page_size, int max_pages,
+                         int page_size, int max_pages, int num_pages,
                          long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
-                         long long scale_stride_page, long long scale_stride_head, int device, void* stream);
+                         long long scale_stride_page, long long scale_stride_head, int* status, int device, void* stream);
 int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool,
                      const float* k_scale_pool, const float* v_scale_pool,
                      const int* page_table, const int* seq_lens, const void* meta,
                      void* out, int* block_idx_out, void* workspace, size_t workspace_bytes,
                      int B, int N, int Hq, int Hkv, int D, int kv_dtype,
-                     int block_size, int top_k_blocks, int page_size, int max_pages,
+                     int block_size, int top_k_blocks, int page_size, int max_pages, int num_pages,
                      long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
                      long long scale_stride_page, long long scale_stride_head,
                      float scale, int device, void* stream);
@@ -143,14 +149,15 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool,
  * sequence whose position lies past its max_pages * page_size slots stores nothing.
  * meta (optional, else NULL): the fp16 [B,Hkv,meta_num_blocks,2,D] metadata of skv_quest_build_meta, whose block
  * containing the new token is updated with the dequantised new key (re-initialised when the token opens a block).
- * D = 128. */
+ * num_pages: pages in the pools; a table entry outside [0, num_pages) stores nothing and sets SKV_DEV_BAD_PAGE in
+ * *status (optional int32 device word, else NULL).  D = 128. */
 int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k_pool, void* v_pool,
                           float* k_scale_pool, float* v_scale_pool, const int* page_table, const int* seq_lens,
                           int B, int Hq, int Hkv, int D, int kv_dtype, int page_size, int max_pages,
                           long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
                           long long scale_stride_page, long long scale_stride_head,
                           float rope_theta, void* meta, int meta_block_size, int meta_num_blocks,
-                          int device, void* stream);
+                          int num_pages, int* status, int device, void* stream);
 
 /* ---- token-sparse decode ----------------------------------------------------------
  * Replaces kv_evict_quant_forward(Q, K, V, top_k, use_int8=false)  (csrc/kernels/kv_evict_quant.cu:272-364,
@@ -196,6 +203,10 @@ int skv_block_sparse_decode(const void* q, const void* k, const void* v, void* o
  *                mode 2: scale = amax/448 (1.0 if zero),            code = e4m3_rne_satfinite(x/scale)
  * k_cache/v_cache fp16 [B,H,T,D] with element strides.  D is 16, 32, 64, 128 or 256, keep <= 8192. */
 int skv_kv_evict_keep_count(int T, int budget, int recent);
+/* on = 1 (default): position-order evictions of rows with at most 32768 competing scores and D = 64 or 128 run as ONE
+ * launch (a 4-CTA cluster per (b,h) selects, then gathers and quantises its own head's rows); on = 0: selection and
+ * gather always run as two launches.  Same results either way; process-wide.  No reference counterpart. */
+int skv_kv_evict_set_fused(int on);
 int skv_kv_evict_quant(const void* k_cache, const void* v_cache, const float* scores, int* idx_out,
                        void* k_out, void* v_out, float* k_scale_out, float* v_scale_out,
                        int B, int H, int T, int D,
@@ -222,7 +233,7 @@ int skv_gqa_decode_mass(const void* q, const void* k, const void* v, void* out, 
  * The scratch is a fixed array inside the library: SKV_GQA_STATIC_SCRATCH_BYTES per GPU that loads
  * the library, kept until exit.  Problems whose skv_gqa_decode_workspace_bytes() is larger are
  * rejected with SKV_ERR_WORKSPACE.  The first call on a device looks the array's device address up
- * (make that call before any stream capture).  All calls on a GPU share the array: what must be
+ * (make that call before any stream capture; made during a capture it returns SKV_ERR_CUDA).  All calls on a GPU share the array: what must be
  * zero is cleared on `stream` before each launch, and calls that can overlap on one GPU race.
  * Calls no cudaMalloc / cudaFree / allocating library routine. */
 #define SKV_GQA_STATIC_SCRATCH_BYTES (4u << 20)
@@ -230,6 +241,10 @@ int skv_gqa_decode_noalloc(const void* q, const void* k, const void* v, void* ou
                            int B, int N, int Hq, int Hkv, int D,
                            long long kv_stride_b, long long kv_stride_n, long long kv_stride_h,
                            const int* seq_lens, float scale, int device, void* stream);
+/* Reads the status word of that built-in array on `device` (SKV_DEV_TIMEOUT when a bounded wait inside the kernel
+ * ran out; the per-call clearing leaves this word alone, so a bit stays set until the process ends).  SYNCHRONISES
+ * `stream`.  Allocates nothing.  No counterpart in the reference. */
+int skv_gqa_decode_noalloc_status(int device, void* stream, int* status_out);
 
 /* ---- decode-step glue around the attention call -------------------------------------
  * The reference runs Hugging Face's LlamaRMSNorm / LlamaMLP modules here (the model it patches,

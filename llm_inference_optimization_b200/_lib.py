@@ -39,6 +39,7 @@ SIGNATURES = {
     "skv_block_sparse_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i,
                                      _ll, _ll, _ll, _ll, _ll, _i, _i, _f, _i, _vp]),
     "skv_kv_evict_keep_count": (_i, [_i, _i, _i]),
+    "skv_kv_evict_set_fused": (_i, [_i]),
     "skv_kv_evict_quant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll,
                                 _i, _i, _i, _i, _i, _vp]),
     "skv_gqa_set_q8_stages": (_i, [_i]),
@@ -47,15 +48,16 @@ SIGNATURES = {
                                   _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp]),
     "skv_quest_num_blocks": (_i, [_i, _i]),
     "skv_quest_workspace_bytes": (_sz, [_i, _i, _i, _i]),
-    "skv_quest_build_meta": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
-                                  _ll, _ll, _ll, _ll, _ll, _i, _vp]),
+    "skv_quest_build_meta": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i,
+                                  _ll, _ll, _ll, _ll, _ll, _vp, _i, _vp]),
     "skv_quest_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i,
-                              _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp]),
+                              _i, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp]),
     "skv_residual_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp]),
     "skv_allreduce_residual_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, C.c_uint, _i, _vp]),
     "skv_silu_mul": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "skv_rope_quant_append": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
-                                   _ll, _ll, _ll, _ll, _ll, _f, _vp, _i, _i, _i, _vp]),
+                                   _ll, _ll, _ll, _ll, _ll, _f, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "skv_gqa_decode_noalloc_status": (_i, [_i, _vp, C.POINTER(_i)]),
     "skv_gqa_decode_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _ll, _vp, _f, _i, _vp]),
 }
 

@@ -142,10 +142,19 @@ def bench_evict(t, dev, g, peak, pk):
     K, V = randn16((B, H, T, D), dev, g), randn16((B, H, T, D), dev, g)
     scores = torch.rand((B, H, T), device=dev, generator=g, dtype=torch.float32)
     keep = budget + recent
+    from . import _lib
+    lib = _lib.load()
+    nbytes = B * H * T * 4 + 2 * B * H * keep * D * 2 + 2 * B * H * keep * D + 2 * B * H * keep * 4 + B * H * keep * 4
     for quant in ("int8", "fp8"):
-        us, mn = t(lambda: eviction.fused_kv_evict(K, V, scores, budget, recent_tokens=recent, quant=quant, return_aux=True))
-        nbytes = B * H * T * 4 + 2 * B * H * keep * D * 2 + 2 * B * H * keep * D + 2 * B * H * keep * 4 + B * H * keep * 4
-        emit("kv_evict_quant_" + quant, {"B": B, "H": H, "T": T, "D": D, "budget": budget, "recent": recent}, us, mn, nbytes, peak, pk)
+        for fused in (1, 0):
+            lib.skv_kv_evict_set_fused(fused)
+            try:
+                us, mn = t(lambda: eviction.fused_kv_evict(K, V, scores, budget, recent_tokens=recent, quant=quant, return_aux=True))
+            finally:
+                lib.skv_kv_evict_set_fused(1)
+            emit("kv_evict_quant_" + quant, {"B": B, "H": H, "T": T, "D": D, "budget": budget, "recent": recent,
+                                             "launches": "one (cluster selects and gathers)" if fused else "two (select, gather)"},
+                 us, mn, nbytes, peak, pk)
 
 
 def bench_quest(t, dev, g, peak, pk):

@@ -547,10 +547,29 @@ int skv_gqa_decode_mass(const void* q, const void* k, const void* v, void* out, 
 //   * Nothing here calls cudaMalloc, cudaFree or any allocating library routine.
 // ---------------------------------------------------------------------------
 #define SKV_GQA_STATIC_SCRATCH_BYTES (4u << 20)
+static_assert(SKV_GQA_STATIC_SCRATCH_BYTES == 4194304u, "keep in step with include/skv_b200.h");
 
 static __device__ __align__(256) unsigned char skv_gqa_static_scratch[SKV_GQA_STATIC_SCRATCH_BYTES];
 static void* g_static_scratch_ptr[64] = {nullptr};  // device address of the array, per device ordinal
 static std::mutex g_static_scratch_mu;
+
+// Device address of the array on `device` (which must be current).  The one-time lookup refuses to run while `stream`
+// is being captured: a capture must not be the first thing that touches the array on a device.
+static int static_scratch_address(int device, cudaStream_t stream, void** out) {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    void* scratch = g_static_scratch_ptr[device];
+    if (!scratch) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+            return fail(SKV_ERR_CUDA, "the first skv_gqa_decode_noalloc call on a device must be made outside stream capture");
+        cudaError_t e = cudaGetSymbolAddress(&scratch, skv_gqa_static_scratch);
+        if (e != cudaSuccess || !scratch)
+            return fail(SKV_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+        g_static_scratch_ptr[device] = scratch;
+    }
+    *out = scratch;
+    return SKV_OK;
+}
 
 int skv_gqa_decode_noalloc(const void* q, const void* k, const void* v, void* out, int B, int N, int Hq, int Hkv,
                            int D, long long kv_stride_b, long long kv_stride_n, long long kv_stride_h,
@@ -568,20 +587,30 @@ int skv_gqa_decode_noalloc(const void* q, const void* k, const void* v, void* ou
                     "call skv_gqa_decode with a caller-provided workspace",
                     pl.total, (unsigned)SKV_GQA_STATIC_SCRATCH_BYTES);
     void* scratch = nullptr;
-    {
-        std::lock_guard<std::mutex> lock(g_static_scratch_mu);
-        scratch = g_static_scratch_ptr[device];
-        if (!scratch) {  // one-time set-up for this device (it is the current device here)
-            cudaError_t e = cudaGetSymbolAddress(&scratch, skv_gqa_static_scratch);
-            if (e != cudaSuccess || !scratch)
-                return fail(SKV_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
-            g_static_scratch_ptr[device] = scratch;
-        }
-    }
-    // status word + tickets must be zero when the kernel starts; the partials need no clearing
-    SKV_CUDA_TRY(cudaMemsetAsync(scratch, 0, pl.off_ml, static_cast<cudaStream_t>(stream)));
+    const int rc = static_scratch_address(device, static_cast<cudaStream_t>(stream), &scratch);
+    if (rc) return rc;
+    // The tickets must be zero when the kernel starts; the partials need no clearing.  The status word in front of
+    // them is NOT cleared: a bounded wait that ran out stays visible to skv_gqa_decode_noalloc_status.
+    SKV_CUDA_TRY(cudaMemsetAsync(static_cast<unsigned char*>(scratch) + pl.off_tickets, 0, pl.off_ml - pl.off_tickets,
+                                 static_cast<cudaStream_t>(stream)));
     return skv_gqa_decode(q, k, v, out, scratch, (size_t)SKV_GQA_STATIC_SCRATCH_BYTES, B, N, Hq, Hkv, D, SKV_KV_F16,
                           nullptr, nullptr, kv_stride_b, kv_stride_n, kv_stride_h, seq_lens, scale, device, stream);
+}
+
+// The status word of the built-in scratch array on `device` (bit SKV_DEV_TIMEOUT: a bounded wait inside the kernel
+// gave up); the word keeps its bits until the process ends.  Synchronises `stream`.  Allocates nothing.
+int skv_gqa_decode_noalloc_status(int device, void* stream, int* status_out) {
+    if (!status_out) return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode_noalloc_status: null pointer");
+    if (device < 0 || device >= 64) return fail(SKV_ERR_BAD_ARG, "device ordinal %d out of range", device);
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
+    void* scratch = nullptr;
+    const int rc = static_scratch_address(device, static_cast<cudaStream_t>(stream), &scratch);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    SKV_CUDA_TRY(cudaMemcpyAsync(status_out, scratch, sizeof(int), cudaMemcpyDeviceToHost, st));
+    SKV_CUDA_TRY(cudaStreamSynchronize(st));
+    return SKV_OK;
 }
 
 }  // extern "C"

@@ -78,6 +78,7 @@ struct Q8Params {
     int N, Hq, Hkv, G;
     int tiles_per_split, num_splits, stages;
     int page_size, max_pages;
+    int num_pages;           // pages in the pools: ids read from the table are checked against it
     int mode;                // Q8_SEPARATE16, Q8_SEPARATE64 or Q8_FUSED
     int out_bf16;            // output elements are bf16 instead of fp16
     int early_kv;            // pages, page table and seq_lens are not produced by the previous kernel
@@ -187,6 +188,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         int s = 0;
         uint32_t ph = 0;
         int ok = 1;
+        bool bad_page = false;
         for (int it0 = 0; it0 < ntiles && ok; it0 += 32) {
             int page = -1, slot = 0;
             {
@@ -195,6 +197,9 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                     const int lp = t / P;
                     slot = t - lp * P;
                     page = p.page_table ? __ldg(p.page_table + (long long)b * p.max_pages + lp) : b * p.max_pages + lp;
+                    // A page id outside the pools (a stale or corrupt table entry) must not become an address:
+                    // page 0 is read in its place, so the output stays finite, and the status word says so.
+                    page = checked_page(page, p.num_pages, bad_page);
                 }
             }
             const int jn = min(32, ntiles - it0);
@@ -230,6 +235,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 if (++s == p.stages) { s = 0; ph ^= 1u; }
             }
         }
+        report_bad_page(bad_page, p.status);
         return;
     }
 
@@ -565,6 +571,7 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.early_kv = gqa::tuning().early_kv;
     p.page_size = page_size;
     p.max_pages = max_pages;
+    p.num_pages = num_pages;
     p.mode = mode;
     p.sc_sp = scale_stride_page; p.sc_sh = scale_stride_head;
     p.q_stride_b = (long long)Hq * D; p.q_stride_h = D;

@@ -27,7 +27,8 @@ struct Params {
     const int* page_table;                // [B, max_pages] or null
     const int* seq_lens;                  // [B]: position the new token takes
     long long sp, sh, ss, csp, csh;
-    int B, Hq, Hkv, page_size, max_pages, kv_dtype;
+    int B, Hq, Hkv, page_size, max_pages, num_pages, kv_dtype;
+    int* status;                          // optional device status word (SKV_DEV_BAD_PAGE)
     float log2_theta;
     __half* meta;                         // optional [B, Hkv, nb, 2, D] min/max block metadata to keep current
     int meta_block, meta_nb;
@@ -98,6 +99,10 @@ rope_quant_append_kernel(const Params p) {
     const int lp = pos / p.page_size, slot = pos - lp * p.page_size;
     if (pos < 0 || lp >= p.max_pages) return;   // no room left in this sequence's page list: nothing is stored
     const int page = p.page_table ? p.page_table[(long long)b * p.max_pages + lp] : b * p.max_pages + lp;
+    if ((unsigned)page >= (unsigned)p.num_pages) {   // a stale or corrupt table entry: store nothing, report it
+        if (lane == 0 && p.status) atomicOr(p.status, SKV_DEV_BAD_PAGE);
+        return;
+    }
     uint8_t* row = (is_v ? p.v_codes : p.k_codes) + page * p.sp + h * p.sh + slot * p.ss;
     *reinterpret_cast<uint16_t*>(row + lane * 2) = (uint16_t)(code[0] | (code[1] << 8));
     *reinterpret_cast<uint16_t*>(row + D / 2 + lane * 2) = (uint16_t)(code[2] | (code[3] << 8));
@@ -142,10 +147,10 @@ int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k
                           int D, int kv_dtype, int page_size, int max_pages, long long pool_stride_page,
                           long long pool_stride_head, long long pool_stride_slot, long long scale_stride_page,
                           long long scale_stride_head, float rope_theta, void* meta, int meta_block_size,
-                          int meta_num_blocks, int device, void* stream) {
+                          int meta_num_blocks, int num_pages, int* status, int device, void* stream) {
     if (!qkv || !q_out || !k_pool || !v_pool || !k_scale_pool || !v_scale_pool || !seq_lens)
         return fail(SKV_ERR_BAD_ARG, "skv_rope_quant_append: null pointer");
-    if (B <= 0 || Hq <= 0 || Hkv <= 0 || page_size <= 0 || max_pages <= 0)
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || page_size <= 0 || max_pages <= 0 || num_pages <= 0)
         return fail(SKV_ERR_BAD_ARG, "skv_rope_quant_append: sizes must be positive");
     if (D != app::D) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (128)", D);
     if (kv_dtype != SKV_KV_I8 && kv_dtype != SKV_KV_E4M3) return fail(SKV_ERR_UNSUPPORTED, "kv_dtype %d is not an 8-bit type", kv_dtype);
@@ -160,6 +165,7 @@ int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k
     p.sp = pool_stride_page; p.sh = pool_stride_head; p.ss = pool_stride_slot;
     p.csp = scale_stride_page; p.csh = scale_stride_head;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.max_pages = max_pages; p.kv_dtype = kv_dtype;
+    p.num_pages = num_pages; p.status = status;
     p.log2_theta = log2f(rope_theta);
     p.meta = static_cast<__half*>(meta);
     p.meta_block = meta_block_size > 0 ? meta_block_size : 1;

@@ -9,15 +9,19 @@
 // topk over the scores, gather of the chosen rows, optional int8 cast -- extended
 // by scaled quantisation and an always-kept window of recent tokens.
 //
-// Two launches, the evicted rows are never read:
-//   1. evict_select_kernel -- one 1024-thread CTA per (b, h): exact top-`budget`
-//      over the first T - recent scores (radix select, ascending positions), the
-//      last `recent` positions appended; optional re-ordering by descending score
-//      (the order torch.topk returns) with a shared-memory bitonic sort.
-//   2. evict_gather_quant_kernel -- D/8 lanes per surviving row, 16-byte loads of
-//      the K and V rows, row amax by shuffles, IEEE divide + round-half-even, one
-//      8-byte store of codes per lane.  HBM-bound: 2 x 256 B read and 2 x 128 B
-//      written per kept token at D = 128.
+// The evicted rows are never read.  Kernels:
+//   evict_fused_cluster_kernel -- the single-pass path (position order, rows of up to 32 K competing scores, D = 64
+//      or 128): a thread-block cluster of four 1024-thread CTAs per (b, h) keeps the row's score keys in registers,
+//      finds the exact budget-th largest with four radix passes whose digit histograms are summed across the
+//      cluster through distributed shared memory, writes the ascending position list, and then the same four CTAs
+//      gather and quantise that head's surviving K and V rows, a quarter of the list each -- no second launch and
+//      no wait for other heads.
+//   evict_select_cluster_kernel / evict_select_kernel + evict_gather_quant_kernel -- the two-launch path for
+//      everything else (descending-score order re-sorts with a shared-memory bitonic sort; longer rows take the
+//      single-CTA radix select).
+//   Quantisation: D/8 lanes per surviving row, 16-byte loads, row amax by shuffles, scale = amax / qmax by one IEEE
+//      divide per row, codes by multiplication with the reciprocal and a magic-number round-half-even, with the
+//      IEEE divide redone only where the product lies within 1e-4 of a rounding boundary (INT8 codes are bit-exact).
 #include <cooperative_groups.h>
 #include <cuda_fp8.h>
 
@@ -108,11 +112,7 @@ evict_select_kernel(const SelectParams p) {
 constexpr int CL = 4;   // CTAs per cluster
 constexpr int KR = 8;   // keys per thread
 
-__global__ void __cluster_dims__(CL, 1, 1) __launch_bounds__(SEL_THREADS)
-evict_select_cluster_kernel(const SelectParams p) {
-    pdl_launch_dependents();  // the kernel that consumes the kept positions may be scheduled now; it waits for this grid to finish
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
+__device__ __forceinline__ void cluster_select_row(const SelectParams& p, cooperative_groups::cluster_group& cluster) {
     constexpr int NW = SEL_THREADS / 32;
     __shared__ uint32_t hist[NW * 256];   // per-warp private digit counts
     __shared__ uint32_t chist[2][256];    // this CTA's folded counts, double-buffered across passes
@@ -287,7 +287,15 @@ evict_select_cluster_kernel(const SelectParams p) {
     }
     if (crank == 0)
         for (int i = tid; i < recent; i += SEL_THREADS) out[kb + i] = head + i;
+    __threadfence();  // the position list is read back by the other CTAs of the cluster in the fused kernel
     cluster.sync();   // nobody leaves while a neighbour may still read its shared memory
+}
+
+__global__ void __cluster_dims__(CL, 1, 1) __launch_bounds__(SEL_THREADS)
+evict_select_cluster_kernel(const SelectParams p) {
+    pdl_launch_dependents();  // the kernel that consumes the kept positions may be scheduled now; it waits for this grid to finish
+    cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+    cluster_select_row(p, cluster);
 }
 
 struct GatherParams {
@@ -431,6 +439,79 @@ evict_gather_quant_kernel(const GatherParams p) {
     }
 }
 
+
+// Selection and gather in one launch: after cluster_select_row the (b, h) row's ascending position list is complete
+// in global memory (and in L2); CTA c of the cluster takes list entries [c * per, (c + 1) * per).  Same lane layout
+// and quantisation as evict_gather_quant_kernel; U = 4 rows per lane group and step, the next step's positions
+// fetched while this step's rows are in flight.
+template <int D, int MODE>
+__global__ void __cluster_dims__(CL, 1, 1) __launch_bounds__(SEL_THREADS)
+evict_fused_cluster_kernel(const SelectParams p, const GatherParams g) {
+    cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+    cluster_select_row(p, cluster);
+
+    constexpr int LPR = D / 8;
+    constexpr int GPB = SEL_THREADS / LPR;
+    constexpr int U = 4;
+    const int crank = (int)cluster.block_rank();
+    const long long row = blockIdx.x / CL;                 // (b, h)
+    const int sub = threadIdx.x % LPR, grp = threadIdx.x / LPR;
+    const int per = (p.keep + CL - 1) / CL;
+    const int j0 = min(p.keep, crank * per), j1 = min(p.keep, j0 + per);
+    if (j0 >= j1) return;
+    const int* list = p.idx + row * p.keep;
+    const long long base = (row / g.H) * g.sb + (row % g.H) * g.sh + sub * 8;
+    const long long orow = row * p.keep;
+    int tn[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) tn[u] = __ldcg(list + min(j0 + u * GPB + grp, j1 - 1));
+    for (int jb = j0; jb < j1; jb += GPB * U) {
+        int t[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) t[u] = tn[u];
+        if (jb + GPB * U < j1) {   // block-uniform
+#pragma unroll
+            for (int u = 0; u < U; ++u) tn[u] = __ldcg(list + min(jb + GPB * U + u * GPB + grp, j1 - 1));
+        }
+        uint4 kr[U], vr[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {   // rows past the end repeat the slice's last row; only their stores are dropped
+            const long long src = base + (long long)max(t[u], 0) * g.st;
+            kr[u] = ld_stream16(g.k + src);
+            vr[u] = ld_stream16(g.v + src);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = jb + u * GPB + grp;
+            const bool valid = j < j1;
+            const long long r = orow + j;
+            if (MODE == SKV_QUANT_NONE) {
+                quant_row<MODE>(kr[u], sub, LPR, nullptr, nullptr, static_cast<__half*>(g.k_out) + r * D, valid);
+                quant_row<MODE>(vr[u], sub, LPR, nullptr, nullptr, static_cast<__half*>(g.v_out) + r * D, valid);
+            } else {
+                quant_row<MODE>(kr[u], sub, LPR, static_cast<uint8_t*>(g.k_out) + r * D, g.k_scale + r, nullptr, valid);
+                quant_row<MODE>(vr[u], sub, LPR, static_cast<uint8_t*>(g.v_out) + r * D, g.v_scale + r, nullptr, valid);
+            }
+        }
+    }
+}
+
+template <int D>
+static int launch_fused(const SelectParams& sp, const GatherParams& gp, int mode, long long rows, cudaStream_t st) {
+    const dim3 grid((unsigned)(rows * CL)), block(SEL_THREADS);
+    switch (mode) {
+        case SKV_QUANT_NONE: evict_fused_cluster_kernel<D, SKV_QUANT_NONE><<<grid, block, 0, st>>>(sp, gp); break;
+        case SKV_QUANT_INT8: evict_fused_cluster_kernel<D, SKV_QUANT_INT8><<<grid, block, 0, st>>>(sp, gp); break;
+        case SKV_QUANT_E4M3: evict_fused_cluster_kernel<D, SKV_QUANT_E4M3><<<grid, block, 0, st>>>(sp, gp); break;
+        default: evict_fused_cluster_kernel<D, SKV_QUANT_CAST><<<grid, block, 0, st>>>(sp, gp); break;
+    }
+    SKV_CUDA_TRY(cudaGetLastError());
+    return SKV_OK;
+}
+
+inline int& fused_flag() { static int on = 1; return on; }
+inline bool fused_enabled() { return fused_flag() != 0; }
+
 static size_t select_smem() { return (size_t)TopkSmem<SEL_THREADS>::WORDS * 4 + (size_t)MAX_KEEP * 8; }
 
 template <int D>
@@ -465,6 +546,12 @@ int skv_kv_evict_keep_count(int T, int budget, int recent) {
     const int r = recent < T ? recent : T;
     const int kb = budget < T - r ? budget : T - r;
     return kb + r;
+}
+
+// 1 (default): the single-launch cluster kernel serves the cases it covers; 0: always select and gather in two launches.
+int skv_kv_evict_set_fused(int on) {
+    evq::fused_flag() = on ? 1 : 0;
+    return SKV_OK;
 }
 
 int skv_kv_evict_quant(const void* k_cache, const void* v_cache, const float* scores, int* idx_out,
@@ -502,14 +589,6 @@ int skv_kv_evict_quant(const void* k_cache, const void* v_cache, const float* sc
     }
     evq::SelectParams sp;
     sp.scores = scores; sp.idx = idx_out; sp.T = T; sp.budget = budget; sp.recent = recent; sp.keep = keep; sp.order = order;
-    const int competing = T - (recent < T ? recent : T);
-    if (order == SKV_ORDER_POSITION && competing <= evq::CL * evq::SEL_THREADS * evq::KR && (long long)B * H * evq::CL <= 65535LL * 32) {
-        evq::evict_select_cluster_kernel<<<(unsigned)((long long)B * H * evq::CL), evq::SEL_THREADS, 0, st>>>(sp);
-    } else {
-        evq::evict_select_kernel<<<(unsigned)((long long)B * H), evq::SEL_THREADS, smem, st>>>(sp);
-    }
-    SKV_CUDA_TRY(cudaGetLastError());
-
     evq::GatherParams gp;
     gp.k = static_cast<const __half*>(k_cache);
     gp.v = static_cast<const __half*>(v_cache);
@@ -517,6 +596,20 @@ int skv_kv_evict_quant(const void* k_cache, const void* v_cache, const float* sc
     gp.k_out = k_out; gp.v_out = v_out; gp.k_scale = k_scale_out; gp.v_scale = v_scale_out;
     gp.H = H; gp.keep = keep; gp.rows_total = (long long)B * H * keep;
     gp.sb = kv_stride_b; gp.sh = kv_stride_h; gp.st = kv_stride_t;
+
+    const int competing = T - (recent < T ? recent : T);
+    const bool cluster_ok = order == SKV_ORDER_POSITION && competing <= evq::CL * evq::SEL_THREADS * evq::KR &&
+                            (long long)B * H * evq::CL <= 65535LL * 32;
+    if (cluster_ok && evq::fused_enabled() && (D == 128 || D == 64)) {   // one launch: select, then gather by the same cluster
+        return D == 128 ? evq::launch_fused<128>(sp, gp, quant_mode, (long long)B * H, st)
+                        : evq::launch_fused<64>(sp, gp, quant_mode, (long long)B * H, st);
+    }
+    if (cluster_ok) {
+        evq::evict_select_cluster_kernel<<<(unsigned)((long long)B * H * evq::CL), evq::SEL_THREADS, 0, st>>>(sp);
+    } else {
+        evq::evict_select_kernel<<<(unsigned)((long long)B * H), evq::SEL_THREADS, smem, st>>>(sp);
+    }
+    SKV_CUDA_TRY(cudaGetLastError());
     switch (D) {
         case 16: return evq::launch_gather<16>(gp, quant_mode, device, st);
         case 32: return evq::launch_gather<32>(gp, quant_mode, device, st);

@@ -29,7 +29,7 @@ namespace quest {
 constexpr int D = 128;
 constexpr int META_THREADS = 256;
 constexpr int SCORE_THREADS = 256;
-constexpr int ATT_THREADS = 256;
+constexpr int ATT_THREADS = 512;
 constexpr int MAX_SEL_TOKENS = 2048;  // top_k_blocks * block_size upper bound
 constexpr int MAX_TOPK = 256;
 constexpr int PAST_END = 1 << 30;  // flag in the slot word of a gathered token that lies past the sequence end
@@ -61,7 +61,8 @@ struct MetaParams {
     const int* page_table;  // [B, max_pages] or null
     const int* seq_lens;    // [B] or null
     __half* meta;           // [B, Hkv, nb, 2, D]
-    int B, Hkv, N, nb, block_size, page_size, max_pages;
+    int* status;            // optional device status word (SKV_DEV_BAD_PAGE)
+    int B, Hkv, N, nb, block_size, page_size, max_pages, num_pages;
 };
 
 __device__ __forceinline__ int phys_page(const int* page_table, int b, int max_pages, int lp) {
@@ -97,6 +98,7 @@ block_meta_build_kernel(const MetaParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane & 7, rw = lane >> 3;
     const long long total = (long long)p.B * p.Hkv * p.nb;
+    bool bad_page = false;
     for (long long item = (long long)blockIdx.x * (META_THREADS / 32) + warp; item < total;
          item += (long long)gridDim.x * (META_THREADS / 32)) {
         const int blk = (int)(item % p.nb);
@@ -120,7 +122,7 @@ block_meta_build_kernel(const MetaParams p) {
                 const int t = min(tb + 4 * u, t1 - 1);
                 const int lp = t / p.page_size;
                 slot[u] = t - lp * p.page_size;
-                page[u] = phys_page(p.page_table, b, p.max_pages, lp);
+                page[u] = checked_page(phys_page(p.page_table, b, p.max_pages, lp), p.num_pages, bad_page);
             }
             uint4 raw[RU];
             float sc[RU];
@@ -165,6 +167,7 @@ block_meta_build_kernel(const MetaParams p) {
             *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
         }
     }
+    report_bad_page(bad_page, p.status);
 }
 
 struct ScoreParams {
@@ -176,17 +179,19 @@ struct ScoreParams {
 };
 
 // grid (ceil(nb / blocks_per_cta), Hkv, B); 16 lanes per block (8 channels each), 2 blocks per warp step.
-// max(q*lo, q*hi) is q*hi for q > 0 and q*lo for q < 0 (lo <= hi), so with q split into its positive and negative
-// parts the bound is two FMAs per channel and head, one of which adds an exact zero.
+// With lo <= hi, max(q*lo, q*hi) = q*(hi+lo)/2 + |q|*(hi-lo)/2; hi+lo and hi-lo are exact in fp32 (fp16 inputs), the
+// halving is folded into q, and |q| is an operand modifier of the FMA, so a channel costs two FMAs per head and the
+// query needs one register per channel and head.  That leaves room for U = 8 blocks (sixteen 16-byte loads) in
+// flight per lane at 128 registers: two CTAs per SM then keep 128 KB of metadata in flight per SM.
 template <int MAXG>
-__global__ void __launch_bounds__(SCORE_THREADS)
+__global__ void __launch_bounds__(SCORE_THREADS, 2)
 quest_scores_kernel(const ScoreParams p, int blocks_per_cta) {
     pdl_launch_dependents();  // the kernel that consumes these results may be scheduled now; it waits for this grid to finish
     static_assert(MAXG == 4 || MAXG == 8, "the packed reduction below is written for 4 or 8 heads");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane & 15, rw = lane >> 4;
     const int h = blockIdx.y, b = blockIdx.z;
-    float qp[MAXG][8], qn[MAXG][8];
+    float qh[MAXG][8];   // half the query
 #pragma unroll
     for (int g = 0; g < MAXG; ++g) {
         float q[8];
@@ -195,11 +200,11 @@ quest_scores_kernel(const ScoreParams p, int blocks_per_cta) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) q[i] = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { qp[g][i] = fmaxf(q[i], 0.f); qn[g][i] = fminf(q[i], 0.f); }
+        for (int i = 0; i < 8; ++i) qh[g][i] = 0.5f * q[i];
     }
     const __half* mbase = p.meta + ((long long)b * p.Hkv + h) * p.nb * 2 * D + sub * 8;
     const int j0 = blockIdx.x * blocks_per_cta, j1 = min(p.nb, j0 + blocks_per_cta);
-    constexpr int U = 4;  // blocks per half-warp and step: eight 16-byte loads in flight per lane
+    constexpr int U = MAXG == 4 ? 8 : 4;  // blocks per half-warp and step
     for (int base = j0 + warp * 2 * U; base < j1; base += (SCORE_THREADS / 32) * 2 * U) {
         uint4 lo4[U], hi4[U];
 #pragma unroll
@@ -215,10 +220,16 @@ quest_scores_kernel(const ScoreParams p, int blocks_per_cta) {
             unpack8(lo4[u], lo);
             unpack8(hi4[u], hi);
 #pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float s = hi[i] + lo[i], d = hi[i] - lo[i];
+                lo[i] = s;   // hi + lo
+                hi[i] = d;   // hi - lo >= 0
+            }
+#pragma unroll
             for (int g = 0; g < MAXG; ++g) {
                 acc[g] = 0.f;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[g] = fmaf(qn[g][i], lo[i], fmaf(qp[g][i], hi[i], acc[g]));
+                for (int i = 0; i < 8; ++i) acc[g] = fmaf(qh[g][i], lo[i], fmaf(fabsf(qh[g][i]), hi[i], acc[g]));
             }
             // Sum over the 16 lanes of the half-warp, several heads at once: at each of the first steps a lane
             // keeps half of its values and hands the other half to its partner, so MAXG values cost
@@ -255,7 +266,6 @@ quest_scores_kernel(const ScoreParams p, int blocks_per_cta) {
                 head += up ? 1 : 0;
             }
             v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
-            if (MAXG == 4) v1 += 0.f;  // (for 4 heads the xor-8 step above was a plain sum, so all 16 lanes are covered)
             if (j < j1 && (sub & 1) == 0 && head < p.G)
                 p.scores[((long long)b * p.Hq + h * p.G + head) * p.nb + j] = v1 * p.scale;
         }
@@ -270,66 +280,95 @@ struct AttendParams {
     const int* seq_lens;
     __half* out;           // [B, Hq, D]
     int* block_idx;        // optional [B, Hq, top_k]
-    int Hq, G, N, nb, block_size, page_size, max_pages, top_k;
+    int* status;           // device status word (SKV_DEV_BAD_PAGE)
+    int Hq, G, N, nb, block_size, page_size, max_pages, num_pages, top_k;
     float scale;
 };
 
-// grid (B * Hq)
+constexpr int VSTAGE_TOKENS = 512;                                  // gathered tokens whose V rows are staged in shared memory
+constexpr size_t ATT_DYN_SMEM = (size_t)VSTAGE_TOKENS * (D + 4);    // V codes [512][128] then V scales [512]
+
+// grid (B * Hq), one 512-thread CTA per (sequence, query head), two CTAs per SM.
+// The kernel is a chain of dependent steps (select -> page lookup -> K gather -> softmax -> V gather), so what it costs
+// is the number of memory round trips.  They are cut to three: (1) the block scores, selected with shuffle-based
+// arg-max extraction when top_k <= 32 (no histogram passes); (2) the page ids of the gathered tokens; (3) ALL K rows
+// in one batch of 16-byte loads (8 lanes per row, 64 rows per pass, 8 passes in flight) while the V rows and V scales
+// of the same tokens travel to shared memory as per-thread asynchronous copies issued before the K loads -- by the
+// time the softmax weights exist the V rows are already on chip.
 template <int KVT>
-__global__ void __launch_bounds__(ATT_THREADS)
+__global__ void __launch_bounds__(ATT_THREADS, 2)
 quest_select_attend_kernel(const AttendParams p) {
-    pdl_wait_prior_grids();   // launched as a programmatic dependent of the scoring kernel: its results are complete from here on
+    extern __shared__ __align__(16) uint8_t vstage[];   // ATT_DYN_SMEM bytes
     __shared__ uint32_t tk[TopkSmem<ATT_THREADS>::WORDS];
     __shared__ int sel[MAX_TOPK];
     __shared__ float w[MAX_SEL_TOKENS];
     __shared__ int2 where[MAX_SEL_TOKENS];  // (page, slot) of every gathered token; PAST_END set in slot past the sequence end
     __shared__ float qs[D];
-    __shared__ float red[ATT_THREADS / 8 * 16 + 32];  // per row-group partial outputs are reduced through here
+    __shared__ float red[ATT_THREADS / 32];
     __shared__ float bcast[2];
+    constexpr int NWARP = ATT_THREADS / 32, GROUPS = ATT_THREADS / 8;
+    static_assert(MAX_SEL_TOKENS >= NWARP * D, "the weight array is reused for the per-warp partial outputs");
 
     const int row = blockIdx.x, hq = row % p.Hq, b = row / p.Hq, h = hq / p.G;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // q, seq_lens and the page table are older than the scoring kernel this launch depends on: read them first
     const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
     const int nb = (len + p.block_size - 1) / p.block_size;  // blocks this sequence really has
+    for (int i = tid; i < D; i += ATT_THREADS) qs[i] = __half2float(p.q[(long long)row * D + i]);
+    pdl_wait_prior_grids();   // launched as a programmatic dependent of the scoring kernel: its results are complete from here on
     const float* sc = p.scores + (long long)row * p.nb;
     const int kk = min(p.top_k, nb);
-    block_topk_sorted_auto<ATT_THREADS, 16>(sc, nb, kk, sel, tk);
-    for (int i = tid; i < D; i += ATT_THREADS) qs[i] = __half2float(p.q[(long long)row * D + i]);
+    if (kk <= 32 && nb <= ATT_THREADS * 4) block_topk_small<ATT_THREADS, 4>(sc, nb, kk, sel, reinterpret_cast<unsigned long long*>(tk));
+    else if (kk <= 32 && nb <= ATT_THREADS * 16) block_topk_small<ATT_THREADS, 16>(sc, nb, kk, sel, reinterpret_cast<unsigned long long*>(tk));
+    else block_topk_sorted_auto<ATT_THREADS, 16>(sc, nb, kk, sel, tk);
     __syncthreads();
     if (p.block_idx)
         for (int i = tid; i < p.top_k; i += ATT_THREADS) p.block_idx[(long long)row * p.top_k + i] = i < kk ? sel[i] : -1;
 
-    // ---- scores of the gathered tokens: 8 lanes per token row, 32 rows per pass
-    const int sub = tid & 7, grp = tid >> 3;  // grp in [0, 32)
+    const int sub = tid & 7, grp = tid >> 3;  // 8 lanes per token row; grp in [0, 64)
     const int ntok = kk * p.block_size;
-    float qv[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) qv[i] = qs[sub * 16 + i];
+    const bool staged = ntok <= VSTAGE_TOKENS;
+    float* vsc_sm = reinterpret_cast<float*>(vstage + (size_t)VSTAGE_TOKENS * D);
     // resolve every gathered token's page once (one page-table read per token, all in flight together)
+    bool bad_page = false;
     for (int r = tid; r < ntok; r += ATT_THREADS) {
         const int t = sel[r / p.block_size] * p.block_size + r % p.block_size;
         // a token past the end points at the last real token and carries a flag, so that every later load has a
         // valid address and needs no condition (conditional loads are issued one behind the other)
         const int tc = min(t, len - 1);
-        where[r] = make_int2(phys_page(p.page_table, b, p.max_pages, tc / p.page_size),
-                             (tc % p.page_size) | (t < len ? 0 : PAST_END));
+        const int pg = checked_page(phys_page(p.page_table, b, p.max_pages, tc / p.page_size), p.num_pages, bad_page);
+        const int slot = tc % p.page_size;
+        where[r] = make_int2(pg, slot | (t < len ? 0 : PAST_END));
+        if (staged) cp_async4(smem_u32(vsc_sm + r), p.v.scales + pg * p.v.csp + h * p.v.csh + slot);
     }
     __syncthreads();
+    if (staged) {   // V rows on their way to shared memory: 8 x 16 bytes per row, nothing held in registers
+        const uint32_t vdst = smem_u32(vstage);
+        for (int c = tid; c < ntok * 8; c += ATT_THREADS) {
+            const int2 pw = where[c >> 3];
+            cp_async16(vdst + c * 16, p.v.codes + pw.x * p.v.sp + h * p.v.sh + (pw.y & ~PAST_END) * p.v.ss + (c & 7) * 16);
+        }
+    }
+
+    // ---- scores of the gathered tokens: 8 lanes per token row, 64 rows per pass
+    float qv[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) qv[i] = qs[sub * 16 + i];
     constexpr int RU = 8;  // token rows per group and step: their code and scale loads are issued back to back
     float mx = -INFINITY;
-    for (int r0 = 0; r0 < ntok; r0 += RU * (ATT_THREADS / 8)) {  // uniform trip count: the shuffles need whole warps
+    for (int r0 = 0; r0 < ntok; r0 += RU * GROUPS) {  // uniform trip count: the shuffles need whole warps
         uint4 raw[RU];
         float ksc[RU];
 #pragma unroll
         for (int u = 0; u < RU; ++u) {
-            const int2 pw = where[min(r0 + u * (ATT_THREADS / 8) + grp, ntok - 1)];
+            const int2 pw = where[min(r0 + u * GROUPS + grp, ntok - 1)];
             const int slot = pw.y & ~PAST_END;
             raw[u] = ld_stream16(p.k.codes + pw.x * p.k.sp + h * p.k.sh + slot * p.k.ss + sub * 16);
             ksc[u] = __ldg(p.k.scales + pw.x * p.k.csp + h * p.k.csh + slot);
         }
 #pragma unroll
         for (int u = 0; u < RU; ++u) {
-            const int r = r0 + u * (ATT_THREADS / 8) + grp;
+            const int r = r0 + u * GROUPS + grp;
             const bool valid = r < ntok && !(where[min(r, ntok - 1)].y & PAST_END);
             float x[16];
             unpack16<KVT>(raw[u], x);
@@ -348,7 +387,7 @@ quest_select_attend_kernel(const AttendParams p) {
     if (lane == 0) red[warp] = mx;
     __syncthreads();
     if (warp == 0) {
-        float m2 = lane < ATT_THREADS / 32 ? red[lane] : -INFINITY;
+        float m2 = lane < NWARP ? red[lane] : -INFINITY;
         m2 = warp_max(m2);
         if (lane == 0) bcast[0] = m2;
     }
@@ -361,11 +400,11 @@ quest_select_attend_kernel(const AttendParams p) {
         sum += e;
     }
     sum = warp_sum(sum);
-    __syncthreads();
     if (lane == 0) red[warp] = sum;
+    if (staged) cp_async_wait_all();   // this thread's V copies have landed; the barrier below publishes everybody's
     __syncthreads();
     if (warp == 0) {
-        float s2 = lane < ATT_THREADS / 32 ? red[lane] : 0.f;
+        float s2 = lane < NWARP ? red[lane] : 0.f;
         s2 = warp_sum(s2);
         if (lane == 0) bcast[1] = s2;
     }
@@ -376,35 +415,47 @@ quest_select_attend_kernel(const AttendParams p) {
     float acc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-    for (int r0 = grp; r0 < ntok; r0 += RU * (ATT_THREADS / 8)) {
-        uint4 raw[RU];
-        float wt[RU];
-#pragma unroll
-        for (int u = 0; u < RU; ++u) {
-            const int r = r0 + u * (ATT_THREADS / 8);
-            const int2 pw = where[min(r, ntok - 1)];
-            const int slot = pw.y & ~PAST_END;
-            raw[u] = ld_stream16(p.v.codes + pw.x * p.v.sp + h * p.v.sh + slot * p.v.ss + sub * 16);
-            // the weight of a token past the end is already an exact zero; rows past ntok get zero here
-            const float vs = __ldg(p.v.scales + pw.x * p.v.csp + h * p.v.csh + slot);
-            wt[u] = r < ntok ? w[min(r, ntok - 1)] * vs : 0.f;
-        }
-#pragma unroll
-        for (int u = 0; u < RU; ++u) {
+    if (staged) {
+        // the weight of a token past the end is an exact zero and its row is a real (clamped) one, so no flag test
+        for (int r = grp; r < ntok; r += GROUPS) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(vstage + (size_t)r * D + sub * 16);
+            const float wt = w[r] * vsc_sm[r];
             float x[16];
-            unpack16<KVT>(raw[u], x);
+            unpack16<KVT>(raw, x);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] = fmaf(wt[u], x[i], acc[i]);
+            for (int i = 0; i < 16; ++i) acc[i] = fmaf(wt, x[i], acc[i]);
+        }
+    } else {
+        for (int r0 = grp; r0 < ntok; r0 += RU * GROUPS) {
+            uint4 raw[RU];
+            float wt[RU];
+#pragma unroll
+            for (int u = 0; u < RU; ++u) {
+                const int r = r0 + u * GROUPS;
+                const int2 pw = where[min(r, ntok - 1)];
+                const int slot = pw.y & ~PAST_END;
+                raw[u] = ld_stream16(p.v.codes + pw.x * p.v.sp + h * p.v.sh + slot * p.v.ss + sub * 16);
+                // the weight of a token past the end is already an exact zero; rows past ntok get zero here
+                const float vs = __ldg(p.v.scales + pw.x * p.v.csp + h * p.v.csh + slot);
+                wt[u] = r < ntok ? w[min(r, ntok - 1)] * vs : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < RU; ++u) {
+                float x[16];
+                unpack16<KVT>(raw[u], x);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[i] = fmaf(wt[u], x[i], acc[i]);
+            }
         }
     }
-    // reduce the 32 row-groups: first inside each warp (4 groups), then across the 8 warps through shared memory
+    // reduce the 64 row-groups: first inside each warp (4 groups), then across the warps through shared memory
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 8);
         acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 16);
     }
     __syncthreads();
-    float* part = w;  // the token weights are no longer needed: reuse as [8 warps][D]
+    float* part = w;  // the token weights are no longer needed: reuse as [NWARP][D]
     if (lane < 8) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) part[warp * D + sub * 16 + i] = acc[i];
@@ -413,9 +464,10 @@ quest_select_attend_kernel(const AttendParams p) {
     for (int d = tid; d < D; d += ATT_THREADS) {
         float o = 0.f;
 #pragma unroll
-        for (int w2 = 0; w2 < ATT_THREADS / 32; ++w2) o += part[w2 * D + d];
+        for (int w2 = 0; w2 < NWARP; ++w2) o += part[w2 * D + d];
         p.out[(long long)row * D + d] = __float2half_rn(o * inv);
     }
+    report_bad_page(bad_page, p.status);
 }
 
 }  // namespace quest
@@ -444,13 +496,13 @@ size_t skv_quest_workspace_bytes(int B, int Hq, int N, int block_size) {
 
 int skv_quest_build_meta(const void* k_pool, const float* k_scale_pool, const int* page_table, const int* seq_lens,
                          void* meta_out, int B, int N, int Hkv, int D, int kv_dtype, int block_size, int page_size,
-                         int max_pages, long long pool_stride_page, long long pool_stride_head,
+                         int max_pages, int num_pages, long long pool_stride_page, long long pool_stride_head,
                          long long pool_stride_slot, long long scale_stride_page, long long scale_stride_head,
-                         int device, void* stream) {
+                         int* status, int device, void* stream) {
     if (!meta_out) return fail(SKV_ERR_BAD_ARG, "skv_quest_build_meta: null output");
     int rc = check_pool_args(k_pool, k_scale_pool, page_size, pool_stride_slot, "skv_quest_build_meta");
     if (rc) return rc;
-    if (B <= 0 || N <= 0 || Hkv <= 0 || block_size <= 0 || max_pages <= 0)
+    if (B <= 0 || N <= 0 || Hkv <= 0 || block_size <= 0 || max_pages <= 0 || num_pages <= 0)
         return fail(SKV_ERR_BAD_ARG, "skv_quest_build_meta: sizes must be positive");
     if (D != quest::D) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (128)", D);
     if (kv_dtype != SKV_KV_I8 && kv_dtype != SKV_KV_E4M3) return fail(SKV_ERR_UNSUPPORTED, "kv_dtype %d is not an 8-bit type", kv_dtype);
@@ -464,6 +516,7 @@ int skv_quest_build_meta(const void* k_pool, const float* k_scale_pool, const in
     p.page_table = page_table; p.seq_lens = seq_lens; p.meta = static_cast<__half*>(meta_out);
     p.B = B; p.Hkv = Hkv; p.N = N; p.nb = skv_quest_num_blocks(N, block_size);
     p.block_size = block_size; p.page_size = page_size; p.max_pages = max_pages;
+    p.num_pages = num_pages; p.status = status;
     const long long items = (long long)B * Hkv * p.nb;
     long long blocks = (items + quest::META_THREADS / 32 - 1) / (quest::META_THREADS / 32);
     const long long cap = (long long)sm_count(device) * 16;
@@ -479,14 +532,15 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
                      const float* v_scale_pool, const int* page_table, const int* seq_lens, const void* meta,
                      void* out, int* block_idx_out, void* workspace, size_t workspace_bytes, int B, int N, int Hq,
                      int Hkv, int D, int kv_dtype, int block_size, int top_k_blocks, int page_size, int max_pages,
-                     long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
+                     int num_pages, long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
                      long long scale_stride_page, long long scale_stride_head, float scale, int device, void* stream) {
     if (!q || !meta || !out) return fail(SKV_ERR_BAD_ARG, "skv_quest_decode: null tensor pointer");
     int rc = check_pool_args(k_pool, k_scale_pool, page_size, pool_stride_slot, "skv_quest_decode");
     if (rc) return rc;
     rc = check_pool_args(v_pool, v_scale_pool, page_size, pool_stride_slot, "skv_quest_decode");
     if (rc) return rc;
-    if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || max_pages <= 0) return fail(SKV_ERR_BAD_ARG, "skv_quest_decode: sizes must be positive");
+    if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || max_pages <= 0 || num_pages <= 0)
+        return fail(SKV_ERR_BAD_ARG, "skv_quest_decode: sizes must be positive");
     if (Hq % Hkv != 0) return fail(SKV_ERR_BAD_ARG, "Hq=%d must be divisible by Hkv=%d", Hq, Hkv);
     const int G = Hq / Hkv;
     if (G > 8) return fail(SKV_ERR_UNSUPPORTED, "group size %d exceeds 8", G);
@@ -513,11 +567,12 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
     sp.Hq = Hq; sp.Hkv = Hkv; sp.G = G; sp.nb = nb; sp.scale = scale;
     const long long rows = (long long)B * Hkv;
 #ifndef SKV_QUEST_SCORE_CTAS_PER_SM
-#define SKV_QUEST_SCORE_CTAS_PER_SM 4
+#define SKV_QUEST_SCORE_CTAS_PER_SM 2   // what the kernel's 128 registers allow: one wave of CTAs
 #endif
     long long want = ((long long)sm_count(device) * SKV_QUEST_SCORE_CTAS_PER_SM + rows - 1) / rows;
     int blocks_per_cta = (int)((nb + want - 1) / want);
-    blocks_per_cta = ((blocks_per_cta + 63) / 64) * 64;  // one CTA step covers 8 warps x 2 half-warps x 4 blocks
+    const int step = G <= 4 ? 128 : 64;   // one CTA step covers 8 warps x 2 half-warps x U blocks
+    blocks_per_cta = ((blocks_per_cta + step - 1) / step) * step;
     dim3 g1((nb + blocks_per_cta - 1) / blocks_per_cta, Hkv, B);
     if (G <= 4) quest::quest_scores_kernel<4><<<g1, quest::SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);
     else quest::quest_scores_kernel<8><<<g1, quest::SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);
@@ -533,8 +588,16 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
     ap.out = static_cast<__half*>(out); ap.block_idx = block_idx_out;
     ap.Hq = Hq; ap.G = G; ap.N = N; ap.nb = nb; ap.block_size = block_size; ap.page_size = page_size;
     ap.max_pages = max_pages; ap.top_k = top_k_blocks; ap.scale = scale;
-    if (kv_dtype == SKV_KV_E4M3) SKV_CUDA_TRY(launch_pdl(quest::quest_select_attend_kernel<SKV_KV_E4M3>, dim3((unsigned)(B * Hq)), dim3(quest::ATT_THREADS), 0, st, ap));
-    else SKV_CUDA_TRY(launch_pdl(quest::quest_select_attend_kernel<SKV_KV_I8>, dim3((unsigned)(B * Hq)), dim3(quest::ATT_THREADS), 0, st, ap));
+    ap.num_pages = num_pages;
+    ap.status = reinterpret_cast<int*>(workspace);   // status word at offset 0, as skv_workspace_status reads it
+    static bool configured[64] = {false};
+    if (device < 64 && !configured[device]) {
+        SKV_CUDA_TRY(cudaFuncSetAttribute(quest::quest_select_attend_kernel<SKV_KV_E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)quest::ATT_DYN_SMEM));
+        SKV_CUDA_TRY(cudaFuncSetAttribute(quest::quest_select_attend_kernel<SKV_KV_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)quest::ATT_DYN_SMEM));
+        configured[device] = true;
+    }
+    if (kv_dtype == SKV_KV_E4M3) SKV_CUDA_TRY(launch_pdl(quest::quest_select_attend_kernel<SKV_KV_E4M3>, dim3((unsigned)(B * Hq)), dim3(quest::ATT_THREADS), quest::ATT_DYN_SMEM, st, ap));
+    else SKV_CUDA_TRY(launch_pdl(quest::quest_select_attend_kernel<SKV_KV_I8>, dim3((unsigned)(B * Hq)), dim3(quest::ATT_THREADS), quest::ATT_DYN_SMEM, st, ap));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }

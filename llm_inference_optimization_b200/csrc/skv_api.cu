@@ -7,7 +7,7 @@ extern "C" {
 const char* skv_last_error(void) { return skv::last_error_buf(); }
 
 // ABI revision; bumped whenever a signature in include/skv_b200.h changes.
-int skv_abi_version(void) { return 1; }
+int skv_abi_version(void) { return 2; }
 
 // Reads the device status word at offset 0 of a workspace (bit SKV_DEV_TIMEOUT set
 // when a bounded wait inside a kernel gave up).  Synchronises `stream`.

@@ -30,6 +30,8 @@
 
 // Bit set in the per-workspace device status word when a bounded wait gave up.
 #define SKV_DEV_TIMEOUT 1
+// Bit set when a page id read from a caller's page table lay outside the pools (the access was redirected or skipped).
+#define SKV_DEV_BAD_PAGE 2
 
 namespace skv {
 
@@ -103,6 +105,18 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 // Device helpers
 // ---------------------------------------------------------------------------
 #if defined(__CUDACC__)
+
+// A page id from a caller's table, made safe to turn into an address: an id outside [0, num_pages) becomes page 0
+// and raises `bad`.  Branch-free on purpose -- a conditional atomic between two loads would pin their order and
+// serialise a batch of gathers; the caller reports once, after its loads, with report_bad_page().  Never traps.
+__device__ __forceinline__ int checked_page(int page, int num_pages, bool& bad) {
+    const bool out_of_range = (unsigned)page >= (unsigned)num_pages;
+    bad |= out_of_range;
+    return out_of_range ? 0 : page;
+}
+__device__ __forceinline__ void report_bad_page(bool bad, int* status) {
+    if (bad && status) atomicOr(status, SKV_DEV_BAD_PAGE);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -187,6 +201,18 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
         : "memory");
+}
+
+// Per-thread asynchronous copies global -> shared (Ampere-style cp.async): the data never occupies a register, so a
+// thread can keep many of them in flight; completion is awaited by the issuing thread with cp_async_wait_all().
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {

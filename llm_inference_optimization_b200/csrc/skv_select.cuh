@@ -339,6 +339,65 @@ __device__ void block_topk_sorted_cached(const float* sc, int T, int k, int* out
     __syncthreads();
 }
 
+// Exact top-k for a SMALL k (k <= 32) over T <= NT * R scores: arg-max extraction instead of histogram passes.
+// Every score becomes a 64-bit key (order-preserving score bits, then the complemented position, so that among equal
+// scores the lower position is the larger key).  Each warp extracts the k best of its contiguous segment with
+// shuffles only (lane i keeps the i-th best), the NT/32 candidate lists meet in shared memory, and warp 0 extracts
+// the k best of those the same way and writes their positions in ascending order.  Two barriers in all, against six
+// per pass of the radix routine.  `cand` is NT 64-bit words of shared memory.  All NT threads must call it.
+template <int R>
+__device__ __forceinline__ unsigned long long warp_extract_topk(unsigned long long (&key)[R], int k, int lane) {
+    unsigned long long mine = 0ull;
+    for (int it = 0; it < k; ++it) {
+        unsigned long long m = key[0];
+#pragma unroll
+        for (int j = 1; j < R; ++j) m = key[j] > m ? key[j] : m;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long v = __shfl_xor_sync(0xffffffffu, m, o);
+            m = v > m ? v : m;
+        }
+        if (lane == it) mine = m;
+#pragma unroll
+        for (int j = 0; j < R; ++j)
+            if (key[j] == m) key[j] = 0ull;   // keys are unique (the position is part of them); 0 never wins again
+    }
+    return mine;
+}
+
+template <int NT, int R>
+__device__ void block_topk_small(const float* sc, int T, int k, int* out, unsigned long long* cand) {
+    constexpr int NW = NT / 32;
+    static_assert(NW <= 32, "warp 0 holds one candidate list per lane group");
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (k <= 0) return;
+    unsigned long long key[R];
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+        const int i = (warp * R + j) * 32 + lane;
+        key[j] = i < T ? ((unsigned long long)score_key(sc[i]) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i) : 0ull;
+    }
+    cand[warp * 32 + lane] = warp_extract_topk<R>(key, k, lane);   // lanes >= k hold 0
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long k2[NW];
+#pragma unroll
+        for (int j = 0; j < NW; ++j) k2[j] = cand[j * 32 + lane];
+        const unsigned long long best = warp_extract_topk<NW>(k2, k, lane);
+        // lane i < k holds the i-th best (0 when fewer than k scores exist): order the positions ascending
+        const uint32_t pos = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull);
+        const bool have = best != 0ull;
+        int rank = 0;
+        for (int i = 0; i < k; ++i) {
+            const uint32_t other = __shfl_sync(0xffffffffu, pos, i);
+            const bool oh = __shfl_sync(0xffffffffu, (int)have, i) != 0;
+            rank += (oh && other < pos) ? 1 : 0;
+        }
+        if (have && lane < k) out[rank] = (int)pos;
+    }
+    __syncthreads();
+}
+
 // Picks the register-cached routine when the row is short enough for R keys per thread.
 template <int NT, int R>
 __device__ __forceinline__ void block_topk_sorted_auto(const float* sc, int T, int k, int* out, uint32_t* sm) {

@@ -37,6 +37,39 @@ inline EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// A decode step encodes the same maps again and again (one call per layer and token over caches that do not move),
+// so the last few encodings are kept per host thread, keyed by every argument that goes into them.
+template <typename Pos>
+struct TmapCache {
+    static constexpr int SLOTS = 128;
+    struct Entry {
+        long long key[12];
+        CUtensorMap map;
+        Pos pos;
+        bool valid = false;
+    };
+    Entry e[SLOTS];
+    const Entry* find(const long long (&key)[12]) const {
+        const Entry& x = e[slot(key)];
+        if (!x.valid) return nullptr;
+        for (int i = 0; i < 12; ++i)
+            if (x.key[i] != key[i]) return nullptr;
+        return &x;
+    }
+    void put(const long long (&key)[12], const CUtensorMap& m, const Pos& pos) {
+        Entry& x = e[slot(key)];
+        for (int i = 0; i < 12; ++i) x.key[i] = key[i];
+        x.map = m;
+        x.pos = pos;
+        x.valid = true;
+    }
+    static int slot(const long long (&key)[12]) {
+        unsigned long long h = 1469598103934665603ull;
+        for (int i = 0; i < 12; ++i) h = (h ^ (unsigned long long)key[i]) * 1099511628211ull;
+        return (int)((h >> 20) % SLOTS);
+    }
+};
+
 // Where each logical coordinate sits among the tensor map's dimensions 1..4
 // (dimension 0 is always the contiguous channel run).
 struct KvMapPos {
@@ -50,6 +83,14 @@ struct KvMapPos {
 inline int make_kv_tmap(CUtensorMap* out, KvMapPos* pos, const void* base, int elem_bytes, int inner_elems,
                         int n_half, long long B, long long N, long long Hkv, long long stride_b, long long stride_n,
                         long long stride_h, int tile_tokens) {
+    static thread_local TmapCache<KvMapPos> cache;
+    const long long key[12] = {(long long)reinterpret_cast<uintptr_t>(base), elem_bytes, inner_elems, n_half, B, N, Hkv,
+                               stride_b, stride_n, stride_h, tile_tokens, 0};
+    if (const auto* hit = cache.find(key)) {
+        *out = hit->map;
+        *pos = hit->pos;
+        return SKV_OK;
+    }
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(SKV_ERR_DRIVER, "cuTensorMapEncodeTiled entry point not available");
     if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
@@ -93,6 +134,7 @@ inline int make_kv_tmap(CUtensorMap* out, KvMapPos* pos, const void* base, int e
     CUresult r = enc(out, dt, 5, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SKV_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    cache.put(key, *out, *pos);
     return SKV_OK;
 }
 
@@ -106,6 +148,14 @@ struct PoolMapPos {
 inline int make_pool_tmap(CUtensorMap* out, PoolMapPos* pos, const void* base, int D, long long num_pages,
                           long long Hkv, long long page_size, long long stride_page, long long stride_head,
                           long long stride_slot, int box_slots) {
+    static thread_local TmapCache<PoolMapPos> cache;
+    const long long key[12] = {(long long)reinterpret_cast<uintptr_t>(base), D, num_pages, Hkv, page_size, stride_page,
+                               stride_head, stride_slot, box_slots, 0, 0, 1};
+    if (const auto* hit = cache.find(key)) {
+        *out = hit->map;
+        *pos = hit->pos;
+        return SKV_OK;
+    }
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(SKV_ERR_DRIVER, "cuTensorMapEncodeTiled entry point not available");
     if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
@@ -139,6 +189,7 @@ inline int make_pool_tmap(CUtensorMap* out, PoolMapPos* pos, const void* base, i
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SKV_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    cache.put(key, *out, *pos);
     return SKV_OK;
 }
 

@@ -87,8 +87,12 @@ def _pool_args(kv: PagedKV):
     return (kp.stride(0), kp.stride(1), kp.stride(2), ks.stride(0), ks.stride(1))
 
 
-def build_block_meta(kv: PagedKV, block_size: int = 64, max_seq_len: int | None = None) -> Tensor:
-    """Channel-wise min/max of the dequantised keys per block: fp16 ``[B, Hkv, nb, 2, D]``."""
+def build_block_meta(kv: PagedKV, block_size: int = 64, max_seq_len: int | None = None, *,
+                     status: Tensor | None = None) -> Tensor:
+    """Channel-wise min/max of the dequantised keys per block: fp16 ``[B, Hkv, nb, 2, D]``.
+
+    ``status`` (optional int32 device tensor of one element) receives ``SKV_DEV_BAD_PAGE`` (2) when a page-table
+    entry lies outside the pool; page 0 is read in its place."""
     strides = _pool_args(kv)
     lib = _lib.load()
     _, Hkv, P, D = kv.k_pool.shape
@@ -99,8 +103,8 @@ def build_block_meta(kv: PagedKV, block_size: int = 64, max_seq_len: int | None 
     rc = lib.skv_quest_build_meta(
         kv.k_pool.data_ptr(), kv.k_scale.data_ptr(), None if kv.page_table is None else kv.page_table.data_ptr(),
         None if kv.seq_lens is None else kv.seq_lens.data_ptr(), meta.data_ptr(), kv.batch, N, Hkv, D,
-        _C._code_dtype(kv.k_pool), int(block_size), P, kv.max_pages, *strides, dev,
-        torch.cuda.current_stream(kv.k_pool.device).cuda_stream)
+        _C._code_dtype(kv.k_pool), int(block_size), P, kv.max_pages, kv.k_pool.shape[0], *strides,
+        None if status is None else status.data_ptr(), dev, torch.cuda.current_stream(kv.k_pool.device).cuda_stream)
     _lib.check(rc, "build_block_meta")
     return meta
 
@@ -131,20 +135,22 @@ def quest_sparse_decode(Q: Tensor, kv: PagedKV, meta: Tensor, scale: float, bloc
         None if kv.page_table is None else kv.page_table.data_ptr(),
         None if kv.seq_lens is None else kv.seq_lens.data_ptr(), meta.data_ptr(), out.data_ptr(),
         None if idx is None else idx.data_ptr(), ws.data_ptr(), ws.numel(), B, N, Hq, Hkv, D,
-        _C._code_dtype(kv.k_pool), int(block_size), int(top_k_blocks), P, kv.max_pages, *strides, float(scale), dev,
+        _C._code_dtype(kv.k_pool), int(block_size), int(top_k_blocks), P, kv.max_pages, kv.k_pool.shape[0], *strides,
+        float(scale), dev,
         torch.cuda.current_stream(Q.device).cuda_stream)
     _lib.check(rc, "quest_sparse_decode")
     return (out, idx) if return_indices else out
 
 
 def rope_quant_append(qkv: Tensor, kv: PagedKV, Hq: int, rope_theta: float, *, meta: Tensor | None = None,
-                      block_size: int = 64) -> Tensor:
+                      block_size: int = 64, status: Tensor | None = None) -> Tensor:
     """RoPE the new token's q and k, quantise k and v and store them at position ``seq_lens[b]`` of the cache.
 
     ``qkv`` ``[B, (Hq + 2*Hkv) * 128]`` fp16 or bf16 (fused projection output); returns the rotated query
     ``[B, Hq, 128]`` fp16.  ``kv.seq_lens`` is read, not advanced.  With ``meta`` (the tensor
     ``build_block_meta`` returns) the min/max metadata of the block that receives the token is updated in the
-    same launch (``skv_rope_quant_append``).
+    same launch (``skv_rope_quant_append``).  A page-table entry outside the pool stores nothing and sets bit
+    ``SKV_DEV_BAD_PAGE`` (2) in ``status`` (an int32 device tensor of one element), when one is given.
     """
     strides = _pool_args(kv)
     _, Hkv, P, D = kv.k_pool.shape
@@ -161,6 +167,7 @@ def rope_quant_append(qkv: Tensor, kv: PagedKV, Hq: int, rope_theta: float, *, m
         kv.k_scale.data_ptr(), kv.v_scale.data_ptr(), None if kv.page_table is None else kv.page_table.data_ptr(),
         kv.seq_lens.data_ptr(), B, Hq, Hkv, D, _C._code_dtype(kv.k_pool), P, kv.max_pages, *strides, float(rope_theta),
         None if meta is None else meta.data_ptr(), int(block_size), 0 if meta is None else meta.shape[2],
+        kv.k_pool.shape[0], None if status is None else status.data_ptr(),
         _C._dev_index(qkv), torch.cuda.current_stream(qkv.device).cuda_stream)
     _lib.check(rc, "rope_quant_append")
     return q

@@ -84,5 +84,35 @@ def test_config3_full_size(cuda_device):
     # descending-score order of the same call is a permutation of the same set
     rs = skv.fused_kv_evict(Kd, Vd, sd, 4096, recent_tokens=64, quant="int8", order="score", return_aux=True)
     assert torch.equal(rs.indices.cpu().long().sort(-1).values, idx)
-    s_sorted = torch.gather(scores, 2, rs.indices.cpu().long())
-    assert (s_sorted[..., :4095] >= s_sorted[..., 1:4096]).all() or True  # recent rows are not score-ordered
+    # the order torch.topk returns: all 4160 kept rows by descending score (the recent window carries +inf in the
+    # selection but is ordered here by its real scores), equal scores by ascending position
+    order_idx = rs.indices.cpu().long()
+    s_sorted = torch.gather(scores, 2, order_idx)
+    assert (s_sorted[..., :-1] >= s_sorted[..., 1:]).all()
+    ties = s_sorted[..., :-1] == s_sorted[..., 1:]
+    assert (order_idx[..., :-1][ties] < order_idx[..., 1:][ties]).all()
+    want_order = torch.gather(idx, 2, torch.sort(torch.gather(scores, 2, idx), dim=-1, descending=True, stable=True).indices)
+    assert torch.equal(order_idx, want_order)
+
+
+@pytest.mark.parametrize("quant", ["int8", "fp8", "none"])
+@pytest.mark.parametrize("B,H,T,D,budget,recent", [(4, 8, 32768, 128, 4096, 64), (2, 3, 5000, 64, 300, 7),
+                                                   (1, 2, 96, 128, 10, 90), (1, 1, 40, 128, 64, 0)])
+def test_single_launch_and_two_launch_paths_agree(cuda_device, lib, quant, B, H, T, D, budget, recent):
+    """The cluster kernel that selects and gathers in one launch against the select + gather launches: bit-identical."""
+    K, V, scores = workloads.eviction(B, H, T, D, rounds=4, seed=T + 1)
+    Kd, Vd, sd = K.to(cuda_device), V.to(cuda_device), scores.to(cuda_device)
+    kw = dict(recent_tokens=recent, return_aux=True)
+    kw.update(dict(use_int8=False, order="position") if quant == "none" else dict(quant=quant))
+    try:
+        assert lib.skv_kv_evict_set_fused(1) == 0
+        one = skv.fused_kv_evict(Kd, Vd, sd, budget, **kw)
+        assert lib.skv_kv_evict_set_fused(0) == 0
+        two = skv.fused_kv_evict(Kd, Vd, sd, budget, **kw)
+    finally:
+        lib.skv_kv_evict_set_fused(1)
+    assert torch.equal(one.indices, two.indices)
+    assert torch.equal(one.indices.cpu().long(), oracle.eviction_keep_indices(scores, budget, recent))
+    assert torch.equal(one.K.view(torch.uint8), two.K.view(torch.uint8)) and torch.equal(one.V.view(torch.uint8), two.V.view(torch.uint8))
+    if quant != "none":
+        assert torch.equal(one.k_scale, two.k_scale) and torch.equal(one.v_scale, two.v_scale)

@@ -48,3 +48,16 @@ def test_noalloc_entry_rejects_problems_beyond_its_scratch(cuda_device, lib):
     out = torch.empty_like(Q)
     with pytest.raises(RuntimeError, match="scratch"):
         call_noalloc(lib, Q, K, K, 1.0, out)
+
+
+def test_noalloc_status_word_is_readable_and_clean(cuda_device, lib):
+    """The built-in array's status word can be read back (a caller of this entry never holds a workspace pointer)."""
+    import ctypes
+    Q, K, V, scale = workloads.dense_gqa(4096, seed=33)
+    Qd, Kd, Vd = Q.to(cuda_device), K.to(cuda_device), V.to(cuda_device)
+    out = torch.empty_like(Qd)
+    call_noalloc(lib, Qd, Kd, Vd, scale, out)
+    st = ctypes.c_int(-1)
+    rc = lib.skv_gqa_decode_noalloc_status(cuda_device.index, torch.cuda.current_stream(cuda_device).cuda_stream, ctypes.byref(st))
+    _lib.check(rc, "skv_gqa_decode_noalloc_status")
+    assert st.value == 0
