@@ -27,6 +27,56 @@ def ideal_bytes(cfg: ds.ModelConfig, lens: torch.Tensor, world: int) -> dict:
     return {"weight_bytes_per_gpu": int(weights), "kv_bytes_per_gpu": int(kv)}
 
 
+PARITY_CFG = ds.ModelConfig(layers=2, hidden=1024, Hq=32, Hkv=8, D=128, mlp=2048, vocab=1024)
+PARITY_TOL = {"max_abs_over_logit_scale": 3e-2, "cos_min": 0.999}
+
+
+def tp_parity(world: int, rank: int, dev, fused_allreduce: bool) -> dict | None:
+    """Tensor-parallel ranks against one rank, on real GPUs, before anything is timed.
+
+    A 2-layer model of reduced width (same head layout, so it shards over up to 8 ranks) takes one decode step on
+    all ranks with the all-reduce the benchmark uses, and on rank 0 alone as a single-rank model built from the same
+    full weights and cache bytes.  bf16 sums in a different order: the logits must agree to a few percent of the
+    logit scale.  Raises on rank 0 (after every rank has left the collective calls) when they do not."""
+    cfg = PARITY_CFG
+    lens = torch.tensor([700, 37, 100, 1500], dtype=torch.int32)
+    tok = torch.tensor([3, 100, 250, 999], device=dev)
+    m = ds.DecodeModel(cfg, shard_heads(cfg.Hq, cfg.Hkv, world, rank), dev, seed=11)
+    m.init_cache(lens, fill="normal", seed=11)
+    if fused_allreduce:   # every rank takes the same path: NCCL for all when one of them cannot set the kernel up
+        try:
+            m.enable_fused_allreduce(lens.numel())
+            ok = 1
+        except Exception:  # noqa: BLE001
+            ok = 0
+        agree = torch.tensor([ok], device=dev, dtype=torch.int32)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        fused_allreduce = bool(int(agree.item()))
+        m.fused_allreduce = fused_allreduce
+    got = m.step(tok).float()
+    torch.cuda.synchronize()
+    dist.barrier()
+    res = None
+    if rank == 0:
+        single = ds.DecodeModel(cfg, shard_heads(cfg.Hq, cfg.Hkv, 1, 0), dev, seed=11)
+        single.init_cache(lens, fill="normal", seed=11)
+        want = single.step(tok).float()
+        scale = max(1e-6, want.abs().max().item())
+        res = {"world": world, "max_abs": (got - want).abs().max().item(), "logit_scale": scale,
+               "cos_min": torch.nn.functional.cosine_similarity(got, want, dim=-1).min().item(),
+               "tol": PARITY_TOL, "all_reduce": "fused peer-memory kernel" if fused_allreduce else "nccl",
+               "model": "2 layers, hidden 1024, 32/8 heads, bf16, FP8 paged cache"}
+        del single
+    del m
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    dist.barrier()
+    if res is not None and (res["max_abs"] > PARITY_TOL["max_abs_over_logit_scale"] * res["logit_scale"]
+                            or res["cos_min"] < PARITY_TOL["cos_min"]):
+        raise RuntimeError(f"tensor-parallel logits differ from the single-rank model: {res}")
+    return res
+
+
 def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, seed: int = 4, use_graph: bool = True,
         fill: str = "random_codes", fused_allreduce: bool = True) -> dict | None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -36,6 +86,10 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
     dev = torch.device("cuda", local)
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
+    parity = None
+    if world > 1:
+        # with the all-reduce the timed run uses (the fused kernel when this machine offers symmetric memory)
+        parity = tp_parity(world, rank, dev, fused_allreduce)
     cfg = ds.ModelConfig(layers=layers)
     g = torch.Generator().manual_seed(seed)
     lens = torch.randint(8192, 131073, (batch,), generator=g, dtype=torch.int32)
@@ -100,6 +154,7 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
     out = {
         "metric": "decode_step_tokens_per_s", "value": batch / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms,
         "n_gpus": world, "steps": steps, "warmup": warmup, "cuda_graph": use_graph, "logits_finite": finite,
+        "tp_parity": parity,
         "config": {"model": "Llama-3.1-8B architecture, random init N(0,0.02), bf16 weights", "layers": layers,
                    "batch": batch, "context_lengths": "uniform 8192..131072, seed 4", "total_context_tokens": int(lens.sum()),
                    "kv": "FP8-E4M3 paged (page 16, fused page records), per-token-per-head fp32 scales, " + fill,

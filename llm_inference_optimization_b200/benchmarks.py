@@ -151,7 +151,7 @@ def bench_evict(t, dev, g, peak, pk):
             try:
                 us, mn = t(lambda: eviction.fused_kv_evict(K, V, scores, budget, recent_tokens=recent, quant=quant, return_aux=True))
             finally:
-                lib.skv_kv_evict_set_fused(1)
+                lib.skv_kv_evict_set_fused(0)
             emit("kv_evict_quant_" + quant, {"B": B, "H": H, "T": T, "D": D, "budget": budget, "recent": recent,
                                              "launches": "one (cluster selects and gathers)" if fused else "two (select, gather)"},
                  us, mn, nbytes, peak, pk)

@@ -112,15 +112,28 @@ evict_select_kernel(const SelectParams p) {
 constexpr int CL = 4;   // CTAs per cluster
 constexpr int KR = 8;   // keys per thread
 
+constexpr int MAX_CAND = 1024;   // threshold-bucket size up to which the last 16 key bits are resolved by ranking
+
+// Exact top-`budget` of one (b, h) row by a cluster of CL CTAs; writes the ascending position list.
+// Whatever CTAs exchange is PUSHED: the owner stores its counts into every CTA's shared memory before the cluster
+// barrier, so that after the barrier everything is local (a remote load costs a round trip of about a microsecond on
+// the critical path, a remote store costs nothing the barrier does not already wait for).
+// Two 8-bit radix passes fix the upper 16 key bits.  The bucket that holds the budget-th key is then usually a few
+// hundred keys: its members are pushed to every CTA (key, then complemented position: among equal scores the lower
+// position ranks higher) and each member counts how many members outrank it; the one outranked by exactly
+// remaining - 1 others is the last key kept.  Larger buckets (many equal scores) take two more radix passes.
 __device__ __forceinline__ void cluster_select_row(const SelectParams& p, cooperative_groups::cluster_group& cluster) {
     constexpr int NW = SEL_THREADS / 32;
-    __shared__ uint32_t hist[NW * 256];   // per-warp private digit counts
-    __shared__ uint32_t chist[2][256];    // this CTA's folded counts, double-buffered across passes
-    __shared__ uint32_t thist[256];       // cluster-wide counts
+    static_assert(NW == 32, "warp 0 scans one count per warp with its 32 lanes");
+    __shared__ uint32_t hist[NW * 256];        // per-warp private digit counts; later the candidate list
+    __shared__ uint32_t xhist[2][CL][256];     // every CTA's folded counts of a pass (pushed), double-buffered across passes
+    __shared__ uint32_t thist[256];            // cluster-wide counts
     __shared__ uint32_t wcnt[4 * NW];
-    __shared__ uint32_t ctot[2];          // this CTA's (greater, equal) totals
-    __shared__ uint32_t bc[4];
+    __shared__ uint32_t xtot[CL][2];           // every CTA's (greater, equal) totals (pushed)
+    __shared__ uint32_t bc[6];                 // digit, remaining, bucket size; threshold key and tie count of the ranking step
+    __shared__ uint32_t ncand;                 // CTA 0's copy hands out slots of the candidate list
 
+    SKV_PHASE(0);
     const int crank = (int)cluster.block_rank();
     const int row = blockIdx.x / CL;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -129,6 +142,7 @@ __device__ __forceinline__ void cluster_select_row(const SelectParams& p, cooper
     const int head = p.T - recent;        // positions competing on score
     const int kb = min(p.budget, head);   // how many of them survive
     int* out = p.idx + (long long)row * p.keep;
+    if (tid == 0) ncand = 0;              // two cluster barriers pass before anybody adds to it
 
     // slice of this CTA, then a contiguous 32-aligned segment per warp; lane l holds elements s0 + 32 j + l
     int span = (head + CL - 1) / CL;
@@ -146,6 +160,7 @@ __device__ __forceinline__ void cluster_select_row(const SelectParams& p, cooper
         if (i < s1) { key[j] = score_key(sc[i]); have |= 1u << j; }
     }
 
+    SKV_PHASE(1);
     uint32_t thr = 0;
     int need = 0;
     if (kb < head && kb > 0) {
@@ -178,13 +193,14 @@ __device__ __forceinline__ void cluster_select_row(const SelectParams& p, cooper
                 uint32_t t = 0;
 #pragma unroll 8
                 for (int w = 0; w < NW; ++w) t += hist[w * 256 + tid];
-                chist[pass & 1][tid] = t;
+#pragma unroll
+                for (int c = 0; c < CL; ++c) cluster.map_shared_rank(&xhist[pass & 1][crank][0], c)[tid] = t;
             }
-            cluster.sync();   // every CTA's folded counts of this pass are in place
+            cluster.sync();   // every CTA's folded counts of this pass have arrived here
             if (tid < 256) {
                 uint32_t t = 0;
 #pragma unroll
-                for (int c = 0; c < CL; ++c) t += cluster.map_shared_rank(&chist[pass & 1][0], c)[tid];
+                for (int c = 0; c < CL; ++c) t += xhist[pass & 1][c][tid];
                 thist[tid] = t;
             }
             __syncthreads();
@@ -210,13 +226,48 @@ __device__ __forceinline__ void cluster_select_row(const SelectParams& p, cooper
                     }
                     bc[0] = (uint32_t)d;
                     bc[1] = (uint32_t)remaining - above;
+                    bc[2] = thist[d];             // keys in the chosen bucket, cluster-wide
                 }
             }
             __syncthreads();
             prefix |= bc[0] << shift;
             mask |= 0xFFu << shift;
             remaining = (int)bc[1];
-            __syncthreads();
+            const uint32_t bucket = bc[2];
+            SKV_PHASE(2 + pass);
+            if (pass == 1 && bucket <= (uint32_t)MAX_CAND) {
+                // hist is idle in every CTA by now (each finished its fold before the barrier above)
+                unsigned long long* all64 = reinterpret_cast<unsigned long long*>(hist);   // [MAX_CAND], same content in every CTA
+                uint32_t* slots = cluster.map_shared_rank(&ncand, 0);
+#pragma unroll
+                for (int j = 0; j < KR; ++j)
+                    if (((have >> j) & 1u) && (key[j] & mask) == prefix) {
+                        const uint32_t slot = atomicAdd(slots, 1u);
+                        const unsigned long long me =
+                            ((unsigned long long)key[j] << 32) | (0xFFFFFFFFu - (uint32_t)(s0 + j * 32 + lane));
+#pragma unroll
+                        for (int c = 0; c < CL; ++c) cluster.map_shared_rank(all64, c)[slot] = me;
+                    }
+                cluster.sync();
+                const int n = (int)bucket;
+                for (int i = tid; i < n; i += SEL_THREADS) {
+                    const unsigned long long me = all64[i];
+                    int rank = 0;
+                    for (int q = 0; q < n; ++q) rank += all64[q] > me ? 1 : 0;
+                    if (rank == remaining - 1) {
+                        int ties = 0;   // members with the same key that are kept: this one and those ranked above it
+                        for (int q = 0; q < n; ++q) ties += ((all64[q] >> 32) == (me >> 32) && all64[q] >= me) ? 1 : 0;
+                        bc[3] = (uint32_t)(me >> 32);
+                        bc[4] = (uint32_t)ties;
+                    }
+                }
+                __syncthreads();
+                prefix = bc[3];
+                remaining = (int)bc[4];
+                SKV_PHASE(6);
+                break;
+            }
+            __syncthreads();   // bc is rewritten in the next pass
         }
         thr = prefix;
         need = remaining;
@@ -224,6 +275,7 @@ __device__ __forceinline__ void cluster_select_row(const SelectParams& p, cooper
         need = head;  // kb >= head: every competing score survives (thr = 0 makes every key "greater or equal")
     }
 
+    SKV_PHASE(7);
     // per-warp counts of keys above / equal to the threshold
     uint32_t gt = 0, eq = 0;
 #pragma unroll
@@ -234,18 +286,24 @@ __device__ __forceinline__ void cluster_select_row(const SelectParams& p, cooper
     }
     if (lane == 0) { wcnt[warp] = gt; wcnt[NW + warp] = eq; }
     __syncthreads();
-    if (tid == 0) {
-        uint32_t g = 0, e = 0;
-        for (int w = 0; w < NW; ++w) { g += wcnt[w]; e += wcnt[NW + w]; }
-        ctot[0] = g;
-        ctot[1] = e;
+    if (warp == 0) {   // this CTA's totals, pushed to everybody
+        uint32_t g = wcnt[lane], e = wcnt[NW + lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            g += __shfl_xor_sync(0xffffffffu, g, o);
+            e += __shfl_xor_sync(0xffffffffu, e, o);
+        }
+        if (lane < CL) {
+            uint32_t* dst = cluster.map_shared_rank(&xtot[crank][0], lane);
+            dst[0] = g;
+            dst[1] = e;
+        }
     }
     cluster.sync();
     // ties and selected positions in the CTAs before this one
     uint32_t eq_before = 0, sel_before = 0;
     for (int c = 0; c < crank; ++c) {
-        const uint32_t* o = cluster.map_shared_rank(&ctot[0], c);
-        const uint32_t g = o[0], e = o[1];
+        const uint32_t g = xtot[c][0], e = xtot[c][1];
         sel_before += g + (uint32_t)max(0, min((int)e, need - (int)eq_before));
         eq_before += e;
     }
@@ -287,8 +345,12 @@ __device__ __forceinline__ void cluster_select_row(const SelectParams& p, cooper
     }
     if (crank == 0)
         for (int i = tid; i < recent; i += SEL_THREADS) out[kb + i] = head + i;
-    __threadfence();  // the position list is read back by the other CTAs of the cluster in the fused kernel
-    cluster.sync();   // nobody leaves while a neighbour may still read its shared memory
+    SKV_PHASE(8);
+    // Release/acquire at cluster scope: the position list written above is visible to the other CTAs of the cluster
+    // after this barrier (the fused kernel reads it back), and nobody leaves while a neighbour may still write to or
+    // read from its shared memory.
+    cluster.sync();
+    SKV_PHASE(9);
 }
 
 __global__ void __cluster_dims__(CL, 1, 1) __launch_bounds__(SEL_THREADS)
@@ -311,10 +373,31 @@ struct GatherParams {
     long long sb, sh, st;
 };
 
+// a / b for a constant b, correctly rounded, in three instructions: with rb = RN(1/b) and q = RN(a * rb) (a faithful
+// quotient), the residual r = a - q * b is exact in one FMA and RN(q + r * rb) is the correctly rounded a / b
+// (Markstein's correction step; it holds for every b whose significand is not all ones -- 127 and 448 are not).
+__device__ __forceinline__ float div_const_rn(float a, float b, float rb) {
+    const float q = a * rb;
+    const float r = fmaf(-q, b, a);
+    return fmaf(r, rb, q);
+}
+
 // `valid` only guards the stores: every lane of the warp runs the shuffles.
+// The quantisation is written for instruction count: with 8-bit outputs this code, not HBM, is what a gather of
+// 256-byte rows costs.  Row maximum on packed halves (|x| and max are exact in fp16); one reciprocal per row; per
+// element one FMA whose addend 1.5 * 2^23 rounds x * inv to the integer grid (half to even) and leaves the integer,
+// in two's complement, in the low mantissa bits.  x * inv differs from the IEEE quotient x / scale by at most 2 ulp
+// (<= 2e-5 for |q| <= 127), so the code can only differ where the product lies within 1e-4 of a rounding boundary:
+// a second FMA forms that distance, one flag per lane collects "too close", and the rare lane with the flag set
+// redoes its eight codes with the IEEE divide.  INT8 codes are therefore bit-exact; FP8 codes, allowed one code
+// step, take the product as it is through the paired saturating conversion.
 template <int MODE>
 __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, uint8_t* out_row, float* scale_out,
                                           __half* out_row_f16, bool valid) {
+    if (MODE == SKV_QUANT_NONE) {
+        if (valid) *reinterpret_cast<uint4*>(out_row_f16 + sub * 8) = raw;
+        return;
+    }
     const __half2* hx = reinterpret_cast<const __half2*>(&raw);
     float x[8];
 #pragma unroll
@@ -322,10 +405,6 @@ __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, ui
         const float2 f = __half22float2(hx[i]);
         x[2 * i] = f.x;
         x[2 * i + 1] = f.y;
-    }
-    if (MODE == SKV_QUANT_NONE) {
-        if (valid) *reinterpret_cast<uint4*>(out_row_f16 + sub * 8) = raw;
-        return;
     }
     if (MODE == SKV_QUANT_CAST) {
         uint32_t lo = 0, hi = 0;
@@ -337,43 +416,55 @@ __device__ __forceinline__ void quant_row(const uint4& raw, int sub, int lpr, ui
         if (valid) *reinterpret_cast<uint2*>(out_row + sub * 8) = make_uint2(lo, hi);
         return;
     }
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
-    for (int o = lpr / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    const float qmax = MODE == SKV_QUANT_INT8 ? 127.f : 448.f;
-    const float scale = amax > 0.f ? __fdiv_rn(amax, qmax) : 1.f;
-    uint32_t lo = 0, hi = 0;
-    // x / scale by an IEEE divide costs ~10 instructions per element and made this kernel issue-bound.
-    // x * (1 / scale) is within 2 ulp of the correctly rounded quotient, so for INT8 (codes must be bit-exact)
-    // the divide is only redone when the product lies within 1e-4 of a rounding boundary (|q| <= 127, ulp <= 8e-6);
-    // FP8 codes are allowed one code step and take the product as is.
-    // INT8 rounding: y + 1.5 * 2^23 is rounded to the integer grid (half to even) by the add itself and leaves
-    // the integer, in two's complement, in the low mantissa bits -- its low byte is the code.
-    const float inv = __frcp_rn(scale);
-    constexpr float MAGIC = 12582912.f;
-    int c[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float y = x[i] * inv;
-        if (MODE == SKV_QUANT_INT8) {
-            // |y| <= 127 (1 + 2^-22) because |x| <= amax = 127 * scale, so rounding already lands in [-127, 127]
-            float r = y + MAGIC;
-            if (fabsf(y - (r - MAGIC)) > 0.5f - 1e-4f) r = __fdiv_rn(x[i], scale) + MAGIC;
-            c[i] = __float_as_int(r);
-        } else {
-            c[i] = (int)__nv_cvt_float_to_fp8(fminf(fmaxf(y, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
-        }
+    __half2 m2 = __hmax2(__hmax2(__habs2(hx[0]), __habs2(hx[1])), __hmax2(__habs2(hx[2]), __habs2(hx[3])));
+    for (int o = lpr / 2; o > 0; o >>= 1) {
+        const uint32_t t = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<const uint32_t*>(&m2), o);
+        m2 = __hmax2(m2, *reinterpret_cast<const __half2*>(&t));
     }
-    // low bytes of eight ints -> two words
-    lo = __byte_perm(__byte_perm(c[0], c[1], 0x0040), __byte_perm(c[2], c[3], 0x0040), 0x5410);
-    hi = __byte_perm(__byte_perm(c[4], c[5], 0x0040), __byte_perm(c[6], c[7], 0x0040), 0x5410);
+    const float amax = fmaxf(__low2float(m2), __high2float(m2));
+    const float scale = amax > 0.f ? (MODE == SKV_QUANT_INT8 ? div_const_rn(amax, 127.f, 1.f / 127.f)
+                                                             : div_const_rn(amax, 448.f, 1.f / 448.f))
+                                   : 1.f;
+    float inv;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(scale));   // within 1 ulp; the boundary test below covers it
+    uint32_t lo, hi;
+    if (MODE == SKV_QUANT_INT8) {
+        constexpr float MAGIC = 12582912.f;
+        // |x * inv| <= 127 (1 + 2^-22) because |x| <= amax = 127 * scale, so rounding already lands in [-127, 127]
+        // Two reciprocals that bracket 1 / scale (the approximation is within 1 ulp, 1.2e-7 relative; they sit 3e-7 to
+        // either side): x / scale, and its fp32 rounding, lie between x * inv_lo and x * inv_hi, so when both products
+        // round to the same integer that integer is the code.  One xor-or per element collects "they differ".
+        const float inv_lo = inv * (1.f - 3e-7f), inv_hi = inv * (1.f + 3e-7f);
+        float r[8];
+        uint32_t differ = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            r[i] = fmaf(x[i], inv_lo, MAGIC);
+            differ |= __float_as_uint(r[i]) ^ __float_as_uint(fmaf(x[i], inv_hi, MAGIC));
+        }
+        if (differ) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[i] = __fdiv_rn(x[i], scale) + MAGIC;
+        }
+        // low bytes of eight words -> two words
+        lo = __byte_perm(__byte_perm(__float_as_uint(r[0]), __float_as_uint(r[1]), 0x0040),
+                         __byte_perm(__float_as_uint(r[2]), __float_as_uint(r[3]), 0x0040), 0x5410);
+        hi = __byte_perm(__byte_perm(__float_as_uint(r[4]), __float_as_uint(r[5]), 0x0040),
+                         __byte_perm(__float_as_uint(r[6]), __float_as_uint(r[7]), 0x0040), 0x5410);
+    } else {
+        uint32_t c[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            c[i] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(x[2 * i] * inv, x[2 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+        lo = __byte_perm(c[0], c[1], 0x5410);
+        hi = __byte_perm(c[2], c[3], 0x5410);
+    }
     if (valid) *reinterpret_cast<uint2*>(out_row + sub * 8) = make_uint2(lo, hi);
     if (valid && sub == 0) *scale_out = scale;
 }
 
-// one group of D/8 lanes per kept (row, j); grid-stride over all kept rows, four rows per group and step
-// so that four index loads and then eight 16-byte row loads are in flight per lane
+// Two-launch path: grid (chunks, B * H); one group of D/8 lanes per kept row, four rows per group and step, the CTAs
+// of a (b, h) striding over its `keep` list entries.  No integer division anywhere on the row path.
 #ifndef SKV_GATHER_MIN_CTAS
 #define SKV_GATHER_MIN_CTAS 4
 #endif
@@ -385,49 +476,41 @@ evict_gather_quant_kernel(const GatherParams p) {
     constexpr int GPB = GQ_THREADS / LPR;
     constexpr int U = 4;
     const int sub = threadIdx.x % LPR, grp = threadIdx.x / LPR;
-    // A CTA takes GPB * U consecutive kept rows per step (row of (u, group) = base + u * GPB + group) and strides
-    // over the whole list.  Rows past the end fall back to the group's first row of the step -- a real row that
-    // is in flight anyway -- and only their stores are suppressed: loads under a condition would be issued one by
-    // one, each behind the use of the one before, and one shared fallback row would be a hot spot.
-    constexpr long long CHUNK = (long long)GPB * U;
-    const long long step = (long long)gridDim.x * CHUNK;
-    const long long last = p.rows_total - 1;
+    const int row = blockIdx.y;                              // (b, h)
+    const int b = row / p.H, h = row - b * p.H;
+    const int* list = p.idx + (long long)row * p.keep;
+    const long long base = (long long)b * p.sb + (long long)h * p.sh + sub * 8;
+    const long long orow = (long long)row * p.keep;
+    // Rows past the end repeat the list's last entry -- a real row that is in flight anyway -- and only their stores
+    // are dropped: loads under a condition would be issued one by one, each behind the use of the one before.
     // The positions of the NEXT step are fetched while this step's rows are in flight, so a step costs one memory
     // round trip instead of two dependent ones.  The trip count is the same for every lane of a CTA.
+    constexpr int CHUNK = GPB * U;
+    const int step = gridDim.x * CHUNK;
+    const int last = p.keep - 1;
     int tn[U];
-    {
-        const long long r0 = (long long)blockIdx.x * CHUNK + grp;
 #pragma unroll
-        for (int u = 0; u < U; ++u) tn[u] = __ldg(p.idx + min(r0 + u * GPB, last));
-    }
-    for (long long rb = (long long)blockIdx.x * CHUNK; rb < p.rows_total; rb += step) {
-        const long long r0 = rb + grp;
-        const long long safe = min(r0, last);
+    for (int u = 0; u < U; ++u) tn[u] = __ldg(list + min((int)blockIdx.x * CHUNK + u * GPB + grp, last));
+    for (int jb = blockIdx.x * CHUNK; jb < p.keep; jb += step) {
         int t[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) t[u] = tn[u];
-        if (rb + step < p.rows_total) {   // block-uniform
+        if (jb + step < p.keep) {   // block-uniform
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const long long rn = r0 + step + u * GPB;
-                tn[u] = __ldg(p.idx + (rn <= last ? rn : safe));
-            }
+            for (int u = 0; u < U; ++u) tn[u] = __ldg(list + min(jb + step + u * GPB + grp, last));
         }
         uint4 kr[U], vr[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const long long r = r0 + u * GPB;
-            const long long rr = r <= last ? r : safe;
-            const long long row = rr / p.keep;  // (b, h)
-            const int tt = r <= last ? t[u] : t[0];
-            const long long src = (row / p.H) * p.sb + (row % p.H) * p.sh + (long long)max(tt, 0) * p.st + sub * 8;
+            const long long src = base + (long long)max(t[u], 0) * p.st;
             kr[u] = ld_stream16(p.k + src);
             vr[u] = ld_stream16(p.v + src);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const long long r = r0 + u * GPB;
-            const bool valid = r < p.rows_total;
+            const int j = jb + u * GPB + grp;
+            const bool valid = j < p.keep;
+            const long long r = orow + j;
             if (MODE == SKV_QUANT_NONE) {
                 quant_row<MODE>(kr[u], sub, LPR, nullptr, nullptr, static_cast<__half*>(p.k_out) + r * D, valid);
                 quant_row<MODE>(vr[u], sub, LPR, nullptr, nullptr, static_cast<__half*>(p.v_out) + r * D, valid);
@@ -438,7 +521,6 @@ evict_gather_quant_kernel(const GatherParams p) {
         }
     }
 }
-
 
 // Selection and gather in one launch: after cluster_select_row the (b, h) row's ascending position list is complete
 // in global memory (and in L2); CTA c of the cluster takes list entries [c * per, (c + 1) * per).  Same lane layout
@@ -459,6 +541,7 @@ evict_fused_cluster_kernel(const SelectParams p, const GatherParams g) {
     const int per = (p.keep + CL - 1) / CL;
     const int j0 = min(p.keep, crank * per), j1 = min(p.keep, j0 + per);
     if (j0 >= j1) return;
+    SKV_PHASE(10);
     const int* list = p.idx + row * p.keep;
     const long long base = (row / g.H) * g.sb + (row % g.H) * g.sh + sub * 8;
     const long long orow = row * p.keep;
@@ -494,6 +577,7 @@ evict_fused_cluster_kernel(const SelectParams p, const GatherParams g) {
             }
         }
     }
+    SKV_PHASE(11);
 }
 
 template <int D>
@@ -509,7 +593,7 @@ static int launch_fused(const SelectParams& sp, const GatherParams& gp, int mode
     return SKV_OK;
 }
 
-inline int& fused_flag() { static int on = 1; return on; }
+inline int& fused_flag() { static int on = 0; return on; }   // two launches measure faster on B200 (see skv_kv_evict_set_fused)
 inline bool fused_enabled() { return fused_flag() != 0; }
 
 static size_t select_smem() { return (size_t)TopkSmem<SEL_THREADS>::WORDS * 4 + (size_t)MAX_KEEP * 8; }
@@ -517,17 +601,20 @@ static size_t select_smem() { return (size_t)TopkSmem<SEL_THREADS>::WORDS * 4 + 
 template <int D>
 static int launch_gather(const GatherParams& gp, int mode, int device, cudaStream_t st) {
     constexpr int GPB = GQ_THREADS / (D / 8);
-    long long blocks = (gp.rows_total + GPB * 4 - 1) / (GPB * 4);   // U = 4 rows per group and step
+    const long long rows = gp.rows_total / gp.keep;               // B * H
+    if (rows > 65535) return fail(SKV_ERR_UNSUPPORTED, "B * H = %lld exceeds 65535", rows);
+    int chunks = (gp.keep + GPB * 4 - 1) / (GPB * 4);             // U = 4 rows per group and step
 #ifndef SKV_GATHER_CAP
 #define SKV_GATHER_CAP 16
 #endif
-    const long long cap = (long long)sm_count(device) * SKV_GATHER_CAP;
-    if (blocks > cap) blocks = cap;
+    const long long cap = ((long long)sm_count(device) * SKV_GATHER_CAP + rows - 1) / rows;   // CTAs per (b, h)
+    if (chunks > cap) chunks = (int)(cap > 0 ? cap : 1);
+    const dim3 grid((unsigned)chunks, (unsigned)rows), block(GQ_THREADS);
     switch (mode) {
-        case SKV_QUANT_NONE: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_NONE>, dim3((unsigned)blocks), dim3(GQ_THREADS), 0, st, gp)); break;
-        case SKV_QUANT_INT8: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_INT8>, dim3((unsigned)blocks), dim3(GQ_THREADS), 0, st, gp)); break;
-        case SKV_QUANT_E4M3: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_E4M3>, dim3((unsigned)blocks), dim3(GQ_THREADS), 0, st, gp)); break;
-        default: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_CAST>, dim3((unsigned)blocks), dim3(GQ_THREADS), 0, st, gp)); break;
+        case SKV_QUANT_NONE: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_NONE>, grid, block, 0, st, gp)); break;
+        case SKV_QUANT_INT8: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_INT8>, grid, block, 0, st, gp)); break;
+        case SKV_QUANT_E4M3: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_E4M3>, grid, block, 0, st, gp)); break;
+        default: SKV_CUDA_TRY(launch_pdl(evict_gather_quant_kernel<D, SKV_QUANT_CAST>, grid, block, 0, st, gp)); break;
     }
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
@@ -548,7 +635,13 @@ int skv_kv_evict_keep_count(int T, int budget, int recent) {
     return kb + r;
 }
 
-// 1 (default): the single-launch cluster kernel serves the cases it covers; 0: always select and gather in two launches.
+#ifdef SKV_PROFILE_PHASES
+int skv_debug_phase_ts_evict(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, skv_phase_ts, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : -4;
+}
+#endif
+
+// 1: the single-launch cluster kernel serves the cases it covers; 0 (default): select and gather in two launches.
 int skv_kv_evict_set_fused(int on) {
     evq::fused_flag() = on ? 1 : 0;
     return SKV_OK;

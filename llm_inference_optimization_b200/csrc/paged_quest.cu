@@ -17,7 +17,8 @@
 //       block, all G query heads of the group scored from one read.
 //   quest_select_attend_kernel -- one CTA per (b, query head): exact top-k over
 //       the block scores, then scores / softmax / weighted value sum over the
-//       <= k * block_size gathered tokens, all fp32.
+//       <= k * block_size gathered tokens, all fp32; the V rows travel to shared
+//       memory as asynchronous copies while the K rows are scored.
 #include <cuda_fp8.h>
 
 #include "skv_common.cuh"
@@ -43,11 +44,38 @@ __device__ __forceinline__ float code_to_float(uint32_t byte) {
     return (float)(int)(int8_t)byte;
 }
 
+// Four codes of one 32-bit word as floats.
+template <int KVT>
+__device__ __forceinline__ void word_to_floats(uint32_t w, float (&f)[4]) {
+    if (KVT == SKV_KV_E4M3) {
+        uint32_t h0, h1;
+        asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\t"
+            "cvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+            : "=r"(h0), "=r"(h1)
+            : "r"(w));
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h0));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h1));
+        f[0] = f0.x; f[1] = f0.y; f[2] = f1.x; f[3] = f1.y;
+    } else {
+        // int8 b -> float: the bits 0x4B000000 | (b ^ 0x80) are 2^23 + b + 128 exactly
+        const uint32_t x = w ^ 0x80808080u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540u + i)) - 8388736.f;
+    }
+}
+
+// Sixteen codes of one 16-byte load as floats.  FP8 goes through the paired conversion (one instruction per two
+// codes): converting byte by byte made the gather kernel wait on the conversion pipe rather than on memory.
 template <int KVT>
 __device__ __forceinline__ void unpack16(const uint4& raw, float (&x)[16]) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int i = 0; i < 16; ++i) x[i] = code_to_float<KVT>((w[i >> 2] >> (8 * (i & 3))) & 0xFFu);
+    for (int i = 0; i < 4; ++i) {
+        float f[4];
+        word_to_floats<KVT>(w[i], f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[4 * i + j] = f[j];
+    }
 }
 
 struct Pool {
@@ -69,31 +97,11 @@ __device__ __forceinline__ int phys_page(const int* page_table, int b, int max_p
     return page_table ? __ldg(page_table + (long long)b * max_pages + lp) : b * max_pages + lp;
 }
 
-// Four codes of one 32-bit word as floats.
-template <int KVT>
-__device__ __forceinline__ void word_to_floats(uint32_t w, float (&f)[4]) {
-    if (KVT == SKV_KV_E4M3) {
-        uint32_t h0, h1;
-        asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\t"
-            "cvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
-            : "=r"(h0), "=r"(h1)
-            : "r"(w));
-        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h0));
-        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h1));
-        f[0] = f0.x; f[1] = f0.y; f[2] = f1.x; f[3] = f1.y;
-    } else {
-        // int8 b -> float: the bits 0x4B000000 | (b ^ 0x80) are 2^23 + b + 128 exactly
-        const uint32_t x = w ^ 0x80808080u;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) f[i] = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540u + i)) - 8388736.f;
-    }
-}
-
 // one warp per (b, h, block); lanes: 8 per token row (16 codes each), 4 rows per step.  The dequantised value
 // code * scale is formed in fp32 and rounded to fp16 BEFORE the comparisons (rounding is monotone, so the minimum
 // of the rounded values is the rounded minimum): minima and maxima then run two channels per instruction.
 template <int KVT>
-__global__ void __launch_bounds__(META_THREADS)
+__global__ void __launch_bounds__(META_THREADS, 4)   // 64 registers: four CTAs per SM keep enough rows in flight
 block_meta_build_kernel(const MetaParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane & 7, rw = lane >> 3;
@@ -178,98 +186,116 @@ struct ScoreParams {
     float scale;
 };
 
-// grid (ceil(nb / blocks_per_cta), Hkv, B); 16 lanes per block (8 channels each), 2 blocks per warp step.
+// 16 lanes per block (8 channels each), 2 blocks per warp-wide load, U loads of each half in flight per lane.
 // With lo <= hi, max(q*lo, q*hi) = q*(hi+lo)/2 + |q|*(hi-lo)/2; hi+lo and hi-lo are exact in fp32 (fp16 inputs), the
 // halving is folded into q, and |q| is an operand modifier of the FMA, so a channel costs two FMAs per head and the
-// query needs one register per channel and head.  That leaves room for U = 8 blocks (sixteen 16-byte loads) in
+// query needs one register per channel and head.  That leaves room for up to 8 blocks (sixteen 16-byte loads) in
 // flight per lane at 128 registers: two CTAs per SM then keep 128 KB of metadata in flight per SM.
-template <int MAXG>
+//
+// Schedule: the (b, kv-head, block) space is flattened and cut into one contiguous range per WARP of a grid of exactly
+// two CTAs per SM (blocks_per_warp, a multiple of 2U, chosen on the host so that the ranges cover the space with the
+// least idle tail -- the kernel is a single wave and its duration is that of its slowest SM).  A range may cross
+// into the next (b, kv-head): the query registers are reloaded there.
+template <int MAXG, int U>
 __global__ void __launch_bounds__(SCORE_THREADS, 2)
-quest_scores_kernel(const ScoreParams p, int blocks_per_cta) {
+quest_scores_kernel(const ScoreParams p, long long total_blocks, int blocks_per_warp) {
     pdl_launch_dependents();  // the kernel that consumes these results may be scheduled now; it waits for this grid to finish
     static_assert(MAXG == 4 || MAXG == 8, "the packed reduction below is written for 4 or 8 heads");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane & 15, rw = lane >> 4;
-    const int h = blockIdx.y, b = blockIdx.z;
-    float qh[MAXG][8];   // half the query
+    const long long gw = (long long)blockIdx.x * (SCORE_THREADS / 32) + warp;
+    long long g0 = gw * blocks_per_warp;
+    const long long g1 = min(total_blocks, g0 + blocks_per_warp);
+    while (g0 < g1) {
+        const long long row = g0 / p.nb;            // (b, kv-head)
+        const int j0 = (int)(g0 - row * p.nb);
+        const int j1 = (int)min((long long)p.nb, j0 + (g1 - g0));
+        const int b = (int)(row / p.Hkv), h = (int)(row - (long long)b * p.Hkv);
+        float qh[MAXG][8];   // half the query
 #pragma unroll
-    for (int g = 0; g < MAXG; ++g) {
-        float q[8];
-        if (g < p.G) unpack8(*reinterpret_cast<const uint4*>(p.q + ((long long)b * p.Hq + h * p.G + g) * D + sub * 8), q);
-        else
+        for (int g = 0; g < MAXG; ++g) {
+            float q[8];
+            if (g < p.G) unpack8(*reinterpret_cast<const uint4*>(p.q + ((long long)b * p.Hq + h * p.G + g) * D + sub * 8), q);
+            else
 #pragma unroll
-            for (int i = 0; i < 8; ++i) q[i] = 0.f;
+                for (int i = 0; i < 8; ++i) q[i] = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) qh[g][i] = 0.5f * q[i];
-    }
-    const __half* mbase = p.meta + ((long long)b * p.Hkv + h) * p.nb * 2 * D + sub * 8;
-    const int j0 = blockIdx.x * blocks_per_cta, j1 = min(p.nb, j0 + blocks_per_cta);
-    constexpr int U = MAXG == 4 ? 8 : 4;  // blocks per half-warp and step
-    for (int base = j0 + warp * 2 * U; base < j1; base += (SCORE_THREADS / 32) * 2 * U) {
-        uint4 lo4[U], hi4[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int j = min(base + u * 2 + rw, j1 - 1);  // clamped; the store below is guarded
-            lo4[u] = ld_stream16(mbase + (long long)j * 2 * D);
-            hi4[u] = ld_stream16(mbase + (long long)j * 2 * D + D);
+            for (int i = 0; i < 8; ++i) qh[g][i] = 0.5f * q[i];
         }
+        const __half* mbase = p.meta + row * p.nb * 2 * D + sub * 8;
+        for (int base = j0; base < j1; base += 2 * U) {
+            uint4 lo4[U], hi4[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int j = base + u * 2 + rw;
-            float lo[8], hi[8], acc[MAXG];
-            unpack8(lo4[u], lo);
-            unpack8(hi4[u], hi);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float s = hi[i] + lo[i], d = hi[i] - lo[i];
-                lo[i] = s;   // hi + lo
-                hi[i] = d;   // hi - lo >= 0
+            for (int u = 0; u < U; ++u) {
+                const int j = min(base + u * 2 + rw, j1 - 1);  // clamped; the store below is guarded
+                lo4[u] = ld_stream16(mbase + (long long)j * 2 * D);
+                hi4[u] = ld_stream16(mbase + (long long)j * 2 * D + D);
             }
 #pragma unroll
-            for (int g = 0; g < MAXG; ++g) {
-                acc[g] = 0.f;
+            for (int u = 0; u < U; ++u) {
+                const int j = base + u * 2 + rw;
+                float lo[8], hi[8], acc[MAXG];
+                unpack8(lo4[u], lo);
+                unpack8(hi4[u], hi);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[g] = fmaf(qh[g][i], lo[i], fmaf(fabsf(qh[g][i]), hi[i], acc[g]));
-            }
-            // Sum over the 16 lanes of the half-warp, several heads at once: at each of the first steps a lane
-            // keeps half of its values and hands the other half to its partner, so MAXG values cost
-            // MAXG/2 + MAXG/4 + ... + 1 shuffles plus the remaining plain steps instead of 4 * MAXG.
-            int head = 0;  // which head this lane ends up holding
-            float v4[4];
-            if (MAXG == 8) {
-                const bool up = sub & 8;
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const float keep = up ? acc[g + 4] : acc[g], send = up ? acc[g] : acc[g + 4];
-                    v4[g] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                for (int i = 0; i < 8; ++i) {
+                    const float s = hi[i] + lo[i], d = hi[i] - lo[i];
+                    lo[i] = s;   // hi + lo
+                    hi[i] = d;   // hi - lo >= 0
                 }
-                head = up ? 4 : 0;
-            } else {
 #pragma unroll
-                for (int g = 0; g < 4; ++g) v4[g] = acc[g] + __shfl_xor_sync(0xffffffffu, acc[g], 8);
-            }
-            float v2[2];
-            {
-                const bool up = sub & 4;
+                for (int g = 0; g < MAXG; ++g) {
+                    acc[g] = 0.f;
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    const float keep = up ? v4[g + 2] : v4[g], send = up ? v4[g] : v4[g + 2];
-                    v2[g] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+                    for (int i = 0; i < 8; ++i) acc[g] = fmaf(qh[g][i], lo[i], fmaf(fabsf(qh[g][i]), hi[i], acc[g]));
                 }
-                head += up ? 2 : 0;
+                // Sum over the 16 lanes of the half-warp, several heads at once: at each of the first steps a lane
+                // keeps half of its values and hands the other half to its partner, so MAXG values cost
+                // MAXG/2 + MAXG/4 + ... + 1 shuffles plus the remaining plain steps instead of 4 * MAXG.
+                int head = 0;  // which head this lane ends up holding
+                float v4[4];
+                if (MAXG == 8) {
+                    const bool up = sub & 8;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const float keep = up ? acc[g + 4] : acc[g], send = up ? acc[g] : acc[g + 4];
+                        v4[g] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                    }
+                    head = up ? 4 : 0;
+                } else {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) v4[g] = acc[g] + __shfl_xor_sync(0xffffffffu, acc[g], 8);
+                }
+                float v2[2];
+                {
+                    const bool up = sub & 4;
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) {
+                        const float keep = up ? v4[g + 2] : v4[g], send = up ? v4[g] : v4[g + 2];
+                        v2[g] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+                    }
+                    head += up ? 2 : 0;
+                }
+                float v1;
+                {
+                    const bool up = sub & 2;
+                    const float keep = up ? v2[1] : v2[0], send = up ? v2[0] : v2[1];
+                    v1 = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+                    head += up ? 1 : 0;
+                }
+                v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+                if (j < j1 && (sub & 1) == 0 && head < p.G)
+                    p.scores[((long long)b * p.Hq + h * p.G + head) * p.nb + j] = v1 * p.scale;
             }
-            float v1;
-            {
-                const bool up = sub & 2;
-                const float keep = up ? v2[1] : v2[0], send = up ? v2[0] : v2[1];
-                v1 = keep + __shfl_xor_sync(0xffffffffu, send, 2);
-                head += up ? 1 : 0;
-            }
-            v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
-            if (j < j1 && (sub & 1) == 0 && head < p.G)
-                p.scores[((long long)b * p.Hq + h * p.G + head) * p.nb + j] = v1 * p.scale;
         }
+        g0 += j1 - j0;
     }
+}
+
+template <int MAXG, int U>
+static cudaError_t launch_scores(const ScoreParams& sp, long long total_blocks, int blocks_per_warp, int ctas, cudaStream_t st) {
+    quest_scores_kernel<MAXG, U><<<(unsigned)ctas, SCORE_THREADS, 0, st>>>(sp, total_blocks, blocks_per_warp);
+    return cudaGetLastError();
 }
 
 struct AttendParams {
@@ -314,8 +340,10 @@ quest_select_attend_kernel(const AttendParams p) {
     // q, seq_lens and the page table are older than the scoring kernel this launch depends on: read them first
     const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
     const int nb = (len + p.block_size - 1) / p.block_size;  // blocks this sequence really has
+    SKV_PHASE(0);
     for (int i = tid; i < D; i += ATT_THREADS) qs[i] = __half2float(p.q[(long long)row * D + i]);
     pdl_wait_prior_grids();   // launched as a programmatic dependent of the scoring kernel: its results are complete from here on
+    SKV_PHASE(1);
     const float* sc = p.scores + (long long)row * p.nb;
     const int kk = min(p.top_k, nb);
     if (kk <= 32 && nb <= ATT_THREADS * 4) block_topk_small<ATT_THREADS, 4>(sc, nb, kk, sel, reinterpret_cast<unsigned long long*>(tk));
@@ -325,6 +353,7 @@ quest_select_attend_kernel(const AttendParams p) {
     if (p.block_idx)
         for (int i = tid; i < p.top_k; i += ATT_THREADS) p.block_idx[(long long)row * p.top_k + i] = i < kk ? sel[i] : -1;
 
+    SKV_PHASE(2);
     const int sub = tid & 7, grp = tid >> 3;  // 8 lanes per token row; grp in [0, 64)
     const int ntok = kk * p.block_size;
     const bool staged = ntok <= VSTAGE_TOKENS;
@@ -342,14 +371,8 @@ quest_select_attend_kernel(const AttendParams p) {
         if (staged) cp_async4(smem_u32(vsc_sm + r), p.v.scales + pg * p.v.csp + h * p.v.csh + slot);
     }
     __syncthreads();
-    if (staged) {   // V rows on their way to shared memory: 8 x 16 bytes per row, nothing held in registers
-        const uint32_t vdst = smem_u32(vstage);
-        for (int c = tid; c < ntok * 8; c += ATT_THREADS) {
-            const int2 pw = where[c >> 3];
-            cp_async16(vdst + c * 16, p.v.codes + pw.x * p.v.sp + h * p.v.sh + (pw.y & ~PAST_END) * p.v.ss + (c & 7) * 16);
-        }
-    }
 
+    SKV_PHASE(3);
     // ---- scores of the gathered tokens: 8 lanes per token row, 64 rows per pass
     float qv[16];
 #pragma unroll
@@ -365,6 +388,15 @@ quest_select_attend_kernel(const AttendParams p) {
             const int slot = pw.y & ~PAST_END;
             raw[u] = ld_stream16(p.k.codes + pw.x * p.k.sp + h * p.k.sh + slot * p.k.ss + sub * 16);
             ksc[u] = __ldg(p.k.scales + pw.x * p.k.csp + h * p.k.csh + slot);
+        }
+        if (staged && r0 == 0) {
+            // V rows on their way to shared memory (8 x 16 bytes per row, nothing held in registers), queued BEHIND
+            // the K loads above: K is needed first, V only after the softmax.
+            const uint32_t vdst = smem_u32(vstage);
+            for (int c = tid; c < ntok * 8; c += ATT_THREADS) {
+                const int2 pw = where[c >> 3];
+                cp_async16(vdst + c * 16, p.v.codes + pw.x * p.v.sp + h * p.v.sh + (pw.y & ~PAST_END) * p.v.ss + (c & 7) * 16);
+            }
         }
 #pragma unroll
         for (int u = 0; u < RU; ++u) {
@@ -383,6 +415,7 @@ quest_select_attend_kernel(const AttendParams p) {
             mx = fmaxf(mx, sv);
         }
     }
+    SKV_PHASE(4);
     mx = warp_max(mx);
     if (lane == 0) red[warp] = mx;
     __syncthreads();
@@ -411,6 +444,7 @@ quest_select_attend_kernel(const AttendParams p) {
     __syncthreads();
     const float inv = bcast[1] > 0.f ? 1.f / bcast[1] : 0.f;
 
+    SKV_PHASE(5);
     // ---- out = sum_t p_t * vs_t * vc_t
     float acc[16];
 #pragma unroll
@@ -448,6 +482,7 @@ quest_select_attend_kernel(const AttendParams p) {
             }
         }
     }
+    SKV_PHASE(6);
     // reduce the 64 row-groups: first inside each warp (4 groups), then across the warps through shared memory
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -468,6 +503,7 @@ quest_select_attend_kernel(const AttendParams p) {
         p.out[(long long)row * D + d] = __float2half_rn(o * inv);
     }
     report_bad_page(bad_page, p.status);
+    SKV_PHASE(7);
 }
 
 }  // namespace quest
@@ -484,6 +520,12 @@ static int check_pool_args(const void* codes, const float* scales, int page_size
 }
 
 extern "C" {
+
+#ifdef SKV_PROFILE_PHASES
+int skv_debug_phase_ts_quest(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, skv_phase_ts, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : -4;
+}
+#endif
 
 // Number of metadata blocks for a cache of N tokens.
 int skv_quest_num_blocks(int N, int block_size) { return (N <= 0 || block_size <= 0) ? 0 : (N + block_size - 1) / block_size; }
@@ -566,17 +608,35 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
     sp.scores = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
     sp.Hq = Hq; sp.Hkv = Hkv; sp.G = G; sp.nb = nb; sp.scale = scale;
     const long long rows = (long long)B * Hkv;
-#ifndef SKV_QUEST_SCORE_CTAS_PER_SM
-#define SKV_QUEST_SCORE_CTAS_PER_SM 2   // what the kernel's 128 registers allow: one wave of CTAs
-#endif
-    long long want = ((long long)sm_count(device) * SKV_QUEST_SCORE_CTAS_PER_SM + rows - 1) / rows;
-    int blocks_per_cta = (int)((nb + want - 1) / want);
-    const int step = G <= 4 ? 128 : 64;   // one CTA step covers 8 warps x 2 half-warps x U blocks
-    blocks_per_cta = ((blocks_per_cta + step - 1) / step) * step;
-    dim3 g1((nb + blocks_per_cta - 1) / blocks_per_cta, Hkv, B);
-    if (G <= 4) quest::quest_scores_kernel<4><<<g1, quest::SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);
-    else quest::quest_scores_kernel<8><<<g1, quest::SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);
-    SKV_CUDA_TRY(cudaGetLastError());
+    // One wave of two CTAs per SM; every warp takes blocks_per_warp consecutive blocks of the flattened space.  U (loads
+    // of each half in flight per lane) is picked so that the iterations cover the space with the smallest idle tail.
+    const long long total_blocks = rows * nb;
+    int ctas = sm_count(device) * 2;
+    const long long warps = (long long)ctas * (quest::SCORE_THREADS / 32);
+    const long long share = (total_blocks + warps - 1) / warps;   // blocks a warp must take at least
+    const int umax = G <= 4 ? 8 : 4, umin = G <= 4 ? 5 : 3;
+    int best_u = umax;
+    long long best_cover = -1;
+    for (int u = umax; u >= umin; --u) {
+        const long long per = (share + 2 * u - 1) / (2 * u) * (2 * u);
+        if (best_cover < 0 || per < best_cover) { best_cover = per; best_u = u; }
+    }
+    const int blocks_per_warp = (int)best_cover;
+    const long long need_ctas = (total_blocks + (long long)blocks_per_warp * 8 - 1) / ((long long)blocks_per_warp * 8);
+    if (need_ctas < ctas) ctas = (int)need_ctas;
+    cudaError_t le;
+    if (G <= 4) {
+        switch (best_u) {
+            case 8: le = quest::launch_scores<4, 8>(sp, total_blocks, blocks_per_warp, ctas, st); break;
+            case 7: le = quest::launch_scores<4, 7>(sp, total_blocks, blocks_per_warp, ctas, st); break;
+            case 6: le = quest::launch_scores<4, 6>(sp, total_blocks, blocks_per_warp, ctas, st); break;
+            default: le = quest::launch_scores<4, 5>(sp, total_blocks, blocks_per_warp, ctas, st); break;
+        }
+    } else {
+        le = best_u == 4 ? quest::launch_scores<8, 4>(sp, total_blocks, blocks_per_warp, ctas, st)
+                         : quest::launch_scores<8, 3>(sp, total_blocks, blocks_per_warp, ctas, st);
+    }
+    SKV_CUDA_TRY(le);
 
     quest::AttendParams ap;
     ap.q = sp.q; ap.scores = sp.scores;

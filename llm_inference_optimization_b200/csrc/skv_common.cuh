@@ -118,6 +118,22 @@ __device__ __forceinline__ void report_bad_page(bool bad, int* status) {
     if (bad && status) atomicOr(status, SKV_DEV_BAD_PAGE);
 }
 
+// Phase timestamps for kernel tuning (instrumented builds only: -DSKV_PROFILE_PHASES): thread 0 of CTA 0 records the
+// global timer at numbered points; a per-file skv_debug_phase_ts_*() copies them out.  Compiled out of the shipped library.
+#ifdef SKV_PROFILE_PHASES
+static __device__ unsigned long long skv_phase_ts[32];   // one copy per translation unit
+#define SKV_PHASE(i)                                                                   \
+    do {                                                                               \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) { \
+            unsigned long long t_;                                                     \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                     \
+            skv_phase_ts[i] = t_;                                                      \
+        }                                                                              \
+    } while (0)
+#else
+#define SKV_PHASE(i) do {} while (0)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

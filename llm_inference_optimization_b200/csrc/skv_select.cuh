@@ -341,10 +341,19 @@ __device__ void block_topk_sorted_cached(const float* sc, int T, int k, int* out
 
 // Exact top-k for a SMALL k (k <= 32) over T <= NT * R scores: arg-max extraction instead of histogram passes.
 // Every score becomes a 64-bit key (order-preserving score bits, then the complemented position, so that among equal
-// scores the lower position is the larger key).  Each warp extracts the k best of its contiguous segment with
-// shuffles only (lane i keeps the i-th best), the NT/32 candidate lists meet in shared memory, and warp 0 extracts
-// the k best of those the same way and writes their positions in ascending order.  Two barriers in all, against six
-// per pass of the radix routine.  `cand` is NT 64-bit words of shared memory.  All NT threads must call it.
+// scores the lower position is the larger key).  Each warp extracts the k best of its contiguous segment (lane i keeps
+// the i-th best); a warp-wide maximum of a 64-bit key is two redux.sync instructions (upper words, then the lower
+// words of the lanes that hold the winning upper word).  The NT/32 * k candidates meet in shared memory, where a
+// candidate is kept when fewer than k candidates outrank it, and the kept positions are written in ascending order.
+// Four barriers in all, against six per pass of the radix routine.  `cand` is NT 64-bit words of shared memory.
+// All NT threads must call it.
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+    const uint32_t hi = (uint32_t)(v >> 32), lo = (uint32_t)v;
+    const uint32_t mh = __reduce_max_sync(0xffffffffu, hi);
+    const uint32_t ml = __reduce_max_sync(0xffffffffu, hi == mh ? lo : 0u);
+    return ((unsigned long long)mh << 32) | ml;
+}
+
 template <int R>
 __device__ __forceinline__ unsigned long long warp_extract_topk(unsigned long long (&key)[R], int k, int lane) {
     unsigned long long mine = 0ull;
@@ -352,11 +361,7 @@ __device__ __forceinline__ unsigned long long warp_extract_topk(unsigned long lo
         unsigned long long m = key[0];
 #pragma unroll
         for (int j = 1; j < R; ++j) m = key[j] > m ? key[j] : m;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const unsigned long long v = __shfl_xor_sync(0xffffffffu, m, o);
-            m = v > m ? v : m;
-        }
+        m = warp_max_u64(m);
         if (lane == it) mine = m;
 #pragma unroll
         for (int j = 0; j < R; ++j)
@@ -368,7 +373,6 @@ __device__ __forceinline__ unsigned long long warp_extract_topk(unsigned long lo
 template <int NT, int R>
 __device__ void block_topk_small(const float* sc, int T, int k, int* out, unsigned long long* cand) {
     constexpr int NW = NT / 32;
-    static_assert(NW <= 32, "warp 0 holds one candidate list per lane group");
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (k <= 0) return;
     unsigned long long key[R];
@@ -377,23 +381,29 @@ __device__ void block_topk_small(const float* sc, int T, int k, int* out, unsign
         const int i = (warp * R + j) * 32 + lane;
         key[j] = i < T ? ((unsigned long long)score_key(sc[i]) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i) : 0ull;
     }
-    cand[warp * 32 + lane] = warp_extract_topk<R>(key, k, lane);   // lanes >= k hold 0
+    const unsigned long long mine = warp_extract_topk<R>(key, k, lane);   // lane i < k holds this warp's i-th best
+    if (lane < k) cand[warp * k + lane] = mine;                           // NW * k candidates, packed (0: no such score)
     __syncthreads();
-    if (warp == 0) {
-        unsigned long long k2[NW];
-#pragma unroll
-        for (int j = 0; j < NW; ++j) k2[j] = cand[j * 32 + lane];
-        const unsigned long long best = warp_extract_topk<NW>(k2, k, lane);
-        // lane i < k holds the i-th best (0 when fewer than k scores exist): order the positions ascending
-        const uint32_t pos = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull);
-        const bool have = best != 0ull;
-        int rank = 0;
-        for (int i = 0; i < k; ++i) {
-            const uint32_t other = __shfl_sync(0xffffffffu, pos, i);
-            const bool oh = __shfl_sync(0xffffffffu, (int)have, i) != 0;
-            rank += (oh && other < pos) ? 1 : 0;
+    __shared__ int by_rank[32];  // position of the candidate that exactly r others outrank, r < k
+    const int total = NW * k;    // <= NT because k <= 32
+    if (tid < 32) by_rank[tid] = -1;
+    __syncthreads();
+    if (tid < total) {
+        const unsigned long long me = cand[tid];
+        if (me != 0ull) {
+            int outranked = 0;
+            for (int q = 0; q < total; ++q) outranked += cand[q] > me ? 1 : 0;
+            if (outranked < k) by_rank[outranked] = (int)(0xFFFFFFFFu - (uint32_t)me);
         }
-        if (have && lane < k) out[rank] = (int)pos;
+    }
+    __syncthreads();
+    if (tid < k) {   // ascending positions: a kept position goes to the slot numbered by how many kept ones lie below it
+        const int pos = by_rank[tid];
+        if (pos >= 0) {
+            int lower = 0;
+            for (int q = 0; q < k; ++q) lower += (by_rank[q] >= 0 && by_rank[q] < pos) ? 1 : 0;
+            out[lower] = pos;
+        }
     }
     __syncthreads();
 }

@@ -19,7 +19,10 @@ def _rms(x, w, eps):
     return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
 
 
-def _rope(x, pos, theta):
+def rope(x, pos, theta):
+    """Rotate-half rotary embedding of ``x [B, H, D]`` (fp32) at integer positions ``pos [B]``: channel d pairs with
+    d + D/2, angle ``pos * theta^(-2d/D)`` -- the form of the Hugging Face Llama model the reference patches
+    (benchmarks/llama_integration_benchmark.py:152-160)."""
     D = x.shape[-1]
     inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
     ang = pos.float()[:, None] * inv[None, :]
@@ -38,8 +41,8 @@ def decode_step(weights: dict, cfg, tokens, k_hist, v_hist, seq_lens):
     pos = seq_lens.long()
     for l, w in enumerate(weights["layers"]):
         h = _rms(x, w["n1"], cfg.rms_eps)
-        q = _rope((h @ w["wq"]).view(B, Hq, D), pos, cfg.rope_theta)
-        k = _rope((h @ w["wk"]).view(B, Hkv, D), pos, cfg.rope_theta)
+        q = rope((h @ w["wq"]).view(B, Hq, D), pos, cfg.rope_theta)
+        k = rope((h @ w["wk"]).view(B, Hkv, D), pos, cfg.rope_theta)
         v = (h @ w["wv"]).view(B, Hkv, D)
         kc, ks = skv_oracle.quantize_e4m3(k)
         vc, vs = skv_oracle.quantize_e4m3(v)

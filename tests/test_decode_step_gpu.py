@@ -54,6 +54,23 @@ def test_fp32_weights_match_oracle_model(cuda_device):
     assert (got - want).abs().max().item() <= 5e-3 * max(1.0, want.abs().max().item())
 
 
+def test_bf16_fused_glue_path_matches_oracle_model(cuda_device):
+    """The path the decode benchmark times -- bf16 weights, fused RoPE/quantise/append, residual-RMSNorm and SiLU
+    kernels, bf16 attention output -- against the fp32 CPU oracle evaluated on the same (bf16-rounded) weights."""
+    m = ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, 1, 0), cuda_device, dtype=torch.bfloat16)
+    assert m.fused_glue
+    m.init_cache(LENS)
+    weights, k_hist, v_hist = oracle_inputs(m)            # .float() of bf16 tensors: the rounded weights themselves
+    want = dso.decode_step(weights, CFG, TOK, k_hist, v_hist, LENS.clone())
+    got = m.step(TOK.to(cuda_device)).float().cpu()
+    err = (got - want).abs().max().item()
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1).min().item()
+    print(f"bf16 fused-glue step vs fp32 oracle: max-abs {err:.3e} (logits up to {want.abs().max().item():.3f}), cos {cos:.6f}")
+    # bf16 activations carry 8 mantissa bits through two layers: a few 1e-3 of the logit scale
+    assert err <= 2e-2 * max(1.0, want.abs().max().item())
+    assert cos > 0.999
+
+
 def test_bf16_weights_and_cuda_graph_replay(cuda_device):
     ref = ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, 1, 0), cuda_device, dtype=torch.float32)
     ref.init_cache(LENS)
@@ -138,8 +155,8 @@ def test_rope_quant_append_kernel(cuda_device, dtype, code_dtype):
     kv = paged.PagedKV.from_fused(buf, code_dtype, table.to(cuda_device), lens.to(cuda_device), B)
     q = paged.rope_quant_append(qkv.to(cuda_device), kv, Hq, 500000.0).float().cpu()
     x = qkv.float().view(B, Hq + 2 * Hkv, D)
-    want_q = ds.rope(x[:, :Hq], lens, 500000.0)
-    want_k = ds.rope(x[:, Hq:Hq + Hkv], lens, 500000.0)
+    want_q = dso.rope(x[:, :Hq], lens, 500000.0)          # the oracle's restatement, not the package's own function
+    want_k = dso.rope(x[:, Hq:Hq + Hkv], lens, 500000.0)
     want_v = x[:, Hq + Hkv:]
     assert (q - want_q).abs().max().item() <= 4e-3
     quant = oracle.quantize_int8 if code_dtype == torch.int8 else oracle.quantize_e4m3

@@ -110,7 +110,7 @@ def test_single_launch_and_two_launch_paths_agree(cuda_device, lib, quant, B, H,
         assert lib.skv_kv_evict_set_fused(0) == 0
         two = skv.fused_kv_evict(Kd, Vd, sd, budget, **kw)
     finally:
-        lib.skv_kv_evict_set_fused(1)
+        lib.skv_kv_evict_set_fused(0)
     assert torch.equal(one.indices, two.indices)
     assert torch.equal(one.indices.cpu().long(), oracle.eviction_keep_indices(scores, budget, recent))
     assert torch.equal(one.K.view(torch.uint8), two.K.view(torch.uint8)) and torch.equal(one.V.view(torch.uint8), two.V.view(torch.uint8))
