@@ -100,6 +100,10 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool,
                          long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
                          long long scale_stride_page, long long scale_stride_head,
                          float scale, int device, void* stream);
+/* Ragged batches (seq_lens given, at most 64 sequences): the host plans splits for the longest sequence the launch may
+ * hold; with waves > 0 the kernel adds up the real lengths and lengthens the splits so that the real tokens make about
+ * waves x (CTAs resident on the GPU) CTAs.  0 switches the adjustment off.  Process-wide.  No reference counterpart. */
+int skv_gqa_set_ragged_waves(int waves);
 /* Ring depth of the 8-bit kernel (an even number of 17 KB stages in 4..12); process-wide.  No reference counterpart. */
 int skv_gqa_set_q8_stages(int stages);
 /* The decode kernels are launched with programmatic stream serialisation.  on = 0 (default): they wait for the
@@ -123,6 +127,10 @@ int skv_gqa_set_early_kv(int on);
  *   read in its place and SKV_DEV_BAD_PAGE is set in the status word (skv_quest_build_meta: in *status, an optional
  *   int32 device word; skv_quest_decode: at offset 0 of the workspace, read with skv_workspace_status). */
 int skv_quest_num_blocks(int N, int block_size);
+/* on = 1: skv_quest_decode scores the blocks with the kernel that streams the metadata through a shared-memory
+ * ring by bulk asynchronous copies; on = 0 (default): with the register-load kernel, which measures faster on B200.
+ * Same results; process-wide.  No reference counterpart. */
+int skv_quest_set_ring_scores(int on);
 size_t skv_quest_workspace_bytes(int B, int Hq, int N, int block_size);
 int skv_quest_build_meta(const void* k_pool, const float* k_scale_pool, const int* page_table, const int* seq_lens,
                          void* meta_out, int B, int N, int Hkv, int D, int kv_dtype, int block_size,

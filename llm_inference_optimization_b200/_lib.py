@@ -43,10 +43,12 @@ SIGNATURES = {
     "skv_kv_evict_quant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll,
                                 _i, _i, _i, _i, _i, _vp]),
     "skv_gqa_set_q8_stages": (_i, [_i]),
+    "skv_gqa_set_ragged_waves": (_i, [_i]),
     "skv_gqa_set_early_kv": (_i, [_i]),
     "skv_gqa_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i,
                                   _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp]),
     "skv_quest_num_blocks": (_i, [_i, _i]),
+    "skv_quest_set_ring_scores": (_i, [_i]),
     "skv_quest_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "skv_quest_build_meta": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i,
                                   _ll, _ll, _ll, _ll, _ll, _vp, _i, _vp]),

@@ -78,7 +78,7 @@ def tp_parity(world: int, rank: int, dev, fused_allreduce: bool) -> dict | None:
 
 
 def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, seed: int = 4, use_graph: bool = True,
-        fill: str = "random_codes", fused_allreduce: bool = True) -> dict | None:
+        fill: str = "random_codes", fused_allreduce: bool = True, hybrid_dense_layers: int | None = None) -> dict | None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -94,7 +94,7 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
     g = torch.Generator().manual_seed(seed)
     lens = torch.randint(8192, 131073, (batch,), generator=g, dtype=torch.int32)
     model = ds.DecodeModel(cfg, shard_heads(cfg.Hq, cfg.Hkv, world, rank), dev, seed=seed)
-    model.init_cache(lens, fill=fill, seed=seed, extra_tokens=steps + warmup + 16)
+    model.init_cache(lens, fill=fill, seed=seed, extra_tokens=2 * (steps + warmup) + 32)
     fused_allreduce = fused_allreduce and world > 1
     if fused_allreduce:
         # all-reduce + residual + RMSNorm in one peer-memory kernel, no NCCL call; if the symmetric-memory
@@ -112,49 +112,87 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
             fused_allreduce = False
     tok = torch.randint(0, cfg.vocab, (batch,), generator=g).to(dev)
 
-    for _ in range(warmup):
-        logits = model.step(tok)
-    torch.cuda.synchronize()
-    if use_graph:
-        graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            model.step(tok)  # once on the capture stream so that its workspaces exist
-        torch.cuda.current_stream().wait_stream(side)
-        with torch.cuda.graph(graph):
+    def timed_run():
+        """Warm up, capture one step in a CUDA graph (optional), replay it `steps` times; ms per step, max over ranks."""
+        logits = None
+        for _ in range(warmup):
             logits = model.step(tok)
-        step = graph.replay
-    else:
-        def step():
-            nonlocal logits
-            logits = model.step(tok)
-    step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
+        torch.cuda.synchronize()
+        graph = None
+        if use_graph:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                model.step(tok)  # once on the capture stream so that its workspaces exist
+            torch.cuda.current_stream().wait_stream(side)
+            with torch.cuda.graph(graph):
+                logits = model.step(tok)
+            step = graph.replay
+        else:
+            holder = {}
+
+            def step():
+                holder["logits"] = model.step(tok)
         step()
-    e1.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    ms = e0.elapsed_time(e1) / steps
-    if world > 1:
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    finite = bool(torch.isfinite(logits.float()).all().item())
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms_ = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms_], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_ = float(t.item())
+        if not use_graph:
+            logits = holder["logits"]
+        fin = bool(torch.isfinite(logits.float()).all().item())
+        # the captured graph holds NCCL kernels: release it before anybody tears the communicator down
+        step = None
+        del graph
+        torch.cuda.synchronize()
+        return ms_, fin
+
+    ms, finite = timed_run()
+
+    hybrid = None
+    if hybrid_dense_layers is not None and 0 <= hybrid_dense_layers < layers:
+        # The reference's layer sweep (results/llama_run_20260628_233732/layer_sweep.json:20-37): sparse attention in
+        # some layers only.  Same token, same cache, dense schedule against the hybrid one, then the hybrid step timed.
+        saved = model.seq_lens.clone()
+        logits_dense = model.step(tok).float()
+        model.seq_lens.copy_(saved)
+        modes = ["dense"] * hybrid_dense_layers + ["quest"] * (layers - hybrid_dense_layers)
+        model.set_layer_modes(modes)
+        logits_hybrid = model.step(tok).float()
+        drift = (logits_hybrid - logits_dense).abs()
+        match = (logits_hybrid.argmax(-1) == logits_dense.argmax(-1)).float().mean()
+        ms_h, fin_h = timed_run()
+        hybrid = {"dense_layers": hybrid_dense_layers, "sparse_layers": layers - hybrid_dense_layers,
+                  "sparse_rule": f"Quest min/max bound, top {model.quest_top_k} blocks of {model.quest_block} tokens per query head",
+                  "ms_per_step": ms_h, "value": batch / (ms_h * 1e-3), "unit": "tok/s", "logits_finite": fin_h,
+                  "speedup_vs_all_dense": ms / ms_h,
+                  "mean_abs_logit_diff_vs_all_dense": float(drift.mean().item()),
+                  "max_abs_logit_diff_vs_all_dense": float(drift.max().item()),
+                  "argmax_match_vs_all_dense": float(match.item()),
+                  "note": "random-init weights and a random cache: the drift says what the schedule does to THESE logits, "
+                          "not what it does to a trained model"}
+        model.set_layer_modes(None)
     if fused_allreduce and model.arn.status() != 0:
         raise RuntimeError("a bounded wait for a peer ran out inside the fused all-reduce kernel")
     ib = ideal_bytes(cfg, lens, world)
     out = {
         "metric": "decode_step_tokens_per_s", "value": batch / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms,
         "n_gpus": world, "steps": steps, "warmup": warmup, "cuda_graph": use_graph, "logits_finite": finite,
-        "tp_parity": parity,
+        "tp_parity": parity, "hybrid_schedule": hybrid,
         "config": {"model": "Llama-3.1-8B architecture, random init N(0,0.02), bf16 weights", "layers": layers,
                    "batch": batch, "context_lengths": "uniform 8192..131072, seed 4", "total_context_tokens": int(lens.sum()),
                    "kv": "FP8-E4M3 paged (page 16, fused page records), per-token-per-head fp32 scales, " + fill,
@@ -165,10 +203,6 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
         "hbm_bytes_per_step_per_gpu": ib["weight_bytes_per_gpu"] + ib["kv_bytes_per_gpu"],
         "achieved_GBps_per_gpu": (ib["weight_bytes_per_gpu"] + ib["kv_bytes_per_gpu"]) / (ms * 1e-3) / 1e9,
     }
-    # the captured graph holds NCCL kernels: release it (and the model) before anybody tears the communicator down
-    step = None
-    if use_graph:
-        del graph
     del model
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
@@ -183,9 +217,11 @@ def main():
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--nccl-allreduce", action="store_true", help="use NCCL all-reduces instead of the fused kernel")
+    ap.add_argument("--hybrid-dense-layers", type=int, default=None,
+                    help="also time a schedule with dense attention in the first N layers and Quest block-sparse attention in the rest")
     args = ap.parse_args()
     res = run(args.steps, args.warmup, args.layers, args.batch, use_graph=not args.no_graph,
-              fused_allreduce=not args.nccl_allreduce)
+              fused_allreduce=not args.nccl_allreduce, hybrid_dense_layers=args.hybrid_dense_layers)
     if res is not None:
         print(json.dumps(res), flush=True)
     if dist.is_initialized():

@@ -117,6 +117,48 @@ def bench_paged(t, dev, g, peak, pk):
             del buf, kv
 
 
+def bench_ragged(t, dev, g, peak, pk):
+    """The decode step's attention launch: batch 16, context lengths uniform in 8K..128K (the seed of bench_decode), FP8
+    fused page records, with the kv-heads one rank owns at tensor-parallel degree 8 (one) and 1 (eight)."""
+    from . import _lib
+    lib = _lib.load()
+    D, P, B = 128, 16, 16
+    lens = torch.randint(8192, 131073, (B,), generator=torch.Generator().manual_seed(4), dtype=torch.int32)
+    cap = (int(lens.max()) + 15) // 16
+    pages_per_seq = [(int(n) + 15) // 16 for n in lens.tolist()]
+    total = sum(pages_per_seq)
+    perm = torch.randperm(total, generator=torch.Generator().manual_seed(4))
+    table = torch.zeros((B, cap), dtype=torch.int32)
+    o = 0
+    for b, n in enumerate(pages_per_seq):
+        table[b, :n] = perm[o:o + n].to(torch.int32)
+        o += n
+    table, dl = table.to(dev), lens.to(dev)
+    for Hkv in (1, 8):
+        Hq = 4 * Hkv
+        buf = torch.randint(0, 256, (total, Hkv, paged.RECORD_ROWS, 128), device=dev, generator=g, dtype=torch.uint8)
+        buf[:, :, :32] = torch.where((buf[:, :, :32] & 0x7F) == 0x7F, buf[:, :, :32] & 0xFE, buf[:, :, :32])
+        kv = paged.PagedKV.from_fused(buf, torch.float8_e4m3fn, table, dl, B)
+        kv.k_scale.copy_(torch.rand(kv.k_scale.shape, device=dev, generator=g) * 0.004 + 0.006)
+        kv.v_scale.copy_(torch.rand(kv.v_scale.shape, device=dev, generator=g) * 0.004 + 0.006)
+        Q = randn16((B, Hq, D), dev, g)
+        out = torch.empty_like(Q)
+        nbytes = int(lens.sum()) * Hkv * 2 * (D + 4)
+        for waves in (0, 1, 2, 3, 4, 6):
+            lib.skv_gqa_set_ragged_waves(waves)
+            try:
+                us, mn = t(lambda: _C.fused_gqa_paged(Q, kv.k_pool, kv.v_pool, kv.k_scale, kv.v_scale, table, dl, D ** -0.5,
+                                                      max_seq_len=cap * 16, out=out))
+            finally:
+                lib.skv_gqa_set_ragged_waves(RAGGED_WAVES_DEFAULT)
+            emit("dense_gqa_paged_fp8_ragged", {"B": B, "Hq": Hq, "Hkv": Hkv, "D": D, "ctx": "8K..128K (sum %d)" % int(lens.sum()),
+                                                 "ragged_waves": waves}, us, mn, nbytes, peak, pk)
+        del buf, kv
+
+
+RAGGED_WAVES_DEFAULT = 0
+
+
 def bench_token(t, dev, g, peak, pk):
     D, H = 128, 32
     for T in (4096, 16384, 65536, 131072):
@@ -175,7 +217,7 @@ def bench_quest(t, dev, g, peak, pk):
          us, mn, nbytes, peak, pk)
 
 
-ALL = {"dense": bench_dense, "paged": bench_paged, "token": bench_token, "block": bench_block, "evict": bench_evict,
+ALL = {"dense": bench_dense, "paged": bench_paged, "ragged": bench_ragged, "token": bench_token, "block": bench_block, "evict": bench_evict,
        "quest": bench_quest}
 
 

@@ -16,6 +16,9 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent / "csrc"
 LIB_NAME = "libskv_b200.so"
 LIB_PATH = CSRC / LIB_NAME
+# The same sources with -DSKV_BOUNDS: every data-dependent index is range-checked and the first violation recorded
+# (a self-checking debug build; point SKV_B200_LIB at it to run any program against it).
+BOUNDS_LIB_PATH = CSRC / "libskv_b200_bounds.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -29,22 +32,26 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def needs_build() -> bool:
-    if not LIB_PATH.exists():
+def needs_build(path: Path = LIB_PATH) -> bool:
+    if not path.exists():
         return True
-    built = LIB_PATH.stat().st_mtime
+    built = path.stat().st_mtime
     deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh"))
     return any(p.stat().st_mtime > built for p in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every ``csrc/*.cu`` into ``csrc/libskv_b200.so``; returns its path."""
-    if not force and not needs_build():
+def build(force: bool = False, verbose: bool = False, bounds: bool = False) -> Path:
+    """Compile every ``csrc/*.cu`` into ``csrc/libskv_b200.so`` (``bounds``: the range-checking debug library
+    ``csrc/libskv_b200_bounds.so``); returns its path."""
+    LIB_PATH = BOUNDS_LIB_PATH if bounds else globals()["LIB_PATH"]
+    if not force and not needs_build(LIB_PATH):
         return LIB_PATH
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: the sm_100a kernels cannot be built")
     cmd = [nvcc, *NVCC_FLAGS]
+    if bounds:
+        cmd += ["-DSKV_BOUNDS"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     tmp = LIB_PATH.with_suffix(".so.tmp")
@@ -59,5 +66,5 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv, bounds="--bounds" in sys.argv)
     print(path)

@@ -111,7 +111,7 @@ block_select_attend_kernel(const AttendParams p) {
     // softmax over the kk selected block scores, folded with 1 / count of each block
     float mx = -INFINITY;
     for (int i = tid; i < kk; i += ATT_THREADS) {
-        const float x = sc[sel[i]];
+        const float x = sc[SKV_INDEX(sel[i], p.nb)];
         w[i] = x;
         mx = fmaxf(mx, x);
     }
@@ -143,7 +143,7 @@ block_select_attend_kernel(const AttendParams p) {
     __syncthreads();
     const float inv = 1.f / fmaxf(bcast[1], 1e-9f);
     for (int i = tid; i < kk; i += ATT_THREADS) {
-        const int t0 = sel[i] * p.block_size;
+        const int t0 = SKV_INDEX(sel[i], p.nb) * p.block_size;
         const int cnt = min(p.T, t0 + p.block_size) - t0;
         w[i] = w[i] * inv / (float)cnt;  // per-token weight of block i
     }
@@ -157,7 +157,7 @@ block_select_attend_kernel(const AttendParams p) {
     const long long total = (long long)kk * p.block_size;
     for (long long r = grp; r < total; r += GROUPS) {
         const int i = (int)(r / p.block_size);
-        const int t = sel[i] * p.block_size + (int)(r - (long long)i * p.block_size);
+        const int t = SKV_INDEX(sel[i], p.nb) * p.block_size + (int)(r - (long long)i * p.block_size);
         if (t < p.T) {
             float x[8];
             unpack8(*reinterpret_cast<const uint4*>(vbase + (long long)t * p.v_st), x);
@@ -264,3 +264,5 @@ int skv_block_sparse_decode(const void* q, const void* k, const void* v, void* o
 }
 
 }  // extern "C"
+
+SKV_BOUNDS_GETTER(skv_debug_bounds_block_sparse)

@@ -79,6 +79,7 @@ struct Q8Params {
     int tiles_per_split, num_splits, stages;
     int page_size, max_pages;
     int num_pages;           // pages in the pools: ids read from the table are checked against it
+    int adapt_slots;         // > 0: CTA slots the real work of a ragged batch is spread over (see the kernel); 0: static splits
     int mode;                // Q8_SEPARATE16, Q8_SEPARATE64 or Q8_FUSED
     int out_bf16;            // output elements are bf16 instead of fp16
     int early_kv;            // pages, page table and seq_lens are not produced by the previous kernel
@@ -138,7 +139,19 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     // Ordered like any other kernel unless the caller declared the cache static (see the fp16 kernel).
     if (!p.early_kv) pdl_wait_prior_grids();
     const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
-    const int tokens_per_split = p.tiles_per_split * TILE;
+    // The host cuts the KV length for the LONGEST sequence the launch may hold (it cannot read seq_lens), which for a
+    // ragged batch with few (sequence, kv-head) pairs means many short splits: each pays its pipeline fill, its merge
+    // and a partial, and the last CTA of a long sequence combines all of them alone at the very end.  With
+    // adapt_slots set, every CTA adds up the batch's real length and lengthens the splits so that the real work
+    // makes about adapt_slots CTAs in all; splits beyond a sequence's (now smaller) count exit at once.
+    int tiles_per_split = p.tiles_per_split;
+    if (p.adapt_slots > 0) {
+        long long tiles = 0;
+        for (int i = 0; i < (int)gridDim.z; ++i) tiles += (min(max(p.seq_lens[i], 0), p.N) + TILE - 1) / TILE;
+        const long long want = (tiles * p.Hkv + p.adapt_slots - 1) / p.adapt_slots;
+        if (want > tiles_per_split) tiles_per_split = (int)want;
+    }
+    const int tokens_per_split = tiles_per_split * TILE;
     const int n_splits = len > 0 ? (len + tokens_per_split - 1) / tokens_per_split : 1;
     if (split >= n_splits) return;
     const int t_begin = split * tokens_per_split;
@@ -486,6 +499,14 @@ int skv_gqa_set_q8_stages(int stages) {
     return SKV_OK;
 }
 
+// Ragged batches (seq_lens given, at most 64 sequences): the kernel lengthens its splits so that the batch's real
+// tokens make about waves x (CTAs resident on the GPU) CTAs.  0 switches the adjustment off.  Process-wide.
+int skv_gqa_set_ragged_waves(int waves) {
+    if (waves < 0 || waves > 16) return fail(SKV_ERR_BAD_ARG, "ragged waves must be in 0..16: %d", waves);
+    gqa::tuning().ragged_waves = waves;
+    return SKV_OK;
+}
+
 int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, const float* k_scale_pool,
                          const float* v_scale_pool, const int* page_table, const int* seq_lens, void* out,
                          void* workspace, size_t workspace_bytes, int B, int N, int Hq, int Hkv, int D, int kv_dtype,
@@ -572,6 +593,8 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.page_size = page_size;
     p.max_pages = max_pages;
     p.num_pages = num_pages;
+    p.adapt_slots = (seq_lens != nullptr && B <= 64 && gqa::tuning().ragged_waves > 0)
+                        ? sm_count(device) * slots * gqa::tuning().ragged_waves : 0;
     p.mode = mode;
     p.sc_sp = scale_stride_page; p.sc_sh = scale_stride_head;
     p.q_stride_b = (long long)Hq * D; p.q_stride_h = D;

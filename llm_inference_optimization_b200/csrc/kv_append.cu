@@ -103,7 +103,7 @@ rope_quant_append_kernel(const Params p) {
         if (lane == 0 && p.status) atomicOr(p.status, SKV_DEV_BAD_PAGE);
         return;
     }
-    uint8_t* row = (is_v ? p.v_codes : p.k_codes) + page * p.sp + h * p.sh + slot * p.ss;
+    uint8_t* row = (is_v ? p.v_codes : p.k_codes) + SKV_INDEX(page, p.num_pages) * p.sp + h * p.sh + SKV_INDEX(slot, p.page_size) * p.ss;
     *reinterpret_cast<uint16_t*>(row + lane * 2) = (uint16_t)(code[0] | (code[1] << 8));
     *reinterpret_cast<uint16_t*>(row + D / 2 + lane * 2) = (uint16_t)(code[2] | (code[3] << 8));
     if (lane == 0) (is_v ? p.v_scale : p.k_scale)[page * p.csp + h * p.csh + slot] = scale;
@@ -180,3 +180,5 @@ int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k
 }
 
 }  // extern "C"
+
+SKV_BOUNDS_GETTER(skv_debug_bounds_kv_append)

@@ -338,7 +338,7 @@ __device__ __forceinline__ void cluster_select_row(const SelectParams& p, cooper
             const uint32_t beq = __ballot_sync(0xffffffffu, iseq);
             const bool sel = isgt || (iseq && (int)(eqrun + __popc(beq & lt)) < need);
             const uint32_t bsel = __ballot_sync(0xffffffffu, sel);
-            if (sel) out[pos + __popc(bsel & lt)] = s0 + j * 32 + lane;
+            if (sel) out[SKV_INDEX(pos + __popc(bsel & lt), p.keep)] = s0 + j * 32 + lane;
             pos += __popc(bsel);
             eqrun += __popc(beq);
         }
@@ -368,7 +368,7 @@ struct GatherParams {
     void* v_out;
     float* k_scale;    // [rows, keep] (scaled modes only)
     float* v_scale;
-    int H, keep;
+    int H, keep, T;
     long long rows_total;  // B * H * keep
     long long sb, sh, st;
 };
@@ -502,7 +502,7 @@ evict_gather_quant_kernel(const GatherParams p) {
         uint4 kr[U], vr[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const long long src = base + (long long)max(t[u], 0) * p.st;
+            const long long src = base + (long long)SKV_INDEX(max(t[u], 0), p.T) * p.st;
             kr[u] = ld_stream16(p.k + src);
             vr[u] = ld_stream16(p.v + src);
         }
@@ -559,7 +559,7 @@ evict_fused_cluster_kernel(const SelectParams p, const GatherParams g) {
         uint4 kr[U], vr[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {   // rows past the end repeat the slice's last row; only their stores are dropped
-            const long long src = base + (long long)max(t[u], 0) * g.st;
+            const long long src = base + (long long)SKV_INDEX(max(t[u], 0), p.T) * g.st;
             kr[u] = ld_stream16(g.k + src);
             vr[u] = ld_stream16(g.v + src);
         }
@@ -687,7 +687,7 @@ int skv_kv_evict_quant(const void* k_cache, const void* v_cache, const float* sc
     gp.v = static_cast<const __half*>(v_cache);
     gp.idx = idx_out;
     gp.k_out = k_out; gp.v_out = v_out; gp.k_scale = k_scale_out; gp.v_scale = v_scale_out;
-    gp.H = H; gp.keep = keep; gp.rows_total = (long long)B * H * keep;
+    gp.H = H; gp.keep = keep; gp.T = T; gp.rows_total = (long long)B * H * keep;
     gp.sb = kv_stride_b; gp.sh = kv_stride_h; gp.st = kv_stride_t;
 
     const int competing = T - (recent < T ? recent : T);
@@ -713,3 +713,5 @@ int skv_kv_evict_quant(const void* k_cache, const void* v_cache, const float* sc
 }
 
 }  // extern "C"
+
+SKV_BOUNDS_GETTER(skv_debug_bounds_kv_evict)

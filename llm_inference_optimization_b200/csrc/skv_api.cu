@@ -23,3 +23,27 @@ int skv_workspace_status(const void* workspace, int device, void* stream, int* s
 }
 
 }  // extern "C"
+
+#ifdef SKV_BOUNDS
+// Self-test of the range-check instrumentation: a kernel pushes one index that is in range and one that is not
+// through SKV_INDEX without touching memory through them; returns what the macro gave back and what it recorded.
+namespace skv {
+__global__ void bounds_selftest_kernel(int* out) {
+    const int i = threadIdx.x;           // not a compile-time constant
+    out[0] = SKV_INDEX(i + 2, 3);        // in range: 2
+    out[1] = SKV_INDEX(i + 5, 3);        // out of range: replaced by 0, line recorded
+}
+}  // namespace skv
+extern "C" int skv_debug_bounds_selftest(int* in_range, int* clamped, int* recorded_line) {
+    int* d = nullptr;
+    int h[2] = {-1, -1};
+    if (cudaMalloc(&d, 2 * sizeof(int)) != cudaSuccess) return SKV_ERR_CUDA;
+    skv::bounds_selftest_kernel<<<1, 1>>>(d);
+    cudaError_t e = cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (e != cudaSuccess) return SKV_ERR_CUDA;
+    *in_range = h[0];
+    *clamped = h[1];
+    return cudaMemcpyFromSymbol(recorded_line, skv::skv_bounds_word, sizeof(int)) == cudaSuccess ? SKV_OK : SKV_ERR_CUDA;
+}
+#endif

@@ -118,6 +118,31 @@ __device__ __forceinline__ void report_bad_page(bool bad, int* status) {
     if (bad && status) atomicOr(status, SKV_DEV_BAD_PAGE);
 }
 
+// Range checks of data-dependent indices (instrumented builds only: -DSKV_BOUNDS).  compute-sanitizer stands in for
+// nothing here, so the debug library checks itself: every index that is computed from data (a selected token or block,
+// a page id, a list entry) goes through SKV_INDEX(i, n) before it becomes an address.  In the instrumented build an
+// index outside [0, n) records the source line of the FIRST violation in a per-file device word, read back by that
+// file's skv_debug_bounds_*(), and is replaced by 0 so that the access stays inside the buffer; nothing traps.  In the
+// shipped build the macro is the index itself.
+#ifdef SKV_BOUNDS
+static __device__ int skv_bounds_word;   // one copy per translation unit; 0 = no violation seen
+__device__ __forceinline__ long long skv_checked_index(long long i, long long n, int line) {
+    if (i < 0 || i >= n) {
+        atomicCAS(&skv_bounds_word, 0, line);
+        return 0;
+    }
+    return i;
+}
+#define SKV_INDEX(i, n) ((int)::skv::skv_checked_index((long long)(i), (long long)(n), __LINE__))
+#define SKV_BOUNDS_GETTER(name)                                                                            \
+    extern "C" int name(int* out) {                                                                        \
+        return cudaMemcpyFromSymbol(out, ::skv::skv_bounds_word, sizeof(int)) == cudaSuccess ? 0 : -4;     \
+    }
+#else
+#define SKV_INDEX(i, n) (i)
+#define SKV_BOUNDS_GETTER(name)
+#endif
+
 // Phase timestamps for kernel tuning (instrumented builds only: -DSKV_PROFILE_PHASES): thread 0 of CTA 0 records the
 // global timer at numbered points; a per-file skv_debug_phase_ts_*() copies them out.  Compiled out of the shipped library.
 #ifdef SKV_PROFILE_PHASES

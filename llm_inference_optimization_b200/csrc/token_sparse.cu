@@ -157,7 +157,7 @@ token_select_attend_kernel(const AttendParams p) {
         // lower candidate index first" is the same rule as "lower token position first"
         block_topk_sorted_auto<ATT_THREADS, 4>(p.cand_score + (long long)row * p.nc, p.nc, kk, top, tk);
         __syncthreads();
-        for (int i = tid; i < kk; i += ATT_THREADS) top[i] = p.cand_pos[(long long)row * p.nc + top[i]];
+        for (int i = tid; i < kk; i += ATT_THREADS) top[i] = p.cand_pos[(long long)row * p.nc + SKV_INDEX(top[i], p.nc)];
         __syncthreads();
     } else {
         block_topk_sorted_auto<ATT_THREADS, 8>(sc, p.T, kk, top, tk);
@@ -191,7 +191,7 @@ token_select_attend_kernel(const AttendParams p) {
     // 3. softmax over the kept scores
     float mx = -INFINITY;
     for (int i = tid; i < n; i += ATT_THREADS) {
-        const float x = sc[sel[i]];
+        const float x = sc[SKV_INDEX(sel[i], p.T)];
         w[i] = x;
         mx = fmaxf(mx, x);
     }
@@ -230,7 +230,7 @@ token_select_attend_kernel(const AttendParams p) {
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     const __half* vbase = p.v + b * p.v_sb + h * p.v_sh + sub * 8;
     for (int j = grp; j < n; j += GROUPS) {
-        const uint4 vv = *reinterpret_cast<const uint4*>(vbase + (long long)sel[j] * p.v_st);
+        const uint4 vv = *reinterpret_cast<const uint4*>(vbase + (long long)SKV_INDEX(sel[j], p.T) * p.v_st);
         const float wj = w[j];
         const __half2* hv = reinterpret_cast<const __half2*>(&vv);
 #pragma unroll
@@ -371,3 +371,5 @@ int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* o
 }
 
 }  // extern "C"
+
+SKV_BOUNDS_GETTER(skv_debug_bounds_token_sparse)

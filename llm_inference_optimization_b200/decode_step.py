@@ -111,9 +111,18 @@ class DecodeModel:
     """The rank-local slice of the model and of every layer's cache."""
 
     def __init__(self, cfg: ModelConfig, shard: HeadShard, device, *, seed: int = 4, dtype=torch.bfloat16,
-                 attention: AttentionFn = kernel_attention, group=None):
+                 attention: AttentionFn = kernel_attention, group=None, layer_modes: list[str] | None = None,
+                 quest_block: int = 64, quest_top_k: int = 8):
+        """``layer_modes``: per layer ``"dense"`` (attention over the whole cache) or ``"quest"`` (block-sparse: the
+        ``quest_top_k`` blocks of ``quest_block`` tokens with the highest min/max upper-bound score per query head).
+        The reference's layer sweep found sparse attention harmless in the first half of the layers only
+        (results/llama_run_20260628_233732/layer_sweep.json:20-37; ``sparse_layers`` of its ``patch_attention``,
+        benchmarks/llama_integration_benchmark.py:114-230): a schedule is this list."""
         self.cfg, self.shard, self.device, self.dtype = cfg, shard, torch.device(device), dtype
         self.attention, self.group = attention, group
+        self.quest_block, self.quest_top_k = int(quest_block), int(quest_top_k)
+        self.metas: list[Tensor | None] = []
+        self.set_layer_modes(layer_modes)
         # the fused RoPE + quantise + append kernel needs fp16/bf16 activations on a CUDA device
         self.fused_glue = (self.device.type == "cuda" and dtype in (torch.float16, torch.bfloat16)
                            and attention is kernel_attention)
@@ -142,6 +151,38 @@ class DecodeModel:
         self.page_table: Tensor | None = None
         self.seq_lens: Tensor | None = None
         self.max_seq_len = 0
+
+    # ------------------------------------------------------------------ per-layer sparsity schedule
+    def set_layer_modes(self, layer_modes: list[str] | None) -> None:
+        """Choose dense or Quest block-sparse attention per layer; builds the block metadata of layers that turn sparse."""
+        modes = list(layer_modes) if layer_modes is not None else ["dense"] * self.cfg.layers
+        if len(modes) != self.cfg.layers or any(m not in ("dense", "quest") for m in modes):
+            raise ValueError("layer_modes must name 'dense' or 'quest' for every layer")
+        self.layer_modes = modes
+        if getattr(self, "caches", None):
+            for l, m in enumerate(modes):   # a dense layer's appends do not maintain metadata: drop what would go stale
+                if m == "dense" and l < len(self.metas):
+                    self.metas[l] = None
+            self._build_missing_metas()
+
+    def _layer_kv(self, cache: "LayerCache", lens: Tensor):
+        return paged.PagedKV(cache.k, cache.v, cache.ks, cache.vs, self.page_table, lens, lens.numel())
+
+    def _build_missing_metas(self) -> None:
+        if len(self.metas) != len(self.caches):
+            self.metas = [None] * len(self.caches)
+        for l, (mode, cache) in enumerate(zip(self.layer_modes, self.caches)):
+            if mode == "quest" and self.metas[l] is None:
+                self.metas[l] = paged.build_block_meta(self._layer_kv(cache, self.seq_lens), self.quest_block,
+                                                       max_seq_len=self.max_seq_len)
+
+    def _quest_attention(self, q: Tensor, l: int, new_lens: Tensor, scale: float, meta_is_current: bool) -> Tensor:
+        """Block-sparse attention of layer ``l`` for fp16 ``q [B, n_q, D]`` over the cache holding ``new_lens`` tokens."""
+        kv = self._layer_kv(self.caches[l], new_lens)
+        if not meta_is_current:   # the eager append of the fp32 test path does not touch the metadata
+            self.metas[l] = paged.build_block_meta(kv, self.quest_block, max_seq_len=self.max_seq_len)
+        return paged.quest_sparse_decode(q, kv, self.metas[l], scale, self.quest_block, self.quest_top_k,
+                                         max_seq_len=self.max_seq_len)
 
     # ------------------------------------------------------------------ cache set-up
     def init_cache(self, seq_lens: Tensor, *, fill: str = "normal", seed: int = 4, extra_tokens: int = 64) -> None:
@@ -188,6 +229,8 @@ class DecodeModel:
                 elif fill != "zeros":
                     raise ValueError(f"unknown fill {fill!r}")
             self.caches.append(c)
+        self.metas = [None] * cfg.layers
+        self._build_missing_metas()
 
     # ------------------------------------------------------------------ the step
     def _all_reduce(self, x: Tensor) -> Tensor:
@@ -207,11 +250,7 @@ class DecodeModel:
         h = glue.residual_rmsnorm(x, None, self.layers[0]["n1"], cfg.rms_eps)
         for li, (w, cache) in enumerate(zip(self.layers, self.caches)):
             qkv = h @ w["wqkv"]
-            kvv = paged.PagedKV(cache.k, cache.v, cache.ks, cache.vs, self.page_table, pos, B)
-            q = paged.rope_quant_append(qkv, kvv, sh.n_q, cfg.rope_theta)
-            a = torch.empty((B, sh.n_q, D), dtype=x.dtype, device=x.device)
-            _C.fused_gqa_paged(q, cache.k, cache.v, cache.ks, cache.vs, self.page_table, new_lens, scale,
-                               max_seq_len=self.max_seq_len, out=a)
+            a = self._fused_attention(li, qkv, cache, pos, new_lens, scale, x.dtype)
             torch.matmul(a.view(B, sh.n_q * D), w["wo"], out=arn.partial(0))
             h = arn.reduce_norm(0, x, w["n2"], cfg.rms_eps)
             torch.matmul(glue.silu_mul(h @ w["wgu"]), w["wd"], out=arn.partial(1))
@@ -219,6 +258,22 @@ class DecodeModel:
             h = arn.reduce_norm(1, x, nxt, cfg.rms_eps)
         self.seq_lens.add_(1)
         return h @ self.lm_head
+
+    def _fused_attention(self, li: int, qkv: Tensor, cache: "LayerCache", pos: Tensor, new_lens: Tensor, scale: float,
+                         dtype) -> Tensor:
+        """RoPE + quantise + append (one launch, which also keeps a sparse layer's block metadata current), then the
+        layer's attention: dense over the whole paged cache, or Quest block-sparse; ``[B, n_q, D]`` in ``dtype``."""
+        from . import _C
+        sh, D, B = self.shard, self.cfg.D, qkv.shape[0]
+        sparse = self.layer_modes[li] == "quest"
+        q = paged.rope_quant_append(qkv, self._layer_kv(cache, pos), sh.n_q, self.cfg.rope_theta,
+                                    meta=self.metas[li] if sparse else None, block_size=self.quest_block)
+        if sparse:
+            return self._quest_attention(q, li, new_lens, scale, meta_is_current=True).to(dtype)
+        a = torch.empty((B, sh.n_q, D), dtype=dtype, device=qkv.device)
+        _C.fused_gqa_paged(q, cache.k, cache.v, cache.ks, cache.vs, self.page_table, new_lens, scale,
+                           max_seq_len=self.max_seq_len, out=a)
+        return a
 
     def enable_fused_allreduce(self, batch: int) -> None:
         """Replace the two NCCL all-reduces per layer by the fused peer-memory kernel (CUDA, world > 1, fixed batch)."""
@@ -245,20 +300,16 @@ class DecodeModel:
             if self.fused_allreduce:
                 return self._step_fused_allreduce(x, pos, new_lens, scale)
             delta = None
-            for w, cache in zip(self.layers, self.caches):
+            for li, (w, cache) in enumerate(zip(self.layers, self.caches)):
                 h = glue.residual_rmsnorm(x, delta, w["n1"], cfg.rms_eps)
                 qkv = h @ w["wqkv"]
-                kvv = paged.PagedKV(cache.k, cache.v, cache.ks, cache.vs, self.page_table, pos, B)
-                q = paged.rope_quant_append(qkv, kvv, sh.n_q, cfg.rope_theta)
-                a = torch.empty((B, sh.n_q, D), dtype=x.dtype, device=x.device)
-                _C.fused_gqa_paged(q, cache.k, cache.v, cache.ks, cache.vs, self.page_table, new_lens, scale,
-                                   max_seq_len=self.max_seq_len, out=a)
+                a = self._fused_attention(li, qkv, cache, pos, new_lens, scale, x.dtype)
                 o = self._all_reduce(a.view(B, sh.n_q * D) @ w["wo"])
                 h = glue.residual_rmsnorm(x, o, w["n2"], cfg.rms_eps)
                 delta = self._all_reduce(glue.silu_mul(h @ w["wgu"]) @ w["wd"])
             self.seq_lens.add_(1)
             return glue.residual_rmsnorm(x, delta, self.final_norm, cfg.rms_eps) @ self.lm_head
-        for w, cache in zip(self.layers, self.caches):
+        for li, (w, cache) in enumerate(zip(self.layers, self.caches)):
             h = rms_norm(x, w["n1"], cfg.rms_eps)
             qkv = h @ w["wqkv"]
             q = qkv[:, :sh.n_q * D].view(B, sh.n_q, D)
@@ -266,7 +317,10 @@ class DecodeModel:
             v = qkv[:, (sh.n_q + sh.n_kv) * D:].view(B, sh.n_kv, D)
             q, k = rope(q, pos, cfg.rope_theta), rope(k, pos, cfg.rope_theta)
             cache.append(k, v, self.page_table, pos)
-            a = self.attention(q, cache, self.page_table, new_lens, scale, self.max_seq_len)
+            if self.layer_modes[li] == "quest":
+                a = self._quest_attention(q.to(torch.float16).contiguous(), li, new_lens, scale, meta_is_current=False)
+            else:
+                a = self.attention(q, cache, self.page_table, new_lens, scale, self.max_seq_len)
             o = a.to(x.dtype).reshape(B, sh.n_q * D) @ w["wo"]
             x = x + self._all_reduce(o)
             h = rms_norm(x, w["n2"], cfg.rms_eps)

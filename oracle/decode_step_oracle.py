@@ -32,9 +32,29 @@ def rope(x, pos, theta):
     return x * cos + rot * sin
 
 
-def decode_step(weights: dict, cfg, tokens, k_hist, v_hist, seq_lens):
+def quest_attention(q, K, V, lens, block: int, top_k: int, scale: float):
+    """Block-sparse attention of one layer, sequence by sequence (no reference counterpart; the rule is the one of
+    ``skv_oracle.quest_block_scores``): min/max metadata of the sequence's own tokens, upper-bound block scores per
+    query head, the ``top_k`` best blocks (ties: lower block), exact softmax attention over their tokens.
+    ``q [B, Hq, D]``, ``K``/``V [B, Hkv, T, D]`` fp32, ``lens [B]`` -> ``[B, Hq, D]`` fp32."""
+    out = torch.zeros(q.shape[0], q.shape[1], q.shape[2])
+    for b in range(q.shape[0]):
+        n = int(lens[b])
+        nb = (n + block - 1) // block
+        meta = skv_oracle.block_minmax_meta(K[b:b + 1, :, :n], block)
+        sc = skv_oracle.quest_block_scores(q[b:b + 1], meta, scale)
+        idx = skv_oracle.topk_blocks(sc, min(top_k, nb))
+        out[b] = skv_oracle.attend_selected_blocks(q[b:b + 1], K[b:b + 1], V[b:b + 1], idx, block, scale,
+                                                   lens[b:b + 1].to(torch.int32))[0]
+    return out
+
+
+def decode_step(weights: dict, cfg, tokens, k_hist, v_hist, seq_lens, layer_modes=None, quest_block: int = 64,
+                quest_top_k: int = 8):
     """``weights``: fp32 full matrices (embed, lm_head, final_norm, layers[l][wq|wk|wv|wo|wg|wu|wd|n1|n2]);
-    ``k_hist[l]``/``v_hist[l]``: ``[B, Hkv, Tmax, D]`` fp32 dequantised history; returns logits ``[B, vocab]``."""
+    ``k_hist[l]``/``v_hist[l]``: ``[B, Hkv, Tmax, D]`` fp32 dequantised history; returns logits ``[B, vocab]``.
+    ``layer_modes[l] == "quest"`` replaces the layer's dense attention by ``quest_attention`` (the per-layer schedule
+    of the reference's ``sparse_layers``, benchmarks/llama_integration_benchmark.py:114-230)."""
     B = tokens.shape[0]
     D, Hq, Hkv = cfg.D, cfg.Hq, cfg.Hkv
     x = weights["embed"][tokens]
@@ -51,8 +71,11 @@ def decode_step(weights: dict, cfg, tokens, k_hist, v_hist, seq_lens):
         for b in range(B):
             K[b, :, pos[b]] = kq[b]
             V[b, :, pos[b]] = vq[b]
-        a = skv_oracle.dense_gqa_decode(q.half().float(), K.permute(0, 2, 1, 3), V.permute(0, 2, 1, 3), 1.0 / math.sqrt(D),
-                                        (seq_lens + 1).to(torch.int32))
+        if layer_modes is not None and layer_modes[l] == "quest":
+            a = quest_attention(q.half().float(), K, V, seq_lens + 1, quest_block, quest_top_k, 1.0 / math.sqrt(D))
+        else:
+            a = skv_oracle.dense_gqa_decode(q.half().float(), K.permute(0, 2, 1, 3), V.permute(0, 2, 1, 3),
+                                            1.0 / math.sqrt(D), (seq_lens + 1).to(torch.int32))
         x = x + a.reshape(B, Hq * D) @ w["wo"]
         h = _rms(x, w["n2"], cfg.rms_eps)
         x = x + (torch.nn.functional.silu(h @ w["wg"]) * (h @ w["wu"])) @ w["wd"]

@@ -71,6 +71,42 @@ def test_bf16_fused_glue_path_matches_oracle_model(cuda_device):
     assert cos > 0.999
 
 
+def test_hybrid_layer_schedule_matches_oracle_model(cuda_device):
+    """Dense attention in layer 0, Quest block-sparse attention (4 blocks of 64 tokens) in layer 1, against the oracle
+    model with the same schedule."""
+    modes = ["dense", "quest"]
+    m = ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, 1, 0), cuda_device, dtype=torch.float32, layer_modes=modes,
+                       quest_block=64, quest_top_k=4)
+    m.init_cache(LENS)
+    weights, k_hist, v_hist = oracle_inputs(m)
+    want = dso.decode_step(weights, CFG, TOK, k_hist, v_hist, LENS.clone(), layer_modes=modes, quest_block=64, quest_top_k=4)
+    dense = dso.decode_step(weights, CFG, TOK, k_hist, v_hist, LENS.clone())
+    got = m.step(TOK.to(cuda_device)).cpu()
+    assert (got - want).abs().max().item() <= 5e-3 * max(1.0, want.abs().max().item())
+    assert (want - dense).abs().max().item() > 1e-3      # the schedule really changes the longest sequence's result
+
+
+def test_sparse_layers_that_select_every_block_equal_the_dense_model(cuda_device):
+    """The benchmarked path (bf16, fused glue kernels) with every layer block-sparse and top_k covering the whole
+    cache must reproduce the all-dense model, also on the second token, whose blocks' metadata was brought up to
+    date by the append kernel rather than rebuilt."""
+    tok = TOK.to(cuda_device)
+    dense = ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, 1, 0), cuda_device, dtype=torch.bfloat16)
+    dense.init_cache(LENS)
+    sparse = ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, 1, 0), cuda_device, dtype=torch.bfloat16,
+                            layer_modes=["quest", "quest"], quest_block=64, quest_top_k=16)
+    sparse.init_cache(LENS)
+    for _ in range(2):
+        want, got = dense.step(tok).float(), sparse.step(tok).float()
+        assert (got - want).abs().max().item() <= 3e-2 * max(1.0, want.abs().max().item())
+    # switching a layer back to dense and then to sparse again rebuilds its metadata instead of reusing a stale one
+    sparse.set_layer_modes(["dense", "quest"])
+    dense.step(tok), sparse.step(tok)
+    sparse.set_layer_modes(["quest", "quest"])
+    want, got = dense.step(tok).float(), sparse.step(tok).float()
+    assert (got - want).abs().max().item() <= 3e-2 * max(1.0, want.abs().max().item())
+
+
 def test_bf16_weights_and_cuda_graph_replay(cuda_device):
     ref = ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, 1, 0), cuda_device, dtype=torch.float32)
     ref.init_cache(LENS)
