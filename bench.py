@@ -271,6 +271,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip every leg but the headline loop (profiling runs)")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-decode-step", action="store_true", help="skip the full decode-step tokens/s leg")
+    ap.add_argument("--no-graph", action="store_true", help="enqueue every launch from Python instead of replaying a CUDA graph of one step")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -320,7 +321,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return [float(v) for v in t.tolist()]
 
-    def time_steps(ctx, n_layers, steps, warm, early_kv=False):
+    def time_steps(ctx, n_layers, steps, warm, early_kv=False, use_graph=True):
         """ms per step (max over ranks), every rank's ms, and the host's enqueue time per call in us."""
         Q, Ks, Vs = make_layers(ctx, n_layers, seed=1)
         out = torch.empty(batch, hq_l, D, device=dev, dtype=torch.float16)
@@ -332,37 +333,61 @@ def main():
         # early_kv: the caller's statement that no launch writes the K/V a later launch reads (true here: the
         # caches are static), which lets a launch stream K/V while the previous launch's combine tail drains.
         lib.skv_gqa_set_early_kv(1 if early_kv else 0)
+        graph = None
         try:
             for _ in range(warm):
                 step()
+            torch.cuda.synchronize()
+            # the host's enqueue cost per call, from an un-synchronised eager pass (the GPU is still busy when it ends)
+            h0 = time.perf_counter()
+            step()
+            host_us = (time.perf_counter() - h0) * 1e6 / n_layers
+            torch.cuda.synchronize()
+            if use_graph:
+                # One step (32 launches) captured in a CUDA graph and replayed: the timed region then does not depend
+                # on how fast each rank's Python loop enqueues (with 8 single-threaded ranks on one host the slowest
+                # rank's launch path, not a kernel, set the max-over-ranks time).
+                graph = torch.cuda.CUDAGraph()
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    step()   # once on the capture stream so that its workspace exists
+                torch.cuda.current_stream().wait_stream(side)
+                with torch.cuda.graph(graph, stream=side):
+                    step()
+                run_step = graph.replay
+            else:
+                run_step = step
+            for _ in range(2):
+                run_step()
             torch.cuda.synchronize()
             if world > 1:
                 dist.barrier()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            h0 = time.perf_counter()
             e0.record()
             for _ in range(steps):
-                step()
+                run_step()
             e1.record()
-            host_us = (time.perf_counter() - h0) * 1e6 / (steps * n_layers)   # un-synchronised: the enqueue cost
             torch.cuda.synchronize()
             if world > 1:
                 dist.barrier()
             torch.cuda.synchronize()
         finally:
             lib.skv_gqa_set_early_kv(0)
+            del graph
         ms_all = gather_ranks(e0.elapsed_time(e1) / steps)
-        st = _workspace.status(_workspace.get("gqa", 0, dev))
-        if st != 0:
-            raise SystemExit(f"device status word {st}: a bounded wait inside the decode kernel ran out")
+        for ws in _workspace.all_of("gqa", dev):
+            st = _workspace.status(ws)
+            if st != 0:
+                raise SystemExit(f"device status word {st}: a bounded wait inside the decode kernel ran out")
         del Ks, Vs
         torch.cuda.empty_cache()
         return max(ms_all), ms_all, max(gather_ranks(host_us))
 
     sampler = ClockSampler(local)
     with sampler:
-        ms_step, ms_ranks, host_us = time_steps(args.ctx, layers, args.steps, warmup)
+        ms_step, ms_ranks, host_us = time_steps(args.ctx, layers, args.steps, warmup, use_graph=not args.no_graph)
     clocks = sampler.summary()
 
     bytes_layer_rank = kv_bytes(args.ctx, hkv_l, batch)
@@ -379,6 +404,7 @@ def main():
         "dtype": DTYPE, "data": "synthetic (seeded N(0,1)/sqrt(D), generated on device)",
         "config": workload_config(args.ctx, layers, world),
         "launch": {
+            "cuda_graph": not args.no_graph,
             "kv_splits": lib.skv_gqa_decode_splits(batch, args.ctx, hq_l, hkv_l, D, local),
             "order": "default: every launch waits for the one before it (what a real decode step needs, since the "
                      "layer's K/V page is written just before its attention launch); 'early_kv_launches' times the "
@@ -399,7 +425,7 @@ def main():
     if not args.no_extras:
         half = max(3, args.steps // 2)
         # ---- the opt-in launch mode for static caches, and the 128K point of the metric (fewer layers: same bytes)
-        ms_e, _, _ = time_steps(args.ctx, layers, half, 3, early_kv=True)
+        ms_e, _, _ = time_steps(args.ctx, layers, half, 3, early_kv=True, use_graph=not args.no_graph)
         g_e = bytes_layer_rank / (ms_e * 1e-3 / layers) / 1e9
         line["early_kv_launches"] = {"us_per_layer": ms_e * 1e3 / layers, "gbs_per_gpu": g_e, "frac_of_peak": g_e / peak,
                                      "note": "skv_gqa_set_early_kv(1): a launch streams K/V before the previous launch "
@@ -407,7 +433,7 @@ def main():
         by_ctx = {str(args.ctx): {"us_per_layer": us_layer, "gbs_per_gpu": per_gpu_gbs, "frac_of_peak": per_gpu_gbs / peak}}
         if args.ctx != 131072:
             l128 = max(2, layers // 2)
-            ms128, _, _ = time_steps(131072, l128, half, 3)
+            ms128, _, _ = time_steps(131072, l128, half, 3, use_graph=not args.no_graph)
             us128 = ms128 * 1e3 / l128
             g128 = kv_bytes(131072, hkv_l, batch) / (us128 * 1e-6) / 1e9
             by_ctx["131072"] = {"us_per_layer": us128, "gbs_per_gpu": g128, "frac_of_peak": g128 / peak}
@@ -424,10 +450,24 @@ def main():
         hO = torch.empty(batch, hq_l, D, dtype=torch.float16).pin_memory()
         dQ, dK, dV = torch.empty_like(hQ, device=dev), torch.empty_like(hK, device=dev), torch.empty_like(hV, device=dev)
 
+        # K and V cross the bus in eight chunks alternating between two copy streams: one stream alone leaves a few
+        # percent of the PCIe link unused (51 against 54 GB/s measured)
+        c1, c2 = torch.cuda.Stream(), torch.cuda.Stream()
+        n_chunks = 8
+        chunk = (args.ctx + n_chunks - 1) // n_chunks
+
         def e2e_host_kv():
+            cur = torch.cuda.current_stream()
+            c1.wait_stream(cur)
+            c2.wait_stream(cur)
+            for i in range(n_chunks):
+                lo, hi = i * chunk, min(args.ctx, (i + 1) * chunk)
+                with torch.cuda.stream(c1 if i % 2 == 0 else c2):
+                    dK[:, lo:hi].copy_(hK[:, lo:hi], non_blocking=True)
+                    dV[:, lo:hi].copy_(hV[:, lo:hi], non_blocking=True)
             dQ.copy_(hQ, non_blocking=True)
-            dK.copy_(hK, non_blocking=True)
-            dV.copy_(hV, non_blocking=True)
+            cur.wait_stream(c1)
+            cur.wait_stream(c2)
             o = _C.fused_gqa(dQ, dK, dV, scale)
             hO.copy_(o, non_blocking=True)
 

@@ -104,6 +104,10 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool,
  * hold; with waves > 0 the kernel adds up the real lengths and lengthens the splits so that the real tokens make about
  * waves x (CTAs resident on the GPU) CTAs.  0 switches the adjustment off.  Process-wide.  No reference counterpart. */
 int skv_gqa_set_ragged_waves(int waves);
+/* FP8 caches, at most 8 query heads per kv-head: mode 1 forces the kernel variant that fits two CTAs on an SM, 0 the
+ * variant with one CTA per SM, -1 (default) lets the launcher choose by problem size.  Process-wide.  No reference
+ * counterpart. */
+int skv_gqa_set_q8_two_per_sm(int mode);
 /* Ring depth of the 8-bit kernel (an even number of 17 KB stages in 4..12); process-wide.  No reference counterpart. */
 int skv_gqa_set_q8_stages(int stages);
 /* The decode kernels are launched with programmatic stream serialisation.  on = 0 (default): they wait for the

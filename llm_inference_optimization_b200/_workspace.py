@@ -25,6 +25,12 @@ def get(kind: str, nbytes: int, device: torch.device) -> torch.Tensor:
     return buf
 
 
+def all_of(kind: str, device: torch.device) -> list[torch.Tensor]:
+    """Every cached workspace of one kind on a device (one per stream that has launched with it)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return [buf for (k, d, _), buf in _cache.items() if k == kind and d == index]
+
+
 def status(buf: torch.Tensor) -> int:
     """Read (and synchronise on) the device status word of a workspace."""
     out = C.c_int(0)

@@ -78,7 +78,11 @@ def tp_parity(world: int, rank: int, dev, fused_allreduce: bool) -> dict | None:
 
 
 def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, seed: int = 4, use_graph: bool = True,
-        fill: str = "random_codes", fused_allreduce: bool = True, hybrid_dense_layers: int | None = None) -> dict | None:
+        fill: str = "random_codes", fused_allreduce: bool = True, hybrid_dense_layers: int | None = None,
+        emulate_tp: int = 0) -> dict | None:
+    """``emulate_tp`` (single process only): build rank 0's shard of an ``emulate_tp``-way tensor-parallel model on one
+    GPU and run its step without the exchange -- every kernel then has the shapes it has at that degree, which is what
+    a per-kernel launch list needs (a profiler must not wrap a multi-rank run)."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -93,7 +97,10 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
     cfg = ds.ModelConfig(layers=layers)
     g = torch.Generator().manual_seed(seed)
     lens = torch.randint(8192, 131073, (batch,), generator=g, dtype=torch.int32)
-    model = ds.DecodeModel(cfg, shard_heads(cfg.Hq, cfg.Hkv, world, rank), dev, seed=seed)
+    shard_world = emulate_tp if (emulate_tp > 1 and world == 1) else world
+    model = ds.DecodeModel(cfg, shard_heads(cfg.Hq, cfg.Hkv, shard_world, rank), dev, seed=seed)
+    if shard_world != world:
+        model._all_reduce = lambda x: x   # one rank of the emulated group: its partial sums stand in for the reduced ones
     model.init_cache(lens, fill=fill, seed=seed, extra_tokens=2 * (steps + warmup) + 32)
     fused_allreduce = fused_allreduce and world > 1
     if fused_allreduce:
@@ -188,10 +195,10 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
         model.set_layer_modes(None)
     if fused_allreduce and model.arn.status() != 0:
         raise RuntimeError("a bounded wait for a peer ran out inside the fused all-reduce kernel")
-    ib = ideal_bytes(cfg, lens, world)
+    ib = ideal_bytes(cfg, lens, shard_world)
     out = {
         "metric": "decode_step_tokens_per_s", "value": batch / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms,
-        "n_gpus": world, "steps": steps, "warmup": warmup, "cuda_graph": use_graph, "logits_finite": finite,
+        "n_gpus": world, "emulated_tp_shard": shard_world if shard_world != world else None, "steps": steps, "warmup": warmup, "cuda_graph": use_graph, "logits_finite": finite,
         "tp_parity": parity, "hybrid_schedule": hybrid,
         "config": {"model": "Llama-3.1-8B architecture, random init N(0,0.02), bf16 weights", "layers": layers,
                    "batch": batch, "context_lengths": "uniform 8192..131072, seed 4", "total_context_tokens": int(lens.sum()),
@@ -217,11 +224,14 @@ def main():
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--nccl-allreduce", action="store_true", help="use NCCL all-reduces instead of the fused kernel")
+    ap.add_argument("--emulate-tp", type=int, default=0,
+                    help="single process: run rank 0's shard of an N-way tensor-parallel model without the exchange")
     ap.add_argument("--hybrid-dense-layers", type=int, default=None,
                     help="also time a schedule with dense attention in the first N layers and Quest block-sparse attention in the rest")
     args = ap.parse_args()
     res = run(args.steps, args.warmup, args.layers, args.batch, use_graph=not args.no_graph,
-              fused_allreduce=not args.nccl_allreduce, hybrid_dense_layers=args.hybrid_dense_layers)
+              fused_allreduce=not args.nccl_allreduce, hybrid_dense_layers=args.hybrid_dense_layers,
+              emulate_tp=args.emulate_tp)
     if res is not None:
         print(json.dumps(res), flush=True)
     if dist.is_initialized():

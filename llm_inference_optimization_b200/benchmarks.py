@@ -117,6 +117,47 @@ def bench_paged(t, dev, g, peak, pk):
             del buf, kv
 
 
+def bench_paged_stream(t, dev, g, peak, pk):
+    """One sequence over a paged FP8 cache the way a model runs it: launches back to back over eight layers' caches
+    (1.1 GB per cycle at 64K, so no launch finds its input in L2), CUDA events around 25 cycles.  The isolated-call
+    figures of `paged` carry the launch, ramp and last-combine tail of a single launch, which consecutive launches
+    overlap (programmatic dependent launch)."""
+    D, Hq, Hkv, P, L = 128, 32, 8, 16, 8
+    for N in (65536, 131072):
+        pages = N // P
+        caches = []
+        for _ in range(L):
+            buf = torch.randint(0, 256, (pages, Hkv, paged.RECORD_ROWS, 128), device=dev, generator=g, dtype=torch.uint8)
+            buf[:, :, :32] = torch.where((buf[:, :, :32] & 0x7F) == 0x7F, buf[:, :, :32] & 0xFE, buf[:, :, :32])
+            kv = paged.PagedKV.from_fused(buf, torch.float8_e4m3fn, None, None, 1)
+            kv.k_scale.fill_(0.008)
+            kv.v_scale.fill_(0.008)
+            caches.append(kv)
+        table = torch.randperm(pages, device=dev, generator=g).to(torch.int32).view(1, pages)
+        Q = randn16((1, Hq, D), dev, g)
+        out = torch.empty_like(Q)
+
+        def cycle():
+            for kv in caches:
+                _C.fused_gqa_paged(Q, kv.k_pool, kv.v_pool, kv.k_scale, kv.v_scale, table, None, D ** -0.5, out=out)
+
+        for _ in range(3):
+            cycle()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 25
+        e0.record()
+        for _ in range(reps):
+            cycle()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        us = e0.elapsed_time(e1) * 1e3 / (reps * L)
+        emit("dense_gqa_paged_fp8_back_to_back", {"B": 1, "Hq": Hq, "Hkv": Hkv, "D": D, "ctx": N, "page": P,
+                                                   "layout": "fused page records", "layers_per_cycle": L},
+             us, us, 2 * N * Hkv * (D + 4), peak, pk)
+        del caches
+
+
 def bench_ragged(t, dev, g, peak, pk):
     """The decode step's attention launch: batch 16, context lengths uniform in 8K..128K (the seed of bench_decode), FP8
     fused page records, with the kv-heads one rank owns at tensor-parallel degree 8 (one) and 1 (eight)."""
@@ -217,7 +258,7 @@ def bench_quest(t, dev, g, peak, pk):
          us, mn, nbytes, peak, pk)
 
 
-ALL = {"dense": bench_dense, "paged": bench_paged, "ragged": bench_ragged, "token": bench_token, "block": bench_block, "evict": bench_evict,
+ALL = {"dense": bench_dense, "paged": bench_paged, "paged_stream": bench_paged_stream, "ragged": bench_ragged, "token": bench_token, "block": bench_block, "evict": bench_evict,
        "quest": bench_quest}
 
 

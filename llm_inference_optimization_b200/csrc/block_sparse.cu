@@ -103,7 +103,7 @@ block_select_attend_kernel(const AttendParams p) {
     const float* sc = p.scores + (long long)row * p.nb;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kk = min(p.top_k, p.nb);
-    block_topk_sorted_auto<ATT_THREADS, 4>(sc, p.nb, kk, sel, tk);
+    block_topk_fast<ATT_THREADS, 4>(sc, p.nb, kk, sel, tk);
     __syncthreads();
     if (p.block_idx)
         for (int i = tid; i < p.top_k; i += ATT_THREADS) p.block_idx[(long long)row * p.top_k + i] = i < kk ? sel[i] : -1;

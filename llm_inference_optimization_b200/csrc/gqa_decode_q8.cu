@@ -135,9 +135,11 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     constexpr int NCH = D / 16;  // 16-byte chunks per row = MMA k-steps of S = Q K^T
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+    SKV_PHASE(0);
 
     // Ordered like any other kernel unless the caller declared the cache static (see the fp16 kernel).
     if (!p.early_kv) pdl_wait_prior_grids();
+    SKV_PHASE(1);
     const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
     // The host cuts the KV length for the LONGEST sequence the launch may hold (it cannot read seq_lens), which for a
     // ragged batch with few (sequence, kv-head) pairs means many short splits: each pays its pipeline fill, its merge
@@ -312,12 +314,14 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 
     int s = group;          // stage of tile `it`; p.stages >= Q8_GROUPS, so one wrap per step at most
     uint32_t ph = 0;
+    SKV_PHASE(2);
     for (int it = group; it < ntiles; it += Q8_GROUPS, s += Q8_GROUPS) {
         if (s >= p.stages) { s -= p.stages; ph ^= 1u; }
         if (!mbar_wait(full_bar + s * 8, ph)) {
             if (lane == 0) atomicOr(p.status, SKV_DEV_TIMEOUT);
             break;
         }
+        if (it == group) SKV_PHASE(3);
         const int tok0 = t_begin + it * TILE + wtok;
         if (tok0 < t_end) {
             const uint32_t kbase = ring + s * Q8_STAGE_BYTES + k_off + ld_row_off;   // this lane's K row
@@ -432,6 +436,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         if (lane == 0) mbar_arrive(empty_bar + s * 8);
     }
 
+    SKV_PHASE(4);
     // the running sums are per lane (its two token rows): total over the 8 lanes g
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
@@ -466,7 +471,9 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     ea.partial_o = p.partial_o; ea.partial_ml = p.partial_ml; ea.tickets = p.tickets; ea.out = p.out;
     ea.out_bf16 = p.out_bf16 != 0;
     ea.Hkv = p.Hkv; ea.G = G; ea.num_splits = p.num_splits; ea.o_stride_b = p.o_stride_b; ea.o_stride_h = p.o_stride_h;
+    SKV_PHASE(5);
     merge_and_combine<D, Q8_WARPS>(ea, smem, last_flag, b, h, split, n_splits, 1.f / P_BOOST);
+    SKV_PHASE(6);
 }
 
 template <int KVT, int NT, int NG>
@@ -492,6 +499,12 @@ using namespace skv;
 
 extern "C" {
 
+#ifdef SKV_PROFILE_PHASES
+int skv_debug_phase_ts_q8(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, skv_phase_ts, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : -4;
+}
+#endif
+
 int skv_gqa_set_q8_stages(int stages) {
     // even, so that a stage is always drained by the same consumer group
     if (stages < 4 || stages > 12 || stages % 2) return fail(SKV_ERR_BAD_ARG, "q8 stages must be even and in 4..12: %d", stages);
@@ -501,6 +514,14 @@ int skv_gqa_set_q8_stages(int stages) {
 
 // Ragged batches (seq_lens given, at most 64 sequences): the kernel lengthens its splits so that the batch's real
 // tokens make about waves x (CTAs resident on the GPU) CTAs.  0 switches the adjustment off.  Process-wide.
+// FP8 caches with up to 8 query heads per kv-head: 1 forces the one-group kernel variant that fits two CTAs on an SM,
+// 0 forces the two-group variant (one CTA per SM), -1 (default) lets the launcher choose by problem size.  Process-wide.
+int skv_gqa_set_q8_two_per_sm(int mode) {
+    if (mode < -1 || mode > 1) return fail(SKV_ERR_BAD_ARG, "mode must be -1, 0 or 1: %d", mode);
+    gqa::tuning().q8_two_per_sm = mode;
+    return SKV_OK;
+}
+
 int skv_gqa_set_ragged_waves(int waves) {
     if (waves < 0 || waves > 16) return fail(SKV_ERR_BAD_ARG, "ragged waves must be in 0..16: %d", waves);
     gqa::tuning().ragged_waves = waves;
@@ -534,7 +555,11 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     DeviceGuard guard(device);
     if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
 
-    const bool many = seq_lens != nullptr || (long long)B * Hkv * 2 > sm_count(device);
+    // FP8 with up to 8 heads per group runs the one-group variant, two CTAs per SM: measured equal or faster at every
+    // size tried (one sequence of 64K: equal; 4 x 64K: 0.76 -> 0.92 of the copy bandwidth; 16 x 64K: 0.89 -> 0.96)
+    const int two = gqa::tuning().q8_two_per_sm;   // -1: as above; 0 / 1: forced (experiments)
+    const bool many = two >= 0 ? two != 0 : true;
+    const bool one_wave = seq_lens == nullptr && (long long)B * Hkv * 2 <= sm_count(device);
     const int slots = (kv_dtype == SKV_KV_E4M3 && G <= 8 && many) ? 2 : 1;   // CTAs resident per SM
     gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device, seq_lens != nullptr, slots);
     if (!workspace || workspace_bytes < pl.total)
@@ -587,7 +612,10 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.N = N; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
     p.tiles_per_split = pl.tiles_per_split;
     p.num_splits = pl.splits;
-    p.stages = slots == 2 ? (gqa::tuning().q8_stages < 6 ? gqa::tuning().q8_stages : 6) : gqa::tuning().q8_stages;
+    // two CTAs per SM share the shared memory: at most 6 stages each, 4 when the launch is a single wave of CTAs
+    // (a shorter ring fills sooner, which is what a short-lived CTA notices)
+    const int cap2 = one_wave ? 4 : 6;
+    p.stages = slots == 2 ? (gqa::tuning().q8_stages < cap2 ? gqa::tuning().q8_stages : cap2) : gqa::tuning().q8_stages;
     p.out_bf16 = out_bf16;
     p.early_kv = gqa::tuning().early_kv;
     p.page_size = page_size;

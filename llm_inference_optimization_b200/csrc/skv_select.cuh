@@ -415,4 +415,29 @@ __device__ __forceinline__ void block_topk_sorted_auto(const float* sc, int T, i
     else block_topk_sorted<NT>(sc, T, k, out, sm);
 }
 
+// The quickest exact routine for the problem: arg-max extraction for k <= 32 over rows of up to 16 scores per
+// thread, the register-cached radix select for rows of up to R scores per thread, the streaming radix select
+// otherwise.  `sm` is TopkSmem<NT>::WORDS words (the small routine uses the first 2 * NT of them).  Output ascending.
+template <int NT, int R>
+__device__ __forceinline__ void block_topk_fast(const float* sc, int T, int k, int* out, uint32_t* sm) {
+    static_assert(TopkSmem<NT>::WORDS >= 2 * NT, "candidate scratch of the small routine");
+    unsigned long long* cand = reinterpret_cast<unsigned long long*>(sm);
+    if (k >= T) {   // everything is kept
+        for (int i = threadIdx.x; i < T; i += NT) out[i] = i;
+        __syncthreads();
+        return;
+    }
+    // The small routine's last round compares every candidate with every other ((NT/32 * k)^2 comparisons spread over
+    // the CTA): it wins while that is a few hundred candidates and loses badly beyond (top-32 with 32 warps is 1024
+    // candidates, a million comparisons: 25 us against 5 us for the radix passes).
+    // The first round costs k extraction steps per warp: measured a loss already at k = 32 (token-sparse top-32 at 64K:
+    // 134 us against 124 us with the radix passes), a gain at k = 8.
+    const bool small = k <= 8 && (NT / 32) * k <= 256;
+    if (small && T <= NT * 2) block_topk_small<NT, 2>(sc, T, k, out, cand);
+    else if (small && T <= NT * 4) block_topk_small<NT, 4>(sc, T, k, out, cand);
+    else if (small && T <= NT * 8) block_topk_small<NT, 8>(sc, T, k, out, cand);
+    else if (small && T <= NT * 16) block_topk_small<NT, 16>(sc, T, k, out, cand);
+    else block_topk_sorted_auto<NT, R>(sc, T, k, out, sm);
+}
+
 }  // namespace skv

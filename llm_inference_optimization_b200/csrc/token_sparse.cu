@@ -106,7 +106,7 @@ token_scores_kernel(const ScoreParams p, int tokens_per_cta) {
         int* csel = reinterpret_cast<int*>(tk + TopkSmem<SCORE_THREADS>::WORDS);
         const int n = t1 - t0, kc = min(p.cand_k, n);
         __syncthreads();
-        block_topk_sorted_auto<SCORE_THREADS, 16>(chunk_sc, n, kc, csel, tk);
+        block_topk_fast<SCORE_THREADS, 16>(chunk_sc, n, kc, csel, tk);
         __syncthreads();
         const long long row = ((long long)b * p.H + h) * p.S + s;
         const long long o = (row * gridDim.x + blockIdx.x) * p.cand_k;
@@ -155,12 +155,12 @@ token_select_attend_kernel(const AttendParams p) {
     if (p.cand_score) {
         // candidates are ordered by token position (chunk by chunk, ascending inside a chunk), so "equal scores:
         // lower candidate index first" is the same rule as "lower token position first"
-        block_topk_sorted_auto<ATT_THREADS, 4>(p.cand_score + (long long)row * p.nc, p.nc, kk, top, tk);
+        block_topk_fast<ATT_THREADS, 4>(p.cand_score + (long long)row * p.nc, p.nc, kk, top, tk);
         __syncthreads();
         for (int i = tid; i < kk; i += ATT_THREADS) top[i] = p.cand_pos[(long long)row * p.nc + SKV_INDEX(top[i], p.nc)];
         __syncthreads();
     } else {
-        block_topk_sorted_auto<ATT_THREADS, 8>(sc, p.T, kk, top, tk);
+        block_topk_fast<ATT_THREADS, 8>(sc, p.T, kk, top, tk);
     }
     if (p.topk_idx) {
         for (int i = tid; i < p.top_k; i += ATT_THREADS) p.topk_idx[(long long)row * p.top_k + i] = i < kk ? top[i] : -1;

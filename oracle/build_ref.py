@@ -28,7 +28,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT_DIR = HERE / "_ref"
 MODULE = "sparse_kv_ref_C"
-DEFAULT_REFERENCE = Path(os.environ.get("SKV_REFERENCE_DIR", "/root/reference"))
+# the reference checkout: SKV_REFERENCE_DIR, else a directory `reference` beside this repository
+DEFAULT_REFERENCE = Path(os.environ.get("SKV_REFERENCE_DIR") or HERE.parent.parent / "reference")
 
 SOURCES = [
     "csrc/pybind/bindings.cpp",
