@@ -100,10 +100,12 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool,
                          long long pool_stride_page, long long pool_stride_head, long long pool_stride_slot,
                          long long scale_stride_page, long long scale_stride_head,
                          float scale, int device, void* stream);
-/* Ragged batches (seq_lens given, at most 64 sequences): the host plans splits for the longest sequence the launch may
- * hold; with waves > 0 the kernel adds up the real lengths and lengthens the splits so that the real tokens make about
- * waves x (CTAs resident on the GPU) CTAs.  0 switches the adjustment off.  Process-wide.  No reference counterpart. */
-int skv_gqa_set_ragged_waves(int waves);
+/* Ragged batches (seq_lens given): the host cannot read the lengths, so its split plan is sized for the longest
+ * sequence the launch may hold.  on = 1 (default): when the batch has few (sequence, kv-head) pairs (at most 64
+ * sequences and a quarter of the resident CTA slots) every CTA derives a work list of (sequence, split) items from
+ * the real lengths -- one wave of CTAs of nearly equal length, none launched only to exit; on = 0: always the static
+ * plan.  Same results either way.  Process-wide.  No reference counterpart. */
+int skv_gqa_set_ragged_worklist(int on);
 /* FP8 caches, at most 8 query heads per kv-head: mode 1 forces the kernel variant that fits two CTAs on an SM, 0 the
  * variant with one CTA per SM, -1 (default) lets the launcher choose by problem size.  Process-wide.  No reference
  * counterpart. */

@@ -43,7 +43,7 @@ SIGNATURES = {
     "skv_kv_evict_quant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll,
                                 _i, _i, _i, _i, _i, _vp]),
     "skv_gqa_set_q8_stages": (_i, [_i]),
-    "skv_gqa_set_ragged_waves": (_i, [_i]),
+    "skv_gqa_set_ragged_worklist": (_i, [_i]),
     "skv_gqa_set_q8_two_per_sm": (_i, [_i]),
     "skv_gqa_set_early_kv": (_i, [_i]),
     "skv_gqa_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i,

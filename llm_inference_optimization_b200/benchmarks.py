@@ -175,7 +175,7 @@ def bench_ragged(t, dev, g, peak, pk):
         table[b, :n] = perm[o:o + n].to(torch.int32)
         o += n
     table, dl = table.to(dev), lens.to(dev)
-    for Hkv in (1, 8):
+    for Hkv in (1, 2, 4, 8):
         Hq = 4 * Hkv
         buf = torch.randint(0, 256, (total, Hkv, paged.RECORD_ROWS, 128), device=dev, generator=g, dtype=torch.uint8)
         buf[:, :, :32] = torch.where((buf[:, :, :32] & 0x7F) == 0x7F, buf[:, :, :32] & 0xFE, buf[:, :, :32])
@@ -185,19 +185,18 @@ def bench_ragged(t, dev, g, peak, pk):
         Q = randn16((B, Hq, D), dev, g)
         out = torch.empty_like(Q)
         nbytes = int(lens.sum()) * Hkv * 2 * (D + 4)
-        for waves in (0, 1, 2, 3, 4, 6):
-            lib.skv_gqa_set_ragged_waves(waves)
+        for worklist in (1, 2, 3, 0):
+            lib.skv_gqa_set_ragged_worklist(worklist)
             try:
                 us, mn = t(lambda: _C.fused_gqa_paged(Q, kv.k_pool, kv.v_pool, kv.k_scale, kv.v_scale, table, dl, D ** -0.5,
                                                       max_seq_len=cap * 16, out=out))
             finally:
-                lib.skv_gqa_set_ragged_waves(RAGGED_WAVES_DEFAULT)
+                lib.skv_gqa_set_ragged_worklist(1)
             emit("dense_gqa_paged_fp8_ragged", {"B": B, "Hq": Hq, "Hkv": Hkv, "D": D, "ctx": "8K..128K (sum %d)" % int(lens.sum()),
-                                                 "ragged_waves": waves}, us, mn, nbytes, peak, pk)
+                                                 "schedule": f"work list from the real lengths, {worklist} wave(s)" if worklist else "static split plan"},
+                 us, mn, nbytes, peak, pk)
         del buf, kv
 
-
-RAGGED_WAVES_DEFAULT = 0
 
 
 def bench_token(t, dev, g, peak, pk):

@@ -79,7 +79,8 @@ struct Q8Params {
     int tiles_per_split, num_splits, stages;
     int page_size, max_pages;
     int num_pages;           // pages in the pools: ids read from the table are checked against it
-    int adapt_slots;         // > 0: CTA slots the real work of a ragged batch is spread over (see the kernel); 0: static splits
+    int list_items;          // > 0: grid.y indexes a work list of (sequence, split) items built from seq_lens (see the kernel); 0: grid (Hkv, splits, B)
+    int B;                   // sequences (the work-list mode has no batch dimension in its grid)
     int mode;                // Q8_SEPARATE16, Q8_SEPARATE64 or Q8_FUSED
     int out_bf16;            // output elements are bf16 instead of fp16
     int early_kv;            // pages, page table and seq_lens are not produced by the previous kernel
@@ -134,28 +135,46 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     constexpr int Q8_CONSUMER_THREADS = Q8_WARPS * 32;
     constexpr int NCH = D / 16;  // 16-byte chunks per row = MMA k-steps of S = Q K^T
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+    const int h = blockIdx.x;
+    int split = blockIdx.y, b = blockIdx.z;
     SKV_PHASE(0);
 
     // Ordered like any other kernel unless the caller declared the cache static (see the fp16 kernel).
     if (!p.early_kv) pdl_wait_prior_grids();
     SKV_PHASE(1);
-    const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
-    // The host cuts the KV length for the LONGEST sequence the launch may hold (it cannot read seq_lens), which for a
-    // ragged batch with few (sequence, kv-head) pairs means many short splits: each pays its pipeline fill, its merge
-    // and a partial, and the last CTA of a long sequence combines all of them alone at the very end.  With
-    // adapt_slots set, every CTA adds up the batch's real length and lengthens the splits so that the real work
-    // makes about adapt_slots CTAs in all; splits beyond a sequence's (now smaller) count exit at once.
-    int tiles_per_split = p.tiles_per_split;
-    if (p.adapt_slots > 0) {
+    int len, tiles_per_split = p.tiles_per_split, n_splits;
+    if (p.list_items > 0) {
+        // Work-list mode, for a ragged batch with few (sequence, kv-head) pairs.  The host cannot read seq_lens, so
+        // its plan cuts the LONGEST possible sequence into many short splits and launches that many CTAs for every
+        // sequence: short splits each pay a pipeline fill, a merge and a partial, and the CTAs past a sequence's
+        // end are launched only to exit (measured at 16 sequences x 1 kv-head: 0.62 of the copy bandwidth against
+        // 0.83 for the same bytes with lengths the host knows).  Here every CTA adds up the real lengths, sizes
+        // the splits so that all (sequence, split) items of a kv-head fit the list_items CTAs launched for it --
+        // one wave of CTAs of nearly equal length -- and finds its own item by a prefix walk over the sequences.
         long long tiles = 0;
-        for (int i = 0; i < (int)gridDim.z; ++i) tiles += (min(max(p.seq_lens[i], 0), p.N) + TILE - 1) / TILE;
-        const long long want = (tiles * p.Hkv + p.adapt_slots - 1) / p.adapt_slots;
-        if (want > tiles_per_split) tiles_per_split = (int)want;
+        for (int i = 0; i < p.B; ++i) tiles += (min(max(p.seq_lens[i], 0), p.N) + TILE - 1) / TILE;
+        const long long room = max(1, p.list_items - p.B);           // every sequence may add one partial split
+        tiles_per_split = max(tiles_per_split, (int)((tiles + room - 1) / room));
+        const int item = blockIdx.y;
+        int acc = 0;
+        b = -1;
+        len = 0;
+        n_splits = 1;
+        for (int i = 0; i < p.B; ++i) {
+            const int li = min(max(p.seq_lens[i], 0), p.N);
+            const int ti = (li + TILE - 1) / TILE;
+            const int ns = ti > 0 ? (ti + tiles_per_split - 1) / tiles_per_split : 1;
+            if (b < 0 && item < acc + ns) { b = i; split = item - acc; len = li; n_splits = ns; }
+            acc += ns;
+        }
+        if (b < 0) return;   // past the end of the work list
+    } else {
+        len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
+        const int tps_tokens = tiles_per_split * TILE;
+        n_splits = len > 0 ? (len + tps_tokens - 1) / tps_tokens : 1;
+        if (split >= n_splits) return;
     }
     const int tokens_per_split = tiles_per_split * TILE;
-    const int n_splits = len > 0 ? (len + tokens_per_split - 1) / tokens_per_split : 1;
-    if (split >= n_splits) return;
     const int t_begin = split * tokens_per_split;
     const int t_end = min(len, t_begin + tokens_per_split);
     const int ntiles = (t_end - t_begin + TILE - 1) / TILE;
@@ -486,7 +505,7 @@ static int launch_q8(const CUtensorMap& tmK, const CUtensorMap& tmV, const Q8Par
         SKV_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_q8_kernel<KVT, NT, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured_smem[dev] = (int)smem;
     }
-    dim3 grid(p.Hkv, p.num_splits, B);
+    const dim3 grid = p.list_items > 0 ? dim3(p.Hkv, p.list_items, 1) : dim3(p.Hkv, p.num_splits, B);
     SKV_CUDA_TRY(launch_pdl(gqa_decode_q8_kernel<KVT, NT, NG>, grid, dim3(q8_threads(NG)), smem, stream, tmK, tmV, p));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
@@ -512,8 +531,6 @@ int skv_gqa_set_q8_stages(int stages) {
     return SKV_OK;
 }
 
-// Ragged batches (seq_lens given, at most 64 sequences): the kernel lengthens its splits so that the batch's real
-// tokens make about waves x (CTAs resident on the GPU) CTAs.  0 switches the adjustment off.  Process-wide.
 // FP8 caches with up to 8 query heads per kv-head: 1 forces the one-group kernel variant that fits two CTAs on an SM,
 // 0 forces the two-group variant (one CTA per SM), -1 (default) lets the launcher choose by problem size.  Process-wide.
 int skv_gqa_set_q8_two_per_sm(int mode) {
@@ -522,9 +539,12 @@ int skv_gqa_set_q8_two_per_sm(int mode) {
     return SKV_OK;
 }
 
-int skv_gqa_set_ragged_waves(int waves) {
-    if (waves < 0 || waves > 16) return fail(SKV_ERR_BAD_ARG, "ragged waves must be in 0..16: %d", waves);
-    gqa::tuning().ragged_waves = waves;
+// 1 (default): a ragged batch (seq_lens given) with few (sequence, kv-head) pairs is scheduled from a work list that
+// every CTA derives from the real lengths (one wave of CTAs of nearly equal length); 0: always the host's static
+// split plan.  Same results either way.  Process-wide.
+int skv_gqa_set_ragged_worklist(int on) {
+    if (on < 0 || on > 4) return fail(SKV_ERR_BAD_ARG, "work-list waves must be in 0..4: %d", on);
+    gqa::tuning().ragged_worklist = on;   // values above 1: that many waves of proportionally shorter CTAs (experiments)
     return SKV_OK;
 }
 
@@ -621,8 +641,14 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.page_size = page_size;
     p.max_pages = max_pages;
     p.num_pages = num_pages;
-    p.adapt_slots = (seq_lens != nullptr && B <= 64 && gqa::tuning().ragged_waves > 0)
-                        ? sm_count(device) * slots * gqa::tuning().ragged_waves : 0;
+    // work-list mode: ragged lengths, few pairs (a quarter of the resident CTA slots at most), a short batch to walk
+    const int slots_total = sm_count(device) * slots;
+    // (measured at 16 ragged sequences: 1 kv-head 0.60 -> 0.77 of the copy bandwidth, 2 kv-heads 0.75 -> 0.86, 4 kv-heads
+    // 0.88 -> 0.84: the static plan is kept from a quarter of the slots up)
+    const int waves = gqa::tuning().ragged_worklist;
+    const bool worklist = seq_lens != nullptr && waves > 0 && B <= 64 && (long long)B * Hkv * 8 <= slots_total;
+    p.list_items = worklist ? slots_total * waves / Hkv : 0;
+    p.B = B;
     p.mode = mode;
     p.sc_sp = scale_stride_page; p.sc_sh = scale_stride_head;
     p.q_stride_b = (long long)Hq * D; p.q_stride_h = D;

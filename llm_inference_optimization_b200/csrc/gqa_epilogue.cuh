@@ -34,7 +34,7 @@ struct Tuning {
     int q8_stages = 8;     // 8-bit ring depth (stages of 17 KB)
     int early_kv = 0;      // 1: K/V, page table and lengths may be read before the previous kernel has completed
     int q8_two_per_sm = -1;  // FP8 kernel variant: -1 chosen by the launcher, 0 one CTA per SM, 1 two CTAs per SM
-    int ragged_waves = 0;  // > 0: the 8-bit kernel sizes the splits of a ragged batch on the device for this many waves of CTAs
+    int ragged_worklist = 1;  // the 8-bit kernel schedules a ragged batch with few pairs from a device-side work list
 };
 inline Tuning& tuning() {
     static Tuning t;

@@ -91,3 +91,27 @@ def test_compacted_cache_without_page_table(cuda_device):
     want = oracle.dense_gqa_decode(Q, oracle.dequantize(kc, ks).permute(0, 2, 1, 3),
                                    oracle.dequantize(vc, vs).permute(0, 2, 1, 3), 128 ** -0.5)
     assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,T,lens", [(5, 4, 1, 8192, [8192, 17, 5000, 64, 1000]), (3, 8, 2, 4096, [4096, 4096, 4096]),
+                                             (4, 4, 1, 2048, [1, 2048, 0, 700]), (16, 4, 1, 1024, None)])
+def test_ragged_batch_work_list_schedule(cuda_device, lib, B, Hq, Hkv, T, lens):
+    """A ragged batch with few (sequence, kv-head) pairs is scheduled from a work list that every CTA derives from
+    seq_lens (one wave of nearly equal CTAs) instead of the host's plan for the longest sequence: same output as that
+    plan and as the oracle, with an empty sequence, a one-token sequence and equal lengths among the cases."""
+    Q, pools, (Kd, Vd) = make_case(B, Hq, Hkv, T, "fp8", seed=B * T)
+    kp, vp, ksp, vsp, table = (t.to(cuda_device) for t in pools)
+    sl = torch.tensor(lens if lens is not None else [T - 37 * i for i in range(B)], dtype=torch.int32)
+    scale = 128 ** -0.5
+    outs = {}
+    try:
+        for mode in (1, 0):
+            assert lib.skv_gqa_set_ragged_worklist(mode) == 0
+            outs[mode] = _C.fused_gqa_paged(Q.to(cuda_device), kp, vp, ksp, vsp, table, sl.to(cuda_device), scale)
+            torch.cuda.synchronize()
+            assert _workspace.status(_workspace.get("gqa", 0, cuda_device)) == 0
+    finally:
+        lib.skv_gqa_set_ragged_worklist(1)
+    want = oracle.dense_gqa_decode(Q, Kd, Vd, scale, sl)
+    for mode in (1, 0):
+        assert (outs[mode].float().cpu() - want).abs().max().item() <= TOL, mode
