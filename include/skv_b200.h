@@ -273,6 +273,19 @@ int skv_residual_rmsnorm(const void* delta, void* resid, const void* weight, voi
                          int is_bf16, int device, void* stream);
 int skv_silu_mul(const void* gate_up, void* out, int rows, int inter, int is_bf16, int device, void* stream);
 
+/* ---- decode-step projections: skinny GEMM ------------------------------------------------------------
+ * The reference runs the q/k/v, o, gate/up and down projections as Hugging Face nn.Linear modules (the model it
+ * patches, benchmarks/llama_integration_benchmark.py:266-279).  out[M,N] = x[M,K] . w[K,N], all row-major and
+ * contiguous, fp16 (is_bf16 = 0) or bf16 elements, fp32 accumulation; 1 <= M <= 16, K % 32 == 0, N % 64 == 0
+ * (other shapes: SKV_ERR_UNSUPPORTED, and skv_skinny_gemm_workspace_bytes returns 0).  The workspace is zero-filled
+ * once before its first use; its status word (offset 0) is read with skv_workspace_status.  The result does not
+ * depend on the order in which CTAs finish.  skv_skinny_gemm_set_min_blocks (tuning, process-wide): the fewest
+ * 16 KB blocks of w a CTA streams on small problems (default 16); it changes the workspace size of a shape. */
+int skv_skinny_gemm_set_min_blocks(int blocks);
+size_t skv_skinny_gemm_workspace_bytes(int M, int K, int N, int device);
+int skv_skinny_gemm(const void* x, const void* w, void* out, void* workspace, size_t workspace_bytes,
+                    int M, int K, int N, int is_bf16, int device, void* stream);
+
 /* ---- tensor-parallel decode step: all-reduce + residual add + RMSNorm in one kernel over peer memory ----
  * No reference counterpart (the reference is single-GPU).  Every rank passes the same arrays, indexed by rank:
  * peer_partials[r] = device address, valid on THIS GPU, of rank r's [rows, hidden] partial sum (peer-mapped /

@@ -43,6 +43,7 @@ struct Params {
     const int* seq_lens; // [B] or null
     int N, Hq, Hkv, G;
     int tiles_per_split, num_splits, stages;
+    int list_items, B;   // list_items > 0: grid (Hkv, list_items), work-list schedule of a ragged batch (worklist_item)
     long long q_stride_b, q_stride_h, o_stride_b, o_stride_h;
     float scale_log2;    // softmax scale * log2(e)
     int early_kv;        // K/V and seq_lens are not produced by the previous kernel: stream them before it completes
@@ -84,17 +85,26 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     constexpr int NT_O = D / 8;     // 8-channel output tiles
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+    const int h = blockIdx.x;
+    int split = blockIdx.y, b = blockIdx.z;
 
     // Launched with programmatic stream serialisation, this kernel may start before the previous one in the stream
     // has completed.  By default every thread waits for it here, so the kernel is ordered like any other; only when
     // the caller has declared that K, V and seq_lens are not produced by the previous kernel (early_kv) does the
     // wait move down to the consumers, and the producer streams K/V meanwhile.
     if (!p.early_kv) pdl_wait_prior_grids();
-    const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
-    const int tokens_per_split = p.tiles_per_split * TILE;
-    const int n_splits = len > 0 ? (len + tokens_per_split - 1) / tokens_per_split : 1;
-    if (split >= n_splits) return;
+    int len, n_splits, tiles_per_split = p.tiles_per_split;
+    if (p.list_items > 0) {   // work-list schedule of a ragged batch (see worklist_item)
+        const SplitItem it = worklist_item(p.seq_lens, p.B, p.N, p.list_items, blockIdx.y, p.tiles_per_split);
+        if (it.b < 0) return;
+        b = it.b; split = it.split; len = it.len; n_splits = it.n_splits; tiles_per_split = it.tiles_per_split;
+    } else {
+        len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
+        const int tps_tokens = tiles_per_split * TILE;
+        n_splits = len > 0 ? (len + tps_tokens - 1) / tps_tokens : 1;
+        if (split >= n_splits) return;
+    }
+    const int tokens_per_split = tiles_per_split * TILE;
     const int t_begin = split * tokens_per_split;
     const int t_end = min(len, t_begin + tokens_per_split);
     const int ntiles = (t_end - t_begin + TILE - 1) / TILE;  // 0 for an empty sequence
@@ -379,7 +389,7 @@ static int launch_f16(const CUtensorMap& tmK, const CUtensorMap& tmV, const Para
         SKV_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_f16_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured_smem[dev] = (int)smem;
     }
-    dim3 grid(p.Hkv, p.num_splits, B);
+    const dim3 grid = p.list_items > 0 ? dim3(p.Hkv, p.list_items, 1) : dim3(p.Hkv, p.num_splits, B);
     SKV_CUDA_TRY(launch_pdl(gqa_decode_f16_kernel<D>, grid, dim3(THREADS), smem, stream, tmK, tmV, p));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
@@ -479,6 +489,13 @@ static int decode_f16_impl(const void* q, const void* k, const void* v, void* ou
     p.num_splits = pl.splits;
     p.stages = gqa::tuning().stages;
     p.early_kv = gqa::tuning().early_kv;
+    {   // ragged lengths, few pairs: one wave of CTAs from a device-side work list (the condition of the 8-bit kernel)
+        const int slots_total = sm_count(device) * gqa::tuning().ctas_per_sm;
+        const int waves = gqa::tuning().ragged_worklist;
+        const bool worklist = seq_lens != nullptr && waves > 0 && B <= 64 && (long long)B * Hkv * 8 <= slots_total;
+        p.list_items = worklist ? slots_total * waves / Hkv : 0;
+        p.B = B;
+    }
     p.q_stride_b = (long long)Hq * D; p.q_stride_h = D;
     p.o_stride_b = (long long)Hq * D; p.o_stride_h = D;
     p.scale_log2 = scale * 1.4426950408889634f;

@@ -143,31 +143,10 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     if (!p.early_kv) pdl_wait_prior_grids();
     SKV_PHASE(1);
     int len, tiles_per_split = p.tiles_per_split, n_splits;
-    if (p.list_items > 0) {
-        // Work-list mode, for a ragged batch with few (sequence, kv-head) pairs.  The host cannot read seq_lens, so
-        // its plan cuts the LONGEST possible sequence into many short splits and launches that many CTAs for every
-        // sequence: short splits each pay a pipeline fill, a merge and a partial, and the CTAs past a sequence's
-        // end are launched only to exit (measured at 16 sequences x 1 kv-head: 0.62 of the copy bandwidth against
-        // 0.83 for the same bytes with lengths the host knows).  Here every CTA adds up the real lengths, sizes
-        // the splits so that all (sequence, split) items of a kv-head fit the list_items CTAs launched for it --
-        // one wave of CTAs of nearly equal length -- and finds its own item by a prefix walk over the sequences.
-        long long tiles = 0;
-        for (int i = 0; i < p.B; ++i) tiles += (min(max(p.seq_lens[i], 0), p.N) + TILE - 1) / TILE;
-        const long long room = max(1, p.list_items - p.B);           // every sequence may add one partial split
-        tiles_per_split = max(tiles_per_split, (int)((tiles + room - 1) / room));
-        const int item = blockIdx.y;
-        int acc = 0;
-        b = -1;
-        len = 0;
-        n_splits = 1;
-        for (int i = 0; i < p.B; ++i) {
-            const int li = min(max(p.seq_lens[i], 0), p.N);
-            const int ti = (li + TILE - 1) / TILE;
-            const int ns = ti > 0 ? (ti + tiles_per_split - 1) / tiles_per_split : 1;
-            if (b < 0 && item < acc + ns) { b = i; split = item - acc; len = li; n_splits = ns; }
-            acc += ns;
-        }
-        if (b < 0) return;   // past the end of the work list
+    if (p.list_items > 0) {   // work-list schedule of a ragged batch (see worklist_item)
+        const SplitItem it = worklist_item(p.seq_lens, p.B, p.N, p.list_items, blockIdx.y, p.tiles_per_split);
+        if (it.b < 0) return;
+        b = it.b; split = it.split; len = it.len; n_splits = it.n_splits; tiles_per_split = it.tiles_per_split;
     } else {
         len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
         const int tps_tokens = tiles_per_split * TILE;

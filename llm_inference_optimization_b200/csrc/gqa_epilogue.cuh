@@ -51,6 +51,8 @@ inline Tuning& tuning() {
 #define SKV_RAGGED_WAVES 8
 #endif
 
+constexpr size_t WORKSPACE_HEAD_BYTES = 65536;   // status word + tickets, at the same place for every problem size
+
 struct Plan {
     int splits, tiles_per_split;
     size_t off_status, off_tickets, off_ml, off_o, total;
@@ -96,10 +98,16 @@ inline Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device, bool rag
     pl.splits = (int)splits;
     pl.tiles_per_split = (int)tps;
     auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
-    size_t off = 256;  // the device status word sits at offset 0 of every workspace
+    // The device status word sits at offset 0 of every workspace and the tickets (which must be zero when a launch
+    // starts, and are left zero by it) behind it, in a head region whose size does not depend on the problem: a
+    // later call with more (batch, kv-head) pairs must not find an earlier call's partial sums where its tickets
+    // live.  Beyond 16320 pairs the region grows with the problem and such a workspace must be cleared before it
+    // is reused with more pairs.
+    size_t off = 256;
     pl.off_status = 0;
     pl.off_tickets = off;
     off += up((size_t)B * Hkv * sizeof(int));
+    if (off < WORKSPACE_HEAD_BYTES) off = WORKSPACE_HEAD_BYTES;
     pl.off_ml = off;
     off += up((size_t)B * Hkv * splits * G * 2 * sizeof(float));
     pl.off_o = off;
@@ -109,6 +117,40 @@ inline Plan make_plan(int B, int N, int Hq, int Hkv, int D, int device, bool rag
 }
 
 #if defined(__CUDACC__)
+
+// Work-list schedule of a ragged batch with few (sequence, kv-head) pairs.  The host cannot read seq_lens, so its
+// plan cuts the LONGEST possible sequence into many short splits and launches that many CTAs for every sequence:
+// short splits each pay a pipeline fill, a merge and a partial, and the CTAs past a sequence's end are launched only
+// to exit (measured at 16 sequences x 1 kv-head: 0.60 of the copy bandwidth against 0.83 for the same bytes with
+// lengths the host knows).  In this mode the grid is (Hkv, list_items): every CTA adds up the real lengths, sizes
+// the splits so that all (sequence, split) items of a kv-head fit the list_items CTAs launched for it -- one wave of
+// CTAs of nearly equal length -- and finds its own item by a prefix walk over the sequences (B <= 64).
+struct SplitItem {
+    int b, split, len, n_splits, tiles_per_split;   // b < 0: past the end of the work list
+};
+
+__device__ __forceinline__ SplitItem worklist_item(const int* seq_lens, int B, int N, int list_items, int item,
+                                                   int host_tiles_per_split) {
+    long long tiles = 0;
+    for (int i = 0; i < B; ++i) tiles += (min(max(seq_lens[i], 0), N) + TILE - 1) / TILE;
+    const long long room = max(1, list_items - B);   // every sequence may add one partial split
+    SplitItem it;
+    // never shorter than the host's splits: the partial arrays are sized for the host's split count
+    it.tiles_per_split = max(host_tiles_per_split, (int)((tiles + room - 1) / room));
+    it.b = -1;
+    it.split = 0;
+    it.len = 0;
+    it.n_splits = 1;
+    int acc = 0;
+    for (int i = 0; i < B; ++i) {
+        const int li = min(max(seq_lens[i], 0), N);
+        const int ti = (li + TILE - 1) / TILE;
+        const int ns = ti > 0 ? (ti + it.tiles_per_split - 1) / it.tiles_per_split : 1;   // an empty sequence still writes zeros
+        if (it.b < 0 && item < acc + ns) { it.b = i; it.split = item - acc; it.len = li; it.n_splits = ns; }
+        acc += ns;
+    }
+    return it;
+}
 
 struct EpilogueArgs {
     float* partial_o;    // [B, Hkv, S, G, D]

@@ -138,6 +138,35 @@ inline int make_kv_tmap(CUtensorMap* out, KvMapPos* pos, const void* base, int e
     return SKV_OK;
 }
 
+// Map over a row-major 16-bit matrix [rows, cols] with `ld` elements between rows: box = box_rows x box_cols, with
+// box_cols 64 (128-byte rows, 128-byte swizzle) or 32 (64-byte rows, 64-byte swizzle).  Coordinates: (column, row).
+// Rows past `rows` and columns past `cols` read as zero.
+inline int make_matrix_tmap(CUtensorMap* out, const void* base, long long rows, long long cols, long long ld,
+                            int box_rows, int box_cols, bool bf16) {
+    static thread_local TmapCache<int> cache;
+    const long long key[12] = {(long long)reinterpret_cast<uintptr_t>(base), rows, cols, ld, box_rows, bf16 ? 1 : 0, box_cols, 0, 0, 0, 0, 2};
+    if (const auto* hit = cache.find(key)) {
+        *out = hit->map;
+        return SKV_OK;
+    }
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(SKV_ERR_DRIVER, "cuTensorMapEncodeTiled entry point not available");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0)
+        return fail(SKV_ERR_BAD_ARG, "matrix base and row pitch must be 16-byte aligned for TMA");
+    cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t gstr[1] = {(cuuint64_t)ld * 2};
+    if (box_cols != 64 && box_cols != 32) return fail(SKV_ERR_BAD_ARG, "matrix box must be 32 or 64 elements wide");
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                     const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SKV_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    cache.put(key, *out, 0);
+    return SKV_OK;
+}
+
 // Where each logical coordinate of a paged 8-bit pool sits among tensor-map dimensions 1..3.
 struct PoolMapPos {
     int slot, head, page;

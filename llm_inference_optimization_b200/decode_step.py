@@ -112,7 +112,7 @@ class DecodeModel:
 
     def __init__(self, cfg: ModelConfig, shard: HeadShard, device, *, seed: int = 4, dtype=torch.bfloat16,
                  attention: AttentionFn = kernel_attention, group=None, layer_modes: list[str] | None = None,
-                 quest_block: int = 64, quest_top_k: int = 8):
+                 quest_block: int = 64, quest_top_k: int = 8, skinny_gemm: bool = False):
         """``layer_modes``: per layer ``"dense"`` (attention over the whole cache) or ``"quest"`` (block-sparse: the
         ``quest_top_k`` blocks of ``quest_block`` tokens with the highest min/max upper-bound score per query head).
         The reference's layer sweep found sparse attention harmless in the first half of the layers only
@@ -121,6 +121,10 @@ class DecodeModel:
         self.cfg, self.shard, self.device, self.dtype = cfg, shard, torch.device(device), dtype
         self.attention, self.group = attention, group
         self.quest_block, self.quest_top_k = int(quest_block), int(quest_top_k)
+        # True: the four projections of a layer run on this library's weight-streaming kernel (batches of up to 16
+        # rows) instead of library GEMMs.  Off by default: measured on B200 the library GEMMs are faster at every
+        # Llama-3-8B projection shape (graph replay, 16 rows: 79 us against 116 us per layer on one GPU).
+        self.skinny_gemm = bool(skinny_gemm)
         self.metas: list[Tensor | None] = []
         self.set_layer_modes(layer_modes)
         # the fused RoPE + quantise + append kernel needs fp16/bf16 activations on a CUDA device
@@ -249,15 +253,22 @@ class DecodeModel:
         D, B = cfg.D, x.shape[0]
         h = glue.residual_rmsnorm(x, None, self.layers[0]["n1"], cfg.rms_eps)
         for li, (w, cache) in enumerate(zip(self.layers, self.caches)):
-            qkv = h @ w["wqkv"]
+            qkv = self._mm(h, w["wqkv"])
             a = self._fused_attention(li, qkv, cache, pos, new_lens, scale, x.dtype)
-            torch.matmul(a.view(B, sh.n_q * D), w["wo"], out=arn.partial(0))
+            self._mm(a.view(B, sh.n_q * D), w["wo"], out=arn.partial(0))
             h = arn.reduce_norm(0, x, w["n2"], cfg.rms_eps)
-            torch.matmul(glue.silu_mul(h @ w["wgu"]), w["wd"], out=arn.partial(1))
+            self._mm(glue.silu_mul(self._mm(h, w["wgu"])), w["wd"], out=arn.partial(1))
             nxt = self.layers[li + 1]["n1"] if li + 1 < len(self.layers) else self.final_norm
             h = arn.reduce_norm(1, x, nxt, cfg.rms_eps)
         self.seq_lens.add_(1)
         return h @ self.lm_head
+
+    def _mm(self, x: Tensor, w: Tensor, out: Tensor | None = None) -> Tensor:
+        """``x @ w`` of the fused-glue path: the weight-streaming kernel where it applies, else the library GEMM."""
+        from . import glue
+        if self.skinny_gemm and glue.skinny_gemm_supported(x.shape[0], w.shape[0], w.shape[1]) and x.is_contiguous():
+            return glue.skinny_gemm(x, w, out=out)
+        return torch.matmul(x, w, out=out) if out is not None else x @ w
 
     def _fused_attention(self, li: int, qkv: Tensor, cache: "LayerCache", pos: Tensor, new_lens: Tensor, scale: float,
                          dtype) -> Tensor:
@@ -302,11 +313,11 @@ class DecodeModel:
             delta = None
             for li, (w, cache) in enumerate(zip(self.layers, self.caches)):
                 h = glue.residual_rmsnorm(x, delta, w["n1"], cfg.rms_eps)
-                qkv = h @ w["wqkv"]
+                qkv = self._mm(h, w["wqkv"])
                 a = self._fused_attention(li, qkv, cache, pos, new_lens, scale, x.dtype)
-                o = self._all_reduce(a.view(B, sh.n_q * D) @ w["wo"])
+                o = self._all_reduce(self._mm(a.view(B, sh.n_q * D), w["wo"]))
                 h = glue.residual_rmsnorm(x, o, w["n2"], cfg.rms_eps)
-                delta = self._all_reduce(glue.silu_mul(h @ w["wgu"]) @ w["wd"])
+                delta = self._all_reduce(self._mm(glue.silu_mul(self._mm(h, w["wgu"])), w["wd"]))
             self.seq_lens.add_(1)
             return glue.residual_rmsnorm(x, delta, self.final_norm, cfg.rms_eps) @ self.lm_head
         for li, (w, cache) in enumerate(zip(self.layers, self.caches)):

@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 from torch import Tensor
 
-from . import _C, _lib
+from . import _C, _lib, _workspace
 
 
 def _check_2d(t: Tensor, what: str) -> None:
@@ -51,6 +51,38 @@ def silu_mul(gate_up: Tensor, out: Tensor | None = None) -> Tensor:
     rc = _lib.load().skv_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, inter, int(gate_up.dtype == torch.bfloat16),
                                   _C._dev_index(gate_up), torch.cuda.current_stream(gate_up.device).cuda_stream)
     _lib.check(rc, "silu_mul")
+    return out
+
+
+def skinny_gemm_supported(rows: int, K: int, N: int) -> bool:
+    """Shapes the weight-streaming GEMM serves: at most 16 rows, K a multiple of 32, N a multiple of 64."""
+    return 0 < rows <= 16 and K % 32 == 0 and N % 64 == 0
+
+
+def skinny_gemm(x: Tensor, w: Tensor, out: Tensor | None = None) -> Tensor:
+    """``x [rows <= 16, K] @ w [K, N]`` (fp16 or bf16, fp32 accumulation) by the weight-streaming kernel.
+
+    The decode step's projections: with a batch of 16 rows they are pure weight streaming, which this kernel does
+    with every CTA reading an equal share of ``w`` (``skv_skinny_gemm``).  ``out`` may be any contiguous ``[rows, N]``
+    tensor of the same dtype, for example the symmetric-memory buffer a fused all-reduce reads.
+    """
+    _check_2d(x, "x")
+    _check_2d(w, "w")
+    rows, K = x.shape
+    N = w.shape[1]
+    _C._require(w.shape[0] == K and w.dtype == x.dtype and w.device == x.device, "w must be [K, N] of x's dtype on x's device")
+    _C._require(skinny_gemm_supported(rows, K, N), "skinny_gemm serves rows <= 16, K % 32 == 0, N % 64 == 0")
+    if out is None:
+        out = torch.empty((rows, N), dtype=x.dtype, device=x.device)
+    else:
+        _C._require(out.shape == (rows, N) and out.dtype == x.dtype and out.is_contiguous() and out.device == x.device,
+                    "out must be a contiguous [rows, N] tensor of x's dtype on x's device")
+    lib = _lib.load()
+    dev = _C._dev_index(x)
+    ws = _workspace.get("skinny_gemm", lib.skv_skinny_gemm_workspace_bytes(rows, K, N, dev), x.device)
+    rc = lib.skv_skinny_gemm(x.data_ptr(), w.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), rows, K, N,
+                             int(x.dtype == torch.bfloat16), dev, torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc, "skinny_gemm")
     return out
 
 

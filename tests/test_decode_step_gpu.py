@@ -71,6 +71,19 @@ def test_bf16_fused_glue_path_matches_oracle_model(cuda_device):
     assert cos > 0.999
 
 
+def test_weight_streaming_gemm_option_matches_oracle_model(cuda_device):
+    """skinny_gemm=True routes the four projections of every layer through this library's GEMM kernel."""
+    m = ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, 1, 0), cuda_device, dtype=torch.bfloat16, skinny_gemm=True)
+    m.init_cache(LENS)
+    weights, k_hist, v_hist = oracle_inputs(m)
+    want = dso.decode_step(weights, CFG, TOK, k_hist, v_hist, LENS.clone())
+    got = m.step(TOK.to(cuda_device)).float().cpu()
+    from llm_inference_optimization_b200 import _workspace
+    assert _workspace.all_of("skinny_gemm", cuda_device), "the weight-streaming kernel did not run"
+    assert (got - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item())
+    assert torch.nn.functional.cosine_similarity(got, want, dim=-1).min().item() > 0.999
+
+
 def test_hybrid_layer_schedule_matches_oracle_model(cuda_device):
     """Dense attention in layer 0, Quest block-sparse attention (4 blocks of 64 tokens) in layer 1, against the oracle
     model with the same schedule."""

@@ -127,3 +127,24 @@ def test_back_to_back_launches_both_launch_orders(cuda_device, early):
     assert _workspace.status(_workspace.get("gqa", 0, cuda_device)) == 0
     for (Q, K, V, s), o in zip(cases, outs):
         assert (o.float().cpu() - oracle.dense_gqa_decode(Q, K, V, s)).abs().max().item() <= 2e-3
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,N,lens", [(4, 8, 2, 6000, [6000, 1, 0, 3333]), (2, 32, 8, 9000, [9000, 4097]),
+                                             (6, 4, 1, 2048, [2048, 2048, 64, 65, 1000, 7])])
+def test_ragged_batch_work_list_schedule(cuda_device, lib, B, Hq, Hkv, N, lens):
+    """With seq_lens and few (sequence, kv-head) pairs the fp16 kernel schedules from a work list derived from the
+    real lengths (one wave of nearly equal CTAs); switched off it uses the host's plan for the longest sequence.
+    Both must give the oracle's result, also with an empty and a one-token sequence, and the attention-mass output."""
+    Q, K, V, scale = workloads.dense_gqa(N, B=B, Hq=Hq, Hkv=Hkv, seed=N)
+    sl = torch.tensor(lens, dtype=torch.int32)
+    want = oracle.dense_gqa_decode(Q, K, V, scale, sl)
+    try:
+        for mode in (1, 0):
+            assert lib.skv_gqa_set_ragged_worklist(mode) == 0
+            got = run(Q, K, V, scale, cuda_device, sl)
+            assert (got - want).abs().max().item() <= TOL, mode
+            mass = torch.zeros(B, Hkv, N, dtype=torch.float32, device=cuda_device)
+            _C.fused_gqa(Q.to(cuda_device), K.to(cuda_device), V.to(cuda_device), scale, seq_lens=sl.to(cuda_device), mass=mass)
+            assert (mass.cpu() - oracle.attention_mass(Q, K, scale, sl)).abs().max().item() <= 1e-3, mode
+    finally:
+        lib.skv_gqa_set_ragged_worklist(1)
