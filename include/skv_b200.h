@@ -117,6 +117,10 @@ int skv_gqa_set_q8_stages(int stages);
  * before that kernel has completed -- valid when it produces none of them (consecutive layers' decode calls over
  * caches written earlier); q, out and the workspace are always ordered.  Process-wide.  No reference counterpart. */
 int skv_gqa_set_early_kv(int on);
+/* Short contexts (up to 24 K tokens) of skv_gqa_decode: on = 1 (default) launches the splits of one (batch, kv-head)
+ * as a thread-block cluster and sums them through distributed shared memory; on = 0 always uses the fp32 partials
+ * in the workspace and the last-CTA ticket.  Results agree to fp32 rounding.  Process-wide.  No reference counterpart. */
+int skv_gqa_set_cluster_combine(int on);
 
 /* ---- Quest-style block-sparse decode over a paged 8-bit cache ----------------------
  * No reference counterpart (the reference scores blocks by the mean of q.k over an unpaged fp16 cache,

@@ -46,6 +46,7 @@ SIGNATURES = {
     "skv_gqa_set_ragged_worklist": (_i, [_i]),
     "skv_gqa_set_q8_two_per_sm": (_i, [_i]),
     "skv_gqa_set_early_kv": (_i, [_i]),
+    "skv_gqa_set_cluster_combine": (_i, [_i]),
     "skv_gqa_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i,
                                   _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp]),
     "skv_quest_num_blocks": (_i, [_i, _i]),

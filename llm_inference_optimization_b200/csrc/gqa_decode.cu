@@ -44,6 +44,7 @@ struct Params {
     int N, Hq, Hkv, G;
     int tiles_per_split, num_splits, stages;
     int list_items, B;   // list_items > 0: grid (Hkv, list_items), work-list schedule of a ragged batch (worklist_item)
+    int cluster_combine; // 1: launched with clusters of num_splits CTAs along y; splits are summed through shared memory
     long long q_stride_b, q_stride_h, o_stride_b, o_stride_h;
     float scale_log2;    // softmax scale * log2(e)
     int early_kv;        // K/V and seq_lens are not produced by the previous kernel: stream them before it completes
@@ -60,8 +61,7 @@ struct Smem {
     static constexpr int STAGE_BYTES = 2 * KV_BYTES;
     static size_t bytes(int stages) {
         size_t ring = (size_t)stages * STAGE_BYTES;
-        size_t merge = (size_t)CONSUMER_WARPS * MAX_GROUP * D * 4 + CONSUMER_WARPS * MAX_GROUP * 8 +
-                       (size_t)CONSUMER_WARPS * MAX_SPLITS * 4;
+        size_t merge = epilogue_smem_bytes<D>();
         size_t body = ring > merge ? ring : merge;
         return 1024 /*alignment slack*/ + body + 2 * stages * 8 + 16;
     }
@@ -92,6 +92,7 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     // has completed.  By default every thread waits for it here, so the kernel is ordered like any other; only when
     // the caller has declared that K, V and seq_lens are not produced by the previous kernel (early_kv) does the
     // wait move down to the consumers, and the producer streams K/V meanwhile.
+    SKV_PHASE(0);
     if (!p.early_kv) pdl_wait_prior_grids();
     int len, n_splits, tiles_per_split = p.tiles_per_split;
     if (p.list_items > 0) {   // work-list schedule of a ragged batch (see worklist_item)
@@ -102,7 +103,13 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.N) : p.N;
         const int tps_tokens = tiles_per_split * TILE;
         n_splits = len > 0 ? (len + tps_tokens - 1) / tps_tokens : 1;
-        if (split >= n_splits) return;
+        if (split >= n_splits) {
+            if (p.cluster_combine) {   // nothing to add, but every thread of a cluster passes both of its barriers
+                cluster_barrier();
+                cluster_barrier();
+            }
+            return;
+        }
     }
     const int tokens_per_split = tiles_per_split * TILE;
     const int t_begin = split * tokens_per_split;
@@ -113,11 +120,7 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t ring = smem_u32(smem);
     size_t body = (size_t)p.stages * S::STAGE_BYTES;
-    {
-        size_t merge = (size_t)CONSUMER_WARPS * MAX_GROUP * D * 4 + CONSUMER_WARPS * MAX_GROUP * 8 +
-                       (size_t)CONSUMER_WARPS * MAX_SPLITS * 4;
-        if (merge > body) body = merge;
-    }
+    if (epilogue_smem_bytes<D>() > body) body = epilogue_smem_bytes<D>();
     const uint32_t full_bar = ring + (uint32_t)body;
     const uint32_t empty_bar = full_bar + p.stages * 8;
     int* last_flag = reinterpret_cast<int*>(smem + body + 2 * p.stages * 8);
@@ -130,6 +133,7 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         fence_barrier_init();
     }
     __syncthreads();
+    SKV_PHASE(1);
     // ------------------------------------------------------------------ producer
     if (warp == CONSUMER_WARPS) {
         if (lane == 0) {
@@ -154,6 +158,11 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
                     kv_tile_load(kdst + S::KV_BYTES + hf * S::HALF_BYTES, &tmV, bar, p.pos, hf, tok, h, b, policy);
                 }
             }
+        }
+        if (p.cluster_combine) {
+            __syncwarp();
+            cluster_barrier();
+            cluster_barrier();
         }
         return;
     }
@@ -198,12 +207,14 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
 
     int s = 0;
     uint32_t ph = 0;
+    SKV_PHASE(2);
     for (int it = 0; it < ntiles; ++it, ++s) {
         if (s == p.stages) { s = 0; ph ^= 1u; }
         if (!mbar_wait(full_bar + s * 8, ph)) {
             if (lane == 0) atomicOr(p.status, SKV_DEV_TIMEOUT);
             break;
         }
+        if (it == 0) SKV_PHASE(3);
         const int tok0 = t_begin + it * TILE + wtok;  // global index of this warp's first token
         if (tok0 < t_end) {
             const uint32_t kbase = ring + s * S::STAGE_BYTES;
@@ -323,6 +334,7 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     }
 
     // ------------------------------------------------- merge the four warps
+    SKV_PHASE(4);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -352,7 +364,23 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     ea.partial_o = p.partial_o; ea.partial_ml = p.partial_ml; ea.tickets = p.tickets; ea.out = p.out;
     ea.Hkv = p.Hkv; ea.G = G; ea.num_splits = p.num_splits; ea.o_stride_b = p.o_stride_b; ea.o_stride_h = p.o_stride_h;
     ea.ml_final = p.ml_final;
+    if (p.cluster_combine) {
+        // The splits of this (b, h) are the CTAs of one cluster (rank == split): each leaves its merged result in its
+        // own shared memory, rank 0 sums them through distributed shared memory, and nobody leaves before it has.
+        SKV_PHASE(5);
+        cluster_merge_publish<D>(smem, G, 1.f);
+        SKV_PHASE(6);
+        cluster_barrier();
+        SKV_PHASE(7);
+        if (cluster_cta_rank() == 0) cluster_combine_rank0<D>(ea, smem, b, h, n_splits);
+        SKV_PHASE(8);
+        cluster_barrier();
+        SKV_PHASE(9);
+        return;
+    }
+    SKV_PHASE(5);
     merge_and_combine<D>(ea, smem, last_flag, b, h, split, n_splits, 1.f);
+    SKV_PHASE(9);
 }
 
 // Attention mass of every cached token, summed over the query heads of its group and ADDED to `mass`:
@@ -379,6 +407,43 @@ attention_mass_kernel(const float* __restrict__ score, const float* __restrict__
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
+// How many clusters of S CTAs of this kernel the device holds at once with `smem` bytes of dynamic shared memory
+// (0: that cluster size cannot be launched).  Asked of the driver once per device and size.
+template <int D>
+static int cluster_room(int device, size_t smem, int S) {
+    static int cached[64][MAX_CLUSTER_SPLITS + 1];   // 1 + answer
+    static int cached_smem[64] = {0};
+    if (device < 0 || device >= 64 || S < 2 || S > MAX_CLUSTER_SPLITS) return 0;
+    if (cached_smem[device] != (int)smem) {
+        for (int i = 0; i <= MAX_CLUSTER_SPLITS; ++i) cached[device][i] = 0;
+        cached_smem[device] = (int)smem;
+        if (cudaFuncSetAttribute(gqa_decode_f16_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaFuncSetAttribute(gqa_decode_f16_kernel<D>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+            cudaGetLastError();
+            for (int i = 0; i <= MAX_CLUSTER_SPLITS; ++i) cached[device][i] = 1;   // no cluster launches on this device
+        }
+    }
+    if (cached[device][S] == 0) cached[device][S] = 1 + max_active_clusters(gqa_decode_f16_kernel<D>, dim3(THREADS), smem, S);
+    return cached[device][S] - 1;
+}
+
+// Short contexts: how many splits per (batch, kv-head) to launch as one cluster, 0 for the ticket combine.  The
+// cluster variant replaces the partial sums' trip through global memory (store, fence, ticket, reload by the last CTA)
+// by two cluster barriers and loads from the other CTAs' shared memory.  It pays only while every cluster is resident
+// at once -- measured on B200: 4 sequences x 8 kv-heads at 4 K tokens 22.5 -> 20.5 us, but 16 sequences at 8 K tokens,
+// whose clusters need several waves, 104 -> 135 us (a cluster waits for a whole group of free SMs) -- and clusters
+// of 16 of this kernel do not fit eight at a time, so one sequence of 8 kv-heads (16-18 splits) keeps the tickets.
+template <int D>
+static int cluster_splits(int device, size_t smem, int plan_splits, long long total_tiles, long long pairs) {
+    constexpr long long MAX_TILES = 384;   // 24 K tokens: beyond, the fixed cost this removes is a few percent
+    if (plan_splits < 2 || total_tiles > MAX_TILES) return 0;
+    int S = plan_splits < MAX_CLUSTER_SPLITS ? plan_splits : MAX_CLUSTER_SPLITS;
+    const long long tps = (total_tiles + S - 1) / S;
+    S = (int)((total_tiles + tps - 1) / tps);
+    if (S < 2 || S * 4 < plan_splits * 3) return 0;   // far fewer CTAs than the plan wanted: streaming would cost more than it saves
+    return cluster_room<D>(device, smem, S) >= pairs ? S : 0;
+}
+
 template <int D>
 static int launch_f16(const CUtensorMap& tmK, const CUtensorMap& tmV, const Params& p, int B, cudaStream_t stream) {
     static int configured_smem[64] = {0};
@@ -390,7 +455,10 @@ static int launch_f16(const CUtensorMap& tmK, const CUtensorMap& tmV, const Para
         configured_smem[dev] = (int)smem;
     }
     const dim3 grid = p.list_items > 0 ? dim3(p.Hkv, p.list_items, 1) : dim3(p.Hkv, p.num_splits, B);
-    SKV_CUDA_TRY(launch_pdl(gqa_decode_f16_kernel<D>, grid, dim3(THREADS), smem, stream, tmK, tmV, p));
+    if (p.cluster_combine)
+        SKV_CUDA_TRY(launch_pdl_cluster(gqa_decode_f16_kernel<D>, grid, dim3(THREADS), smem, stream, p.num_splits, tmK, tmV, p));
+    else
+        SKV_CUDA_TRY(launch_pdl(gqa_decode_f16_kernel<D>, grid, dim3(THREADS), smem, stream, tmK, tmV, p));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }
@@ -409,6 +477,13 @@ int skv_gqa_set_tuning(int stages, int ctas_per_sm) {
         return fail(SKV_ERR_BAD_ARG, "tuning out of range: stages=%d ctas_per_sm=%d", stages, ctas_per_sm);
     gqa::tuning().stages = stages;
     gqa::tuning().ctas_per_sm = ctas_per_sm;
+    return SKV_OK;
+}
+
+// 1 (default): short contexts launch the splits of a (batch, kv-head) as one thread-block cluster and sum them through
+// shared memory; 0: always the global-memory partials and ticket.  Results agree to fp32 rounding.  Process-wide.
+int skv_gqa_set_cluster_combine(int on) {
+    gqa::tuning().cluster_combine = on ? 1 : 0;
     return SKV_OK;
 }
 
@@ -496,6 +571,18 @@ static int decode_f16_impl(const void* q, const void* k, const void* v, void* ou
         p.list_items = worklist ? slots_total * waves / Hkv : 0;
         p.B = B;
     }
+    p.cluster_combine = 0;
+    if (gqa::tuning().cluster_combine && !mass && p.list_items == 0) {
+        const long long total_tiles = (N + gqa::TILE - 1) / gqa::TILE;
+        const size_t smem = D == 128 ? gqa::Smem<128>::bytes(p.stages) : gqa::Smem<64>::bytes(p.stages);
+        const int S = D == 128 ? gqa::cluster_splits<128>(device, smem, pl.splits, total_tiles, (long long)B * Hkv)
+                               : gqa::cluster_splits<64>(device, smem, pl.splits, total_tiles, (long long)B * Hkv);
+        if (S > 0) {
+            p.cluster_combine = 1;
+            p.num_splits = S;
+            p.tiles_per_split = (int)((total_tiles + S - 1) / S);
+        }
+    }
     p.q_stride_b = (long long)Hq * D; p.q_stride_h = D;
     p.o_stride_b = (long long)Hq * D; p.o_stride_h = D;
     p.scale_log2 = scale * 1.4426950408889634f;
@@ -536,6 +623,12 @@ int skv_gqa_decode_mass(const void* q, const void* k, const void* v, void* out, 
     return decode_f16_impl(q, k, v, out, mass, workspace, workspace_bytes, B, N, Hq, Hkv, D, SKV_KV_F16, kv_stride_b,
                            kv_stride_n, kv_stride_h, seq_lens, scale, device, stream);
 }
+
+#ifdef SKV_PROFILE_PHASES
+int skv_debug_phase_ts_f16(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, skv_phase_ts, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : -4;
+}
+#endif
 
 // ---------------------------------------------------------------------------
 // Allocation-free variant of skv_gqa_decode.

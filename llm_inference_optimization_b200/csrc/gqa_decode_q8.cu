@@ -26,7 +26,8 @@
 //     query heads on the 8-wide N side: a group of <= 8 heads needs one n-tile;
 //     P is moved to the B-operand layout with movmatrix;
 //   * codes are converted to fp16 in registers right after ldmatrix (e4m3x2 ->
-//     f16x2 by cvt, int8 by a byte-permute + subtract); because four bytes arrive
+//     f16x2 by cvt; int8 by a byte-permute into the mantissa of 1024 + x, whose bias is taken out of the
+//     accumulators instead of every element, see cvt_quad_k); because four bytes arrive
 //     per lane where an fp16 fragment has two halves, the contraction index of
 //     S^T and the output channels of O^T are permuted consistently;
 //   * ks[t] multiplies the fp32 score; vs[t] (times 2^6, undone at the end, to stay
@@ -114,6 +115,37 @@ __device__ __forceinline__ void cvt_quad(uint32_t v, uint32_t& lo, uint32_t& hi)
         const __half2 rb = __hsub2(*reinterpret_cast<__half2*>(&b), bias);
         lo = *reinterpret_cast<const uint32_t*>(&ra);
         hi = *reinterpret_cast<const uint32_t*>(&rb);
+    }
+}
+
+// The same for the tensor-core operands, where INT8 codes keep the bias of the exponent trick: 0x6400 | (b ^ 0x80) is
+// the fp16 number b + 1152, and instead of subtracting 1152 from every element (two HSUB2 per four codes, more than the
+// conversion itself) the products are corrected once per accumulator:
+//     sum_d q_d (k_d + 1152) = q.k + 1152 sum_d q_d          (per head: a constant of the launch)
+//     sum_t p_t (v_t + 1152) = p.v + 1152 sum_t p_t          (per head: one more MMA per step, against a tile of ones)
+// Every product is exact in fp32 (11-bit q or p times an integer below 2048).  cvt_quad_v also folds in the byte
+// shuffle of the transposed V tile ([c0, c2 | c1, c3] of the register).
+constexpr float INT8_BIAS = 1152.f;
+
+template <int KVT>
+__device__ __forceinline__ void cvt_quad_k(uint32_t v, uint32_t& lo, uint32_t& hi) {
+    if (KVT == SKV_KV_E4M3) {
+        cvt_quad<KVT>(v, lo, hi);
+    } else {
+        const uint32_t x = v ^ 0x80808080u;
+        lo = __byte_perm(x, 0x64646464u, 0x4140);
+        hi = __byte_perm(x, 0x64646464u, 0x4342);
+    }
+}
+
+template <int KVT>
+__device__ __forceinline__ void cvt_quad_v(uint32_t v, uint32_t& lo, uint32_t& hi) {
+    if (KVT == SKV_KV_E4M3) {
+        cvt_quad<KVT>(__byte_perm(v, 0u, 0x3120), lo, hi);
+    } else {
+        const uint32_t x = v ^ 0x80808080u;
+        lo = __byte_perm(x, 0x64646464u, 0x4240);
+        hi = __byte_perm(x, 0x64646464u, 0x4341);
     }
 }
 
@@ -279,8 +311,29 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         }
     }
 
+    // INT8: 1152 * (sum of the query's channels) for this lane's two score columns, heads 8nt+2tq and 8nt+2tq+1
+    float qbias[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        qbias[nt][0] = qbias[nt][1] = 0.f;
+        if (KVT != SKV_KV_E4M3) {
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                const float2 u = __half22float2(*reinterpret_cast<const __half2*>(&qb[nt][c][0]));
+                const float2 w = __half22float2(*reinterpret_cast<const __half2*>(&qb[nt][c][1]));
+                sum += (u.x + u.y) + (w.x + w.y);
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);          // lanes (g, *): all channels of head 8nt+g
+            qbias[nt][0] = INT8_BIAS * __shfl_sync(0xffffffffu, sum, (2 * tq) * 4);
+            qbias[nt][1] = INT8_BIAS * __shfl_sync(0xffffffffu, sum, (2 * tq + 1) * 4);
+        }
+    }
+
     // o[nt][c][j], o[nt][c][j+2]: channels 16c+2g and 16c+2g+1 of head 8nt+2tq+j
     float o[NT][NCH][4];
+    float psum[NT][4];   // INT8: sum over tokens of the P operand, in o's layout (every channel row the same)
     float mrun[NT][2], lrun[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -288,6 +341,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         for (int c = 0; c < NCH; ++c) o[nt][c][0] = o[nt][c][1] = o[nt][c][2] = o[nt][c][3] = 0.f;
         mrun[nt][0] = mrun[nt][1] = -INFINITY;
         lrun[nt][0] = lrun[nt][1] = 0.f;
+        psum[nt][0] = psum[nt][1] = psum[nt][2] = psum[nt][3] = 0.f;
     }
     const int lj = lane >> 3, r8 = lane & 7;
     const int group = warp >> 2;          // consumer group: takes the stages with it % Q8_GROUPS == group
@@ -348,10 +402,10 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 uint32_t r0, r1, r2, r3;
                 ldsm_x4(kbase + (((uint32_t)(2 * m) + ld_ch) ^ sw) * 16, r0, r1, r2, r3);
                 uint32_t a0[4], a1[4];
-                cvt_quad<KVT>(r0, a0[0], a0[2]);   // token g:   k-indices 2tq.. and 2tq+8..
-                cvt_quad<KVT>(r1, a0[1], a0[3]);   // token g+8
-                cvt_quad<KVT>(r2, a1[0], a1[2]);
-                cvt_quad<KVT>(r3, a1[1], a1[3]);
+                cvt_quad_k<KVT>(r0, a0[0], a0[2]);   // token g:   k-indices 2tq.. and 2tq+8..
+                cvt_quad_k<KVT>(r1, a0[1], a0[3]);   // token g+8
+                cvt_quad_k<KVT>(r2, a1[0], a1[2]);
+                cvt_quad_k<KVT>(r3, a1[1], a1[3]);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     mma_f16(sc[nt], a0, qb[nt][2 * m][0], qb[nt][2 * m][1]);
@@ -369,6 +423,10 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             bool grow = false;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
+                if (KVT != SKV_KV_E4M3) {   // the biased codes added 1152 * sum(q) to every score of a head
+                    sc[nt][0] -= qbias[nt][0]; sc[nt][1] -= qbias[nt][1];
+                    sc[nt][2] -= qbias[nt][0]; sc[nt][3] -= qbias[nt][1];
+                }
                 sc[nt][0] = dead0 ? -INFINITY : (sc[nt][0] + sd[nt][0]) * ks0;
                 sc[nt][1] = dead0 ? -INFINITY : (sc[nt][1] + sd[nt][1]) * ks0;
                 sc[nt][2] = dead1 ? -INFINITY : (sc[nt][2] + sd[nt][2]) * ks1;
@@ -393,6 +451,10 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                     for (int c = 0; c < NCH; ++c) {
                         o[nt][c][0] *= c0; o[nt][c][1] *= c1;
                         o[nt][c][2] *= c0; o[nt][c][3] *= c1;
+                    }
+                    if (KVT != SKV_KV_E4M3) {
+                        psum[nt][0] *= c0; psum[nt][1] *= c1;
+                        psum[nt][2] *= c0; psum[nt][3] *= c1;
                     }
                     mrun[nt][0] = mnew[nt][0];
                     mrun[nt][1] = mnew[nt][1];
@@ -419,15 +481,20 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 uint32_t r0, r1, r2, r3;
                 ldsm_x4_t(vbase + (((uint32_t)(2 * m) + ld_ch) ^ sw) * 16, r0, r1, r2, r3);
                 uint32_t a0[4], a1[4];
-                cvt_quad<KVT>(__byte_perm(r0, 0u, 0x3120), a0[0], a0[1]);   // tokens 0-7:  even | odd channel
-                cvt_quad<KVT>(__byte_perm(r1, 0u, 0x3120), a0[2], a0[3]);   // tokens 8-15
-                cvt_quad<KVT>(__byte_perm(r2, 0u, 0x3120), a1[0], a1[1]);
-                cvt_quad<KVT>(__byte_perm(r3, 0u, 0x3120), a1[2], a1[3]);
+                cvt_quad_v<KVT>(r0, a0[0], a0[1]);   // tokens 0-7:  even | odd channel
+                cvt_quad_v<KVT>(r1, a0[2], a0[3]);   // tokens 8-15
+                cvt_quad_v<KVT>(r2, a1[0], a1[1]);
+                cvt_quad_v<KVT>(r3, a1[2], a1[3]);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     mma_f16(o[nt][2 * m], a0, pb[nt][0], pb[nt][1]);
                     mma_f16(o[nt][2 * m + 1], a1, pb[nt][0], pb[nt][1]);
                 }
+            }
+            if (KVT != SKV_KV_E4M3) {   // sum_t p_t on the same path as O: a tile of ones in V's place
+                const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma_f16(psum[nt], ones, pb[nt][0], pb[nt][1]);
             }
         }
         __syncwarp();
@@ -435,6 +502,14 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     }
 
     SKV_PHASE(4);
+    if (KVT != SKV_KV_E4M3) {   // take the codes' bias out of O
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int c = 0; c < NCH; ++c)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o[nt][c][j] -= INT8_BIAS * psum[nt][j];
+    }
     // the running sums are per lane (its two token rows): total over the 8 lanes g
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
@@ -555,11 +630,13 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     if (!guard.ok) return fail(SKV_ERR_CUDA, "cannot switch to device %d", device);
 
     // FP8 with up to 8 heads per group runs the one-group variant, two CTAs per SM: measured equal or faster at every
-    // size tried (one sequence of 64K: equal; 4 x 64K: 0.76 -> 0.92 of the copy bandwidth; 16 x 64K: 0.89 -> 0.96)
+    // size tried (one sequence of 64K: equal; 4 x 64K: 0.76 -> 0.92 of the copy bandwidth; 16 x 64K: 0.89 -> 0.96).
+    // INT8 takes it when the launch has more CTAs than one wave (16 x 64K: 0.87 -> 0.90); a single wave is faster
+    // with two groups in one CTA per SM (one sequence of 64K: 34.9 against 37.9 us).
     const int two = gqa::tuning().q8_two_per_sm;   // -1: as above; 0 / 1: forced (experiments)
-    const bool many = two >= 0 ? two != 0 : true;
     const bool one_wave = seq_lens == nullptr && (long long)B * Hkv * 2 <= sm_count(device);
-    const int slots = (kv_dtype == SKV_KV_E4M3 && G <= 8 && many) ? 2 : 1;   // CTAs resident per SM
+    const bool many = two >= 0 ? two != 0 : (kv_dtype == SKV_KV_E4M3 || !one_wave);
+    const int slots = (G <= 8 && many) ? 2 : 1;   // CTAs resident per SM
     gqa::Plan pl = gqa::make_plan(B, N, Hq, Hkv, D, device, seq_lens != nullptr, slots);
     if (!workspace || workspace_bytes < pl.total)
         return fail(SKV_ERR_WORKSPACE, "workspace of %zu bytes is smaller than the %zu required", workspace_bytes, pl.total);
@@ -635,7 +712,9 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.scale_log2 = scale * 1.4426950408889634f;
     p.pos = pos;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (slots == 2) return gqa::launch_q8<SKV_KV_E4M3, 1, 1>(tmK, tmV, p, B, st);
+    if (slots == 2)
+        return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3, 1, 1>(tmK, tmV, p, B, st)
+                                       : gqa::launch_q8<SKV_KV_I8, 1, 1>(tmK, tmV, p, B, st);
     if (G <= 8)
         return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3, 1, 2>(tmK, tmV, p, B, st)
                                        : gqa::launch_q8<SKV_KV_I8, 1, 2>(tmK, tmV, p, B, st);

@@ -28,6 +28,19 @@ __host__ __device__ constexpr size_t merge_smem_bytes() {
     return (size_t)NW * MAX_GROUP * D * 4 + (size_t)NW * MAX_GROUP * 8 + (size_t)NW * MAX_SPLITS * 4;
 }
 
+// Short contexts: the splits of one (batch, kv-head) form a thread-block cluster and the split results are summed
+// through distributed shared memory instead of a global-memory round trip (merge_and_combine_cluster).
+constexpr int MAX_CLUSTER_SPLITS = 16;
+// Each CTA's merged result for that sum: O [MAX_GROUP][D] and (max, sum) [MAX_GROUP][2], behind the merge area.
+template <int D, int NW = CONSUMER_WARPS>
+__host__ __device__ constexpr size_t cluster_area_offset() {
+    return (merge_smem_bytes<D, NW>() + 15) & ~size_t(15);
+}
+template <int D, int NW = CONSUMER_WARPS>
+__host__ __device__ constexpr size_t epilogue_smem_bytes() {
+    return cluster_area_offset<D, NW>() + (size_t)MAX_GROUP * D * 4 + (size_t)MAX_GROUP * 8;
+}
+
 struct Tuning {
     int stages = 4;        // fp16 ring depth (64-token stages of 32 KB at D = 128)
     int ctas_per_sm = 1;
@@ -35,6 +48,7 @@ struct Tuning {
     int early_kv = 0;      // 1: K/V, page table and lengths may be read before the previous kernel has completed
     int q8_two_per_sm = -1;  // FP8 kernel variant: -1 chosen by the launcher, 0 one CTA per SM, 1 two CTAs per SM
     int ragged_worklist = 1;  // the 8-bit kernel schedules a ragged batch with few pairs from a device-side work list
+    int cluster_combine = 1;  // short contexts: splits of a (batch, kv-head) as one cluster, summed through shared memory
 };
 inline Tuning& tuning() {
     static Tuning t;
@@ -264,6 +278,83 @@ __device__ __forceinline__ void merge_and_combine(const EpilogueArgs& p, uint8_t
             *reinterpret_cast<uint2*>(p.out + (long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + lane * 4) = pk;
         }
         __syncwarp();
+    }
+}
+
+// The cluster variant of merge_and_combine, for a launch whose clusters hold all splits of one (batch, kv-head) with
+// cluster rank == split.  Called by the consumer threads of a CTA that has a split, after the same preparation as
+// merge_and_combine; the caller then runs the two cluster barriers with EVERY thread of the cluster:
+//     cluster_merge_publish (consumers)  ->  cluster_barrier (all)  ->  cluster_combine_rank0 (consumers of rank 0)
+//     ->  cluster_barrier (all: no CTA leaves while rank 0 may still read its shared memory)
+template <int D, int NW = CONSUMER_WARPS>
+__device__ __forceinline__ void cluster_merge_publish(uint8_t* smem, int G, float out_scale) {
+    float* mo = reinterpret_cast<float*>(smem);
+    float* mm = mo + NW * MAX_GROUP * D;
+    float* ml = mm + NW * MAX_GROUP;
+    float* co = reinterpret_cast<float*>(smem + cluster_area_offset<D, NW>());   // [MAX_GROUP][D]
+    float* cml = co + MAX_GROUP * D;                                             // [MAX_GROUP][2]
+    for (int idx = threadIdx.x; idx < G * D; idx += (NW * 32)) {
+        const int r = idx / D, d = idx - r * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, mm[w * MAX_GROUP + r]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float mw = mm[w * MAX_GROUP + r];
+            const float wgt = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+            L += ml[w * MAX_GROUP + r] * wgt;
+            O += mo[(w * MAX_GROUP + r) * D + d] * wgt;
+        }
+        co[idx] = O * out_scale;
+        if (d == 0) {
+            cml[2 * r] = M;
+            cml[2 * r + 1] = L;
+        }
+    }
+}
+
+template <int D, int NW = CONSUMER_WARPS>
+__device__ __forceinline__ void cluster_combine_rank0(const EpilogueArgs& p, uint8_t* smem, int b, int h, int n_splits) {
+    const int G = p.G;
+    const uint32_t co = smem_u32(smem + cluster_area_offset<D, NW>());
+    const uint32_t cml = co + MAX_GROUP * D * 4;
+    const long long bh = (long long)b * p.Hkv + h;
+    for (int i4 = threadIdx.x; i4 < G * D / 4; i4 += (NW * 32)) {
+        const int r = (i4 * 4) / D, d = i4 * 4 - r * D;
+        float ms[MAX_CLUSTER_SPLITS], ls[MAX_CLUSTER_SPLITS];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER_SPLITS; ++s) {
+            ms[s] = -INFINITY;
+            ls[s] = 0.f;
+            if (s < n_splits) {
+                const float2 v = ld_cluster_f2(cluster_map(cml + r * 8, s));
+                ms[s] = v.x;
+                ls[s] = v.y;
+                mx = fmaxf(mx, v.x);
+            }
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float Ls = 0.f;
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER_SPLITS; ++s) {   // in split order: the sum does not depend on timing
+            if (s < n_splits) {
+                const float w = (ms[s] == -INFINITY) ? 0.f : fast_exp2(ms[s] - mx);
+                const float4 v = ld_cluster_f4(cluster_map(co + i4 * 16, s));
+                Ls += ls[s] * w;
+                acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+            }
+        }
+        if (p.ml_final && d == 0) {
+            p.ml_final[(bh * G + r) * 2] = mx;
+            p.ml_final[(bh * G + r) * 2 + 1] = Ls;
+        }
+        const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+        uint2 pk;
+        pk.x = (uint32_t)out_bits(acc.x * inv, p.out_bf16) | ((uint32_t)out_bits(acc.y * inv, p.out_bf16) << 16);
+        pk.y = (uint32_t)out_bits(acc.z * inv, p.out_bf16) | ((uint32_t)out_bits(acc.w * inv, p.out_bf16) << 16);
+        *reinterpret_cast<uint2*>(p.out + (long long)b * p.o_stride_b + (long long)(h * G + r) * p.o_stride_h + d) = pk;
     }
 }
 

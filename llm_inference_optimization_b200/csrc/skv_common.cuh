@@ -99,6 +99,50 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
+
+// The same, with the CTAs of grid dimension y grouped into thread-block clusters of `cluster_y` (which must divide
+// grid.y).  Sizes above 8 need cudaFuncAttributeNonPortableClusterSizeAllowed on the kernel.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      int cluster_y, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = (unsigned)cluster_y;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// How many clusters of `cluster_y` CTAs of this kernel the device can hold at once (0: such a launch would fail).
+template <typename... KArgs>
+inline int max_active_clusters(void (*kernel)(KArgs...), dim3 block, size_t smem, int cluster_y) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, (unsigned)cluster_y, 1);
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)cluster_y;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
 #endif
 
 // ---------------------------------------------------------------------------
@@ -326,6 +370,38 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 // ... and, in that next kernel, wait until every earlier kernel has finished and its writes are visible.
 __device__ __forceinline__ void pdl_wait_prior_grids() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// ---- thread-block clusters: rank, barrier, and loads from another CTA's shared memory ----
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// Barrier over every thread of the cluster; all 32 lanes of a warp must reach it together.  Shared-memory writes made
+// before it are visible to the other CTAs' loads after it.
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Address of this CTA's shared-memory location `local` in the CTA of rank `rank` of the same cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ float2 ld_cluster_f2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {

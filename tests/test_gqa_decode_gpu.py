@@ -148,3 +148,26 @@ def test_ragged_batch_work_list_schedule(cuda_device, lib, B, Hq, Hkv, N, lens):
             assert (mass.cpu() - oracle.attention_mass(Q, K, scale, sl)).abs().max().item() <= 1e-3, mode
     finally:
         lib.skv_gqa_set_ragged_worklist(1)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,D,N,lens", [
+    (1, 32, 8, 128, 4096, None), (1, 32, 8, 128, 16384, None), (1, 32, 8, 128, 24576, None),   # config-2 short contexts
+    (2, 32, 8, 128, 8192, [8192, 130]), (3, 16, 2, 128, 5000, [5000, 0, 1]),                  # ragged, empty, one token
+    (1, 8, 1, 64, 3000, None), (16, 32, 8, 128, 4096, None), (1, 16, 1, 128, 2048, None)])    # D = 64, many pairs, G = 16
+def test_short_context_cluster_combine(cuda_device, lib, B, Hq, Hkv, D, N, lens):
+    """Short contexts launch the splits of a (batch, kv-head) as one thread-block cluster and sum them through
+    distributed shared memory; switched off, the same call goes through global-memory partials and the ticket.
+    Both give the oracle's result, and they agree with each other to fp16 rounding."""
+    Q, K, V, scale = workloads.dense_gqa(N, B=B, Hq=Hq, Hkv=Hkv, D=D, seed=N + B)
+    sl = None if lens is None else torch.tensor(lens, dtype=torch.int32)
+    want = oracle.dense_gqa_decode(Q, K, V, scale, sl)
+    got = {}
+    try:
+        for mode in (1, 0):
+            assert lib.skv_gqa_set_cluster_combine(mode) == 0
+            for _ in range(2):
+                got[mode] = run(Q, K, V, scale, cuda_device, sl)
+            assert (got[mode] - want).abs().max().item() <= TOL, mode
+    finally:
+        lib.skv_gqa_set_cluster_combine(1)
+    assert (got[1] - got[0]).abs().max().item() <= 2.0 ** -10 * max(1.0, want.abs().max().item())
