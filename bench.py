@@ -524,7 +524,7 @@ def main():
         from llm_inference_optimization_b200 import bench_decode
         torch.cuda.empty_cache()
         try:
-            res = bench_decode.run(steps=10, warmup=3, hybrid_dense_layers=16)
+            res = bench_decode.run(steps=10, warmup=3, hybrid_dense_layers=16, mixed_pages=True)
         except Exception as e:  # reported, never fatal for the headline line
             res = {"error": f"{type(e).__name__}: {e}"}
         if rank == 0:

@@ -41,6 +41,15 @@ extern "C" {
 #define SKV_KV_E4M3 2
 /* OR-ed into kv_dtype of skv_gqa_decode_paged: the output tensor holds bf16 instead of fp16 elements. */
 #define SKV_OUT_BF16 0x100
+/* OR-ed into kv_dtype of skv_gqa_decode_paged and skv_rope_quant_append: mixed-precision pages.  K stays 8-bit
+ * (SKV_KV_I8 or SKV_KV_E4M3); V is 4-bit: code q = clamp(rne(v / scale), -7, 7) with scale = amax / 7 (1.0 for a zero
+ * row), stored as the nibble q + 8, channel 2j in the low and 2j+1 in the high nibble of byte j (64 bytes per token).
+ * The cache is one buffer of page records, [num_pages, Hkv, 25, 128] bytes: per (page, head) 16 rows of K codes,
+ * 8 rows of V codes (two tokens per row), one row of 16 K scales then 16 V scales (fp32); pages hold 16 tokens.
+ * Pass k_pool = record base, v_pool = base + 2048, k_scale_pool = base + 3072, v_scale_pool = base + 3136 (bytes),
+ * pool strides (Hkv * 3200, 3200, 128) and scale strides (Hkv * 800, 800).  Up to 8 query heads per kv-head.
+ * No reference counterpart. */
+#define SKV_V_INT4 0x200
 
 /* bit in the workspace status word: a bounded wait inside a kernel ran out */
 #define SKV_DEV_TIMEOUT 1
@@ -137,9 +146,10 @@ int skv_gqa_set_cluster_combine(int on);
  *   read in its place and SKV_DEV_BAD_PAGE is set in the status word (skv_quest_build_meta: in *status, an optional
  *   int32 device word; skv_quest_decode: at offset 0 of the workspace, read with skv_workspace_status). */
 int skv_quest_num_blocks(int N, int block_size);
-/* on = 1: skv_quest_decode scores the blocks with the kernel that streams the metadata through a shared-memory
- * ring by bulk asynchronous copies; on = 0 (default): with the register-load kernel, which measures faster on B200.
- * Same results; process-wide.  No reference counterpart. */
+/* on = 1 (default): skv_quest_decode scores the blocks on the tensor cores -- the bound sum_c max(q_c lo_c, q_c hi_c)
+ * equals the dot product of (lo | hi) with (min(q, 0) | max(q, 0)) -- with the metadata streamed through a
+ * shared-memory ring by TMA (up to 8 query heads per kv-head); on = 0: with the register-load kernel (also used for
+ * larger groups).  Both sum the same exact products, in different orders.  Process-wide.  No reference counterpart. */
 int skv_quest_set_ring_scores(int on);
 size_t skv_quest_workspace_bytes(int B, int Hq, int N, int block_size);
 int skv_quest_build_meta(const void* k_pool, const float* k_scale_pool, const int* page_table, const int* seq_lens,

@@ -170,6 +170,7 @@ def sparse_attention_forward(Q: Tensor, K: Tensor, V: Tensor, block_size: int, t
 
 
 SKV_OUT_BF16 = 0x100  # OR-ed into the kv_dtype argument of skv_gqa_decode_paged: bf16 output elements
+SKV_V_INT4 = 0x200    # ... and of skv_rope_quant_append: V is 4-bit (mixed-precision page records)
 
 
 def _code_dtype(t: Tensor) -> int:
@@ -182,8 +183,11 @@ def _code_dtype(t: Tensor) -> int:
 
 def fused_gqa_paged(Q: Tensor, k_pool: Tensor, v_pool: Tensor, k_scale: Tensor, v_scale: Tensor,
                     page_table: Tensor | None, seq_lens: Tensor | None, scale: float, *,
-                    max_seq_len: int | None = None, out: Tensor | None = None) -> Tensor:
+                    max_seq_len: int | None = None, out: Tensor | None = None, v_bits: int = 8) -> Tensor:
     """Dense GQA decode over a paged INT8 / FP8-E4M3 cache with per-token-per-head fp32 scales.
+
+    ``v_bits=4``: the pools are the views of a mixed-precision record buffer (``paged.mixed_views``): ``v_pool`` is
+    uint8 ``[num_pages, Hkv, 16, 64]`` of packed 4-bit codes, ``k_pool`` stays 8-bit.
 
     Q ``[B,Hq,128]`` fp16; pools ``[num_pages, Hkv, page_size, 128]`` int8 or float8_e4m3fn; scale pools
     ``[num_pages, Hkv, page_size]`` fp32; ``page_table`` int32 ``[B, max_pages]`` (``None``: sequence b owns
@@ -193,13 +197,20 @@ def fused_gqa_paged(Q: Tensor, k_pool: Tensor, v_pool: Tensor, k_scale: Tensor, 
     """
     _require(Q.is_cuda and Q.dtype == torch.float16 and Q.dim() == 3 and Q.is_contiguous(),
              "Q must be a contiguous fp16 CUDA tensor [B,Hq,D]")
-    _require(k_pool.dim() == 4 and v_pool.shape == k_pool.shape and k_pool.dtype == v_pool.dtype,
-             "k_pool and v_pool must both be [num_pages,Hkv,page_size,D] of one 8-bit dtype")
+    _require(v_bits in (4, 8), "v_bits must be 4 or 8")
     kvt = _code_dtype(k_pool)
     B, Hq, D = Q.shape
+    _require(k_pool.dim() == 4, "k_pool must be [num_pages,Hkv,page_size,D]")
     num_pages, Hkv, P, Dk = k_pool.shape
     _require(Dk == D, "pool head_dim must match Q")
-    _require(k_pool.stride(-1) == 1 and k_pool.stride() == v_pool.stride(), "pools must share a channel-contiguous layout")
+    if v_bits == 4:
+        _require(v_pool.dtype == torch.uint8 and v_pool.shape == (num_pages, Hkv, P, D // 2) and k_pool.stride(-1) == 1,
+                 "with v_bits=4, v_pool must be uint8 [num_pages,Hkv,page_size,D/2] of packed 4-bit codes")
+        kvt |= SKV_V_INT4
+    else:
+        _require(v_pool.shape == k_pool.shape and k_pool.dtype == v_pool.dtype,
+                 "k_pool and v_pool must both be [num_pages,Hkv,page_size,D] of one 8-bit dtype")
+        _require(k_pool.stride(-1) == 1 and k_pool.stride() == v_pool.stride(), "pools must share a channel-contiguous layout")
     _require(k_scale.shape == (num_pages, Hkv, P) and v_scale.shape == k_scale.shape and k_scale.dtype == torch.float32
              and v_scale.dtype == torch.float32 and k_scale.stride() == v_scale.stride() and k_scale.stride(-1) == 1,
              "scale pools must be fp32 [num_pages,Hkv,page_size] with one layout")

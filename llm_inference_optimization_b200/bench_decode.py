@@ -79,10 +79,11 @@ def tp_parity(world: int, rank: int, dev, fused_allreduce: bool) -> dict | None:
 
 def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, seed: int = 4, use_graph: bool = True,
         fill: str = "random_codes", fused_allreduce: bool = True, hybrid_dense_layers: int | None = None,
-        emulate_tp: int = 0) -> dict | None:
+        emulate_tp: int = 0, mixed_pages: bool = False) -> dict | None:
     """``emulate_tp`` (single process only): build rank 0's shard of an ``emulate_tp``-way tensor-parallel model on one
     GPU and run its step without the exchange -- every kernel then has the shapes it has at that degree, which is what
-    a per-kernel launch list needs (a profiler must not wrap a multi-rank run)."""
+    a per-kernel launch list needs (a profiler must not wrap a multi-rank run).  ``mixed_pages``: afterwards the same
+    step is timed over caches of mixed-precision page records (FP8 keys, 4-bit values)."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -195,11 +196,30 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
         model.set_layer_modes(None)
     if fused_allreduce and model.arn.status() != 0:
         raise RuntimeError("a bounded wait for a peer ran out inside the fused all-reduce kernel")
+    mixed = None
+    if mixed_pages:
+        # the same model, lengths and page tables over mixed-precision page records: 200 instead of 264 bytes per token
+        # and kv-head (the first model's caches are freed first: the two do not fit side by side at every size)
+        del model
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        model = ds.DecodeModel(cfg, shard_heads(cfg.Hq, cfg.Hkv, shard_world, rank), dev, seed=seed, v_bits=4)
+        if shard_world != world:
+            model._all_reduce = lambda x: x
+        model.init_cache(lens, fill=fill, seed=seed, extra_tokens=2 * (steps + warmup) + 32)
+        if fused_allreduce:
+            model.enable_fused_allreduce(batch)
+        ms_m, fin_m = timed_run()
+        if fused_allreduce and model.arn.status() != 0:
+            raise RuntimeError("a bounded wait for a peer ran out inside the fused all-reduce kernel")
+        mixed = {"kv": "FP8-E4M3 keys, 4-bit values (mixed-precision page records), " + fill, "ms_per_step": ms_m,
+                 "value": batch / (ms_m * 1e-3), "unit": "tok/s", "logits_finite": fin_m, "speedup_vs_fp8_values": ms / ms_m,
+                 "kv_bytes_per_gpu": ideal_bytes(cfg, lens, shard_world)["kv_bytes_per_gpu"] * 200 // 264}
     ib = ideal_bytes(cfg, lens, shard_world)
     out = {
         "metric": "decode_step_tokens_per_s", "value": batch / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms,
         "n_gpus": world, "emulated_tp_shard": shard_world if shard_world != world else None, "steps": steps, "warmup": warmup, "cuda_graph": use_graph, "logits_finite": finite,
-        "tp_parity": parity, "hybrid_schedule": hybrid,
+        "tp_parity": parity, "hybrid_schedule": hybrid, "mixed_precision_pages": mixed,
         "config": {"model": "Llama-3.1-8B architecture, random init N(0,0.02), bf16 weights", "layers": layers,
                    "batch": batch, "context_lengths": "uniform 8192..131072, seed 4", "total_context_tokens": int(lens.sum()),
                    "kv": "FP8-E4M3 paged (page 16, fused page records), per-token-per-head fp32 scales, " + fill,
@@ -228,10 +248,12 @@ def main():
                     help="single process: run rank 0's shard of an N-way tensor-parallel model without the exchange")
     ap.add_argument("--hybrid-dense-layers", type=int, default=None,
                     help="also time a schedule with dense attention in the first N layers and Quest block-sparse attention in the rest")
+    ap.add_argument("--mixed-pages", action="store_true",
+                    help="also time the step over mixed-precision page records (FP8 keys, 4-bit values)")
     args = ap.parse_args()
     res = run(args.steps, args.warmup, args.layers, args.batch, use_graph=not args.no_graph,
               fused_allreduce=not args.nccl_allreduce, hybrid_dense_layers=args.hybrid_dense_layers,
-              emulate_tp=args.emulate_tp)
+              emulate_tp=args.emulate_tp, mixed_pages=args.mixed_pages)
     if res is not None:
         print(json.dumps(res), flush=True)
     if dist.is_initialized():

@@ -117,6 +117,30 @@ def bench_paged(t, dev, g, peak, pk):
             del buf, kv
 
 
+def bench_mixed(t, dev, g, peak, pk):
+    """Dense decode over mixed-precision page records (8-bit K, 4-bit V): 200 bytes per token and head against the
+    264 of an all-8-bit cache.  Random codes with fixed scales."""
+    D, Hq, Hkv, P = 128, 32, 8, 16
+    for fp8 in (True, False):
+        for B, N in ((1, 65536), (1, 131072), (16, 65536)):
+            pages = B * N // P
+            buf = torch.randint(0, 256, (pages, Hkv, paged.MIXED_RECORD_ROWS, 128), device=dev, generator=g, dtype=torch.uint8)
+            if fp8:   # no NaN codes among the keys
+                buf[:, :, :16] = torch.where((buf[:, :, :16] & 0x7F) == 0x7F, buf[:, :, :16] & 0xFE, buf[:, :, :16])
+            table = torch.randperm(pages, device=dev, generator=g).to(torch.int32).view(B, N // P)
+            kv = paged.PagedKV.from_mixed(buf, torch.float8_e4m3fn if fp8 else torch.int8, table, None, B)
+            kv.k_scale.fill_(0.008)
+            kv.v_scale.fill_(0.05)
+            Q = randn16((B, Hq, D), dev, g)
+            out = torch.empty_like(Q)
+            us, mn = t(lambda: kv.decode(Q, D ** -0.5, out=out))
+            nbytes = B * N * Hkv * (D + D // 2 + 8)
+            emit("dense_gqa_paged_" + ("fp8" if fp8 else "int8") + "_k_int4_v", {"B": B, "Hq": Hq, "Hkv": Hkv, "D": D, "ctx": N, "page": P,
+                                                                                  "layout": "mixed-precision page records"},
+                 us, mn, nbytes, peak, pk, us_per_8bit_byte_count=round(us * 264 / 200, 2))
+            del buf, kv
+
+
 def bench_paged_stream(t, dev, g, peak, pk):
     """One sequence over a paged FP8 cache the way a model runs it: launches back to back over eight layers' caches
     (1.1 GB per cycle at 64K, so no launch finds its input in L2), CUDA events around 25 cycles.  The isolated-call
@@ -257,7 +281,7 @@ def bench_quest(t, dev, g, peak, pk):
          us, mn, nbytes, peak, pk)
 
 
-ALL = {"dense": bench_dense, "paged": bench_paged, "paged_stream": bench_paged_stream, "ragged": bench_ragged, "token": bench_token, "block": bench_block, "evict": bench_evict,
+ALL = {"dense": bench_dense, "paged": bench_paged, "mixed": bench_mixed, "paged_stream": bench_paged_stream, "ragged": bench_ragged, "token": bench_token, "block": bench_block, "evict": bench_evict,
        "quest": bench_quest}
 
 

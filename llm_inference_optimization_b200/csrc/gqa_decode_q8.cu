@@ -55,6 +55,15 @@ constexpr float P_BOOST = 64.f;
 constexpr int Q8_SEPARATE16 = 0, Q8_SEPARATE64 = 1, Q8_FUSED = 2;
 constexpr int RECORD_ROWS = 33;                            // 16 K rows, 16 V rows, 1 row of 16 + 16 fp32 scales
 constexpr int RECORD_BYTES = RECORD_ROWS * Q8_D;           // 4224
+// Mixed-precision page records: K in 8 bits, V in 4 (two channels per byte, 64 bytes per token, two tokens per
+// 128-byte row): 16 K rows, 8 V rows, 1 row of scales.  A stage of four such records is padded to a multiple of
+// 1 KB so that every stage starts at the same phase of the 128-byte swizzle.
+constexpr int V4_RECORD_ROWS = 25;
+constexpr int V4_RECORD_BYTES = V4_RECORD_ROWS * Q8_D;     // 3200
+constexpr int V4_STAGE_BYTES = 13 * 1024;                  // 4 * 3200 = 12800, padded
+// A 4-bit V code is stored as u = q + 8 (q in -7..7); 0x6400 | u is the fp16 number q + 1032, and the 1032 is taken
+// out of the accumulators like the INT8 bias (see cvt_quad_k).
+constexpr float V4_BIAS = 1032.f;
 // Consumer groups of four warps; group g takes the stages with it % groups == g.  The ring depth must be a
 // multiple of the group count so that a stage always belongs to the same group: a group that could reach a
 // stage two uses ahead of another group's wait would pass a parity wait meant for the use before.  Two groups
@@ -91,9 +100,9 @@ struct Q8Params {
     PoolMapPos pos;
 };
 
-template <int NG>
+template <int NG, bool V4 = false>
 static size_t q8_smem_bytes(int stages) {
-    size_t ring = (size_t)stages * Q8_STAGE_BYTES;
+    size_t ring = (size_t)stages * (V4 ? V4_STAGE_BYTES : Q8_STAGE_BYTES);
     size_t merge = merge_smem_bytes<Q8_D, NG * CONSUMER_WARPS>();
     return 1024 + (ring > merge ? ring : merge) + 2 * stages * 8 + 16;
 }
@@ -127,6 +136,13 @@ __device__ __forceinline__ void cvt_quad(uint32_t v, uint32_t& lo, uint32_t& hi)
 // shuffle of the transposed V tile ([c0, c2 | c1, c3] of the register).
 constexpr float INT8_BIAS = 1152.f;
 
+// (a & b) | c in one LOP3
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 template <int KVT>
 __device__ __forceinline__ void cvt_quad_k(uint32_t v, uint32_t& lo, uint32_t& hi) {
     if (KVT == SKV_KV_E4M3) {
@@ -157,11 +173,15 @@ __device__ __forceinline__ void pool_tile_load(uint32_t dst, const CUtensorMap* 
     tma_load_4d(dst, tm, bar, c[0], c[1], c[2], c[3], policy);
 }
 
-template <int KVT, int NT, int NG>
+template <int KVT, int NT, int NG, bool V4 = false>
 __global__ void __launch_bounds__(q8_threads(NG), NG == 1 ? 2 : 1)
 gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const Q8Params p) {
     constexpr int D = Q8_D;
+    constexpr int STAGE_BYTES = V4 ? V4_STAGE_BYTES : Q8_STAGE_BYTES;     // V4: fused records only
+    constexpr int REC_BYTES = V4 ? V4_RECORD_BYTES : RECORD_BYTES;
+    constexpr bool V_BIASED = V4 || KVT != SKV_KV_E4M3;                   // V operand carries an additive bias
+    constexpr float V_BIAS = V4 ? V4_BIAS : INT8_BIAS;
     constexpr int Q8_GROUPS = NG;
     constexpr int Q8_WARPS = Q8_GROUPS * CONSUMER_WARPS;
     constexpr int Q8_CONSUMER_THREADS = Q8_WARPS * 32;
@@ -193,7 +213,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t ring = smem_u32(smem);
-    size_t body = (size_t)p.stages * Q8_STAGE_BYTES;
+    size_t body = (size_t)p.stages * STAGE_BYTES;
     if (merge_smem_bytes<D, Q8_WARPS>() > body) body = merge_smem_bytes<D, Q8_WARPS>();
     const uint32_t full_bar = ring + (uint32_t)body;
     const uint32_t empty_bar = full_bar + p.stages * 8;
@@ -227,7 +247,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         const int P = p.page_size;
         const bool big = p.mode == Q8_SEPARATE64;
         const int tok_off = big ? 0 : pw * CHUNK;                 // first token of this warp's share inside a stage
-        const uint32_t my_tx = p.mode == Q8_FUSED ? (uint32_t)RECORD_BYTES
+        const uint32_t my_tx = p.mode == Q8_FUSED ? (uint32_t)REC_BYTES
                              : big ? (pw < 2 ? (uint32_t)(TILE * D) : (uint32_t)(TILE * 4))
                                    : (uint32_t)(2 * CHUNK * D + 2 * CHUNK * 4);
         int s = 0;
@@ -259,10 +279,10 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                         mbar_arrive(bar);                         // nothing of this warp's share lies inside the sequence
                     } else {
                         mbar_expect_tx(bar, my_tx);
-                        const uint32_t kdst = ring + s * Q8_STAGE_BYTES;
+                        const uint32_t kdst = ring + s * STAGE_BYTES;
                         const long long so = (long long)pg * p.sc_sp + (long long)h * p.sc_sh + sl;
                         if (p.mode == Q8_FUSED) {
-                            pool_tile_load(kdst + pw * RECORD_BYTES, &tmK, bar, p.pos, 0, h, pg, policy);
+                            pool_tile_load(kdst + pw * REC_BYTES, &tmK, bar, p.pos, 0, h, pg, policy);
                         } else if (big) {
                             if (pw == 0) pool_tile_load(kdst, &tmK, bar, p.pos, sl, h, pg, policy);
                             else if (pw == 1) pool_tile_load(kdst + Q8_CODE_BYTES, &tmV, bar, p.pos, sl, h, pg, policy);
@@ -350,9 +370,9 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     // Byte offsets inside a stage of this warp's 16 K rows, 16 V rows and 16 + 16 scales, and the swizzle
     // phase of its first row (rows are 128 bytes; TMA XORs the 16-byte chunk index with the row index mod 8).
     const bool fused = p.mode == Q8_FUSED;
-    const uint32_t k_off = fused ? wc * RECORD_BYTES : wtok * D;
-    const uint32_t v_off = fused ? wc * RECORD_BYTES + 16 * D : Q8_CODE_BYTES + wtok * D;
-    const uint32_t ks_off = fused ? wc * RECORD_BYTES + 32 * D : 2 * Q8_CODE_BYTES + wtok * 4;
+    const uint32_t k_off = fused ? wc * REC_BYTES : wtok * D;
+    const uint32_t v_off = fused ? wc * REC_BYTES + 16 * D : Q8_CODE_BYTES + wtok * D;
+    const uint32_t ks_off = fused ? wc * REC_BYTES + (V4 ? 24 : 32) * D : 2 * Q8_CODE_BYTES + wtok * 4;
     const uint32_t vs_off = fused ? ks_off + 64 : ks_off + 256;
     const int sc_phase = fused ? wc : 0;                  // the scale row of a record is swizzled too
     const uint32_t sw = (uint32_t)((r8 + (fused ? wc : 0)) & 7);
@@ -360,6 +380,12 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     // (tokens 0-7, chunk c+1), (tokens 8-15, chunk c+1)
     const uint32_t ld_row_off = (uint32_t)(((lj & 1) * 8 + r8) * 128);
     const uint32_t ld_ch = (uint32_t)(lj >> 1);
+    // 4-bit V rows hold two tokens (64 bytes each): the lane's token (lj & 1) * 8 + r8 sits in row token / 2 at chunk
+    // (token & 1) * 4 + (32-channel chunk), swizzled with that row's phase
+    const int v4_tok = (lj & 1) * 8 + r8;
+    const uint32_t v4_row_off = (uint32_t)((v4_tok >> 1) * 128);
+    const uint32_t v4ch = (uint32_t)((v4_tok & 1) * 4 + (lj >> 1));
+    const uint32_t v4sw = (uint32_t)(((v4_tok >> 1) + wc) & 7);
     // scales of this lane's two tokens (rows g and g+8 of the warp's 16)
     const uint32_t sc_off0 = (uint32_t)(((((g) >> 2) ^ sc_phase) << 4) + (g & 3) * 4);
     const uint32_t sc_off1 = (uint32_t)(((((g + 8) >> 2) ^ sc_phase) << 4) + (g & 3) * 4);
@@ -376,16 +402,17 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         if (it == group) SKV_PHASE(3);
         const int tok0 = t_begin + it * TILE + wtok;
         if (tok0 < t_end) {
-            const uint32_t kbase = ring + s * Q8_STAGE_BYTES + k_off + ld_row_off;   // this lane's K row
-            const uint32_t vbase = ring + s * Q8_STAGE_BYTES + v_off + ld_row_off;   // this lane's V row
-            const uint8_t* stage = smem + (size_t)s * Q8_STAGE_BYTES;
+            const uint32_t kbase = ring + s * STAGE_BYTES + k_off + ld_row_off;   // this lane's K row
+            const uint32_t vbase = ring + s * STAGE_BYTES + v_off + ld_row_off;   // this lane's V row
+            const uint32_t v4base = ring + s * STAGE_BYTES + v_off + v4_row_off;  // this lane's row of 4-bit V codes
+            const uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
             const bool ragged = tok0 + 16 > t_end;
-            if (ragged) {
+            if (ragged && !V4) {   // (4-bit codes are integers: a stale row times a zero weight is zero)
                 // rows past the end hold stale bytes (possibly NaN codes): zero them in V
                 for (int idx = lane; idx < 16 * 8; idx += 32) {
                     const int r = idx >> 3, c = idx & 7;
                     if (tok0 + r >= t_end)
-                        *reinterpret_cast<uint4*>(smem + (size_t)s * Q8_STAGE_BYTES + v_off + (size_t)r * 128 +
+                        *reinterpret_cast<uint4*>(smem + (size_t)s * STAGE_BYTES + v_off + (size_t)r * 128 +
                                                   (size_t)c * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 __syncwarp();
@@ -452,7 +479,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                         o[nt][c][0] *= c0; o[nt][c][1] *= c1;
                         o[nt][c][2] *= c0; o[nt][c][3] *= c1;
                     }
-                    if (KVT != SKV_KV_E4M3) {
+                    if (V_BIASED) {
                         psum[nt][0] *= c0; psum[nt][1] *= c1;
                         psum[nt][2] *= c0; psum[nt][3] *= c1;
                     }
@@ -476,6 +503,39 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             // O^T += V^T P^T.  A transposed 8x8 b16 matrix hands lane (g, tq) the bytes
             // [v(t0,2g), v(t0,2g+1), v(t0+1,2g), v(t0+1,2g+1)], t0 = 2tq, of a 16-byte chunk: after the byte
             // shuffle the even channel 2g of both tokens is row g and the odd channel 2g+1 row g+8 of the M tile.
+            if (V4) {
+                // A transposed 8x8 b16 matrix of 4-bit codes hands lane (g, tq) the 16-bit words of tokens 2tq and
+                // 2tq+1 that hold channels 4g..4g+3 of a 32-channel chunk: nibble i of both words, put into the
+                // mantissa of 1024, is the A register (channel 4g+i, tokens 2tq | 2tq+1).  Rows g / g+8 of the M tile
+                // are channels 4g, 4g+1 for accumulator 2c and 4g+2, 4g+3 for accumulator 2c+1 of chunk c.
+#pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    uint32_t r[4];   // (tokens 0-7, chunk 2m), (tokens 8-15, chunk 2m), (0-7, 2m+1), (8-15, 2m+1)
+                    ldsm_x4_t(v4base + ((v4ch + (uint32_t)(2 * m)) ^ v4sw) * 16, r[0], r[1], r[2], r[3]);
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const uint32_t lo = r[2 * cc], hi = r[2 * cc + 1];   // tokens 0-7 | 8-15 of chunk 2m + cc
+                        // nibbles 0 and 2 go into mantissa bits 0-3 (the number u + 1024), nibbles 1 and 3 stay in bits
+                        // 4-7 (the number 16 u + 1024): no shift per nibble, and the factor 16 of the odd channels
+                        // (rows g+8 of the M tile) is divided out of the accumulators at the end
+                        const uint32_t lo8 = __byte_perm(lo, 0u, 0x4341), hi8 = __byte_perm(hi, 0u, 0x4341);   // >> 8 of both halves
+                        uint32_t a0[4], a1[4];
+                        a0[0] = and_or(lo, 0x000F000Fu, 0x64006400u);
+                        a0[1] = and_or(lo, 0x00F000F0u, 0x64006400u);
+                        a1[0] = and_or(lo8, 0x000F000Fu, 0x64006400u);
+                        a1[1] = and_or(lo8, 0x00F000F0u, 0x64006400u);
+                        a0[2] = and_or(hi, 0x000F000Fu, 0x64006400u);
+                        a0[3] = and_or(hi, 0x00F000F0u, 0x64006400u);
+                        a1[2] = and_or(hi8, 0x000F000Fu, 0x64006400u);
+                        a1[3] = and_or(hi8, 0x00F000F0u, 0x64006400u);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            mma_f16(o[nt][2 * (2 * m + cc)], a0, pb[nt][0], pb[nt][1]);
+                            mma_f16(o[nt][2 * (2 * m + cc) + 1], a1, pb[nt][0], pb[nt][1]);
+                        }
+                    }
+                }
+            } else {
 #pragma unroll
             for (int m = 0; m < NCH / 2; ++m) {
                 uint32_t r0, r1, r2, r3;
@@ -491,7 +551,8 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                     mma_f16(o[nt][2 * m + 1], a1, pb[nt][0], pb[nt][1]);
                 }
             }
-            if (KVT != SKV_KV_E4M3) {   // sum_t p_t on the same path as O: a tile of ones in V's place
+            }
+            if (V_BIASED) {   // sum_t p_t on the same path as O: a tile of ones in V's place
                 const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) mma_f16(psum[nt], ones, pb[nt][0], pb[nt][1]);
@@ -502,13 +563,23 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     }
 
     SKV_PHASE(4);
-    if (KVT != SKV_KV_E4M3) {   // take the codes' bias out of O
+    if (V4) {   // rows g hold u + 1024 = q + 1032, rows g+8 hold 16 u + 1024 = 16 (q + 72)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int c = 0; c < NCH; ++c)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) o[nt][c][j] -= INT8_BIAS * psum[nt][j];
+                for (int j = 0; j < 2; ++j) {
+                    o[nt][c][j] -= V4_BIAS * psum[nt][j];
+                    o[nt][c][j + 2] = (o[nt][c][j + 2] - (1024.f + 16.f * 8.f) * psum[nt][j + 2]) * 0.0625f;
+                }
+    } else if (V_BIASED) {   // take the codes' bias out of O
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int c = 0; c < NCH; ++c)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o[nt][c][j] -= V_BIAS * psum[nt][j];
     }
     // the running sums are per lane (its two token rows): total over the 8 lanes g
 #pragma unroll
@@ -533,8 +604,10 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 const int head = nt * 8 + tq * 2 + j;
                 if (head < G) {
 #pragma unroll
-                    for (int c = 0; c < NCH; ++c)
-                        *reinterpret_cast<float2*>(my + head * D + c * 16 + g * 2) = make_float2(o[nt][c][j], o[nt][c][j + 2]);
+                    for (int c = 0; c < NCH; ++c) {
+                        const int ch = V4 ? (c >> 1) * 32 + g * 4 + (c & 1) * 2 : c * 16 + g * 2;
+                        *reinterpret_cast<float2*>(my + head * D + ch) = make_float2(o[nt][c][j], o[nt][c][j + 2]);
+                    }
                     if (g == 0) { mm[warp * MAX_GROUP + head] = mrun[nt][j]; ml[warp * MAX_GROUP + head] = lrun[nt][j]; }
                 }
             }
@@ -549,18 +622,18 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     SKV_PHASE(6);
 }
 
-template <int KVT, int NT, int NG>
+template <int KVT, int NT, int NG, bool V4 = false>
 static int launch_q8(const CUtensorMap& tmK, const CUtensorMap& tmV, const Q8Params& p, int B, cudaStream_t stream) {
     static int configured_smem[64] = {0};
-    const size_t smem = q8_smem_bytes<NG>(p.stages);
+    const size_t smem = q8_smem_bytes<NG, V4>(p.stages);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && configured_smem[dev] < (int)smem) {
-        SKV_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_q8_kernel<KVT, NT, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        SKV_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_q8_kernel<KVT, NT, NG, V4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured_smem[dev] = (int)smem;
     }
     const dim3 grid = p.list_items > 0 ? dim3(p.Hkv, p.list_items, 1) : dim3(p.Hkv, p.num_splits, B);
-    SKV_CUDA_TRY(launch_pdl(gqa_decode_q8_kernel<KVT, NT, NG>, grid, dim3(q8_threads(NG)), smem, stream, tmK, tmV, p));
+    SKV_CUDA_TRY(launch_pdl(gqa_decode_q8_kernel<KVT, NT, NG, V4>, grid, dim3(q8_threads(NG)), smem, stream, tmK, tmV, p));
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }
@@ -609,7 +682,8 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
                          long long pool_stride_head, long long pool_stride_slot, long long scale_stride_page,
                          long long scale_stride_head, float scale, int device, void* stream) {
     const int out_bf16 = (kv_dtype & SKV_OUT_BF16) ? 1 : 0;
-    kv_dtype &= ~SKV_OUT_BF16;
+    const bool v4 = (kv_dtype & SKV_V_INT4) != 0;
+    kv_dtype &= ~(SKV_OUT_BF16 | SKV_V_INT4);
     if (!q || !k_pool || !v_pool || !k_scale_pool || !v_scale_pool || !out)
         return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode_paged: null tensor pointer");
     if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || num_pages <= 0 || max_pages <= 0)
@@ -655,10 +729,28 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     else if (page_size % gqa::TILE == 0)
         mode = gqa::Q8_SEPARATE64;
 
+    if (v4) {
+        // K in 8 bits, V in 4: only as mixed-precision page records, [num_pages, Hkv, 25, 128] bytes
+        if (G > 8) return fail(SKV_ERR_UNSUPPORTED, "4-bit V pages serve up to 8 query heads per kv-head (got %d)", G);
+        if (!(page_size == gqa::CHUNK && static_cast<const uint8_t*>(v_pool) == kb + 16 * D &&
+              reinterpret_cast<const uint8_t*>(k_scale_pool) == kb + 24 * D &&
+              reinterpret_cast<const uint8_t*>(v_scale_pool) == kb + 24 * D + 64 && pool_stride_slot == D &&
+              pool_stride_head == gqa::V4_RECORD_BYTES && pool_stride_page == (long long)Hkv * gqa::V4_RECORD_BYTES &&
+              scale_stride_head * 4 == pool_stride_head && scale_stride_page * 4 == pool_stride_page))
+            return fail(SKV_ERR_UNSUPPORTED, "SKV_V_INT4 needs the four pools to be views of one [num_pages, Hkv, 25, 128]-byte "
+                                             "buffer of mixed-precision page records (16-token pages)");
+        mode = gqa::Q8_FUSED;
+    }
+
     CUtensorMap tmK, tmV;
     PoolMapPos pos, pos2;
     int rc;
-    if (mode == gqa::Q8_FUSED) {
+    if (v4) {
+        rc = make_pool_tmap(&tmK, &pos, k_pool, D, num_pages, Hkv, gqa::V4_RECORD_ROWS, pool_stride_page, pool_stride_head,
+                            pool_stride_slot, gqa::V4_RECORD_ROWS);
+        if (rc) return rc;
+        tmV = tmK;
+    } else if (mode == gqa::Q8_FUSED) {
         rc = make_pool_tmap(&tmK, &pos, k_pool, D, num_pages, Hkv, gqa::RECORD_ROWS, pool_stride_page, pool_stride_head,
                             pool_stride_slot, gqa::RECORD_ROWS);
         if (rc) return rc;
@@ -712,6 +804,13 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     p.scale_log2 = scale * 1.4426950408889634f;
     p.pos = pos;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (v4) {
+        if (slots == 2)
+            return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3, 1, 1, true>(tmK, tmV, p, B, st)
+                                           : gqa::launch_q8<SKV_KV_I8, 1, 1, true>(tmK, tmV, p, B, st);
+        return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3, 1, 2, true>(tmK, tmV, p, B, st)
+                                       : gqa::launch_q8<SKV_KV_I8, 1, 2, true>(tmK, tmV, p, B, st);
+    }
     if (slots == 2)
         return kv_dtype == SKV_KV_E4M3 ? gqa::launch_q8<SKV_KV_E4M3, 1, 1>(tmK, tmV, p, B, st)
                                        : gqa::launch_q8<SKV_KV_I8, 1, 1>(tmK, tmV, p, B, st);

@@ -6,7 +6,8 @@
 //
 // qkv : [B, (Hq + 2 Hkv) * D] bf16 or fp16, the output of the fused q/k/v projection (q heads, then k, then v)
 // q_out : [B, Hq, D] fp16, rotated query for the decode kernel
-// pools : as for skv_gqa_decode_paged (separate or fused page records; addressed through strides)
+// pools : as for skv_gqa_decode_paged (separate or fused page records; addressed through strides); with SKV_V_INT4
+//         the value row is quantised to 4 bits (scale = amax / 7) and packed two channels per byte
 // One warp per (b, head): D = 128 -> 4 channels per lane; rotate-half pairs channel d with d + D/2.
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -28,6 +29,7 @@ struct Params {
     const int* seq_lens;                  // [B]: position the new token takes
     long long sp, sh, ss, csp, csh;
     int B, Hq, Hkv, page_size, max_pages, num_pages, kv_dtype;
+    int v4;                               // V rows are stored as 4-bit codes, 64 bytes per token (mixed-precision pages)
     int* status;                          // optional device status word (SKV_DEV_BAD_PAGE)
     float log2_theta;
     __half* meta;                         // optional [B, Hkv, nb, 2, D] min/max block metadata to keep current
@@ -84,14 +86,17 @@ rope_quant_append_kernel(const Params p) {
     const int h = is_v ? hh - p.Hq - p.Hkv : hh - p.Hq;
     float amax = fmaxf(fmaxf(fabsf(lo0), fabsf(lo1)), fmaxf(fabsf(hi0), fabsf(hi1)));
     amax = warp_max(amax);
-    const float qmax = p.kv_dtype == SKV_KV_E4M3 ? 448.f : 127.f;
+    const bool v4 = is_v && p.v4;
+    const float qmax = v4 ? 7.f : p.kv_dtype == SKV_KV_E4M3 ? 448.f : 127.f;
     const float scale = amax > 0.f ? __fdiv_rn(amax, qmax) : 1.f;
     const float x[4] = {lo0, lo1, hi0, hi1};
     uint32_t code[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float y = __fdiv_rn(x[i], scale);
-        if (p.kv_dtype == SKV_KV_E4M3)
+        if (v4)
+            code[i] = (uint32_t)(max(-7, min(7, __float2int_rn(y))) + 8);
+        else if (p.kv_dtype == SKV_KV_E4M3)
             code[i] = (uint32_t)__nv_cvt_float_to_fp8(fminf(fmaxf(y, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3);
         else
             code[i] = (uint32_t)max(-127, min(127, __float2int_rn(y))) & 0xFFu;
@@ -103,9 +108,15 @@ rope_quant_append_kernel(const Params p) {
         if (lane == 0 && p.status) atomicOr(p.status, SKV_DEV_BAD_PAGE);
         return;
     }
-    uint8_t* row = (is_v ? p.v_codes : p.k_codes) + SKV_INDEX(page, p.num_pages) * p.sp + h * p.sh + SKV_INDEX(slot, p.page_size) * p.ss;
-    *reinterpret_cast<uint16_t*>(row + lane * 2) = (uint16_t)(code[0] | (code[1] << 8));
-    *reinterpret_cast<uint16_t*>(row + D / 2 + lane * 2) = (uint16_t)(code[2] | (code[3] << 8));
+    if (v4) {   // byte j of the 64-byte row: channel 2j in the low nibble, 2j+1 in the high one
+        uint8_t* row = p.v_codes + SKV_INDEX(page, p.num_pages) * p.sp + h * p.sh + SKV_INDEX(slot, p.page_size) * (D / 2);
+        row[lane] = (uint8_t)(code[0] | (code[1] << 4));
+        row[D / 4 + lane] = (uint8_t)(code[2] | (code[3] << 4));
+    } else {
+        uint8_t* row = (is_v ? p.v_codes : p.k_codes) + SKV_INDEX(page, p.num_pages) * p.sp + h * p.sh + SKV_INDEX(slot, p.page_size) * p.ss;
+        *reinterpret_cast<uint16_t*>(row + lane * 2) = (uint16_t)(code[0] | (code[1] << 8));
+        *reinterpret_cast<uint16_t*>(row + D / 2 + lane * 2) = (uint16_t)(code[2] | (code[3] << 8));
+    }
     if (lane == 0) (is_v ? p.v_scale : p.k_scale)[page * p.csp + h * p.csh + slot] = scale;
 
     // Keep the Quest metadata of the key's block current: min/max with the DEQUANTISED new key (code * scale),
@@ -153,6 +164,8 @@ int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || page_size <= 0 || max_pages <= 0 || num_pages <= 0)
         return fail(SKV_ERR_BAD_ARG, "skv_rope_quant_append: sizes must be positive");
     if (D != app::D) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (128)", D);
+    const int v4 = (kv_dtype & SKV_V_INT4) ? 1 : 0;   // V rows as 4-bit codes, 64 bytes per token slot
+    kv_dtype &= ~SKV_V_INT4;
     if (kv_dtype != SKV_KV_I8 && kv_dtype != SKV_KV_E4M3) return fail(SKV_ERR_UNSUPPORTED, "kv_dtype %d is not an 8-bit type", kv_dtype);
     if (!(rope_theta > 1.f)) return fail(SKV_ERR_BAD_ARG, "rope_theta must exceed 1");
     DeviceGuard guard(device);
@@ -166,6 +179,7 @@ int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k
     p.csp = scale_stride_page; p.csh = scale_stride_head;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.max_pages = max_pages; p.kv_dtype = kv_dtype;
     p.num_pages = num_pages; p.status = status;
+    p.v4 = v4;
     p.log2_theta = log2f(rope_theta);
     p.meta = static_cast<__half*>(meta);
     p.meta_block = meta_block_size > 0 ? meta_block_size : 1;

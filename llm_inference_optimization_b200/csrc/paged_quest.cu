@@ -23,6 +23,7 @@
 
 #include "skv_common.cuh"
 #include "skv_select.cuh"
+#include "skv_tmap.cuh"
 
 namespace skv {
 namespace quest {
@@ -293,74 +294,98 @@ quest_scores_kernel(const ScoreParams p, long long total_blocks, int blocks_per_
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Ring variant of the scoring kernel (opt-in, see skv_quest_set_ring_scores).  Here the metadata
-// travels by bulk asynchronous copies into a shared-memory ring, the way the dense decode kernels stream K/V: one
-// persistent CTA per SM takes a contiguous range of the flattened (b, kv-head, block) space; a producer lane issues
-// one copy per 64-block stage (32 KB) into a 6-stage ring and sixteen consumer warps score two blocks per warp step
-// out of shared memory.  In flight per SM: the ring, 192 KB.  Every wait is bounded; a wait that runs out sets
-// SKV_DEV_TIMEOUT in the status word and the CTA stops.  Measured on config 4 it is slower than the register-load
-// kernel (25 us against 21 us): with sixteen consumer warps per SM the scoring arithmetic (about 120 instructions
-// per block and lane), not the copy, is what it waits for.
+// Tensor-core variant of the scoring kernel (see skv_quest_set_ring_scores).  With lo <= hi,
+//     sum_c max(q_c lo_c, q_c hi_c) = sum_c min(q_c, 0) lo_c + sum_c max(q_c, 0) hi_c,
+// i.e. the score of a block is one dot product of its 256 stored numbers (128 minima, then 128 maxima) with the
+// 256-vector (min(q, 0) | max(q, 0)): scoring is a [blocks x 256] . [256 x heads] product, and the register-load
+// kernel's ~120 instructions per block and lane become 16 MMAs per 16 blocks.  The metadata then streams like K in
+// the dense decode kernel: one persistent CTA per SM takes a contiguous range of (row, 64-block tile) items, a
+// producer lane issues four TMA boxes per tile ([64 blocks][64 numbers], 128-byte swizzle, evict-first) into a
+// 5-stage ring, four consumer warps take 16 blocks each (ldmatrix + mma.sync.m16n8k16, blocks on the M side, up to 8
+// query heads on the N side).  A tile never spans two (b, kv-head) rows; what a box reads past the end of its row is
+// computed and not stored.  Every wait is bounded; one that runs out sets SKV_DEV_TIMEOUT and the CTA stops.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int RING_STAGE_BLOCKS = 64;
-constexpr int RING_STAGE_BYTES = RING_STAGE_BLOCKS * 2 * D * 2;   // 32 KB
-constexpr int RING_STAGES = 6;
-constexpr int RING_CONSUMER_WARPS = 16;
-constexpr int RING_THREADS = (RING_CONSUMER_WARPS + 1) * 32;
-constexpr size_t RING_SMEM = (size_t)RING_STAGES * RING_STAGE_BYTES + 2 * RING_STAGES * 8 + 1024;
+constexpr int MS_TILE = 64;                               // blocks per stage
+constexpr int MS_BOX_BYTES = MS_TILE * 128;               // one [64][64 halves] box
+constexpr int MS_STAGE_BYTES = 4 * MS_BOX_BYTES;          // 32 KB
+constexpr int MS_STAGES = 5;
+constexpr int MS_CONSUMER_WARPS = 4;
+constexpr int MS_THREADS = (MS_CONSUMER_WARPS + 1) * 32;
+constexpr size_t MS_SMEM = (size_t)MS_STAGES * MS_STAGE_BYTES + 2 * MS_STAGES * 8 + 1024;
 
-template <int MAXG>
-__global__ void __launch_bounds__(RING_THREADS, 1)
-quest_scores_ring_kernel(const ScoreParams p, long long total_blocks, long long blocks_per_cta, int* status) {
+__global__ void __launch_bounds__(MS_THREADS, 1)
+quest_scores_mma_kernel(const __grid_constant__ CUtensorMap tmM, const ScoreParams p, int tiles_per_row,
+                        long long total_items, long long items_per_cta, int* status) {
     pdl_launch_dependents();  // the kernel that consumes these results may be scheduled now; it waits for this grid to finish
-    static_assert(MAXG == 4 || MAXG == 8, "the packed reduction below is written for 4 or 8 heads");
-    extern __shared__ uint8_t ring_raw[];
-    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ uint8_t ms_raw[];
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ms_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t ring_u32 = smem_u32(ring);
-    const uint32_t full_bar = ring_u32 + RING_STAGES * RING_STAGE_BYTES, empty_bar = full_bar + RING_STAGES * 8;
+    const uint32_t full_bar = ring_u32 + MS_STAGES * MS_STAGE_BYTES, empty_bar = full_bar + MS_STAGES * 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long c0 = min(total_blocks, (long long)blockIdx.x * blocks_per_cta);
-    const long long c1 = min(total_blocks, c0 + blocks_per_cta);
-    const int nstage = (int)((c1 - c0 + RING_STAGE_BLOCKS - 1) / RING_STAGE_BLOCKS);
+    const long long i0 = min(total_items, (long long)blockIdx.x * items_per_cta);
+    const long long i1 = min(total_items, i0 + items_per_cta);
     if (threadIdx.x == 0) {
-        for (int s = 0; s < RING_STAGES; ++s) {
+        for (int s = 0; s < MS_STAGES; ++s) {
             mbar_init(full_bar + s * 8, 1);
-            mbar_init(empty_bar + s * 8, RING_CONSUMER_WARPS);
+            mbar_init(empty_bar + s * 8, MS_CONSUMER_WARPS);
         }
         fence_barrier_init();
     }
     __syncthreads();
+    int row = (int)(i0 / tiles_per_row), tile = (int)(i0 - (long long)row * tiles_per_row);
 
-    if (warp == RING_CONSUMER_WARPS) {   // producer: one lane, one bulk copy per stage
+    if (warp == MS_CONSUMER_WARPS) {   // producer: one lane, four boxes per tile
         if (lane == 0) {
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.meta) + c0 * (2 * D * 2);
+            tma_prefetch_desc(&tmM);
+            const uint64_t policy = l2_policy_evict_first();
             int s = 0;
             uint32_t ph = 0;
-            for (int i = 0; i < nstage; ++i) {
-                if (i >= RING_STAGES && !mbar_wait(empty_bar + s * 8, ph ^ 1u)) {
+            long long n = 0;
+            for (long long it = i0; it < i1; ++it, ++n) {
+                if (n >= MS_STAGES && !mbar_wait(empty_bar + s * 8, ph ^ 1u)) {
                     atomicOr(status, SKV_DEV_TIMEOUT);
                     break;
                 }
-                const long long first = (long long)i * RING_STAGE_BLOCKS;
-                const uint32_t bytes = (uint32_t)min((long long)RING_STAGE_BLOCKS, c1 - c0 - first) * (2 * D * 2);
-                mbar_expect_tx(full_bar + s * 8, bytes);
-                bulk_load(ring_u32 + s * RING_STAGE_BYTES, src + first * (2 * D * 2), bytes, full_bar + s * 8);
-                if (++s == RING_STAGES) { s = 0; ph ^= 1u; }
+                const uint32_t dst = ring_u32 + s * MS_STAGE_BYTES, bar = full_bar + s * 8;
+                mbar_expect_tx(bar, MS_STAGE_BYTES);
+                const int first = row * p.nb + tile * MS_TILE;      // first block (a row of the [blocks][256] matrix)
+#pragma unroll
+                for (int hf = 0; hf < 4; ++hf) tma_load_2d(dst + hf * MS_BOX_BYTES, &tmM, bar, hf * 64, first, policy);
+                if (++s == MS_STAGES) { s = 0; ph ^= 1u; }
+                if (++tile == tiles_per_row) { tile = 0; ++row; }
             }
         }
         return;
     }
 
-    // consumers: lanes 0..15 take block 2w, lanes 16..31 block 2w+1 of every 32-block half of a stage
-    const int sub = lane & 15, rw = lane >> 4;
-    float qh[MAXG][8];     // half the query of the row this half-warp is in
+    // consumers: warp w scores blocks 16w .. 16w+15 of every tile; lane (g, tq) ends up with blocks g and g+8 for heads
+    // 2tq and 2tq+1
+    const int g = lane >> 2, tq = lane & 3;
+    const int lj = lane >> 3, r8 = lane & 7;
+    const uint32_t a_row_off = (uint32_t)((warp * 16 + (lj & 1) * 8 + r8) * 128);   // this lane's ldmatrix row (row & 7 == r8)
+    uint32_t qb[16][2];    // B operand: k-steps 0..7 hold min(q, 0) (against the minima), 8..15 max(q, 0)
     int cur_row = -1;
     int s = 0;
     uint32_t ph = 0;
-    // (row, block-in-row) of the first block of the current stage, advanced without divisions (a 64-bit division per
-    // block costs as much as scoring the block)
-    int row0 = (int)(c0 / p.nb), j0 = (int)(c0 - (long long)row0 * p.nb);
-    for (int i = 0; i < nstage; ++i) {
+    for (long long it = i0; it < i1; ++it) {
+        if (row != cur_row) {
+            cur_row = row;
+            const __half* qrow = p.q + ((long long)row * p.G + g) * D;
+            const __half2 zero = __float2half2_rn(0.f);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                __half2 u = zero, v = zero;
+                if (g < p.G) {
+                    u = *reinterpret_cast<const __half2*>(qrow + kk * 16 + tq * 2);
+                    v = *reinterpret_cast<const __half2*>(qrow + kk * 16 + 8 + tq * 2);
+                }
+                const __half2 un = __hmin2(u, zero), vn = __hmin2(v, zero), up = __hmax2(u, zero), vp = __hmax2(v, zero);
+                qb[kk][0] = *reinterpret_cast<const uint32_t*>(&un);
+                qb[kk][1] = *reinterpret_cast<const uint32_t*>(&vn);
+                qb[kk + 8][0] = *reinterpret_cast<const uint32_t*>(&up);
+                qb[kk + 8][1] = *reinterpret_cast<const uint32_t*>(&vp);
+            }
+        }
         int ok = 1;
         if (lane == 0) ok = mbar_wait(full_bar + s * 8, ph) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -368,89 +393,34 @@ quest_scores_ring_kernel(const ScoreParams p, long long total_blocks, long long 
             if (lane == 0) atomicOr(status, SKV_DEV_TIMEOUT);
             return;
         }
-        const long long stage_first = c0 + (long long)i * RING_STAGE_BLOCKS;
-        const int nblk = (int)min((long long)RING_STAGE_BLOCKS, c1 - stage_first);
-        const uint8_t* st = ring + s * RING_STAGE_BYTES;
+        const uint32_t base = ring_u32 + s * MS_STAGE_BYTES + a_row_off;
+        float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};   // even / odd k-steps: half the dependent chain
 #pragma unroll
-        for (int half = 0; half < RING_STAGE_BLOCKS / (2 * RING_CONSUMER_WARPS); ++half) {
-            const int blk = half * 2 * RING_CONSUMER_WARPS + warp * 2 + rw;
-            const bool live = blk < nblk;
-            const int bc = live ? blk : 0;            // out-of-range half-warps recompute block 0; their store is dropped
-            int row = row0, j = j0 + bc;              // (b, kv-head) and block inside it
-            while (j >= p.nb) { j -= p.nb; ++row; }
-            if (row != cur_row) {                     // rare: a range crosses into the next (b, kv-head)
-                cur_row = row;
-#pragma unroll
-                for (int gq = 0; gq < MAXG; ++gq) {
-                    float q[8];
-                    if (gq < p.G) unpack8(*reinterpret_cast<const uint4*>(p.q + ((long long)row * p.G + gq) * D + sub * 8), q);
-                    else
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) q[e] = 0.f;
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) qh[gq][e] = 0.5f * q[e];
-                }
-            }
-            const uint4 lo4 = *reinterpret_cast<const uint4*>(st + bc * (2 * D * 2) + sub * 16);
-            const uint4 hi4 = *reinterpret_cast<const uint4*>(st + bc * (2 * D * 2) + D * 2 + sub * 16);
-            float lo[8], hi[8], acc[MAXG];
-            unpack8(lo4, lo);
-            unpack8(hi4, hi);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const float sm = hi[e] + lo[e], df = hi[e] - lo[e];
-                lo[e] = sm;   // hi + lo
-                hi[e] = df;   // hi - lo >= 0
-            }
-#pragma unroll
-            for (int gq = 0; gq < MAXG; ++gq) {
-                acc[gq] = 0.f;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc[gq] = fmaf(qh[gq][e], lo[e], fmaf(fabsf(qh[gq][e]), hi[e], acc[gq]));
-            }
-            int head = 0;  // which head this lane ends up holding (same packed reduction as the kernel above)
-            float v4[4];
-            if (MAXG == 8) {
-                const bool up = sub & 8;
-#pragma unroll
-                for (int gq = 0; gq < 4; ++gq) {
-                    const float keep = up ? acc[gq + 4] : acc[gq], send = up ? acc[gq] : acc[gq + 4];
-                    v4[gq] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-                }
-                head = up ? 4 : 0;
-            } else {
-#pragma unroll
-                for (int gq = 0; gq < 4; ++gq) v4[gq] = acc[gq] + __shfl_xor_sync(0xffffffffu, acc[gq], 8);
-            }
-            float v2[2];
-            {
-                const bool up = sub & 4;
-#pragma unroll
-                for (int gq = 0; gq < 2; ++gq) {
-                    const float keep = up ? v4[gq + 2] : v4[gq], send = up ? v4[gq] : v4[gq + 2];
-                    v2[gq] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-                }
-                head += up ? 2 : 0;
-            }
-            float v1;
-            {
-                const bool up = sub & 2;
-                const float keep = up ? v2[1] : v2[0], send = up ? v2[0] : v2[1];
-                v1 = keep + __shfl_xor_sync(0xffffffffu, send, 2);
-                head += up ? 1 : 0;
-            }
-            v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
-            if (live && (sub & 1) == 0 && head < p.G) p.scores[((long long)row * p.G + head) * p.nb + j] = v1 * p.scale;
+        for (int kk = 0; kk < 16; ++kk) {
+            const int c = 2 * kk + (lj >> 1);        // 16-byte chunk of the block's 512 bytes
+            uint32_t a[4];
+            ldsm_x4(base + (uint32_t)(c >> 3) * MS_BOX_BYTES + (uint32_t)(((c & 7) ^ r8) << 4), a[0], a[1], a[2], a[3]);
+            if (kk & 1) mma_f16(acc1, a, qb[kk][0], qb[kk][1]);
+            else mma_f16(acc0, a, qb[kk][0], qb[kk][1]);
+        }
+        const int j = tile * MS_TILE + warp * 16 + g;
+        float* dst = p.scores + ((long long)row * p.G + tq * 2) * p.nb + j;
+        if (tq * 2 < p.G) {
+            if (j < p.nb) dst[0] = (acc0[0] + acc1[0]) * p.scale;
+            if (j + 8 < p.nb) dst[8] = (acc0[2] + acc1[2]) * p.scale;
+        }
+        if (tq * 2 + 1 < p.G) {
+            if (j < p.nb) dst[p.nb] = (acc0[1] + acc1[1]) * p.scale;
+            if (j + 8 < p.nb) dst[p.nb + 8] = (acc0[3] + acc1[3]) * p.scale;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar + s * 8);
-        if (++s == RING_STAGES) { s = 0; ph ^= 1u; }
-        j0 += RING_STAGE_BLOCKS;
-        while (j0 >= p.nb) { j0 -= p.nb; ++row0; }
+        if (++s == MS_STAGES) { s = 0; ph ^= 1u; }
+        if (++tile == tiles_per_row) { tile = 0; ++row; }
     }
 }
 
-inline int& ring_scores_flag() { static int on = 0; return on; }   // the register-load kernel measures faster on B200
+inline int& ring_scores_flag() { static int on = 1; return on; }   // tensor-core scoring: config 4 end to end 46 -> 40 us
 inline bool use_ring_scores() { return ring_scores_flag() != 0; }
 
 template <int MAXG, int U>
@@ -688,8 +658,10 @@ int skv_debug_phase_ts_quest(unsigned long long* out) {
 }
 #endif
 
-// 1: the block scores are computed by the shared-memory ring kernel (bulk asynchronous copies); 0 (default): by the
-// register-load kernel, which measures faster (config 4: 21 us against 25 us).  Same arithmetic, same results.
+// 1 (default): the block scores are computed by the tensor-core kernel that streams the metadata through a
+// shared-memory ring (up to 8 query heads per kv-head; larger groups always use the other kernel); 0: by the
+// register-load kernel.  The two sum the same exact products in different
+// orders (fp32), so scores agree to rounding.
 int skv_quest_set_ring_scores(int on) {
     quest::ring_scores_flag() = on ? 1 : 0;
     return SKV_OK;
@@ -777,21 +749,23 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
     sp.Hq = Hq; sp.Hkv = Hkv; sp.G = G; sp.nb = nb; sp.scale = scale;
     const long long rows = (long long)B * Hkv;
     const long long total_blocks = rows * nb;
-    if (quest::use_ring_scores()) {
-        // one persistent CTA per SM, each a contiguous range of the flattened block space, streamed through shared memory
-        static bool ring_configured[64] = {false};
-        if (device < 64 && !ring_configured[device]) {
-            SKV_CUDA_TRY(cudaFuncSetAttribute(quest::quest_scores_ring_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)quest::RING_SMEM));
-            SKV_CUDA_TRY(cudaFuncSetAttribute(quest::quest_scores_ring_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)quest::RING_SMEM));
-            ring_configured[device] = true;
+    if (quest::use_ring_scores() && G <= 8) {
+        // tensor-core scoring: one persistent CTA per SM, each a contiguous range of (row, 64-block tile) items
+        static bool ms_configured[64] = {false};
+        if (device < 64 && !ms_configured[device]) {
+            SKV_CUDA_TRY(cudaFuncSetAttribute(quest::quest_scores_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)quest::MS_SMEM));
+            ms_configured[device] = true;
         }
+        CUtensorMap tmM;
+        const int mrc = make_matrix_tmap(&tmM, meta, total_blocks, 2 * quest::D, 2 * quest::D, quest::MS_TILE, 64, false);
+        if (mrc) return mrc;
+        const int tiles_per_row = (nb + quest::MS_TILE - 1) / quest::MS_TILE;
+        const long long total_items = rows * tiles_per_row;
         int ctas = sm_count(device);
-        long long per = (total_blocks + ctas - 1) / ctas;
-        if (per < quest::RING_STAGE_BLOCKS) per = quest::RING_STAGE_BLOCKS;   // short problems: fewer CTAs, whole stages
-        ctas = (int)((total_blocks + per - 1) / per);
+        const long long per = (total_items + ctas - 1) / ctas;
+        ctas = (int)((total_items + per - 1) / per);
         int* st_word = reinterpret_cast<int*>(workspace);
-        if (G <= 4) quest::quest_scores_ring_kernel<4><<<ctas, quest::RING_THREADS, quest::RING_SMEM, st>>>(sp, total_blocks, per, st_word);
-        else quest::quest_scores_ring_kernel<8><<<ctas, quest::RING_THREADS, quest::RING_SMEM, st>>>(sp, total_blocks, per, st_word);
+        quest::quest_scores_mma_kernel<<<ctas, quest::MS_THREADS, quest::MS_SMEM, st>>>(tmM, sp, tiles_per_row, total_items, per, st_word);
         SKV_CUDA_TRY(cudaGetLastError());
     } else {
     // One wave of two CTAs per SM; every warp takes blocks_per_warp consecutive blocks of the flattened space.  U (loads

@@ -75,12 +75,25 @@ def quantize_rows_e4m3(x: Tensor):
     return (xf / scale[..., None]).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn), scale
 
 
-class LayerCache:
-    """Paged FP8 cache of one layer on one rank (fused page records, page size 16)."""
+def quantize_rows_int4(x: Tensor):
+    """Packed 4-bit codes (nibble = code + 8, even channel low) and fp32 scales = amax / 7 of ``x [..., D]``."""
+    xf = x.float()
+    amax = xf.abs().amax(dim=-1)
+    scale = torch.where(amax > 0, amax / 7.0, torch.ones_like(amax))
+    u = (torch.round(xf / scale[..., None]).clamp_(-7.0, 7.0) + 8).to(torch.uint8)
+    return (u[..., 0::2] | (u[..., 1::2] << 4)).contiguous(), scale
 
-    def __init__(self, num_pages: int, n_kv: int, device):
-        self.buf = torch.zeros((num_pages, n_kv, paged.RECORD_ROWS, 128), dtype=torch.uint8, device=device)
-        self.k, self.v, self.ks, self.vs = paged.fused_views(self.buf, torch.float8_e4m3fn)
+
+class LayerCache:
+    """Paged cache of one layer on one rank, page size 16: fused FP8 page records, or with ``v_bits=4`` mixed-precision
+    records (FP8 keys, 4-bit values)."""
+
+    def __init__(self, num_pages: int, n_kv: int, device, v_bits: int = 8):
+        self.v_bits = v_bits
+        rows = paged.MIXED_RECORD_ROWS if v_bits == 4 else paged.RECORD_ROWS
+        self.buf = torch.zeros((num_pages, n_kv, rows, 128), dtype=torch.uint8, device=device)
+        views = paged.mixed_views if v_bits == 4 else paged.fused_views
+        self.k, self.v, self.ks, self.vs = views(self.buf, torch.float8_e4m3fn)
 
     def append(self, k: Tensor, v: Tensor, page_table: Tensor, seq_lens: Tensor) -> None:
         """Quantise the new token's ``k, v [B, n_kv, D]`` and store them at position ``seq_lens[b]``."""
@@ -89,7 +102,7 @@ class LayerCache:
         page = page_table[torch.arange(B, device=k.device), lens // 16].long()
         slot = lens % 16
         kc, ksc = quantize_rows_e4m3(k)
-        vc, vsc = quantize_rows_e4m3(v)
+        vc, vsc = quantize_rows_int4(v) if self.v_bits == 4 else quantize_rows_e4m3(v)
         self.k.view(torch.uint8)[page, :, slot] = kc.view(torch.uint8)
         self.v.view(torch.uint8)[page, :, slot] = vc.view(torch.uint8)
         self.ks[page, :, slot] = ksc
@@ -104,7 +117,7 @@ def kernel_attention(q: Tensor, cache: LayerCache, page_table: Tensor, seq_lens:
     """The product path: paged FP8 decode attention on the sm_100a kernel (fp16 query in, fp16 out)."""
     from . import _C
     return _C.fused_gqa_paged(q.to(torch.float16).contiguous(), cache.k, cache.v, cache.ks, cache.vs, page_table,
-                              seq_lens, scale, max_seq_len=max_seq_len)
+                              seq_lens, scale, max_seq_len=max_seq_len, v_bits=cache.v_bits)
 
 
 class DecodeModel:
@@ -112,7 +125,7 @@ class DecodeModel:
 
     def __init__(self, cfg: ModelConfig, shard: HeadShard, device, *, seed: int = 4, dtype=torch.bfloat16,
                  attention: AttentionFn = kernel_attention, group=None, layer_modes: list[str] | None = None,
-                 quest_block: int = 64, quest_top_k: int = 8, skinny_gemm: bool = False):
+                 quest_block: int = 64, quest_top_k: int = 8, skinny_gemm: bool = False, v_bits: int = 8):
         """``layer_modes``: per layer ``"dense"`` (attention over the whole cache) or ``"quest"`` (block-sparse: the
         ``quest_top_k`` blocks of ``quest_block`` tokens with the highest min/max upper-bound score per query head).
         The reference's layer sweep found sparse attention harmless in the first half of the layers only
@@ -125,6 +138,11 @@ class DecodeModel:
         # rows) instead of library GEMMs.  Off by default: measured on B200 the library GEMMs are faster at every
         # Llama-3-8B projection shape (graph replay, 16 rows: 79 us against 116 us per layer on one GPU).
         self.skinny_gemm = bool(skinny_gemm)
+        # 4: the caches are mixed-precision page records (FP8 keys, 4-bit values: 200 instead of 264 bytes per token
+        # and head); dense layers only, the block-sparse kernel reads 8-bit values
+        if v_bits not in (4, 8):
+            raise ValueError("v_bits must be 4 or 8")
+        self.v_bits = v_bits
         self.metas: list[Tensor | None] = []
         self.set_layer_modes(layer_modes)
         # the fused RoPE + quantise + append kernel needs fp16/bf16 activations on a CUDA device
@@ -162,6 +180,8 @@ class DecodeModel:
         modes = list(layer_modes) if layer_modes is not None else ["dense"] * self.cfg.layers
         if len(modes) != self.cfg.layers or any(m not in ("dense", "quest") for m in modes):
             raise ValueError("layer_modes must name 'dense' or 'quest' for every layer")
+        if self.v_bits == 4 and "quest" in modes:
+            raise ValueError("block-sparse layers need 8-bit values (v_bits=8)")
         self.layer_modes = modes
         if getattr(self, "caches", None):
             for l, m in enumerate(modes):   # a dense layer's appends do not maintain metadata: drop what would go stale
@@ -170,7 +190,7 @@ class DecodeModel:
             self._build_missing_metas()
 
     def _layer_kv(self, cache: "LayerCache", lens: Tensor):
-        return paged.PagedKV(cache.k, cache.v, cache.ks, cache.vs, self.page_table, lens, lens.numel())
+        return paged.PagedKV(cache.k, cache.v, cache.ks, cache.vs, self.page_table, lens, lens.numel(), v_bits=cache.v_bits)
 
     def _build_missing_metas(self) -> None:
         if len(self.metas) != len(self.caches):
@@ -215,21 +235,23 @@ class DecodeModel:
         self.caches = []
         gd = torch.Generator(device=dev)
         for l in range(cfg.layers):
-            c = LayerCache(total, self.shard.n_kv, dev)
+            c = LayerCache(total, self.shard.n_kv, dev, self.v_bits)
             for i, head in enumerate(self.shard.kv_heads):  # keyed by the GLOBAL head: same bytes at every TP degree
                 gd.manual_seed((seed * 7919 + l * 131 + head) & 0x7FFFFFFF)
                 if fill == "normal":
-                    for dst, dsc in ((c.k, c.ks), (c.v, c.vs)):
-                        codes, sc = quantize_rows_e4m3(torch.randn((total, 16, 128), generator=gd, device=dev))
+                    for dst, dsc, quant in ((c.k, c.ks, quantize_rows_e4m3),
+                                            (c.v, c.vs, quantize_rows_int4 if self.v_bits == 4 else quantize_rows_e4m3)):
+                        codes, sc = quant(torch.randn((total, 16, 128), generator=gd, device=dev))
                         dst.view(torch.uint8)[:, i].copy_(codes.view(torch.uint8))
                         dsc[:, i].copy_(sc)
                 elif fill == "random_codes":
-                    codes = torch.randint(0, 256, (total, paged.RECORD_ROWS, 128), generator=gd, device=dev, dtype=torch.uint8)
+                    codes = torch.randint(0, 256, (total, c.buf.shape[2], 128), generator=gd, device=dev, dtype=torch.uint8)
                     codes = torch.where((codes & 0x7F) == 0x7F, codes & 0xFE, codes)  # keep clear of the NaN patterns
                     c.buf[:, i].copy_(codes)
                     del codes
                     c.ks[:, i].copy_(torch.rand((total, 16), generator=gd, device=dev) * 0.004 + 0.006)
-                    c.vs[:, i].copy_(torch.rand((total, 16), generator=gd, device=dev) * 0.004 + 0.006)
+                    # (4-bit values span -8..7 where FP8 codes span +-448: a scale that keeps the values within about +-4)
+                    c.vs[:, i].copy_((torch.rand((total, 16), generator=gd, device=dev) * 0.004 + 0.006) * (64.0 if self.v_bits == 4 else 1.0))
                 elif fill != "zeros":
                     raise ValueError(f"unknown fill {fill!r}")
             self.caches.append(c)
@@ -283,7 +305,7 @@ class DecodeModel:
             return self._quest_attention(q, li, new_lens, scale, meta_is_current=True).to(dtype)
         a = torch.empty((B, sh.n_q, D), dtype=dtype, device=qkv.device)
         _C.fused_gqa_paged(q, cache.k, cache.v, cache.ks, cache.vs, self.page_table, new_lens, scale,
-                           max_seq_len=self.max_seq_len, out=a)
+                           max_seq_len=self.max_seq_len, out=a, v_bits=cache.v_bits)
         return a
 
     def enable_fused_allreduce(self, batch: int) -> None:

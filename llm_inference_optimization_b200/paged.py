@@ -23,6 +23,7 @@ class PagedKV:
     page_table: Tensor | None   # int32 [B, max_pages]; None: sequence b owns pages b*max_pages ...
     seq_lens: Tensor | None     # int32 [B]
     batch: int
+    v_bits: int = 8             # 4: mixed-precision page records, v_pool is uint8 [num_pages, Hkv, 16, 64] (see mixed_views)
 
     @property
     def page_size(self) -> int:
@@ -43,10 +44,17 @@ class PagedKV:
         k, v, ks, vs = fused_views(buf, code_dtype)
         return cls(k, v, ks, vs, page_table, seq_lens, batch)
 
-    def decode(self, Q: Tensor, scale: float, max_seq_len: int | None = None) -> Tensor:
+    @classmethod
+    def from_mixed(cls, buf: Tensor, code_dtype: torch.dtype, page_table: Tensor | None, seq_lens: Tensor | None,
+                   batch: int) -> "PagedKV":
+        """Cache of mixed-precision page records: 8-bit K, 4-bit V (see ``mixed_views``)."""
+        k, v, ks, vs = mixed_views(buf, code_dtype)
+        return cls(k, v, ks, vs, page_table, seq_lens, batch, v_bits=4)
+
+    def decode(self, Q: Tensor, scale: float, max_seq_len: int | None = None, out: Tensor | None = None) -> Tensor:
         """Dense GQA decode over the whole cache (``_C.fused_gqa_paged``)."""
         return _C.fused_gqa_paged(Q, self.k_pool, self.v_pool, self.k_scale, self.v_scale, self.page_table,
-                                  self.seq_lens, scale, max_seq_len=max_seq_len)
+                                  self.seq_lens, scale, max_seq_len=max_seq_len, out=out, v_bits=self.v_bits)
 
 
 RECORD_ROWS = 33  # rows of 128 bytes per (page, head): 16 of K codes, 16 of V codes, 1 of 16 + 16 fp32 scales
@@ -78,7 +86,45 @@ def pack_fused(k_pool: Tensor, v_pool: Tensor, k_scale: Tensor, v_scale: Tensor)
     return buf
 
 
+MIXED_RECORD_ROWS = 25  # 16 rows of K codes, 8 rows of 4-bit V codes (two tokens per row), 1 row of 16 + 16 fp32 scales
+
+
+def mixed_views(buf: Tensor, code_dtype: torch.dtype):
+    """Views ``(k_pool, v4_pool, k_scale, v_scale)`` over a buffer of mixed-precision page records.
+
+    ``buf`` is uint8 ``[num_pages, Hkv, 25, 128]``.  K keeps 8-bit codes (``[num_pages,Hkv,16,128]`` of ``code_dtype``);
+    V is stored in 4 bits, ``[num_pages,Hkv,16,64]`` uint8 with channel ``2j`` in the low and ``2j+1`` in the high
+    nibble of byte ``j`` (nibble = code + 8, code in -7..7, scale = amax / 7): 200 bytes per token and head instead of
+    264.  The decode kernel fetches a record with one TMA request and unpacks V in registers.
+    """
+    _C._require(buf.dtype == torch.uint8 and buf.dim() == 4 and buf.shape[2:] == (MIXED_RECORD_ROWS, 128) and buf.is_contiguous(),
+                "mixed-precision buffer must be contiguous uint8 [num_pages, Hkv, 25, 128]")
+    num_pages, Hkv = buf.shape[:2]
+    k = buf[:, :, 0:16, :].view(code_dtype)
+    v = buf[:, :, 16:24, :].unflatten(-1, (2, 64)).flatten(2, 3)   # [num_pages, Hkv, 16, 64]: token t = row t // 2, half t % 2
+    sc = buf[:, :, 24, :].view(torch.float32)
+    return k, v, sc[:, :, 0:16], sc[:, :, 16:32]
+
+
+def pack_mixed(k_pool: Tensor, v4_pool: Tensor, k_scale: Tensor, v_scale: Tensor) -> Tensor:
+    """Copy 8-bit K codes ``[num_pages,Hkv,16,128]``, packed 4-bit V codes ``[num_pages,Hkv,16,64]`` uint8 and their
+    scales into one buffer of mixed-precision page records."""
+    num_pages, Hkv, P, D = k_pool.shape
+    _C._require(P == 16 and D == 128 and v4_pool.shape == (num_pages, Hkv, 16, 64) and v4_pool.dtype == torch.uint8,
+                "mixed-precision records need page_size 16, head_dim 128 and uint8 [num_pages,Hkv,16,64] V codes")
+    buf = torch.zeros((num_pages, Hkv, MIXED_RECORD_ROWS, 128), dtype=torch.uint8, device=k_pool.device)
+    k, v, ks, vs = mixed_views(buf, k_pool.dtype)
+    k.copy_(k_pool); v.copy_(v4_pool); ks.copy_(k_scale); vs.copy_(v_scale)
+    return buf
+
+
 def _pool_args(kv: PagedKV):
+    if kv.v_bits == 4:
+        kp, ks = kv.k_pool, kv.k_scale
+        _C._require(kp.is_cuda and kp.dim() == 4 and kp.shape[2:] == (16, 128) and kv.v_pool.shape == (*kp.shape[:2], 16, 64)
+                    and kv.v_pool.dtype == torch.uint8 and kv.v_pool.data_ptr() == kp.data_ptr() + 2048
+                    and kp.stride() == (kp.shape[1] * 3200, 3200, 128, 1), "not a cache of mixed-precision page records")
+        return (kp.stride(0), kp.stride(1), kp.stride(2), ks.stride(0), ks.stride(1))
     kp, ks = kv.k_pool, kv.k_scale
     _C._require(kp.is_cuda and kp.dim() == 4 and kp.stride(-1) == 1 and kv.v_pool.shape == kp.shape
                 and kv.v_pool.stride() == kp.stride(), "pools must be CUDA [num_pages,Hkv,page_size,D] with one layout")
@@ -165,7 +211,8 @@ def rope_quant_append(qkv: Tensor, kv: PagedKV, Hq: int, rope_theta: float, *, m
     rc = _lib.load().skv_rope_quant_append(
         qkv.data_ptr(), int(qkv.dtype == torch.bfloat16), q.data_ptr(), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(),
         kv.k_scale.data_ptr(), kv.v_scale.data_ptr(), None if kv.page_table is None else kv.page_table.data_ptr(),
-        kv.seq_lens.data_ptr(), B, Hq, Hkv, D, _C._code_dtype(kv.k_pool), P, kv.max_pages, *strides, float(rope_theta),
+        kv.seq_lens.data_ptr(), B, Hq, Hkv, D, _C._code_dtype(kv.k_pool) | (_C.SKV_V_INT4 if kv.v_bits == 4 else 0),
+        P, kv.max_pages, *strides, float(rope_theta),
         None if meta is None else meta.data_ptr(), int(block_size), 0 if meta is None else meta.shape[2],
         kv.k_pool.shape[0], None if status is None else status.data_ptr(),
         _C._dev_index(qkv), torch.cuda.current_stream(qkv.device).cuda_stream)

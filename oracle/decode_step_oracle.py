@@ -50,11 +50,12 @@ def quest_attention(q, K, V, lens, block: int, top_k: int, scale: float):
 
 
 def decode_step(weights: dict, cfg, tokens, k_hist, v_hist, seq_lens, layer_modes=None, quest_block: int = 64,
-                quest_top_k: int = 8):
+                quest_top_k: int = 8, v_bits: int = 8):
     """``weights``: fp32 full matrices (embed, lm_head, final_norm, layers[l][wq|wk|wv|wo|wg|wu|wd|n1|n2]);
     ``k_hist[l]``/``v_hist[l]``: ``[B, Hkv, Tmax, D]`` fp32 dequantised history; returns logits ``[B, vocab]``.
     ``layer_modes[l] == "quest"`` replaces the layer's dense attention by ``quest_attention`` (the per-layer schedule
-    of the reference's ``sparse_layers``, benchmarks/llama_integration_benchmark.py:114-230)."""
+    of the reference's ``sparse_layers``, benchmarks/llama_integration_benchmark.py:114-230).  ``v_bits=4``: the new
+    token's value row is stored in 4 bits (mixed-precision pages) instead of FP8."""
     B = tokens.shape[0]
     D, Hq, Hkv = cfg.D, cfg.Hq, cfg.Hkv
     x = weights["embed"][tokens]
@@ -65,8 +66,11 @@ def decode_step(weights: dict, cfg, tokens, k_hist, v_hist, seq_lens, layer_mode
         k = rope((h @ w["wk"]).view(B, Hkv, D), pos, cfg.rope_theta)
         v = (h @ w["wv"]).view(B, Hkv, D)
         kc, ks = skv_oracle.quantize_e4m3(k)
-        vc, vs = skv_oracle.quantize_e4m3(v)
-        kq, vq = skv_oracle.dequantize(kc, ks), skv_oracle.dequantize(vc, vs)
+        if v_bits == 4:
+            vq = skv_oracle.dequantize_int4(*skv_oracle.quantize_int4(v))
+        else:
+            vq = skv_oracle.dequantize(*skv_oracle.quantize_e4m3(v))
+        kq = skv_oracle.dequantize(kc, ks)
         K, V = k_hist[l].clone(), v_hist[l].clone()
         for b in range(B):
             K[b, :, pos[b]] = kq[b]

@@ -208,6 +208,32 @@ def quantize_e4m3(x: Tensor):
     return y.to(torch.float8_e4m3fn), scale
 
 
+INT4_MAX = 7.0
+
+
+def quantize_int4(x: Tensor):
+    """Symmetric 4-bit codes per row of D channels, for the V half of mixed-precision pages.
+
+    ``scale = amax / 7`` (1.0 for a zero row); ``q = clamp(round_half_even(x / scale), -7, 7)``; the stored nibble is
+    ``q + 8`` (1..15) and byte ``j`` of a row holds channel ``2j`` in its low and channel ``2j+1`` in its high nibble.
+    Returns (uint8 [..., D/2] packed codes, fp32 scales[...]).  No reference counterpart.
+    """
+    xf = x.float()
+    amax = xf.abs().amax(dim=-1)
+    scale = torch.where(amax > 0, amax / INT4_MAX, torch.ones_like(amax))
+    q = torch.round(xf / scale.unsqueeze(-1)).clamp_(-INT4_MAX, INT4_MAX)
+    u = (q + 8).to(torch.uint8)
+    return (u[..., 0::2] | (u[..., 1::2] << 4)).contiguous(), scale
+
+
+def dequantize_int4(packed: Tensor, scale: Tensor) -> Tensor:
+    """fp32 values of 4-bit codes packed by :func:`quantize_int4`."""
+    lo = (packed & 0x0F).to(torch.int16) - 8
+    hi = (packed >> 4).to(torch.int16) - 8
+    q = torch.stack((lo, hi), dim=-1).reshape(*packed.shape[:-1], packed.shape[-1] * 2)
+    return q.float() * scale.float().unsqueeze(-1)
+
+
 def dequantize(codes: Tensor, scale: Tensor) -> Tensor:
     return codes.float() * scale.unsqueeze(-1)
 

@@ -28,7 +28,8 @@ def oracle_inputs(m):
         for b in range(B):
             pg = pt[b].long()
             K[b] = oracle.dequantize(k[pg], ks[pg]).permute(1, 0, 2, 3).reshape(CFG.Hkv, T, 128)
-            V[b] = oracle.dequantize(v[pg], vs[pg]).permute(1, 0, 2, 3).reshape(CFG.Hkv, T, 128)
+            vd = oracle.dequantize_int4(v[pg], vs[pg]) if c.v_bits == 4 else oracle.dequantize(v[pg], vs[pg])
+            V[b] = vd.permute(1, 0, 2, 3).reshape(CFG.Hkv, T, 128)
         k_hist.append(K)
         v_hist.append(V)
     D = CFG.D
@@ -82,6 +83,22 @@ def test_weight_streaming_gemm_option_matches_oracle_model(cuda_device):
     assert _workspace.all_of("skinny_gemm", cuda_device), "the weight-streaming kernel did not run"
     assert (got - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item())
     assert torch.nn.functional.cosine_similarity(got, want, dim=-1).min().item() > 0.999
+
+
+def test_mixed_precision_pages_match_oracle_model(cuda_device):
+    """v_bits=4: FP8 keys and 4-bit values in every layer's cache -- appended by the fused kernel, read by the decode
+    kernel's 4-bit path -- against the oracle model that stores the new value row by the same 4-bit rule."""
+    m = ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, 1, 0), cuda_device, dtype=torch.bfloat16, v_bits=4)
+    m.init_cache(LENS)
+    assert m.caches[0].buf.shape[2] == 25
+    weights, k_hist, v_hist = oracle_inputs(m)
+    want = dso.decode_step(weights, CFG, TOK, k_hist, v_hist, LENS.clone(), v_bits=4)
+    got = m.step(TOK.to(cuda_device)).float().cpu()
+    assert (got - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item())
+    assert torch.nn.functional.cosine_similarity(got, want, dim=-1).min().item() > 0.999
+    with pytest.raises(ValueError):
+        ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, 1, 0), cuda_device, dtype=torch.bfloat16, v_bits=4,
+                       layer_modes=["dense", "quest"])
 
 
 def test_hybrid_layer_schedule_matches_oracle_model(cuda_device):

@@ -188,3 +188,24 @@ def test_reference_token_kernel_is_not_a_pin():
     exact = oracle.token_sparse_attention(Q.float(), K.float(), V.float(), 32, 0)
     diff = (exact - want).abs().max().item()
     assert torch.isfinite(want).all() and 1e-3 < diff < 1.0
+
+
+def test_int4_rule_for_mixed_precision_pages():
+    """4-bit V codes: scale = amax / 7, round-half-even, nibble = code + 8, even channel in the low nibble."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(3, 5, 128, generator=g).half()
+    x[0, 0] = 0
+    x[1, 1] = 0
+    x[1, 1, :6] = torch.tensor([7.0, -7.0, 0.5, 1.5, 2.5, -3.5])   # amax 7 -> scale 1: grid points and exact ties
+    packed, scale = oracle.quantize_int4(x)
+    assert packed.dtype == torch.uint8 and packed.shape == (3, 5, 64) and scale.shape == (3, 5)
+    assert scale[0, 0] == 1.0 and bool((packed[0, 0] == 0x88).all())
+    assert torch.equal(scale[1:], x[1:].float().abs().amax(-1) / 7)
+    lo, hi = (packed & 0xF).int() - 8, (packed >> 4).int() - 8
+    assert int(lo.min()) >= -7 and int(hi.max()) <= 7
+    assert [int(lo[1, 1, 0]), int(hi[1, 1, 0]), int(lo[1, 1, 1]), int(hi[1, 1, 1]), int(lo[1, 1, 2]), int(hi[1, 1, 2])] == \
+        [7, -7, 0, 2, 2, -4]   # ties go to the even code
+    back = oracle.dequantize_int4(packed, scale)
+    assert back.shape == x.shape
+    assert bool(((back - x.float()).abs() <= scale.unsqueeze(-1) * 0.5 + 1e-6).all())
+    assert bool((back.abs().amax(-1)[1:] == x[1:].float().abs().amax(-1)).all())          # the row maximum is exact

@@ -103,9 +103,10 @@ def test_append_keeps_block_metadata_current(cuda_device):
 
 @pytest.mark.parametrize("B,Hq,Hkv,T", [(2, 32, 8, 8192), (3, 8, 2, 2048), (1, 8, 1, 131072)])
 def test_ring_and_register_scoring_kernels_agree(cuda_device, lib, B, Hq, Hkv, T):
-    """The block scores come from either of two kernels (metadata streamed through shared memory by bulk copies, or
-    loaded into registers): same arithmetic, so the same blocks and the same output, also when a CTA's range of the
-    flattened (sequence, kv-head, block) space crosses from one kv-head into the next and with ragged lengths."""
+    """The block scores come from either of two kernels: metadata streamed through shared memory into tensor-core
+    products with (min(q, 0) | max(q, 0)), or loaded into registers and scored with FMAs.  Both sum the same exact
+    products (in different orders), so on a cache with planted high-affinity blocks they pick the same blocks and
+    give the same output, also when a CTA's range crosses from one kv-head into the next and with ragged lengths."""
     Q, K, V, _ = workloads.planted_block_cache(B, Hq, Hkv, T, seed=29)
     lens = None if B == 1 else torch.tensor([T, T // 3 + 5, 70][:B], dtype=torch.int32)
     kv, Kd, Vd = paged_case(Q, K, V, "fp8", cuda_device, seed=7, seq_lens=lens)
@@ -116,7 +117,7 @@ def test_ring_and_register_scoring_kernels_agree(cuda_device, lib, B, Hq, Hkv, T
             assert lib.skv_quest_set_ring_scores(ring) == 0
             res[ring] = paged.quest_sparse_decode(Q.to(cuda_device), kv, meta, 128 ** -0.5, 64, 8, return_indices=True)
     finally:
-        lib.skv_quest_set_ring_scores(0)
+        lib.skv_quest_set_ring_scores(1)
     assert torch.equal(res[1][1], res[0][1])
     assert torch.equal(res[1][0], res[0][0])
     want = oracle.attend_selected_blocks(Q, Kd, Vd, res[1][1].cpu().long(), 64, 128 ** -0.5, lens)
