@@ -196,6 +196,10 @@ int skv_rope_quant_append(const void* qkv, int qkv_is_bf16, void* q_out, void* k
  * out [B,H,S,D] fp16 contiguous; topk_idx_out optional int32 [B,H,S,top_k], ascending, -1 padded.
  * D is 16, 32, 64, 128 or 256; min(top_k,T) + min(sink_tokens,T) <= 4096.  Workspace holds fp32 scores [B,H,S,T]. */
 size_t skv_token_sparse_workspace_bytes(int B, int H, int S, int T);
+/* on = 1 (default): decode-shaped calls (S = 1, D = 64 or 128) score the keys on the tensor cores, K streamed through a
+ * shared-memory ring by TMA; on = 0: always the register-load kernel.  Both sum the same exact products in different
+ * orders.  Process-wide.  The device status word (bit SKV_DEV_TIMEOUT) is at offset 0 of the workspace. */
+int skv_token_sparse_set_mma_scores(int on);
 int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* out, int* topk_idx_out,
                             void* workspace, size_t workspace_bytes, int B, int H, int S, int T, int D,
                             long long q_stride_b, long long q_stride_h, long long q_stride_s,
@@ -212,6 +216,11 @@ int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* o
  * sparse_attention.cu:213-215,243).  D is 16, 32, 64, 128 or 256; min(top_k_blocks, nb) <= 4096.
  * Workspace holds fp32 block scores [B,H,nb]. */
 size_t skv_block_sparse_workspace_bytes(int B, int H, int T, int block_size);
+/* on = 1 (default): with D = 64 or 128 and a block size that is a multiple of 16 the block scores are computed on the
+ * tensor cores (the mean of q . k_t over a block is the sum of its tokens' scores over their count), K streamed through
+ * a shared-memory ring by TMA; on = 0: always the register-load kernel.  Process-wide.  The device status word (bit
+ * SKV_DEV_TIMEOUT) is at offset 0 of the workspace. */
+int skv_block_sparse_set_mma_scores(int on);
 int skv_block_sparse_decode(const void* q, const void* k, const void* v, void* out, int* block_idx_out,
                             void* workspace, size_t workspace_bytes, int B, int H, int T, int D,
                             long long q_stride_b, long long q_stride_h,

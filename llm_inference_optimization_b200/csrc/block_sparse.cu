@@ -15,6 +15,7 @@
 //      the block scores, softmax over k values, gather of k * block_size V rows.
 #include "skv_common.cuh"
 #include "skv_select.cuh"
+#include "skv_tmap.cuh"
 
 namespace skv {
 namespace bsp {
@@ -73,6 +74,108 @@ block_mean_scores_kernel(const ScoreParams p, int blocks_per_cta) {
         }
         acc = warp_sum(acc + acc1);
         if (lane == 0) srow[j] = acc * p.scale / (float)(t1 - t0);
+    }
+}
+
+// Tensor-core variant of the scoring kernel (D = 64 or 128, block_size a multiple of 16).  The mean over a block of
+// q . k_t is the sum of the tokens' scores divided by their count, so the keys stream exactly as in the token-sparse
+// scoring kernel -- TMA boxes of 128 tokens x 64 channels into a 3-stage ring, one [128 tokens x D] . [D x 8] product per
+// tile with the query in column 0 -- and each warp leaves the sum of its 16 tokens' scores in shared memory; when the
+// CTA's chunk has streamed, every block adds its block_size / 16 partial sums in token order (the same order in every
+// run).  Tokens past T read as zero.  Thread 0 refills a stage right after the block-wide barrier that ends its previous
+// use; every wait is bounded, and one that runs out sets SKV_DEV_TIMEOUT and ends the CTA's loop.
+// grid (ceil(nb / blocks_per_cta), H, B); blocks_per_cta * block_size is a multiple of 128
+constexpr int MMA_TILE = 128;
+constexpr int MMA_STAGES = 3;
+template <int D>
+__host__ __device__ constexpr int mma_stage_bytes() { return MMA_TILE * D * 2; }
+template <int D>
+__host__ __device__ constexpr size_t mma_ring_bytes() { return (size_t)MMA_STAGES * mma_stage_bytes<D>() + 64; }
+
+template <int D>
+__global__ void __launch_bounds__(SCORE_THREADS, 2)
+block_mean_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const ScoreParams p, const KvMapPos pos,
+                             int blocks_per_cta, int* status) {
+    pdl_launch_dependents();
+    constexpr int NH = D / 64, KSTEPS = D / 16, HALF_BYTES = MMA_TILE * 128, STAGE = mma_stage_bytes<D>();
+    extern __shared__ uint8_t mma_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(mma_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t ring = smem_u32(smem);
+    const uint32_t full_bar = ring + MMA_STAGES * STAGE;
+    float* part16 = reinterpret_cast<float*>(smem + mma_ring_bytes<D>());   // sums of 16 tokens' scores, [chunk tokens / 16]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, tq = lane & 3, lj = lane >> 3, r8 = lane & 7;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int j0 = blockIdx.x * blocks_per_cta, j1 = min(p.nb, j0 + blocks_per_cta);
+    const int t0 = j0 * p.block_size, t1 = min(p.T, j1 * p.block_size);
+    const int ntiles = (t1 - t0 + MMA_TILE - 1) / MMA_TILE;
+    if (tid == 0) {
+        for (int s = 0; s < MMA_STAGES; ++s) mbar_init(full_bar + s * 8, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    const uint64_t policy = l2_policy_evict_first();
+    auto issue = [&](int tile) {   // thread 0 only
+        const int s = tile % MMA_STAGES;
+        const uint32_t bar = full_bar + s * 8, dst = ring + s * STAGE;
+        mbar_expect_tx(bar, STAGE);
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) {
+            int c[5] = {0, 0, 0, 0, 0};
+#pragma unroll
+            for (int i = 1; i < 5; ++i) c[i] = (i == pos.half) ? hf : (i == pos.tok) ? t0 + tile * MMA_TILE : (i == pos.head) ? h : b;
+            tma_load_5d(dst + hf * HALF_BYTES, &tmK, bar, c[0], c[1], c[2], c[3], c[4], policy);
+        }
+    };
+    if (tid == 0) {
+        tma_prefetch_desc(&tmK);
+        for (int i = 0; i < MMA_STAGES - 1 && i < ntiles; ++i) issue(i);
+    }
+    uint32_t qb[KSTEPS][2];   // the query as the B operand: column 0 of the 8-wide N side, the other columns zero
+    {
+        const __half* qrow = p.q + b * p.q_sb + h * p.q_sh;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            qb[kk][0] = g == 0 ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + tq * 2) : 0u;
+            qb[kk][1] = g == 0 ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + 8 + tq * 2) : 0u;
+        }
+    }
+    const uint32_t a_row_off = (uint32_t)((warp * 16 + (lj & 1) * 8 + r8) * 128);
+    for (int i = 0; i < ntiles; ++i) {
+        if (tid == 0 && i + MMA_STAGES - 1 < ntiles) issue(i + MMA_STAGES - 1);
+        const int s = i % MMA_STAGES;
+        int ok = mbar_wait(full_bar + s * 8, (uint32_t)((i / MMA_STAGES) & 1)) ? 1 : 0;
+        if (ok) {
+            const uint32_t base = ring + s * STAGE + a_row_off;
+            float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+                const int c = 2 * kk + (lj >> 1);
+                uint32_t a[4];
+                ldsm_x4(base + (uint32_t)(c >> 3) * HALF_BYTES + (uint32_t)(((c & 7) ^ r8) << 4), a[0], a[1], a[2], a[3]);
+                if (kk & 1) mma_f16(acc1, a, qb[kk][0], qb[kk][1]);
+                else mma_f16(acc0, a, qb[kk][0], qb[kk][1]);
+            }
+            // column 0 (lanes tq == 0) holds the scores of tokens g and g + 8: sum the warp's 16 tokens over the 8 lanes g
+            float v = tq == 0 ? (acc0[0] + acc1[0]) + (acc0[2] + acc1[2]) : 0.f;
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            if (lane == 0) part16[i * (MMA_TILE / 16) + warp] = v;
+        }
+        if (!__syncthreads_and(ok)) {   // also: everybody is done with tile i
+            if (tid == 0) atomicOr(status, SKV_DEV_TIMEOUT);
+            return;
+        }
+    }
+    __syncthreads();
+    float* srow = p.scores + ((long long)b * p.H + h) * p.nb;
+    const int per = p.block_size / 16;
+    for (int j = j0 + tid; j < j1; j += SCORE_THREADS) {
+        const int bt0 = j * p.block_size, bt1 = min(p.T, bt0 + p.block_size);
+        float sum = 0.f;
+        for (int u = 0; u < per; ++u) sum += part16[(j - j0) * per + u];   // (16-token groups past T hold zeros)
+        srow[j] = sum * p.scale / (float)(bt1 - bt0);
     }
 }
 
@@ -178,8 +281,12 @@ block_select_attend_kernel(const AttendParams p) {
     }
 }
 
+// 1 (default): D = 64 or 128 with block sizes that are multiples of 16 are scored by the tensor-core kernel; 0: always
+// the register-load kernel.
+inline int& mma_scores_flag() { static int on = 1; return on; }
+
 template <int D>
-static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int device, cudaStream_t st) {
+static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int device, cudaStream_t st, int* status) {
     static bool configured[64] = {false};
     const size_t smem = (size_t)TopkSmem<ATT_THREADS>::WORDS * 4 + (size_t)MAX_TOPK_BLOCKS * 8 +
                         (size_t)(ATT_THREADS / (D / 8)) * D * 4;
@@ -193,7 +300,32 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     const int warps = SCORE_THREADS / 32;
     blocks_per_cta = ((blocks_per_cta + warps - 1) / warps) * warps;
     dim3 g1((sp.nb + blocks_per_cta - 1) / blocks_per_cta, sp.H, B);
-    block_mean_scores_kernel<D><<<g1, SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);
+    bool scored = false;
+    if constexpr (D == 64 || D == 128) {
+        if (mma_scores_flag() && sp.block_size % 16 == 0 && sp.block_size <= 1024) {
+            // chunks of whole 128-token tiles (so that a 16-token group never belongs to two CTAs), at most 16 K tokens
+            const int unit = sp.block_size % MMA_TILE == 0 ? 1 : MMA_TILE / 16;   // blocks per chunk: a multiple of this
+            int bpc = ((blocks_per_cta + unit - 1) / unit) * unit;
+            const int max_bpc = (16384 / sp.block_size) / unit * unit;
+            if (bpc > max_bpc) bpc = max_bpc;
+            if (bpc >= unit && (long long)bpc * sp.block_size % MMA_TILE == 0) {
+                CUtensorMap tmK;
+                KvMapPos pos;
+                const int rc = make_kv_tmap(&tmK, &pos, sp.k, 2, 64, D / 64, B, sp.T, sp.H, sp.k_sb, sp.k_st, sp.k_sh, MMA_TILE);
+                if (rc) return rc;
+                const size_t smem_mma = 1024 + mma_ring_bytes<D>() + (size_t)bpc * sp.block_size / 16 * 4;
+                static int configured_mma[64] = {0};
+                if (device < 64 && configured_mma[device] < (int)smem_mma) {
+                    SKV_CUDA_TRY(cudaFuncSetAttribute(block_mean_scores_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma));
+                    configured_mma[device] = (int)smem_mma;
+                }
+                dim3 g2((sp.nb + bpc - 1) / bpc, sp.H, B);
+                block_mean_scores_mma_kernel<D><<<g2, SCORE_THREADS, smem_mma, st>>>(tmK, sp, pos, bpc, status);
+                scored = true;
+            }
+        }
+    }
+    if (!scored) block_mean_scores_kernel<D><<<g1, SCORE_THREADS, 0, st>>>(sp, blocks_per_cta);
     SKV_CUDA_TRY(cudaGetLastError());
     SKV_CUDA_TRY(launch_pdl(block_select_attend_kernel<D>, dim3((unsigned)rows), dim3(ATT_THREADS), smem, st, ap));
     SKV_CUDA_TRY(cudaGetLastError());
@@ -206,6 +338,13 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
 using namespace skv;
 
 extern "C" {
+
+// 1 (default): D = 64 or 128 with a block size that is a multiple of 16 scores the blocks on the tensor cores; 0: always
+// with the register-load kernel.  Process-wide.
+int skv_block_sparse_set_mma_scores(int on) {
+    bsp::mma_scores_flag() = on ? 1 : 0;
+    return SKV_OK;
+}
 
 size_t skv_block_sparse_workspace_bytes(int B, int H, int T, int block_size) {
     if (B <= 0 || H <= 0 || T <= 0 || block_size <= 0) return 0;
@@ -254,12 +393,13 @@ int skv_block_sparse_decode(const void* q, const void* k, const void* v, void* o
     ap.H = H; ap.T = T; ap.block_size = block_size; ap.nb = nb; ap.top_k = top_k_blocks;
     ap.v_sb = kv_stride_b; ap.v_sh = kv_stride_h; ap.v_st = kv_stride_t;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int* st_word = static_cast<int*>(workspace);   // the device status word sits at offset 0 of the workspace
     switch (D) {
-        case 16: return bsp::launch<16>(sp, ap, B, device, st);
-        case 32: return bsp::launch<32>(sp, ap, B, device, st);
-        case 64: return bsp::launch<64>(sp, ap, B, device, st);
-        case 128: return bsp::launch<128>(sp, ap, B, device, st);
-        default: return bsp::launch<256>(sp, ap, B, device, st);
+        case 16: return bsp::launch<16>(sp, ap, B, device, st, st_word);
+        case 32: return bsp::launch<32>(sp, ap, B, device, st, st_word);
+        case 64: return bsp::launch<64>(sp, ap, B, device, st, st_word);
+        case 128: return bsp::launch<128>(sp, ap, B, device, st, st_word);
+        default: return bsp::launch<256>(sp, ap, B, device, st, st_word);
     }
 }
 

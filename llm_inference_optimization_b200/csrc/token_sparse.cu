@@ -16,6 +16,7 @@
 //      kept V rows.
 #include "skv_common.cuh"
 #include "skv_select.cuh"
+#include "skv_tmap.cuh"
 
 namespace skv {
 namespace tsp {
@@ -111,6 +112,123 @@ token_scores_kernel(const ScoreParams p, int tokens_per_cta) {
         const long long row = ((long long)b * p.H + h) * p.S + s;
         const long long o = (row * gridDim.x + blockIdx.x) * p.cand_k;
         for (int i = threadIdx.x; i < p.cand_k; i += SCORE_THREADS) {
+            p.cand_pos[o + i] = i < kc ? t0 + csel[i] : -1;
+            p.cand_score[o + i] = i < kc ? chunk_sc[csel[i]] : -INFINITY;
+        }
+    }
+}
+
+// Tensor-core variant of the scoring kernel for one query per (b, h) (decode) and D = 64 or 128.  The register-load
+// kernel above spends about 40 instructions per KB of keys on conversions, FMAs and lane reductions and reaches 0.73 of
+// the copy bandwidth; here the keys stream like K in the dense decode kernel -- TMA boxes of 128 tokens x 64 channels
+// (128-byte swizzle, evict-first) into a 2- or 3-stage ring -- and a tile's scores are one [128 tokens x D] . [D x 8] product
+// (ldmatrix + mma.sync.m16n8k16, tokens on the M side, the query in column 0 of the N side).  Same grid, chunks and
+// per-chunk candidates as the kernel above.  Thread 0 refills a stage right after the block-wide barrier that ends
+// its previous use; every wait is bounded, and a wait that runs out sets SKV_DEV_TIMEOUT and ends the CTA's loop.
+// grid (ceil(T / tokens_per_cta), H, B)
+constexpr int MMA_TILE = 128;     // tokens per stage: 16 per warp
+template <int D>
+__host__ __device__ constexpr int mma_stage_bytes() { return MMA_TILE * D * 2; }
+template <int D, int MMA_STAGES>
+__host__ __device__ constexpr size_t mma_ring_bytes() { return (size_t)MMA_STAGES * mma_stage_bytes<D>() + 64; }
+
+// MMA_STAGES = 2 with three CTAs per SM for chunks of up to 2 K tokens (the per-chunk candidate selection of one CTA
+// then overlaps two others' streaming: 64K 122 -> 116 us), 3 with two CTAs per SM for longer chunks (128K: 189 against
+// 196 us with the short ring).
+template <int D, int MMA_STAGES>
+__global__ void __launch_bounds__(SCORE_THREADS, MMA_STAGES == 2 ? 3 : 2)
+token_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const ScoreParams p, const KvMapPos pos,
+                        int tokens_per_cta, int* status) {
+    pdl_launch_dependents();
+    constexpr int NH = D / 64, KSTEPS = D / 16, HALF_BYTES = MMA_TILE * 128, STAGE = mma_stage_bytes<D>();
+    extern __shared__ uint8_t mma_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(mma_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t ring = smem_u32(smem);
+    const uint32_t full_bar = ring + MMA_STAGES * STAGE;
+    float* chunk_sc = reinterpret_cast<float*>(smem + mma_ring_bytes<D, MMA_STAGES>());   // candidate mode: [tokens_per_cta]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, tq = lane & 3, lj = lane >> 3, r8 = lane & 7;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int t0 = blockIdx.x * tokens_per_cta, t1 = min(p.T, t0 + tokens_per_cta);
+    const int ntiles = (t1 - t0 + MMA_TILE - 1) / MMA_TILE;
+    if (tid == 0) {
+        for (int s = 0; s < MMA_STAGES; ++s) mbar_init(full_bar + s * 8, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    const uint64_t policy = l2_policy_evict_first();
+    auto issue = [&](int tile) {   // thread 0 only
+        const int s = tile % MMA_STAGES;
+        const uint32_t bar = full_bar + s * 8, dst = ring + s * STAGE;
+        mbar_expect_tx(bar, STAGE);
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) {
+            int c[5] = {0, 0, 0, 0, 0};
+#pragma unroll
+            for (int i = 1; i < 5; ++i) c[i] = (i == pos.half) ? hf : (i == pos.tok) ? t0 + tile * MMA_TILE : (i == pos.head) ? h : b;
+            tma_load_5d(dst + hf * HALF_BYTES, &tmK, bar, c[0], c[1], c[2], c[3], c[4], policy);
+        }
+    };
+    if (tid == 0) {
+        tma_prefetch_desc(&tmK);
+        for (int i = 0; i < MMA_STAGES - 1 && i < ntiles; ++i) issue(i);
+    }
+    // the query as the B operand: column 0 of the 8-wide N side, the other columns zero
+    uint32_t qb[KSTEPS][2];
+    {
+        const __half* qrow = p.q + b * p.q_sb + h * p.q_sh;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            qb[kk][0] = g == 0 ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + tq * 2) : 0u;
+            qb[kk][1] = g == 0 ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + 8 + tq * 2) : 0u;
+        }
+    }
+    float* srow = p.scores + ((long long)b * p.H + h) * p.T;
+    const uint32_t a_row_off = (uint32_t)((warp * 16 + (lj & 1) * 8 + r8) * 128);   // this lane's ldmatrix row (row & 7 == r8)
+    for (int i = 0; i < ntiles; ++i) {
+        // (everybody has passed the barrier that ended tile i-1, so the stage tile i + STAGES - 1 goes into is free)
+        if (tid == 0 && i + MMA_STAGES - 1 < ntiles) issue(i + MMA_STAGES - 1);
+        const int s = i % MMA_STAGES;
+        int ok = mbar_wait(full_bar + s * 8, (uint32_t)((i / MMA_STAGES) & 1)) ? 1 : 0;
+        if (ok) {
+            const uint32_t base = ring + s * STAGE + a_row_off;
+            float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+                const int c = 2 * kk + (lj >> 1);
+                uint32_t a[4];
+                ldsm_x4(base + (uint32_t)(c >> 3) * HALF_BYTES + (uint32_t)(((c & 7) ^ r8) << 4), a[0], a[1], a[2], a[3]);
+                if (kk & 1) mma_f16(acc1, a, qb[kk][0], qb[kk][1]);
+                else mma_f16(acc0, a, qb[kk][0], qb[kk][1]);
+            }
+            if (tq == 0) {   // column 0: the query; rows g and g + 8 of this warp's 16 tokens
+                const int tok = t0 + i * MMA_TILE + warp * 16 + g;
+                const float v0 = (acc0[0] + acc1[0]) * p.scale, v1 = (acc0[2] + acc1[2]) * p.scale;
+                if (tok < t1) {
+                    srow[tok] = v0;
+                    if (p.cand_k > 0) chunk_sc[tok - t0] = v0;
+                }
+                if (tok + 8 < t1) {
+                    srow[tok + 8] = v1;
+                    if (p.cand_k > 0) chunk_sc[tok + 8 - t0] = v1;
+                }
+            }
+        }
+        if (!__syncthreads_and(ok)) {   // also: everybody is done with tile i
+            if (tid == 0) atomicOr(status, SKV_DEV_TIMEOUT);
+            break;
+        }
+    }
+    if (p.cand_k > 0) {   // as in token_scores_kernel; the select scratch reuses the drained ring (every copy has landed)
+        uint32_t* tk = reinterpret_cast<uint32_t*>(smem);
+        int* csel = reinterpret_cast<int*>(tk + TopkSmem<SCORE_THREADS>::WORDS);
+        const int n = t1 - t0, kc = min(p.cand_k, n);
+        __syncthreads();
+        block_topk_fast<SCORE_THREADS, 16>(chunk_sc, n, kc, csel, tk);
+        __syncthreads();
+        const long long row = (long long)b * p.H + h;
+        const long long o = (row * gridDim.x + blockIdx.x) * p.cand_k;
+        for (int i = tid; i < p.cand_k; i += SCORE_THREADS) {
             p.cand_pos[o + i] = i < kc ? t0 + csel[i] : -1;
             p.cand_score[o + i] = i < kc ? chunk_sc[csel[i]] : -INFINITY;
         }
@@ -257,8 +375,12 @@ static size_t attend_smem() {
     return (size_t)TopkSmem<ATT_THREADS>::WORDS * 4 + (size_t)MAX_KEEP * 8 + (size_t)(ATT_THREADS / (D / 8)) * D * 4;
 }
 
+// 1 (default): one query per (b, h) with D = 64 or 128 is scored by the tensor-core kernel; 0: always the register-load
+// kernel.  The two sum the same exact products in different orders.
+inline int& mma_scores_flag() { static int on = 1; return on; }
+
 template <int D>
-static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int device, cudaStream_t st, float* cand_base) {
+static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int device, cudaStream_t st, float* cand_base, int* status) {
     static bool configured[64] = {false};
     const size_t smem = attend_smem<D>();
     if (device < 64 && !configured[device]) {
@@ -296,7 +418,33 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
             configured1[device] = true;
         }
     }
-    token_scores_kernel<D><<<g1, SCORE_THREADS, smem1, st>>>(sp2, tokens_per_cta);
+    bool scored = false;
+    if constexpr (D == 64 || D == 128) {
+        if (mma_scores_flag() && sp.S == 1) {
+            CUtensorMap tmK;
+            KvMapPos pos;
+            const int rc = make_kv_tmap(&tmK, &pos, sp.k, 2, 64, D / 64, B, sp.T, sp.H, sp.k_sb, sp.k_st, sp.k_sh, MMA_TILE);
+            if (rc) return rc;
+            // ring + the chunk's scores (candidate mode)
+            const bool short_ring = tokens_per_cta <= 2048;
+            const size_t ring_bytes = short_ring ? mma_ring_bytes<D, 2>() : mma_ring_bytes<D, 3>();
+            const size_t smem_mma = 1024 + ring_bytes + (sp2.cand_k > 0 ? (size_t)tokens_per_cta * 4 : 0);
+            static_assert((size_t)2 * mma_stage_bytes<D>() >= (size_t)TopkSmem<SCORE_THREADS>::WORDS * 4 + MAX_CAND_K * 4,
+                          "the candidate select scratch lives in the drained ring");
+            static int configured_mma[64][2] = {{0}};
+            if (device < 64 && configured_mma[device][short_ring] < (int)smem_mma) {
+                if (short_ring)
+                    SKV_CUDA_TRY(cudaFuncSetAttribute(token_scores_mma_kernel<D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma));
+                else
+                    SKV_CUDA_TRY(cudaFuncSetAttribute(token_scores_mma_kernel<D, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma));
+                configured_mma[device][short_ring] = (int)smem_mma;
+            }
+            if (short_ring) token_scores_mma_kernel<D, 2><<<g1, SCORE_THREADS, smem_mma, st>>>(tmK, sp2, pos, tokens_per_cta, status);
+            else token_scores_mma_kernel<D, 3><<<g1, SCORE_THREADS, smem_mma, st>>>(tmK, sp2, pos, tokens_per_cta, status);
+            scored = true;
+        }
+    }
+    if (!scored) token_scores_kernel<D><<<g1, SCORE_THREADS, smem1, st>>>(sp2, tokens_per_cta);
     SKV_CUDA_TRY(cudaGetLastError());
     SKV_CUDA_TRY(launch_pdl(token_select_attend_kernel<D>, dim3((unsigned)rows), dim3(ATT_THREADS), smem, st, ap2));
     SKV_CUDA_TRY(cudaGetLastError());
@@ -309,6 +457,13 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
 using namespace skv;
 
 extern "C" {
+
+// 1 (default): decode-shaped calls (one query per head, D = 64 or 128) score the keys on the tensor cores; 0: always with
+// the register-load kernel.  Process-wide.
+int skv_token_sparse_set_mma_scores(int on) {
+    tsp::mma_scores_flag() = on ? 1 : 0;
+    return SKV_OK;
+}
 
 size_t skv_token_sparse_workspace_bytes(int B, int H, int S, int T) {
     if (B <= 0 || H <= 0 || S <= 0 || T <= 0) return 0;
@@ -361,12 +516,13 @@ int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* o
     const size_t scores_bytes = (((size_t)B * H * S * T * sizeof(float)) + 255) & ~size_t(255);
     float* cand_base = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256 + scores_bytes);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int* st_word = static_cast<int*>(workspace);   // the device status word sits at offset 0 of the workspace
     switch (D) {
-        case 16: return tsp::launch<16>(sp, ap, B, device, st, cand_base);
-        case 32: return tsp::launch<32>(sp, ap, B, device, st, cand_base);
-        case 64: return tsp::launch<64>(sp, ap, B, device, st, cand_base);
-        case 128: return tsp::launch<128>(sp, ap, B, device, st, cand_base);
-        default: return tsp::launch<256>(sp, ap, B, device, st, cand_base);
+        case 16: return tsp::launch<16>(sp, ap, B, device, st, cand_base, st_word);
+        case 32: return tsp::launch<32>(sp, ap, B, device, st, cand_base, st_word);
+        case 64: return tsp::launch<64>(sp, ap, B, device, st, cand_base, st_word);
+        case 128: return tsp::launch<128>(sp, ap, B, device, st, cand_base, st_word);
+        default: return tsp::launch<256>(sp, ap, B, device, st, cand_base, st_word);
     }
 }
 

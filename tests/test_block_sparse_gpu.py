@@ -49,6 +49,37 @@ def test_shapes(cuda_device, B, H, T, D, bs, k):
     check(cuda_device, Q, K, V, bs, k)
 
 
+@pytest.mark.parametrize("B,H,T,D,bs,k", [(1, 32, 65536, 128, 64, 8), (2, 3, 5000, 128, 16, 8), (1, 2, 9000, 64, 48, 4),
+                                          (1, 4, 300, 64, 64, 4), (1, 2, 40000, 128, 256, 3), (1, 1, 40, 128, 64, 1)])
+def test_tensor_core_and_register_scoring_agree(cuda_device, B, H, T, D, bs, k):
+    """The block scores come from the tensor-core kernel (sum of the tokens' scores over their count) or, switched off,
+    from the register-load kernel: both against the oracle, with ragged tails, block sizes that do not divide the
+    128-token tile, and a token-major cache viewed head-major (strided rows)."""
+    from llm_inference_optimization_b200 import _lib, _workspace
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(T + bs)
+    Q = torch.randn(B, H, 1, D, generator=g).half()
+    Kt = torch.randn(B, T, H, D, generator=g).half()
+    Vt = torch.randn(B, T, H, D, generator=g).half()
+    K, V = Kt.permute(0, 2, 1, 3), Vt.permute(0, 2, 1, 3)
+    want, blocks = oracle.block_sparse_mean_attention(Q, K, V, bs, k)
+    res = {}
+    try:
+        for mode in (1, 0):
+            assert lib.skv_block_sparse_set_mma_scores(mode) == 0
+            res[mode] = _C.sparse_attention_forward(Q.to(cuda_device), Kt.to(cuda_device).permute(0, 2, 1, 3),
+                                                    Vt.to(cuda_device).permute(0, 2, 1, 3), bs, k, return_indices=True)
+            torch.cuda.synchronize()
+            assert all(_workspace.status(w) == 0 for w in _workspace.all_of("block_sparse", cuda_device))
+            assert (res[mode][0].float().cpu() - want).abs().max().item() <= TOL, mode
+    finally:
+        lib.skv_block_sparse_set_mma_scores(1)
+    if gap(Q, K, bs, k) > 1e-6:
+        kk = blocks.shape[-1]
+        assert torch.equal(res[1][1], res[0][1])
+        assert torch.equal(res[1][1][..., :kk].cpu().long(), blocks)
+
+
 def test_deterministic(cuda_device):
     g = torch.Generator().manual_seed(5)
     Q, K, V = (torch.randn(s, generator=g).half().to(cuda_device) for s in ((1, 4, 1, 128), (1, 4, 2048, 128), (1, 4, 2048, 128)))

@@ -93,3 +93,34 @@ def test_reference_binding_semantics(cuda_device):
         skv.kv_evict_quant_forward(Q.float(), K, K, 16, False)
     with pytest.raises(RuntimeError):
         skv.sparse_attention(Q.cpu(), K.cpu(), K.cpu())
+
+
+@pytest.mark.parametrize("B,H,T,D,k,sink", [(1, 32, 4096, 128, 32, 0), (2, 3, 33000, 128, 32, 4), (1, 4, 70001, 64, 256, 0),
+                                            (1, 2, 40000, 128, 8, 2), (3, 2, 129, 64, 16, 0)])
+def test_tensor_core_and_register_scoring_agree(cuda_device, B, H, T, D, k, sink):
+    """Decode-shaped calls score the keys on the tensor cores (K streamed by TMA); switched off, the register-load
+    kernel does it.  Same exact products, so the same top-k sets wherever the k-th gap is not a rounding tie, with and
+    without the per-chunk candidate lists (T >= 32768), ragged T and strided (head-major view of a token-major) caches."""
+    from llm_inference_optimization_b200 import _lib, _workspace
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(T + D)
+    Q = torch.randn(B, H, 1, D, generator=g).half()
+    Kt = torch.randn(B, T, H, D, generator=g).half()          # token-major storage: K[b, h, t] is a strided view
+    Vt = torch.randn(B, T, H, D, generator=g).half()
+    K, V = Kt.permute(0, 2, 1, 3), Vt.permute(0, 2, 1, 3)
+    res = {}
+    try:
+        for mode in (1, 0):
+            assert lib.skv_token_sparse_set_mma_scores(mode) == 0
+            res[mode] = _C.token_sparse_decode(Q.to(cuda_device), Kt.to(cuda_device).permute(0, 2, 1, 3),
+                                               Vt.to(cuda_device).permute(0, 2, 1, 3), k, sink, return_indices=True)
+            torch.cuda.synchronize()
+            assert all(_workspace.status(w) == 0 for w in _workspace.all_of("token_sparse", cuda_device))
+    finally:
+        lib.skv_token_sparse_set_mma_scores(1)
+    want = oracle.token_sparse_attention(Q.float(), K.float(), V.float(), k, sink)
+    for mode in (1, 0):
+        assert (res[mode][0].float().cpu() - want).abs().max().item() <= TOL, mode
+    if boundary_gap(Q, K, k) > 1e-5:
+        assert torch.equal(res[1][1], res[0][1])
+        assert torch.equal(res[1][1][:, :, 0, :min(k, T)].cpu().long(), oracle.token_topk_sets(Q, K, k))
