@@ -22,7 +22,8 @@ from .sharding import shard_heads
 
 def ideal_bytes(cfg: ds.ModelConfig, lens: torch.Tensor, world: int) -> dict:
     per_layer_w = cfg.hidden * (cfg.Hq + 2 * cfg.Hkv) * cfg.D + cfg.Hq * cfg.D * cfg.hidden + 3 * cfg.hidden * cfg.mlp
-    weights = 2 * (cfg.layers * per_layer_w / world + cfg.hidden * cfg.vocab)       # bf16; lm_head replicated
+    head = cfg.hidden * cfg.vocab / (world if cfg.vocab % world == 0 else 1)        # split by vocabulary columns
+    weights = 2 * (cfg.layers * per_layer_w / world + head)                         # bf16
     kv = int(lens.sum()) * cfg.layers * 2 * (cfg.Hkv // world) * (cfg.D + 4)        # fp8 codes + fp32 scales
     return {"weight_bytes_per_gpu": int(weights), "kv_bytes_per_gpu": int(kv)}
 
@@ -102,6 +103,7 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
     model = ds.DecodeModel(cfg, shard_heads(cfg.Hq, cfg.Hkv, shard_world, rank), dev, seed=seed)
     if shard_world != world:
         model._all_reduce = lambda x: x   # one rank of the emulated group: its partial sums stand in for the reduced ones
+        model._all_gather_columns = lambda x: x   # ... and its slice of the logits for all of them
     model.init_cache(lens, fill=fill, seed=seed, extra_tokens=2 * (steps + warmup) + 32)
     fused_allreduce = fused_allreduce and world > 1
     if fused_allreduce:
@@ -206,6 +208,7 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
         model = ds.DecodeModel(cfg, shard_heads(cfg.Hq, cfg.Hkv, shard_world, rank), dev, seed=seed, v_bits=4)
         if shard_world != world:
             model._all_reduce = lambda x: x
+            model._all_gather_columns = lambda x: x
         model.init_cache(lens, fill=fill, seed=seed, extra_tokens=2 * (steps + warmup) + 32)
         if fused_allreduce:
             model.enable_fused_allreduce(batch)

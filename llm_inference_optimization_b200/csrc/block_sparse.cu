@@ -164,7 +164,14 @@ block_mean_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const Scor
             if (lane == 0) part16[i * (MMA_TILE / 16) + warp] = v;
         }
         if (!__syncthreads_and(ok)) {   // also: everybody is done with tile i
-            if (tid == 0) atomicOr(status, SKV_DEV_TIMEOUT);
+            if (tid == 0) {
+                atomicOr(status, SKV_DEV_TIMEOUT);
+                // copies already issued for later tiles still target this CTA's shared memory: give them a (bounded)
+                // chance to land before the CTA may leave
+                for (int t = i + 1; t < ntiles && t < i + MMA_STAGES; ++t)
+                    mbar_wait(full_bar + (t % MMA_STAGES) * 8, (uint32_t)((t / MMA_STAGES) & 1));
+            }
+            __syncthreads();
             return;
         }
     }
@@ -304,7 +311,10 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     if constexpr (D == 64 || D == 128) {
         if (mma_scores_flag() && sp.block_size % 16 == 0 && sp.block_size <= 1024) {
             // chunks of whole 128-token tiles (so that a 16-token group never belongs to two CTAs), at most 16 K tokens
-            const int unit = sp.block_size % MMA_TILE == 0 ? 1 : MMA_TILE / 16;   // blocks per chunk: a multiple of this
+            // blocks per chunk: a multiple of the fewest whole blocks that make whole 128-token tiles
+            int gcd = MMA_TILE, r = sp.block_size % MMA_TILE;
+            while (r) { const int t = gcd % r; gcd = r; r = t; }
+            const int unit = MMA_TILE / gcd;
             int bpc = ((blocks_per_cta + unit - 1) / unit) * unit;
             const int max_bpc = (16384 / sp.block_size) / unit * unit;
             if (bpc > max_bpc) bpc = max_bpc;

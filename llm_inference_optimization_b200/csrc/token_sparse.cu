@@ -215,7 +215,14 @@ token_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const ScorePara
             }
         }
         if (!__syncthreads_and(ok)) {   // also: everybody is done with tile i
-            if (tid == 0) atomicOr(status, SKV_DEV_TIMEOUT);
+            if (tid == 0) {
+                atomicOr(status, SKV_DEV_TIMEOUT);
+                // copies already issued for later tiles still target this CTA's shared memory: give them a (bounded)
+                // chance to land before the CTA may leave
+                for (int t = i + 1; t < ntiles && t < i + MMA_STAGES; ++t)
+                    mbar_wait(full_bar + (t % MMA_STAGES) * 8, (uint32_t)((t / MMA_STAGES) & 1));
+            }
+            __syncthreads();
             break;
         }
     }
@@ -396,6 +403,7 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     int tokens_per_cta = (int)((sp.T + want - 1) / want);
     tokens_per_cta = ((tokens_per_cta + 255) / 256) * 256;
     if (tokens_per_cta < 512) tokens_per_cta = 512;
+    const bool mma_path = (D == 64 || D == 128) && mma_scores_flag() && sp.S == 1;
     dim3 g1((sp.T + tokens_per_cta - 1) / tokens_per_cta, sp.H, B * sp.S);
     ScoreParams sp2 = sp;
     AttendParams ap2 = ap;
@@ -420,7 +428,7 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     }
     bool scored = false;
     if constexpr (D == 64 || D == 128) {
-        if (mma_scores_flag() && sp.S == 1) {
+        if (mma_path) {
             CUtensorMap tmK;
             KvMapPos pos;
             const int rc = make_kv_tmap(&tmK, &pos, sp.k, 2, 64, D / 64, B, sp.T, sp.H, sp.k_sb, sp.k_st, sp.k_sh, MMA_TILE);

@@ -156,7 +156,14 @@ class DecodeModel:
         ms = slice(ms.start, ms.stop)
         mk = lambda l, n, shp: _matrix(seed, l, n, shp, self.device, dtype, cfg.init_std)  # noqa: E731
         self.embed = mk(-1, "embed", (cfg.vocab, hid))
-        self.lm_head = mk(-2, "lm_head", (hid, cfg.vocab))
+        # The output projection is split by vocabulary columns like the MLP (every rank streams 1/world of its 1 GB and
+        # the logits are all-gathered) when the vocabulary divides evenly; otherwise every rank keeps the whole matrix.
+        self.vocab_sharded = shard.world > 1 and cfg.vocab % shard.world == 0
+        lm_head = mk(-2, "lm_head", (hid, cfg.vocab))
+        if self.vocab_sharded:
+            vs = shard_columns(cfg.vocab, shard.world, shard.rank)
+            lm_head = lm_head[:, vs.start:vs.stop].contiguous()
+        self.lm_head = lm_head
         self.final_norm = torch.ones(hid, device=self.device, dtype=dtype)
         self.layers = []
         for l in range(cfg.layers):
@@ -283,7 +290,21 @@ class DecodeModel:
             nxt = self.layers[li + 1]["n1"] if li + 1 < len(self.layers) else self.final_norm
             h = arn.reduce_norm(1, x, nxt, cfg.rms_eps)
         self.seq_lens.add_(1)
-        return h @ self.lm_head
+        return self._logits(h)
+
+    def _logits(self, h: Tensor) -> Tensor:
+        """``h [B, hidden]`` -> logits ``[B, vocab]`` (all-gather of the ranks' column slices when the head is sharded)."""
+        local = h @ self.lm_head
+        if not self.vocab_sharded:
+            return local
+        return self._all_gather_columns(local)
+
+    def _all_gather_columns(self, local: Tensor) -> Tensor:
+        world = self.shard.world
+        B, cols = local.shape
+        parts = torch.empty((world * B, cols), dtype=local.dtype, device=local.device)   # rank r's rows at [r*B, (r+1)*B)
+        dist.all_gather_into_tensor(parts, local.contiguous(), group=self.group)
+        return parts.view(world, B, cols).permute(1, 0, 2).reshape(B, world * cols)
 
     def _mm(self, x: Tensor, w: Tensor, out: Tensor | None = None) -> Tensor:
         """``x @ w`` of the fused-glue path: the weight-streaming kernel where it applies, else the library GEMM."""
@@ -341,7 +362,7 @@ class DecodeModel:
                 h = glue.residual_rmsnorm(x, o, w["n2"], cfg.rms_eps)
                 delta = self._all_reduce(self._mm(glue.silu_mul(self._mm(h, w["wgu"])), w["wd"]))
             self.seq_lens.add_(1)
-            return glue.residual_rmsnorm(x, delta, self.final_norm, cfg.rms_eps) @ self.lm_head
+            return self._logits(glue.residual_rmsnorm(x, delta, self.final_norm, cfg.rms_eps))
         for li, (w, cache) in enumerate(zip(self.layers, self.caches)):
             h = rms_norm(x, w["n1"], cfg.rms_eps)
             qkv = h @ w["wqkv"]
@@ -362,4 +383,4 @@ class DecodeModel:
             act = torch.nn.functional.silu(gu[:, :half]) * gu[:, half:]
             x = x + self._all_reduce(act @ w["wd"])
         self.seq_lens.add_(1)
-        return rms_norm(x, self.final_norm, cfg.rms_eps) @ self.lm_head
+        return self._logits(rms_norm(x, self.final_norm, cfg.rms_eps))
