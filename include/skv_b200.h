@@ -50,6 +50,13 @@ extern "C" {
  * pool strides (Hkv * 3200, 3200, 128) and scale strides (Hkv * 800, 800).  Up to 8 query heads per kv-head.
  * No reference counterpart. */
 #define SKV_V_INT4 0x200
+/* OR-ed into kv_dtype of skv_gqa_decode_paged: the kernel that precedes this call in the stream wrote nothing this call
+ * reads except the query and each sequence's LAST token (position seq_lens[b] - 1: its code rows and scales), as
+ * skv_rope_quant_append does.  The decode kernel, launched as a programmatic dependent, then streams every tile but the
+ * one holding that token before the previous kernel has completed, and waits for it before reading that tile or the
+ * query.  seq_lens and the page table must be older than the previous kernel.  Without the flag the kernel is ordered
+ * like any other (or follows skv_gqa_set_early_kv). */
+#define SKV_EARLY_EXCEPT_LAST 0x400
 
 /* bit in the workspace status word: a bounded wait inside a kernel ran out */
 #define SKV_DEV_TIMEOUT 1

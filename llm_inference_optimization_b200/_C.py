@@ -171,6 +171,7 @@ def sparse_attention_forward(Q: Tensor, K: Tensor, V: Tensor, block_size: int, t
 
 SKV_OUT_BF16 = 0x100  # OR-ed into the kv_dtype argument of skv_gqa_decode_paged: bf16 output elements
 SKV_V_INT4 = 0x200    # ... and of skv_rope_quant_append: V is 4-bit (mixed-precision page records)
+SKV_EARLY_EXCEPT_LAST = 0x400   # skv_gqa_decode_paged: the previous kernel wrote only the query and each sequence's last token
 
 
 def _code_dtype(t: Tensor) -> int:
@@ -183,9 +184,14 @@ def _code_dtype(t: Tensor) -> int:
 
 def fused_gqa_paged(Q: Tensor, k_pool: Tensor, v_pool: Tensor, k_scale: Tensor, v_scale: Tensor,
                     page_table: Tensor | None, seq_lens: Tensor | None, scale: float, *,
-                    max_seq_len: int | None = None, out: Tensor | None = None, v_bits: int = 8) -> Tensor:
+                    max_seq_len: int | None = None, out: Tensor | None = None, v_bits: int = 8,
+                    after_append: bool = False) -> Tensor:
     """Dense GQA decode over a paged INT8 / FP8-E4M3 cache with per-token-per-head fp32 scales.
 
+    ``after_append=True``: the kernel launched just before this call on the same stream was ``paged.rope_quant_append``
+    for the same step (it wrote the query and each sequence's last token, nothing else this call reads, and
+    ``seq_lens`` / ``page_table`` are older than it): the decode kernel then streams the rest of the cache while that
+    kernel is still running (``SKV_EARLY_EXCEPT_LAST``).
     ``v_bits=4``: the pools are the views of a mixed-precision record buffer (``paged.mixed_views``): ``v_pool`` is
     uint8 ``[num_pages, Hkv, 16, 64]`` of packed 4-bit codes, ``k_pool`` stays 8-bit.
 
@@ -234,6 +240,8 @@ def fused_gqa_paged(Q: Tensor, k_pool: Tensor, v_pool: Tensor, k_scale: Tensor, 
              and out.device == Q.device, "out must be a contiguous fp16 or bf16 [B,Hq,D] tensor on Q's device")
     if out.dtype == torch.bfloat16:
         kvt |= SKV_OUT_BF16
+    if after_append:
+        kvt |= SKV_EARLY_EXCEPT_LAST
     ws = _workspace.get("gqa", lib.skv_gqa_decode_workspace_bytes(B, N, Hq, Hkv, D, dev), Q.device)
     stream = torch.cuda.current_stream(Q.device).cuda_stream
     rc = lib.skv_gqa_decode_paged(

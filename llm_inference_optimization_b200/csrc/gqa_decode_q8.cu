@@ -93,7 +93,8 @@ struct Q8Params {
     int B;                   // sequences (the work-list mode has no batch dimension in its grid)
     int mode;                // Q8_SEPARATE16, Q8_SEPARATE64 or Q8_FUSED
     int out_bf16;            // output elements are bf16 instead of fp16
-    int early_kv;            // pages, page table and seq_lens are not produced by the previous kernel
+    int early_kv;            // 1: pages, page table and seq_lens are not produced by the previous kernel; 2: the same except
+                             // for each sequence's LAST token (appended by the previous kernel): its tile waits
     long long sc_sp, sc_sh;
     long long q_stride_b, q_stride_h, o_stride_b, o_stride_h;
     float scale_log2;
@@ -254,6 +255,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         uint32_t ph = 0;
         int ok = 1;
         bool bad_page = false;
+        bool waited_for_append = false;
         for (int it0 = 0; it0 < ntiles && ok; it0 += 32) {
             int page = -1, slot = 0;
             {
@@ -270,6 +272,12 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             const int jn = min(32, ntiles - it0);
             for (int j = 0; j < jn; ++j) {
                 const int pg = __shfl_sync(0xffffffffu, page, j), sl = __shfl_sync(0xffffffffu, slot, j);
+                // early_kv == 2: the previous kernel in the stream stores the sequence's last token (position len - 1);
+                // every tile before the one that holds it streams at once, that one only after the kernel is done
+                if (p.early_kv == 2 && !waited_for_append && t_begin + (it0 + j + 1) * TILE >= len) {
+                    pdl_wait_prior_grids();
+                    waited_for_append = true;
+                }
                 if (lane == 0) {
                     const uint32_t bar = full_bar + s * 8;
                     if (it0 + j >= p.stages && !mbar_wait(empty_bar + s * 8, ph ^ 1u)) {
@@ -683,7 +691,8 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
                          long long scale_stride_head, float scale, int device, void* stream) {
     const int out_bf16 = (kv_dtype & SKV_OUT_BF16) ? 1 : 0;
     const bool v4 = (kv_dtype & SKV_V_INT4) != 0;
-    kv_dtype &= ~(SKV_OUT_BF16 | SKV_V_INT4);
+    const bool early_except_last = (kv_dtype & SKV_EARLY_EXCEPT_LAST) != 0;
+    kv_dtype &= ~(SKV_OUT_BF16 | SKV_V_INT4 | SKV_EARLY_EXCEPT_LAST);
     if (!q || !k_pool || !v_pool || !k_scale_pool || !v_scale_pool || !out)
         return fail(SKV_ERR_BAD_ARG, "skv_gqa_decode_paged: null tensor pointer");
     if (B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || num_pages <= 0 || max_pages <= 0)
@@ -785,7 +794,7 @@ int skv_gqa_decode_paged(const void* q, const void* k_pool, const void* v_pool, 
     const int cap2 = one_wave ? 4 : 6;
     p.stages = slots == 2 ? (gqa::tuning().q8_stages < cap2 ? gqa::tuning().q8_stages : cap2) : gqa::tuning().q8_stages;
     p.out_bf16 = out_bf16;
-    p.early_kv = gqa::tuning().early_kv;
+    p.early_kv = early_except_last ? 2 : gqa::tuning().early_kv;
     p.page_size = page_size;
     p.max_pages = max_pages;
     p.num_pages = num_pages;

@@ -51,6 +51,10 @@ __device__ __forceinline__ float load_elem<__nv_bfloat16>(const void* p, long lo
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 rope_quant_append_kernel(const Params p) {
+    // A decode kernel launched behind this one as a programmatic dependent (SKV_EARLY_EXCEPT_LAST) may start now: it
+    // streams everything but the tile of the token stored here, and waits for this grid before it touches that
+    // tile or the rotated query.
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = p.Hq + 2 * p.Hkv;
     const long long item = (long long)blockIdx.x * (THREADS / 32) + warp;

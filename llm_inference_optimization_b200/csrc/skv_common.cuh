@@ -28,6 +28,7 @@
 #define SKV_KV_E4M3 2
 #define SKV_OUT_BF16 0x100
 #define SKV_V_INT4 0x200      // paged decode: V codes are 4-bit (mixed-precision page records)
+#define SKV_EARLY_EXCEPT_LAST 0x400   // paged decode: only each sequence's last token is written by the previous kernel
 
 // Bit set in the per-workspace device status word when a bounded wait gave up.
 #define SKV_DEV_TIMEOUT 1

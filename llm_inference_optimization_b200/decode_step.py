@@ -138,6 +138,8 @@ class DecodeModel:
         # rows) instead of library GEMMs.  Off by default: measured on B200 the library GEMMs are faster at every
         # Llama-3-8B projection shape (graph replay, 16 rows: 79 us against 116 us per layer on one GPU).
         self.skinny_gemm = bool(skinny_gemm)
+        # the dense attention kernel starts streaming the cache while the append kernel of the same layer is still running
+        self.overlap_append = True
         # 4: the caches are mixed-precision page records (FP8 keys, 4-bit values: 200 instead of 264 bytes per token
         # and head); dense layers only, the block-sparse kernel reads 8-bit values
         if v_bits not in (4, 8):
@@ -325,8 +327,9 @@ class DecodeModel:
         if sparse:
             return self._quest_attention(q, li, new_lens, scale, meta_is_current=True).to(dtype)
         a = torch.empty((B, sh.n_q, D), dtype=dtype, device=qkv.device)
+        # the append kernel above is the launch right before this one and wrote only q and position new_lens - 1
         _C.fused_gqa_paged(q, cache.k, cache.v, cache.ks, cache.vs, self.page_table, new_lens, scale,
-                           max_seq_len=self.max_seq_len, out=a, v_bits=cache.v_bits)
+                           max_seq_len=self.max_seq_len, out=a, v_bits=cache.v_bits, after_append=self.overlap_append)
         return a
 
     def enable_fused_allreduce(self, batch: int) -> None:

@@ -115,3 +115,39 @@ def test_ragged_batch_work_list_schedule(cuda_device, lib, B, Hq, Hkv, T, lens):
     want = oracle.dense_gqa_decode(Q, Kd, Vd, scale, sl)
     for mode in (1, 0):
         assert (outs[mode].float().cpu() - want).abs().max().item() <= TOL, mode
+
+
+def test_decode_overlapping_the_append_kernel_reads_the_appended_token(cuda_device):
+    """after_append=True lets the decode kernel stream the cache while the append kernel of the same step is still
+    running; only the tile that holds the appended token waits.  Fifty steps of append + decode over sequences whose
+    lengths cross tile and page boundaries must equal the ordered launch bit for bit."""
+    from llm_inference_optimization_b200 import paged
+    B, Hq, Hkv, D, pages_per_seq = 6, 8, 2, 128, 24
+    g = torch.Generator().manual_seed(21)
+    total = B * pages_per_seq
+    buf = torch.randint(0, 256, (total, Hkv, paged.RECORD_ROWS, 128), generator=g, dtype=torch.uint8)
+    buf[:, :, :32] = torch.where((buf[:, :, :32] & 0x7F) == 0x7F, buf[:, :, :32] & 0xFE, buf[:, :, :32])
+    buf = buf.to(cuda_device)
+    table = torch.randperm(total, generator=g).view(B, pages_per_seq).to(torch.int32).to(cuda_device)
+    lens0 = torch.tensor([0, 62, 63, 64, 127, 300], dtype=torch.int32)
+    outs = {}
+    for overlap in (True, False):
+        work = buf.clone()
+        kv = paged.PagedKV.from_fused(work, torch.float8_e4m3fn, table, lens0.to(cuda_device).clone(), B)
+        kv.k_scale.fill_(0.01)
+        kv.v_scale.fill_(0.01)
+        gs = torch.Generator().manual_seed(5)
+        res = []
+        for step in range(50):
+            qkv = torch.randn(B, (Hq + 2 * Hkv) * D, generator=gs).to(torch.bfloat16).to(cuda_device)
+            q = paged.rope_quant_append(qkv, kv, Hq, 500000.0)
+            new_lens = kv.seq_lens + 1
+            out = _C.fused_gqa_paged(q, kv.k_pool, kv.v_pool, kv.k_scale, kv.v_scale, table, new_lens, D ** -0.5,
+                                     after_append=overlap)
+            kv.seq_lens.copy_(new_lens)
+            res.append(out)
+        torch.cuda.synchronize()
+        assert _workspace.status(_workspace.get("gqa", 0, cuda_device)) == 0
+        outs[overlap] = torch.stack(res)
+    assert torch.isfinite(outs[True].float()).all()
+    assert torch.equal(outs[True], outs[False])
