@@ -41,7 +41,7 @@ extern "C" {
 #define SKV_KV_E4M3 2
 /* OR-ed into kv_dtype of skv_gqa_decode_paged: the output tensor holds bf16 instead of fp16 elements. */
 #define SKV_OUT_BF16 0x100
-/* OR-ed into kv_dtype of skv_gqa_decode_paged and skv_rope_quant_append: mixed-precision pages.  K stays 8-bit
+/* OR-ed into kv_dtype of skv_gqa_decode_paged, skv_quest_decode and skv_rope_quant_append: mixed-precision pages.  K stays 8-bit
  * (SKV_KV_I8 or SKV_KV_E4M3); V is 4-bit: code q = clamp(rne(v / scale), -7, 7) with scale = amax / 7 (1.0 for a zero
  * row), stored as the nibble q + 8, channel 2j in the low and 2j+1 in the high nibble of byte j (64 bytes per token).
  * The cache is one buffer of page records, [num_pages, Hkv, 25, 128] bytes: per (page, head) 16 rows of K codes,
@@ -149,6 +149,8 @@ int skv_gqa_set_cluster_combine(int on);
  *   attention over the tokens of those blocks (dequantised, fp32).  block_idx_out optional int32 [B,Hq,top_k_blocks],
  *   ascending, -1 padded.  D = 128, Hq/Hkv <= 8, top_k_blocks <= 256, top_k_blocks*block_size <= 2048.
  *   Workspace holds a status word (offset 0) and fp32 block scores [B,Hq,nb].
+ *   kv_dtype | SKV_V_INT4: the cache is a buffer of mixed-precision page records (see SKV_V_INT4): v_pool rows are 64
+ *   bytes of 4-bit codes; top_k_blocks*block_size <= 512 then.
  * num_pages: pages in the pools.  A page-table entry outside [0, num_pages) is never turned into an address: page 0 is
  *   read in its place and SKV_DEV_BAD_PAGE is set in the status word (skv_quest_build_meta: in *status, an optional
  *   int32 device word; skv_quest_decode: at offset 0 of the workspace, read with skv_workspace_status). */

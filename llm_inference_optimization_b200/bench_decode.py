@@ -218,6 +218,11 @@ def run(steps: int = 20, warmup: int = 3, layers: int = 32, batch: int = 16, see
         mixed = {"kv": "FP8-E4M3 keys, 4-bit values (mixed-precision page records), " + fill, "ms_per_step": ms_m,
                  "value": batch / (ms_m * 1e-3), "unit": "tok/s", "logits_finite": fin_m, "speedup_vs_fp8_values": ms / ms_m,
                  "kv_bytes_per_gpu": ideal_bytes(cfg, lens, shard_world)["kv_bytes_per_gpu"] * 200 // 264}
+        if hybrid is not None:   # both together: the hybrid schedule over the mixed-precision caches
+            model.set_layer_modes(["dense"] * hybrid_dense_layers + ["quest"] * (layers - hybrid_dense_layers))
+            ms_mh, fin_mh = timed_run()
+            mixed["hybrid_schedule"] = {"ms_per_step": ms_mh, "value": batch / (ms_mh * 1e-3), "unit": "tok/s",
+                                        "logits_finite": fin_mh, "speedup_vs_all_dense_fp8_values": ms / ms_mh}
     ib = ideal_bytes(cfg, lens, shard_world)
     out = {
         "metric": "decode_step_tokens_per_s", "value": batch / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms,

@@ -79,6 +79,17 @@ __device__ __forceinline__ void unpack16(const uint4& raw, float (&x)[16]) {
     }
 }
 
+// Sixteen 4-bit value codes (eight bytes: channel 2j in the low, 2j+1 in the high nibble of byte j; nibble = code + 8)
+__device__ __forceinline__ void unpack16_v4(const uint2& raw, float (&x)[16]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t w = j < 4 ? raw.x : raw.y;
+        const uint32_t byte = (w >> (8 * (j & 3))) & 0xFFu;
+        x[2 * j] = (float)(int)(byte & 15u) - 8.f;
+        x[2 * j + 1] = (float)(int)(byte >> 4) - 8.f;
+    }
+}
+
 struct Pool {
     const uint8_t* codes;   // element (page,h,slot,d) at page*sp + h*sh + slot*ss + d
     const float* scales;    // element (page,h,slot) at page*csp + h*csh + slot
@@ -439,6 +450,7 @@ struct AttendParams {
     int* block_idx;        // optional [B, Hq, top_k]
     int* status;           // device status word (SKV_DEV_BAD_PAGE)
     int Hq, G, N, nb, block_size, page_size, max_pages, num_pages, top_k;
+    int v4;                // V rows hold 4-bit codes, 64 bytes per token (mixed-precision page records; v.ss = 64)
     float scale;
 };
 
@@ -524,9 +536,11 @@ quest_select_attend_kernel(const AttendParams p) {
             // V rows on their way to shared memory (8 x 16 bytes per row, nothing held in registers), queued BEHIND
             // the K loads above: K is needed first, V only after the softmax.
             const uint32_t vdst = smem_u32(vstage);
-            for (int c = tid; c < ntok * 8; c += ATT_THREADS) {
-                const int2 pw = where[c >> 3];
-                cp_async16(vdst + c * 16, p.v.codes + pw.x * p.v.sp + h * p.v.sh + (pw.y & ~PAST_END) * p.v.ss + (c & 7) * 16);
+            const int cshift = p.v4 ? 2 : 3;   // 16-byte chunks per V row: 4 (4-bit codes) or 8
+            for (int c = tid; c < (ntok << cshift); c += ATT_THREADS) {
+                const int2 pw = where[c >> cshift];
+                cp_async16(vdst + c * 16, p.v.codes + pw.x * p.v.sp + h * p.v.sh + (pw.y & ~PAST_END) * p.v.ss +
+                                              (c & ((1 << cshift) - 1)) * 16);
             }
         }
 #pragma unroll
@@ -583,10 +597,10 @@ quest_select_attend_kernel(const AttendParams p) {
     if (staged) {
         // the weight of a token past the end is an exact zero and its row is a real (clamped) one, so no flag test
         for (int r = grp; r < ntok; r += GROUPS) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(vstage + (size_t)r * D + sub * 16);
             const float wt = w[r] * vsc_sm[r];
             float x[16];
-            unpack16<KVT>(raw, x);
+            if (p.v4) unpack16_v4(*reinterpret_cast<const uint2*>(vstage + (size_t)r * (D / 2) + sub * 8), x);
+            else unpack16<KVT>(*reinterpret_cast<const uint4*>(vstage + (size_t)r * D + sub * 16), x);
 #pragma unroll
             for (int i = 0; i < 16; ++i) acc[i] = fmaf(wt, x[i], acc[i]);
         }
@@ -727,8 +741,12 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
     const int G = Hq / Hkv;
     if (G > 8) return fail(SKV_ERR_UNSUPPORTED, "group size %d exceeds 8", G);
     if (D != quest::D) return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (128)", D);
+    const int v4 = (kv_dtype & SKV_V_INT4) ? 1 : 0;   // mixed-precision page records: V in 4 bits, 64 bytes per token
+    kv_dtype &= ~SKV_V_INT4;
     if (kv_dtype != SKV_KV_I8 && kv_dtype != SKV_KV_E4M3) return fail(SKV_ERR_UNSUPPORTED, "kv_dtype %d is not an 8-bit type", kv_dtype);
     if (block_size <= 0 || top_k_blocks <= 0) return fail(SKV_ERR_BAD_ARG, "block_size and top_k_blocks must be positive");
+    if (v4 && (long long)top_k_blocks * block_size > quest::VSTAGE_TOKENS)
+        return fail(SKV_ERR_UNSUPPORTED, "with 4-bit values top_k_blocks * block_size must not exceed %d tokens", quest::VSTAGE_TOKENS);
     if (top_k_blocks > quest::MAX_TOPK || (long long)top_k_blocks * block_size > quest::MAX_SEL_TOKENS)
         return fail(SKV_ERR_UNSUPPORTED, "top_k_blocks * block_size = %lld exceeds %d tokens (or %d blocks)",
                     (long long)top_k_blocks * block_size, quest::MAX_SEL_TOKENS, quest::MAX_TOPK);
@@ -810,6 +828,8 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
     ap.Hq = Hq; ap.G = G; ap.N = N; ap.nb = nb; ap.block_size = block_size; ap.page_size = page_size;
     ap.max_pages = max_pages; ap.top_k = top_k_blocks; ap.scale = scale;
     ap.num_pages = num_pages;
+    ap.v4 = v4;
+    if (v4) ap.v.ss = quest::D / 2;
     ap.status = reinterpret_cast<int*>(workspace);   // status word at offset 0, as skv_workspace_status reads it
     static bool configured[64] = {false};
     if (device < 64 && !configured[device]) {

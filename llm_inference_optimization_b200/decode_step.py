@@ -141,7 +141,7 @@ class DecodeModel:
         # the dense attention kernel starts streaming the cache while the append kernel of the same layer is still running
         self.overlap_append = True
         # 4: the caches are mixed-precision page records (FP8 keys, 4-bit values: 200 instead of 264 bytes per token
-        # and head); dense layers only, the block-sparse kernel reads 8-bit values
+        # and head)
         if v_bits not in (4, 8):
             raise ValueError("v_bits must be 4 or 8")
         self.v_bits = v_bits
@@ -189,8 +189,8 @@ class DecodeModel:
         modes = list(layer_modes) if layer_modes is not None else ["dense"] * self.cfg.layers
         if len(modes) != self.cfg.layers or any(m not in ("dense", "quest") for m in modes):
             raise ValueError("layer_modes must name 'dense' or 'quest' for every layer")
-        if self.v_bits == 4 and "quest" in modes:
-            raise ValueError("block-sparse layers need 8-bit values (v_bits=8)")
+        if self.v_bits == 4 and "quest" in modes and self.quest_block * self.quest_top_k > 512:
+            raise ValueError("block-sparse layers over 4-bit values gather at most 512 tokens (quest_block * quest_top_k)")
         self.layer_modes = modes
         if getattr(self, "caches", None):
             for l, m in enumerate(modes):   # a dense layer's appends do not maintain metadata: drop what would go stale

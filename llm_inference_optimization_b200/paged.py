@@ -181,7 +181,8 @@ def quest_sparse_decode(Q: Tensor, kv: PagedKV, meta: Tensor, scale: float, bloc
         None if kv.page_table is None else kv.page_table.data_ptr(),
         None if kv.seq_lens is None else kv.seq_lens.data_ptr(), meta.data_ptr(), out.data_ptr(),
         None if idx is None else idx.data_ptr(), ws.data_ptr(), ws.numel(), B, N, Hq, Hkv, D,
-        _C._code_dtype(kv.k_pool), int(block_size), int(top_k_blocks), P, kv.max_pages, kv.k_pool.shape[0], *strides,
+        _C._code_dtype(kv.k_pool) | (_C.SKV_V_INT4 if kv.v_bits == 4 else 0), int(block_size), int(top_k_blocks), P,
+        kv.max_pages, kv.k_pool.shape[0], *strides,
         float(scale), dev,
         torch.cuda.current_stream(Q.device).cuda_stream)
     _lib.check(rc, "quest_sparse_decode")

@@ -96,9 +96,22 @@ def test_mixed_precision_pages_match_oracle_model(cuda_device):
     got = m.step(TOK.to(cuda_device)).float().cpu()
     assert (got - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item())
     assert torch.nn.functional.cosine_similarity(got, want, dim=-1).min().item() > 0.999
-    with pytest.raises(ValueError):
+    with pytest.raises(ValueError):   # block-sparse layers over 4-bit values gather at most 512 tokens
         ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, 1, 0), cuda_device, dtype=torch.bfloat16, v_bits=4,
-                       layer_modes=["dense", "quest"])
+                       layer_modes=["dense", "quest"], quest_block=64, quest_top_k=16)
+
+
+def test_hybrid_schedule_over_mixed_precision_pages_matches_oracle_model(cuda_device):
+    """Dense layer 0, Quest block-sparse layer 1, both over FP8 keys and 4-bit values."""
+    modes = ["dense", "quest"]
+    m = ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, 1, 0), cuda_device, dtype=torch.float32, layer_modes=modes,
+                       quest_block=16, quest_top_k=3, v_bits=4)
+    m.init_cache(LENS)
+    weights, k_hist, v_hist = oracle_inputs(m)
+    want = dso.decode_step(weights, CFG, TOK, k_hist, v_hist, LENS.clone(), layer_modes=modes, quest_block=16,
+                           quest_top_k=3, v_bits=4)
+    got = m.step(TOK.to(cuda_device)).cpu()
+    assert (got - want).abs().max().item() <= 5e-3 * max(1.0, want.abs().max().item())
 
 
 def test_hybrid_layer_schedule_matches_oracle_model(cuda_device):

@@ -110,3 +110,27 @@ def test_append_quantises_v_to_four_bits_like_the_oracle(cuda_device, dtype, cod
         Vd[b] = oracle.dequantize_int4(v4[pg], vs[pg]).permute(0, 2, 1, 3).reshape(T, Hkv, D)
     want = oracle.dense_gqa_decode(q.cpu(), Kd, Vd, D ** -0.5, new_lens)
     assert (out.float().cpu() - want).abs().max().item() <= TOL
+
+
+@pytest.mark.parametrize("fmt", ["fp8", "int8"])
+def test_quest_block_sparse_decode_over_mixed_precision_pages(cuda_device, fmt):
+    """The Quest path (metadata from the 8-bit keys, exact attention inside the chosen blocks) reads 4-bit values too."""
+    from llm_inference_optimization_b200 import workloads
+    B, Hq, Hkv, T = 2, 8, 2, 4096
+    Q, K, V, _ = workloads.planted_block_cache(B, Hq, Hkv, T, seed=9)
+    Q, K, V = Q.half(), K.half(), V.half()
+    kc, ks = (oracle.quantize_e4m3 if fmt == "fp8" else oracle.quantize_int8)(K)
+    vc, vs = oracle.quantize_int4(V)
+    perm = torch.randperm(B * (T // 16) + 3, generator=torch.Generator().manual_seed(2))
+    kp, ksp, table = oracle.build_paged_cache(kc, ks, 16, perm)
+    vp, vsp, _ = oracle.build_paged_cache(vc, vs, 16, perm)
+    lens = [T, 1500]
+    kv = mixed_cache((kp, vp, ksp, vsp, table), cuda_device, lens, B)
+    meta = paged.build_block_meta(kv, 64)
+    out, idx = paged.quest_sparse_decode(Q.to(cuda_device), kv, meta, D ** -0.5, 64, 8, return_indices=True)
+    torch.cuda.synchronize()
+    Kd, Vd = oracle.dequantize(kc, ks), oracle.dequantize_int4(vc, vs)
+    want = oracle.attend_selected_blocks(Q, Kd, Vd, idx.cpu().long(), 64, D ** -0.5, torch.tensor(lens, dtype=torch.int32))
+    assert (out.float().cpu() - want).abs().max().item() <= TOL
+    with pytest.raises(RuntimeError):   # more than 512 gathered tokens are not served over 4-bit values
+        paged.quest_sparse_decode(Q.to(cuda_device), kv, meta, D ** -0.5, 64, 16)
