@@ -454,17 +454,22 @@ def main():
         # percent of the PCIe link unused (51 against 54 GB/s measured)
         c1, c2 = torch.cuda.Stream(), torch.cuda.Stream()
         n_chunks = 8
-        chunk = (args.ctx + n_chunks - 1) // n_chunks
+        # chunks of whole token rows over the flattened (sequence, token) axis: every chunk is one contiguous range of
+        # bytes (a slice along the token axis of a [batch, ctx, ...] tensor is not, for batch > 1, and a strided
+        # host-to-device copy runs at a seventh of the link rate)
+        rows_total = batch * args.ctx
+        chunk = (rows_total + n_chunks - 1) // n_chunks
+        hKf, hVf, dKf, dVf = (t.view(rows_total, hkv_l, D) for t in (hK, hV, dK, dV))
 
         def e2e_host_kv():
             cur = torch.cuda.current_stream()
             c1.wait_stream(cur)
             c2.wait_stream(cur)
             for i in range(n_chunks):
-                lo, hi = i * chunk, min(args.ctx, (i + 1) * chunk)
+                lo, hi = i * chunk, min(rows_total, (i + 1) * chunk)
                 with torch.cuda.stream(c1 if i % 2 == 0 else c2):
-                    dK[:, lo:hi].copy_(hK[:, lo:hi], non_blocking=True)
-                    dV[:, lo:hi].copy_(hV[:, lo:hi], non_blocking=True)
+                    dKf[lo:hi].copy_(hKf[lo:hi], non_blocking=True)
+                    dVf[lo:hi].copy_(hVf[lo:hi], non_blocking=True)
             dQ.copy_(hQ, non_blocking=True)
             cur.wait_stream(c1)
             cur.wait_stream(c2)
@@ -498,8 +503,7 @@ def main():
             "h2d_bytes_per_step": qo + bytes_layer_rank, "d2h_bytes_per_step": qo,
             "ms_per_layer": ms_e2e, "steps": e2e_steps,
             "note": "one layer per step: pinned host Q, K, V -> device, fused_gqa(), output -> pinned host; PCIe-bound by "
-                    "construction (the whole KV cache crosses the bus every step), and at N > 1 every rank pushes its "
-                    "cache through the host's PCIe complex at once, so the per-GPU figure falls with N",
+                    "construction (the whole KV cache crosses the bus every step); every rank has its own link",
         }
         line["e2e_resident_kv"] = {
             "value": world * bytes_layer_rank / (ms_res * 1e-3) / 1e9, "unit": "GB/s",
@@ -507,7 +511,7 @@ def main():
             "note": "the reference API takes CUDA-resident caches (gqa_decode.cu:225): only the query goes in "
                     "and the output comes back each step",
         }
-        del dK, dV, hK, hV
+        del dK, dV, hK, hV, dKf, dVf, hKf, hVf
 
         # ---- the other two ops of the path at their configs, head-partitioned like the headline (weak scaling)
         line["other_configs"] = other_configs(dev, world, rank, peak, gather_ranks)
