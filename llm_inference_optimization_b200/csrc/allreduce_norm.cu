@@ -61,8 +61,8 @@ __device__ __forceinline__ uint4 pack8h(const float (&x)[8]) {
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
@@ -88,10 +88,10 @@ allreduce_residual_rmsnorm_kernel(const Peers pp, uint32_t* sync, uint16_t* __re
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(sync) + 1u;   // committed only after every CTA is done
 
-    if (blockIdx.x == 0 && tid < WORLD) {
-        __threadfence_system();
-        st_release_sys(pp.flags[tid] + rank, epoch);
-    }
+    // The partial sums this flag announces were written by an EARLIER kernel of this stream (the GEMM), so they are
+    // complete and visible to the peers before this kernel runs: the flag needs no fence in front of it, and a relaxed
+    // system-scope store saves the one or two microseconds a system-wide fence costs on every call.
+    if (blockIdx.x == 0 && tid < WORLD) st_relaxed_sys(pp.flags[tid] + rank, epoch);
     // Once a wait has run out the status word stays set and later calls do not wait again: a dead peer costs one
     // bounded wait, not one per call.
     const bool failed_before = *reinterpret_cast<volatile uint32_t*>(sync + 2) != 0u;
