@@ -331,6 +331,17 @@ int skv_skinny_gemm(const void* x, const void* w, void* out, void* workspace, si
 int skv_allreduce_residual_rmsnorm(const void* const* peer_partials, void* const* peer_flags, void* sync_words,
                                    void* resid, const void* weight, void* out, int rows, int hidden, float eps,
                                    int is_bf16, int rank, int world, unsigned max_spins, int device, void* stream);
+/* Push variant of the same step: instead of announcing its partial and letting the peers read it (two NVLink traversals
+ * in sequence), every rank WRITES its partial row into a receive region of every peer, in 8-byte words that carry 4 bytes
+ * of the partial and the 32-bit epoch of the call -- the data is its own flag, no fence is needed, one traversal.  The
+ * kernel then polls its own receive region (bounded like the waits above) and sums the ranks' rows in rank order.
+ * partial: this rank's [rows, hidden] partial sum in its own memory.  peer_recv[r]: device address, valid on THIS GPU,
+ * of rank r's receive region for this call: world * rows * hidden * 4 bytes ([source rank][rows][hidden / 2] words),
+ * zero-filled before the first call; consecutive calls must alternate between two regions.  hidden <= 4096.
+ * sync_words and every other argument as above.  No reference counterpart. */
+int skv_allreduce_residual_rmsnorm_push(const void* partial, void* const* peer_recv, void* sync_words, void* resid,
+                                        const void* weight, void* out, int rows, int hidden, float eps, int is_bf16,
+                                        int rank, int world, unsigned max_spins, int device, void* stream);
 
 #ifdef __cplusplus
 }

@@ -60,6 +60,7 @@ SIGNATURES = {
                               _i, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp]),
     "skv_residual_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp]),
     "skv_allreduce_residual_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, C.c_uint, _i, _vp]),
+    "skv_allreduce_residual_rmsnorm_push": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, C.c_uint, _i, _vp]),
     "skv_skinny_gemm_set_min_blocks": (_i, [_i]),
     "skv_skinny_gemm_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "skv_skinny_gemm": (_i, [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _vp]),

@@ -19,6 +19,7 @@ then sliced, so every tensor-parallel degree computes with the same full-model w
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Callable
 
@@ -332,12 +333,18 @@ class DecodeModel:
                            max_seq_len=self.max_seq_len, out=a, v_bits=cache.v_bits, after_append=self.overlap_append)
         return a
 
-    def enable_fused_allreduce(self, batch: int) -> None:
-        """Replace the two NCCL all-reduces per layer by the fused peer-memory kernel (CUDA, world > 1, fixed batch)."""
+    def enable_fused_allreduce(self, batch: int, protocol: str | None = None) -> None:
+        """Replace the two NCCL all-reduces per layer by the fused peer-memory kernel (CUDA, world > 1, fixed batch).
+        ``protocol``: ``"pull"`` (flag, then loads from the peers; the default) or ``"push"`` (every rank writes its
+        tagged partial into the peers' receive regions: measured faster on 2 GPUs, 6.8 against 7.7 us per call, and
+        slower from 4 GPUs up, where the doubled NVLink bytes of the tagged words cost more than the saved traversal);
+        ``SKV_ALLREDUCE_PROTOCOL`` in the environment overrides the default."""
         from . import glue
         if not self.fused_glue or self.shard.world == 1:
             raise RuntimeError("the fused all-reduce needs the CUDA glue path and more than one rank")
-        self.arn = glue.AllReduceNorm(batch, self.cfg.hidden, self.dtype, self.device, self.group)
+        if protocol is None:
+            protocol = os.environ.get("SKV_ALLREDUCE_PROTOCOL") or "pull"
+        self.arn = glue.AllReduceNorm(batch, self.cfg.hidden, self.dtype, self.device, self.group, protocol=protocol)
         self.fused_allreduce = True
 
     def step(self, tokens: Tensor) -> Tensor:

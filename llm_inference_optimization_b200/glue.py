@@ -100,14 +100,45 @@ class AllReduceNorm:
     FLAG_WORDS = 8
 
     def __init__(self, rows: int, hidden: int, dtype: torch.dtype, device, group=None, *, max_spins: int = 1 << 21,
-                 peers=None, rank: int | None = None):
+                 peers=None, rank: int | None = None, protocol: str = "pull", push_peers=None):
+        """``protocol="push"``: every rank writes its partial, tagged with the call's epoch word by word, into the peers'
+        receive regions and then polls its own (one NVLink traversal instead of a flag followed by remote loads;
+        ``skv_allreduce_residual_rmsnorm_push``, rows of up to 4096 elements).  ``push_peers`` (tests only):
+        ``push_peers[parity][r]`` = rank r's receive region, uint8 ``[world * rows * hidden * 4]``."""
         import ctypes
 
         _C._require(dtype in (torch.float16, torch.bfloat16), "dtype must be fp16 or bf16")
+        _C._require(protocol in ("pull", "push"), "protocol must be 'pull' or 'push'")
         self.rows, self.hidden, self.dtype, self.device = rows, hidden, dtype, torch.device(device)
         self.max_spins = int(max_spins)
+        self.protocol = protocol
         part_bytes = (rows * hidden * 2 + 255) // 256 * 256
         self.sync = torch.zeros(4, dtype=torch.int32, device=self.device)
+        if protocol == "push":
+            _C._require(hidden <= 4096, "the push protocol serves rows of up to 4096 elements")
+            arr_t = None
+            if push_peers is None:
+                import torch.distributed as dist
+                import torch.distributed._symmetric_memory as symm
+
+                group = group if group is not None else dist.group.WORLD
+                self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+                region = self.world * rows * hidden * 4
+                self._buf = symm.empty(2 * region, dtype=torch.uint8, device=self.device)
+                self._buf.zero_()
+                torch.cuda.synchronize(self.device)
+                handle = symm.rendezvous(self._buf, group)
+                dist.barrier(group)                  # every rank's receive regions are zero before anybody pushes
+                bases = [int(p) for p in handle.buffer_ptrs]
+                recv_ptrs = [[b + i * region for b in bases] for i in range(2)]
+            else:
+                self.world, self.rank = len(push_peers[0]), int(rank or 0)
+                self._keep = push_peers
+                recv_ptrs = [[t.data_ptr() for t in push_peers[i]] for i in range(2)]
+            self._partials = [torch.zeros((rows, hidden), dtype=dtype, device=self.device) for _ in range(2)]
+            arr = ctypes.c_void_p * self.world
+            self._recv_arr = [arr(*ptrs) for ptrs in recv_ptrs]
+            return
         if peers is None:
             import torch.distributed as dist
             import torch.distributed._symmetric_memory as symm
@@ -145,6 +176,13 @@ class AllReduceNorm:
                     "weight must be a contiguous [hidden] vector of the buffers' dtype")
         if out is None:
             out = torch.empty_like(resid)
+        if self.protocol == "push":
+            rc = _lib.load().skv_allreduce_residual_rmsnorm_push(
+                self._partials[i].data_ptr(), self._recv_arr[i], self.sync.data_ptr(), resid.data_ptr(), weight.data_ptr(),
+                out.data_ptr(), self.rows, self.hidden, float(eps), int(self.dtype == torch.bfloat16), self.rank, self.world,
+                self.max_spins, _C._dev_index(resid), torch.cuda.current_stream(resid.device).cuda_stream)
+            _lib.check(rc, "allreduce_residual_rmsnorm_push")
+            return out
         rc = _lib.load().skv_allreduce_residual_rmsnorm(
             self._part_arr[i], self._flag_arr, self.sync.data_ptr(), resid.data_ptr(), weight.data_ptr(), out.data_ptr(),
             self.rows, self.hidden, float(eps), int(self.dtype == torch.bfloat16), self.rank, self.world, self.max_spins,

@@ -102,11 +102,11 @@ def _tp_worker(rank, world, port, ret):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         outs = []
-        for fused in (False, True):
+        for fused in (False, "pull", "push"):
             m = ds.DecodeModel(CFG, shard_heads(CFG.Hq, CFG.Hkv, world, rank), dev, dtype=torch.bfloat16)
             m.init_cache(LENS, fill="normal")
             if fused:
-                m.enable_fused_allreduce(len(TOK))
+                m.enable_fused_allreduce(len(TOK), protocol=fused)
             for _ in range(3):
                 out = m.step(TOK.cuda())
             torch.cuda.synchronize()
@@ -133,10 +133,77 @@ def test_two_gpu_decode_step_without_nccl_allreduce(cuda_device):
     procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, ret)) for r in range(2)]
     for p in procs:
         p.start()
-    nccl, fused = (torch.from_numpy(a) for a in ret.get(timeout=300))
+    nccl, pull, push = (torch.from_numpy(a) for a in ret.get(timeout=300))
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
-    cos = torch.nn.functional.cosine_similarity(nccl, fused, dim=-1)
-    assert cos.min().item() > 0.999
-    assert (nccl - fused).abs().max().item() <= 3e-2 * nccl.abs().max().item()
+    for fused in (pull, push):
+        cos = torch.nn.functional.cosine_similarity(nccl, fused, dim=-1)
+        assert cos.min().item() > 0.999
+        assert (nccl - fused).abs().max().item() <= 3e-2 * nccl.abs().max().item()
+    assert torch.equal(pull, push)       # both protocols sum the ranks' rows in rank order
+
+
+def _ll_words(part, epoch):
+    """[rows, hidden] 16-bit values -> the 8-byte words a pushing rank writes: 4 bytes of data, then the epoch."""
+    data = part.contiguous().view(torch.int32).reshape(-1)              # two 16-bit values per word
+    return torch.stack((data, torch.full_like(data, epoch)), dim=1).reshape(-1)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_push_protocol_with_emulated_peers(cuda_device, dtype, world):
+    """The push variant: the peers' rows arrive in this rank's receive region as (data, epoch) words -- written by the
+    test here -- and this rank's own row goes out into every peer's region the same way."""
+    rows, hidden = 16, 4096
+    g = torch.Generator().manual_seed(10 + world)
+    region = world * rows * hidden * 4
+    recv = [[torch.zeros(region, dtype=torch.uint8, device=cuda_device) for _ in range(world)] for _ in range(2)]
+    arn = glue.AllReduceNorm(rows, hidden, dtype, cuda_device, push_peers=recv, rank=0, max_spins=2000, protocol="push")
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dtype).to(cuda_device)
+    resid = torch.randn(rows, hidden, generator=g).to(dtype).to(cuda_device)
+    ulp = 2.0 ** (-8 if dtype == torch.bfloat16 else -11)
+    per_src = rows * hidden // 2 * 2                                     # int32 words per source rank
+    for call in range(3):
+        i, epoch = call % 2, call + 1
+        parts = [(torch.randn(rows, hidden, generator=g) * 0.5).to(dtype).to(cuda_device) for _ in range(world)]
+        arn.partial(i).copy_(parts[0])
+        mine = recv[i][0].view(torch.int32)
+        for r in range(1, world):                                        # "peer r has pushed its row of this epoch"
+            mine[r * per_src:(r + 1) * per_src] = _ll_words(parts[r], epoch)
+        before = resid.clone()
+        out = arn.reduce_norm(i, resid, w, 1e-5)
+        torch.cuda.synchronize()
+        want_resid, want = _want(parts, before, w, 1e-5, dtype)
+        assert arn.status() == 0
+        assert torch.equal(resid, want_resid)
+        assert ((out.float() - want).abs() <= ulp * want.abs() + 1e-6).all()
+        for r in range(1, world):                                        # what this rank pushed into peer r's region
+            got = recv[i][r].view(torch.int32)[0:per_src]
+            assert torch.equal(got, _ll_words(parts[0], epoch))
+        assert int(arn.sync[0]) == epoch and int(arn.sync[1]) == 0
+
+
+def test_push_protocol_missing_peer_times_out_and_recovers(cuda_device):
+    rows, hidden, dtype, world = 4, 1024, torch.bfloat16, 2
+    g = torch.Generator().manual_seed(4)
+    region = world * rows * hidden * 4
+    recv = [[torch.zeros(region, dtype=torch.uint8, device=cuda_device) for _ in range(world)] for _ in range(2)]
+    arn = glue.AllReduceNorm(rows, hidden, dtype, cuda_device, push_peers=recv, rank=0, max_spins=500, protocol="push")
+    w = torch.ones(hidden, dtype=dtype, device=cuda_device)
+    resid = torch.randn(rows, hidden, generator=g).to(dtype).to(cuda_device)
+    parts = [(torch.randn(rows, hidden, generator=g) * 0.5).to(dtype).to(cuda_device) for _ in range(world)]
+    before = resid.clone()
+    arn.partial(0).copy_(parts[0])
+    arn.reduce_norm(0, resid, w, 1e-5)                       # nothing has arrived from peer 1
+    torch.cuda.synchronize()
+    assert arn.status() == 1 and torch.equal(resid, before) and int(arn.sync[0]) == 1
+    arn.sync[2] = 0
+    arn.partial(1).copy_(parts[0])
+    per_src = rows * hidden
+    recv[1][0].view(torch.int32)[per_src:2 * per_src] = _ll_words(parts[1], 2)
+    out = arn.reduce_norm(1, resid, w, 1e-5)
+    torch.cuda.synchronize()
+    want_resid, want = _want(parts, before, w, 1e-5, dtype)
+    assert arn.status() == 0 and torch.equal(resid, want_resid)
+    assert ((out.float() - want).abs() <= 2.0 ** -8 * want.abs() + 1e-6).all()
