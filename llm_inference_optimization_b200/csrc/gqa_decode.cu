@@ -93,28 +93,6 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     // the caller has declared that K, V and seq_lens are not produced by the previous kernel (early_kv) does the
     // wait move down to the consumers, and the producer streams K/V meanwhile.
     SKV_PHASE(0);
-    // What needs nothing from memory comes first: when this launch follows another one as its programmatic dependent,
-    // the shared-memory carve-up, the barrier set-up and the descriptor prefetch run while that kernel drains.
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t ring = smem_u32(smem);
-    size_t body = (size_t)p.stages * S::STAGE_BYTES;
-    if (epilogue_smem_bytes<D>() > body) body = epilogue_smem_bytes<D>();
-    const uint32_t full_bar = ring + (uint32_t)body;
-    const uint32_t empty_bar = full_bar + p.stages * 8;
-    int* last_flag = reinterpret_cast<int*>(smem + body + 2 * p.stages * 8);
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(full_bar + s * 8, 1);
-            mbar_init(empty_bar + s * 8, CONSUMER_WARPS);
-        }
-        fence_barrier_init();
-    }
-    if (threadIdx.x == CONSUMER_THREADS) {
-        tma_prefetch_desc(&tmK);
-        tma_prefetch_desc(&tmV);
-    }
-
     if (!p.early_kv) pdl_wait_prior_grids();
     int len, n_splits, tiles_per_split = p.tiles_per_split;
     if (p.list_items > 0) {   // work-list schedule of a ragged batch (see worklist_item)
@@ -137,11 +115,30 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const int t_begin = split * tokens_per_split;
     const int t_end = min(len, t_begin + tokens_per_split);
     const int ntiles = (t_end - t_begin + TILE - 1) / TILE;  // 0 for an empty sequence
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t ring = smem_u32(smem);
+    size_t body = (size_t)p.stages * S::STAGE_BYTES;
+    if (epilogue_smem_bytes<D>() > body) body = epilogue_smem_bytes<D>();
+    const uint32_t full_bar = ring + (uint32_t)body;
+    const uint32_t empty_bar = full_bar + p.stages * 8;
+    int* last_flag = reinterpret_cast<int*>(smem + body + 2 * p.stages * 8);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full_bar + s * 8, 1);
+            mbar_init(empty_bar + s * 8, CONSUMER_WARPS);
+        }
+        fence_barrier_init();
+    }
     __syncthreads();
     SKV_PHASE(1);
     // ------------------------------------------------------------------ producer
     if (warp == CONSUMER_WARPS) {
         if (lane == 0) {
+            tma_prefetch_desc(&tmK);
+            tma_prefetch_desc(&tmV);
             const uint64_t policy = l2_policy_evict_first();
             int s = 0;        // stage and ring-pass phase advance incrementally: no divisions in this loop
             uint32_t ph = 0;

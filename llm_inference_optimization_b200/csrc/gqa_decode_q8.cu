@@ -192,28 +192,6 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     int split = blockIdx.y, b = blockIdx.z;
     SKV_PHASE(0);
 
-    // What needs nothing from memory comes first (it overlaps the previous kernel's tail when this launch is its
-    // programmatic dependent): shared-memory carve-up, barrier set-up, descriptor prefetch.
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t ring = smem_u32(smem);
-    size_t body = (size_t)p.stages * STAGE_BYTES;
-    if (merge_smem_bytes<D, Q8_WARPS>() > body) body = merge_smem_bytes<D, Q8_WARPS>();
-    const uint32_t full_bar = ring + (uint32_t)body;
-    const uint32_t empty_bar = full_bar + p.stages * 8;
-    int* last_flag = reinterpret_cast<int*>(smem + body + 2 * p.stages * 8);
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(full_bar + s * 8, Q8_PRODUCERS);
-            mbar_init(empty_bar + s * 8, CONSUMER_WARPS);
-        }
-        fence_barrier_init();
-    }
-    if (threadIdx.x == Q8_CONSUMER_THREADS) {
-        tma_prefetch_desc(&tmK);
-        tma_prefetch_desc(&tmV);
-    }
-
     // Ordered like any other kernel unless the caller declared the cache static (see the fp16 kernel).
     if (!p.early_kv) pdl_wait_prior_grids();
     SKV_PHASE(1);
@@ -232,6 +210,23 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const int t_begin = split * tokens_per_split;
     const int t_end = min(len, t_begin + tokens_per_split);
     const int ntiles = (t_end - t_begin + TILE - 1) / TILE;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t ring = smem_u32(smem);
+    size_t body = (size_t)p.stages * STAGE_BYTES;
+    if (merge_smem_bytes<D, Q8_WARPS>() > body) body = merge_smem_bytes<D, Q8_WARPS>();
+    const uint32_t full_bar = ring + (uint32_t)body;
+    const uint32_t empty_bar = full_bar + p.stages * 8;
+    int* last_flag = reinterpret_cast<int*>(smem + body + 2 * p.stages * 8);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full_bar + s * 8, Q8_PRODUCERS);
+            mbar_init(empty_bar + s * 8, CONSUMER_WARPS);
+        }
+        fence_barrier_init();
+    }
     __syncthreads();
 
     // ------------------------------------------------------------------ producers
@@ -245,6 +240,10 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     // read per lane per 32 tiles; lane 0 does the waiting and issuing.
     if (warp >= Q8_WARPS) {
         const int pw = warp - Q8_WARPS;
+        if (lane == 0 && pw == 0) {
+            tma_prefetch_desc(&tmK);
+            tma_prefetch_desc(&tmV);
+        }
         const uint64_t policy = l2_policy_evict_first();
         const int P = p.page_size;
         const bool big = p.mode == Q8_SEPARATE64;
