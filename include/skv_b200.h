@@ -160,6 +160,12 @@ int skv_quest_num_blocks(int N, int block_size);
  * shared-memory ring by TMA (up to 8 query heads per kv-head); on = 0: with the register-load kernel (also used for
  * larger groups).  Both sum the same exact products, in different orders.  Process-wide.  No reference counterpart. */
 int skv_quest_set_ring_scores(int on);
+/* on = 1: where it applies (tensor-core scoring on, Hq/Hkv <= 8, at most 2048 blocks per sequence)
+ * skv_quest_decode is ONE kernel: thread-block clusters of Hq/Hkv CTAs (the query heads of a kv-head) stream the
+ * kv-head's metadata together, score it for all heads and hand every head its scores through distributed shared memory,
+ * then each CTA selects and attends; on = 0 (default): a scoring kernel followed by the select/attend kernel (the two
+ * paths measure the same).  The scores are the same numbers either way.  Process-wide.  No reference counterpart. */
+int skv_quest_set_fused(int on);
 size_t skv_quest_workspace_bytes(int B, int Hq, int N, int block_size);
 int skv_quest_build_meta(const void* k_pool, const float* k_scale_pool, const int* page_table, const int* seq_lens,
                          void* meta_out, int B, int N, int Hkv, int D, int kv_dtype, int block_size,

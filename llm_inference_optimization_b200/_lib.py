@@ -53,6 +53,7 @@ SIGNATURES = {
                                   _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp]),
     "skv_quest_num_blocks": (_i, [_i, _i]),
     "skv_quest_set_ring_scores": (_i, [_i]),
+    "skv_quest_set_fused": (_i, [_i]),
     "skv_quest_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "skv_quest_build_meta": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i,
                                   _ll, _ll, _ll, _ll, _ll, _vp, _i, _vp]),

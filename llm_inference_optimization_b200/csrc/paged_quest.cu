@@ -19,6 +19,8 @@
 //       the block scores, then scores / softmax / weighted value sum over the
 //       <= k * block_size gathered tokens, all fp32; the V rows travel to shared
 //       memory as asynchronous copies while the K rows are scored.
+#include <cstring>
+
 #include <cuda_fp8.h>
 
 #include "skv_common.cuh"
@@ -431,6 +433,7 @@ quest_scores_mma_kernel(const __grid_constant__ CUtensorMap tmM, const ScorePara
     }
 }
 
+inline int& fused_flag() { static int on = 0; return on; }   // 1: score inside the attend kernel (clusters of G CTAs); measures the same (config 4: 38.9 against 38.0 us)
 inline int& ring_scores_flag() { static int on = 1; return on; }   // tensor-core scoring: config 4 end to end 46 -> 40 us
 inline bool use_ring_scores() { return ring_scores_flag() != 0; }
 
@@ -464,9 +467,16 @@ constexpr size_t ATT_DYN_SMEM = (size_t)VSTAGE_TOKENS * (D + 4);    // V codes [
 // in one batch of 16-byte loads (8 lanes per row, 64 rows per pass, 8 passes in flight) while the V rows and V scales
 // of the same tokens travel to shared memory as per-thread asynchronous copies issued before the K loads -- by the
 // time the softmax weights exist the V rows are already on chip.
-template <int KVT>
+// FUSED: the kernel also scores the blocks itself, and no scoring kernel runs before it.  It is launched in clusters of
+// G CTAs -- the query heads of one kv-head, cluster rank = head within the group.  CTA r streams the 64-block tiles
+// r, r + G, ... of the row's metadata (TMA into a two-stage ring that lies where the V rows are staged later), scores
+// each tile for ALL heads of the group on the tensor cores exactly like quest_scores_mma_kernel, and PUSHES every head's
+// scores into that head's CTA (stores into distributed shared memory, into the array that later holds the token
+// weights).  After one cluster barrier every CTA has the scores of its own head in its shared memory: the score round
+// trip through global memory, one launch and the wait between the two kernels are gone.  nb <= MAX_SEL_TOKENS.
+template <int KVT, bool FUSED>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
-quest_select_attend_kernel(const AttendParams p) {
+quest_select_attend_kernel(const __grid_constant__ CUtensorMap tmM, const AttendParams p) {
     extern __shared__ __align__(16) uint8_t vstage[];   // ATT_DYN_SMEM bytes
     __shared__ uint32_t tk[TopkSmem<ATT_THREADS>::WORDS];
     __shared__ int sel[MAX_TOPK];
@@ -485,9 +495,109 @@ quest_select_attend_kernel(const AttendParams p) {
     const int nb = (len + p.block_size - 1) / p.block_size;  // blocks this sequence really has
     SKV_PHASE(0);
     for (int i = tid; i < D; i += ATT_THREADS) qs[i] = __half2float(p.q[(long long)row * D + i]);
-    pdl_wait_prior_grids();   // launched as a programmatic dependent of the scoring kernel: its results are complete from here on
-    SKV_PHASE(1);
     const float* sc = p.scores + (long long)row * p.nb;
+    if (FUSED) {
+        __shared__ __align__(8) unsigned long long fbar[4];   // full[2], empty[2]
+        constexpr int FS = 2;                                  // ring stages of MS_STAGE_BYTES
+        const uint32_t ring = (smem_u32(vstage) + 1023u) & ~1023u;
+        const uint32_t full_bar = smem_u32(&fbar[0]), empty_bar = smem_u32(&fbar[2]);
+        const int G = p.G, crank = (int)cluster_cta_rank();
+        const int rowh = row / G;                              // (b, kv-head)
+        const int tiles = (p.nb + MS_TILE - 1) / MS_TILE;
+        const int my_tiles = crank < tiles ? (tiles - crank + G - 1) / G : 0;
+        if (tid == 0) {
+            for (int st = 0; st < FS; ++st) {
+                mbar_init(full_bar + st * 8, 1);
+                mbar_init(empty_bar + st * 8, MS_CONSUMER_WARPS);
+            }
+            fence_barrier_init();
+        }
+        __syncthreads();
+        if (warp == MS_CONSUMER_WARPS) {            // producer: one lane, four boxes per tile
+            if (lane == 0) {
+                tma_prefetch_desc(&tmM);
+                const uint64_t policy = l2_policy_evict_first();
+                int st = 0;
+                uint32_t ph = 0;
+                for (int i = 0; i < my_tiles; ++i) {
+                    if (i >= FS && !mbar_wait(empty_bar + st * 8, ph ^ 1u)) {
+                        atomicOr(p.status, SKV_DEV_TIMEOUT);
+                        break;
+                    }
+                    const uint32_t dst = ring + st * MS_STAGE_BYTES, bar = full_bar + st * 8;
+                    mbar_expect_tx(bar, MS_STAGE_BYTES);
+                    const int first = rowh * p.nb + (crank + i * G) * MS_TILE;
+#pragma unroll
+                    for (int hf = 0; hf < 4; ++hf) tma_load_2d(dst + hf * MS_BOX_BYTES, &tmM, bar, hf * 64, first, policy);
+                    if (++st == FS) { st = 0; ph ^= 1u; }
+                }
+            }
+        } else if (warp < MS_CONSUMER_WARPS) {      // consumers: warp w scores blocks 16w .. 16w+15 of every tile
+            const int g = lane >> 2, tq = lane & 3, lj = lane >> 3, r8 = lane & 7;
+            const uint32_t a_row_off = (uint32_t)((warp * 16 + (lj & 1) * 8 + r8) * 128);
+            uint32_t qb[16][2];
+            {
+                const __half* qrow = p.q + ((long long)rowh * G + g) * D;
+                const __half2 zero = __float2half2_rn(0.f);
+#pragma unroll
+                for (int kk2 = 0; kk2 < 8; ++kk2) {
+                    __half2 u = zero, v = zero;
+                    if (g < G) {
+                        u = *reinterpret_cast<const __half2*>(qrow + kk2 * 16 + tq * 2);
+                        v = *reinterpret_cast<const __half2*>(qrow + kk2 * 16 + 8 + tq * 2);
+                    }
+                    const __half2 un = __hmin2(u, zero), vn = __hmin2(v, zero), up = __hmax2(u, zero), vp = __hmax2(v, zero);
+                    qb[kk2][0] = *reinterpret_cast<const uint32_t*>(&un);
+                    qb[kk2][1] = *reinterpret_cast<const uint32_t*>(&vn);
+                    qb[kk2 + 8][0] = *reinterpret_cast<const uint32_t*>(&up);
+                    qb[kk2 + 8][1] = *reinterpret_cast<const uint32_t*>(&vp);
+                }
+            }
+            // head 2tq lives in CTA 2tq of the cluster, head 2tq+1 in CTA 2tq+1: where this lane's results go
+            const uint32_t w_local = smem_u32(w);
+            const uint32_t dst0 = 2 * tq < G ? cluster_map(w_local, 2 * tq) : 0u;
+            const uint32_t dst1 = 2 * tq + 1 < G ? cluster_map(w_local, 2 * tq + 1) : 0u;
+            int st = 0;
+            uint32_t ph = 0;
+            for (int i = 0; i < my_tiles; ++i) {
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(full_bar + st * 8, ph) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    if (lane == 0) atomicOr(p.status, SKV_DEV_TIMEOUT);
+                    break;
+                }
+                const uint32_t base = ring + st * MS_STAGE_BYTES + a_row_off;
+                float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int kk2 = 0; kk2 < 16; ++kk2) {
+                    const int c = 2 * kk2 + (lj >> 1);
+                    uint32_t a[4];
+                    ldsm_x4(base + (uint32_t)(c >> 3) * MS_BOX_BYTES + (uint32_t)(((c & 7) ^ r8) << 4), a[0], a[1], a[2], a[3]);
+                    if (kk2 & 1) mma_f16(acc1, a, qb[kk2][0], qb[kk2][1]);
+                    else mma_f16(acc0, a, qb[kk2][0], qb[kk2][1]);
+                }
+                const int j = (crank + i * G) * MS_TILE + warp * 16 + g;
+                if (dst0) {
+                    if (j < p.nb) st_cluster_f32(dst0 + j * 4, (acc0[0] + acc1[0]) * p.scale);
+                    if (j + 8 < p.nb) st_cluster_f32(dst0 + (j + 8) * 4, (acc0[2] + acc1[2]) * p.scale);
+                }
+                if (dst1) {
+                    if (j < p.nb) st_cluster_f32(dst1 + j * 4, (acc0[1] + acc1[1]) * p.scale);
+                    if (j + 8 < p.nb) st_cluster_f32(dst1 + (j + 8) * 4, (acc0[3] + acc1[3]) * p.scale);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar + st * 8);
+                if (++st == FS) { st = 0; ph ^= 1u; }
+            }
+        }
+        __syncwarp();
+        cluster_barrier();    // every head's scores have arrived in its CTA (and every CTA is done with its ring)
+        sc = w;
+    } else {
+        pdl_wait_prior_grids();   // launched as a programmatic dependent of the scoring kernel: its results are complete from here on
+    }
+    SKV_PHASE(1);
     const int kk = min(p.top_k, nb);
     if (kk <= 32 && nb <= ATT_THREADS * 4) block_topk_small<ATT_THREADS, 4>(sc, nb, kk, sel, reinterpret_cast<unsigned long long*>(tk));
     else if (kk <= 32 && nb <= ATT_THREADS * 16) block_topk_small<ATT_THREADS, 16>(sc, nb, kk, sel, reinterpret_cast<unsigned long long*>(tk));
@@ -672,6 +782,16 @@ int skv_debug_phase_ts_quest(unsigned long long* out) {
 }
 #endif
 
+// 1: where it applies (tensor-core scoring on, up to 8 heads per group, at most 2048 blocks per sequence) ONE kernel
+// scores the blocks and attends: clusters of G CTAs share a kv-head's metadata and exchange the scores through
+// distributed shared memory; 0 (default): the scoring kernel followed by the select/attend kernel.  The two measure
+// the same on B200 -- the fused scoring phase streams at the full HBM rate (10.5 us for 67 MB), but the two-kernel path
+// hides the second launch and its prologue behind the scoring kernel.  Process-wide.
+int skv_quest_set_fused(int on) {
+    quest::fused_flag() = on ? 1 : 0;
+    return SKV_OK;
+}
+
 // 1 (default): the block scores are computed by the tensor-core kernel that streams the metadata through a
 // shared-memory ring (up to 8 query heads per kv-head; larger groups always use the other kernel); 0: by the
 // register-load kernel.  The two sum the same exact products in different
@@ -767,7 +887,26 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
     sp.Hq = Hq; sp.Hkv = Hkv; sp.G = G; sp.nb = nb; sp.scale = scale;
     const long long rows = (long long)B * Hkv;
     const long long total_blocks = rows * nb;
-    if (quest::use_ring_scores() && G <= 8) {
+    // One launch instead of two when the group's heads can share the scoring as a cluster: the attend kernel scores the
+    // blocks itself (see its FUSED variant).  Needs the scores of a row to fit the token-weight array.
+    static int cluster_ok[64][9] = {{0}};   // [device][G]: 0 unknown, 1 no, 2 yes
+    bool fused = quest::fused_flag() && quest::use_ring_scores() && G <= 8 && nb <= quest::MAX_SEL_TOKENS && device < 64;
+    CUtensorMap tmF;
+    memset(&tmF, 0, sizeof(tmF));
+    if (fused) {
+        if (cluster_ok[device][G] == 0) {
+            bool ok = cudaFuncSetAttribute(quest::quest_select_attend_kernel<SKV_KV_E4M3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)quest::ATT_DYN_SMEM) == cudaSuccess &&
+                      cudaFuncSetAttribute(quest::quest_select_attend_kernel<SKV_KV_I8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)quest::ATT_DYN_SMEM) == cudaSuccess;
+            ok = ok && max_active_clusters_x(quest::quest_select_attend_kernel<SKV_KV_E4M3, true>, dim3(quest::ATT_THREADS), quest::ATT_DYN_SMEM, G) > 0;
+            cudaGetLastError();
+            cluster_ok[device][G] = ok ? 2 : 1;
+        }
+        fused = cluster_ok[device][G] == 2;
+    }
+    if (fused) {
+        const int mrc = make_matrix_tmap(&tmF, meta, total_blocks, 2 * quest::D, 2 * quest::D, quest::MS_TILE, 64, false);
+        if (mrc) return mrc;
+    } else if (quest::use_ring_scores() && G <= 8) {
         // tensor-core scoring: one persistent CTA per SM, each a contiguous range of (row, 64-block tile) items
         static bool ms_configured[64] = {false};
         if (device < 64 && !ms_configured[device]) {
@@ -833,12 +972,19 @@ int skv_quest_decode(const void* q, const void* k_pool, const void* v_pool, cons
     ap.status = reinterpret_cast<int*>(workspace);   // status word at offset 0, as skv_workspace_status reads it
     static bool configured[64] = {false};
     if (device < 64 && !configured[device]) {
-        SKV_CUDA_TRY(cudaFuncSetAttribute(quest::quest_select_attend_kernel<SKV_KV_E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)quest::ATT_DYN_SMEM));
-        SKV_CUDA_TRY(cudaFuncSetAttribute(quest::quest_select_attend_kernel<SKV_KV_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)quest::ATT_DYN_SMEM));
+        SKV_CUDA_TRY(cudaFuncSetAttribute(quest::quest_select_attend_kernel<SKV_KV_E4M3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)quest::ATT_DYN_SMEM));
+        SKV_CUDA_TRY(cudaFuncSetAttribute(quest::quest_select_attend_kernel<SKV_KV_I8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)quest::ATT_DYN_SMEM));
         configured[device] = true;
     }
-    if (kv_dtype == SKV_KV_E4M3) SKV_CUDA_TRY(launch_pdl(quest::quest_select_attend_kernel<SKV_KV_E4M3>, dim3((unsigned)(B * Hq)), dim3(quest::ATT_THREADS), quest::ATT_DYN_SMEM, st, ap));
-    else SKV_CUDA_TRY(launch_pdl(quest::quest_select_attend_kernel<SKV_KV_I8>, dim3((unsigned)(B * Hq)), dim3(quest::ATT_THREADS), quest::ATT_DYN_SMEM, st, ap));
+    const dim3 agrid((unsigned)(B * Hq)), ablock(quest::ATT_THREADS);
+    if (fused) {   // clusters of G CTAs along x: the query heads of one kv-head
+        if (kv_dtype == SKV_KV_E4M3) SKV_CUDA_TRY(launch_cluster_x(quest::quest_select_attend_kernel<SKV_KV_E4M3, true>, agrid, ablock, quest::ATT_DYN_SMEM, st, G, tmF, ap));
+        else SKV_CUDA_TRY(launch_cluster_x(quest::quest_select_attend_kernel<SKV_KV_I8, true>, agrid, ablock, quest::ATT_DYN_SMEM, st, G, tmF, ap));
+    } else if (kv_dtype == SKV_KV_E4M3) {
+        SKV_CUDA_TRY(launch_pdl(quest::quest_select_attend_kernel<SKV_KV_E4M3, false>, agrid, ablock, quest::ATT_DYN_SMEM, st, tmF, ap));
+    } else {
+        SKV_CUDA_TRY(launch_pdl(quest::quest_select_attend_kernel<SKV_KV_I8, false>, agrid, ablock, quest::ATT_DYN_SMEM, st, tmF, ap));
+    }
     SKV_CUDA_TRY(cudaGetLastError());
     return SKV_OK;
 }

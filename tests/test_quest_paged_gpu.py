@@ -122,3 +122,30 @@ def test_ring_and_register_scoring_kernels_agree(cuda_device, lib, B, Hq, Hkv, T
     assert torch.equal(res[1][0], res[0][0])
     want = oracle.attend_selected_blocks(Q, Kd, Vd, res[1][1].cpu().long(), 64, 128 ** -0.5, lens)
     assert (res[1][0].float().cpu() - want).abs().max().item() <= TOL
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,T,top", [(2, 32, 8, 8192, 8), (3, 8, 2, 2048, 4), (1, 8, 1, 131072, 8), (2, 6, 2, 4096, 8), (1, 4, 4, 1024, 2)])
+def test_one_kernel_and_two_kernel_paths_agree(cuda_device, lib, B, Hq, Hkv, T, top):
+    """The decode can run as one kernel (clusters of Hq/Hkv CTAs score a kv-head's metadata together and hand every
+    head its scores through distributed shared memory); by default a scoring kernel runs first.  The scores are the
+    same numbers, so blocks and outputs are identical -- for groups of 8, 4, 3 and 1 heads, ragged lengths and the
+    longest sequence the fused path serves (2048 blocks)."""
+    Q, K, V, _ = workloads.planted_block_cache(B, Hq, Hkv, T, seed=31)
+    lens = None if B == 1 else torch.tensor([T, T // 3 + 5, 70][:B], dtype=torch.int32)
+    kv, Kd, Vd = paged_case(Q, K, V, "fp8", cuda_device, seed=8, seq_lens=lens)
+    meta = paged.build_block_meta(kv, 64)
+    res = {}
+    try:
+        for fused in (1, 0):
+            assert lib.skv_quest_set_fused(fused) == 0
+            for _ in range(2):
+                res[fused] = paged.quest_sparse_decode(Q.to(cuda_device), kv, meta, 128 ** -0.5, 64, top, return_indices=True)
+            torch.cuda.synchronize()
+    finally:
+        lib.skv_quest_set_fused(0)
+    from llm_inference_optimization_b200 import _workspace
+    assert all(_workspace.status(w) == 0 for w in _workspace.all_of("quest", cuda_device))
+    assert torch.equal(res[1][1], res[0][1])
+    assert torch.equal(res[1][0], res[0][0])
+    want = oracle.attend_selected_blocks(Q, Kd, Vd, res[1][1].cpu().long(), 64, 128 ** -0.5, lens)
+    assert (res[1][0].float().cpu() - want).abs().max().item() <= TOL
