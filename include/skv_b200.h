@@ -215,6 +215,10 @@ size_t skv_token_sparse_workspace_bytes(int B, int H, int S, int T);
  * shared-memory ring by TMA; on = 0: always the register-load kernel.  Both sum the same exact products in different
  * orders.  Process-wide.  The device status word (bit SKV_DEV_TIMEOUT) is at offset 0 of the workspace. */
 int skv_token_sparse_set_mma_scores(int on);
+/* on = 1 (default): the tensor-core scoring kernel cuts a row into chunks of unequal length (1.5 down to 0.5 times the
+ * mean), so that the CTAs' per-chunk candidate selections are spread over time instead of coinciding wave after wave;
+ * on = 0: equal chunks.  Same results either way.  Process-wide.  No reference counterpart. */
+int skv_token_sparse_set_stagger(int on);
 int skv_token_sparse_decode(const void* q, const void* k, const void* v, void* out, int* topk_idx_out,
                             void* workspace, size_t workspace_bytes, int B, int H, int S, int T, int D,
                             long long q_stride_b, long long q_stride_h, long long q_stride_s,

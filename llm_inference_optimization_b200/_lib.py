@@ -34,6 +34,7 @@ SIGNATURES = {
     "skv_gqa_decode_mass": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _ll, _ll, _ll, _vp, _f, _i, _vp]),
     "skv_token_sparse_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "skv_token_sparse_set_mma_scores": (_i, [_i]),
+    "skv_token_sparse_set_stagger": (_i, [_i]),
     "skv_token_sparse_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i,
                                      _ll, _ll, _ll, _ll, _ll, _ll, _i, _i, _f, _i, _vp]),
     "skv_block_sparse_workspace_bytes": (_sz, [_i, _i, _i, _i]),

@@ -27,7 +27,7 @@ constexpr int MAX_KEEP = 4096;  // top_k + sink_tokens upper bound
 constexpr int MAX_CAND_K = 256;  // largest top_k served by the per-chunk candidate path
 
 // Chunk slots reserved in the workspace for candidates (scores CTAs: about 8 per SM plus one per row).
-inline long long cand_capacity_chunks(long long rows) { return 2048 + 2 * rows; }
+inline long long cand_capacity_chunks(long long rows) { return 4096 + 2 * rows; }
 
 struct ScoreParams {
     const __half* q;   // element (b,h,s,d) at b*q_sb + h*q_sh + s*q_ss + d
@@ -127,6 +127,13 @@ token_scores_kernel(const ScoreParams p, int tokens_per_cta) {
 // its previous use; every wait is bounded, and a wait that runs out sets SKV_DEV_TIMEOUT and ends the CTA's loop.
 // grid (ceil(T / tokens_per_cta), H, B)
 constexpr int MMA_TILE = 128;     // tokens per stage: 16 per warp
+// Staggered chunks: chunk x of n covers the tiles [chunk_first_tile(x), chunk_first_tile(x + 1)) of a row of nt tiles,
+// with lengths falling linearly from 1.5 to 0.5 times the mean.  CTAs of equal chunks start together, stream together
+// and run their candidate selection together, wave after wave, and the memory system idles during every selection;
+// unequal chunks spread the selections over time.
+__host__ __device__ inline int chunk_first_tile(int x, int n, int nt) {
+    return (int)((long long)nt * (3LL * x * n - (long long)x * x) / (2LL * n * n));
+}
 template <int D>
 __host__ __device__ constexpr int mma_stage_bytes() { return MMA_TILE * D * 2; }
 template <int D, int MMA_STAGES>
@@ -138,7 +145,7 @@ __host__ __device__ constexpr size_t mma_ring_bytes() { return (size_t)MMA_STAGE
 template <int D, int MMA_STAGES>
 __global__ void __launch_bounds__(SCORE_THREADS, MMA_STAGES == 2 ? 3 : 2)
 token_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const ScoreParams p, const KvMapPos pos,
-                        int tokens_per_cta, int* status) {
+                        int tokens_per_cta, int stagger_tiles, int* status) {
     pdl_launch_dependents();
     constexpr int NH = D / 64, KSTEPS = D / 16, HALF_BYTES = MMA_TILE * 128, STAGE = mma_stage_bytes<D>();
     extern __shared__ uint8_t mma_raw[];
@@ -149,7 +156,10 @@ token_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const ScorePara
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, tq = lane & 3, lj = lane >> 3, r8 = lane & 7;
     const int h = blockIdx.y, b = blockIdx.z;
-    const int t0 = blockIdx.x * tokens_per_cta, t1 = min(p.T, t0 + tokens_per_cta);
+    // stagger_tiles > 0: the row's tile count; the chunks are the staggered ones
+    const int t0 = stagger_tiles > 0 ? chunk_first_tile(blockIdx.x, gridDim.x, stagger_tiles) * MMA_TILE : blockIdx.x * tokens_per_cta;
+    const int t1 = stagger_tiles > 0 ? min(p.T, chunk_first_tile(blockIdx.x + 1, gridDim.x, stagger_tiles) * MMA_TILE)
+                                     : min(p.T, t0 + tokens_per_cta);
     const int ntiles = (t1 - t0 + MMA_TILE - 1) / MMA_TILE;
     if (tid == 0) {
         for (int s = 0; s < MMA_STAGES; ++s) mbar_init(full_bar + s * 8, 1);
@@ -385,6 +395,7 @@ static size_t attend_smem() {
 // 1 (default): one query per (b, h) with D = 64 or 128 is scored by the tensor-core kernel; 0: always the register-load
 // kernel.  The two sum the same exact products in different orders.
 inline int& mma_scores_flag() { static int on = 1; return on; }
+inline int& stagger_flag() { static int on = 1; return on; }   // chunks of unequal length for the tensor-core scoring kernel
 
 template <int D>
 static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int device, cudaStream_t st, float* cand_base, int* status) {
@@ -405,6 +416,25 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     if (tokens_per_cta < 512) tokens_per_cta = 512;
     const bool mma_path = (D == 64 || D == 128) && mma_scores_flag() && sp.S == 1;
     dim3 g1((sp.T + tokens_per_cta - 1) / tokens_per_cta, sp.H, B * sp.S);
+    // Staggered chunks for the tensor-core kernel: as many as keep the longest (the first) within the tokens that the
+    // ring's shared-memory budget leaves for a chunk's scores (2048 beside the short ring, 3584 beside the long one).
+    int stagger_tiles = 0;
+    const int stagger_cap = tokens_per_cta <= 2048 ? 2048 : 3584;
+    if (mma_path && stagger_flag() && sp.T >= 16 * 1024) {
+        const int nt = (sp.T + MMA_TILE - 1) / MMA_TILE;
+        int n = (int)g1.x;
+        auto longest = [&](int nn) {
+            int m = 0;
+            for (int x = 0; x < nn; ++x) m = std::max(m, chunk_first_tile(x + 1, nn, nt) - chunk_first_tile(x, nn, nt));
+            return m;
+        };
+        while (longest(n) * MMA_TILE > stagger_cap) ++n;
+        if ((long long)rows * n <= cand_capacity_chunks(rows)) {
+            stagger_tiles = nt;
+            g1.x = (unsigned)n;
+            tokens_per_cta = stagger_cap;
+        }
+    }
     ScoreParams sp2 = sp;
     AttendParams ap2 = ap;
     const int nchunks = (int)g1.x;
@@ -447,8 +477,8 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
                     SKV_CUDA_TRY(cudaFuncSetAttribute(token_scores_mma_kernel<D, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma));
                 configured_mma[device][short_ring] = (int)smem_mma;
             }
-            if (short_ring) token_scores_mma_kernel<D, 2><<<g1, SCORE_THREADS, smem_mma, st>>>(tmK, sp2, pos, tokens_per_cta, status);
-            else token_scores_mma_kernel<D, 3><<<g1, SCORE_THREADS, smem_mma, st>>>(tmK, sp2, pos, tokens_per_cta, status);
+            if (short_ring) token_scores_mma_kernel<D, 2><<<g1, SCORE_THREADS, smem_mma, st>>>(tmK, sp2, pos, tokens_per_cta, stagger_tiles, status);
+            else token_scores_mma_kernel<D, 3><<<g1, SCORE_THREADS, smem_mma, st>>>(tmK, sp2, pos, tokens_per_cta, stagger_tiles, status);
             scored = true;
         }
     }
@@ -470,6 +500,13 @@ extern "C" {
 // the register-load kernel.  Process-wide.
 int skv_token_sparse_set_mma_scores(int on) {
     tsp::mma_scores_flag() = on ? 1 : 0;
+    return SKV_OK;
+}
+
+// 1 (default): the tensor-core scoring kernel's chunks have unequal lengths (1.5 to 0.5 times the mean along a row), so
+// that the CTAs' candidate selections do not all fall into the same moments; 0: equal chunks.  Same results.  Process-wide.
+int skv_token_sparse_set_stagger(int on) {
+    tsp::stagger_flag() = on ? 1 : 0;
     return SKV_OK;
 }
 

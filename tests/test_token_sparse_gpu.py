@@ -124,3 +124,28 @@ def test_tensor_core_and_register_scoring_agree(cuda_device, B, H, T, D, k, sink
     if boundary_gap(Q, K, k) > 1e-5:
         assert torch.equal(res[1][1], res[0][1])
         assert torch.equal(res[1][1][:, :, 0, :min(k, T)].cpu().long(), oracle.token_topk_sets(Q, K, k))
+
+
+@pytest.mark.parametrize("H,T,k", [(4, 16384, 32), (2, 40000, 8), (3, 70001, 32), (1, 131072, 64), (1, 300000, 32)])
+def test_staggered_and_equal_chunks_select_the_same_tokens(cuda_device, H, T, k):
+    """The tensor-core scoring kernel cuts a row into chunks of unequal length by default; with equal chunks the scores
+    are the same numbers, so outputs and indices are identical bit for bit."""
+    from llm_inference_optimization_b200 import _lib, _workspace
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(T)
+    Q = torch.randn(1, H, 1, 128, generator=g).half().to(cuda_device)
+    K = torch.randn(1, H, T, 128, generator=g).half().to(cuda_device)
+    V = torch.randn(1, H, T, 128, generator=g).half().to(cuda_device)
+    res = {}
+    try:
+        for mode in (1, 0):
+            assert lib.skv_token_sparse_set_stagger(mode) == 0
+            res[mode] = _C.token_sparse_decode(Q, K, V, k, 0, return_indices=True)
+            torch.cuda.synchronize()
+            assert all(_workspace.status(w) == 0 for w in _workspace.all_of("token_sparse", cuda_device))
+    finally:
+        lib.skv_token_sparse_set_stagger(1)
+    assert torch.equal(res[1][0], res[0][0])
+    assert torch.equal(res[1][1], res[0][1])
+    if boundary_gap(Q.cpu(), K.cpu(), k) > 1e-5:
+        assert torch.equal(res[1][1][:, :, 0, :k].cpu().long(), oracle.token_topk_sets(Q.cpu(), K.cpu(), k))
