@@ -422,7 +422,7 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     const int stagger_cap = tokens_per_cta <= 2048 ? 2048 : 3584;
     if (mma_path && stagger_flag() && sp.T >= 16 * 1024) {
         const int nt = (sp.T + MMA_TILE - 1) / MMA_TILE;
-        int n = (int)g1.x;
+        int n = std::max((int)g1.x, (int)((3LL * nt * MMA_TILE) / (2LL * stagger_cap)));   // the longest chunk is about 1.5 means
         auto longest = [&](int nn) {
             int m = 0;
             for (int x = 0; x < nn; ++x) m = std::max(m, chunk_first_tile(x + 1, nn, nt) - chunk_first_tile(x, nn, nt));
