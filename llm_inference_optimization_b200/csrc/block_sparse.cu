@@ -218,6 +218,32 @@ block_select_attend_kernel(const AttendParams p) {
     if (p.block_idx)
         for (int i = tid; i < p.top_k; i += ATT_THREADS) p.block_idx[(long long)row * p.top_k + i] = i < kk ? sel[i] : -1;
 
+    // The value rows' addresses are known now, their weights only after the softmax: VU rows per thread are loaded
+    // together (rows past the end are clamped to a real row and weighted zero, so no load waits on a condition), the
+    // first batch before the softmax.
+    constexpr int VU = 4;
+    const int grp = tid / LPR, sub = tid % LPR;
+    const __half* vbase = p.v + b * p.v_sb + h * p.v_sh + sub * 8;
+    const long long total = (long long)kk * p.block_size;
+    auto row_token = [&](long long r, int& i) {   // token of gathered row r (clamped), its block slot in i; < 0: past the end
+        const long long rc = r < total ? r : total - 1;
+        i = (int)(rc / p.block_size);
+        const int t = SKV_INDEX(sel[i], p.nb) * p.block_size + (int)(rc - (long long)i * p.block_size);
+        return (r < total && t < p.T) ? t : -1 - min(t, p.T - 1);
+    };
+    uint4 vraw[VU];
+    int vslot[VU];
+    auto load_batch = [&](long long r0) {
+#pragma unroll
+        for (int u = 0; u < VU; ++u) {
+            int i;
+            const int t = row_token(r0 + (long long)u * GROUPS, i);
+            vslot[u] = t >= 0 ? i : -1;
+            vraw[u] = *reinterpret_cast<const uint4*>(vbase + (long long)(t >= 0 ? t : -1 - t) * p.v_st);
+        }
+    };
+    if (total > 0) load_batch(grp);
+
     // softmax over the kk selected block scores, folded with 1 / count of each block
     float mx = -INFINITY;
     for (int i = tid; i < kk; i += ATT_THREADS) {
@@ -259,19 +285,16 @@ block_select_attend_kernel(const AttendParams p) {
     }
     __syncthreads();
 
-    const int grp = tid / LPR, sub = tid % LPR;
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    const __half* vbase = p.v + b * p.v_sb + h * p.v_sh + sub * 8;
-    const long long total = (long long)kk * p.block_size;
-    for (long long r = grp; r < total; r += GROUPS) {
-        const int i = (int)(r / p.block_size);
-        const int t = SKV_INDEX(sel[i], p.nb) * p.block_size + (int)(r - (long long)i * p.block_size);
-        if (t < p.T) {
+    for (long long r0 = grp; r0 < total; r0 += (long long)VU * GROUPS) {
+        if (r0 != grp) load_batch(r0);
+#pragma unroll
+        for (int u = 0; u < VU; ++u) {
             float x[8];
-            unpack8(*reinterpret_cast<const uint4*>(vbase + (long long)t * p.v_st), x);
-            const float wi = w[i];
+            unpack8(vraw[u], x);
+            const float wi = vslot[u] >= 0 ? w[vslot[u]] : 0.f;
 #pragma unroll
             for (int c = 0; c < 8; ++c) acc[c] = fmaf(wi, x[c], acc[c]);
         }

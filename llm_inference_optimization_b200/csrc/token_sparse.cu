@@ -147,6 +147,7 @@ __global__ void __launch_bounds__(SCORE_THREADS, MMA_STAGES == 2 ? 3 : 2)
 token_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const ScoreParams p, const KvMapPos pos,
                         int tokens_per_cta, int stagger_tiles, int* status) {
     pdl_launch_dependents();
+    SKV_PHASE(0);
     constexpr int NH = D / 64, KSTEPS = D / 16, HALF_BYTES = MMA_TILE * 128, STAGE = mma_stage_bytes<D>();
     extern __shared__ uint8_t mma_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(mma_raw) + 1023) & ~uintptr_t(1023));
@@ -236,6 +237,7 @@ token_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const ScorePara
             break;
         }
     }
+    SKV_PHASE(1);
     if (p.cand_k > 0) {   // as in token_scores_kernel; the select scratch reuses the drained ring (every copy has landed)
         uint32_t* tk = reinterpret_cast<uint32_t*>(smem);
         int* csel = reinterpret_cast<int*>(tk + TopkSmem<SCORE_THREADS>::WORDS);
@@ -250,6 +252,7 @@ token_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const ScorePara
             p.cand_score[o + i] = i < kc ? chunk_sc[csel[i]] : -INFINITY;
         }
     }
+    SKV_PHASE(2);
 }
 
 struct AttendParams {
@@ -268,7 +271,9 @@ struct AttendParams {
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS)
 token_select_attend_kernel(const AttendParams p) {
+    SKV_PHASE(3);
     pdl_wait_prior_grids();   // launched as a programmatic dependent of the scoring kernel: its results are complete from here on
+    SKV_PHASE(4);
     constexpr int LPR = D / 8;
     constexpr int GROUPS = ATT_THREADS / LPR;  // value rows gathered in parallel
     extern __shared__ uint32_t dsm[];
@@ -285,18 +290,26 @@ token_select_attend_kernel(const AttendParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kk = min(p.top_k, p.T), sink = min(max(p.sink, 0), p.T);
 
+    // the scores of the sink prefix are needed whatever gets selected: on their way before the selection starts
+    const float sink_sc0 = tid < sink ? sc[tid] : 0.f;
     // 1. exact top-k, ascending positions, into sel[sink ...)
     int* top = sel + sink;
+    float* top_sc = w + sink;   // candidate mode: the kept candidates' scores travel with their positions
     if (p.cand_score) {
         // candidates are ordered by token position (chunk by chunk, ascending inside a chunk), so "equal scores:
         // lower candidate index first" is the same rule as "lower token position first"
         block_topk_fast<ATT_THREADS, 4>(p.cand_score + (long long)row * p.nc, p.nc, kk, top, tk);
         __syncthreads();
-        for (int i = tid; i < kk; i += ATT_THREADS) top[i] = p.cand_pos[(long long)row * p.nc + SKV_INDEX(top[i], p.nc)];
+        for (int i = tid; i < kk; i += ATT_THREADS) {
+            const long long ci = (long long)row * p.nc + SKV_INDEX(top[i], p.nc);
+            top[i] = p.cand_pos[ci];
+            top_sc[i] = p.cand_score[ci];   // the same number the scoring kernel stored at scores[position]
+        }
         __syncthreads();
     } else {
         block_topk_fast<ATT_THREADS, 8>(sc, p.T, kk, top, tk);
     }
+    SKV_PHASE(5);
     if (p.topk_idx) {
         for (int i = tid; i < p.top_k; i += ATT_THREADS) p.topk_idx[(long long)row * p.top_k + i] = i < kk ? top[i] : -1;
     }
@@ -317,16 +330,27 @@ token_select_attend_kernel(const AttendParams p) {
     for (int base = 0; base < kk - c; base += ATT_THREADS) {
         const int i = base + tid;
         const int v = i < kk - c ? top[c + i] : 0;
+        const float vs = (p.cand_score && i < kk - c) ? top_sc[c + i] : 0.f;
         __syncthreads();
-        if (i < kk - c) sel[sink + i] = v;
+        if (i < kk - c) {
+            sel[sink + i] = v;
+            if (p.cand_score) w[sink + i] = vs;
+        }
     }
     for (int i = tid; i < sink; i += ATT_THREADS) sel[i] = i;
     __syncthreads();
 
+    // the first pass of value rows: their addresses are known now, their weights only after the softmax
+    const int grp = tid / LPR, sub = tid % LPR;
+    const __half* vbase = p.v + b * p.v_sb + h * p.v_sh + sub * 8;
+    uint4 v_first = make_uint4(0u, 0u, 0u, 0u);
+    if (grp < n) v_first = *reinterpret_cast<const uint4*>(vbase + (long long)SKV_INDEX(sel[grp], p.T) * p.v_st);
+
+    SKV_PHASE(6);
     // 3. softmax over the kept scores
     float mx = -INFINITY;
     for (int i = tid; i < n; i += ATT_THREADS) {
-        const float x = sc[SKV_INDEX(sel[i], p.T)];
+        const float x = i < sink ? (i == tid ? sink_sc0 : sc[i]) : (p.cand_score ? w[i] : sc[SKV_INDEX(sel[i], p.T)]);
         w[i] = x;
         mx = fmaxf(mx, x);
     }
@@ -358,14 +382,13 @@ token_select_attend_kernel(const AttendParams p) {
     __syncthreads();
     const float inv = 1.f / bcast[1];
 
+    SKV_PHASE(7);
     // 4. out = sum_j w_j V[sel_j] / sum
-    const int grp = tid / LPR, sub = tid % LPR;
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    const __half* vbase = p.v + b * p.v_sb + h * p.v_sh + sub * 8;
     for (int j = grp; j < n; j += GROUPS) {
-        const uint4 vv = *reinterpret_cast<const uint4*>(vbase + (long long)SKV_INDEX(sel[j], p.T) * p.v_st);
+        const uint4 vv = j == grp ? v_first : *reinterpret_cast<const uint4*>(vbase + (long long)SKV_INDEX(sel[j], p.T) * p.v_st);
         const float wj = w[j];
         const __half2* hv = reinterpret_cast<const __half2*>(&vv);
 #pragma unroll
@@ -385,6 +408,7 @@ token_select_attend_kernel(const AttendParams p) {
         for (int g2 = 0; g2 < GROUPS; ++g2) o += red[g2 * D + d];
         p.out[(long long)row * D + d] = __float2half_rn(o * inv);
     }
+    SKV_PHASE(8);
 }
 
 template <int D>
@@ -495,6 +519,12 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
 using namespace skv;
 
 extern "C" {
+
+#ifdef SKV_PROFILE_PHASES
+int skv_debug_phase_ts_token(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, skv_phase_ts, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : -4;
+}
+#endif
 
 // 1 (default): decode-shaped calls (one query per head, D = 64 or 128) score the keys on the tensor cores; 0: always with
 // the register-load kernel.  Process-wide.
