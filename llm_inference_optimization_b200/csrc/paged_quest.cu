@@ -478,7 +478,7 @@ template <int KVT, bool FUSED>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 quest_select_attend_kernel(const __grid_constant__ CUtensorMap tmM, const AttendParams p) {
     extern __shared__ __align__(16) uint8_t vstage[];   // ATT_DYN_SMEM bytes
-    __shared__ uint32_t tk[TopkSmem<ATT_THREADS>::WORDS];
+    __shared__ __align__(16) uint32_t tk[TopkSmem<ATT_THREADS>::WORDS];
     __shared__ int sel[MAX_TOPK];
     __shared__ float w[MAX_SEL_TOKENS];
     __shared__ int2 where[MAX_SEL_TOKENS];  // (page, slot) of every gathered token; PAST_END set in slot past the sequence end

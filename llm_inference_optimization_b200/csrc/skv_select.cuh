@@ -408,41 +408,26 @@ __device__ void block_topk_small(const float* sc, int T, int k, int* out, unsign
     __syncthreads();
 }
 
-// Exact top-k for k <= min(NT / 2, 256) over T <= NT * R scores without histogram passes.  The threads are cut into
-// G >= 2k groups of consecutive lanes; the k-th largest of the G group maxima is a lower bound of the k-th largest
-// score (the maxima are G distinct elements), and for scores in no particular order only about 0.7 G elements reach
-// it.  Those survivors are appended to shared memory as 64-bit words (order-preserving score bits, then the
-// complemented position, so that a greater word is a better rank and no two are equal); every survivor's rank is
-// counted by a whole warp (lanes stride over the list, one ballot per 32 comparisons -- a single thread looping over
-// the list pays a shared-memory latency per element), and the k best are written in ascending position the same way.
-// Six barriers, one atomic per warp; a row on which more than NT / 2 elements survive (long runs of equal scores,
-// say) goes to the radix routine instead.  Same result as block_topk_sorted.  All NT threads must call it; `sm` is
-// TopkSmem<NT>::WORDS words, 8-byte aligned.
-template <int NT, int R>
-__device__ void block_topk_pivot(const float* sc, int T, int k, int* out, uint32_t* sm) {
-    static_assert(TopkSmem<NT>::WORDS >= 3 * NT + 4, "shared memory of the pivot routine");
+// ---- Exact top-k without histogram passes, for k <= min(NT / 2, 256).
+// The threads are cut into G >= 2k groups of consecutive lanes; the k-th largest of the G group maxima is a lower
+// bound of the k-th largest score (the maxima are G distinct elements), and for scores in no particular order only
+// about 0.7 G elements reach it.  Those survivors are appended to shared memory as 64-bit words (order-preserving
+// score bits, then the complemented position, so that a greater word is a better rank and no two are equal); every
+// survivor's rank is counted by a whole warp (lanes stride over the list, one ballot per 32 comparisons -- a single
+// thread looping over the list pays a shared-memory latency per element), and the k best are written in ascending
+// position the same way.  Six barriers, one atomic per warp; a row on which more than NT / 2 elements survive (long
+// runs of equal scores, say) goes to the radix routine instead.  Same result as block_topk_sorted.  All NT threads
+// must call these; `sm` is TopkSmem<NT>::WORDS words, 8-byte aligned:
+//   gm = sm [NT]: group maxima, later the kept survivors' positions; surv = sm + NT [NT / 2 x 64 bit]; misc = sm + 3 NT.
+
+// The pivot from every thread's maximum key m (0: the thread has no element).
+template <int NT>
+__device__ __forceinline__ uint32_t pivot_from_thread_maxima(uint32_t m, int k, uint32_t* sm) {
+    static_assert(TopkSmem<NT>::WORDS >= 3 * NT + 4, "shared memory of the pivot routines");
     constexpr int NW = NT / 32;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    uint32_t* gm = sm;              // [G] group maxima, later [total] the kept survivors' positions
-    unsigned long long* surv = reinterpret_cast<unsigned long long*>(sm + NT);   // [NT / 2 used] survivors
-    uint32_t* misc = sm + 3 * NT;   // [0] the pivot, [1] the survivor count
-
-    int seg = (T + NW - 1) / NW;
-    seg = (seg + 31) & ~31;  // <= 32 * R because T <= NT * R
-    const int s0 = min(T, warp * seg), s1 = min(T, s0 + seg);
-    uint32_t key[R];
-    uint32_t m = 0;
-    {
-        float raw[R];   // (unconditional loads at clamped positions: all in flight together)
-#pragma unroll
-        for (int j = 0; j < R; ++j) raw[j] = sc[min(s0 + j * 32 + lane, T - 1)];
-#pragma unroll
-        for (int j = 0; j < R; ++j) {
-            key[j] = s0 + j * 32 + lane < s1 ? score_key(raw[j]) : 0u;   // 0: below every real key's use here (never >= a real pivot unless the row is all such)
-            m = max(m, key[j]);
-        }
-    }
-    SKV_PHASE(10);
+    uint32_t* gm = sm;
+    uint32_t* misc = sm + 3 * NT;
     int gs = 32;   // lanes per group: the largest power of two that leaves at least 2k groups
     while (gs > 1 && NT / gs < 2 * k) gs >>= 1;
     const int G = NT / gs;
@@ -450,7 +435,6 @@ __device__ void block_topk_pivot(const float* sc, int T, int k, int* out, uint32
     if ((tid & (gs - 1)) == 0) gm[tid / gs] = m;
     if (tid == 0) misc[1] = 0u;
     __syncthreads();
-    SKV_PHASE(11);
     for (int t = warp; t < G; t += NW) {   // the group maximum that exactly k - 1 others outrank is the pivot
         const uint32_t v = gm[t];
         int c = 0;
@@ -462,45 +446,37 @@ __device__ void block_topk_pivot(const float* sc, int T, int k, int* out, uint32
         if (c == k - 1 && lane == 0) misc[0] = v;
     }
     __syncthreads();
-    SKV_PHASE(12);
-    const uint32_t pivot = misc[0];
-    {
-        uint32_t mask = 0;
+    return misc[0];
+}
+
+// First free slot for this lane's `cnt` survivors: a scan inside the warp, one atomic per warp.
+template <int NT>
+__device__ __forceinline__ uint32_t pivot_reserve_slots(uint32_t cnt, uint32_t* sm) {
+    const int lane = threadIdx.x & 31;
+    uint32_t incl = cnt;
 #pragma unroll
-        for (int j = 0; j < R; ++j)
-            if (s0 + j * 32 + lane < s1 && key[j] >= pivot) mask |= 1u << j;
-        const uint32_t cnt = __popc(mask);
-        uint32_t incl = cnt;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += v;
-        }
-        const uint32_t wtotal = __shfl_sync(0xffffffffu, incl, 31);
-        uint32_t base = 0;
-        if (lane == 0 && wtotal) base = atomicAdd(&misc[1], wtotal);
-        base = __shfl_sync(0xffffffffu, base, 0);
-        uint32_t slot = base + incl - cnt;
-#pragma unroll
-        for (int j = 0; j < R; ++j) {
-            if ((mask >> j) & 1u) {
-                if (slot < (uint32_t)(NT / 2))
-                    surv[slot] = ((unsigned long long)key[j] << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)(s0 + j * 32 + lane));
-                ++slot;
-            }
-        }
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
     }
-    __syncthreads();
-    SKV_PHASE(13);
-    const int total = (int)misc[1];
-#ifdef SKV_PROFILE_PHASES
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) skv_phase_ts[20] = (unsigned long long)total;
-#endif
-    if (total > NT / 2) {   // (the same decision in every thread)
-        __syncthreads();
-        block_topk_sorted_cached<NT, R>(sc, T, k, out, sm);
-        return;
-    }
+    const uint32_t wtotal = __shfl_sync(0xffffffffu, incl, 31);
+    uint32_t base = 0;
+    if (lane == 0 && wtotal) base = atomicAdd(sm + 3 * NT + 1, wtotal);
+    base = __shfl_sync(0xffffffffu, base, 0);
+    return base + incl - cnt;
+}
+
+__device__ __forceinline__ unsigned long long pivot_word(uint32_t key, int pos) {
+    return ((unsigned long long)key << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)pos);
+}
+
+// Ranks the `total` (<= NT / 2) survivors and writes the k best positions, ascending.  Ends with a barrier.
+template <int NT>
+__device__ __forceinline__ void pivot_rank_and_write(int total, int k, int* out, uint32_t* sm) {
+    constexpr int NW = NT / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t* gm = sm;
+    const unsigned long long* surv = reinterpret_cast<const unsigned long long*>(sm + NT);
     for (int t = warp; t < total; t += NW) {   // gm[t]: the survivor's position if fewer than k others outrank it
         const unsigned long long mine = surv[t];
         int c = 0;
@@ -510,7 +486,6 @@ __device__ void block_topk_pivot(const float* sc, int T, int k, int* out, uint32
         }
         if (lane == 0) gm[t] = c < k ? 0xFFFFFFFFu - (uint32_t)mine : 0xFFFFFFFFu;
     }
-    SKV_PHASE(14);
     __syncthreads();
     for (int t = warp; t < total; t += NW) {
         const uint32_t mine = gm[t];
@@ -523,7 +498,100 @@ __device__ void block_topk_pivot(const float* sc, int T, int k, int* out, uint32
         if (lane == 0) out[pos] = (int)mine;
     }
     __syncthreads();
-    SKV_PHASE(15);
+}
+
+// Rows of up to NT * R scores: every score is loaded once and its key kept in a register.
+template <int NT, int R>
+__device__ void block_topk_pivot(const float* sc, int T, int k, int* out, uint32_t* sm) {
+    constexpr int NW = NT / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned long long* surv = reinterpret_cast<unsigned long long*>(sm + NT);
+    int seg = (T + NW - 1) / NW;
+    seg = (seg + 31) & ~31;  // <= 32 * R because T <= NT * R
+    const int s0 = min(T, warp * seg), s1 = min(T, s0 + seg);
+    uint32_t key[R];
+    uint32_t m = 0;
+    {
+        float raw[R];   // (unconditional loads at clamped positions: all in flight together)
+#pragma unroll
+        for (int j = 0; j < R; ++j) raw[j] = sc[min(s0 + j * 32 + lane, T - 1)];
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            key[j] = s0 + j * 32 + lane < s1 ? score_key(raw[j]) : 0u;
+            m = max(m, key[j]);
+        }
+    }
+    const uint32_t pivot = pivot_from_thread_maxima<NT>(m, k, sm);
+    uint32_t mask = 0;
+#pragma unroll
+    for (int j = 0; j < R; ++j)
+        if (s0 + j * 32 + lane < s1 && key[j] >= pivot) mask |= 1u << j;
+    uint32_t slot = pivot_reserve_slots<NT>(__popc(mask), sm);
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+        if ((mask >> j) & 1u) {
+            if (slot < (uint32_t)(NT / 2)) surv[slot] = pivot_word(key[j], s0 + j * 32 + lane);
+            ++slot;
+        }
+    }
+    __syncthreads();
+    const int total = (int)sm[3 * NT + 1];
+    if (total > NT / 2) {   // (the same decision in every thread)
+        __syncthreads();
+        block_topk_sorted_cached<NT, R>(sc, T, k, out, sm);
+        return;
+    }
+    pivot_rank_and_write<NT>(total, k, out, sm);
+}
+
+// Rows of any length: three passes over the scores (thread maxima, survivor counts, survivor words), thread t taking
+// the elements t, t + NT, ...; eight loads in flight per thread.
+template <int NT>
+__device__ void block_topk_pivot_stream(const float* sc, int T, int k, int* out, uint32_t* sm) {
+    constexpr int U = 8;
+    const int tid = threadIdx.x;
+    unsigned long long* surv = reinterpret_cast<unsigned long long*>(sm + NT);
+    uint32_t m = 0;
+    for (int i0 = tid; i0 < T; i0 += U * NT) {
+        float raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) raw[u] = sc[min(i0 + u * NT, T - 1)];
+#pragma unroll
+        for (int u = 0; u < U; ++u) m = max(m, i0 + u * NT < T ? score_key(raw[u]) : 0u);
+    }
+    const uint32_t pivot = pivot_from_thread_maxima<NT>(m, k, sm);
+    uint32_t cnt = 0;
+    for (int i0 = tid; i0 < T; i0 += U * NT) {
+        float raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) raw[u] = sc[min(i0 + u * NT, T - 1)];
+#pragma unroll
+        for (int u = 0; u < U; ++u) cnt += (i0 + u * NT < T && score_key(raw[u]) >= pivot) ? 1u : 0u;
+    }
+    uint32_t slot = pivot_reserve_slots<NT>(cnt, sm);
+    if (cnt) {
+        for (int i0 = tid; i0 < T; i0 += U * NT) {
+            float raw[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) raw[u] = sc[min(i0 + u * NT, T - 1)];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t key = score_key(raw[u]);
+                if (i0 + u * NT < T && key >= pivot) {
+                    if (slot < (uint32_t)(NT / 2)) surv[slot] = pivot_word(key, i0 + u * NT);
+                    ++slot;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    const int total = (int)sm[3 * NT + 1];
+    if (total > NT / 2) {   // (the same decision in every thread)
+        __syncthreads();
+        block_topk_sorted<NT>(sc, T, k, out, sm);
+        return;
+    }
+    pivot_rank_and_write<NT>(total, k, out, sm);
 }
 
 #ifndef SKV_TOPK_PIVOT
@@ -539,7 +607,8 @@ __device__ __forceinline__ void block_topk_sorted_auto(const float* sc, int T, i
 
 // The quickest exact routine for the problem: arg-max extraction for k <= 8 over rows of up to 16 scores per
 // thread, the pivot routine for k up to min(NT / 2, 256) over rows of up to R scores per thread, the register-cached
-// radix select for other rows of that length, the streaming radix select otherwise.  `sm` is TopkSmem<NT>::WORDS words (the small routine uses the first 2 * NT of them).  Output ascending.
+// radix select for other rows of that length; longer rows: the streaming pivot routine for such k, the streaming radix
+// select otherwise.  `sm` is TopkSmem<NT>::WORDS words (the small routine uses the first 2 * NT of them).  Output ascending.
 template <int NT, int R>
 __device__ __forceinline__ void block_topk_fast(const float* sc, int T, int k, int* out, uint32_t* sm) {
     static_assert(TopkSmem<NT>::WORDS >= 2 * NT, "candidate scratch of the small routine");
@@ -560,6 +629,7 @@ __device__ __forceinline__ void block_topk_fast(const float* sc, int T, int k, i
     else if (small && T <= NT * 8) block_topk_small<NT, 8>(sc, T, k, out, cand);
     else if (small && T <= NT * 16) block_topk_small<NT, 16>(sc, T, k, out, cand);
     else if (SKV_TOPK_PIVOT && k > 0 && 2 * k <= NT && k <= 256 && T <= NT * R) block_topk_pivot<NT, R>(sc, T, k, out, sm);
+    else if (SKV_TOPK_PIVOT && k > 0 && 2 * k <= NT && k <= 256) block_topk_pivot_stream<NT>(sc, T, k, out, sm);
     else block_topk_sorted_auto<NT, R>(sc, T, k, out, sm);
 }
 

@@ -443,10 +443,10 @@ static int launch(const ScoreParams& sp, const AttendParams& ap, int B, int devi
     // Staggered chunks for the tensor-core kernel: as many as keep the longest (the first) within the tokens that the
     // ring's shared-memory budget leaves for a chunk's scores (2048 beside the short ring, 3584 beside the long one).
     int stagger_tiles = 0;
-    const int stagger_cap = tokens_per_cta <= 2048 ? 2048 : 3584;
+    const int stagger_cap = tokens_per_cta <= 1536 ? 2048 : 3584;   // (64K x 32 rows: 27 long chunks beside the long ring 103 us, 48 short ones 107 us)
     if (mma_path && stagger_flag() && sp.T >= 16 * 1024) {
         const int nt = (sp.T + MMA_TILE - 1) / MMA_TILE;
-        int n = std::max((int)g1.x, (int)((3LL * nt * MMA_TILE) / (2LL * stagger_cap)));   // the longest chunk is about 1.5 means
+        int n = std::max(2, (int)((3LL * nt * MMA_TILE) / (2LL * stagger_cap)));   // the longest chunk is about 1.5 means
         auto longest = [&](int nn) {
             int m = 0;
             for (int x = 0; x < nn; ++x) m = std::max(m, chunk_first_tile(x + 1, nn, nt) - chunk_first_tile(x, nn, nt));

@@ -149,3 +149,25 @@ def test_staggered_and_equal_chunks_select_the_same_tokens(cuda_device, H, T, k)
     assert torch.equal(res[1][1], res[0][1])
     if boundary_gap(Q.cpu(), K.cpu(), k) > 1e-5:
         assert torch.equal(res[1][1][:, :, 0, :k].cpu().long(), oracle.token_topk_sets(Q.cpu(), K.cpu(), k))
+
+
+@pytest.mark.parametrize("T,k", [(2000, 32), (4096, 100), (40000, 32)])
+def test_equal_and_sorted_scores(cuda_device, T, k):
+    """Rows the selection's shortcut cannot thin out: all scores equal (every element reaches any threshold; the kept
+    set is the first k positions) and scores rising with the position (the k best sit in one thread group)."""
+    g = torch.Generator().manual_seed(T)
+    Q = torch.zeros(1, 2, 1, 64).half()
+    Q[..., 0] = 1.0
+    K = torch.zeros(1, 2, T, 64).half()
+    K[0, 0, :, 0] = 0.5                                               # head 0: all equal
+    K[0, 1, :, 0] = (torch.arange(T).float() / T).half()              # head 1: non-decreasing, runs of equal values
+    K[..., 1:] = torch.randn(1, 2, T, 63, generator=g).half()         # orthogonal to q
+    V = torch.randn(1, 2, T, 64, generator=g).half()
+    out, idx = _C.token_sparse_decode(Q.to(cuda_device), K.to(cuda_device), V.to(cuda_device), k, 0, return_indices=True)
+    s = (K.float() @ Q.float().transpose(-1, -2))[..., 0]             # [1, 2, T]
+    for h in range(2):
+        want = torch.argsort(s[0, h], descending=True, stable=True)[:k].sort().values
+        assert torch.equal(idx[0, h, 0].cpu().long(), want), h
+        # (the oracle's torch.topk breaks ties its own way: attend over the expected set directly)
+        w = torch.softmax(s[0, h, want] * 64 ** -0.5, dim=0)
+        assert (out[0, h, 0].float().cpu() - w @ V[0, h, want].float()).abs().max().item() <= TOL
