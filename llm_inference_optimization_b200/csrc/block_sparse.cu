@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(SCORE_THREADS, 2)
 block_mean_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const ScoreParams p, const KvMapPos pos,
                              int blocks_per_cta, int* status) {
     pdl_launch_dependents();
+    SKV_PHASE(0);
     constexpr int NH = D / 64, KSTEPS = D / 16, HALF_BYTES = MMA_TILE * 128, STAGE = mma_stage_bytes<D>();
     extern __shared__ uint8_t mma_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(mma_raw) + 1023) & ~uintptr_t(1023));
@@ -176,6 +177,7 @@ block_mean_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const Scor
         }
     }
     __syncthreads();
+    SKV_PHASE(1);
     float* srow = p.scores + ((long long)b * p.H + h) * p.nb;
     const int per = p.block_size / 16;
     for (int j = j0 + tid; j < j1; j += SCORE_THREADS) {
@@ -199,7 +201,9 @@ struct AttendParams {
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS)
 block_select_attend_kernel(const AttendParams p) {
+    SKV_PHASE(3);
     pdl_wait_prior_grids();   // launched as a programmatic dependent of the scoring kernel: its results are complete from here on
+    SKV_PHASE(4);
     constexpr int LPR = D / 8;
     constexpr int GROUPS = ATT_THREADS / LPR;
     extern __shared__ uint32_t dsm[];
@@ -215,6 +219,7 @@ block_select_attend_kernel(const AttendParams p) {
     const int kk = min(p.top_k, p.nb);
     block_topk_fast<ATT_THREADS, 4>(sc, p.nb, kk, sel, tk);
     __syncthreads();
+    SKV_PHASE(5);
     if (p.block_idx)
         for (int i = tid; i < p.top_k; i += ATT_THREADS) p.block_idx[(long long)row * p.top_k + i] = i < kk ? sel[i] : -1;
 
@@ -224,28 +229,44 @@ block_select_attend_kernel(const AttendParams p) {
     constexpr int VU = 4;
     const int grp = tid / LPR, sub = tid % LPR;
     const __half* vbase = p.v + b * p.v_sb + h * p.v_sh + sub * 8;
-    const long long total = (long long)kk * p.block_size;
-    auto row_token = [&](long long r, int& i) {   // token of gathered row r (clamped), its block slot in i; < 0: past the end
-        const long long rc = r < total ? r : total - 1;
-        i = (int)(rc / p.block_size);
-        const int t = SKV_INDEX(sel[i], p.nb) * p.block_size + (int)(rc - (long long)i * p.block_size);
+    const int total = kk * p.block_size;   // gathered rows: at most T rounded up to a block, which the entry point keeps below 2^31
+    auto row_token = [&](int r, int& i) {   // token of gathered row r (clamped), its block slot in i; < 0: past the end
+        const int rc = r < total ? r : total - 1;
+        i = rc / p.block_size;
+        const int t = SKV_INDEX(sel[i], p.nb) * p.block_size + (rc - i * p.block_size);
         return (r < total && t < p.T) ? t : -1 - min(t, p.T - 1);
     };
     uint4 vraw[VU];
     int vslot[VU];
-    auto load_batch = [&](long long r0) {
+    auto load_batch = [&](int r0) {
 #pragma unroll
         for (int u = 0; u < VU; ++u) {
             int i;
-            const int t = row_token(r0 + (long long)u * GROUPS, i);
+            const int t = row_token(r0 + u * GROUPS, i);
             vslot[u] = t >= 0 ? i : -1;
             vraw[u] = *reinterpret_cast<const uint4*>(vbase + (long long)(t >= 0 ? t : -1 - t) * p.v_st);
         }
     };
     if (total > 0) load_batch(grp);
 
+    SKV_PHASE(6);
+    // Up to 32 selected blocks (the usual case): every warp computes the k weights for itself, lane i holding block
+    // i's, and hands them out by shuffle -- no shared memory and no block-wide barrier between selection and gather.
+    const bool few = kk <= 32;
+    float wlane = 0.f;
+    if (few) {
+        const float x = lane < kk ? sc[SKV_INDEX(sel[lane], p.nb)] : -INFINITY;
+        const float mxw = warp_max(x);
+        const float e = lane < kk ? __expf(x - mxw) : 0.f;
+        const float inv = 1.f / fmaxf(warp_sum(e), 1e-9f);
+        if (lane < kk) {
+            const int t0 = SKV_INDEX(sel[lane], p.nb) * p.block_size;
+            wlane = e * inv / (float)(min(p.T, t0 + p.block_size) - t0);
+        }
+    }
     // softmax over the kk selected block scores, folded with 1 / count of each block
     float mx = -INFINITY;
+    if (!few) {
     for (int i = tid; i < kk; i += ATT_THREADS) {
         const float x = sc[SKV_INDEX(sel[i], p.nb)];
         w[i] = x;
@@ -284,21 +305,30 @@ block_select_attend_kernel(const AttendParams p) {
         w[i] = w[i] * inv / (float)cnt;  // per-token weight of block i
     }
     __syncthreads();
+    }
 
+    SKV_PHASE(7);
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (long long r0 = grp; r0 < total; r0 += (long long)VU * GROUPS) {
-        if (r0 != grp) load_batch(r0);
+    for (int base = 0; base < total; base += VU * GROUPS) {   // (the same trip count in every thread: the shuffles below need whole warps; rows past the end weigh zero)
+        if (base) load_batch(base + grp);
 #pragma unroll
         for (int u = 0; u < VU; ++u) {
             float x[8];
             unpack8(vraw[u], x);
-            const float wi = vslot[u] >= 0 ? w[vslot[u]] : 0.f;
+            float wi;
+            if (few) {
+                const float ws = __shfl_sync(0xffffffffu, wlane, max(vslot[u], 0));
+                wi = vslot[u] >= 0 ? ws : 0.f;
+            } else {
+                wi = vslot[u] >= 0 ? w[vslot[u]] : 0.f;
+            }
 #pragma unroll
             for (int c = 0; c < 8; ++c) acc[c] = fmaf(wi, x[c], acc[c]);
         }
     }
+    SKV_PHASE(8);
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < 8; ++i) red[grp * D + sub * 8 + i] = acc[i];
@@ -309,6 +339,7 @@ block_select_attend_kernel(const AttendParams p) {
         for (int g2 = 0; g2 < GROUPS; ++g2) o += red[g2 * D + d];
         p.out[(long long)row * D + d] = __float2half_rn(o);
     }
+    SKV_PHASE(9);
 }
 
 // 1 (default): D = 64 or 128 with block sizes that are multiples of 16 are scored by the tensor-core kernel; 0: always
@@ -372,6 +403,12 @@ using namespace skv;
 
 extern "C" {
 
+#ifdef SKV_PROFILE_PHASES
+int skv_debug_phase_ts_block(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, skv_phase_ts, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : -4;
+}
+#endif
+
 // 1 (default): D = 64 or 128 with a block size that is a multiple of 16 scores the blocks on the tensor cores; 0: always
 // with the register-load kernel.  Process-wide.
 int skv_block_sparse_set_mma_scores(int on) {
@@ -397,6 +434,8 @@ int skv_block_sparse_decode(const void* q, const void* k, const void* v, void* o
     if (D != 16 && D != 32 && D != 64 && D != 128 && D != 256)
         return fail(SKV_ERR_UNSUPPORTED, "head dim %d not supported (16, 32, 64, 128 or 256)", D);
     const int nb = (T + block_size - 1) / block_size;
+    if ((long long)nb * block_size > 2147483647LL)
+        return fail(SKV_ERR_UNSUPPORTED, "skv_block_sparse_decode: T rounded up to a block must stay below 2^31");
     if ((top_k_blocks < nb ? top_k_blocks : nb) > bsp::MAX_TOPK_BLOCKS)
         return fail(SKV_ERR_UNSUPPORTED, "top_k_blocks=%d exceeds %d", top_k_blocks, bsp::MAX_TOPK_BLOCKS);
     if (H > 65535 || B > 65535) return fail(SKV_ERR_UNSUPPORTED, "grid dimension too large");

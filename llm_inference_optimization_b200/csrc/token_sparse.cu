@@ -314,88 +314,130 @@ token_select_attend_kernel(const AttendParams p) {
         for (int i = tid; i < p.top_k; i += ATT_THREADS) p.topk_idx[(long long)row * p.top_k + i] = i < kk ? top[i] : -1;
     }
     __syncthreads();
-    // 2. kept set = sink prefix U {top positions >= sink}: drop the leading top entries that fall inside the prefix
-    int c = 0;  // top is ascending, so entries < sink form a prefix of length c
-    {
-        int lo = 0, hi = kk;
-        while (lo < hi) {
-            const int mid = (lo + hi) >> 1;
-            if (top[mid] < sink) lo = mid + 1; else hi = mid;
-        }
-        c = lo;
-    }
-    const int n = sink + kk - c;
-    __syncthreads();
-    // compact in place: positions [0, sink) then top[c ..)
-    for (int base = 0; base < kk - c; base += ATT_THREADS) {
-        const int i = base + tid;
-        const int v = i < kk - c ? top[c + i] : 0;
-        const float vs = (p.cand_score && i < kk - c) ? top_sc[c + i] : 0.f;
-        __syncthreads();
-        if (i < kk - c) {
-            sel[sink + i] = v;
-            if (p.cand_score) w[sink + i] = vs;
-        }
-    }
-    for (int i = tid; i < sink; i += ATT_THREADS) sel[i] = i;
-    __syncthreads();
-
-    // the first pass of value rows: their addresses are known now, their weights only after the softmax
     const int grp = tid / LPR, sub = tid % LPR;
     const __half* vbase = p.v + b * p.v_sb + h * p.v_sh + sub * 8;
-    uint4 v_first = make_uint4(0u, 0u, 0u, 0u);
-    if (grp < n) v_first = *reinterpret_cast<const uint4*>(vbase + (long long)SKV_INDEX(sel[grp], p.T) * p.v_st);
-
-    SKV_PHASE(6);
-    // 3. softmax over the kept scores
-    float mx = -INFINITY;
-    for (int i = tid; i < n; i += ATT_THREADS) {
-        const float x = i < sink ? (i == tid ? sink_sc0 : sc[i]) : (p.cand_score ? w[i] : sc[SKV_INDEX(sel[i], p.T)]);
-        w[i] = x;
-        mx = fmaxf(mx, x);
-    }
-    mx = warp_max(mx);
-    if (lane == 0) red[warp] = mx;
-    __syncthreads();
-    if (warp == 0) {
-        float m2 = lane < ATT_THREADS / 32 ? red[lane] : -INFINITY;
-        m2 = warp_max(m2);
-        if (lane == 0) bcast[0] = m2;
-    }
-    __syncthreads();
-    mx = bcast[0];
-    float sum = 0.f;
-    for (int i = tid; i < n; i += ATT_THREADS) {
-        const float e = __expf(w[i] - mx);
-        w[i] = e;
-        sum += e;
-    }
-    sum = warp_sum(sum);
-    __syncthreads();
-    if (lane == 0) red[warp] = sum;
-    __syncthreads();
-    if (warp == 0) {
-        float s2 = lane < ATT_THREADS / 32 ? red[lane] : 0.f;
-        s2 = warp_sum(s2);
-        if (lane == 0) bcast[1] = s2;
-    }
-    __syncthreads();
-    const float inv = 1.f / bcast[1];
-
-    SKV_PHASE(7);
-    // 4. out = sum_j w_j V[sel_j] / sum
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int j = grp; j < n; j += GROUPS) {
-        const uint4 vv = j == grp ? v_first : *reinterpret_cast<const uint4*>(vbase + (long long)SKV_INDEX(sel[j], p.T) * p.v_st);
-        const float wj = w[j];
-        const __half2* hv = reinterpret_cast<const __half2*>(&vv);
+    float inv;
+    if (sink + kk <= 64) {
+        // Few kept tokens (the usual decode case): every warp works the kept set out for itself -- lane l holds the
+        // weights of kept tokens l and l + 32 and hands them out by shuffle -- so that nothing is compacted in shared
+        // memory and no block-wide barrier stands between the selection and the gather.
+        const int tp0 = lane < kk ? top[lane] : 0x7fffffff, tp1 = lane + 32 < kk ? top[lane + 32] : 0x7fffffff;
+        const int c = __popc(__ballot_sync(0xffffffffu, tp0 < sink)) + __popc(__ballot_sync(0xffffffffu, tp1 < sink));
+        const int n = sink + kk - c;   // kept token j: position j for j < sink, top[c + j - sink] after that
+        constexpr int PASSES = (64 + GROUPS - 1) / GROUPS;   // value rows per thread
+        uint4 vv[PASSES];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(hv[i]);
-            acc[2 * i] = fmaf(wj, f.x, acc[2 * i]);
-            acc[2 * i + 1] = fmaf(wj, f.y, acc[2 * i + 1]);
+        for (int u = 0; u < PASSES; ++u) {   // (rows past the kept set: a clamped row, weighted zero below)
+            const int j = min(u * GROUPS + grp, n - 1);
+            const int pos = j < sink ? j : top[c + j - sink];
+            vv[u] = *reinterpret_cast<const uint4*>(vbase + (long long)SKV_INDEX(pos, p.T) * p.v_st);
+        }
+        float x[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int j = lane + 32 * r;
+            x[r] = -INFINITY;
+            if (j < n) x[r] = j < sink ? sc[j] : (p.cand_score ? top_sc[c + j - sink] : sc[SKV_INDEX(top[c + j - sink], p.T)]);
+        }
+        const float mxw = warp_max(fmaxf(x[0], x[1]));
+        const float e0 = lane < n ? __expf(x[0] - mxw) : 0.f, e1 = lane + 32 < n ? __expf(x[1] - mxw) : 0.f;
+        inv = 1.f / warp_sum(e0 + e1);
+        SKV_PHASE(7);
+#pragma unroll
+        for (int u = 0; u < PASSES; ++u) {
+            const int j = u * GROUPS + grp;
+            const float w0 = __shfl_sync(0xffffffffu, e0, j & 31), w1 = __shfl_sync(0xffffffffu, e1, j & 31);
+            const float wj = j < n ? ((j & 32) ? w1 : w0) : 0.f;
+            const __half2* hv = reinterpret_cast<const __half2*>(&vv[u]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(hv[i]);
+                acc[2 * i] = fmaf(wj, f.x, acc[2 * i]);
+                acc[2 * i + 1] = fmaf(wj, f.y, acc[2 * i + 1]);
+            }
+        }
+    } else {
+        // 2. kept set = sink prefix U {top positions >= sink}: drop the leading top entries that fall inside the prefix
+        int c = 0;  // top is ascending, so entries < sink form a prefix of length c
+        {
+            int lo = 0, hi = kk;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (top[mid] < sink) lo = mid + 1; else hi = mid;
+            }
+            c = lo;
+        }
+        const int n = sink + kk - c;
+        __syncthreads();
+        // compact in place: positions [0, sink) then top[c ..)
+        for (int base = 0; base < kk - c; base += ATT_THREADS) {
+            const int i = base + tid;
+            const int v = i < kk - c ? top[c + i] : 0;
+            const float vs = (p.cand_score && i < kk - c) ? top_sc[c + i] : 0.f;
+            __syncthreads();
+            if (i < kk - c) {
+                sel[sink + i] = v;
+                if (p.cand_score) w[sink + i] = vs;
+            }
+        }
+        for (int i = tid; i < sink; i += ATT_THREADS) sel[i] = i;
+        __syncthreads();
+
+        // the first pass of value rows: their addresses are known now, their weights only after the softmax
+        uint4 v_first = make_uint4(0u, 0u, 0u, 0u);
+        if (grp < n) v_first = *reinterpret_cast<const uint4*>(vbase + (long long)SKV_INDEX(sel[grp], p.T) * p.v_st);
+
+        SKV_PHASE(6);
+        // 3. softmax over the kept scores
+        float mx = -INFINITY;
+        for (int i = tid; i < n; i += ATT_THREADS) {
+            const float x = i < sink ? (i == tid ? sink_sc0 : sc[i]) : (p.cand_score ? w[i] : sc[SKV_INDEX(sel[i], p.T)]);
+            w[i] = x;
+            mx = fmaxf(mx, x);
+        }
+        mx = warp_max(mx);
+        if (lane == 0) red[warp] = mx;
+        __syncthreads();
+        if (warp == 0) {
+            float m2 = lane < ATT_THREADS / 32 ? red[lane] : -INFINITY;
+            m2 = warp_max(m2);
+            if (lane == 0) bcast[0] = m2;
+        }
+        __syncthreads();
+        mx = bcast[0];
+        float sum = 0.f;
+        for (int i = tid; i < n; i += ATT_THREADS) {
+            const float e = __expf(w[i] - mx);
+            w[i] = e;
+            sum += e;
+        }
+        sum = warp_sum(sum);
+        __syncthreads();
+        if (lane == 0) red[warp] = sum;
+        __syncthreads();
+        if (warp == 0) {
+            float s2 = lane < ATT_THREADS / 32 ? red[lane] : 0.f;
+            s2 = warp_sum(s2);
+            if (lane == 0) bcast[1] = s2;
+        }
+        __syncthreads();
+        inv = 1.f / bcast[1];
+
+        SKV_PHASE(7);
+        // 4. out = sum_j w_j V[sel_j] / sum
+        for (int j = grp; j < n; j += GROUPS) {
+            const uint4 vv = j == grp ? v_first : *reinterpret_cast<const uint4*>(vbase + (long long)SKV_INDEX(sel[j], p.T) * p.v_st);
+            const float wj = w[j];
+            const __half2* hv = reinterpret_cast<const __half2*>(&vv);
+    #pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(hv[i]);
+                acc[2 * i] = fmaf(wj, f.x, acc[2 * i]);
+                acc[2 * i + 1] = fmaf(wj, f.y, acc[2 * i + 1]);
+            }
         }
     }
     __syncthreads();
