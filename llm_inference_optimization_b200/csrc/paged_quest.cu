@@ -759,6 +759,7 @@ quest_select_attend_kernel(const __grid_constant__ CUtensorMap tmM, const Attend
     }
     report_bad_page(bad_page, p.status);
     SKV_PHASE(7);
+    SKV_PHASE_LAST_END();
 }
 
 }  // namespace quest

@@ -241,8 +241,18 @@ static __device__ unsigned long long skv_phase_ts[32];   // one copy per transla
             skv_phase_ts[i] = t_;                                                      \
         }                                                                              \
     } while (0)
+// the latest end of any CTA (slot 31; never reset: later launches end later)
+#define SKV_PHASE_LAST_END()                                                           \
+    do {                                                                               \
+        if (threadIdx.x == 0) {                                                        \
+            unsigned long long t_;                                                     \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                     \
+            atomicMax(&skv_phase_ts[31], t_);                                          \
+        }                                                                              \
+    } while (0)
 #else
 #define SKV_PHASE(i) do {} while (0)
+#define SKV_PHASE_LAST_END() do {} while (0)
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
