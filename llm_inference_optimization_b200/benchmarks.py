@@ -35,6 +35,8 @@ def hbm_peak() -> tuple[float, str]:
 
 
 class Timer:
+    last_mean = None   # mean of the most recent measurement, picked up (and cleared) by emit()
+
     def __init__(self, dev, iters):
         self.dev, self.iters = dev, iters
         self.flush_buf = torch.zeros(128 << 20, dtype=torch.int32, device=dev)
@@ -53,11 +55,17 @@ class Timer:
             e1.record()
             torch.cuda.synchronize(self.dev)
             times.append(e0.elapsed_time(e1) * 1e3)
+        # CUDA event pairs around one short call resolve about 2 us here (the medians of the short ops land on a
+        # 2.05 us grid); the mean over the iterations is kept beside the median for telling such ops apart
+        Timer.last_mean = statistics.fmean(times)
         return statistics.median(times), min(times)
 
 
 def emit(name, cfg, us, us_min, nbytes, peak, peak_kind, **extra):
     gbs = nbytes / us / 1e3
+    if Timer.last_mean is not None:
+        extra = {"us_mean": round(Timer.last_mean, 2), **extra}
+        Timer.last_mean = None
     line = {"workload": name, **cfg, "us": round(us, 2), "us_min": round(us_min, 2), "algorithmic_MB": round(nbytes / 1e6, 2),
             "GBps": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3), "peak_GBps": peak, "peak_source": peak_kind, **extra}
     print(json.dumps(line), flush=True)
