@@ -9,11 +9,12 @@
 // with an exact top-k instead of the reference kernel's lossy per-thread heaps.
 //
 // Two launches:
-//   1. token_scores_kernel   -- streams K once (HBM-bound), 16-byte loads, one
-//      row of D channels per D/8 lanes, scores to an fp32 scratch [rows, T];
-//   2. token_select_attend_kernel -- one 1024-thread CTA per (b, h, query):
-//      radix-select top-k over the scratch (L2 resident), softmax, gather of the
-//      kept V rows.
+//   1. token_scores_mma_kernel (decode shape, D = 64 / 128: K by TMA through a ring, scores on the
+//      tensor cores) or token_scores_kernel (16-byte loads, one row of D channels per D/8 lanes)
+//      -- streams K once (HBM-bound), scores to an fp32 scratch [rows, T]; for long rows every
+//      CTA also leaves the top-k of its chunk as candidates;
+//   2. token_select_attend_kernel -- one 1024-thread CTA per (b, h, query): exact top-k over the
+//      candidates or the scratch (L2 resident; skv_select.cuh), softmax, gather of the kept V rows.
 #include "skv_common.cuh"
 #include "skv_select.cuh"
 #include "skv_tmap.cuh"
