@@ -74,6 +74,23 @@ constexpr float V4_BIAS = 1032.f;
 constexpr int Q8_PRODUCERS = 4;                            // producer warps: each issues one share of every stage
 __host__ __device__ constexpr int q8_threads(int ng) { return (ng * CONSUMER_WARPS + Q8_PRODUCERS) * 32; }
 
+#ifdef SKV_PROFILE_PHASES
+static __device__ unsigned long long skv_cta_ts[5][1024];
+#define SKV_CTA_STAMP(slot)                                                                              \
+    do {                                                                                                 \
+        const unsigned lin_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);            \
+        if ((threadIdx.x & 31) == 0 && lin_ < 1024) {                                                    \
+            unsigned long long t_;                                                                       \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                       \
+            if ((slot) == 0 || (slot) == 1) atomicMin(&skv_cta_ts[slot][lin_], t_);                      \
+            else atomicMax(&skv_cta_ts[slot][lin_], t_);                                                 \
+            if ((slot) == 0) { unsigned sm_; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_)); skv_cta_ts[4][lin_] = sm_; } \
+        }                                                                                                \
+    } while (0)
+#else
+#define SKV_CTA_STAMP(slot) do {} while (0)
+#endif
+
 struct Q8Params {
     const __half* q;
     __half* out;
@@ -191,6 +208,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const int h = blockIdx.x;
     int split = blockIdx.y, b = blockIdx.z;
     SKV_PHASE(0);
+    SKV_CTA_STAMP(0);
 
     // Ordered like any other kernel unless the caller declared the cache static (see the fp16 kernel).
     if (!p.early_kv) pdl_wait_prior_grids();
@@ -407,7 +425,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             if (lane == 0) atomicOr(p.status, SKV_DEV_TIMEOUT);
             break;
         }
-        if (it == group) SKV_PHASE(3);
+        if (it == group) { SKV_PHASE(3); SKV_CTA_STAMP(1); }
         const int tok0 = t_begin + it * TILE + wtok;
         if (tok0 < t_end) {
             const uint32_t kbase = ring + s * STAGE_BYTES + k_off + ld_row_off;   // this lane's K row
@@ -571,6 +589,7 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     }
 
     SKV_PHASE(4);
+    SKV_CTA_STAMP(2);
     if (V4) {   // rows g hold u + 1024 = q + 1032, rows g+8 hold 16 u + 1024 = 16 (q + 72)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
@@ -626,8 +645,10 @@ gqa_decode_q8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     ea.out_bf16 = p.out_bf16 != 0;
     ea.Hkv = p.Hkv; ea.G = G; ea.num_splits = p.num_splits; ea.o_stride_b = p.o_stride_b; ea.o_stride_h = p.o_stride_h;
     SKV_PHASE(5);
-    merge_and_combine<D, Q8_WARPS>(ea, smem, last_flag, b, h, split, n_splits, 1.f / P_BOOST);
+    merge_and_combine<D, Q8_WARPS, (NG == 1 ? 8 : 20)>(ea, smem, last_flag, b, h, split, n_splits, 1.f / P_BOOST);   // (the two-CTAs-per-SM variants have 128 registers)
     SKV_PHASE(6);
+    SKV_PHASE_LAST_END();
+    SKV_CTA_STAMP(3);
 }
 
 template <int KVT, int NT, int NG, bool V4 = false>
@@ -656,6 +677,10 @@ extern "C" {
 #ifdef SKV_PROFILE_PHASES
 int skv_debug_phase_ts_q8(unsigned long long* out) {
     return cudaMemcpyFromSymbol(out, skv_phase_ts, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : -4;
+}
+// per CTA (linear id < 1024): first instruction, first tile consumed, last tile consumed, exit; and the SM it ran on
+int skv_debug_cta_ts_q8(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, skv::gqa::skv_cta_ts, sizeof(unsigned long long) * 5 * 1024) == cudaSuccess ? 0 : -4;
 }
 #endif
 

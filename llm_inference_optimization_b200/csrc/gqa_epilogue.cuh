@@ -185,7 +185,7 @@ __device__ __forceinline__ uint16_t out_bits(float x, bool bf16) {
 // warp has stored its state at `smem`: O [NW][MAX_GROUP][D], running max
 // [NW][MAX_GROUP] (exp2 domain), running sum [NW][MAX_GROUP], and after a named
 // barrier.  `out_scale` multiplies the un-normalised output (1 for fp16 KV).
-template <int D, int NW = CONSUMER_WARPS>
+template <int D, int NW = CONSUMER_WARPS, int CB = 24>   // CB: partial rows in flight per lane in the last CTA's combine
 __device__ __forceinline__ void merge_and_combine(const EpilogueArgs& p, uint8_t* smem, int* last_flag, int b, int h,
                                                   int split, int n_splits, float out_scale) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -242,18 +242,47 @@ __device__ __forceinline__ void merge_and_combine(const EpilogueArgs& p, uint8_t
     if (!*last_flag) return;
     __threadfence();
 
+    // One warp per query head.  The partial rows do not depend on the weights, so the first CB of them are on their
+    // way before the (max, sum) pairs are even read, and those pairs are read once and kept in registers: a combine
+    // of up to CB splits costs one round trip to L2 where a weights-first order costs three or more, and it sits on
+    // the critical path of every split launch.  Splits past the end read a real (clamped) row with weight zero, so
+    // no load waits on a condition.  The sums run over the splits in ascending order, as before.
     const long long rbase = bh * p.num_splits * G;
     float* wrow = wts + warp * MAX_SPLITS;
+    constexpr int MLR = 4;    // (max, sum) pairs per lane kept in registers: splits lane, lane + 32, ...
+    const bool ol = lane < D / 4;
+    const long long sstride = (long long)G * D;
     for (int r = warp; r < G; r += NW) {
+        const float* src = p.partial_o + (rbase + r) * D + (ol ? lane * 4 : 0);
+        float4 vo[CB];
+#pragma unroll
+        for (int j = 0; j < CB; ++j) vo[j] = __ldcg(reinterpret_cast<const float4*>(src + (long long)min(j, n_splits - 1) * sstride));
+        float2 mlv[MLR];
         float mx = -INFINITY;
-        for (int s = lane; s < n_splits; s += 32) mx = fmaxf(mx, __ldcg(&p.partial_ml[(rbase + (long long)s * G + r) * 2]));
+#pragma unroll
+        for (int i = 0; i < MLR; ++i) {
+            const int sidx = lane + 32 * i;
+            mlv[i] = __ldcg(reinterpret_cast<const float2*>(&p.partial_ml[(rbase + (long long)min(sidx, n_splits - 1) * G + r) * 2]));
+            if (sidx >= n_splits) mlv[i] = make_float2(-INFINITY, 0.f);
+            mx = fmaxf(mx, mlv[i].x);
+        }
+        for (int sidx = lane + 32 * MLR; sidx < n_splits; sidx += 32) mx = fmaxf(mx, __ldcg(&p.partial_ml[(rbase + (long long)sidx * G + r) * 2]));
         mx = warp_max(mx);
         float Ls = 0.f;
-        for (int s = lane; s < n_splits; s += 32) {
-            const float2 v = __ldcg(reinterpret_cast<const float2*>(&p.partial_ml[(rbase + (long long)s * G + r) * 2]));
+#pragma unroll
+        for (int i = 0; i < MLR; ++i) {
+            const int sidx = lane + 32 * i;
+            if (sidx < n_splits) {
+                const float w = (mlv[i].x == -INFINITY) ? 0.f : fast_exp2(mlv[i].x - mx);
+                Ls += mlv[i].y * w;
+                wrow[sidx] = w;
+            }
+        }
+        for (int sidx = lane + 32 * MLR; sidx < n_splits; sidx += 32) {
+            const float2 v = __ldcg(reinterpret_cast<const float2*>(&p.partial_ml[(rbase + (long long)sidx * G + r) * 2]));
             const float w = (v.x == -INFINITY) ? 0.f : fast_exp2(v.x - mx);
             Ls += v.y * w;
-            wrow[s] = w;
+            wrow[sidx] = w;
         }
         Ls = warp_sum(Ls);
         if (p.ml_final && lane == 0) {
@@ -261,16 +290,19 @@ __device__ __forceinline__ void merge_and_combine(const EpilogueArgs& p, uint8_t
             p.ml_final[(bh * G + r) * 2 + 1] = Ls;
         }
         __syncwarp();
-        if (lane < D / 4) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            const float* src = p.partial_o + (rbase + r) * D + lane * 4;
-            const long long sstride = (long long)G * D;
-#pragma unroll 8
-            for (int s = 0; s < n_splits; ++s) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + s * sstride));
-                const float w = wrow[s];
-                acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < n_splits; s0 += CB) {
+            if (s0) {
+#pragma unroll
+                for (int j = 0; j < CB; ++j) vo[j] = __ldcg(reinterpret_cast<const float4*>(src + (long long)min(s0 + j, n_splits - 1) * sstride));
             }
+#pragma unroll
+            for (int j = 0; j < CB; ++j) {
+                const float w = s0 + j < n_splits ? wrow[s0 + j] : 0.f;
+                acc.x += vo[j].x * w; acc.y += vo[j].y * w; acc.z += vo[j].z * w; acc.w += vo[j].w * w;
+            }
+        }
+        if (ol) {
             const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
             uint2 pk;
             pk.x = (uint32_t)out_bits(acc.x * inv, p.out_bf16) | ((uint32_t)out_bits(acc.y * inv, p.out_bf16) << 16);

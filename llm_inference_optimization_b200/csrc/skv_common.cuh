@@ -244,7 +244,7 @@ static __device__ unsigned long long skv_phase_ts[32];   // one copy per transla
 // the latest end of any CTA (slot 31; never reset: later launches end later)
 #define SKV_PHASE_LAST_END()                                                           \
     do {                                                                               \
-        if (threadIdx.x == 0) {                                                        \
+        if ((threadIdx.x & 31) == 0) {                                                 \
             unsigned long long t_;                                                     \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                     \
             atomicMax(&skv_phase_ts[31], t_);                                          \
