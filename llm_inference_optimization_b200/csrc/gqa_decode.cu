@@ -381,6 +381,7 @@ gqa_decode_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     SKV_PHASE(5);
     merge_and_combine<D>(ea, smem, last_flag, b, h, split, n_splits, 1.f);
     SKV_PHASE(9);
+    SKV_PHASE_LAST_END();
 }
 
 // Attention mass of every cached token, summed over the query heads of its group and ADDED to `mass`:

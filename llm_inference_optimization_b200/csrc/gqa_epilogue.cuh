@@ -354,29 +354,29 @@ __device__ __forceinline__ void cluster_combine_rank0(const EpilogueArgs& p, uin
     const long long bh = (long long)b * p.Hkv + h;
     for (int i4 = threadIdx.x; i4 < G * D / 4; i4 += (NW * 32)) {
         const int r = (i4 * 4) / D, d = i4 * 4 - r * D;
-        float ms[MAX_CLUSTER_SPLITS], ls[MAX_CLUSTER_SPLITS];
+        // every remote load is issued before the first use (ranks past the last split read a real CTA's area, clamped,
+        // and weigh zero): one trip through the cluster's shared memory instead of one per dependent step
+        float2 mlv[MAX_CLUSTER_SPLITS];
+        float4 ov[MAX_CLUSTER_SPLITS];
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER_SPLITS; ++s) {
+            const int rank = min(s, n_splits - 1);
+            mlv[s] = ld_cluster_f2(cluster_map(cml + r * 8, rank));
+            ov[s] = ld_cluster_f4(cluster_map(co + i4 * 16, rank));
+        }
         float mx = -INFINITY;
 #pragma unroll
         for (int s = 0; s < MAX_CLUSTER_SPLITS; ++s) {
-            ms[s] = -INFINITY;
-            ls[s] = 0.f;
-            if (s < n_splits) {
-                const float2 v = ld_cluster_f2(cluster_map(cml + r * 8, s));
-                ms[s] = v.x;
-                ls[s] = v.y;
-                mx = fmaxf(mx, v.x);
-            }
+            if (s >= n_splits) mlv[s] = make_float2(-INFINITY, 0.f);
+            mx = fmaxf(mx, mlv[s].x);
         }
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         float Ls = 0.f;
 #pragma unroll
         for (int s = 0; s < MAX_CLUSTER_SPLITS; ++s) {   // in split order: the sum does not depend on timing
-            if (s < n_splits) {
-                const float w = (ms[s] == -INFINITY) ? 0.f : fast_exp2(ms[s] - mx);
-                const float4 v = ld_cluster_f4(cluster_map(co + i4 * 16, s));
-                Ls += ls[s] * w;
-                acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
-            }
+            const float w = (mlv[s].x == -INFINITY) ? 0.f : fast_exp2(mlv[s].x - mx);
+            Ls += mlv[s].y * w;
+            acc.x += ov[s].x * w; acc.y += ov[s].y * w; acc.z += ov[s].z * w; acc.w += ov[s].w * w;
         }
         if (p.ml_final && d == 0) {
             p.ml_final[(bh * G + r) * 2] = mx;
