@@ -153,11 +153,16 @@ __device__ __forceinline__ void cluster_select_row(const SelectParams& p, cooper
     const int s0 = min(e1, e0 + warp * seg), s1 = min(e1, s0 + seg);
     uint32_t key[KR];
     uint32_t have = 0;                    // bit j: element j exists
+    {
+        float raw[KR];   // unconditional loads at clamped positions: all in flight together
 #pragma unroll
-    for (int j = 0; j < KR; ++j) {
-        const int i = s0 + j * 32 + lane;
-        key[j] = 0u;
-        if (i < s1) { key[j] = score_key(sc[i]); have |= 1u << j; }
+        for (int j = 0; j < KR; ++j) raw[j] = sc[min(s0 + j * 32 + lane, p.T - 1)];
+#pragma unroll
+        for (int j = 0; j < KR; ++j) {
+            const int i = s0 + j * 32 + lane;
+            key[j] = 0u;
+            if (i < s1) { key[j] = score_key(raw[j]); have |= 1u << j; }
+        }
     }
 
     SKV_PHASE(1);
