@@ -141,8 +141,9 @@ template <int D, int MMA_STAGES>
 __host__ __device__ constexpr size_t mma_ring_bytes() { return (size_t)MMA_STAGES * mma_stage_bytes<D>() + 64; }
 
 // MMA_STAGES = 2 with three CTAs per SM for chunks of up to 2 K tokens (the per-chunk candidate selection of one CTA
-// then overlaps two others' streaming: 64K 122 -> 116 us), 3 with two CTAs per SM for longer chunks (128K: 189 against
-// 196 us with the short ring).
+// then overlaps two others' streaming), 3 with two CTAs per SM for longer chunks; the host takes the long ring and
+// chunks of up to 3.5 K tokens from 64K x 32 rows up (measured: 64K 103 against 107 us, 128K 189 against 196 us with
+// the short ring).
 template <int D, int MMA_STAGES>
 __global__ void __launch_bounds__(SCORE_THREADS, MMA_STAGES == 2 ? 3 : 2)
 token_scores_mma_kernel(const __grid_constant__ CUtensorMap tmK, const ScoreParams p, const KvMapPos pos,
